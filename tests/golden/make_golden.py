@@ -1,0 +1,190 @@
+"""Generate the golden vectors under tests/golden/ by running the REFERENCE's own
+Python code (PyTorch CPU kernels) on seeded inputs.
+
+    python tests/golden/make_golden.py [/path/to/reference/checkout]
+
+The reference checkout is only needed to (re)generate the files; the tests read
+the committed .npz files and never import the reference.  Inputs are stored
+next to the outputs, so the vectors do not depend on a torch RNG stream.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+sys.dont_write_bytecode = True
+sys.path.insert(0, REF)
+sys.path.insert(0, ROOT)
+
+import knapsack_solver as KS                                   # noqa: E402  (reference)
+from obkv_accel import packing as P                            # noqa: E402  (reference)
+from obkv_accel import trizone_decompress as TD                # noqa: E402  (reference)
+from obkv_accel.triton_k_kernel import k_mixed_qk_dot_ref      # noqa: E402  (reference)
+
+from rdkv_b200 import synth                                     # noqa: E402
+
+LAYER_FIELDS = [
+    "K_2bit", "K_4bit", "K_8bit", "K_ch_scale", "K_ch_zp", "K_ch_sort_idx", "K_ch_perm_padded_idx",
+    "V_2bit", "V_4bit", "V_8bit", "V_scale", "V_zp", "sort_idx",
+    "seg_bounds_per_head", "T_eff_per_head", "softmax_mask",
+    "K_ch_sort_idx_per_head", "K_ch_perm_padded_idx_per_head", "K_ch_seg_bounds_per_head",
+    "K_ch_perm_padded_idx_for_Q", "T_eff_k_per_head", "n_v16_per_head",
+]
+LAYER_SCALARS = ["K_ch_seg_bounds", "seg_bounds", "T_eff", "T_eff_k", "n_v16"]
+
+
+def npy(t):
+    return None if t is None else t.detach().cpu().numpy()
+
+
+def layer_to_dict(pl, prefix=""):
+    out = {}
+    for f in LAYER_FIELDS:
+        v = getattr(pl, f)
+        if v is not None:
+            out[prefix + f] = npy(v)
+    for f in LAYER_SCALARS:
+        out[prefix + f] = np.asarray(getattr(pl, f), dtype=np.int64)
+    return out
+
+
+def ref_pack_kv(K, V, v_bits, k_bits, g):
+    """The reference's per-layer composite (obkv_fast.py:1098-1166), per-head deferred-K path."""
+    H_kv, D = K.shape[1], K.shape[3]
+    layers, v16s = [], []
+    for h in range(H_kv):
+        kept = (v_bits[h] > 0).nonzero(as_tuple=True)[0]
+        if kept.numel() == 0:
+            layers.append(P._empty_packed_layer(1, D, K.device, K.dtype))
+            v16s.append(None)
+            continue
+        kb = v_bits[h][kept]
+        counts = tuple(int((kb == b).sum()) for b in (2, 4, 8))
+        layer, _, v16 = P.build_packed_layer(
+            K[:, h:h + 1].index_select(2, kept).contiguous(),
+            V[:, h:h + 1].index_select(2, kept).contiguous(),
+            kb, k_bits[h], v_segment_counts=counts, defer_k_for_per_head_stack=True)
+        layers.append(layer)
+        v16s.append(v16)
+    return P._pad_and_stack_per_head_layers(
+        layers, v16s, H_q=H_kv * g, gqa_factor=g, head_dim=D, device=K.device, dtype=K.dtype,
+        k_bits_per_head=k_bits)
+
+
+def ref_attend(q, pl, new_v_only, D):
+    """Reference dequantise-then-attend (trizone_decompress.py:185 + fp32 softmax attention)."""
+    cache = P.TriZoneCache(packed=(pl,), new_v_only=[new_v_only], new_both_k=[None], new_both_v=[None],
+                           original_seq_len=0)
+    (K_hat, V_hat), = TD.unpack_trizone_to_past_kv(cache, head_dim=D)
+    g = q.shape[0] // K_hat.shape[1]
+    Kx = K_hat[0].float().repeat_interleave(g, 0)
+    Vx = V_hat[0].float().repeat_interleave(g, 0)
+    s = torch.einsum("hd,htd->ht", q.float(), Kx) / (D ** 0.5) + pl.softmax_mask
+    w = torch.softmax(s, dim=-1)
+    return torch.einsum("ht,htd->hd", w, Vx), K_hat, V_hat
+
+
+def case_unit_tests():
+    """The two packing pins of the reference's own unit tests (tests/test_blockwise_rdkv.py:119-228)."""
+    out = {}
+    torch.manual_seed(1)
+    keys = torch.randn(1, 1, 7, 8, dtype=torch.float16)
+    k_bits = torch.tensor([0, 2, 4, 8, 16, 2, 4, 8])
+    values = torch.randn(1, 1, 6, 8, dtype=torch.float16)
+    v_bits = torch.tensor([2, 4, 8, 2, 8, 4])
+    rk = P.pack_k_mixed(keys.clone(), k_bits)
+    rv = P.pack_v_segments(values.clone(), v_bits)
+    out.update(t1_keys=npy(keys), t1_k_bits=npy(k_bits), t1_values=npy(values), t1_v_bits=npy(v_bits))
+    for name, t in zip(["K_2bit", "K_4bit", "K_8bit", "K_ch_scale", "K_ch_zp", "K_ch_sort_idx",
+                        "K_ch_perm_padded_idx"], rk[:7]):
+        out["t1_" + name] = npy(t)
+    out["t1_K_ch_seg_bounds"] = np.asarray(rk[7], np.int64)
+    for name, t in zip(["V_2bit", "V_4bit", "V_8bit", "V_scale", "V_zp", "sort_idx"], rv[:6]):
+        out["t1_" + name] = npy(t)
+    out["t1_seg_bounds"] = np.asarray(rv[6], np.int64)
+
+    torch.manual_seed(11)
+    keys = torch.randn(1, 2, 7, 8, dtype=torch.float16)
+    values = torch.randn_like(keys)
+    v_bits = torch.tensor([[2, 4, 8, 16, 0, 2, 4], [4, 16, 2, 8, 0, 4, 2]])
+    k_bits = torch.tensor([[2, 4, 8, 0, 16, 2, 4, 8], [4, 2, 0, 8, 16, 4, 2, 8]])
+    pl, nv = ref_pack_kv(keys, values, v_bits, k_bits, 2)
+    out.update(t2_keys=npy(keys), t2_values=npy(values), t2_v_bits=npy(v_bits), t2_k_bits=npy(k_bits),
+               t2_new_v_only=npy(nv))
+    out.update(layer_to_dict(pl, "t2_"))
+    return out
+
+
+def case_layer(tag, H_kv, g, T, N, seed, per_head_N=None, k_mix=((8, 16), (4, 24), (2, 24))):
+    K, V = synth.make_kv(H_kv, T, seed=seed)
+    v_bits = synth.make_v_bits(H_kv, T, N, seed=seed, per_head_N=per_head_N)
+    k_bits = synth.make_k_bits(H_kv, seed=seed, mix=k_mix)
+    q = synth.make_q(H_kv * g, seed=seed + 1)
+    pl, nv = ref_pack_kv(K, V, v_bits, k_bits, g)
+    att, _, _ = ref_attend(q, pl, nv, 128)
+    scores = k_mixed_qk_dot_ref(q, pl, pl.T_eff_k)
+    out = {f"{tag}_K": npy(K), f"{tag}_V": npy(V), f"{tag}_v_bits": npy(v_bits), f"{tag}_k_bits": npy(k_bits),
+           f"{tag}_q": npy(q), f"{tag}_attn_out": npy(att), f"{tag}_k_scores": npy(scores),
+           f"{tag}_g": np.asarray(g)}
+    if nv is not None:
+        out[f"{tag}_new_v_only"] = npy(nv)
+    out.update(layer_to_dict(pl, tag + "_"))
+    return out
+
+
+def case_knapsack():
+    out = {}
+    eps = synth.ALLOC_EPSILON
+    cases = {
+        "v": dict(scores=synth.make_scores(6, 2048, seed=2000), budget=2.0, max_iters=60),
+        "vrow": dict(scores=synth.make_scores(5, 1024, seed=2001),
+                     budget=torch.tensor([0.5, 1.0, 2.0, 6.0, 20.0]), max_iters=60),
+        "k": dict(scores=synth.make_scores(8, 128, seed=2002), budget=2.64, max_iters=60),
+        "kdef": dict(scores=synth.make_scores(4, 128, seed=2003), budget=4.0, max_iters=64),
+        "zeros": dict(scores=torch.zeros(2, 64), budget=2.0, max_iters=60),
+        "nozero": dict(scores=synth.make_scores(3, 256, seed=2004), budget=1.0, max_iters=12,
+                       bit_options=torch.tensor([2., 4., 8.])),
+        "tiny": dict(scores=synth.make_scores(3, 7, seed=2005), budget=3.0, max_iters=60),
+        "tight": dict(scores=synth.make_scores(2, 4096, seed=2006), budget=2.0, max_iters=60, tol=1e-5),
+    }
+    for name, c in cases.items():
+        kw = dict(epsilon=eps, max_iters=c["max_iters"], tol=c.get("tol", 0.01))
+        if "bit_options" in c:
+            kw["bit_options"] = c["bit_options"]
+        res = KS.knapsack_bit_allocation_batched(c["scores"], c["budget"], **kw)
+        out[f"{name}_scores"] = npy(c["scores"])
+        out[f"{name}_budget"] = np.asarray(c["budget"], dtype=np.float32)
+        out[f"{name}_max_iters"] = np.asarray(c["max_iters"])
+        out[f"{name}_tol"] = np.asarray(c.get("tol", 0.01), dtype=np.float64)
+        out[f"{name}_bit_options"] = npy(c.get("bit_options", torch.tensor([0., 2., 4., 8., 16.])))
+        out[f"{name}_bits"] = npy(res)
+    # default-epsilon call, as the reference's smoke test makes it
+    s = synth.make_scores(2, 512, seed=2007, sigma=1.0)
+    out["defeps_scores"] = npy(s)
+    out["defeps_bits"] = npy(KS.knapsack_bit_allocation_batched(s, 2.0))
+    return out
+
+
+def main():
+    torch.set_num_threads(os.cpu_count() or 1)
+    np.savez_compressed(os.path.join(HERE, "packing_unit.npz"), **case_unit_tests())
+    layers = {}
+    layers.update(case_layer("even", H_kv=2, g=4, T=384, N=128, seed=synth.unit_seed(0, 0, 1)))
+    layers.update(case_layer("ragged", H_kv=3, g=2, T=320, N=96, seed=synth.unit_seed(0, 1, 2),
+                             per_head_N=[96, 84, 72], k_mix=((8, 9), (4, 21), (2, 30))))
+    layers.update(case_layer("gqa8", H_kv=1, g=8, T=200, N=64, seed=synth.unit_seed(4, 0, 0),
+                             k_mix=((8, 128),)))
+    np.savez_compressed(os.path.join(HERE, "layers.npz"), **layers)
+    np.savez_compressed(os.path.join(HERE, "knapsack.npz"), **case_knapsack())
+    for f in ("packing_unit.npz", "layers.npz", "knapsack.npz"):
+        print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
+
+
+if __name__ == "__main__":
+    main()

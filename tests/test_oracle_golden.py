@@ -1,0 +1,100 @@
+"""The numpy oracle against vectors produced by the reference's own code (CPU only)."""
+import numpy as np
+import pytest
+
+from conftest import assert_layer_equal, sub
+from oracle import ref_attention as RA
+from oracle import ref_knapsack as RK
+from oracle import ref_packing as RP
+
+
+def test_reference_unit_case_k_and_v(golden_unit):
+    """Shapes and inputs of the reference's segment-count packing test (T=6/7, D=8, seed 1)."""
+    g = sub(golden_unit, "t1")
+    k = RP.pack_k_mixed(g["keys"], g["k_bits"])
+    for f in ["K_2bit", "K_4bit", "K_8bit", "K_ch_scale", "K_ch_zp", "K_ch_sort_idx", "K_ch_perm_padded_idx"]:
+        assert np.array_equal(k[f], g[f]), f
+    assert tuple(g["K_ch_seg_bounds"]) == k["K_ch_seg_bounds"] == (2, 2, 3)
+    v = RP.pack_v_segments(g["values"], g["v_bits"])
+    for f in ["V_2bit", "V_4bit", "V_8bit", "V_scale", "V_zp", "sort_idx"]:
+        assert np.array_equal(v[f], g[f]), f
+    assert tuple(g["seg_bounds"]) == v["seg_bounds"] == (2, 2, 2)
+
+
+def test_reference_unit_case_deferred_k_stack(golden_unit):
+    """Ragged heads with every bit class {0,2,4,8,16} (reference test, seed 11, D=8)."""
+    g = sub(golden_unit, "t2")
+    layer, nv = RP.pack_kv(g["keys"], g["values"], g["v_bits"], g["k_bits"], 2)
+    assert_layer_equal(layer, g, "t2.")
+    assert np.array_equal(nv, g["new_v_only"])
+
+
+@pytest.mark.parametrize("tag", ["even", "ragged", "gqa8"])
+def test_pack_kv_matches_reference(golden_layers, tag):
+    g = sub(golden_layers, tag)
+    layer, nv = RP.pack_kv(g["K"], g["V"], g["v_bits"], g["k_bits"], int(g["g"]))
+    assert_layer_equal(layer, g, tag + ".")
+    if "new_v_only" in g:
+        assert np.array_equal(nv, g["new_v_only"])
+    else:
+        assert nv is None
+
+
+@pytest.mark.parametrize("tag", ["even", "ragged", "gqa8"])
+def test_attention_matches_reference(golden_layers, tag):
+    g = sub(golden_layers, tag)
+    layer, nv = RP.pack_kv(g["K"], g["V"], g["v_bits"], g["k_bits"], int(g["g"]))
+    out, _, _ = RA.decode_attention(g["q"], layer, nv)
+    np.testing.assert_allclose(out, g["attn_out"], rtol=1e-5, atol=2e-6)
+    s = RA.k_scores(g["q"], layer, layer["T_eff_k"])
+    np.testing.assert_allclose(s, g["k_scores"], rtol=1e-5, atol=2e-6)
+
+
+def test_two_stage_equals_fused(golden_layers):
+    """scores -> masked softmax -> weighted sum reproduces the fused oracle."""
+    g = sub(golden_layers, "ragged")
+    layer, nv = RP.pack_kv(g["K"], g["V"], g["v_bits"], g["k_bits"], int(g["g"]))
+    s = RA.k_scores(g["q"], layer, layer["T_eff_k"]) + layer["softmax_mask"]
+    w = np.exp(s - s.max(axis=1, keepdims=True))
+    w /= w.sum(axis=1, keepdims=True)
+    out = RA.v_weighted_sum(w.astype(np.float32), layer, nv)
+    np.testing.assert_allclose(out, g["attn_out"], rtol=1e-5, atol=2e-6)
+
+
+def test_lse_combine_of_halves(golden_layers):
+    g = sub(golden_layers, "even")
+    layer, nv = RP.pack_kv(g["K"], g["V"], g["v_bits"], g["k_bits"], int(g["g"]))
+    full, _, _ = RA.decode_attention(g["q"], layer, nv)
+    # split the stripe in two by masking halves
+    T_k = layer["T_eff_k"]
+    parts = []
+    for lo, hi in ((0, T_k // 3), (T_k // 3, T_k)):
+        half = dict(layer)
+        m = layer["softmax_mask"].copy()
+        m[:, :lo] = -np.inf
+        m[:, hi:] = -np.inf
+        half["softmax_mask"] = m
+        o, mm, ll = RA.decode_attention(g["q"], half, nv)
+        parts.append((mm, ll, o * ll[:, None]))
+    out, _, _ = RA.lse_combine(np.stack([p[0] for p in parts]), np.stack([p[1] for p in parts]),
+                               np.stack([p[2] for p in parts]))
+    np.testing.assert_allclose(out, full, rtol=1e-5, atol=2e-6)
+
+
+KNAP_CASES = ["v", "vrow", "k", "kdef", "zeros", "nozero", "tiny", "tight"]
+
+
+@pytest.mark.parametrize("name", KNAP_CASES)
+def test_knapsack_matches_reference(golden_knapsack, name):
+    from rdkv_b200.synth import ALLOC_EPSILON
+    g = sub(golden_knapsack, name)
+    got = RK.knapsack_batched(g["scores"], g["budget"], ALLOC_EPSILON, max_iters=int(g["max_iters"]),
+                              tol=float(g["tol"]), bit_options=tuple(g["bit_options"].tolist()))
+    assert got.dtype == np.int64
+    assert np.array_equal(got, g["bits"])
+
+
+def test_knapsack_default_epsilon(golden_knapsack):
+    from rdkv_b200.knapsack_solver import DEFAULT_EPSILON
+    got = RK.knapsack_batched(golden_knapsack["defeps_scores"], 2.0, DEFAULT_EPSILON)
+    assert np.array_equal(got, golden_knapsack["defeps_bits"])
