@@ -1,0 +1,214 @@
+/*
+ * rdkv_b200 — C ABI of the B200 (sm_100a) packed-KV decode path.
+ *
+ * Every entry point takes raw device pointers, explicit extents/strides and a
+ * cudaStream_t (passed as void*), returns an int status (0 = RDKV_OK) and never
+ * throws, aborts, allocates or synchronises unless its comment says otherwise.
+ * Kernels are enqueued on the given stream only, so calls may be recorded into
+ * a CUDA graph on a capturing stream.
+ *
+ * Each declaration names the reference interface it replaces, as
+ * file:line inside the reference project (Junkai1860/RDKV).
+ */
+#ifndef RDKV_B200_H
+#define RDKV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ── status codes ─────────────────────────────────────────────────────────── */
+enum {
+  RDKV_OK = 0,
+  RDKV_ERR_BAD_ARG = 1,      /* null pointer, negative extent, unsupported dtype      */
+  RDKV_ERR_BAD_SHAPE = 2,    /* head_dim != 128, H_q % H_kv != 0, group size > 16 ... */
+  RDKV_ERR_TOO_LARGE = 3,    /* extent beyond what the kernel (or its scratch) holds  */
+  RDKV_ERR_LAUNCH = 4,       /* the CUDA runtime refused the launch (see cuda code)   */
+  RDKV_ERR_NO_DEVICE = 5
+};
+
+/* element type tags for query tensors */
+enum { RDKV_F16 = 0, RDKV_BF16 = 1, RDKV_F32 = 2 };
+
+#define RDKV_HEAD_DIM 128
+/* floats per split-sequence partial record: [0]=m (running max, log domain),
+ * [1]=l (sum of exp), [2..3]=0, [4..131]=o (un-normalised output, 128 channels) */
+#define RDKV_PARTIAL_STRIDE 132
+
+/*
+ * One (sequence, layer) of packed cache: H_kv heads in the reference's stacked
+ * per-head layout (PackedKVLayer, obkv_accel/packing.py:43-111, plus the fp16
+ * "Zone B" values TriZoneCache.new_v_only, packing.py:114-135).
+ *
+ * K token axis ("stripe"): rows [0, max_t_v) are the compressed tokens in the
+ * same order as the V segments (2-bit rows, then 4-bit, then 8-bit, each head
+ * filling a prefix), rows [max_t_v, t_k) are the tokens whose V stays fp16.
+ * Per-head counts are read from device memory (v_seg_bounds, n_v16) when the
+ * kernel runs, never from host copies.
+ */
+typedef struct rdkv_layer_view {
+  const uint8_t* k2;          /* [H_kv][rows][n_ch2_pad/4] quarter-split bytes, or NULL */
+  const uint8_t* k4;          /* [H_kv][rows][n_ch4_pad/2] half-split bytes, or NULL    */
+  const uint8_t* k8;          /* [H_kv][rows][n_ch8], or NULL                           */
+  int64_t k2_head_stride;     /* bytes between heads                                    */
+  int64_t k4_head_stride;
+  int64_t k8_head_stride;
+  const uint16_t* k_scale;    /* fp16 [H_kv][d_pad], sorted+padded channel order        */
+  const uint16_t* k_zp;       /* fp16 [H_kv][d_pad]                                     */
+  const int64_t* k_perm;      /* int64 [H_kv][d_pad]: original channel of each slot     */
+  int64_t k_perm_head_stride; /* elements between KV heads (g*d_pad for the per-q table)*/
+  const uint8_t* v2;          /* [H_kv][rows][32] or NULL                               */
+  const uint8_t* v4;          /* [H_kv][rows][64] or NULL                               */
+  const uint8_t* v8;          /* [H_kv][rows][128] or NULL                              */
+  int64_t v2_head_stride;     /* bytes between heads                                    */
+  int64_t v4_head_stride;
+  int64_t v8_head_stride;
+  const uint16_t* v_scale;    /* fp16 [H_kv][v_meta_head_stride], head-local row order  */
+  const uint16_t* v_zp;
+  int64_t v_meta_head_stride; /* elements between heads                                 */
+  const uint16_t* v16;        /* fp16 [H_kv][rows][128] Zone-B values, or NULL          */
+  int64_t v16_head_stride;    /* elements between heads                                 */
+  const int32_t* v_seg_bounds;/* int32 [H_kv][3] = (n2, n4, n8) per head; NULL = use    */
+  int32_t n2, n4, n8;         /*   these shared counts for every head                   */
+  const int32_t* n_v16;       /* int32 [H_kv] Zone-B rows per head; NULL = n_v16_shared */
+  int32_t n_v16_shared;
+  const float* mask;          /* optional additive fp32 [H_q][mask_row_stride] (0/-inf) */
+  int64_t mask_row_stride;
+  int32_t n_ch2_pad;          /* shared-max padded channel counts (multiples of 4/2/1)  */
+  int32_t n_ch4_pad;
+  int32_t n_ch8;
+  int32_t max_t_v;            /* stripe row where Zone B starts                         */
+  int32_t t_k;                /* stripe rows to attend over                             */
+  int32_t reserved;
+} rdkv_layer_view;
+
+/* ── library ──────────────────────────────────────────────────────────────── */
+int rdkv_version(void);                    /* ABI version, bumps on any signature change */
+const char* rdkv_last_error_string(int status);
+int rdkv_last_cuda_error(void);            /* cudaError_t of the last failed launch (this thread) */
+int rdkv_sizeof_layer_view(void);          /* lets a binding check its struct layout     */
+
+/* ── K side: scores over packed channels ─────────────────────────────────────
+ * Replaces k_mixed_qk_dot_into / k_mixed_qk_dot
+ * (obkv_accel/triton_k_kernel.py:1211-1427) and the Triton kernels they dispatch
+ * to (:96-956).  out[h_q][t] = (sum_c code*(q[perm c]*scale c) - sum_c zp c *
+ * q[perm c]*scale c) / sqrt(128) for t < t_eff; columns >= t_eff are untouched.
+ * `view` is a HOST pointer (copied into the launch).  q: [H_q][128] with
+ * q_row_stride elements between rows; out: fp32 with out_row_stride elements. */
+int rdkv_k_scores(const rdkv_layer_view* view, const void* q, int q_dtype, int64_t q_row_stride,
+                  int H_q, int H_kv, int t_eff, float* out, int64_t out_row_stride, void* stream);
+
+/* ── V side: weighted sum over packed tokens ──────────────────────────────────
+ * Replaces v_dequant_weighted_sum_dispatch[_into]
+ * (obkv_accel/triton_v_kernel.py:1274-1313, 1729-1760) and kernels :131-1098.
+ * out[h_q][d] = sum over the head's 2/4/8-bit rows of w[h_q][col]*(code-zp)*scale
+ * (col = head-local row index) + sum over its fp16 rows of
+ * w[h_q][max_t_v + j]*v16[j][d].  out is fully overwritten; summation order is
+ * fixed (no atomics).  `view` is a HOST pointer. */
+int rdkv_v_weighted_sum(const rdkv_layer_view* view, const float* w, int64_t w_row_stride,
+                        int H_q, int H_kv, float* out, int64_t out_row_stride, void* stream);
+
+/* ── fused split-sequence decode attention ────────────────────────────────────
+ * Replaces the attention block of the decode loop
+ * (obkv_accel/fast_decode.py:1701-1784: K kernel, mask add, softmax, V kernel)
+ * for n_views (sequence, layer) pairs in one launch.  views: DEVICE array.
+ * q: [n_views][H_q][128].  The stripe of every view is cut into chunks of
+ * rdkv_decode_chunk_tokens() rows; chunk c of view v, query head h writes one
+ * partial record at partials[((v*H_q + h)*n_chunks + c) * RDKV_PARTIAL_STRIDE].
+ * n_chunks must be >= ceil(max t_k / chunk) (chunks past a view's t_k write an
+ * empty record m=-inf, l=0, o=0). */
+int rdkv_decode_chunk_tokens(void);
+int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,
+                             int H_q, int H_kv, int n_chunks, float* partials, void* stream);
+
+/* Log-sum-exp merge of split-sequence partials (new; the reference has no
+ * split path — it is the combine step of the fused call above and of the
+ * multi-GPU sequence split).  For each of n_rows rows merges n_splits records
+ * found at partials + (row*row_stride + s*split_stride) floats, in index order:
+ * M = max m_s, L = sum l_s e^{m_s-M}, out = sum o_s e^{m_s-M} / L  (0 when L = 0).
+ * out: fp32 [n_rows][128]; out_ml: optional fp32 [n_rows][2] = (M, L);
+ * out_partial: optional record array [n_rows][RDKV_PARTIAL_STRIDE] holding the
+ * merged but un-normalised partial (input of a further combine, e.g. across GPUs). */
+int rdkv_lse_combine(const float* partials, int64_t n_rows, int n_splits, int64_t row_stride,
+                     int64_t split_stride, float* out, float* out_ml, float* out_partial,
+                     void* stream);
+
+/* ── prefill: stable partition of a bit map ───────────────────────────────────
+ * Replaces the argsort(stable)/nonzero bookkeeping of pack_v_segments,
+ * build_packed_layer and pack_k_mixed (obkv_accel/packing.py:733-735, 898-917,
+ * 240-256).  bits: [n_rows][len] integers of elem_size bytes (1,2,4,8).
+ * mode 0 (tokens): classes 2,4,8,16 ; mode 1 (channels): 16 counts as 8, classes 2,4,8.
+ * order[row][j]: source index of the j-th kept element in class order (class 2
+ * first ... each class ascending), -1 past the kept count.  counts[row][4]. */
+int rdkv_partition_by_bits(const void* bits, int elem_size, int64_t row_stride, int n_rows, int len,
+                           int mode, int32_t* order, int32_t* counts, void* stream);
+
+/* ── prefill: per-token V quantise + bit-pack ─────────────────────────────────
+ * Replaces quantize_and_pack(dim=3) + transfer_8bit_to_{2,4}bit_batchwise as
+ * used by pack_v_segments (obkv_accel/packing.py:141-165, 715-778;
+ * obkv_accel/bitpack.py:13-40) and the per-head padding/stacking of
+ * _pad_and_stack_per_head_layers (:1116-1158, 1262-1278).
+ * V: fp16 [H][T][D] (v_head_stride, v_row_stride in elements).  order/counts as
+ * produced by rdkv_partition_by_bits mode 0 (order_row_stride 0 = one map shared
+ * by all heads; order NULL = identity over n_identity rows of class `identity_bits`).
+ * Head h writes rows [0,n2_h) of out2 ([H][max_n2][D/4]), [0,n4_h) of out4
+ * ([H][max_n4][D/2]), [0,n8_h) of out8 ([H][max_n8][D]), rows [0,n16_h) of out16
+ * (fp16 [H][max_n16][D]) and scale/zp[h][0..t_v_h) (fp16 [H][max_t_v]); all
+ * remaining rows up to the max_* extents are zero-filled.
+ * quant_bits_override > 0 quantises every class to that many bits but keeps one
+ * code per byte in out8 (the plain quantize_and_pack(dim=3) contract). */
+int rdkv_pack_v(const uint16_t* V, int64_t v_head_stride, int64_t v_row_stride, int H, int D,
+                const int32_t* order, int64_t order_row_stride, const int32_t* counts,
+                int64_t counts_row_stride, int n_identity, int identity_bits,
+                int max_n2, int max_n4, int max_n8, int max_n16,
+                uint8_t* out2, uint8_t* out4, uint8_t* out8, uint16_t* out16,
+                uint16_t* out_scale, uint16_t* out_zp, int max_t_v, int quant_bits_override,
+                void* stream);
+
+/* ── prefill: per-channel K quantise + bit-pack on the stripe ─────────────────
+ * Replaces pack_k_mixed / pack_k_mixed_per_head (obkv_accel/packing.py:177-578)
+ * run over the zero-padded stripe canvas that _pad_and_stack_per_head_layers
+ * builds (:1186-1206), including its property that pad rows take part in the
+ * per-channel min/max.
+ * K: fp16 [H][T][D].  tok_order/tok_counts: token partition (mode 0) giving the
+ * stripe row -> source token map (row s < t_v_h: order[s]; row max_t_v + j,
+ * j < n16_h: order[t_v_h + j]; other rows are zero rows).  tok_order NULL =
+ * identity over t_k rows.  ch_order/ch_counts: channel partition (mode 1).
+ * Channel slot layout is [n_ch2_pad | n_ch4_pad | n_ch8]; a head's kept
+ * channels fill a prefix of each block, the rest are zero columns.
+ * scratch: fp32 [H][n_slabs][2][d_pad] (n_slabs = rdkv_pack_k_slabs(t_k)).
+ * Outputs: k2 [H][t_k][n_ch2_pad/4], k4 [H][t_k][n_ch4_pad/2], k8 [H][t_k][n_ch8],
+ * scale/zp fp16 [H][d_pad], sort_idx int64 [H][d_kept_max] (0-padded),
+ * perm int64 [H][d_pad] (pad -> 0), perm_q int64 [H*g][d_pad] or NULL,
+ * seg_bounds int32 [H][3].
+ * quant_bits_override > 0: quantise all kept channels with that many bits, one
+ * code per byte in k8 (plain quantize_and_pack(dim=2)). */
+int rdkv_pack_k_slabs(int t_k);
+int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_row_stride, int H, int D,
+                const int32_t* tok_order, int64_t tok_order_row_stride, const int32_t* tok_counts,
+                int64_t tok_counts_row_stride, int max_t_v, int t_k,
+                const int32_t* ch_order, int64_t ch_order_row_stride, const int32_t* ch_counts,
+                int64_t ch_counts_row_stride, int n_ch2_pad, int n_ch4_pad, int n_ch8,
+                int d_kept_max, int gqa, float* scratch,
+                uint8_t* k2, uint8_t* k4, uint8_t* k8, uint16_t* out_scale, uint16_t* out_zp,
+                int64_t* sort_idx, int64_t* perm, int64_t* perm_q, int32_t* seg_bounds,
+                int quant_bits_override, void* stream);
+
+/* ── prefill: batched Lagrangian bit allocator ────────────────────────────────
+ * Replaces knapsack_bit_allocation_batched (knapsack_solver.py:121-248).
+ * scores fp32 [n_rows][len] (row_stride elements); budget fp32 [n_rows];
+ * options: n_options (<= 8) integer-valued bit costs and their distortions,
+ * HOST arrays; out int64 [n_rows][len] receives the chosen bit value of every
+ * unit.  scratch: fp32 [n_rows][2] + int32 [n_rows] = 3*n_rows 4-byte words.
+ * len*max(option) must stay below 2^24 (exact fp32 means, as in the reference). */
+int rdkv_knapsack_batched(const float* scores, int64_t row_stride, int n_rows, int len,
+                          const float* budget, const float* option_bits, const float* option_eps,
+                          int n_options, int max_iters, float tol, int64_t* out, void* scratch,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RDKV_B200_H */

@@ -1,0 +1,476 @@
+// Packed-KV decode attention: K-side scores, V-side weighted sum, the fused
+// split-sequence kernel and the log-sum-exp combine.
+//
+// Math follows the reference's kernels (obkv_accel/triton_k_kernel.py:14-16 "bias
+// trick"; obkv_accel/triton_v_kernel.py:1-31 layouts): scale is folded into q
+// (K side) or into the softmax weight (V side) so the inner loops touch raw
+// integer codes; the zero-point term is subtracted once per row.
+#include "rdkv_common.cuh"
+
+namespace rdkv {
+
+thread_local int g_last_cuda_error = 0;
+
+constexpr int CHUNK_T = 128;          // stripe rows per CTA of the fused kernel
+constexpr int SCORE_THREADS = 128;
+constexpr int GP = 8;                 // query heads handled per register pass
+
+// qs[hq][slot] = q[hq][perm[slot]] * scale[slot]; bias[hq] = sum_slot zp*qs.
+// Called by all threads of the block; smem_qs holds g*d_pad floats, smem_bias g floats,
+// smem_red at least (blockDim.x/32)*g floats.
+__device__ void setup_q(const rdkv_layer_view& v, int h, int g, int d_pad, const void* q, int q_dtype,
+                        int64_t q_head0_off, int64_t q_row_stride, float* smem_qs, float* smem_bias,
+                        float* smem_red) {
+  const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
+  const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
+  const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
+  const int nwarp = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int hq = 0; hq < g; ++hq) {
+    float part = 0.f;
+    for (int c = threadIdx.x; c < d_pad; c += blockDim.x) {
+      float qs = load_q(q, q_dtype, q_head0_off + hq * q_row_stride + perm[c]) * h2f(sc[c]);
+      smem_qs[hq * d_pad + c] = qs;
+      part += h2f(zp[c]) * qs;
+    }
+    part = warp_sum(part);
+    if (lane == 0) smem_red[warp * g + hq] = part;
+  }
+  __syncthreads();
+  if (threadIdx.x < g) {
+    float b = 0.f;
+    for (int w = 0; w < nwarp; ++w) b += smem_red[w * g + threadIdx.x];
+    smem_bias[threadIdx.x] = b;
+  }
+  __syncthreads();
+}
+
+// Raw code dot products of one stripe row against qs for heads [hq0, hq0+np).
+__device__ __forceinline__ void row_dot(const rdkv_layer_view& v, int h, int64_t t, int d_pad,
+                                        const float* smem_qs, int hq0, int np, float* acc) {
+  const int sub2 = v.n_ch2_pad >> 2, sub4 = v.n_ch4_pad >> 1, n8 = v.n_ch8;
+#pragma unroll
+  for (int i = 0; i < GP; ++i) acc[i] = 0.f;
+  if (sub2 > 0) {
+    const uint8_t* row = v.k2 + h * v.k2_head_stride + t * sub2;
+    for (int i = 0; i < sub2; ++i) {
+      const unsigned b = row[i];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float code = (float)((b >> (2 * k)) & 3u);
+        const float* qcol = smem_qs + hq0 * d_pad + i + k * sub2;
+#pragma unroll
+        for (int j = 0; j < GP; ++j)
+          if (j < np) acc[j] = fmaf(code, qcol[j * d_pad], acc[j]);
+      }
+    }
+  }
+  if (sub4 > 0) {
+    const uint8_t* row = v.k4 + h * v.k4_head_stride + t * sub4;
+    const int base = v.n_ch2_pad;
+    for (int i = 0; i < sub4; ++i) {
+      const unsigned b = row[i];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const float code = (float)((b >> (4 * k)) & 15u);
+        const float* qcol = smem_qs + hq0 * d_pad + base + i + k * sub4;
+#pragma unroll
+        for (int j = 0; j < GP; ++j)
+          if (j < np) acc[j] = fmaf(code, qcol[j * d_pad], acc[j]);
+      }
+    }
+  }
+  if (n8 > 0) {
+    const uint8_t* row = v.k8 + h * v.k8_head_stride + t * n8;
+    const int base = v.n_ch2_pad + v.n_ch4_pad;
+    for (int i = 0; i < n8; ++i) {
+      const float code = (float)row[i];
+      const float* qcol = smem_qs + hq0 * d_pad + base + i;
+#pragma unroll
+      for (int j = 0; j < GP; ++j)
+        if (j < np) acc[j] = fmaf(code, qcol[j * d_pad], acc[j]);
+    }
+  }
+}
+
+// ───────────────────────────── K-side scores ────────────────────────────────
+__global__ void __launch_bounds__(SCORE_THREADS)
+k_scores_kernel(rdkv_layer_view v, const void* q, int q_dtype, int64_t q_row_stride, int g,
+                int t_eff, float* out, int64_t out_row_stride) {
+  extern __shared__ float smem[];
+  const int h = blockIdx.y;
+  const int d_pad = v.n_ch2_pad + v.n_ch4_pad + v.n_ch8;
+  float* qs = smem;
+  float* bias = qs + g * d_pad;
+  float* red = bias + MAX_GROUP;
+  setup_q(v, h, g, d_pad, q, q_dtype, (int64_t)h * g * q_row_stride, q_row_stride, qs, bias, red);
+  const int64_t t = (int64_t)blockIdx.x * SCORE_THREADS + threadIdx.x;
+  if (t >= t_eff) return;
+  for (int hq0 = 0; hq0 < g; hq0 += GP) {
+    const int np = min(GP, g - hq0);
+    float acc[GP];
+    row_dot(v, h, t, d_pad, qs, hq0, np, acc);
+#pragma unroll
+    for (int j = 0; j < GP; ++j)
+      if (j < np) out[(int64_t)(h * g + hq0 + j) * out_row_stride + t] = (acc[j] - bias[hq0 + j]) * INV_SQRT_D;
+  }
+}
+
+// ───────────────────── V rows: lane owns channels lane+32k ───────────────────
+// kind: 0 = 2-bit row (32 B), 1 = 4-bit row (64 B), 2 = 8-bit row (128 B), 3 = fp16 row.
+__device__ __forceinline__ void load_v_row(const rdkv_layer_view& v, int h, int kind, int64_t r,
+                                           int lane, float* c) {
+  if (kind == 0) {
+    const unsigned b = v.v2[h * v.v2_head_stride + r * 32 + lane];
+    c[0] = (float)(b & 3u); c[1] = (float)((b >> 2) & 3u);
+    c[2] = (float)((b >> 4) & 3u); c[3] = (float)(b >> 6);
+  } else if (kind == 1) {
+    const uint8_t* row = v.v4 + h * v.v4_head_stride + r * 64;
+    const unsigned b0 = row[lane], b1 = row[lane + 32];
+    c[0] = (float)(b0 & 15u); c[2] = (float)(b0 >> 4);
+    c[1] = (float)(b1 & 15u); c[3] = (float)(b1 >> 4);
+  } else if (kind == 2) {
+    const uint8_t* row = v.v8 + h * v.v8_head_stride + r * 128;
+    c[0] = (float)row[lane]; c[1] = (float)row[lane + 32];
+    c[2] = (float)row[lane + 64]; c[3] = (float)row[lane + 96];
+  } else {
+    const uint16_t* row = v.v16 + h * v.v16_head_stride + r * 128;
+    c[0] = h2f(row[lane]); c[1] = h2f(row[lane + 32]);
+    c[2] = h2f(row[lane + 64]); c[3] = h2f(row[lane + 96]);
+  }
+}
+
+// Maps a head-local Zone-A row to its segment.  Returns kind and the row inside it.
+__device__ __forceinline__ int zone_a_kind(const HeadCounts& hc, int r, int64_t* seg_row) {
+  if (r < hc.n2) { *seg_row = r; return 0; }
+  if (r < hc.n2 + hc.n4) { *seg_row = r - hc.n2; return 1; }
+  *seg_row = r - hc.n2 - hc.n4; return 2;
+}
+
+// ─────────────────────────── V-side weighted sum ────────────────────────────
+constexpr int VSUM_THREADS = 512;
+
+__global__ void __launch_bounds__(VSUM_THREADS)
+v_weighted_sum_kernel(rdkv_layer_view v, const float* w, int64_t w_row_stride, int g, float* out,
+                      int64_t out_row_stride) {
+  extern __shared__ float smem[];     // [nwarp][GP][128]
+  const int h = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = VSUM_THREADS / 32;
+  const HeadCounts hc = head_counts(v, h);
+  const int rows = hc.t_v + hc.n16;
+  for (int hq0 = 0; hq0 < g; hq0 += GP) {
+    const int np = min(GP, g - hq0);
+    float acc[GP][4];
+#pragma unroll
+    for (int j = 0; j < GP; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int r = warp; r < rows; r += nwarp) {
+      float c[4];
+      float sc = 1.f, zp = 0.f;
+      int64_t col;
+      if (r < hc.t_v) {
+        int64_t seg_row;
+        const int kind = zone_a_kind(hc, r, &seg_row);
+        load_v_row(v, h, kind, seg_row, lane, c);
+        sc = h2f(v.v_scale[h * v.v_meta_head_stride + r]);
+        zp = h2f(v.v_zp[h * v.v_meta_head_stride + r]);
+        col = r;
+      } else {
+        load_v_row(v, h, 3, r - hc.t_v, lane, c);
+        col = (int64_t)v.max_t_v + (r - hc.t_v);
+      }
+#pragma unroll
+      for (int j = 0; j < GP; ++j) {
+        if (j < np) {
+          const float ws = w[(int64_t)(h * g + hq0 + j) * w_row_stride + col] * sc;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[j][k] = fmaf(ws, c[k] - zp, acc[j][k]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < GP; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) smem[(warp * GP + j) * D + lane + 32 * k] = acc[j][k];
+    __syncthreads();
+    for (int i = threadIdx.x; i < np * D; i += VSUM_THREADS) {
+      const int j = i / D, d = i % D;
+      float s = 0.f;
+      for (int ww = 0; ww < nwarp; ++ww) s += smem[(ww * GP + j) * D + d];
+      out[(int64_t)(h * g + hq0 + j) * out_row_stride + d] = s;
+    }
+    __syncthreads();
+  }
+}
+
+// ───────────────────── fused split-sequence decode attention ─────────────────
+constexpr int FUSED_THREADS = CHUNK_T;   // one thread per stripe row of the chunk
+constexpr int FUSED_WARPS = FUSED_THREADS / 32;
+
+__global__ void __launch_bounds__(FUSED_THREADS)
+decode_attn_partial_kernel(const rdkv_layer_view* __restrict__ views, const void* q, int q_dtype,
+                           int H_q, int g, int n_chunks, float* __restrict__ partials) {
+  extern __shared__ float smem[];
+  __shared__ rdkv_layer_view v;
+  __shared__ float s_bias[MAX_GROUP], s_m[MAX_GROUP], s_l[MAX_GROUP], s_corr[MAX_GROUP];
+  __shared__ float s_red[FUSED_WARPS * MAX_GROUP];
+  const int chunk = blockIdx.x, h = blockIdx.y, view_idx = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    const int* src = reinterpret_cast<const int*>(views + view_idx);
+    int* dst = reinterpret_cast<int*>(&v);
+    for (int i = threadIdx.x; i < (int)(sizeof(rdkv_layer_view) / 4); i += blockDim.x) dst[i] = src[i];
+  }
+  __syncthreads();
+  const int d_pad = v.n_ch2_pad + v.n_ch4_pad + v.n_ch8;
+  float* qs = smem;                               // [g][d_pad]
+  float* pw = qs + g * d_pad;                     // [g][CHUNK_T] weight * v-scale
+  float* red = pw + g * CHUNK_T;                  // [FUSED_WARPS][GP][128]
+  float* rec0 = partials + ((int64_t)(view_idx * H_q + h * g) * n_chunks + chunk) * RDKV_PARTIAL_STRIDE;
+  const int64_t rec_stride = (int64_t)n_chunks * RDKV_PARTIAL_STRIDE;
+
+  const HeadCounts hc = head_counts(v, h);
+  const int t0 = chunk * CHUNK_T;
+  const int t = t0 + threadIdx.x;
+  // Which rows of this chunk exist for this head.
+  const bool in_a = t < hc.t_v;
+  const bool in_b = (t >= v.max_t_v) && (t < v.max_t_v + hc.n16);
+  bool valid = (t < v.t_k) && (in_a || in_b);
+  const bool chunk_live = (t0 < hc.t_v) || (t0 + CHUNK_T > v.max_t_v && t0 < v.max_t_v + hc.n16);
+  if (!chunk_live || t0 >= v.t_k) {                // whole chunk is padding: empty records
+    for (int i = threadIdx.x; i < g * RDKV_PARTIAL_STRIDE; i += blockDim.x) {
+      const int hq = i / RDKV_PARTIAL_STRIDE, e = i % RDKV_PARTIAL_STRIDE;
+      rec0[hq * rec_stride + e] = (e == 0) ? -INFINITY : 0.f;
+    }
+    return;
+  }
+  setup_q(v, h, g, d_pad, q, q_dtype, ((int64_t)view_idx * H_q + h * g) * D, D, qs, s_bias, s_red);
+
+  float v_scale = 1.f, v_zp = 0.f;
+  if (valid && in_a) {
+    v_scale = h2f(v.v_scale[h * v.v_meta_head_stride + t]);
+    v_zp = h2f(v.v_zp[h * v.v_meta_head_stride + t]);
+  }
+  // scores, chunk max, exp, chunk sum
+  for (int hq0 = 0; hq0 < g; hq0 += GP) {
+    const int np = min(GP, g - hq0);
+    float s[GP];
+    if (valid) row_dot(v, h, t, d_pad, qs, hq0, np, s);
+#pragma unroll
+    for (int j = 0; j < GP; ++j) {
+      if (j < np) {
+        float sv = -INFINITY;
+        if (valid) {
+          sv = (s[j] - s_bias[hq0 + j]) * INV_SQRT_D;
+          if (v.mask != nullptr) sv += v.mask[(int64_t)(h * g + hq0 + j) * v.mask_row_stride + t];
+        }
+        s[j] = sv;
+        const float wm = warp_max(sv);
+        if (lane == 0) s_red[warp * MAX_GROUP + hq0 + j] = wm;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < np) {
+      float m = -INFINITY;
+      for (int w = 0; w < FUSED_WARPS; ++w) m = fmaxf(m, s_red[w * MAX_GROUP + hq0 + threadIdx.x]);
+      s_m[hq0 + threadIdx.x] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < GP; ++j) {
+      if (j < np) {
+        const float m = s_m[hq0 + j];
+        const float p = (s[j] == -INFINITY) ? 0.f : exp2f((s[j] - m) * 1.4426950408889634f);
+        const float ps = p * v_scale;
+        pw[(hq0 + j) * CHUNK_T + threadIdx.x] = ps;
+        const float wl = warp_sum(p);
+        const float wc = warp_sum(ps * v_zp);
+        if (lane == 0) { s_red[warp * MAX_GROUP + hq0 + j] = wl; }
+        __syncwarp();
+        s[j] = wc;                       // keep the zero-point term for the second reduction
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < np) {
+      float l = 0.f;
+      for (int w = 0; w < FUSED_WARPS; ++w) l += s_red[w * MAX_GROUP + hq0 + threadIdx.x];
+      s_l[hq0 + threadIdx.x] = l;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < GP; ++j)
+      if (j < np && lane == 0) s_red[warp * MAX_GROUP + hq0 + j] = s[j];
+    __syncthreads();
+    if (threadIdx.x < np) {
+      float c = 0.f;
+      for (int w = 0; w < FUSED_WARPS; ++w) c += s_red[w * MAX_GROUP + hq0 + threadIdx.x];
+      s_corr[hq0 + threadIdx.x] = c;
+    }
+    __syncthreads();
+  }
+
+  // weighted sum of raw codes over the chunk's rows: warp w takes rows w, w+4, ...
+  for (int hq0 = 0; hq0 < g; hq0 += GP) {
+    const int np = min(GP, g - hq0);
+    float acc[GP][4];
+#pragma unroll
+    for (int j = 0; j < GP; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int i = warp; i < CHUNK_T; i += FUSED_WARPS) {
+      const int tt = t0 + i;
+      int kind;
+      int64_t seg_row;
+      if (tt < hc.t_v) {
+        kind = zone_a_kind(hc, tt, &seg_row);
+      } else if (tt >= v.max_t_v && tt < v.max_t_v + hc.n16 && tt < v.t_k) {
+        kind = 3; seg_row = tt - v.max_t_v;
+      } else {
+        continue;
+      }
+      float c[4];
+      load_v_row(v, h, kind, seg_row, lane, c);
+#pragma unroll
+      for (int j = 0; j < GP; ++j) {
+        if (j < np) {
+          const float ps = pw[(hq0 + j) * CHUNK_T + i];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[j][k] = fmaf(ps, c[k], acc[j][k]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < GP; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) red[(warp * GP + j) * D + lane + 32 * k] = acc[j][k];
+    __syncthreads();
+    for (int i = threadIdx.x; i < np * D; i += blockDim.x) {
+      const int j = i / D, d = i % D;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < FUSED_WARPS; ++w) s += red[(w * GP + j) * D + d];
+      rec0[(hq0 + j) * rec_stride + 4 + d] = s - s_corr[hq0 + j];
+    }
+    if (threadIdx.x < np) {
+      float* r = rec0 + (hq0 + threadIdx.x) * rec_stride;
+      r[0] = s_m[hq0 + threadIdx.x];
+      r[1] = s_l[hq0 + threadIdx.x];
+      r[2] = 0.f; r[3] = 0.f;
+    }
+    __syncthreads();
+  }
+}
+
+// ───────────────────────────── LSE combine ───────────────────────────────────
+__global__ void __launch_bounds__(D)
+lse_combine_kernel(const float* __restrict__ partials, int n_splits, int64_t row_stride,
+                   int64_t split_stride, float* __restrict__ out, float* __restrict__ out_ml,
+                   float* __restrict__ out_partial) {
+  const int64_t row = blockIdx.x;
+  const int d = threadIdx.x;
+  const float* base = partials + row * row_stride;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[s * split_stride]);
+  float L = 0.f, o = 0.f;
+  if (M != -INFINITY) {
+    for (int s = 0; s < n_splits; ++s) {
+      const float* rec = base + s * split_stride;
+      const float m = rec[0];
+      if (m == -INFINITY) continue;
+      const float wgt = exp2f((m - M) * 1.4426950408889634f);
+      L = fmaf(rec[1], wgt, L);
+      o = fmaf(rec[4 + d], wgt, o);
+    }
+  }
+  if (out != nullptr) out[row * D + d] = (L > 0.f) ? o / L : 0.f;
+  if (out_ml != nullptr && d == 0) { out_ml[row * 2] = M; out_ml[row * 2 + 1] = L; }
+  if (out_partial != nullptr) {
+    float* rec = out_partial + row * RDKV_PARTIAL_STRIDE;
+    rec[4 + d] = o;
+    if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
+  }
+}
+
+static int check_view_dims(int H_q, int H_kv) {
+  if (H_q <= 0 || H_kv <= 0) return RDKV_ERR_BAD_ARG;
+  if (H_q % H_kv != 0 || H_q / H_kv > MAX_GROUP) return RDKV_ERR_BAD_SHAPE;
+  return RDKV_OK;
+}
+
+}  // namespace rdkv
+
+using namespace rdkv;
+
+extern "C" int rdkv_decode_chunk_tokens(void) { return CHUNK_T; }
+
+extern "C" int rdkv_k_scores(const rdkv_layer_view* view, const void* q, int q_dtype,
+                             int64_t q_row_stride, int H_q, int H_kv, int t_eff, float* out,
+                             int64_t out_row_stride, void* stream) {
+  if (view == nullptr || q == nullptr || out == nullptr || t_eff < 0) return RDKV_ERR_BAD_ARG;
+  if (q_dtype < RDKV_F16 || q_dtype > RDKV_F32) return RDKV_ERR_BAD_ARG;
+  int st = check_view_dims(H_q, H_kv);
+  if (st != RDKV_OK) return st;
+  if (t_eff == 0) return RDKV_OK;
+  const int g = H_q / H_kv;
+  const int d_pad = view->n_ch2_pad + view->n_ch4_pad + view->n_ch8;
+  if (d_pad <= 0 || d_pad > 3 * D || (view->n_ch2_pad & 3) || (view->n_ch4_pad & 1)) return RDKV_ERR_BAD_SHAPE;
+  if (view->k_scale == nullptr || view->k_zp == nullptr || view->k_perm == nullptr) return RDKV_ERR_BAD_ARG;
+  if ((view->n_ch2_pad && !view->k2) || (view->n_ch4_pad && !view->k4) || (view->n_ch8 && !view->k8))
+    return RDKV_ERR_BAD_ARG;
+  const size_t smem = sizeof(float) * ((size_t)g * d_pad + MAX_GROUP + (SCORE_THREADS / 32) * MAX_GROUP);
+  dim3 grid((t_eff + SCORE_THREADS - 1) / SCORE_THREADS, H_kv);
+  k_scores_kernel<<<grid, SCORE_THREADS, smem, (cudaStream_t)stream>>>(
+      *view, q, q_dtype, q_row_stride, g, t_eff, out, out_row_stride);
+  return launch_status();
+}
+
+extern "C" int rdkv_v_weighted_sum(const rdkv_layer_view* view, const float* w, int64_t w_row_stride,
+                                   int H_q, int H_kv, float* out, int64_t out_row_stride,
+                                   void* stream) {
+  if (view == nullptr || w == nullptr || out == nullptr) return RDKV_ERR_BAD_ARG;
+  int st = check_view_dims(H_q, H_kv);
+  if (st != RDKV_OK) return st;
+  if (view->v_scale == nullptr || view->v_zp == nullptr) return RDKV_ERR_BAD_ARG;
+  const int g = H_q / H_kv;
+  const size_t smem = sizeof(float) * (VSUM_THREADS / 32) * GP * D;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(v_weighted_sum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_done = true;
+  }
+  v_weighted_sum_kernel<<<H_kv, VSUM_THREADS, smem, (cudaStream_t)stream>>>(*view, w, w_row_stride, g, out,
+                                                                           out_row_stride);
+  return launch_status();
+}
+
+extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const void* q,
+                                        int q_dtype, int H_q, int H_kv, int n_chunks, float* partials,
+                                        void* stream) {
+  if (views == nullptr || q == nullptr || partials == nullptr || n_views < 0 || n_chunks <= 0)
+    return RDKV_ERR_BAD_ARG;
+  if (q_dtype < RDKV_F16 || q_dtype > RDKV_F32) return RDKV_ERR_BAD_ARG;
+  int st = check_view_dims(H_q, H_kv);
+  if (st != RDKV_OK) return st;
+  if (n_views == 0) return RDKV_OK;
+  if (n_views > 65535 || H_kv > 65535) return RDKV_ERR_TOO_LARGE;
+  const int g = H_q / H_kv;
+  const size_t smem = sizeof(float) * ((size_t)g * 3 * D + (size_t)g * CHUNK_T + FUSED_WARPS * GP * D);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(decode_attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * ((size_t)MAX_GROUP * 3 * D + (size_t)MAX_GROUP * CHUNK_T + FUSED_WARPS * GP * D)));
+    attr_done = true;
+  }
+  dim3 grid(n_chunks, H_kv, n_views);
+  decode_attn_partial_kernel<<<grid, FUSED_THREADS, smem, (cudaStream_t)stream>>>(
+      views, q, q_dtype, H_q, g, n_chunks, partials);
+  return launch_status();
+}
+
+extern "C" int rdkv_lse_combine(const float* partials, int64_t n_rows, int n_splits, int64_t row_stride,
+                                int64_t split_stride, float* out, float* out_ml, float* out_partial,
+                                void* stream) {
+  if (partials == nullptr || n_rows < 0 || n_splits <= 0) return RDKV_ERR_BAD_ARG;
+  if (out == nullptr && out_partial == nullptr) return RDKV_ERR_BAD_ARG;
+  if (n_rows == 0) return RDKV_OK;
+  if (n_rows > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
+  lse_combine_kernel<<<(unsigned)n_rows, D, 0, (cudaStream_t)stream>>>(partials, n_splits, row_stride,
+                                                                      split_stride, out, out_ml,
+                                                                      out_partial);
+  return launch_status();
+}

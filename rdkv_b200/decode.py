@@ -1,0 +1,139 @@
+"""Fused packed-KV decode attention.
+
+Replaces the attention block of the reference decode loop
+(obkv_accel/fast_decode.py:1701-1784: K kernel -> mask add -> softmax -> V kernel)
+with one split-sequence kernel launch over any number of (sequence, layer)
+pairs followed by a log-sum-exp combine.  Softmax semantics are the
+reference's: one softmax per query head over its live Zone-A and Zone-B rows;
+stripe padding is excluded through the per-head row counts read on the device
+(and through ``softmax_mask`` too when ``use_mask`` is set).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+from torch import Tensor
+
+from ._lib import HEAD_DIM, PARTIAL_STRIDE, LayerView, check, lib, ptr, q_dtype_tag, require_cuda, stream_ptr
+from .packing import PackedKVLayer, layer_view
+
+
+class DecodeTable:
+    """Device-resident array of ``rdkv_layer_view`` records, one per (sequence, layer).
+
+    The table holds references to every tensor it points into.  Per-head row
+    counts stay in the layers' own int32 device tensors, so a caller may rewrite
+    payloads and counts in place between launches.
+    """
+
+    def __init__(self, layers: Sequence[PackedKVLayer], new_v_only: Sequence[Optional[Tensor]], H_q: int,
+                 *, use_mask: bool = False, device=None):
+        if len(layers) == 0:
+            raise ValueError("DecodeTable needs at least one layer")
+        if len(new_v_only) != len(layers):
+            raise ValueError("new_v_only must have one entry per layer")
+        sc = layers[0].K_ch_scale
+        self.H_kv = int(sc.shape[1] if sc.dim() == 4 else sc.shape[0])
+        self.H_q = int(H_q)
+        if self.H_q % self.H_kv:
+            raise ValueError(f"H_q={H_q} is not a multiple of H_kv={self.H_kv}")
+        self.device = torch.device(device) if device is not None else layers[0].K_ch_scale.device
+        self._keep: List = []
+        views = (LayerView * len(layers))()
+        max_t_k = 0
+        for i, (pl, nv) in enumerate(zip(layers, new_v_only)):
+            n2, n4, n8 = pl.K_ch_seg_bounds
+            if n2 + n4 + n8 == 0 or n2 > 128 or n4 > 128 or n8 > 128:
+                raise ValueError("layer has no kept K channels or more than 128 in a segment")
+            if int(pl.n_v16) > 0 and nv is None:
+                raise ValueError(f"layer {i} has fp16 rows but no new_v_only tensor")
+            v, keep = layer_view(pl, nv if (nv is not None and int(pl.n_v16) > 0) else None, use_mask=use_mask)
+            views[i] = v
+            self._keep.append(keep)
+            max_t_k = max(max_t_k, int(v.t_k))
+        self.n_views = len(layers)
+        self.max_t_k = max_t_k
+        self.chunk = lib().rdkv_decode_chunk_tokens()
+        self.n_chunks = max(1, (max_t_k + self.chunk - 1) // self.chunk)
+        raw = bytes(views)
+        host = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+        self.views = host.to(self.device)
+        self._partials: Optional[Tensor] = None
+
+    def workspace(self) -> Tensor:
+        """Split-sequence partial records [n_views*H_q, n_chunks, 132] fp32 (allocated once)."""
+        if self._partials is None:
+            self._partials = torch.empty((self.n_views * self.H_q, self.n_chunks, PARTIAL_STRIDE),
+                                         dtype=torch.float32, device=self.device)
+        return self._partials
+
+
+def lse_combine(partials: Tensor, out: Optional[Tensor] = None, *, out_ml: Optional[Tensor] = None,
+                out_partial: Optional[Tensor] = None) -> Optional[Tensor]:
+    """Merge split-sequence records ``[n_rows, n_splits, 132]`` (m, l, -, -, o[128]) in
+    split-index order.  Returns ``out [n_rows,128]`` fp32 (normalised); ``out_partial``
+    ``[n_rows,132]`` receives the merged un-normalised record instead when given."""
+    require_cuda(partials, "partials")
+    if partials.dim() != 3 or partials.shape[2] != PARTIAL_STRIDE or partials.dtype != torch.float32:
+        raise ValueError("partials must be float32 [n_rows, n_splits, 132]")
+    if partials.stride(2) != 1:
+        partials = partials.contiguous()
+    n_rows, n_splits = partials.shape[0], partials.shape[1]
+    if out is None and out_partial is None:
+        out = torch.empty((n_rows, HEAD_DIM), dtype=torch.float32, device=partials.device)
+    check(lib().rdkv_lse_combine(ptr(partials), n_rows, n_splits, partials.stride(0), partials.stride(1),
+                                 ptr(out), ptr(out_ml), ptr(out_partial), stream_ptr(partials.device)),
+          "rdkv_lse_combine")
+    return out
+
+
+def decode_attention_partial(q: Tensor, table: DecodeTable) -> Tensor:
+    """Run the fused kernel only; returns the per-chunk records (the table's workspace)."""
+    require_cuda(q, "q")
+    if q.shape[-1] != HEAD_DIM or q.numel() != table.n_views * table.H_q * HEAD_DIM:
+        raise ValueError(f"q must be [{table.n_views},{table.H_q},{HEAD_DIM}], got {tuple(q.shape)}")
+    if not q.is_contiguous():
+        q = q.contiguous()
+    part = table.workspace()
+    check(lib().rdkv_decode_attn_partial(ptr(table.views), table.n_views, ptr(q), q_dtype_tag(q), table.H_q,
+                                         table.H_kv, table.n_chunks, ptr(part), stream_ptr(q.device)),
+          "rdkv_decode_attn_partial")
+    return part
+
+
+def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tensor] = None,
+                            out_partial: Optional[Tensor] = None) -> Tensor:
+    """softmax(q·K̂ᵀ/√128)·V̂ over every view of ``table``.
+
+    q [n_views,H_q,128] fp16/bf16/fp32 -> out [n_views,H_q,128] fp32.  With
+    ``out_partial`` ([n_views*H_q,132] fp32) the merged un-normalised (m, l, o)
+    record per query head is written instead, for a later combine across
+    sequence shards.  Two launches, no allocation after the first call, no host
+    synchronisation.
+    """
+    part = decode_attention_partial(q, table)
+    if out_partial is not None:
+        lse_combine(part, None, out_partial=out_partial)
+        return out_partial
+    if out is None:
+        out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
+    lse_combine(part, out)
+    return out
+
+
+def packed_layer_attention(q: Tensor, packed_layer: PackedKVLayer, new_v_only: Optional[Tensor] = None,
+                           *, use_mask: bool = False) -> Tensor:
+    """Single (sequence, layer) convenience form: q [H_q,128] -> [H_q,128] fp32.
+
+    The one-entry table is cached on the layer object, as the reference decode
+    loop caches its pre-squeezed views on the cache object
+    (obkv_accel/fast_decode.py:813-816).
+    """
+    key = (q.shape[0], None if new_v_only is None else new_v_only.data_ptr(), use_mask)
+    cached = getattr(packed_layer, "_rdkv_table", None)
+    if cached is None or cached[0] != key:
+        cached = (key, DecodeTable([packed_layer], [new_v_only], q.shape[0], use_mask=use_mask))
+        packed_layer._rdkv_table = cached
+    return packed_decode_attention(q.reshape(1, q.shape[0], HEAD_DIM), cached[1])[0]

@@ -1,0 +1,649 @@
+"""Packed-cache containers and the prefill quantise-and-bitpack operators.
+
+Host-side mirror of the reference's packing module (obkv_accel/packing.py): same
+function names, argument meaning, return tuples and error behaviour, so that a
+caller of the reference can switch imports.  All arithmetic runs in the CUDA
+library (rdkv_partition_by_bits / rdkv_pack_v / rdkv_pack_k); torch is used for
+allocation and for index bookkeeping only.  Tensors must be on a CUDA device.
+
+Layouts (reference: obkv_accel/packing.py:1-20, obkv_accel/bitpack.py):
+  4-bit half-split     byte[i] = c[i] | c[i+L/2] << 4
+  2-bit quarter-split  byte[i] = c[i] | c[i+L/4] << 2 | c[i+L/2] << 4 | c[i+3L/4] << 6
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import LayerView, check, lib, ptr, require_cuda, stream_ptr
+
+
+# ── containers (reference: obkv_accel/packing.py:43-135) ─────────────────────
+
+@dataclass
+class PackedKVLayer:
+    """One layer of packed cache; field names and shapes as in the reference.
+
+    K: ``K_2bit/K_4bit/K_8bit [1,H_kv,T_k,bytes]`` u8 in the shared-max channel
+    layout, ``K_ch_scale/K_ch_zp [1,H_kv,1,D_pad]`` fp16, index tables int64.
+    V: ``V_2bit [1,H_kv,N2,D/4]``, ``V_4bit [..,N4,D/2]``, ``V_8bit [..,N8,D]`` u8,
+    ``V_scale/V_zp [1,H_kv,T_v,1]`` fp16 in head-local row order.
+    """
+    K_2bit: Optional[Tensor]
+    K_4bit: Optional[Tensor]
+    K_8bit: Optional[Tensor]
+    K_ch_scale: Tensor
+    K_ch_zp: Tensor
+    K_ch_sort_idx: Tensor
+    K_ch_seg_bounds: Tuple[int, int, int]
+    K_ch_perm_padded_idx: Tensor
+    V_2bit: Optional[Tensor]
+    V_4bit: Optional[Tensor]
+    V_8bit: Optional[Tensor]
+    V_scale: Tensor
+    V_zp: Tensor
+    sort_idx: Tensor
+    seg_bounds: Tuple[int, int, int]
+    T_eff: int
+    seg_bounds_per_head: Optional[Tensor] = None
+    T_eff_per_head: Optional[Tensor] = None
+    softmax_mask: Optional[Tensor] = None
+    n_fp16_per_head: Optional[Tensor] = None
+    fp16_gap_mask: Optional[Tensor] = None
+    K_ch_sort_idx_per_head: Optional[Tensor] = None
+    K_ch_perm_padded_idx_per_head: Optional[Tensor] = None
+    K_ch_seg_bounds_per_head: Optional[Tensor] = None
+    K_ch_perm_padded_idx_for_Q: Optional[Tensor] = None
+    T_eff_k: int = 0
+    n_v16: int = 0
+    T_eff_k_per_head: Optional[Tensor] = None
+    n_v16_per_head: Optional[Tensor] = None
+    allocation_v_bits: Optional[Tensor] = None
+    allocation_k_bits: Optional[Tensor] = None
+    deferred_k_for_stack: Optional[Tensor] = None
+
+
+@dataclass
+class TriZoneCache:
+    """Packed layers + per-layer fp16 Zone-B values + decode-appended tail."""
+    packed: Tuple[PackedKVLayer, ...]
+    new_v_only: List[Optional[Tensor]]
+    new_both_k: List[Optional[Tensor]]
+    new_both_v: List[Optional[Tensor]]
+    original_seq_len: int
+
+    @property
+    def new_k(self):
+        return self.new_both_k
+
+    @property
+    def new_v(self):
+        return self.new_both_v
+
+
+DualZoneCache = TriZoneCache
+
+
+def _pad_to(n: int, align: int) -> int:
+    return 0 if n == 0 else ((n + align - 1) // align) * align
+
+
+_seg_padded_len = _pad_to
+
+
+def _as_fp16_rows(x: Tensor, name: str) -> Tensor:
+    require_cuda(x, name)
+    if x.dtype != torch.float16:
+        raise ValueError(f"{name} must be float16, got {x.dtype}")
+    if x.dim() != 4 or x.shape[0] != 1:
+        raise AssertionError(f"Expected {name} [1,H,T,D], got {tuple(x.shape)}")
+    if x.stride(3) != 1 and x.shape[3] > 1:
+        x = x.contiguous()
+    return x
+
+
+# ── C-ABI wrappers ───────────────────────────────────────────────────────────
+
+def partition_by_bits(bits: Tensor, mode: int) -> Tuple[Tensor, Tensor]:
+    """Stable class partition of integer bit maps ``[R,L]``.
+
+    Returns ``(order int32 [R,L], counts int32 [R,4])``; mode 0 = tokens
+    (classes 2,4,8,16), mode 1 = channels (16 counted as 8).
+    """
+    require_cuda(bits, "bits")
+    if bits.dim() != 2:
+        raise ValueError("bits must be [rows, len]")
+    if bits.dtype not in (torch.int8, torch.int16, torch.int32, torch.int64):
+        bits = bits.to(torch.int64)
+    if bits.stride(1) != 1 and bits.shape[1] > 1:
+        bits = bits.contiguous()
+    R, L = bits.shape
+    order = torch.empty((R, L), dtype=torch.int32, device=bits.device)
+    counts = torch.zeros((R, 4), dtype=torch.int32, device=bits.device)
+    if R and L:
+        check(lib().rdkv_partition_by_bits(ptr(bits), bits.element_size(), bits.stride(0), R, L, mode,
+                                           ptr(order), ptr(counts), stream_ptr(bits.device)),
+              "rdkv_partition_by_bits")
+    return order, counts
+
+
+def _launch_pack_v(V: Tensor, order: Optional[Tensor], order_rs: int, counts: Optional[Tensor],
+                   counts_rs: int, n_identity: int, identity_bits: int, mx: Sequence[int], max_t_v: int,
+                   override: int = 0):
+    """Allocates the outputs and runs rdkv_pack_v; returns (v2, v4, v8, v16, scale, zp)."""
+    _, H, _, D = V.shape
+    dev = V.device
+    m2, m4, m8, m16 = (int(x) for x in mx)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    v2 = torch.empty((1, H, m2, D // 4), **u8) if m2 else None
+    v4 = torch.empty((1, H, m4, D // 2), **u8) if m4 else None
+    v8 = torch.empty((1, H, m8, D), **u8) if m8 else None
+    v16 = torch.empty((1, H, m16, D), dtype=torch.float16, device=dev) if m16 else None
+    scale = torch.empty((1, H, max_t_v, 1), dtype=torch.float16, device=dev)
+    zp = torch.empty_like(scale)
+    check(lib().rdkv_pack_v(ptr(V), V.stride(1), V.stride(2), H, D, ptr(order), order_rs, ptr(counts),
+                            counts_rs, n_identity, identity_bits, m2, m4, m8, m16, ptr(v2), ptr(v4), ptr(v8),
+                            ptr(v16), ptr(scale), ptr(zp), max_t_v, override, stream_ptr(dev)),
+          "rdkv_pack_v")
+    return v2, v4, v8, v16, scale, zp
+
+
+def _launch_pack_k(K: Tensor, tok_order, tok_order_rs, tok_counts, tok_counts_rs, max_t_v: int, t_k: int,
+                   ch_order: Tensor, ch_order_rs: int, ch_counts: Tensor, ch_counts_rs: int,
+                   n2p: int, n4p: int, n8p: int, d_kept_max: int, gqa: int, override: int = 0):
+    """Allocates outputs + scratch and runs rdkv_pack_k.
+
+    Returns (k2, k4, k8, scale, zp, sort_idx [H,d_kept_max], perm [H,d_pad], perm_q or None,
+    seg_bounds int32 [H,3]).
+    """
+    _, H, _, D = K.shape
+    dev = K.device
+    d_pad = n2p + n4p + n8p
+    u8 = dict(dtype=torch.uint8, device=dev)
+    i64 = dict(dtype=torch.int64, device=dev)
+    if override:
+        k2 = k4 = None
+        k8 = torch.empty((1, H, t_k, d_pad), **u8)
+    else:
+        k2 = torch.empty((1, H, t_k, n2p // 4), **u8) if n2p else None
+        k4 = torch.empty((1, H, t_k, n4p // 2), **u8) if n4p else None
+        k8 = torch.empty((1, H, t_k, n8p), **u8) if n8p else None
+    scale = torch.empty((1, H, 1, d_pad), dtype=torch.float16, device=dev)
+    zp = torch.empty_like(scale)
+    sort_idx = torch.empty((H, d_kept_max), **i64)
+    perm = torch.empty((H, d_pad), **i64)
+    perm_q = torch.empty((H * gqa, d_pad), **i64) if gqa > 0 else None
+    seg_bounds = torch.empty((H, 3), dtype=torch.int32, device=dev)
+    if d_pad > 0:
+        slabs = lib().rdkv_pack_k_slabs(t_k)
+        scratch = torch.empty(H * slabs * 2 * d_pad, dtype=torch.float32, device=dev)
+        check(lib().rdkv_pack_k(ptr(K), K.stride(1), K.stride(2), H, D, ptr(tok_order), tok_order_rs,
+                                ptr(tok_counts), tok_counts_rs, max_t_v, t_k, ptr(ch_order), ch_order_rs,
+                                ptr(ch_counts), ch_counts_rs, n2p, n4p, n8p, d_kept_max, gqa, ptr(scratch),
+                                ptr(k2), ptr(k4), ptr(k8), ptr(scale), ptr(zp), ptr(sort_idx), ptr(perm),
+                                ptr(perm_q), ptr(seg_bounds), override, stream_ptr(dev)),
+              "rdkv_pack_k")
+    else:
+        seg_bounds.zero_()
+    return k2, k4, k8, scale, zp, sort_idx, perm, perm_q, seg_bounds
+
+
+# ── reference-named operators ────────────────────────────────────────────────
+
+def quantize_and_pack(x: Tensor, n_bits: int, dim: int) -> Tuple[Tensor, Tensor, Tensor]:
+    """Asymmetric uniform quantisation along ``dim`` of a ``[1,H,T,D]`` fp16 tensor
+    (reference: obkv_accel/packing.py:141-165).  Returns (codes u8 like x, scale
+    fp16, zero_point fp16, both keepdim along ``dim``).  dim 3 = per token, dim 2 =
+    per channel; other layouts are not part of the packed-cache path.
+    """
+    x = _as_fp16_rows(x, "x")
+    if n_bits not in (2, 4, 8):
+        raise ValueError(f"Unsupported n_bits={n_bits}")
+    _, H, T, D = x.shape
+    dim = dim % 4
+    if T == 0 or D == 0:
+        raise ValueError("cannot quantise an empty tensor")
+    if dim == 3:
+        if D % 4:
+            raise ValueError("per-token quantisation needs D % 4 == 0")
+        _, _, v8, _, scale, zp = _launch_pack_v(x, None, 0, None, 0, T, 8, (0, 0, T, 0), T, override=n_bits)
+        return v8, scale, zp
+    if dim == 2:
+        dev = x.device
+        ch_order = torch.arange(D, dtype=torch.int32, device=dev).view(1, D)
+        ch_counts = torch.tensor([[0, 0, D, 0]], dtype=torch.int32, device=dev)
+        _, _, k8, scale, zp, *_ = _launch_pack_k(x, None, 0, None, 0, T, T, ch_order, 0, ch_counts, 0,
+                                                 0, 0, D, D, 0, override=n_bits)
+        return k8, scale, zp
+    raise ValueError("quantize_and_pack supports dim=2 (per channel) and dim=3 (per token)")
+
+
+def pack_v_segments(V: Tensor, v_bits: Tensor, *, segment_counts: Optional[Tuple[int, int, int]] = None):
+    """Sort tokens by bit-width (stable) and pack each V segment
+    (reference: obkv_accel/packing.py:715-778).  V [1,H,T,D] fp16, v_bits [T] in {2,4,8}.
+
+    Returns (V_2bit, V_4bit, V_8bit, V_scale, V_zp, sort_idx, (N_2, N_4, N_8)); a
+    segment with no tokens is None.
+    """
+    V = _as_fp16_rows(V, "V")
+    T, D = V.shape[2], V.shape[3]
+    if D % 4:
+        raise AssertionError("head dim must be a multiple of 4")
+    order, counts = partition_by_bits(v_bits.reshape(1, -1).to(V.device), 0)
+    if segment_counts is None:
+        n2, n4, n8 = (int(c) for c in counts[0, :3].tolist())
+    else:
+        n2, n4, n8 = map(int, segment_counts)
+    assert n2 + n4 + n8 == T, f"Segment sizes {n2}+{n4}+{n8} != T_eff={T}"
+    v2, v4, v8, _, scale, zp = _launch_pack_v(V, order, 0, counts, 0, 0, 0, (n2, n4, n8, 0), T)
+    return v2, v4, v8, scale, zp, order[0].to(torch.int64), (n2, n4, n8)
+
+
+def pack_k_mixed(K: Tensor, k_bits: Tensor, *, sub_2_target: Optional[int] = None,
+                 sub_4_target: Optional[int] = None, n_ch_8_target: Optional[int] = None,
+                 segment_counts: Optional[Tuple[int, int, int]] = None):
+    """Per-channel mixed-precision K packing with one bit map for all heads
+    (reference: obkv_accel/packing.py:177-391).  K [1,H,T,D] fp16, k_bits [D] in
+    {0,2,4,8,16} (0 pruned, 16 packed as 8).
+
+    Returns (K_2bit, K_4bit, K_8bit, K_ch_scale, K_ch_zp, ch_sort_idx,
+    ch_perm_padded_idx, (N_ch_2, N_ch_4, N_ch_8)).
+    """
+    K = _as_fp16_rows(K, "K")
+    H, T, D = K.shape[1], K.shape[2], K.shape[3]
+    if T == 0:
+        raise ValueError("pack_k_mixed needs at least one token row")
+    ch_order, ch_counts = partition_by_bits(k_bits.reshape(1, -1).to(K.device), 1)
+    if segment_counts is None:
+        n2, n4, n8 = (int(c) for c in ch_counts[0, :3].tolist())
+    else:
+        n2, n4, n8 = map(int, segment_counts)
+    n2p = 4 * int(sub_2_target) if sub_2_target is not None else _pad_to(n2, 4)
+    n4p = 2 * int(sub_4_target) if sub_4_target is not None else _pad_to(n4, 2)
+    n8o = int(n_ch_8_target) if n_ch_8_target is not None else n8
+    assert n2p >= _pad_to(n2, 4), f"sub_2_target={sub_2_target} too small for N_ch_2={n2}"
+    assert n4p >= _pad_to(n4, 2), f"sub_4_target={sub_4_target} too small for N_ch_4={n4}"
+    assert n8o >= n8, f"n_ch_8_target={n_ch_8_target} < N_ch_8={n8}"
+    k2, k4, k8, scale, zp, sort_idx, perm, _, _ = _launch_pack_k(
+        K, None, 0, None, 0, T, T, ch_order, 0, ch_counts, 0, n2p, n4p, n8o, n2 + n4 + n8, 0)
+    return k2, k4, k8, scale, zp, sort_idx[0].contiguous(), perm[0].contiguous(), (n2, n4, n8)
+
+
+pack_k_mixed_single_head = pack_k_mixed
+
+
+def _pack_k_per_head(K: Tensor, tok_order, tok_counts, max_t_v: int, t_k: int, ch_order: Tensor,
+                     ch_counts: Tensor, ch_host: Sequence[Sequence[int]], gqa: int):
+    """Shared-max channel layout over per-head bit maps; ``ch_host`` = host copy of the counts."""
+    m2 = max(r[0] for r in ch_host)
+    m4 = max(r[1] for r in ch_host)
+    m8 = max(r[2] for r in ch_host)
+    d_kept_max = max(r[0] + r[1] + r[2] for r in ch_host)
+    n2p, n4p = _pad_to(m2, 4), _pad_to(m4, 2)
+    tok_rs = tok_order.stride(0) if tok_order is not None else 0
+    res = _launch_pack_k(K, tok_order, tok_rs, tok_counts, 4 if tok_counts is not None else 0, max_t_v, t_k,
+                         ch_order, ch_order.stride(0), ch_counts, 4, n2p, n4p, m8, d_kept_max, gqa)
+    return res, (m2, m4, m8)
+
+
+def pack_k_mixed_per_head(K: Tensor, k_bits_ph: Tensor):
+    """Per-head K bit maps packed to a shared-max channel layout
+    (reference: obkv_accel/packing.py:399-578).  K [1,H,T,D] fp16, k_bits_ph [H,D].
+
+    Returns the 9-tuple (K_2bit, K_4bit, K_8bit, K_ch_scale, K_ch_zp,
+    K_ch_sort_idx_per_head, K_ch_perm_padded_idx_per_head,
+    K_ch_seg_bounds_per_head, (max_N_ch_2, max_N_ch_4, max_N_ch_8)).
+    """
+    K = _as_fp16_rows(K, "K")
+    H, T = K.shape[1], K.shape[2]
+    assert k_bits_ph.dim() == 2 and k_bits_ph.shape[0] == H, (
+        f"k_bits_ph must be [H_kv={H}, D], got {tuple(k_bits_ph.shape)}")
+    if T == 0:
+        raise ValueError("pack_k_mixed_per_head needs at least one token row")
+    ch_order, ch_counts = partition_by_bits(k_bits_ph.to(K.device), 1)
+    ch_host = ch_counts.cpu().tolist()
+    (k2, k4, k8, scale, zp, sort_idx, perm, _, seg_bounds), mx = _pack_k_per_head(
+        K, None, None, T, T, ch_order, ch_counts, ch_host, 0)
+    return k2, k4, k8, scale, zp, sort_idx, perm, seg_bounds, mx
+
+
+def _empty_packed_layer(H_kv: int, D: int, device, dtype) -> PackedKVLayer:
+    e_v = torch.empty(1, H_kv, 0, 1, dtype=dtype, device=device)
+    e_k = torch.empty(1, H_kv, 1, 0, dtype=dtype, device=device)
+    e_i = torch.empty(0, dtype=torch.long, device=device)
+    return PackedKVLayer(None, None, None, e_k, e_k.clone(), e_i, (0, 0, 0), e_i.clone(),
+                         None, None, None, e_v, e_v.clone(), e_i.clone(), (0, 0, 0), 0)
+
+
+def _softmax_mask(t_v: Tensor, n16: Tensor, max_t_v: int, t_k: int, gqa: int) -> Tensor:
+    """Additive fp32 mask [H_q, t_k]: 0 on a head's live rows, -inf on stripe padding
+    (reference: obkv_accel/packing.py:1236-1257)."""
+    col = torch.arange(t_k, device=t_v.device).view(1, -1)
+    live = (col < t_v.view(-1, 1)) | ((col >= max_t_v) & (col < max_t_v + n16.view(-1, 1)))
+    mask = torch.zeros(live.shape, dtype=torch.float32, device=t_v.device)
+    mask.masked_fill_(~live, float("-inf"))
+    return mask.repeat_interleave(gqa, dim=0).contiguous()
+
+
+def pack_kv(K: Tensor, V: Tensor, v_bits: Tensor, k_bits: Tensor, gqa_factor: int, *,
+            build_mask: bool = True, retain_allocation_metadata: bool = False
+            ) -> Tuple[PackedKVLayer, Optional[Tensor]]:
+    """Select, quantise and pack one layer in the per-head stripe layout.
+
+    The composite the reference runs per layer after bit allocation
+    (obkv_fast.py:1098-1166: per-head ``build_packed_layer`` with deferred K, then
+    ``_pad_and_stack_per_head_layers``), as one device pass with a single host
+    read of the segment counts.
+
+    K, V [1,H_kv,T,D] fp16; v_bits [H_kv,T] in {0,2,4,8,16} (0 evicted, 16 kept
+    fp16); k_bits [H_kv,D] in {0,2,4,8,16}.  Returns (PackedKVLayer, new_v_only
+    [1,H_kv,max_n_v16,D] fp16 or None).
+    """
+    K = _as_fp16_rows(K, "K")
+    V = _as_fp16_rows(V, "V")
+    H, T, D = K.shape[1], K.shape[2], K.shape[3]
+    dev = K.device
+    if tuple(v_bits.shape) != (H, T) or tuple(k_bits.shape) != (H, D):
+        raise ValueError(f"v_bits must be [{H},{T}] and k_bits [{H},{D}]")
+    tok_order, tok_counts = partition_by_bits(v_bits.to(dev), 0)
+    ch_order, ch_counts = partition_by_bits(k_bits.to(dev), 1)
+    host = torch.cat([tok_counts, ch_counts], dim=0).cpu().tolist()        # the one host read
+    tok_host, ch_host = host[:H], host[H:]
+    mx = [max(r[i] for r in tok_host) for i in range(4)]
+    t_v_h = [r[0] + r[1] + r[2] for r in tok_host]
+    max_t_v, max_n16 = max(t_v_h), mx[3]
+    t_k = max_t_v + max_n16
+    if t_k == 0:
+        raise RuntimeError("pack_kv: every head kept zero tokens")
+    v2, v4, v8, v16, v_scale, v_zp = _launch_pack_v(V, tok_order, tok_order.stride(0), tok_counts, 4, 0, 0,
+                                                    mx, max_t_v)
+    (k2, k4, k8, k_scale, k_zp, sort_ph, perm_ph, perm_q, seg_ch), ch_mx = _pack_k_per_head(
+        K, tok_order, tok_counts, max_t_v, t_k, ch_order, ch_counts, ch_host, gqa_factor)
+    t_v = tok_counts[:, :3].sum(dim=1).to(torch.int32)
+    n16 = tok_counts[:, 3].contiguous()
+    # legacy single-head field: V sort order of the first non-empty head, as ranks inside
+    # that head's compressed-token list
+    h0 = next((h for h in range(H) if t_v_h[h] + tok_host[h][3] > 0), 0)
+    is_comp = (v_bits[h0].to(dev) > 0) & (v_bits[h0].to(dev) != 16)
+    rank = torch.cumsum(is_comp.to(torch.int64), 0) - 1
+    sort_idx = rank[tok_order[h0, :t_v_h[h0]].to(torch.int64)]
+    layer = PackedKVLayer(
+        K_2bit=k2, K_4bit=k4, K_8bit=k8, K_ch_scale=k_scale, K_ch_zp=k_zp,
+        K_ch_sort_idx=sort_ph[0], K_ch_seg_bounds=ch_mx, K_ch_perm_padded_idx=perm_ph[0],
+        V_2bit=v2, V_4bit=v4, V_8bit=v8, V_scale=v_scale, V_zp=v_zp, sort_idx=sort_idx,
+        seg_bounds=(mx[0], mx[1], mx[2]), T_eff=max_t_v,
+        seg_bounds_per_head=tok_counts[:, :3].contiguous(), T_eff_per_head=t_v,
+        softmax_mask=_softmax_mask(t_v, n16, max_t_v, t_k, gqa_factor) if build_mask else None,
+        K_ch_sort_idx_per_head=sort_ph, K_ch_perm_padded_idx_per_head=perm_ph,
+        K_ch_seg_bounds_per_head=seg_ch, K_ch_perm_padded_idx_for_Q=perm_q,
+        T_eff_k=t_k, n_v16=max_n16, T_eff_k_per_head=(t_v + n16).to(torch.int32), n_v16_per_head=n16,
+        allocation_v_bits=v_bits.to(device=dev, dtype=torch.int16) if retain_allocation_metadata else None,
+        allocation_k_bits=k_bits.to(device=dev, dtype=torch.int16) if retain_allocation_metadata else None,
+    )
+    return layer, v16
+
+
+def build_packed_layer(K: Tensor, V: Tensor, v_bits: Tensor, k_bits: Tensor, *,
+                       gqa_factor: Optional[int] = None,
+                       v_segment_counts: Optional[Tuple[int, int, int]] = None,
+                       defer_k_for_per_head_stack: bool = False
+                       ) -> Tuple[PackedKVLayer, int, Optional[Tensor]]:
+    """Pack one layer whose heads share one token bit map
+    (reference: obkv_accel/packing.py:801-1013).
+
+    K, V [1,H_kv,T,D] fp16; v_bits [T] in {0,2,4,8,16}; k_bits [D] (shared) or
+    [H_kv,D] (per head, needs gqa_factor).  K rows are laid out as [compressed
+    tokens in V segment order ; fp16-V tokens ascending].  Returns
+    (PackedKVLayer, T_eff_k, v16_V).
+    """
+    K = _as_fp16_rows(K, "K")
+    V = _as_fp16_rows(V, "V")
+    H, T, D = K.shape[1], K.shape[2], K.shape[3]
+    dev = K.device
+    v_bits = v_bits.to(dev)
+    tok_order, tok_counts = partition_by_bits(v_bits.reshape(1, -1), 0)
+    n2, n4, n8, n16 = (int(c) for c in tok_counts[0].tolist())
+    if v_segment_counts is not None:
+        assert tuple(map(int, v_segment_counts)) == (n2, n4, n8), (
+            f"Segment sizes {tuple(v_segment_counts)} != counted {(n2, n4, n8)}")
+    t_v = n2 + n4 + n8
+    t_k = t_v + n16
+    if t_k == 0:
+        return _empty_packed_layer(H, D, dev, torch.float16), 0, None
+    v2, v4, v8, v16, v_scale, v_zp = _launch_pack_v(V, tok_order, 0, tok_counts, 0, 0, 0, (n2, n4, n8, n16), t_v)
+    is_comp = (v_bits > 0) & (v_bits != 16)
+    rank = torch.cumsum(is_comp.to(torch.int64), 0) - 1
+    sort_idx = rank[tok_order[0, :t_v].to(torch.int64)]
+    common = dict(V_2bit=v2, V_4bit=v4, V_8bit=v8, V_scale=v_scale, V_zp=v_zp, sort_idx=sort_idx,
+                  seg_bounds=(n2, n4, n8), T_eff=t_v, T_eff_k=t_k, n_v16=n16)
+    e_k = torch.empty(1, H, 1, 0, dtype=torch.float16, device=dev)
+    e_i = torch.empty(0, dtype=torch.long, device=dev)
+    if defer_k_for_per_head_stack:
+        if k_bits.dim() != 1 or H != 1:
+            raise ValueError("deferred K packing expects one head and 1-D k_bits")
+        rows = K.index_select(2, tok_order[0, :t_k].to(torch.int64)).contiguous()
+        packed = PackedKVLayer(None, None, None, e_k, e_k.clone(), e_i, (0, 0, 0), e_i.clone(),
+                               deferred_k_for_stack=rows, **common)
+        return packed, t_k, v16
+    k_bits = k_bits.to(dev)
+    if k_bits.dim() == 2:
+        assert tuple(k_bits.shape) == (H, D), f"k_bits 2D must be [H_kv={H}, D={D}], got {tuple(k_bits.shape)}"
+        assert gqa_factor is not None, "build_packed_layer: gqa_factor is required when k_bits is 2D (per-head)"
+        ch_order, ch_counts = partition_by_bits(k_bits, 1)
+        ch_host = ch_counts.cpu().tolist()
+        (k2, k4, k8, k_scale, k_zp, sort_ph, perm_ph, perm_q, seg_ch), ch_mx = _pack_k_per_head(
+            K, tok_order.expand(H, -1), tok_counts.expand(H, -1).contiguous(), t_v, t_k, ch_order, ch_counts,
+            ch_host, int(gqa_factor))
+        packed = PackedKVLayer(k2, k4, k8, k_scale, k_zp, sort_ph[0], ch_mx, perm_ph[0],
+                               K_ch_sort_idx_per_head=sort_ph, K_ch_perm_padded_idx_per_head=perm_ph,
+                               K_ch_seg_bounds_per_head=seg_ch, K_ch_perm_padded_idx_for_Q=perm_q, **common)
+        return packed, t_k, v16
+    ch_order, ch_counts = partition_by_bits(k_bits.reshape(1, -1), 1)
+    c2, c4, c8 = (int(c) for c in ch_counts[0, :3].tolist())
+    n2p, n4p = _pad_to(c2, 4), _pad_to(c4, 2)
+    k2, k4, k8, k_scale, k_zp, sort_ph, perm_ph, _, _ = _launch_pack_k(
+        K, tok_order, 0, tok_counts, 0, t_v, t_k, ch_order, 0, ch_counts, 0, n2p, n4p, c8, c2 + c4 + c8, 0)
+    packed = PackedKVLayer(k2, k4, k8, k_scale, k_zp, sort_ph[0].contiguous(), (c2, c4, c8),
+                           perm_ph[0].contiguous(), **common)
+    return packed, t_k, v16
+
+
+def _pad_and_stack_per_head_layers(layers: List[PackedKVLayer], per_head_v16_V: List[Optional[Tensor]],
+                                   H_q: int, gqa_factor: int, head_dim: int, device, dtype, *,
+                                   k_bits_per_head: Optional[Tensor] = None,
+                                   v_bits_per_head: Optional[Tensor] = None,
+                                   retain_allocation_metadata: bool = False
+                                   ) -> Tuple[PackedKVLayer, Optional[Tensor]]:
+    """Stack single-head layers (from ``build_packed_layer`` with deferred K) into the
+    per-head stripe layout (reference: obkv_accel/packing.py:1019-1317).
+
+    V segments, scale/zp and fp16 values are zero-padded to the per-layer maxima;
+    K is quantised once over the zero-padded stripe canvas ``[1,H_kv,max_T_v +
+    max_n_v16,D]``, so pad rows take part in the per-channel range as they do in
+    the reference.
+    """
+    H = len(layers)
+    assert H_q == H * gqa_factor, f"H_q={H_q}, H_kv={H}, gqa={gqa_factor}"
+    if k_bits_per_head is None:
+        raise ValueError("rdkv_b200 stacks per-head layers only in per-head K mode (k_bits_per_head required)")
+    D = head_dim
+    t_v_h = [int(pl.T_eff) for pl in layers]
+    n16_h = [int(pl.n_v16) for pl in layers]
+    seg_h = [tuple(int(x) for x in pl.seg_bounds) for pl in layers]
+    max_t_v, max_n16 = max(t_v_h), max(n16_h)
+    t_k = max_t_v + max_n16
+    mx = tuple(max(s[i] for s in seg_h) for i in range(3))
+    u8 = dict(dtype=torch.uint8, device=device)
+
+    def stack(field: str, idx: int, width: int):
+        if mx[idx] == 0:
+            return None
+        out = torch.zeros((1, H, mx[idx], width), **u8)
+        for h, pl in enumerate(layers):
+            if seg_h[h][idx]:
+                out[0, h, :seg_h[h][idx]] = getattr(pl, field)[0, 0]
+        return out
+
+    v2, v4, v8 = stack("V_2bit", 0, D // 4), stack("V_4bit", 1, D // 2), stack("V_8bit", 2, D)
+    v_scale = torch.zeros((1, H, max_t_v, 1), dtype=torch.float16, device=device)
+    v_zp = torch.zeros_like(v_scale)
+    canvas = torch.zeros((1, H, max(t_k, 1), D), dtype=torch.float16, device=device)[:, :, :t_k]
+    new_v_only = torch.zeros((1, H, max_n16, D), dtype=torch.float16, device=device) if max_n16 else None
+    for h, pl in enumerate(layers):
+        if t_v_h[h]:
+            v_scale[0, h, :t_v_h[h]] = pl.V_scale[0, 0]
+            v_zp[0, h, :t_v_h[h]] = pl.V_zp[0, 0]
+        if t_v_h[h] + n16_h[h] == 0:
+            continue
+        rows = pl.deferred_k_for_stack
+        if rows is None:
+            raise ValueError("inner layers must carry deferred_k_for_stack (defer_k_for_per_head_stack=True)")
+        canvas[0, h, :t_v_h[h]] = rows[0, 0, :t_v_h[h]]
+        if n16_h[h]:
+            canvas[0, h, max_t_v:max_t_v + n16_h[h]] = rows[0, 0, t_v_h[h]:]
+            new_v_only[0, h, :n16_h[h]] = per_head_v16_V[h][0, 0]
+    if t_k == 0:
+        raise RuntimeError("every head kept zero tokens")
+    k2, k4, k8, k_scale, k_zp, sort_ph, perm_ph, seg_ch, ch_mx = pack_k_mixed_per_head(
+        canvas, k_bits_per_head.to(device))
+    ref_pl = next((pl for pl in layers if pl.T_eff_k > 0 or pl.T_eff > 0), layers[0])
+    i32 = dict(dtype=torch.int32, device=device)
+    t_v_t, n16_t = torch.tensor(t_v_h, **i32), torch.tensor(n16_h, **i32)
+    packed = PackedKVLayer(
+        K_2bit=k2, K_4bit=k4, K_8bit=k8, K_ch_scale=k_scale, K_ch_zp=k_zp, K_ch_sort_idx=sort_ph[0],
+        K_ch_seg_bounds=ch_mx, K_ch_perm_padded_idx=perm_ph[0],
+        V_2bit=v2, V_4bit=v4, V_8bit=v8, V_scale=v_scale, V_zp=v_zp, sort_idx=ref_pl.sort_idx,
+        seg_bounds=mx, T_eff=max_t_v, seg_bounds_per_head=torch.tensor(seg_h, **i32).view(H, 3),
+        T_eff_per_head=t_v_t, softmax_mask=_softmax_mask(t_v_t, n16_t, max_t_v, t_k, gqa_factor),
+        K_ch_sort_idx_per_head=sort_ph, K_ch_perm_padded_idx_per_head=perm_ph,
+        K_ch_seg_bounds_per_head=seg_ch,
+        K_ch_perm_padded_idx_for_Q=perm_ph.repeat_interleave(gqa_factor, dim=0),
+        T_eff_k=t_k, n_v16=max_n16, T_eff_k_per_head=t_v_t + n16_t, n_v16_per_head=n16_t,
+        allocation_v_bits=(v_bits_per_head.to(device=device, dtype=torch.int16)
+                           if retain_allocation_metadata and v_bits_per_head is not None else None),
+        allocation_k_bits=(k_bits_per_head.to(device=device, dtype=torch.int16)
+                           if retain_allocation_metadata else None),
+    )
+    return packed, new_v_only
+
+
+def build_packed_cache(past_key_values, v_bits: Tensor, k_bits: Tensor, *, original_seq_len: int,
+                       gqa_factor: Optional[int] = None) -> TriZoneCache:
+    """Pack every layer of an HF-style ``((K, V), ...)`` cache with one token bit map
+    (reference: obkv_accel/packing.py:1323-1421).  k_bits: [D], [L,D], [H_kv,D] or
+    [L,H_kv,D] with the reference's shape dispatch."""
+    L = len(past_key_values)
+    H = int(past_key_values[0][0].shape[1])
+    if k_bits.dim() == 1:
+        per_layer = False
+    elif k_bits.dim() == 2:
+        if k_bits.shape[0] == H and k_bits.shape[0] != L:
+            per_layer = False
+        elif k_bits.shape[0] == L:
+            per_layer = True
+        elif k_bits.shape[0] == H:
+            per_layer = False
+        else:
+            raise ValueError(f"k_bits 2D shape {tuple(k_bits.shape)} matches neither num_layers={L} nor H_kv={H}")
+    elif k_bits.dim() == 3:
+        assert tuple(k_bits.shape[:2]) == (L, H), f"k_bits 3D must be [L={L}, H_kv={H}, D]"
+        per_layer = True
+    else:
+        raise ValueError(f"k_bits must be 1D/2D/3D, got shape {tuple(k_bits.shape)}")
+    packed, v16s = [], []
+    for i, (K, V) in enumerate(past_key_values):
+        layer, _, v16 = build_packed_layer(K, V, v_bits, k_bits[i] if per_layer else k_bits,
+                                           gqa_factor=gqa_factor)
+        packed.append(layer)
+        v16s.append(v16)
+    return TriZoneCache(tuple(packed), v16s, [None] * L, [None] * L, int(original_seq_len))
+
+
+# ── kernel-facing view of a layer ────────────────────────────────────────────
+
+def _squeeze_h(t: Optional[Tensor]) -> Optional[Tensor]:
+    if t is not None and t.dim() == 4 and t.shape[0] == 1:
+        return t[0]
+    return t
+
+
+def layer_view(pl: PackedKVLayer, V16: Optional[Tensor] = None, n_v16_per_head: Optional[Tensor] = None,
+               max_T_v: Optional[int] = None, *, use_mask: bool = False, t_k: Optional[int] = None
+               ) -> Tuple[LayerView, list]:
+    """Fill a ``rdkv_layer_view`` from a PackedKVLayer (+ optional Zone-B values).
+
+    Accepts ``[1,H_kv,...]`` or squeezed ``[H_kv,...]`` fields, like the reference
+    wrappers do (triton_k_kernel.py:1190-1200).  Returns the struct and the list of
+    tensors it points into (keep them alive while the view is in use).
+    """
+    v = LayerView()
+    keep = []
+
+    def put(name, t, stride_name=None, stride_dim=0, bytes_=False):
+        t = _squeeze_h(t)
+        if t is None or t.numel() == 0:
+            setattr(v, name, None)
+            if stride_name:
+                setattr(v, stride_name, 0)
+            return None
+        require_cuda(t, name)
+        if t.stride(-1) != 1:
+            t = t.contiguous()
+        keep.append(t)
+        setattr(v, name, t.data_ptr())
+        if stride_name:
+            setattr(v, stride_name, t.stride(stride_dim) * (t.element_size() if bytes_ else 1))
+        return t
+
+    n2c, n4c, n8c = (int(x) for x in pl.K_ch_seg_bounds)
+    v.n_ch2_pad, v.n_ch4_pad, v.n_ch8 = _pad_to(n2c, 4), _pad_to(n4c, 2), n8c
+    put("k2", pl.K_2bit if v.n_ch2_pad else None, "k2_head_stride", 0, True)
+    put("k4", pl.K_4bit if v.n_ch4_pad else None, "k4_head_stride", 0, True)
+    put("k8", pl.K_8bit if v.n_ch8 else None, "k8_head_stride", 0, True)
+    sc = _squeeze_h(pl.K_ch_scale)
+    put("k_scale", sc.reshape(sc.shape[0], -1) if sc is not None and sc.numel() else None)
+    zp = _squeeze_h(pl.K_ch_zp)
+    put("k_zp", zp.reshape(zp.shape[0], -1) if zp is not None and zp.numel() else None)
+    perm_q = pl.K_ch_perm_padded_idx_for_Q
+    if perm_q is not None:
+        H_kv = sc.shape[0]
+        g = perm_q.shape[0] // H_kv
+        put("k_perm", perm_q)
+        v.k_perm_head_stride = g * perm_q.stride(0)
+    elif pl.K_ch_perm_padded_idx_per_head is not None:
+        put("k_perm", pl.K_ch_perm_padded_idx_per_head, "k_perm_head_stride", 0)
+    else:
+        put("k_perm", pl.K_ch_perm_padded_idx)
+        v.k_perm_head_stride = 0
+    put("v2", pl.V_2bit, "v2_head_stride", 0, True)
+    put("v4", pl.V_4bit, "v4_head_stride", 0, True)
+    put("v8", pl.V_8bit, "v8_head_stride", 0, True)
+    vs = _squeeze_h(pl.V_scale)
+    vz = _squeeze_h(pl.V_zp)
+    put("v_scale", vs.reshape(vs.shape[0], -1) if vs.numel() else None, "v_meta_head_stride", 0)
+    put("v_zp", vz.reshape(vz.shape[0], -1) if vz.numel() else None)
+    if pl.seg_bounds_per_head is not None:
+        sb = pl.seg_bounds_per_head
+        if sb.dtype != torch.int32 or not sb.is_contiguous():
+            sb = sb.to(torch.int32).contiguous()
+        put("v_seg_bounds", sb)
+    v.n2, v.n4, v.n8 = (int(x) for x in pl.seg_bounds)
+    v.max_t_v = int(pl.T_eff if max_T_v is None else max_T_v)
+    if V16 is not None and V16.numel() > 0:
+        t = put("v16", V16, "v16_head_stride", 0)
+        v.n_v16_shared = int(t.shape[-2])
+        nv = n_v16_per_head if n_v16_per_head is not None else pl.n_v16_per_head
+        if nv is not None:
+            if nv.dtype != torch.int32 or not nv.is_contiguous():
+                nv = nv.to(torch.int32).contiguous()
+            put("n_v16", nv)
+    if use_mask and pl.softmax_mask is not None and pl.softmax_mask.numel():
+        put("mask", pl.softmax_mask, "mask_row_stride", 0)
+    full = int(pl.T_eff_k) if pl.T_eff_k > 0 else int(pl.T_eff)
+    v.t_k = int(full if t_k is None else t_k)
+    return v, keep

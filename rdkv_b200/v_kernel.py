@@ -1,0 +1,49 @@
+"""V side of decode attention: softmax weights times per-token quantised V.
+
+Drop-in for the reference's ``v_dequant_weighted_sum_dispatch[_into]``
+(obkv_accel/triton_v_kernel.py:1274-1313, 1729-1760).  Weight columns follow the
+reference: a head's 2/4/8-bit rows use head-local column offsets, the fp16
+"Zone B" rows start at column ``max_T_v``.  ``out`` is fully overwritten and the
+summation order is fixed (the reference's default kernel uses atomics).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import check, lib, ptr, require_cuda, stream_ptr
+from .packing import layer_view
+
+D = 128
+
+
+def _num_kv_heads(packed_layer) -> int:
+    sc = packed_layer.V_scale
+    return sc.shape[1] if sc.dim() == 4 else sc.shape[0]
+
+
+def v_dequant_weighted_sum_dispatch_into(attn_weights_old: torch.Tensor, packed_layer, out: torch.Tensor,
+                                         V16=None, n_v16_per_head=None, max_T_v: int = 0) -> None:
+    """out[h_q, :] = sum_t w[h_q, t] * dequant(V)[h_q // g, t, :] (+ fp16 Zone B rows)."""
+    w = attn_weights_old
+    require_cuda(w, "attn_weights_old")
+    require_cuda(out, "out")
+    if w.dtype != torch.float32 or out.dtype != torch.float32:
+        raise ValueError("attn_weights_old and out must be float32")
+    if w.stride(1) != 1 or out.stride(1) != 1:
+        raise ValueError("attn_weights_old and out need unit column stride")
+    H_q = w.shape[0]
+    view, _keep = layer_view(packed_layer, V16, n_v16_per_head,
+                             max_T_v=int(max_T_v) if V16 is not None else None)
+    check(lib().rdkv_v_weighted_sum(C.byref(view), ptr(w), w.stride(0), H_q, _num_kv_heads(packed_layer),
+                                    ptr(out), out.stride(0), stream_ptr(w.device)), "rdkv_v_weighted_sum")
+
+
+def v_dequant_weighted_sum_dispatch(attn_weights_old: torch.Tensor, packed_layer, V16=None,
+                                    n_v16_per_head=None, max_T_v: int = 0) -> torch.Tensor:
+    """Allocating form: returns ``[H_q, 128]`` fp32."""
+    out = torch.empty((attn_weights_old.shape[0], D), dtype=torch.float32, device=attn_weights_old.device)
+    v_dequant_weighted_sum_dispatch_into(attn_weights_old, packed_layer, out, V16=V16,
+                                         n_v16_per_head=n_v16_per_head, max_T_v=max_T_v)
+    return out

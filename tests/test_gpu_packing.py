@@ -1,0 +1,192 @@
+"""Bit-exact parity of the CUDA quantise-and-bitpack path (through the C ABI) with
+the reference-generated golden vectors and with the numpy oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_layer_equal, sub
+from helpers import cuda, layer_to_np, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def _pack_kv_gpu(K, V, v_bits, k_bits, g, **kw):
+    from rdkv_b200.packing import pack_kv
+    return pack_kv(cuda(K), cuda(V), cuda(v_bits), cuda(k_bits), g, **kw)
+
+
+def test_reference_unit_case_segment_packing(golden_unit):
+    """Inputs of the reference's own segment-count test: pack_k_mixed and pack_v_segments
+    with and without precomputed counts give the golden tensors."""
+    from rdkv_b200.packing import pack_k_mixed, pack_v_segments
+    g = sub(golden_unit, "t1")
+    for counts in (None, (2, 2, 3)):
+        k = pack_k_mixed(cuda(g["keys"]), cuda(g["k_bits"]), segment_counts=counts)
+        for name, got in zip(["K_2bit", "K_4bit", "K_8bit", "K_ch_scale", "K_ch_zp", "K_ch_sort_idx",
+                              "K_ch_perm_padded_idx"], k[:7]):
+            assert np.array_equal(to_np(got), g[name]), name
+        assert k[7] == (2, 2, 3)
+    for counts in (None, (2, 2, 2)):
+        v = pack_v_segments(cuda(g["values"]), cuda(g["v_bits"]), segment_counts=counts)
+        for name, got in zip(["V_2bit", "V_4bit", "V_8bit", "V_scale", "V_zp", "sort_idx"], v[:6]):
+            assert np.array_equal(to_np(got), g[name]), name
+        assert v[6] == (2, 2, 2)
+
+
+def test_reference_unit_case_deferred_k_stack(golden_unit):
+    """The reference's ragged-head test (bits {0,2,4,8,16}, D=8) through the same call
+    sequence: per-head build_packed_layer with deferred K, then pad-and-stack."""
+    from rdkv_b200.packing import _pad_and_stack_per_head_layers, build_packed_layer
+    g = sub(golden_unit, "t2")
+    keys, values = cuda(g["keys"]), cuda(g["values"])
+    v_bits, k_bits = cuda(g["v_bits"]), cuda(g["k_bits"])
+    layers, v16s = [], []
+    for h in range(2):
+        kept = (v_bits[h] > 0).nonzero(as_tuple=True)[0]
+        kb = v_bits[h].index_select(0, kept)
+        counts = tuple(int((kb == b).sum()) for b in (2, 4, 8))
+        layer, _, v16 = build_packed_layer(keys[:, h:h + 1].index_select(2, kept),
+                                           values[:, h:h + 1].index_select(2, kept), kb, k_bits[h],
+                                           v_segment_counts=counts, defer_k_for_per_head_stack=True)
+        assert layer.deferred_k_for_stack is not None
+        layers.append(layer)
+        v16s.append(v16)
+    packed, nv = _pad_and_stack_per_head_layers(layers, v16s, H_q=4, gqa_factor=2, head_dim=8,
+                                                device=keys.device, dtype=keys.dtype, k_bits_per_head=k_bits)
+    assert_layer_equal(layer_to_np(packed), g, "stack.")
+    assert np.array_equal(to_np(nv), g["new_v_only"])
+    assert packed.deferred_k_for_stack is None
+    # the one-pass composite gives the same layer
+    packed2, nv2 = _pack_kv_gpu(g["keys"], g["values"], g["v_bits"], g["k_bits"], 2)
+    assert_layer_equal(layer_to_np(packed2), g, "pack_kv.")
+    assert np.array_equal(to_np(nv2), g["new_v_only"])
+    assert np.array_equal(to_np(packed2.sort_idx), g["sort_idx"])
+    assert np.array_equal(to_np(packed2.K_ch_sort_idx), g["K_ch_sort_idx"])
+    assert np.array_equal(to_np(packed2.K_ch_perm_padded_idx), g["K_ch_perm_padded_idx"])
+
+
+@pytest.mark.parametrize("tag", ["even", "ragged", "gqa8"])
+def test_pack_kv_matches_golden(golden_layers, tag):
+    g = sub(golden_layers, tag)
+    packed, nv = _pack_kv_gpu(g["K"], g["V"], g["v_bits"], g["k_bits"], int(g["g"]))
+    assert_layer_equal(layer_to_np(packed), g, tag + ".")
+    if "new_v_only" in g:
+        assert np.array_equal(to_np(nv), g["new_v_only"])
+    else:
+        assert nv is None
+    assert np.array_equal(to_np(packed.sort_idx), g["sort_idx"])
+
+
+def test_quantize_and_pack_both_axes(golden_layers):
+    from oracle import ref_packing as RP
+    from rdkv_b200.packing import quantize_and_pack
+    g = sub(golden_layers, "even")
+    x = g["K"][:, :, :200]
+    for bits in (2, 4, 8):
+        for dim in (2, 3):
+            c, s, z = quantize_and_pack(cuda(x), bits, dim)
+            rc, rs, rz = RP.quantize(x, bits, dim)
+            assert np.array_equal(to_np(c), rc), (bits, dim)
+            assert np.array_equal(to_np(s), rs) and np.array_equal(to_np(z), rz), (bits, dim)
+
+
+def test_build_packed_layer_shared_and_per_head_k(golden_layers):
+    """Heads sharing one token map: [D] and [H,D] channel maps against the oracle."""
+    from oracle import ref_packing as RP
+    from rdkv_b200.packing import build_packed_layer
+    from rdkv_b200 import synth
+    g = sub(golden_layers, "ragged")
+    K, V = g["K"], g["V"]
+    H = K.shape[1]
+    v_bits = g["v_bits"][0]
+    kb_ph = g["k_bits"]
+    # per-head channel maps
+    pl, t_k, v16 = build_packed_layer(cuda(K), cuda(V), cuda(v_bits), cuda(kb_ph), gqa_factor=2)
+    want, want_nv = RP.pack_kv(K, V, np.repeat(v_bits[None], H, 0), kb_ph, 2)
+    got = layer_to_np(pl)
+    for f in ["K_2bit", "K_4bit", "K_8bit", "K_ch_scale", "K_ch_zp", "V_2bit", "V_4bit", "V_8bit", "V_scale",
+              "V_zp", "K_ch_perm_padded_idx_for_Q", "K_ch_seg_bounds_per_head", "K_ch_sort_idx_per_head"]:
+        assert np.array_equal(got[f], want[f]), f
+    assert t_k == want["T_eff_k"] and np.array_equal(to_np(v16), want_nv)
+    # one channel map for all heads
+    pl1, _, _ = build_packed_layer(cuda(K), cuda(V), cuda(v_bits), cuda(kb_ph[0]))
+    want1, _ = RP.pack_kv(K, V, np.repeat(v_bits[None], H, 0), np.repeat(kb_ph[:1], H, 0), 2)
+    got1 = layer_to_np(pl1)
+    for f in ["K_2bit", "K_4bit", "K_8bit", "K_ch_scale", "K_ch_zp", "V_8bit", "V_scale"]:
+        assert np.array_equal(got1[f], want1[f]), f
+    assert np.array_equal(got1["K_ch_perm_padded_idx"], want1["K_ch_perm_padded_idx_per_head"][0])
+
+
+def test_config0_layer_matches_oracle():
+    """Llama-3.1-8B layer shape: 8 KV heads, context 4096, budget 1024, 64 kept channels."""
+    from oracle import ref_packing as RP
+    from rdkv_b200 import synth
+    seed = synth.unit_seed(0)
+    K, V = synth.make_kv(8, 4096, seed=seed)
+    v_bits = synth.make_v_bits(8, 4096, 1024, seed=seed)
+    k_bits = synth.make_k_bits(8, seed=seed)
+    packed, nv = _pack_kv_gpu(K.numpy(), V.numpy(), v_bits.numpy(), k_bits.numpy(), 4)
+    want, want_nv = RP.pack_kv(K.numpy(), V.numpy(), v_bits.numpy(), k_bits.numpy(), 4)
+    assert_layer_equal(layer_to_np(packed), want, "cfg0.")
+    assert np.array_equal(to_np(nv), want_nv)
+    assert tuple(packed.K_2bit.shape) == (1, 8, 1024, 6) and tuple(packed.V_4bit.shape) == (1, 8, 384, 64)
+
+
+def test_edge_cases():
+    from oracle import ref_packing as RP
+    from rdkv_b200 import synth
+    from rdkv_b200.packing import pack_kv
+    K, V = synth.make_kv(2, 64, seed=5)
+    # a head with no kept token, a head with only fp16 tokens, single segment classes
+    v_bits = torch.zeros(2, 64, dtype=torch.long)
+    v_bits[1, 5:9] = 16
+    k_bits = torch.zeros(2, 128, dtype=torch.long)
+    k_bits[0, :3] = 2
+    k_bits[1, 7] = 16
+    packed, nv = pack_kv(K.cuda(), V.cuda(), v_bits.cuda(), k_bits.cuda(), 1)
+    want, want_nv = RP.pack_kv(K.numpy(), V.numpy(), v_bits.numpy(), k_bits.numpy(), 1)
+    assert_layer_equal(layer_to_np(packed), want, "edge.")
+    assert np.array_equal(to_np(nv), want_nv)
+    # all heads empty -> error, like the reference's "kept zero tokens" failure
+    with pytest.raises(RuntimeError):
+        pack_kv(K.cuda(), V.cuda(), torch.zeros(2, 64, dtype=torch.long).cuda(), k_bits.cuda(), 1)
+    # every channel pruned: no K segments, empty scale
+    v_bits[0, :10] = 4
+    packed, _ = pack_kv(K.cuda(), V.cuda(), v_bits.cuda(), torch.zeros(2, 128, dtype=torch.long).cuda(), 1)
+    assert packed.K_2bit is None and packed.K_8bit is None and packed.K_ch_scale.shape[-1] == 0
+
+
+def test_full_size_properties():
+    """Config-1 layer (8 heads x 32768 tokens, budget 4096): size-independent checks —
+    byte-exact round trip of the codes through dequantise/requantise and range bounds."""
+    from oracle import ref_packing as RP
+    from rdkv_b200 import synth
+    from rdkv_b200.packing import pack_kv, quantize_and_pack
+    seed = synth.unit_seed(1)
+    K, V = synth.make_kv(8, 32768, seed=seed, device="cuda")
+    v_bits = synth.make_v_bits(8, 32768, 4096, seed=seed, device="cuda")
+    k_bits = synth.make_k_bits(8, seed=seed, device="cuda")
+    packed, nv = pack_kv(K, V, v_bits, k_bits, 4)
+    assert packed.T_eff == 3584 and packed.n_v16 == 512 and packed.T_eff_k == 4096
+    assert tuple(packed.V_2bit.shape) == (1, 8, 1024, 32) and tuple(packed.K_4bit.shape) == (1, 8, 4096, 12)
+    # fp16 rows are bit copies of the selected V rows, in ascending token order
+    for h in (0, 7):
+        ids = (v_bits[h] == 16).nonzero(as_tuple=True)[0]
+        assert torch.equal(nv[0, h], V[0, h, ids])
+    # idempotence: dequantised 8-bit V rows re-quantise to the same codes/scale/zp
+    layer = {k: to_np(v) if torch.is_tensor(v) else v for k, v in vars(packed).items()}
+    Vhat = RP.unpack_v(layer, to_np(nv), 128)
+    n2, n4, n8 = (int(x) for x in layer["seg_bounds_per_head"][3])
+    rows8 = torch.from_numpy(Vhat[:, 3:4, n2 + n4:n2 + n4 + n8]).cuda().contiguous()
+    c, s, z = quantize_and_pack(rows8, 8, 3)
+    codes = to_np(c).astype(np.float32)
+    zp = to_np(z).astype(np.float32)
+    again = ((codes - zp) * to_np(s).astype(np.float32)).astype(np.float16)
+    assert np.abs(again.astype(np.float32) - Vhat[:, 3:4, n2 + n4:n2 + n4 + n8].astype(np.float32)).max() <= \
+        float(to_np(s).astype(np.float32).max()) * 1.01
+    # K codes of the whole layer agree with the oracle on a sample of heads
+    want, _ = RP.pack_kv(to_np(K[:, 2:4]), to_np(V[:, 2:4]), to_np(v_bits[2:4]), to_np(k_bits[2:4]), 4)
+    # (heads 2..3 packed alone see the same stripe extents because every head keeps 4096 tokens)
+    for f in ["K_2bit", "K_4bit", "K_8bit"]:
+        assert np.array_equal(to_np(getattr(packed, f))[:, 2:4], want[f]), f
+    assert np.array_equal(to_np(packed.V_scale)[:, 2:4], want["V_scale"])
