@@ -1,0 +1,433 @@
+"""Benchmark of the packed-KV decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode|pack|alloc]
+    python bench.py --impl reference ...         # CPU restatement of the reference path
+
+One "step" of the default workload is one decode step of the full-depth
+Llama-3.1-8B attention shape (32 layers x batch 16 x 8 KV heads / 32 query heads,
+head_dim 128, context 32768, 2048 kept tokens per head at the 1/8 fp16 - 1/4 8-bit -
+3/8 4-bit - 1/4 2-bit mix, 64 of 128 K channels kept as 16@8b + 24@4b + 24@2b):
+a fresh bf16 query per (sequence, layer, head) against the static packed cache.
+With N GPUs the KV heads are sharded (8/N per rank, no collective on the data path).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+CFG3 = dict(layers=32, batch=16, kv_heads=8, q_heads=32, context=32768, budget=2048, config_id=3)
+L2_BYTES = 126 * 1024 * 1024
+METRIC = "packed-KV decode-attn tokens/s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused-kernel launch from the committed ncu
+# capture (profiles/), scaled to this workload by units processed; None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = None
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ── clocks: sampled through NVML (read-only) while the timed regions run ─────
+class ClockSampler:
+    REASONS = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+               0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+               0x100: "display_clock_setting"}
+
+    def __init__(self, cuda_index: int, period_s: float = 0.004):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period_s
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = cuda_index
+            if vis:
+                ids = [v.strip() for v in vis.split(",") if v.strip()]
+                if cuda_index < len(ids) and ids[cuda_index].isdigit():
+                    phys = int(ids[cuda_index])
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ── workload construction ────────────────────────────────────────────────────
+def unit_bytes(pl, nv) -> int:
+    """Algorithmic bytes of one packed (sequence, layer): live packed K and V rows, scale/zp, fp16 rows."""
+    sb = pl.seg_bounds_per_head.cpu().tolist()
+    n16 = pl.n_v16_per_head.cpu().tolist()
+    k_row = sum(t.shape[-1] for t in (pl.K_2bit, pl.K_4bit, pl.K_8bit) if t is not None)
+    total = 0
+    for (n2, n4, n8), n in zip(sb, n16):
+        rows = n2 + n4 + n8 + n
+        total += rows * k_row + 2 * 2 * pl.K_ch_scale.shape[-1]
+        total += n2 * 32 + n4 * 64 + n8 * 128 + (n2 + n4 + n8) * 4 + n * 256
+    return total
+
+
+def build_decode_cache(cfg, h0, h1, replica, device):
+    """Packed cache of this rank's KV heads [h0,h1) for every (layer, sequence): synthetic K/V of
+    the full context generated on the device from the unit's seed, bits prescribed by ranked
+    lognormal importances, packed by the library's own (parity-checked) packer."""
+    from rdkv_b200 import synth
+    from rdkv_b200.packing import pack_kv
+    g = cfg["q_heads"] // cfg["kv_heads"]
+    layers, nvs, nbytes = [], [], 0
+    for layer in range(cfg["layers"]):
+        for seq in range(cfg["batch"]):
+            seed = synth.unit_seed(cfg["config_id"], layer, seq) + 100003 * replica
+            K, V = synth.make_kv(cfg["kv_heads"], cfg["context"], seed=seed, device=device)
+            vb = synth.make_v_bits(cfg["kv_heads"], cfg["context"], cfg["budget"], seed=seed, device=device)
+            kb = synth.make_k_bits(cfg["kv_heads"], seed=seed, device=device)
+            pl, nv = pack_kv(K[:, h0:h1], V[:, h0:h1], vb[h0:h1], kb[h0:h1], g, build_mask=False)
+            layers.append(pl)
+            nvs.append(nv)
+            nbytes += unit_bytes(pl, nv)
+            del K, V
+    return layers, nvs, nbytes
+
+
+def timed_steps(fn, steps, barrier):
+    """Time `steps` calls of fn(i) with CUDA events on the current stream; returns ms."""
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1)
+
+
+def max_over_ranks(x: float, world: int, device) -> float:
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def run_decode(args, rank, world, device):
+    from rdkv_b200._lib import lib
+    from rdkv_b200.decode import DecodeTable, decode_attention_partial, lse_combine, packed_decode_attention
+    cfg = dict(CFG3)
+    if args.small:
+        cfg.update(layers=2, batch=2, context=4096, budget=1024)
+    H_kv = cfg["kv_heads"]
+    assert H_kv % world == 0, "KV heads are sharded across ranks: world size must divide 8"
+    h0, h1 = rank * H_kv // world, (rank + 1) * H_kv // world
+    g = cfg["q_heads"] // H_kv
+    Hq_loc = (h1 - h0) * g
+    n_views = cfg["layers"] * cfg["batch"]
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+
+    # enough distinct cache replicas that consecutive steps cannot be served from L2
+    tables, step_bytes = [], None
+    while True:
+        layers, nvs, nbytes = build_decode_cache(cfg, h0, h1, len(tables), device)
+        tables.append(DecodeTable(layers, nvs, Hq_loc))
+        step_bytes = nbytes
+        if len(tables) * nbytes >= 2.2 * L2_BYTES or args.small:
+            break
+    R = len(tables)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4242 + rank)
+    n_q = min(args.steps + args.warmup, 64)
+    q_pool = [(torch.randn(n_views, Hq_loc, 128, generator=gen, device=device) / 128 ** 0.5).to(torch.bfloat16)
+              for _ in range(n_q)]
+    out = torch.empty((n_views, Hq_loc, 128), dtype=torch.float32, device=device)
+
+    def step(i):
+        packed_decode_attention(q_pool[i % n_q], tables[i % R], out=out)
+
+    for i in range(args.warmup):
+        step(i)
+    sampler = ClockSampler(device.index if device.index is not None else 0)
+    with sampler:
+        ms = timed_steps(step, args.steps, barrier)
+    ms = max_over_ranks(ms, world, device)
+
+    # per-kernel duration of the fused kernel (dominant) inside the same loop, for the roofline
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    with sampler:
+        for i in range(args.steps):
+            tb = tables[i % R]
+            ev[i][0].record()
+            part = decode_attention_partial(q_pool[i % n_q], tb)
+            ev[i][1].record()
+            lse_combine(part, out.view(-1, 128))
+        torch.cuda.synchronize()
+    fused_ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
+    fused_ms = max_over_ranks(fused_ms, world, device)
+
+    # end to end through the public call with host buffers: pinned q in, pinned out back, every step
+    q_host = [q.cpu().pin_memory() for q in q_pool[:min(n_q, 8)]]
+    q_dev = torch.empty_like(q_pool[0])
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def e2e_step(i):
+        q_dev.copy_(q_host[i % len(q_host)], non_blocking=True)
+        packed_decode_attention(q_dev, tables[i % R], out=out)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the caller reads the result before the next step
+
+    for i in range(min(args.warmup, 3)):
+        e2e_step(i)
+    with sampler:
+        e2e_ms = timed_steps(e2e_step, args.steps, barrier)
+    e2e_ms = max_over_ranks(e2e_ms, world, device)
+
+    if rank != 0:
+        return None
+    peak, peak_kind = load_peaks()
+    tokens = cfg["batch"] * args.steps
+    sec = ms / 1e3
+    total_step_bytes = step_bytes * world            # every rank holds the same number of heads
+    achieved = step_bytes / (fused_ms / 1e3) / 1e9   # per-GPU GB/s of the dominant kernel
+    traffic = None if NCU_TRAFFIC_BYTES_PER_ALGO_BYTE is None else NCU_TRAFFIC_BYTES_PER_ALGO_BYTE * step_bytes
+    line = {
+        "metric": METRIC, "value": tokens / sec, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "u8 codes / fp16 scales, fp32 accumulate",
+        "data": "synthetic",
+        "config": {
+            "workload": "config 3: full-depth decode, Llama-3.1-8B attention shape — 32 layers x batch 16 x "
+                        "8 KV heads (32 q heads, head_dim 128), context 32768, 2048 kept tokens/head "
+                        "(1/8 fp16, 1/4 8b, 3/8 4b, 1/4 2b), 64 K channels kept (16@8b,24@4b,24@2b), bf16 q per step",
+            "batch": cfg["batch"], "layers": cfg["layers"], "kv_heads": H_kv, "q_heads": cfg["q_heads"],
+            "token_budget": cfg["budget"], "context": cfg["context"],
+            "parallelism": f"kv-head sharding x{world} (no data-path collective)",
+            "launches_per_step": 2,
+            "l2": f"{R} cache replica(s) rotated per step, {R * step_bytes / 2**20:.0f} MiB per GPU "
+                  f"> 2 x 126 MiB L2; no flush needed",
+            "small": bool(args.small),
+        },
+        "hbm_gbs": total_step_bytes * args.steps / sec / 1e9,
+        "hbm_frac_of_8tbs": total_step_bytes * args.steps / sec / 1e9 / (8000.0 * world),
+        "algorithmic_bytes_per_step": total_step_bytes,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
+                     "kernel": "decode_attn_partial_kernel", "kernel_ms": fused_ms,
+                     "algorithmic_bytes_per_launch": step_bytes},
+        "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s",
+                "h2d_bytes_per_step": q_dev.numel() * q_dev.element_size() * world,
+                "d2h_bytes_per_step": out.numel() * out.element_size() * world,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": 2 * args.steps,
+        "clocks": sampler.summary(),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_decode_baseline(cfg, tables[0], layers_per_sample=1, steps=2)
+    return line
+
+
+# ── CPU arm: the oracle's dequantise-then-attend on the host cores ───────────
+def _layer_to_np(pl):
+    d = {}
+    for k, v in vars(pl).items():
+        if k.startswith("_"):
+            continue
+        d[k] = v.detach().cpu().numpy() if torch.is_tensor(v) else v
+    if d.get("softmax_mask") is None:
+        import numpy as np
+        H = d["V_scale"].shape[1]
+        g = d["K_ch_perm_padded_idx_for_Q"].shape[0] // H
+        col = np.arange(d["T_eff_k"])[None]
+        live = (col < d["T_eff_per_head"][:, None]) | ((col >= d["T_eff"]) &
+                                                        (col < d["T_eff"] + d["n_v16_per_head"][:, None]))
+        d["softmax_mask"] = np.repeat(np.where(live, 0.0, -np.inf).astype(np.float32), g, axis=0)
+    return d
+
+
+def cpu_attend_time(units, q_np, cores, steps, decode_steps_amortised=256):
+    """units: list of (layer dict, new_v_only).  Returns seconds per step over all units:
+    dequantise once (amortised over the decode run) + fp32 attention per step."""
+    import numpy as np
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import ref_packing as RP
+
+    def dequant(u):
+        layer, nv = u
+        return RP.unpack_k(layer, 128)[0].astype(np.float32), RP.unpack_v(layer, nv, 128)[0].astype(np.float32), \
+            layer["softmax_mask"]
+
+    def attend(args):
+        (Kh, Vh, mask), q = args
+        g = q.shape[0] // Kh.shape[0]
+        s = np.einsum("hgd,htd->hgt", q.reshape(Kh.shape[0], g, 128), Kh) / np.float32(128 ** 0.5)
+        s = s + mask.reshape(Kh.shape[0], g, -1)
+        p = np.exp(s - s.max(-1, keepdims=True))
+        return np.einsum("hgt,htd->hgd", p / p.sum(-1, keepdims=True), Vh)
+
+    with ThreadPoolExecutor(cores) as ex:
+        t0 = time.perf_counter()
+        deq = list(ex.map(dequant, units))
+        t_deq = time.perf_counter() - t0
+        times = []
+        for s in range(steps):
+            t0 = time.perf_counter()
+            list(ex.map(attend, [(d, q_np[s % len(q_np)][i]) for i, d in enumerate(deq)]))
+            times.append(time.perf_counter() - t0)
+    return t_deq / decode_steps_amortised + statistics.median(times), t_deq, statistics.median(times)
+
+
+def cpu_decode_baseline(cfg, table, layers_per_sample, steps):
+    """Bounded sample: `layers_per_sample` layer(s) x full batch, timed on all host cores and
+    scaled linearly to the full depth (decode cost is linear in layers)."""
+    import numpy as np
+    cores = os.cpu_count() or 1
+    n_units = layers_per_sample * cfg["batch"]
+    units = [(_layer_to_np(pl), None if nv is None else nv.detach().cpu().numpy())
+             for pl, nv in table.source[:n_units]]
+    rng = np.random.default_rng(0)
+    q = [(rng.standard_normal((n_units, cfg["q_heads"], 128)) / 128 ** 0.5).astype(np.float32) for _ in range(2)]
+    per_step, t_deq, t_att = cpu_attend_time(units, q, cores, steps)
+    full_step = per_step * cfg["layers"] / layers_per_sample
+    return {"value": cfg["batch"] / full_step, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"{layers_per_sample} of {cfg['layers']} layers x batch {cfg['batch']} x {cfg['kv_heads']} heads, "
+                      f"{steps} steps, numpy dequantise-then-attend on {cores} threads; dequantise "
+                      f"({t_deq:.2f}s) amortised over 256 steps + attend {t_att:.3f}s/step; scaled linearly to 32 layers"}
+
+
+def run_reference_arm(args, rank, world):
+    """The reference's CPU path (numpy restatement under oracle/) on the host cores, rank 0 only."""
+    if rank != 0:
+        return None
+    import numpy as np
+    from oracle import ref_packing as RP
+    from rdkv_b200 import synth
+    cfg = dict(CFG3)
+    if args.small:
+        cfg.update(layers=2, batch=2, context=4096, budget=1024)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = cfg["q_heads"] // cfg["kv_heads"]
+    units = []
+    for seq in range(cfg["batch"]):
+        seed = synth.unit_seed(cfg["config_id"], 0, seq)
+        K, V = synth.make_kv(cfg["kv_heads"], cfg["context"], seed=seed)
+        vb = synth.make_v_bits(cfg["kv_heads"], cfg["context"], cfg["budget"], seed=seed)
+        kb = synth.make_k_bits(cfg["kv_heads"], seed=seed)
+        units.append(RP.pack_kv(K.numpy(), V.numpy(), vb.numpy(), kb.numpy(), g))
+    rng = np.random.default_rng(0)
+    q = [(rng.standard_normal((len(units), cfg["q_heads"], 128)) / 128 ** 0.5).astype(np.float32) for _ in range(4)]
+    cpu_attend_time(units, q, cores, max(1, args.warmup))
+    per_step, t_deq, t_att = cpu_attend_time(units, q, cores, args.steps)
+    full_step = per_step * cfg["layers"]
+    value = cfg["batch"] / full_step
+    sample = (f"each step = 1 of {cfg['layers']} layers x batch {cfg['batch']} x {cfg['kv_heads']} heads "
+              f"(dequantise {t_deq:.2f}s amortised over 256 steps + attend {t_att:.3f}s), scaled linearly to "
+              f"{cfg['layers']} layers; numpy on {cores} threads")
+    return {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": full_step * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (numpy)", "data": "synthetic",
+        "config": {"workload": "config 3 decode (same as the CUDA arm)", "batch": cfg["batch"],
+                   "layers": cfg["layers"], "kv_heads": cfg["kv_heads"], "q_heads": cfg["q_heads"],
+                   "token_budget": cfg["budget"], "context": cfg["context"], "small": bool(args.small)},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="rdkv_b200", choices=["rdkv_b200", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "pack", "alloc"])
+    ap.add_argument("--small", action="store_true", help="2 layers x batch 2 (profiling-sized case)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        line = run_reference_arm(args, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    try:
+        if args.workload == "decode":
+            line = run_decode(args, rank, world, device)
+        else:
+            from rdkv_b200 import bench_prefill
+            line = bench_prefill.run(args, rank, world, device)
+        if rank == 0 and line is not None:
+            print(json.dumps(line), flush=True)
+    finally:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -41,6 +41,7 @@ class DecodeTable:
             raise ValueError(f"H_q={H_q} is not a multiple of H_kv={self.H_kv}")
         self.device = torch.device(device) if device is not None else layers[0].K_ch_scale.device
         self._keep: List = []
+        self.source = list(zip(layers, new_v_only))
         views = (LayerView * len(layers))()
         max_t_k = 0
         for i, (pl, nv) in enumerate(zip(layers, new_v_only)):
