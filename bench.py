@@ -209,9 +209,10 @@ def run_decode(args, rank, world, device):
         for i in range(args.steps):
             tb = tables[i % R]
             ev[i][0].record()
-            part = decode_attention_partial(q_pool[i % n_q], tb)
+            part = decode_attention_partial(q_pool[i % n_q], tb, out)
             ev[i][1].record()
-            lse_combine(part, out.view(-1, 128))
+            if tb.n_chunks > 1:
+                lse_combine(part, out.view(-1, 128))
         torch.cuda.synchronize()
     fused_ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
     fused_ms = max_over_ranks(fused_ms, world, device)
@@ -233,6 +234,9 @@ def run_decode(args, rank, world, device):
         e2e_ms = timed_steps(e2e_step, args.steps, barrier)
     e2e_ms = max_over_ranks(e2e_ms, world, device)
 
+    for tb in tables:
+        tb.check_status()
+    launches = 1 if tables[0].n_chunks == 1 else 2
     if rank != 0:
         return None
     peak, peak_kind = load_peaks()
@@ -253,23 +257,23 @@ def run_decode(args, rank, world, device):
             "batch": cfg["batch"], "layers": cfg["layers"], "kv_heads": H_kv, "q_heads": cfg["q_heads"],
             "token_budget": cfg["budget"], "context": cfg["context"],
             "parallelism": f"kv-head sharding x{world} (no data-path collective)",
-            "launches_per_step": 2,
+            "launches_per_step": launches,
             "l2": f"{R} cache replica(s) rotated per step, {R * step_bytes / 2**20:.0f} MiB per GPU "
                   f"> 2 x 126 MiB L2; no flush needed",
-            "small": bool(args.small),
+            "small": bool(args.small), "chunk_rows": tables[0].chunk_rows, "n_chunks": tables[0].n_chunks,
         },
         "hbm_gbs": total_step_bytes * args.steps / sec / 1e9,
         "hbm_frac_of_8tbs": total_step_bytes * args.steps / sec / 1e9 / (8000.0 * world),
         "algorithmic_bytes_per_step": total_step_bytes,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
-                     "kernel": "decode_attn_partial_kernel", "kernel_ms": fused_ms,
+                     "kernel": "decode_fused_kernel", "kernel_ms": fused_ms,
                      "algorithmic_bytes_per_launch": step_bytes},
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s",
                 "h2d_bytes_per_step": q_dev.numel() * q_dev.element_size() * world,
                 "d2h_bytes_per_step": out.numel() * out.element_size() * world,
                 "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": launches * args.steps,
         "clocks": sampler.summary(),
     }
     if world == 1 and not args.no_cpu_baseline:

@@ -82,6 +82,12 @@ typedef struct rdkv_layer_view {
   int32_t max_t_v;            /* stripe row where Zone B starts                         */
   int32_t t_k;                /* stripe rows to attend over                             */
   int32_t reserved;
+  /* Readable extent in bytes from each base pointer (0 for a NULL pointer).  The fused
+   * kernel stages 16-byte-aligned ranges and never touches memory outside
+   * [base, base + extent). */
+  int64_t k2_bytes, k4_bytes, k8_bytes;
+  int64_t v2_bytes, v4_bytes, v8_bytes, v16_bytes;
+  int64_t v_meta_bytes;       /* extent of v_scale and of v_zp                          */
 } rdkv_layer_view;
 
 /* ── library ──────────────────────────────────────────────────────────────── */
@@ -114,14 +120,23 @@ int rdkv_v_weighted_sum(const rdkv_layer_view* view, const float* w, int64_t w_r
  * Replaces the attention block of the decode loop
  * (obkv_accel/fast_decode.py:1701-1784: K kernel, mask add, softmax, V kernel)
  * for n_views (sequence, layer) pairs in one launch.  views: DEVICE array.
- * q: [n_views][H_q][128].  The stripe of every view is cut into chunks of
- * rdkv_decode_chunk_tokens() rows; chunk c of view v, query head h writes one
- * partial record at partials[((v*H_q + h)*n_chunks + c) * RDKV_PARTIAL_STRIDE].
- * n_chunks must be >= ceil(max t_k / chunk) (chunks past a view's t_k write an
- * empty record m=-inf, l=0, o=0). */
-int rdkv_decode_chunk_tokens(void);
+ * q: [n_views][H_q][128].  Every head's live rows (its 2-, 4-, 8-bit rows, then its
+ * fp16 rows; stripe padding is skipped) are cut into chunks of chunk_rows rows;
+ * chunk c of view v, query head h writes one partial record at
+ * partials[((v*H_q + h)*n_chunks + c) * RDKV_PARTIAL_STRIDE] (an empty record
+ * m=-inf, l=0, o=0 when the head has no row in that chunk).  n_chunks must be
+ * >= ceil(max live rows / chunk_rows).  With n_chunks == 1 and out != NULL the
+ * normalised result goes straight to out (fp32 [n_views][H_q][128]) and partials
+ * may be NULL.  k_row_bytes_max: largest K bytes per row (sub_2 + sub_4 + n_ch_8)
+ * over the views; it sizes the shared-memory stages (rdkv_decode_stage_bytes).
+ * status: optional device int32, OR-ed with 1 if a staging wait ran out and with 2
+ * if a view did not fit the launch (k_row_bytes_max too small, or more than 512
+ * padded channels); the affected records are then invalid.
+ * Alignment: V code tensors 4-byte, fp16 V tensor 8-byte, scale/zp 2-byte aligned. */
+int rdkv_decode_stage_bytes(int k_row_bytes_max);
 int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,
-                             int H_q, int H_kv, int n_chunks, float* partials, void* stream);
+                             int H_q, int H_kv, int chunk_rows, int n_chunks, int k_row_bytes_max,
+                             float* partials, float* out, int32_t* status, void* stream);
 
 /* Log-sum-exp merge of split-sequence partials (new; the reference has no
  * split path — it is the combine step of the fused call above and of the

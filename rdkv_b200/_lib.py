@@ -38,6 +38,9 @@ class LayerView(C.Structure):
         ("mask", C.c_void_p), ("mask_row_stride", C.c_int64),
         ("n_ch2_pad", C.c_int32), ("n_ch4_pad", C.c_int32), ("n_ch8", C.c_int32),
         ("max_t_v", C.c_int32), ("t_k", C.c_int32), ("reserved", C.c_int32),
+        ("k2_bytes", C.c_int64), ("k4_bytes", C.c_int64), ("k8_bytes", C.c_int64),
+        ("v2_bytes", C.c_int64), ("v4_bytes", C.c_int64), ("v8_bytes", C.c_int64), ("v16_bytes", C.c_int64),
+        ("v_meta_bytes", C.c_int64),
     ]
 
 
@@ -52,8 +55,8 @@ _PROTOTYPES = {
     "rdkv_sizeof_layer_view": ([], _i),
     "rdkv_k_scores": ([C.POINTER(LayerView), _p, _i, _i64, _i, _i, _i, _p, _i64, _p], _i),
     "rdkv_v_weighted_sum": ([C.POINTER(LayerView), _p, _i64, _i, _i, _p, _i64, _p], _i),
-    "rdkv_decode_chunk_tokens": ([], _i),
-    "rdkv_decode_attn_partial": ([_p, _i, _p, _i, _i, _i, _i, _p, _p], _i),
+    "rdkv_decode_stage_bytes": ([_i], _i),
+    "rdkv_decode_attn_partial": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p], _i),
     "rdkv_lse_combine": ([_p, _i64, _i, _i64, _i64, _p, _p, _p, _p], _i),
     "rdkv_partition_by_bits": ([_p, _i, _i64, _i, _i, _i, _p, _p, _p], _i),
     "rdkv_pack_v": ([_p, _i64, _i64, _i, _i, _p, _i64, _p, _i64, _i, _i, _i, _i, _i, _i,

@@ -1,5 +1,5 @@
-// Packed-KV decode attention: K-side scores, V-side weighted sum, the fused
-// split-sequence kernel and the log-sum-exp combine.
+// Packed-KV decode attention, two-stage operators: K-side scores, V-side weighted
+// sum, and the log-sum-exp combine of split-sequence partial records.
 //
 // Math follows the reference's kernels (obkv_accel/triton_k_kernel.py:14-16 "bias
 // trick"; obkv_accel/triton_v_kernel.py:1-31 layouts): scale is folded into q
@@ -11,7 +11,6 @@ namespace rdkv {
 
 thread_local int g_last_cuda_error = 0;
 
-constexpr int CHUNK_T = 128;          // stripe rows per CTA of the fused kernel
 constexpr int SCORE_THREADS = 128;
 constexpr int GP = 8;                 // query heads handled per register pass
 
@@ -201,162 +200,6 @@ v_weighted_sum_kernel(rdkv_layer_view v, const float* w, int64_t w_row_stride, i
   }
 }
 
-// ───────────────────── fused split-sequence decode attention ─────────────────
-constexpr int FUSED_THREADS = CHUNK_T;   // one thread per stripe row of the chunk
-constexpr int FUSED_WARPS = FUSED_THREADS / 32;
-
-__global__ void __launch_bounds__(FUSED_THREADS)
-decode_attn_partial_kernel(const rdkv_layer_view* __restrict__ views, const void* q, int q_dtype,
-                           int H_q, int g, int n_chunks, float* __restrict__ partials) {
-  extern __shared__ float smem[];
-  __shared__ rdkv_layer_view v;
-  __shared__ float s_bias[MAX_GROUP], s_m[MAX_GROUP], s_l[MAX_GROUP], s_corr[MAX_GROUP];
-  __shared__ float s_red[FUSED_WARPS * MAX_GROUP];
-  const int chunk = blockIdx.x, h = blockIdx.y, view_idx = blockIdx.z;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  {
-    const int* src = reinterpret_cast<const int*>(views + view_idx);
-    int* dst = reinterpret_cast<int*>(&v);
-    for (int i = threadIdx.x; i < (int)(sizeof(rdkv_layer_view) / 4); i += blockDim.x) dst[i] = src[i];
-  }
-  __syncthreads();
-  const int d_pad = v.n_ch2_pad + v.n_ch4_pad + v.n_ch8;
-  float* qs = smem;                               // [g][d_pad]
-  float* pw = qs + g * d_pad;                     // [g][CHUNK_T] weight * v-scale
-  float* red = pw + g * CHUNK_T;                  // [FUSED_WARPS][GP][128]
-  float* rec0 = partials + ((int64_t)(view_idx * H_q + h * g) * n_chunks + chunk) * RDKV_PARTIAL_STRIDE;
-  const int64_t rec_stride = (int64_t)n_chunks * RDKV_PARTIAL_STRIDE;
-
-  const HeadCounts hc = head_counts(v, h);
-  const int t0 = chunk * CHUNK_T;
-  const int t = t0 + threadIdx.x;
-  // Which rows of this chunk exist for this head.
-  const bool in_a = t < hc.t_v;
-  const bool in_b = (t >= v.max_t_v) && (t < v.max_t_v + hc.n16);
-  bool valid = (t < v.t_k) && (in_a || in_b);
-  const bool chunk_live = (t0 < hc.t_v) || (t0 + CHUNK_T > v.max_t_v && t0 < v.max_t_v + hc.n16);
-  if (!chunk_live || t0 >= v.t_k) {                // whole chunk is padding: empty records
-    for (int i = threadIdx.x; i < g * RDKV_PARTIAL_STRIDE; i += blockDim.x) {
-      const int hq = i / RDKV_PARTIAL_STRIDE, e = i % RDKV_PARTIAL_STRIDE;
-      rec0[hq * rec_stride + e] = (e == 0) ? -INFINITY : 0.f;
-    }
-    return;
-  }
-  setup_q(v, h, g, d_pad, q, q_dtype, ((int64_t)view_idx * H_q + h * g) * D, D, qs, s_bias, s_red);
-
-  float v_scale = 1.f, v_zp = 0.f;
-  if (valid && in_a) {
-    v_scale = h2f(v.v_scale[h * v.v_meta_head_stride + t]);
-    v_zp = h2f(v.v_zp[h * v.v_meta_head_stride + t]);
-  }
-  // scores, chunk max, exp, chunk sum
-  for (int hq0 = 0; hq0 < g; hq0 += GP) {
-    const int np = min(GP, g - hq0);
-    float s[GP];
-    if (valid) row_dot(v, h, t, d_pad, qs, hq0, np, s);
-#pragma unroll
-    for (int j = 0; j < GP; ++j) {
-      if (j < np) {
-        float sv = -INFINITY;
-        if (valid) {
-          sv = (s[j] - s_bias[hq0 + j]) * INV_SQRT_D;
-          if (v.mask != nullptr) sv += v.mask[(int64_t)(h * g + hq0 + j) * v.mask_row_stride + t];
-        }
-        s[j] = sv;
-        const float wm = warp_max(sv);
-        if (lane == 0) s_red[warp * MAX_GROUP + hq0 + j] = wm;
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x < np) {
-      float m = -INFINITY;
-      for (int w = 0; w < FUSED_WARPS; ++w) m = fmaxf(m, s_red[w * MAX_GROUP + hq0 + threadIdx.x]);
-      s_m[hq0 + threadIdx.x] = m;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < GP; ++j) {
-      if (j < np) {
-        const float m = s_m[hq0 + j];
-        const float p = (s[j] == -INFINITY) ? 0.f : exp2f((s[j] - m) * 1.4426950408889634f);
-        const float ps = p * v_scale;
-        pw[(hq0 + j) * CHUNK_T + threadIdx.x] = ps;
-        const float wl = warp_sum(p);
-        const float wc = warp_sum(ps * v_zp);
-        if (lane == 0) { s_red[warp * MAX_GROUP + hq0 + j] = wl; }
-        __syncwarp();
-        s[j] = wc;                       // keep the zero-point term for the second reduction
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x < np) {
-      float l = 0.f;
-      for (int w = 0; w < FUSED_WARPS; ++w) l += s_red[w * MAX_GROUP + hq0 + threadIdx.x];
-      s_l[hq0 + threadIdx.x] = l;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < GP; ++j)
-      if (j < np && lane == 0) s_red[warp * MAX_GROUP + hq0 + j] = s[j];
-    __syncthreads();
-    if (threadIdx.x < np) {
-      float c = 0.f;
-      for (int w = 0; w < FUSED_WARPS; ++w) c += s_red[w * MAX_GROUP + hq0 + threadIdx.x];
-      s_corr[hq0 + threadIdx.x] = c;
-    }
-    __syncthreads();
-  }
-
-  // weighted sum of raw codes over the chunk's rows: warp w takes rows w, w+4, ...
-  for (int hq0 = 0; hq0 < g; hq0 += GP) {
-    const int np = min(GP, g - hq0);
-    float acc[GP][4];
-#pragma unroll
-    for (int j = 0; j < GP; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    for (int i = warp; i < CHUNK_T; i += FUSED_WARPS) {
-      const int tt = t0 + i;
-      int kind;
-      int64_t seg_row;
-      if (tt < hc.t_v) {
-        kind = zone_a_kind(hc, tt, &seg_row);
-      } else if (tt >= v.max_t_v && tt < v.max_t_v + hc.n16 && tt < v.t_k) {
-        kind = 3; seg_row = tt - v.max_t_v;
-      } else {
-        continue;
-      }
-      float c[4];
-      load_v_row(v, h, kind, seg_row, lane, c);
-#pragma unroll
-      for (int j = 0; j < GP; ++j) {
-        if (j < np) {
-          const float ps = pw[(hq0 + j) * CHUNK_T + i];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) acc[j][k] = fmaf(ps, c[k], acc[j][k]);
-        }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < GP; ++j)
-#pragma unroll
-      for (int k = 0; k < 4; ++k) red[(warp * GP + j) * D + lane + 32 * k] = acc[j][k];
-    __syncthreads();
-    for (int i = threadIdx.x; i < np * D; i += blockDim.x) {
-      const int j = i / D, d = i % D;
-      float s = 0.f;
-#pragma unroll
-      for (int w = 0; w < FUSED_WARPS; ++w) s += red[(w * GP + j) * D + d];
-      rec0[(hq0 + j) * rec_stride + 4 + d] = s - s_corr[hq0 + j];
-    }
-    if (threadIdx.x < np) {
-      float* r = rec0 + (hq0 + threadIdx.x) * rec_stride;
-      r[0] = s_m[hq0 + threadIdx.x];
-      r[1] = s_l[hq0 + threadIdx.x];
-      r[2] = 0.f; r[3] = 0.f;
-    }
-    __syncthreads();
-  }
-}
-
 // ───────────────────────────── LSE combine ───────────────────────────────────
 __global__ void __launch_bounds__(D)
 lse_combine_kernel(const float* __restrict__ partials, int n_splits, int64_t row_stride,
@@ -397,8 +240,6 @@ static int check_view_dims(int H_q, int H_kv) {
 
 using namespace rdkv;
 
-extern "C" int rdkv_decode_chunk_tokens(void) { return CHUNK_T; }
-
 extern "C" int rdkv_k_scores(const rdkv_layer_view* view, const void* q, int q_dtype,
                              int64_t q_row_stride, int H_q, int H_kv, int t_eff, float* out,
                              int64_t out_row_stride, void* stream) {
@@ -436,29 +277,6 @@ extern "C" int rdkv_v_weighted_sum(const rdkv_layer_view* view, const float* w, 
   }
   v_weighted_sum_kernel<<<H_kv, VSUM_THREADS, smem, (cudaStream_t)stream>>>(*view, w, w_row_stride, g, out,
                                                                            out_row_stride);
-  return launch_status();
-}
-
-extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const void* q,
-                                        int q_dtype, int H_q, int H_kv, int n_chunks, float* partials,
-                                        void* stream) {
-  if (views == nullptr || q == nullptr || partials == nullptr || n_views < 0 || n_chunks <= 0)
-    return RDKV_ERR_BAD_ARG;
-  if (q_dtype < RDKV_F16 || q_dtype > RDKV_F32) return RDKV_ERR_BAD_ARG;
-  int st = check_view_dims(H_q, H_kv);
-  if (st != RDKV_OK) return st;
-  if (n_views == 0) return RDKV_OK;
-  if (n_views > 65535 || H_kv > 65535) return RDKV_ERR_TOO_LARGE;
-  const int g = H_q / H_kv;
-  const size_t smem = sizeof(float) * ((size_t)g * 3 * D + (size_t)g * CHUNK_T + FUSED_WARPS * GP * D);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(decode_attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * ((size_t)MAX_GROUP * 3 * D + (size_t)MAX_GROUP * CHUNK_T + FUSED_WARPS * GP * D)));
-    attr_done = true;
-  }
-  dim3 grid(n_chunks, H_kv, n_views);
-  decode_attn_partial_kernel<<<grid, FUSED_THREADS, smem, (cudaStream_t)stream>>>(
-      views, q, q_dtype, H_q, g, n_chunks, partials);
   return launch_status();
 }
 

@@ -1,0 +1,648 @@
+// Fused split-sequence decode attention over the packed cache (sm_100a).
+//
+// One CTA = (view, KV head, chunk of live rows); 4 warps, each an independent
+// worker with its own 3-stage ring of shared-memory tiles filled by 1-D TMA bulk
+// copies (cp.async.bulk + mbarrier).  Per 16 rows a warp
+//   * computes q.K scores on the tensor cores (mma.sync m16n8k16, query heads on M,
+//     rows on N): packed 2/4/8-bit K codes are masked in place into fp16
+//     SUBNORMAL integers (code * 2^-24, exact), so unpacking is one AND per pair
+//     of codes; bit-position factors (4^v, 16) are folded into q*scale;
+//   * keeps an online softmax per query head (lazy rescale);
+//   * feeds exp(s-m)*v_scale as the B operand of the P.V product with V codes,
+//     again masked in place, as the A operand (channels on M, rows on K).
+// The score fragments of the first product are, element for element, the B
+// fragments of the second, so probabilities never leave registers.
+// Zero points are handled outside the products: sum_c zp*q*scale once per CTA
+// (K side, reference "bias trick", obkv_accel/triton_k_kernel.py:14-16) and
+// sum_t p*scale*zp per head (V side).
+#include "rdkv_common.cuh"
+
+namespace rdkv {
+
+constexpr int FW = 4;                  // warps per CTA
+constexpr int FSTAGES = 3;             // ring depth per warp
+constexpr int TILE_MAX = 64;           // rows per tile (2-bit and 4-bit phases)
+constexpr int V_STAGE = 4096;          // V payload bytes per stage
+constexpr int GH = 8;                  // query heads per CTA pass (N of the P.V product)
+constexpr unsigned WAIT_LIMIT = 1u << 24;
+constexpr float TWO24 = 16777216.f;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__host__ __device__ constexpr int phase_tile_rows(int p) { return p == 0 ? 64 : p == 1 ? 64 : p == 2 ? 32 : 16; }
+
+__host__ __device__ inline int align16i(int x) { return (x + 15) & ~15; }
+
+struct StageLayout {                   // byte offsets inside one stage
+  int v, k2, k4, k8, sc, zp, total;
+};
+
+__host__ __device__ inline StageLayout stage_layout(int sub2, int sub4, int n8) {
+  StageLayout L;
+  L.v = 0;
+  L.k2 = V_STAGE + 32;
+  L.k4 = L.k2 + align16i(TILE_MAX * sub2) + 48;
+  L.k8 = L.k4 + align16i(TILE_MAX * sub4) + 48;
+  L.sc = L.k8 + align16i(TILE_MAX * n8) + 48;
+  L.zp = L.sc + TILE_MAX * 2 + 32;
+  L.total = L.zp + TILE_MAX * 2 + 32;
+  return L;
+}
+
+__host__ __device__ inline int stage_capacity(int k_row_bytes_max) {
+  return V_STAGE + 32 + TILE_MAX * k_row_bytes_max + 3 * 64 + 2 * (TILE_MAX * 2 + 32);
+}
+
+// ── PTX wrappers ─────────────────────────────────────────────────────────────
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Global -> shared bulk copy; src, dst and bytes are multiples of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  return __byte_perm(a, b, sel);
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+// 32 bits starting at an arbitrary byte offset of a shared-memory buffer.
+// `base` must be 4-byte aligned.
+__device__ __forceinline__ uint32_t lds_unaligned(const unsigned char* base, int off) {
+  const uint32_t* p = reinterpret_cast<const uint32_t*>(base + (off & ~3));
+  return __funnelshift_r(p[0], p[1], (off & 3) * 8);
+}
+
+// ── K channel-slot map: which padded channel slot feeds MMA k-index e of thread j ──
+// e = 0..3 stands for k = 2j, 2j+1, 2j+8, 2j+9.  Returns the slot or -1, and the
+// power-of-two factor the masked code carries (folded into q*scale).
+struct KDims { int sub2, sub4, n8, n2p, n4p, nsp2, nsp4, nkb8, nkb; };
+
+__host__ __device__ inline KDims k_dims(int n2p, int n4p, int n8) {
+  KDims d;
+  d.n2p = n2p; d.n4p = n4p; d.n8 = n8;
+  d.sub2 = n2p >> 2; d.sub4 = n4p >> 1;
+  d.nsp2 = (d.sub2 + 7) >> 3; d.nsp4 = (d.sub4 + 15) >> 4; d.nkb8 = (n8 + 15) >> 4;
+  d.nkb = 2 * d.nsp2 + 2 * d.nsp4 + d.nkb8;
+  return d;
+}
+
+__device__ inline int k_slot(const KDims& d, int kb, int j, int e, float* factor) {
+  if (kb < 2 * d.nsp2) {
+    const int s = kb >> 1, half = kb & 1;
+    const int i = 8 * s + 2 * j + (e & 1), v = 2 * half + (e >> 1);
+    *factor = (float)(1 << (2 * v));
+    return i < d.sub2 ? i + v * d.sub2 : -1;
+  }
+  kb -= 2 * d.nsp2;
+  if (kb < 2 * d.nsp4) {
+    const int s = kb >> 1, half = kb & 1;
+    const int i = 16 * s + 4 * j + half + 2 * (e & 1), hi = e >> 1;
+    *factor = hi ? 16.f : 1.f;
+    return i < d.sub4 ? d.n2p + i + hi * d.sub4 : -1;
+  }
+  kb -= 2 * d.nsp4;
+  const int i = 16 * kb + 4 * j + (e >> 1) + 2 * (e & 1);
+  *factor = 1.f;
+  return i < d.n8 ? d.n2p + d.n4p + i : -1;
+}
+
+// Accumulator unit exponent: true value = acc * 2^E(phase, v), v = m-tile & 3.
+__device__ __forceinline__ int acc_exp(int phase, int v) {
+  return phase == 0 ? 24 - 2 * v : phase == 1 ? 24 - 4 * (v >> 1) : phase == 2 ? 24 : 0;
+}
+
+struct Phases { int lo[4], hi[4], first_tile[5]; };   // live-row ranges of this CTA per phase
+
+struct TileDesc { int phase, u0, n; };
+
+__device__ __forceinline__ TileDesc tile_of(const Phases& ph, int idx) {
+  TileDesc t;
+  int p = 0;
+#pragma unroll
+  for (int k = 1; k < 4; ++k)
+    if (idx >= ph.first_tile[k]) p = k;
+  t.phase = p;
+  const int tr = phase_tile_rows(p);
+  t.u0 = ph.lo[p] + (idx - ph.first_tile[p]) * tr;
+  t.n = min(tr, ph.hi[p] - t.u0);
+  return t;
+}
+
+// Stage one byte range: the byte at global address x lands at dst + (x - (src & ~15)).
+// Interior 16-byte blocks go by bulk copy (returns their byte count for expect_tx when
+// `issue` is false); bytes before the tensor's first or after its last whole block are
+// copied by the lanes with plain loads.
+__device__ __forceinline__ uint32_t range_bulk_bytes(const unsigned char* src, int len, const unsigned char* t_lo,
+                                                     const unsigned char* t_hi, uintptr_t* blo, uintptr_t* bhi) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(src);
+  uintptr_t lo = a & ~(uintptr_t)15, hi = (a + len + 15) & ~(uintptr_t)15;
+  const uintptr_t tl = (reinterpret_cast<uintptr_t>(t_lo) + 15) & ~(uintptr_t)15;
+  const uintptr_t th = reinterpret_cast<uintptr_t>(t_hi) & ~(uintptr_t)15;
+  if (lo < tl) lo = tl;
+  if (hi > th) hi = th;
+  if (hi <= lo) { *blo = *bhi = a; return 0; }
+  *blo = lo; *bhi = hi;
+  return (uint32_t)(hi - lo);
+}
+
+struct RangeSpec { const unsigned char* src; int len; const unsigned char* t_lo; const unsigned char* t_hi; int dst_off; };
+
+__global__ void __launch_bounds__(FW * 32, 2)
+decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __restrict__ q, int q_dtype,
+                    int H_q, int g, int chunk_rows, int n_chunks, int stage_bytes,
+                    float* __restrict__ partials, float* __restrict__ out, int* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ rdkv_layer_view v;
+  __shared__ __align__(8) uint64_t bars[FW][FSTAGES];
+  __shared__ float s_bias[GH];
+  __shared__ float s_ml[FW][GH][3];               // per warp: m, l, zero-point term
+
+  const int chunk = blockIdx.x, view_idx = blockIdx.z;
+  const int n_hgrp = (g + GH - 1) / GH;
+  const int h = blockIdx.y / n_hgrp, hgrp = blockIdx.y % n_hgrp;
+  const int gh0 = hgrp * GH, gcnt = min(GH, g - gh0);     // query heads [gh0, gh0+gcnt) of this KV head
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, j = lane & 3;
+
+  {
+    const int* src = reinterpret_cast<const int*>(views + view_idx);
+    int* dst = reinterpret_cast<int*>(&v);
+    for (int i = tid; i < (int)(sizeof(rdkv_layer_view) / 4); i += blockDim.x) dst[i] = src[i];
+  }
+  if (tid < FW * FSTAGES) mbar_init(&bars[tid / FSTAGES][tid % FSTAGES], 1);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+
+  const int hq0 = h * g + gh0;                             // first query head handled here
+  float* rec0 = partials != nullptr
+                    ? partials + ((int64_t)(view_idx * H_q + hq0) * n_chunks + chunk) * RDKV_PARTIAL_STRIDE
+                    : nullptr;
+  const int64_t rec_stride = (int64_t)n_chunks * RDKV_PARTIAL_STRIDE;
+  const bool direct = (n_chunks == 1 && out != nullptr);
+
+  const KDims kd = k_dims(v.n_ch2_pad, v.n_ch4_pad, v.n_ch8);
+  const int d_pad = kd.n2p + kd.n4p + kd.n8;
+  const StageLayout SL = stage_layout(kd.sub2, kd.sub4, kd.n8);
+  const HeadCounts hc = head_counts(v, h);
+
+  // live rows of this head: [0,n2) 2-bit, [n2,n2+n4) 4-bit, [.., t_v) 8-bit, [t_v, t_v+n16) fp16
+  Phases ph;
+  {
+    const int c0 = chunk * chunk_rows, c1 = c0 + chunk_rows;
+    const int b[5] = {0, hc.n2, hc.n2 + hc.n4, hc.t_v, hc.t_v + hc.n16};
+    int acc_tiles = 0;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      ph.lo[p] = max(b[p], c0);
+      ph.hi[p] = min(b[p + 1], c1);
+      if (ph.hi[p] < ph.lo[p]) ph.hi[p] = ph.lo[p];
+      ph.first_tile[p] = acc_tiles;
+      acc_tiles += (ph.hi[p] - ph.lo[p] + phase_tile_rows(p) - 1) / phase_tile_rows(p);
+    }
+    ph.first_tile[4] = acc_tiles;
+  }
+  const int total_tiles = ph.first_tile[4];
+  const bool bad_view = SL.total > stage_bytes || d_pad <= 0 || kd.nkb > 32 ||
+                        (v.n_v16 == nullptr && v.v16 == nullptr && hc.n16 > 0);
+
+  if (total_tiles == 0 || bad_view) {                      // nothing live here: empty records
+    if (bad_view && tid == 0 && status != nullptr) atomicOr(status, 2);
+    if (direct) {
+      for (int i = tid; i < gcnt * D; i += blockDim.x) out[((int64_t)view_idx * H_q + hq0) * D + i] = 0.f;
+    } else {
+      for (int i = tid; i < gcnt * RDKV_PARTIAL_STRIDE; i += blockDim.x) {
+        const int hq = i / RDKV_PARTIAL_STRIDE, e = i % RDKV_PARTIAL_STRIDE;
+        rec0[hq * rec_stride + e] = (e == 0) ? -INFINITY : 0.f;
+      }
+    }
+    return;
+  }
+
+  // ── q*scale in MMA A-fragment order, and the zero-point bias ────────────────
+  unsigned char* stage_base = smem_raw;                    // [FW][FSTAGES][stage_bytes]
+  uint2* qsA = reinterpret_cast<uint2*>(smem_raw + (size_t)FW * FSTAGES * stage_bytes);   // [nkb][32]
+  {
+    float* qs = reinterpret_cast<float*>(stage_base);      // [GH][d_pad] scratch before staging starts
+    const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
+    const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
+    for (int i = tid; i < GH * d_pad; i += blockDim.x) {
+      const int hq = i / d_pad, c = i % d_pad;
+      float val = 0.f;
+      if (hq < gcnt) val = load_q(q, q_dtype, ((int64_t)view_idx * H_q + hq0 + hq) * D + perm[c]) * h2f(sc[c]);
+      qs[i] = val;
+    }
+    __syncthreads();
+    const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
+    float bias_part = 0.f;                                 // thread (r = head, j) sums its own slots
+    for (int kb = warp; kb < kd.nkb; kb += FW) {
+      float val[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float f;
+        const int slot = k_slot(kd, kb, j, e, &f);
+        float x = 0.f;
+        if (slot >= 0) {
+          x = __half2float(__float2half_rn(qs[r * d_pad + slot] / f));
+          bias_part += h2f(zp[slot]) * (x * f);
+        }
+        val[e] = x;
+      }
+      qsA[kb * 32 + lane] = make_uint2(pack_h2(val[0], val[1]), pack_h2(val[2], val[3]));
+    }
+    bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
+    bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
+    if (j == 0) s_ml[warp][r][0] = bias_part;
+    __syncthreads();
+    if (tid < GH) s_bias[tid] = s_ml[0][tid][0] + s_ml[1][tid][0] + s_ml[2][tid][0] + s_ml[3][tid][0];
+    __syncthreads();
+  }
+
+  // ── per-warp worker ─────────────────────────────────────────────────────────
+  unsigned char* wstage = stage_base + (size_t)warp * FSTAGES * stage_bytes;
+  const float bias = s_bias[r];
+  const bool head_ok = r < gcnt;
+  const float* mask_row = (v.mask != nullptr && head_ok) ? v.mask + (int64_t)(hq0 + r) * v.mask_row_stride : nullptr;
+
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f, zc_run = 0.f;      // for head r (replicated over j with partial sums)
+  int cur_phase = -1;
+  bool timed_out = false;
+
+  auto issue_tile = [&](int tile_idx, int stage) {
+    const TileDesc t = tile_of(ph, tile_idx);
+    unsigned char* sb = wstage + (size_t)stage * stage_bytes;
+    uint64_t* bar = &bars[warp][stage];
+    // stripe row of the first live row, V segment row
+    const int64_t krow = t.phase < 3 ? t.u0 : (int64_t)v.max_t_v + (t.u0 - hc.t_v);
+    RangeSpec rs[6];
+    int nr = 0;
+    if (kd.sub2) rs[nr++] = {v.k2 + h * v.k2_head_stride + krow * kd.sub2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, SL.k2};
+    if (kd.sub4) rs[nr++] = {v.k4 + h * v.k4_head_stride + krow * kd.sub4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, SL.k4};
+    if (kd.n8) rs[nr++] = {v.k8 + h * v.k8_head_stride + krow * kd.n8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, SL.k8};
+    if (t.phase == 0) {
+      rs[nr++] = {v.v2 + h * v.v2_head_stride + (int64_t)(t.u0) * 32, t.n * 32, v.v2, v.v2 + v.v2_bytes, SL.v};
+    } else if (t.phase == 1) {
+      rs[nr++] = {v.v4 + h * v.v4_head_stride + (int64_t)(t.u0 - hc.n2) * 64, t.n * 64, v.v4, v.v4 + v.v4_bytes, SL.v};
+    } else if (t.phase == 2) {
+      rs[nr++] = {v.v8 + h * v.v8_head_stride + (int64_t)(t.u0 - hc.n2 - hc.n4) * 128, t.n * 128, v.v8,
+                  v.v8 + v.v8_bytes, SL.v};
+    } else {
+      const unsigned char* b16 = reinterpret_cast<const unsigned char*>(v.v16);
+      rs[nr++] = {b16 + (h * v.v16_head_stride + (int64_t)(t.u0 - hc.t_v) * 128) * 2, t.n * 256, b16,
+                  b16 + v.v16_bytes, SL.v};
+    }
+    if (t.phase < 3) {
+      const unsigned char* bs = reinterpret_cast<const unsigned char*>(v.v_scale);
+      const unsigned char* bz = reinterpret_cast<const unsigned char*>(v.v_zp);
+      rs[nr++] = {bs + (h * v.v_meta_head_stride + t.u0) * 2, t.n * 2, bs, bs + v.v_meta_bytes, SL.sc};
+      rs[nr++] = {bz + (h * v.v_meta_head_stride + t.u0) * 2, t.n * 2, bz, bz + v.v_meta_bytes, SL.zp};
+    }
+    uint32_t total = 0;
+    uintptr_t blo[6], bhi[6];
+    for (int i = 0; i < nr; ++i) total += range_bulk_bytes(rs[i].src, rs[i].len, rs[i].t_lo, rs[i].t_hi, &blo[i], &bhi[i]);
+    if (lane == 0) {
+      mbar_expect_tx(bar, total);
+      for (int i = 0; i < nr; ++i) {
+        if (bhi[i] > blo[i]) {
+          const uintptr_t a0 = reinterpret_cast<uintptr_t>(rs[i].src) & ~(uintptr_t)15;
+          bulk_g2s(sb + rs[i].dst_off + (blo[i] - a0), reinterpret_cast<const void*>(blo[i]),
+                   (uint32_t)(bhi[i] - blo[i]), bar);
+        }
+      }
+    }
+    // edge bytes outside the whole 16-byte blocks of the tensor (rare: tensor ends)
+    for (int i = 0; i < nr; ++i) {
+      const uintptr_t a = reinterpret_cast<uintptr_t>(rs[i].src), e = a + rs[i].len;
+      const uintptr_t a0 = a & ~(uintptr_t)15;
+      if (blo[i] > a || bhi[i] < e) {
+        const uintptr_t f1 = min(e, max(a, blo[i]));            // [a, f1): before the first whole block
+        const uintptr_t b0 = max(f1, min(e, bhi[i]));           // [b0, e): after the last whole block
+        for (uintptr_t x = a + lane; x < f1; x += 32) sb[rs[i].dst_off + (x - a0)] = *reinterpret_cast<const unsigned char*>(x);
+        for (uintptr_t x = b0 + lane; x < e; x += 32) sb[rs[i].dst_off + (x - a0)] = *reinterpret_cast<const unsigned char*>(x);
+      }
+    }
+    // rows past the tile's end must hold finite fp16 data in the fp16 phase
+    if (t.phase == 3 && (t.n & 15)) {
+      const int off = (int)(reinterpret_cast<uintptr_t>(rs[nr - 1].src) & 15);
+      uint32_t* z = reinterpret_cast<uint32_t*>(sb + SL.v + ((off + t.n * 256 + 3) & ~3));
+      const int words = ((16 - (t.n & 15)) * 256) / 4;
+      for (int i = lane; i < words; i += 32) z[i] = 0u;
+    }
+  };
+
+  int n_my = (total_tiles - warp + FW - 1) / FW;           // tiles warp, warp+FW, ...
+  if (n_my < 0) n_my = 0;
+  for (int it = 0; it < min(n_my, FSTAGES); ++it) issue_tile(warp + it * FW, it);
+
+  for (int it = 0; it < n_my; ++it) {
+    const int stage = it % FSTAGES;
+    const uint32_t parity = (it / FSTAGES) & 1;
+    {
+      unsigned spins = 0;
+      while (!mbar_try_wait(&bars[warp][stage], parity)) {
+        if (++spins > WAIT_LIMIT) { timed_out = true; break; }
+      }
+      if (__any_sync(0xffffffffu, timed_out)) { timed_out = true; break; }
+    }
+    __syncwarp();
+    const TileDesc t = tile_of(ph, warp + it * FW);
+    const unsigned char* sb = wstage + (size_t)stage * stage_bytes;
+
+    if (t.phase != cur_phase) {                            // change of accumulator units (powers of two)
+      if (cur_phase >= 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float f = exp2f((float)(acc_exp(cur_phase, i & 3) - acc_exp(t.phase, i & 3)));
+          acc[i][0] *= f; acc[i][1] *= f; acc[i][2] *= f; acc[i][3] *= f;
+        }
+      }
+      cur_phase = t.phase;
+    }
+    const int64_t krow0 = t.phase < 3 ? t.u0 : (int64_t)v.max_t_v + (t.u0 - hc.t_v);
+    const int off_k2 = kd.sub2 ? (int)(reinterpret_cast<uintptr_t>(v.k2 + h * v.k2_head_stride + krow0 * kd.sub2) & 15) : 0;
+    const int off_k4 = kd.sub4 ? (int)(reinterpret_cast<uintptr_t>(v.k4 + h * v.k4_head_stride + krow0 * kd.sub4) & 15) : 0;
+    const int off_k8 = kd.n8 ? (int)(reinterpret_cast<uintptr_t>(v.k8 + h * v.k8_head_stride + krow0 * kd.n8) & 15) : 0;
+    int off_v;
+    if (t.phase == 0) off_v = (int)(reinterpret_cast<uintptr_t>(v.v2 + h * v.v2_head_stride + (int64_t)t.u0 * 32) & 15);
+    else if (t.phase == 1) off_v = (int)(reinterpret_cast<uintptr_t>(v.v4 + h * v.v4_head_stride + (int64_t)(t.u0 - hc.n2) * 64) & 15);
+    else if (t.phase == 2) off_v = (int)(reinterpret_cast<uintptr_t>(v.v8 + h * v.v8_head_stride + (int64_t)(t.u0 - hc.n2 - hc.n4) * 128) & 15);
+    else off_v = (int)(reinterpret_cast<uintptr_t>(v.v16 + h * v.v16_head_stride + (int64_t)(t.u0 - hc.t_v) * 128) & 15);
+    const int off_m = (int)(reinterpret_cast<uintptr_t>(v.v_scale + h * v.v_meta_head_stride + t.u0) & 15);
+    const int off_z = (int)(reinterpret_cast<uintptr_t>(v.v_zp + h * v.v_meta_head_stride + t.u0) & 15);
+    const unsigned char* sk2 = sb + SL.k2;
+    const unsigned char* sk4 = sb + SL.k4;
+    const unsigned char* sk8 = sb + SL.k8;
+    const unsigned char* sv = sb + SL.v + off_v;
+    const uint16_t* ssc = reinterpret_cast<const uint16_t*>(sb + SL.sc + off_m);
+    const uint16_t* szp = reinterpret_cast<const uint16_t*>(sb + SL.zp + off_z);
+
+    for (int g16 = 0; g16 < t.n; g16 += 16) {
+      // ── scores: S[head][row] for rows g16 + {0..7} and g16 + {8..15} ──
+      float sa[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) sa[nt][0] = sa[nt][1] = sa[nt][2] = sa[nt][3] = 0.f;
+      {
+        int kb = 0;
+        for (int s = 0; s < kd.nsp2; ++s, kb += 2) {
+          const uint2 a0 = qsA[kb * 32 + lane], a1 = qsA[(kb + 1) * 32 + lane];
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const int row = g16 + 8 * nt + r;
+            const uint32_t w = lds_unaligned(sk2, off_k2 + row * kd.sub2 + 8 * s + 2 * j);
+            const uint32_t y = prmt(w, 0u, 0x4140);        // byte0 -> bits 0..7, byte1 -> bits 16..23
+            mma16816(sa[nt], a0.x, 0u, a0.y, 0u, y & 0x00030003u, y & 0x000C000Cu);
+            mma16816(sa[nt], a1.x, 0u, a1.y, 0u, y & 0x00300030u, y & 0x00C000C0u);
+          }
+        }
+        for (int s = 0; s < kd.nsp4; ++s, kb += 2) {
+          const uint2 a0 = qsA[kb * 32 + lane], a1 = qsA[(kb + 1) * 32 + lane];
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const int row = g16 + 8 * nt + r;
+            const uint32_t w = lds_unaligned(sk4, off_k4 + row * kd.sub4 + 16 * s + 4 * j);
+            const uint32_t w8 = w >> 8;
+            mma16816(sa[nt], a0.x, 0u, a0.y, 0u, w & 0x000F000Fu, w & 0x00F000F0u);
+            mma16816(sa[nt], a1.x, 0u, a1.y, 0u, w8 & 0x000F000Fu, w8 & 0x00F000F0u);
+          }
+        }
+        for (int b = 0; b < kd.nkb8; ++b, ++kb) {
+          const uint2 a0 = qsA[kb * 32 + lane];
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const int row = g16 + 8 * nt + r;
+            const uint32_t w = lds_unaligned(sk8, off_k8 + row * kd.n8 + 16 * b + 4 * j);
+            mma16816(sa[nt], a0.x, 0u, a0.y, 0u, w & 0x00FF00FFu, (w >> 8) & 0x00FF00FFu);
+          }
+        }
+      }
+      // this thread now holds, for head r, rows g16 + {2j, 2j+1, 8+2j, 9+2j}
+      float sv4[4];
+      float mloc = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = g16 + 2 * j + (e & 1) + 8 * (e >> 1);
+        float s = -INFINITY;
+        if (head_ok && row < t.n) {
+          s = (sa[e >> 1][e & 1] * TWO24 - bias) * INV_SQRT_D;
+          if (mask_row != nullptr) s += mask_row[krow0 + row];
+        }
+        sv4[e] = s;
+        mloc = fmaxf(mloc, s);
+      }
+      mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 1));
+      mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 2));
+      const float m_new = fmaxf(m_run, mloc);
+      if (__any_sync(0xffffffffu, m_new > m_run)) {        // lazy rescale: only when some head's max moved
+        const float alpha = (m_new == -INFINITY) ? 1.f : exp2f((m_run - m_new) * LOG2E);
+        l_run *= alpha; zc_run *= alpha;
+        const float a_even = __shfl_sync(0xffffffffu, alpha, (2 * j) * 4);        // head 2j lives in lanes r = 2j
+        const float a_odd = __shfl_sync(0xffffffffu, alpha, (2 * j + 1) * 4);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { acc[i][0] *= a_even; acc[i][1] *= a_odd; acc[i][2] *= a_even; acc[i][3] *= a_odd; }
+        m_run = m_new;
+      }
+      float p[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        p[e] = (sv4[e] == -INFINITY) ? 0.f : exp2f((sv4[e] - m_run) * LOG2E);
+        l_run += p[e];
+      }
+      uint32_t pb0, pb1;
+      if (t.phase < 3) {
+        float ps[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = g16 + 2 * j + (e & 1) + 8 * (e >> 1);
+          const float sc = h2f(ssc[row]), zp = h2f(szp[row]);
+          const float x = __half2float(__float2half_rn(p[e] * sc));   // the value the tensor core sees
+          const bool live = p[e] != 0.f;                   // dead rows may hold non-finite scale/zp bytes
+          ps[e] = live ? x : 0.f;
+          zc_run += live ? x * zp : 0.f;
+        }
+        pb0 = pack_h2(ps[0], ps[1]); pb1 = pack_h2(ps[2], ps[3]);
+      } else {
+        pb0 = pack_h2(p[0], p[1]); pb1 = pack_h2(p[2], p[3]);
+      }
+      // ── P.V: channels on M, rows on K; this thread supplies rows g16 + {2j,2j+1,8+2j,9+2j} ──
+      const int r0 = g16 + 2 * j;
+      if (t.phase == 2) {
+#pragma unroll
+        for (int vv = 0; vv < 4; ++vv) {
+          const unsigned char* base = sv + 4 * r + 32 * vv;
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + (r0) * 128);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + (r0 + 1) * 128);
+          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + (r0 + 8) * 128);
+          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + (r0 + 9) * 128);
+#pragma unroll
+          for (int qq = 0; qq < 2; ++qq) {
+            const uint32_t sel = qq ? 0x7632u : 0x5410u;
+            const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
+            mma16816(acc[4 * qq + vv], y01 & 0x00FF00FFu, (y01 >> 8) & 0x00FF00FFu, y23 & 0x00FF00FFu,
+                     (y23 >> 8) & 0x00FF00FFu, pb0, pb1);
+          }
+        }
+      } else if (t.phase == 1) {
+#pragma unroll
+        for (int vl = 0; vl < 2; ++vl) {
+          const unsigned char* base = sv + 4 * r + 32 * vl;
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + (r0) * 64);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + (r0 + 1) * 64);
+          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + (r0 + 8) * 64);
+          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + (r0 + 9) * 64);
+#pragma unroll
+          for (int qq = 0; qq < 2; ++qq) {
+            const uint32_t sel = qq ? 0x7632u : 0x5410u;
+            const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
+            const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
+            mma16816(acc[4 * qq + vl], y01 & 0x000F000Fu, z01 & 0x000F000Fu, y23 & 0x000F000Fu, z23 & 0x000F000Fu,
+                     pb0, pb1);
+            mma16816(acc[4 * qq + vl + 2], y01 & 0x00F000F0u, z01 & 0x00F000F0u, y23 & 0x00F000F0u,
+                     z23 & 0x00F000F0u, pb0, pb1);
+          }
+        }
+      } else if (t.phase == 0) {
+        const unsigned char* base = sv + 4 * r;
+        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + (r0) * 32);
+        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + (r0 + 1) * 32);
+        const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + (r0 + 8) * 32);
+        const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + (r0 + 9) * 32);
+#pragma unroll
+        for (int qq = 0; qq < 2; ++qq) {
+          const uint32_t sel = qq ? 0x7632u : 0x5410u;
+          const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
+          const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
+#pragma unroll
+          for (int vv = 0; vv < 4; ++vv) {
+            const uint32_t mk = 0x00030003u << (2 * vv);
+            mma16816(acc[4 * qq + vv], y01 & mk, z01 & mk, y23 & mk, z23 & mk, pb0, pb1);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int vv = 0; vv < 4; ++vv) {
+          const unsigned char* base = sv + 8 * r + 64 * vv;       // fp16 rows: channel c at byte 2c
+          const uint2 w0 = *reinterpret_cast<const uint2*>(base + (r0) * 256);
+          const uint2 w1 = *reinterpret_cast<const uint2*>(base + (r0 + 1) * 256);
+          const uint2 w2 = *reinterpret_cast<const uint2*>(base + (r0 + 8) * 256);
+          const uint2 w3 = *reinterpret_cast<const uint2*>(base + (r0 + 9) * 256);
+          mma16816(acc[vv], prmt(w0.x, w1.x, 0x5410), prmt(w0.x, w1.x, 0x7632), prmt(w2.x, w3.x, 0x5410),
+                   prmt(w2.x, w3.x, 0x7632), pb0, pb1);
+          mma16816(acc[4 + vv], prmt(w0.y, w1.y, 0x5410), prmt(w0.y, w1.y, 0x7632), prmt(w2.y, w3.y, 0x5410),
+                   prmt(w2.y, w3.y, 0x7632), pb0, pb1);
+        }
+      }
+    }
+    __syncwarp();
+    const int nxt = it + FSTAGES;
+    if (nxt < n_my) issue_tile(warp + nxt * FW, stage);
+  }
+
+  if (timed_out && lane == 0 && status != nullptr) atomicOr(status, 1);
+
+  // ── merge the four workers and write the chunk's record ─────────────────────
+  // bring the accumulators to true units
+  if (cur_phase >= 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float f = exp2f((float)acc_exp(cur_phase, i & 3));
+      acc[i][0] *= f; acc[i][1] *= f; acc[i][2] *= f; acc[i][3] *= f;
+    }
+  }
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  zc_run += __shfl_xor_sync(0xffffffffu, zc_run, 1);
+  zc_run += __shfl_xor_sync(0xffffffffu, zc_run, 2);
+  __syncthreads();                                         // every worker is done with its stages
+  float* red = reinterpret_cast<float*>(stage_base);       // [FW][GH][128]
+  if (j == 0) { s_ml[warp][r][0] = m_run; s_ml[warp][r][1] = l_run; s_ml[warp][r][2] = zc_run; }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ch = 4 * r + 2 * (i >> 2) + 32 * (i & 3);
+    float* o0 = red + ((warp * GH + 2 * j) * D);
+    float* o1 = o0 + D;
+    o0[ch] = acc[i][0]; o1[ch] = acc[i][1]; o0[ch + 1] = acc[i][2]; o1[ch + 1] = acc[i][3];
+  }
+  __syncthreads();
+  for (int i = tid; i < gcnt * D; i += blockDim.x) {
+    const int hq = i / D, d = i % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < FW; ++w) M = fmaxf(M, s_ml[w][hq][0]);
+    float L = 0.f, o = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < FW; ++w) {
+        const float mw = s_ml[w][hq][0];
+        if (mw == -INFINITY) continue;
+        const float wgt = exp2f((mw - M) * LOG2E);
+        L = fmaf(s_ml[w][hq][1], wgt, L);
+        o = fmaf(red[(w * GH + hq) * D + d] - s_ml[w][hq][2], wgt, o);
+      }
+    }
+    if (direct) {
+      out[((int64_t)view_idx * H_q + hq0 + hq) * D + d] = L > 0.f ? o / L : 0.f;
+    } else {
+      float* rec = rec0 + hq * rec_stride;
+      rec[4 + d] = o;
+      if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
+    }
+  }
+}
+
+}  // namespace rdkv
+
+using namespace rdkv;
+
+extern "C" int rdkv_decode_stage_bytes(int k_row_bytes_max) { return stage_capacity(k_row_bytes_max); }
+
+extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,
+                                        int H_q, int H_kv, int chunk_rows, int n_chunks, int k_row_bytes_max,
+                                        float* partials, float* out, int* status, void* stream) {
+  if (views == nullptr || q == nullptr || n_views < 0 || n_chunks <= 0 || chunk_rows <= 0) return RDKV_ERR_BAD_ARG;
+  if (partials == nullptr && !(n_chunks == 1 && out != nullptr)) return RDKV_ERR_BAD_ARG;
+  if (q_dtype < RDKV_F16 || q_dtype > RDKV_F32) return RDKV_ERR_BAD_ARG;
+  if (H_q <= 0 || H_kv <= 0 || H_q % H_kv != 0) return RDKV_ERR_BAD_SHAPE;
+  if (k_row_bytes_max <= 0 || k_row_bytes_max > 224) return RDKV_ERR_BAD_SHAPE;
+  if (n_views == 0) return RDKV_OK;
+  const int g = H_q / H_kv;
+  const int n_hgrp = (g + GH - 1) / GH;
+  if (n_views > 65535 || (int64_t)H_kv * n_hgrp > 65535) return RDKV_ERR_TOO_LARGE;
+  const int stage_bytes = align16i(stage_capacity(k_row_bytes_max));
+  const size_t smem = (size_t)FW * FSTAGES * stage_bytes + 32 * 32 * sizeof(uint2);
+  if (smem > 227 * 1024) return RDKV_ERR_TOO_LARGE;
+  cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
+  dim3 grid(n_chunks, H_kv * n_hgrp, n_views);
+  decode_fused_kernel<<<grid, FW * 32, smem, (cudaStream_t)stream>>>(views, q, q_dtype, H_q, g, chunk_rows,
+                                                                     n_chunks, stage_bytes, partials, out, status);
+  return launch_status();
+}

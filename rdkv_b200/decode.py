@@ -56,19 +56,43 @@ class DecodeTable:
             max_t_k = max(max_t_k, int(v.t_k))
         self.n_views = len(layers)
         self.max_t_k = max_t_k
-        self.chunk = lib().rdkv_decode_chunk_tokens()
-        self.n_chunks = max(1, (max_t_k + self.chunk - 1) // self.chunk)
+        self.k_row_bytes_max = max(
+            sum(int(t.shape[-1]) for t in (pl.K_2bit, pl.K_4bit, pl.K_8bit) if t is not None) for pl in layers)
+        for pl, nv in zip(layers, new_v_only):
+            for t, align in ((pl.V_2bit, 4), (pl.V_4bit, 4), (pl.V_8bit, 4), (nv, 8)):
+                if t is not None and t.numel() and t.data_ptr() % align:
+                    raise ValueError(f"packed V tensors must be {align}-byte aligned")
+        # chunking: enough CTAs to fill the GPU a few times over, chunks as long as possible
+        # (every chunk costs one partial record per query head)
+        n_hgrp = (self.H_q // self.H_kv + 7) // 8
+        units = self.n_views * self.H_kv * n_hgrp
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        want = max(1, -(-4 * sms // units))
+        n_chunks = max(1, min(want, -(-max(max_t_k, 1) // 128)))
+        self.chunk_rows = max(64, ((-(-max(max_t_k, 1) // n_chunks) + 63) // 64) * 64)
+        self.n_chunks = max(1, -(-max(max_t_k, 1) // self.chunk_rows))
         raw = bytes(views)
         host = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
         self.views = host.to(self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._partials: Optional[Tensor] = None
 
-    def workspace(self) -> Tensor:
-        """Split-sequence partial records [n_views*H_q, n_chunks, 132] fp32 (allocated once)."""
+    def workspace(self) -> Optional[Tensor]:
+        """Split-sequence partial records [n_views*H_q, n_chunks, 132] fp32 (allocated once);
+        None when one chunk covers every head (results are written directly)."""
+        if self.n_chunks == 1:
+            return None
         if self._partials is None:
             self._partials = torch.empty((self.n_views * self.H_q, self.n_chunks, PARTIAL_STRIDE),
                                          dtype=torch.float32, device=self.device)
         return self._partials
+
+    def check_status(self) -> None:
+        """Host read (synchronises) of the kernel's status word; raises if a launch reported a problem."""
+        st = int(self.status.item())
+        if st:
+            raise RuntimeError(f"rdkv_b200: fused decode kernel reported status {st} "
+                               "(1 = staging wait ran out, 2 = a view did not fit the launch)")
 
 
 def lse_combine(partials: Tensor, out: Optional[Tensor] = None, *, out_ml: Optional[Tensor] = None,
@@ -90,17 +114,28 @@ def lse_combine(partials: Tensor, out: Optional[Tensor] = None, *, out_ml: Optio
     return out
 
 
-def decode_attention_partial(q: Tensor, table: DecodeTable) -> Tensor:
-    """Run the fused kernel only; returns the per-chunk records (the table's workspace)."""
+def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out: Optional[Tensor]) -> None:
     require_cuda(q, "q")
     if q.shape[-1] != HEAD_DIM or q.numel() != table.n_views * table.H_q * HEAD_DIM:
         raise ValueError(f"q must be [{table.n_views},{table.H_q},{HEAD_DIM}], got {tuple(q.shape)}")
     if not q.is_contiguous():
         q = q.contiguous()
-    part = table.workspace()
     check(lib().rdkv_decode_attn_partial(ptr(table.views), table.n_views, ptr(q), q_dtype_tag(q), table.H_q,
-                                         table.H_kv, table.n_chunks, ptr(part), stream_ptr(q.device)),
+                                         table.H_kv, table.chunk_rows, table.n_chunks, table.k_row_bytes_max,
+                                         ptr(partials), ptr(out), ptr(table.status), stream_ptr(q.device)),
           "rdkv_decode_attn_partial")
+
+
+def decode_attention_partial(q: Tensor, table: DecodeTable, out: Optional[Tensor] = None) -> Tensor:
+    """The fused kernel alone: returns the per-chunk records, or ``out`` itself when a
+    single chunk covers every head (the kernel then writes normalised results)."""
+    if table.n_chunks == 1:
+        if out is None:
+            out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
+        _launch_fused(q, table, None, out)
+        return out
+    part = table.workspace()
+    _launch_fused(q, table, part, None)
     return part
 
 
@@ -111,16 +146,28 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
     q [n_views,H_q,128] fp16/bf16/fp32 -> out [n_views,H_q,128] fp32.  With
     ``out_partial`` ([n_views*H_q,132] fp32) the merged un-normalised (m, l, o)
     record per query head is written instead, for a later combine across
-    sequence shards.  Two launches, no allocation after the first call, no host
+    sequence shards.  One launch when a single chunk covers every head, else the
+    fused kernel plus the combine; no allocation after the first call, no host
     synchronisation.
     """
-    part = decode_attention_partial(q, table)
     if out_partial is not None:
-        lse_combine(part, None, out_partial=out_partial)
+        if table.n_chunks == 1:
+            _launch_fused(q, table, out_partial, None)
+        else:
+            part = table.workspace()
+            _launch_fused(q, table, part, None)
+            lse_combine(part, None, out_partial=out_partial)
         return out_partial
     if out is None:
         out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
-    lse_combine(part, out)
+    if not out.is_contiguous() or out.dtype != torch.float32:
+        raise ValueError("out must be contiguous float32 [n_views,H_q,128]")
+    if table.n_chunks == 1:
+        _launch_fused(q, table, None, out)
+    else:
+        part = table.workspace()
+        _launch_fused(q, table, part, None)
+        lse_combine(part, out.view(-1, HEAD_DIM))
     return out
 
 

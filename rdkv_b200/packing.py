@@ -584,7 +584,7 @@ def layer_view(pl: PackedKVLayer, V16: Optional[Tensor] = None, n_v16_per_head: 
     v = LayerView()
     keep = []
 
-    def put(name, t, stride_name=None, stride_dim=0, bytes_=False):
+    def put(name, t, stride_name=None, stride_dim=0, bytes_=False, extent_name=None):
         t = _squeeze_h(t)
         if t is None or t.numel() == 0:
             setattr(v, name, None)
@@ -598,13 +598,17 @@ def layer_view(pl: PackedKVLayer, V16: Optional[Tensor] = None, n_v16_per_head: 
         setattr(v, name, t.data_ptr())
         if stride_name:
             setattr(v, stride_name, t.stride(stride_dim) * (t.element_size() if bytes_ else 1))
+        if extent_name:
+            # last addressable byte + 1, relative to the base pointer
+            last = sum((n - 1) * st for n, st in zip(t.shape, t.stride()))
+            setattr(v, extent_name, (last + 1) * t.element_size())
         return t
 
     n2c, n4c, n8c = (int(x) for x in pl.K_ch_seg_bounds)
     v.n_ch2_pad, v.n_ch4_pad, v.n_ch8 = _pad_to(n2c, 4), _pad_to(n4c, 2), n8c
-    put("k2", pl.K_2bit if v.n_ch2_pad else None, "k2_head_stride", 0, True)
-    put("k4", pl.K_4bit if v.n_ch4_pad else None, "k4_head_stride", 0, True)
-    put("k8", pl.K_8bit if v.n_ch8 else None, "k8_head_stride", 0, True)
+    put("k2", pl.K_2bit if v.n_ch2_pad else None, "k2_head_stride", 0, True, "k2_bytes")
+    put("k4", pl.K_4bit if v.n_ch4_pad else None, "k4_head_stride", 0, True, "k4_bytes")
+    put("k8", pl.K_8bit if v.n_ch8 else None, "k8_head_stride", 0, True, "k8_bytes")
     sc = _squeeze_h(pl.K_ch_scale)
     put("k_scale", sc.reshape(sc.shape[0], -1) if sc is not None and sc.numel() else None)
     zp = _squeeze_h(pl.K_ch_zp)
@@ -620,12 +624,13 @@ def layer_view(pl: PackedKVLayer, V16: Optional[Tensor] = None, n_v16_per_head: 
     else:
         put("k_perm", pl.K_ch_perm_padded_idx)
         v.k_perm_head_stride = 0
-    put("v2", pl.V_2bit, "v2_head_stride", 0, True)
-    put("v4", pl.V_4bit, "v4_head_stride", 0, True)
-    put("v8", pl.V_8bit, "v8_head_stride", 0, True)
+    put("v2", pl.V_2bit, "v2_head_stride", 0, True, "v2_bytes")
+    put("v4", pl.V_4bit, "v4_head_stride", 0, True, "v4_bytes")
+    put("v8", pl.V_8bit, "v8_head_stride", 0, True, "v8_bytes")
     vs = _squeeze_h(pl.V_scale)
     vz = _squeeze_h(pl.V_zp)
-    put("v_scale", vs.reshape(vs.shape[0], -1) if vs.numel() else None, "v_meta_head_stride", 0)
+    put("v_scale", vs.reshape(vs.shape[0], -1) if vs.numel() else None, "v_meta_head_stride", 0, False,
+        "v_meta_bytes")
     put("v_zp", vz.reshape(vz.shape[0], -1) if vz.numel() else None)
     if pl.seg_bounds_per_head is not None:
         sb = pl.seg_bounds_per_head
@@ -635,7 +640,7 @@ def layer_view(pl: PackedKVLayer, V16: Optional[Tensor] = None, n_v16_per_head: 
     v.n2, v.n4, v.n8 = (int(x) for x in pl.seg_bounds)
     v.max_t_v = int(pl.T_eff if max_T_v is None else max_T_v)
     if V16 is not None and V16.numel() > 0:
-        t = put("v16", V16, "v16_head_stride", 0)
+        t = put("v16", V16, "v16_head_stride", 0, False, "v16_bytes")
         v.n_v16_shared = int(t.shape[-2])
         nv = n_v16_per_head if n_v16_per_head is not None else pl.n_v16_per_head
         if nv is not None:

@@ -33,7 +33,7 @@ def test_struct_layout_and_version():
     assert lib.rdkv_sizeof_layer_view() == ctypes.sizeof(_lib.LayerView)
     assert lib.rdkv_last_error_string(0) == b"ok"
     assert b"argument" in lib.rdkv_last_error_string(1)
-    assert lib.rdkv_decode_chunk_tokens() > 0
+    assert lib.rdkv_decode_stage_bytes(34) >= 4096 + 64 * 34
     assert lib.rdkv_pack_k_slabs(1) == 1 and lib.rdkv_pack_k_slabs(10 ** 6) <= 64
 
 
@@ -45,7 +45,7 @@ def test_argument_validation_needs_no_gpu():
     assert lib.rdkv_partition_by_bits(None, 8, 0, 1, 1, 0, None, None, None) == 1
     v = _lib.LayerView()
     assert lib.rdkv_k_scores(ctypes.byref(v), None, 0, 128, 32, 8, 16, None, 16, None) == 1
-    assert lib.rdkv_decode_attn_partial(1, 1, 1, 0, 30, 8, 1, 1, None) == 2   # H_q % H_kv != 0
+    assert lib.rdkv_decode_attn_partial(1, 1, 1, 0, 30, 8, 256, 1, 34, 1, None, None, None) == 2   # H_q % H_kv != 0
 
 
 def test_ops_refuse_cpu_tensors():
