@@ -168,6 +168,8 @@ def run_decode(args, rank, world, device):
     cfg = dict(CFG3)
     if args.small:
         cfg.update(layers=2, batch=2, context=4096, budget=1024)
+    if args.layers:
+        cfg.update(layers=args.layers)
     H_kv = cfg["kv_heads"]
     assert H_kv % world == 0, "KV heads are sharded across ranks: world size must divide 8"
     h0, h1 = rank * H_kv // world, (rank + 1) * H_kv // world
@@ -260,7 +262,7 @@ def run_decode(args, rank, world, device):
             "launches_per_step": launches,
             "l2": f"{R} cache replica(s) rotated per step, {R * step_bytes / 2**20:.0f} MiB per GPU "
                   f"> 2 x 126 MiB L2; no flush needed",
-            "small": bool(args.small), "chunk_rows": tables[0].chunk_rows, "n_chunks": tables[0].n_chunks,
+            "small": bool(args.small or args.layers), "chunk_rows": tables[0].chunk_rows, "n_chunks": tables[0].n_chunks,
         },
         "hbm_gbs": total_step_bytes * args.steps / sec / 1e9,
         "hbm_frac_of_8tbs": total_step_bytes * args.steps / sec / 1e9 / (8000.0 * world),
@@ -398,7 +400,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="rdkv_b200", choices=["rdkv_b200", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "pack", "alloc"])
-    ap.add_argument("--small", action="store_true", help="2 layers x batch 2 (profiling-sized case)")
+    ap.add_argument("--small", action="store_true", help="2 layers x batch 2 (smoke-sized case)")
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling-sized runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

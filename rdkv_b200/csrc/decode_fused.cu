@@ -1,14 +1,14 @@
 // Fused split-sequence decode attention over the packed cache (sm_100a).
 //
 // One CTA = (view, KV head, chunk of live rows); 4 warps, each an independent
-// worker with its own 3-stage ring of shared-memory tiles filled by 1-D TMA bulk
-// copies (cp.async.bulk + mbarrier).  Per 16 rows a warp
+// worker with its own ring of shared-memory tiles filled by 1-D TMA bulk copies
+// (cp.async.bulk + mbarrier).  Per 16 rows a warp
 //   * computes q.K scores on the tensor cores (mma.sync m16n8k16, query heads on M,
 //     rows on N): packed 2/4/8-bit K codes are masked in place into fp16
 //     SUBNORMAL integers (code * 2^-24, exact), so unpacking is one AND per pair
 //     of codes; bit-position factors (4^v, 16) are folded into q*scale;
-//   * keeps an online softmax per query head (lazy rescale);
-//   * feeds exp(s-m)*v_scale as the B operand of the P.V product with V codes,
+//   * keeps an online softmax per query head in base 2 (lazy rescale);
+//   * feeds exp2(s-m)*v_scale as the B operand of the P.V product with V codes,
 //     again masked in place, as the A operand (channels on M, rows on K).
 // The score fragments of the first product are, element for element, the B
 // fragments of the second, so probabilities never leave registers.
@@ -20,15 +20,18 @@
 namespace rdkv {
 
 constexpr int FW = 4;                  // warps per CTA
-constexpr int FSTAGES = 3;             // ring depth per warp
+constexpr int FSTAGES = 2;             // ring depth per warp
 constexpr int TILE_MAX = 64;           // rows per tile (2-bit and 4-bit phases)
 constexpr int V_STAGE = 4096;          // V payload bytes per stage
 constexpr int GH = 8;                  // query heads per CTA pass (N of the P.V product)
+constexpr int KB_MAX = 32;             // 16-channel blocks of the score product
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 constexpr float TWO24 = 16777216.f;
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
 
 __host__ __device__ constexpr int phase_tile_rows(int p) { return p == 0 ? 64 : p == 1 ? 64 : p == 2 ? 32 : 16; }
+__host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : p == 1 ? 64 : p == 2 ? 128 : 256; }
 
 __host__ __device__ inline int align16i(int x) { return (x + 15) & ~15; }
 
@@ -93,6 +96,11 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // 32 bits starting at an arbitrary byte offset of a shared-memory buffer.
 // `base` must be 4-byte aligned.
 __device__ __forceinline__ uint32_t lds_unaligned(const unsigned char* base, int off) {
@@ -139,48 +147,73 @@ __device__ __forceinline__ int acc_exp(int phase, int v) {
   return phase == 0 ? 24 - 2 * v : phase == 1 ? 24 - 4 * (v >> 1) : phase == 2 ? 24 : 0;
 }
 
-struct Phases { int lo[4], hi[4], first_tile[5]; };   // live-row ranges of this CTA per phase
+// Everything a worker needs to find and stage its tiles; filled once per CTA.
+struct CtaGeom {
+  int lo[4], hi[4];                    // live-row range of this CTA per phase (2-bit, 4-bit, 8-bit, fp16)
+  int first_tile[5];
+  int fast;                            // every staged range lies on whole 16-byte blocks of its tensor
+  int64_t krow[4];                     // stripe row of live row lo[p]
+  const unsigned char* k2[4];          // address of the K rows of live row lo[p]
+  const unsigned char* k4[4];
+  const unsigned char* k8[4];
+  const unsigned char* vrow[4];        // address of the V row of live row lo[p]
+  const unsigned char* sc[3];
+  const unsigned char* zp[3];
+};
 
-struct TileDesc { int phase, u0, n; };
+struct TileDesc { int phase, row0, n; };   // row0: offset from lo[phase]
 
-__device__ __forceinline__ TileDesc tile_of(const Phases& ph, int idx) {
+__device__ __forceinline__ TileDesc tile_of(const CtaGeom& G, int idx) {
   TileDesc t;
   int p = 0;
 #pragma unroll
   for (int k = 1; k < 4; ++k)
-    if (idx >= ph.first_tile[k]) p = k;
+    if (idx >= G.first_tile[k]) p = k;
   t.phase = p;
   const int tr = phase_tile_rows(p);
-  t.u0 = ph.lo[p] + (idx - ph.first_tile[p]) * tr;
-  t.n = min(tr, ph.hi[p] - t.u0);
+  t.row0 = (idx - G.first_tile[p]) * tr;
+  t.n = min(tr, G.hi[p] - G.lo[p] - t.row0);
   return t;
 }
 
-// Stage one byte range: the byte at global address x lands at dst + (x - (src & ~15)).
-// Interior 16-byte blocks go by bulk copy (returns their byte count for expect_tx when
-// `issue` is false); bytes before the tensor's first or after its last whole block are
-// copied by the lanes with plain loads.
-__device__ __forceinline__ uint32_t range_bulk_bytes(const unsigned char* src, int len, const unsigned char* t_lo,
-                                                     const unsigned char* t_hi, uintptr_t* blo, uintptr_t* bhi) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(src);
-  uintptr_t lo = a & ~(uintptr_t)15, hi = (a + len + 15) & ~(uintptr_t)15;
+// True when the 16-byte blocks covering [lo, hi) are all inside [t_lo, t_hi).
+__device__ __forceinline__ bool blocks_inside(const unsigned char* lo, const unsigned char* hi,
+                                              const unsigned char* t_lo, const unsigned char* t_hi) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(lo) & ~(uintptr_t)15;
+  const uintptr_t b = (reinterpret_cast<uintptr_t>(hi) + 15) & ~(uintptr_t)15;
+  return a >= reinterpret_cast<uintptr_t>(t_lo) && b <= reinterpret_cast<uintptr_t>(t_hi);
+}
+
+// Stage one byte range whose covering 16-byte blocks may stick out of the tensor (a
+// tensor end that is not 16-byte aligned): whole blocks inside the tensor go by bulk
+// copy, the remaining edge bytes are copied by the lanes.  The byte at global address x
+// lands at dst + (x - (src & ~15)).  Returns the bulk byte count.
+__device__ __noinline__ uint32_t stage_range_guarded(unsigned char* dst, const unsigned char* src, int len,
+                                                     const unsigned char* t_lo, const unsigned char* t_hi,
+                                                     uint64_t* bar, int lane, bool issue) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(src), e = a + len, a0 = a & ~(uintptr_t)15;
+  uintptr_t lo = a0, hi = (e + 15) & ~(uintptr_t)15;
   const uintptr_t tl = (reinterpret_cast<uintptr_t>(t_lo) + 15) & ~(uintptr_t)15;
   const uintptr_t th = reinterpret_cast<uintptr_t>(t_hi) & ~(uintptr_t)15;
   if (lo < tl) lo = tl;
   if (hi > th) hi = th;
-  if (hi <= lo) { *blo = *bhi = a; return 0; }
-  *blo = lo; *bhi = hi;
+  if (hi <= lo) { lo = hi = a; }
+  if (!issue) return (uint32_t)(hi - lo);
+  if (lane == 0 && hi > lo) bulk_g2s(dst + (lo - a0), reinterpret_cast<const void*>(lo), (uint32_t)(hi - lo), bar);
+  const uintptr_t f1 = min(e, max(a, lo));                 // [a, f1): before the first whole block
+  const uintptr_t b0 = max(f1, min(e, hi));                // [b0, e): after the last whole block
+  for (uintptr_t x = a + lane; x < f1; x += 32) dst[x - a0] = *reinterpret_cast<const unsigned char*>(x);
+  for (uintptr_t x = b0 + lane; x < e; x += 32) dst[x - a0] = *reinterpret_cast<const unsigned char*>(x);
   return (uint32_t)(hi - lo);
 }
 
-struct RangeSpec { const unsigned char* src; int len; const unsigned char* t_lo; const unsigned char* t_hi; int dst_off; };
-
-__global__ void __launch_bounds__(FW * 32, 2)
+__global__ void __launch_bounds__(FW * 32, 4)
 decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __restrict__ q, int q_dtype,
                     int H_q, int g, int chunk_rows, int n_chunks, int stage_bytes,
                     float* __restrict__ partials, float* __restrict__ out, int* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ rdkv_layer_view v;
+  __shared__ CtaGeom G;
   __shared__ __align__(8) uint64_t bars[FW][FSTAGES];
   __shared__ float s_bias[GH];
   __shared__ float s_ml[FW][GH][3];               // per warp: m, l, zero-point term
@@ -210,30 +243,61 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   const KDims kd = k_dims(v.n_ch2_pad, v.n_ch4_pad, v.n_ch8);
   const int d_pad = kd.n2p + kd.n4p + kd.n8;
   const StageLayout SL = stage_layout(kd.sub2, kd.sub4, kd.n8);
-  const HeadCounts hc = head_counts(v, h);
 
-  // live rows of this head: [0,n2) 2-bit, [n2,n2+n4) 4-bit, [.., t_v) 8-bit, [t_v, t_v+n16) fp16
-  Phases ph;
-  {
+  // ── geometry: live rows of this head are [0,n2) 2-bit, [n2,n2+n4) 4-bit, [..,t_v) 8-bit,
+  //    [t_v, t_v+n16) fp16; the chunk takes [chunk*chunk_rows, +chunk_rows) of them ──
+  if (tid == 0) {
+    const HeadCounts hc = head_counts(v, h);
     const int c0 = chunk * chunk_rows, c1 = c0 + chunk_rows;
     const int b[5] = {0, hc.n2, hc.n2 + hc.n4, hc.t_v, hc.t_v + hc.n16};
-    int acc_tiles = 0;
-#pragma unroll
+    int tiles = 0;
+    bool fast = true;
+    const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
+    const unsigned char* scb = reinterpret_cast<const unsigned char*>(v.v_scale);
+    const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
     for (int p = 0; p < 4; ++p) {
-      ph.lo[p] = max(b[p], c0);
-      ph.hi[p] = min(b[p + 1], c1);
-      if (ph.hi[p] < ph.lo[p]) ph.hi[p] = ph.lo[p];
-      ph.first_tile[p] = acc_tiles;
-      acc_tiles += (ph.hi[p] - ph.lo[p] + phase_tile_rows(p) - 1) / phase_tile_rows(p);
+      int lo = max(b[p], c0), hi = min(b[p + 1], c1);
+      if (hi < lo) hi = lo;
+      G.lo[p] = lo; G.hi[p] = hi;
+      G.first_tile[p] = tiles;
+      tiles += (hi - lo + phase_tile_rows(p) - 1) / phase_tile_rows(p);
+      const int64_t krow = p < 3 ? lo : (int64_t)v.max_t_v + (lo - hc.t_v);   // stripe row
+      const int n = hi - lo;
+      G.krow[p] = krow;
+      G.k2[p] = kd.sub2 ? v.k2 + h * v.k2_head_stride + krow * kd.sub2 : nullptr;
+      G.k4[p] = kd.sub4 ? v.k4 + h * v.k4_head_stride + krow * kd.sub4 : nullptr;
+      G.k8[p] = kd.n8 ? v.k8 + h * v.k8_head_stride + krow * kd.n8 : nullptr;
+      const unsigned char* vb; const unsigned char* vlo; int64_t vext;
+      if (p == 0) { vlo = v.v2; vext = v.v2_bytes; vb = v.v2 + h * v.v2_head_stride + (int64_t)lo * 32; }
+      else if (p == 1) { vlo = v.v4; vext = v.v4_bytes; vb = v.v4 + h * v.v4_head_stride + (int64_t)(lo - hc.n2) * 64; }
+      else if (p == 2) { vlo = v.v8; vext = v.v8_bytes; vb = v.v8 + h * v.v8_head_stride + (int64_t)(lo - hc.n2 - hc.n4) * 128; }
+      else { vlo = v16b; vext = v.v16_bytes; vb = v16b + (h * v.v16_head_stride + (int64_t)(lo - hc.t_v) * 128) * 2; }
+      G.vrow[p] = vb;
+      if (n > 0) {
+        if (kd.sub2) fast = fast && blocks_inside(G.k2[p], G.k2[p] + (int64_t)n * kd.sub2, v.k2, v.k2 + v.k2_bytes);
+        if (kd.sub4) fast = fast && blocks_inside(G.k4[p], G.k4[p] + (int64_t)n * kd.sub4, v.k4, v.k4 + v.k4_bytes);
+        if (kd.n8) fast = fast && blocks_inside(G.k8[p], G.k8[p] + (int64_t)n * kd.n8, v.k8, v.k8 + v.k8_bytes);
+        fast = fast && blocks_inside(vb, vb + (int64_t)n * phase_row_bytes(p), vlo, vlo + vext);
+      }
+      if (p < 3) {
+        G.sc[p] = scb + (h * v.v_meta_head_stride + lo) * 2;
+        G.zp[p] = zpb + (h * v.v_meta_head_stride + lo) * 2;
+        if (n > 0) {
+          fast = fast && blocks_inside(G.sc[p], G.sc[p] + n * 2, scb, scb + v.v_meta_bytes);
+          fast = fast && blocks_inside(G.zp[p], G.zp[p] + n * 2, zpb, zpb + v.v_meta_bytes);
+        }
+      }
     }
-    ph.first_tile[4] = acc_tiles;
+    G.first_tile[4] = tiles;
+    G.fast = fast ? 1 : 0;
+    if (SL.total > stage_bytes || d_pad <= 0 || kd.nkb > KB_MAX || (hc.n16 > 0 && v.v16 == nullptr))
+      G.first_tile[4] = -1;                                // view does not fit this launch
   }
-  const int total_tiles = ph.first_tile[4];
-  const bool bad_view = SL.total > stage_bytes || d_pad <= 0 || kd.nkb > 32 ||
-                        (v.n_v16 == nullptr && v.v16 == nullptr && hc.n16 > 0);
+  __syncthreads();
+  const int total_tiles = G.first_tile[4];
 
-  if (total_tiles == 0 || bad_view) {                      // nothing live here: empty records
-    if (bad_view && tid == 0 && status != nullptr) atomicOr(status, 2);
+  if (total_tiles <= 0) {                                  // nothing live here: empty records
+    if (total_tiles < 0 && tid == 0 && status != nullptr) atomicOr(status, 2);
     if (direct) {
       for (int i = tid; i < gcnt * D; i += blockDim.x) out[((int64_t)view_idx * H_q + hq0) * D + i] = 0.f;
     } else {
@@ -245,21 +309,82 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     return;
   }
 
-  // ── q*scale in MMA A-fragment order, and the zero-point bias ────────────────
-  unsigned char* stage_base = smem_raw;                    // [FW][FSTAGES][stage_bytes]
+  unsigned char* wstage = smem_raw + (size_t)warp * FSTAGES * stage_bytes;
   uint2* qsA = reinterpret_cast<uint2*>(smem_raw + (size_t)FW * FSTAGES * stage_bytes);   // [nkb][32]
-  {
-    float* qs = reinterpret_cast<float*>(stage_base);      // [GH][d_pad] scratch before staging starts
-    const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
-    const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
-    for (int i = tid; i < GH * d_pad; i += blockDim.x) {
-      const int hq = i / d_pad, c = i % d_pad;
-      float val = 0.f;
-      if (hq < gcnt) val = load_q(q, q_dtype, ((int64_t)view_idx * H_q + hq0 + hq) * D + perm[c]) * h2f(sc[c]);
-      qs[i] = val;
+
+  // Stage tile `tile_idx` of this worker into ring slot `stage`.
+  auto issue_tile = [&](int tile_idx, int stage) {
+    const TileDesc t = tile_of(G, tile_idx);
+    unsigned char* sb = wstage + (size_t)stage * stage_bytes;
+    uint64_t* bar = &bars[warp][stage];
+    const int p = t.phase;
+    const unsigned char* a_k2 = G.k2[p] + (int64_t)t.row0 * kd.sub2;
+    const unsigned char* a_k4 = G.k4[p] + (int64_t)t.row0 * kd.sub4;
+    const unsigned char* a_k8 = G.k8[p] + (int64_t)t.row0 * kd.n8;
+    const unsigned char* a_v = G.vrow[p] + (int64_t)t.row0 * phase_row_bytes(p);
+    if (G.fast) {
+      if (lane == 0) {
+        const unsigned char* src[6];
+        int len[6], dst[6], nr = 0;
+        if (kd.sub2) { src[nr] = a_k2; len[nr] = t.n * kd.sub2; dst[nr++] = SL.k2; }
+        if (kd.sub4) { src[nr] = a_k4; len[nr] = t.n * kd.sub4; dst[nr++] = SL.k4; }
+        if (kd.n8) { src[nr] = a_k8; len[nr] = t.n * kd.n8; dst[nr++] = SL.k8; }
+        src[nr] = a_v; len[nr] = t.n * phase_row_bytes(p); dst[nr++] = SL.v;
+        if (p < 3) {
+          src[nr] = G.sc[p] + t.row0 * 2; len[nr] = t.n * 2; dst[nr++] = SL.sc;
+          src[nr] = G.zp[p] + t.row0 * 2; len[nr] = t.n * 2; dst[nr++] = SL.zp;
+        }
+        uint32_t total = 0;
+        uintptr_t b0[6];
+        uint32_t nb[6];
+        for (int i = 0; i < nr; ++i) {
+          const uintptr_t a = reinterpret_cast<uintptr_t>(src[i]);
+          b0[i] = a & ~(uintptr_t)15;
+          nb[i] = (uint32_t)(((a + len[i] + 15) & ~(uintptr_t)15) - b0[i]);
+          total += nb[i];
+        }
+        mbar_expect_tx(bar, total);
+        for (int i = 0; i < nr; ++i) bulk_g2s(sb + dst[i], reinterpret_cast<const void*>(b0[i]), nb[i], bar);
+      }
+    } else {
+      const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
+      const unsigned char* scb = reinterpret_cast<const unsigned char*>(v.v_scale);
+      const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
+      const unsigned char* vlo = p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : v16b;
+      const int64_t vext = p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes;
+      for (int pass = 0; pass < 2; ++pass) {               // pass 0 sums the bulk bytes, pass 1 copies
+        uint32_t total = 0;
+        const bool go = pass == 1;
+        if (kd.sub2) total += stage_range_guarded(sb + SL.k2, a_k2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, bar, lane, go);
+        if (kd.sub4) total += stage_range_guarded(sb + SL.k4, a_k4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, bar, lane, go);
+        if (kd.n8) total += stage_range_guarded(sb + SL.k8, a_k8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, bar, lane, go);
+        total += stage_range_guarded(sb + SL.v, a_v, t.n * phase_row_bytes(p), vlo, vlo + vext, bar, lane, go);
+        if (p < 3) {
+          total += stage_range_guarded(sb + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, scb, scb + v.v_meta_bytes, bar, lane, go);
+          total += stage_range_guarded(sb + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, zpb, zpb + v.v_meta_bytes, bar, lane, go);
+        }
+        if (pass == 0 && lane == 0) mbar_expect_tx(bar, total);
+      }
     }
-    __syncthreads();
+    // rows past the tile's end must hold finite fp16 data in the fp16 phase
+    if (p == 3 && (t.n & 15)) {
+      const int off = (int)(reinterpret_cast<uintptr_t>(a_v) & 15);
+      uint32_t* z = reinterpret_cast<uint32_t*>(sb + SL.v + ((off + t.n * 256 + 3) & ~3));
+      const int words = ((16 - (t.n & 15)) * 256) / 4;
+      for (int i = lane; i < words; i += 32) z[i] = 0u;
+    }
+  };
+
+  int n_my = (total_tiles - warp + FW - 1) / FW;           // tiles warp, warp+FW, ...
+  if (n_my < 0) n_my = 0;
+  for (int it = 0; it < min(n_my, FSTAGES); ++it) issue_tile(warp + it * FW, it);
+
+  // ── q*scale in MMA A-fragment order and the zero-point bias (overlaps the first copies) ──
+  {
+    const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
     const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
+    const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
+    const int64_t qoff = ((int64_t)view_idx * H_q + hq0 + r) * D;
     float bias_part = 0.f;                                 // thread (r = head, j) sums its own slots
     for (int kb = warp; kb < kd.nkb; kb += FW) {
       float val[4];
@@ -268,8 +393,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         float f;
         const int slot = k_slot(kd, kb, j, e, &f);
         float x = 0.f;
-        if (slot >= 0) {
-          x = __half2float(__float2half_rn(qs[r * d_pad + slot] / f));
+        if (slot >= 0 && r < gcnt) {
+          const float qs = load_q(q, q_dtype, qoff + perm[slot]) * h2f(sc[slot]);
+          x = __half2float(__float2half_rn(qs / f));
           bias_part += h2f(zp[slot]) * (x * f);
         }
         val[e] = x;
@@ -285,83 +411,18 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   }
 
   // ── per-warp worker ─────────────────────────────────────────────────────────
-  unsigned char* wstage = stage_base + (size_t)warp * FSTAGES * stage_bytes;
-  const float bias = s_bias[r];
   const bool head_ok = r < gcnt;
+  const float c1 = TWO24 * INV_SQRT_D * LOG2E;             // scores are kept in base-2 units
+  const float b1 = s_bias[r] * INV_SQRT_D * LOG2E;
   const float* mask_row = (v.mask != nullptr && head_ok) ? v.mask + (int64_t)(hq0 + r) * v.mask_row_stride : nullptr;
+  const bool k_aligned = !(kd.sub2 & 1) && !(kd.sub4 & 3) && !(kd.n8 & 3);
 
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f, zc_run = 0.f;      // for head r (replicated over j with partial sums)
+  float m_run = -INFINITY, l_run = 0.f, zc_run = 0.f;      // for head r (partial sums over this thread's rows)
   int cur_phase = -1;
   bool timed_out = false;
-
-  auto issue_tile = [&](int tile_idx, int stage) {
-    const TileDesc t = tile_of(ph, tile_idx);
-    unsigned char* sb = wstage + (size_t)stage * stage_bytes;
-    uint64_t* bar = &bars[warp][stage];
-    // stripe row of the first live row, V segment row
-    const int64_t krow = t.phase < 3 ? t.u0 : (int64_t)v.max_t_v + (t.u0 - hc.t_v);
-    RangeSpec rs[6];
-    int nr = 0;
-    if (kd.sub2) rs[nr++] = {v.k2 + h * v.k2_head_stride + krow * kd.sub2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, SL.k2};
-    if (kd.sub4) rs[nr++] = {v.k4 + h * v.k4_head_stride + krow * kd.sub4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, SL.k4};
-    if (kd.n8) rs[nr++] = {v.k8 + h * v.k8_head_stride + krow * kd.n8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, SL.k8};
-    if (t.phase == 0) {
-      rs[nr++] = {v.v2 + h * v.v2_head_stride + (int64_t)(t.u0) * 32, t.n * 32, v.v2, v.v2 + v.v2_bytes, SL.v};
-    } else if (t.phase == 1) {
-      rs[nr++] = {v.v4 + h * v.v4_head_stride + (int64_t)(t.u0 - hc.n2) * 64, t.n * 64, v.v4, v.v4 + v.v4_bytes, SL.v};
-    } else if (t.phase == 2) {
-      rs[nr++] = {v.v8 + h * v.v8_head_stride + (int64_t)(t.u0 - hc.n2 - hc.n4) * 128, t.n * 128, v.v8,
-                  v.v8 + v.v8_bytes, SL.v};
-    } else {
-      const unsigned char* b16 = reinterpret_cast<const unsigned char*>(v.v16);
-      rs[nr++] = {b16 + (h * v.v16_head_stride + (int64_t)(t.u0 - hc.t_v) * 128) * 2, t.n * 256, b16,
-                  b16 + v.v16_bytes, SL.v};
-    }
-    if (t.phase < 3) {
-      const unsigned char* bs = reinterpret_cast<const unsigned char*>(v.v_scale);
-      const unsigned char* bz = reinterpret_cast<const unsigned char*>(v.v_zp);
-      rs[nr++] = {bs + (h * v.v_meta_head_stride + t.u0) * 2, t.n * 2, bs, bs + v.v_meta_bytes, SL.sc};
-      rs[nr++] = {bz + (h * v.v_meta_head_stride + t.u0) * 2, t.n * 2, bz, bz + v.v_meta_bytes, SL.zp};
-    }
-    uint32_t total = 0;
-    uintptr_t blo[6], bhi[6];
-    for (int i = 0; i < nr; ++i) total += range_bulk_bytes(rs[i].src, rs[i].len, rs[i].t_lo, rs[i].t_hi, &blo[i], &bhi[i]);
-    if (lane == 0) {
-      mbar_expect_tx(bar, total);
-      for (int i = 0; i < nr; ++i) {
-        if (bhi[i] > blo[i]) {
-          const uintptr_t a0 = reinterpret_cast<uintptr_t>(rs[i].src) & ~(uintptr_t)15;
-          bulk_g2s(sb + rs[i].dst_off + (blo[i] - a0), reinterpret_cast<const void*>(blo[i]),
-                   (uint32_t)(bhi[i] - blo[i]), bar);
-        }
-      }
-    }
-    // edge bytes outside the whole 16-byte blocks of the tensor (rare: tensor ends)
-    for (int i = 0; i < nr; ++i) {
-      const uintptr_t a = reinterpret_cast<uintptr_t>(rs[i].src), e = a + rs[i].len;
-      const uintptr_t a0 = a & ~(uintptr_t)15;
-      if (blo[i] > a || bhi[i] < e) {
-        const uintptr_t f1 = min(e, max(a, blo[i]));            // [a, f1): before the first whole block
-        const uintptr_t b0 = max(f1, min(e, bhi[i]));           // [b0, e): after the last whole block
-        for (uintptr_t x = a + lane; x < f1; x += 32) sb[rs[i].dst_off + (x - a0)] = *reinterpret_cast<const unsigned char*>(x);
-        for (uintptr_t x = b0 + lane; x < e; x += 32) sb[rs[i].dst_off + (x - a0)] = *reinterpret_cast<const unsigned char*>(x);
-      }
-    }
-    // rows past the tile's end must hold finite fp16 data in the fp16 phase
-    if (t.phase == 3 && (t.n & 15)) {
-      const int off = (int)(reinterpret_cast<uintptr_t>(rs[nr - 1].src) & 15);
-      uint32_t* z = reinterpret_cast<uint32_t*>(sb + SL.v + ((off + t.n * 256 + 3) & ~3));
-      const int words = ((16 - (t.n & 15)) * 256) / 4;
-      for (int i = lane; i < words; i += 32) z[i] = 0u;
-    }
-  };
-
-  int n_my = (total_tiles - warp + FW - 1) / FW;           // tiles warp, warp+FW, ...
-  if (n_my < 0) n_my = 0;
-  for (int it = 0; it < min(n_my, FSTAGES); ++it) issue_tile(warp + it * FW, it);
 
   for (int it = 0; it < n_my; ++it) {
     const int stage = it % FSTAGES;
@@ -374,36 +435,38 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       if (__any_sync(0xffffffffu, timed_out)) { timed_out = true; break; }
     }
     __syncwarp();
-    const TileDesc t = tile_of(ph, warp + it * FW);
+    const TileDesc t = tile_of(G, warp + it * FW);
     const unsigned char* sb = wstage + (size_t)stage * stage_bytes;
+    const int p = t.phase;
 
-    if (t.phase != cur_phase) {                            // change of accumulator units (powers of two)
+    if (p != cur_phase) {                                  // change of accumulator units (powers of two)
       if (cur_phase >= 0) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float f = exp2f((float)(acc_exp(cur_phase, i & 3) - acc_exp(t.phase, i & 3)));
+          const float f = exp2f((float)(acc_exp(cur_phase, i & 3) - acc_exp(p, i & 3)));
           acc[i][0] *= f; acc[i][1] *= f; acc[i][2] *= f; acc[i][3] *= f;
         }
       }
-      cur_phase = t.phase;
+      cur_phase = p;
     }
-    const int64_t krow0 = t.phase < 3 ? t.u0 : (int64_t)v.max_t_v + (t.u0 - hc.t_v);
-    const int off_k2 = kd.sub2 ? (int)(reinterpret_cast<uintptr_t>(v.k2 + h * v.k2_head_stride + krow0 * kd.sub2) & 15) : 0;
-    const int off_k4 = kd.sub4 ? (int)(reinterpret_cast<uintptr_t>(v.k4 + h * v.k4_head_stride + krow0 * kd.sub4) & 15) : 0;
-    const int off_k8 = kd.n8 ? (int)(reinterpret_cast<uintptr_t>(v.k8 + h * v.k8_head_stride + krow0 * kd.n8) & 15) : 0;
-    int off_v;
-    if (t.phase == 0) off_v = (int)(reinterpret_cast<uintptr_t>(v.v2 + h * v.v2_head_stride + (int64_t)t.u0 * 32) & 15);
-    else if (t.phase == 1) off_v = (int)(reinterpret_cast<uintptr_t>(v.v4 + h * v.v4_head_stride + (int64_t)(t.u0 - hc.n2) * 64) & 15);
-    else if (t.phase == 2) off_v = (int)(reinterpret_cast<uintptr_t>(v.v8 + h * v.v8_head_stride + (int64_t)(t.u0 - hc.n2 - hc.n4) * 128) & 15);
-    else off_v = (int)(reinterpret_cast<uintptr_t>(v.v16 + h * v.v16_head_stride + (int64_t)(t.u0 - hc.t_v) * 128) & 15);
-    const int off_m = (int)(reinterpret_cast<uintptr_t>(v.v_scale + h * v.v_meta_head_stride + t.u0) & 15);
-    const int off_z = (int)(reinterpret_cast<uintptr_t>(v.v_zp + h * v.v_meta_head_stride + t.u0) & 15);
+    // in-stage byte offsets of the tile's first row (low address bits of the sources)
+    const int off_k2 = (int)((reinterpret_cast<uintptr_t>(G.k2[p]) + (uint32_t)(t.row0 * kd.sub2)) & 15);
+    const int off_k4 = (int)((reinterpret_cast<uintptr_t>(G.k4[p]) + (uint32_t)(t.row0 * kd.sub4)) & 15);
+    const int off_k8 = (int)((reinterpret_cast<uintptr_t>(G.k8[p]) + (uint32_t)(t.row0 * kd.n8)) & 15);
+    const int off_v = (int)((reinterpret_cast<uintptr_t>(G.vrow[p]) + (uint32_t)(t.row0 * phase_row_bytes(p))) & 15);
     const unsigned char* sk2 = sb + SL.k2;
     const unsigned char* sk4 = sb + SL.k4;
     const unsigned char* sk8 = sb + SL.k8;
     const unsigned char* sv = sb + SL.v + off_v;
-    const uint16_t* ssc = reinterpret_cast<const uint16_t*>(sb + SL.sc + off_m);
-    const uint16_t* szp = reinterpret_cast<const uint16_t*>(sb + SL.zp + off_z);
+    const unsigned char* ssc = sb + SL.sc;
+    const unsigned char* szp = sb + SL.zp;
+    int off_m = 0, off_z = 0;
+    if (p < 3) {
+      off_m = (int)((reinterpret_cast<uintptr_t>(G.sc[p]) + (uint32_t)(t.row0 * 2)) & 15);
+      off_z = (int)((reinterpret_cast<uintptr_t>(G.zp[p]) + (uint32_t)(t.row0 * 2)) & 15);
+    }
+    const bool kfast = k_aligned && !(off_k2 & 1) && !(off_k4 & 3) && !(off_k8 & 3);
+    const int64_t krow0 = G.krow[p] + t.row0;              // stripe row of the tile's first row (mask column)
 
     for (int g16 = 0; g16 < t.n; g16 += 16) {
       // ── scores: S[head][row] for rows g16 + {0..7} and g16 + {8..15} ──
@@ -411,58 +474,79 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) sa[nt][0] = sa[nt][1] = sa[nt][2] = sa[nt][3] = 0.f;
       {
+        const int rowA = g16 + r, rowB = rowA + 8;
         int kb = 0;
         for (int s = 0; s < kd.nsp2; ++s, kb += 2) {
           const uint2 a0 = qsA[kb * 32 + lane], a1 = qsA[(kb + 1) * 32 + lane];
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-            const int row = g16 + 8 * nt + r;
-            const uint32_t w = lds_unaligned(sk2, off_k2 + row * kd.sub2 + 8 * s + 2 * j);
-            const uint32_t y = prmt(w, 0u, 0x4140);        // byte0 -> bits 0..7, byte1 -> bits 16..23
-            mma16816(sa[nt], a0.x, 0u, a0.y, 0u, y & 0x00030003u, y & 0x000C000Cu);
-            mma16816(sa[nt], a1.x, 0u, a1.y, 0u, y & 0x00300030u, y & 0x00C000C0u);
+          uint32_t wA, wB;
+          if (kfast) {
+            wA = *reinterpret_cast<const uint16_t*>(sk2 + off_k2 + rowA * kd.sub2 + 8 * s + 2 * j);
+            wB = *reinterpret_cast<const uint16_t*>(sk2 + off_k2 + rowB * kd.sub2 + 8 * s + 2 * j);
+          } else {
+            wA = lds_unaligned(sk2, off_k2 + rowA * kd.sub2 + 8 * s + 2 * j);
+            wB = lds_unaligned(sk2, off_k2 + rowB * kd.sub2 + 8 * s + 2 * j);
           }
+          const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
+          mma16816(sa[0], a0.x, 0u, a0.y, 0u, yA & 0x00030003u, yA & 0x000C000Cu);
+          mma16816(sa[1], a0.x, 0u, a0.y, 0u, yB & 0x00030003u, yB & 0x000C000Cu);
+          mma16816(sa[0], a1.x, 0u, a1.y, 0u, yA & 0x00300030u, yA & 0x00C000C0u);
+          mma16816(sa[1], a1.x, 0u, a1.y, 0u, yB & 0x00300030u, yB & 0x00C000C0u);
         }
         for (int s = 0; s < kd.nsp4; ++s, kb += 2) {
           const uint2 a0 = qsA[kb * 32 + lane], a1 = qsA[(kb + 1) * 32 + lane];
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-            const int row = g16 + 8 * nt + r;
-            const uint32_t w = lds_unaligned(sk4, off_k4 + row * kd.sub4 + 16 * s + 4 * j);
-            const uint32_t w8 = w >> 8;
-            mma16816(sa[nt], a0.x, 0u, a0.y, 0u, w & 0x000F000Fu, w & 0x00F000F0u);
-            mma16816(sa[nt], a1.x, 0u, a1.y, 0u, w8 & 0x000F000Fu, w8 & 0x00F000F0u);
+          uint32_t wA, wB;
+          if (kfast) {
+            wA = *reinterpret_cast<const uint32_t*>(sk4 + off_k4 + rowA * kd.sub4 + 16 * s + 4 * j);
+            wB = *reinterpret_cast<const uint32_t*>(sk4 + off_k4 + rowB * kd.sub4 + 16 * s + 4 * j);
+          } else {
+            wA = lds_unaligned(sk4, off_k4 + rowA * kd.sub4 + 16 * s + 4 * j);
+            wB = lds_unaligned(sk4, off_k4 + rowB * kd.sub4 + 16 * s + 4 * j);
           }
+          const uint32_t vA = wA >> 8, vB = wB >> 8;
+          mma16816(sa[0], a0.x, 0u, a0.y, 0u, wA & 0x000F000Fu, wA & 0x00F000F0u);
+          mma16816(sa[1], a0.x, 0u, a0.y, 0u, wB & 0x000F000Fu, wB & 0x00F000F0u);
+          mma16816(sa[0], a1.x, 0u, a1.y, 0u, vA & 0x000F000Fu, vA & 0x00F000F0u);
+          mma16816(sa[1], a1.x, 0u, a1.y, 0u, vB & 0x000F000Fu, vB & 0x00F000F0u);
         }
         for (int b = 0; b < kd.nkb8; ++b, ++kb) {
           const uint2 a0 = qsA[kb * 32 + lane];
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-            const int row = g16 + 8 * nt + r;
-            const uint32_t w = lds_unaligned(sk8, off_k8 + row * kd.n8 + 16 * b + 4 * j);
-            mma16816(sa[nt], a0.x, 0u, a0.y, 0u, w & 0x00FF00FFu, (w >> 8) & 0x00FF00FFu);
+          uint32_t wA, wB;
+          if (kfast) {
+            wA = *reinterpret_cast<const uint32_t*>(sk8 + off_k8 + rowA * kd.n8 + 16 * b + 4 * j);
+            wB = *reinterpret_cast<const uint32_t*>(sk8 + off_k8 + rowB * kd.n8 + 16 * b + 4 * j);
+          } else {
+            wA = lds_unaligned(sk8, off_k8 + rowA * kd.n8 + 16 * b + 4 * j);
+            wB = lds_unaligned(sk8, off_k8 + rowB * kd.n8 + 16 * b + 4 * j);
           }
+          mma16816(sa[0], a0.x, 0u, a0.y, 0u, wA & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu);
+          mma16816(sa[1], a0.x, 0u, a0.y, 0u, wB & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu);
         }
       }
       // this thread now holds, for head r, rows g16 + {2j, 2j+1, 8+2j, 9+2j}
-      float sv4[4];
-      float mloc = -INFINITY;
+      const int r0 = g16 + 2 * j;
+      const bool full = g16 + 16 <= t.n;
+      float s2[4];
+      s2[0] = fmaf(sa[0][0], c1, -b1); s2[1] = fmaf(sa[0][1], c1, -b1);
+      s2[2] = fmaf(sa[1][0], c1, -b1); s2[3] = fmaf(sa[1][1], c1, -b1);
+      if (mask_row != nullptr) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = g16 + 2 * j + (e & 1) + 8 * (e >> 1);
-        float s = -INFINITY;
-        if (head_ok && row < t.n) {
-          s = (sa[e >> 1][e & 1] * TWO24 - bias) * INV_SQRT_D;
-          if (mask_row != nullptr) s += mask_row[krow0 + row];
+        for (int e = 0; e < 4; ++e) {
+          const int row = r0 + (e & 1) + 8 * (e >> 1);
+          if (row < t.n) s2[e] += mask_row[krow0 + row] * LOG2E;
         }
-        sv4[e] = s;
-        mloc = fmaxf(mloc, s);
       }
+      if (!head_ok) { s2[0] = s2[1] = s2[2] = s2[3] = -INFINITY; }
+      if (!full) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (r0 + (e & 1) + 8 * (e >> 1) >= t.n) s2[e] = -INFINITY;
+      }
+      float mloc = fmaxf(fmaxf(s2[0], s2[1]), fmaxf(s2[2], s2[3]));
       mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 1));
       mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 2));
       const float m_new = fmaxf(m_run, mloc);
       if (__any_sync(0xffffffffu, m_new > m_run)) {        // lazy rescale: only when some head's max moved
-        const float alpha = (m_new == -INFINITY) ? 1.f : exp2f((m_run - m_new) * LOG2E);
+        const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
         l_run *= alpha; zc_run *= alpha;
         const float a_even = __shfl_sync(0xffffffffu, alpha, (2 * j) * 4);        // head 2j lives in lanes r = 2j
         const float a_odd = __shfl_sync(0xffffffffu, alpha, (2 * j + 1) * 4);
@@ -470,38 +554,38 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         for (int i = 0; i < 8; ++i) { acc[i][0] *= a_even; acc[i][1] *= a_odd; acc[i][2] *= a_even; acc[i][3] *= a_odd; }
         m_run = m_new;
       }
-      float p[4];
+      const float m_safe = (m_run == -INFINITY) ? 0.f : m_run;
+      float pe[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        p[e] = (sv4[e] == -INFINITY) ? 0.f : exp2f((sv4[e] - m_run) * LOG2E);
-        l_run += p[e];
-      }
-      uint32_t pb0, pb1;
-      if (t.phase < 3) {
-        float ps[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = g16 + 2 * j + (e & 1) + 8 * (e >> 1);
-          const float sc = h2f(ssc[row]), zp = h2f(szp[row]);
-          const float x = __half2float(__float2half_rn(p[e] * sc));   // the value the tensor core sees
-          const bool live = p[e] != 0.f;                   // dead rows may hold non-finite scale/zp bytes
-          ps[e] = live ? x : 0.f;
-          zc_run += live ? x * zp : 0.f;
+      for (int e = 0; e < 4; ++e) { pe[e] = ex2(s2[e] - m_safe); l_run += pe[e]; }
+      uint32_t pb0 = pack_h2(pe[0], pe[1]), pb1 = pack_h2(pe[2], pe[3]);
+      if (p < 3) {
+        // rows r0, r0+1 and r0+8, r0+9: scale and zero point as fp16 pairs
+        uint32_t sc01 = lds_unaligned(ssc, off_m + 2 * r0), sc23 = lds_unaligned(ssc, off_m + 2 * r0 + 16);
+        uint32_t zp01 = lds_unaligned(szp, off_z + 2 * r0), zp23 = lds_unaligned(szp, off_z + 2 * r0 + 16);
+        if (!full) {                                       // dead rows may hold non-finite bytes
+          if (r0 >= t.n) { sc01 = 0u; zp01 = 0u; } else if (r0 + 1 >= t.n) { sc01 &= 0xFFFFu; zp01 &= 0xFFFFu; }
+          if (r0 + 8 >= t.n) { sc23 = 0u; zp23 = 0u; } else if (r0 + 9 >= t.n) { sc23 &= 0xFFFFu; zp23 &= 0xFFFFu; }
         }
-        pb0 = pack_h2(ps[0], ps[1]); pb1 = pack_h2(ps[2], ps[3]);
-      } else {
-        pb0 = pack_h2(p[0], p[1]); pb1 = pack_h2(p[2], p[3]);
+        const __half2 ps01 = __hmul2(*reinterpret_cast<__half2*>(&pb0), *reinterpret_cast<__half2*>(&sc01));
+        const __half2 ps23 = __hmul2(*reinterpret_cast<__half2*>(&pb1), *reinterpret_cast<__half2*>(&sc23));
+        const float2 f01 = __half22float2(ps01), f23 = __half22float2(ps23);
+        const float2 z01 = __half22float2(*reinterpret_cast<__half2*>(&zp01));
+        const float2 z23 = __half22float2(*reinterpret_cast<__half2*>(&zp23));
+        zc_run = fmaf(f01.x, z01.x, zc_run); zc_run = fmaf(f01.y, z01.y, zc_run);
+        zc_run = fmaf(f23.x, z23.x, zc_run); zc_run = fmaf(f23.y, z23.y, zc_run);
+        pb0 = *reinterpret_cast<const uint32_t*>(&ps01);
+        pb1 = *reinterpret_cast<const uint32_t*>(&ps23);
       }
       // ── P.V: channels on M, rows on K; this thread supplies rows g16 + {2j,2j+1,8+2j,9+2j} ──
-      const int r0 = g16 + 2 * j;
-      if (t.phase == 2) {
+      if (p == 2) {
+        const unsigned char* base = sv + 4 * r + r0 * 128;
 #pragma unroll
         for (int vv = 0; vv < 4; ++vv) {
-          const unsigned char* base = sv + 4 * r + 32 * vv;
-          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + (r0) * 128);
-          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + (r0 + 1) * 128);
-          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + (r0 + 8) * 128);
-          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + (r0 + 9) * 128);
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + 32 * vv);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + 32 * vv + 128);
+          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + 32 * vv + 8 * 128);
+          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + 32 * vv + 9 * 128);
 #pragma unroll
           for (int qq = 0; qq < 2; ++qq) {
             const uint32_t sel = qq ? 0x7632u : 0x5410u;
@@ -510,14 +594,14 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
                      (y23 >> 8) & 0x00FF00FFu, pb0, pb1);
           }
         }
-      } else if (t.phase == 1) {
+      } else if (p == 1) {
+        const unsigned char* base = sv + 4 * r + r0 * 64;
 #pragma unroll
         for (int vl = 0; vl < 2; ++vl) {
-          const unsigned char* base = sv + 4 * r + 32 * vl;
-          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + (r0) * 64);
-          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + (r0 + 1) * 64);
-          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + (r0 + 8) * 64);
-          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + (r0 + 9) * 64);
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + 32 * vl);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + 32 * vl + 64);
+          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + 32 * vl + 8 * 64);
+          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + 32 * vl + 9 * 64);
 #pragma unroll
           for (int qq = 0; qq < 2; ++qq) {
             const uint32_t sel = qq ? 0x7632u : 0x5410u;
@@ -529,12 +613,12 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
                      z23 & 0x00F000F0u, pb0, pb1);
           }
         }
-      } else if (t.phase == 0) {
-        const unsigned char* base = sv + 4 * r;
-        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + (r0) * 32);
-        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + (r0 + 1) * 32);
-        const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + (r0 + 8) * 32);
-        const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + (r0 + 9) * 32);
+      } else if (p == 0) {
+        const unsigned char* base = sv + 4 * r + r0 * 32;
+        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base);
+        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + 32);
+        const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + 8 * 32);
+        const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + 9 * 32);
 #pragma unroll
         for (int qq = 0; qq < 2; ++qq) {
           const uint32_t sel = qq ? 0x7632u : 0x5410u;
@@ -547,13 +631,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           }
         }
       } else {
+        const unsigned char* base = sv + 8 * r + r0 * 256;        // fp16 rows: channel c at byte 2c
 #pragma unroll
         for (int vv = 0; vv < 4; ++vv) {
-          const unsigned char* base = sv + 8 * r + 64 * vv;       // fp16 rows: channel c at byte 2c
-          const uint2 w0 = *reinterpret_cast<const uint2*>(base + (r0) * 256);
-          const uint2 w1 = *reinterpret_cast<const uint2*>(base + (r0 + 1) * 256);
-          const uint2 w2 = *reinterpret_cast<const uint2*>(base + (r0 + 8) * 256);
-          const uint2 w3 = *reinterpret_cast<const uint2*>(base + (r0 + 9) * 256);
+          const uint2 w0 = *reinterpret_cast<const uint2*>(base + 64 * vv);
+          const uint2 w1 = *reinterpret_cast<const uint2*>(base + 64 * vv + 256);
+          const uint2 w2 = *reinterpret_cast<const uint2*>(base + 64 * vv + 8 * 256);
+          const uint2 w3 = *reinterpret_cast<const uint2*>(base + 64 * vv + 9 * 256);
           mma16816(acc[vv], prmt(w0.x, w1.x, 0x5410), prmt(w0.x, w1.x, 0x7632), prmt(w2.x, w3.x, 0x5410),
                    prmt(w2.x, w3.x, 0x7632), pb0, pb1);
           mma16816(acc[4 + vv], prmt(w0.y, w1.y, 0x5410), prmt(w0.y, w1.y, 0x7632), prmt(w2.y, w3.y, 0x5410),
@@ -569,8 +653,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   if (timed_out && lane == 0 && status != nullptr) atomicOr(status, 1);
 
   // ── merge the four workers and write the chunk's record ─────────────────────
-  // bring the accumulators to true units
-  if (cur_phase >= 0) {
+  if (cur_phase >= 0) {                                    // accumulators to true units
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float f = exp2f((float)acc_exp(cur_phase, i & 3));
@@ -582,7 +665,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   zc_run += __shfl_xor_sync(0xffffffffu, zc_run, 1);
   zc_run += __shfl_xor_sync(0xffffffffu, zc_run, 2);
   __syncthreads();                                         // every worker is done with its stages
-  float* red = reinterpret_cast<float*>(stage_base);       // [FW][GH][128]
+  float* red = reinterpret_cast<float*>(smem_raw);         // [FW][GH][128]
   if (j == 0) { s_ml[warp][r][0] = m_run; s_ml[warp][r][1] = l_run; s_ml[warp][r][2] = zc_run; }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -603,7 +686,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       for (int w = 0; w < FW; ++w) {
         const float mw = s_ml[w][hq][0];
         if (mw == -INFINITY) continue;
-        const float wgt = exp2f((mw - M) * LOG2E);
+        const float wgt = ex2(mw - M);
         L = fmaf(s_ml[w][hq][1], wgt, L);
         o = fmaf(red[(w * GH + hq) * D + d] - s_ml[w][hq][2], wgt, o);
       }
@@ -613,7 +696,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     } else {
       float* rec = rec0 + hq * rec_stride;
       rec[4 + d] = o;
-      if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
+      if (d == 0) { rec[0] = M * LN2; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }   // m in natural-log units
     }
   }
 }
@@ -637,7 +720,9 @@ extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_view
   const int n_hgrp = (g + GH - 1) / GH;
   if (n_views > 65535 || (int64_t)H_kv * n_hgrp > 65535) return RDKV_ERR_TOO_LARGE;
   const int stage_bytes = align16i(stage_capacity(k_row_bytes_max));
-  const size_t smem = (size_t)FW * FSTAGES * stage_bytes + 32 * 32 * sizeof(uint2);
+  size_t smem = (size_t)FW * FSTAGES * stage_bytes + KB_MAX * 32 * sizeof(uint2);
+  const size_t epilogue = (size_t)FW * GH * D * sizeof(float);
+  if (smem < epilogue) smem = epilogue;
   if (smem > 227 * 1024) return RDKV_ERR_TOO_LARGE;
   cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
