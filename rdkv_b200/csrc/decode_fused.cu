@@ -1,8 +1,9 @@
 // Fused split-sequence decode attention over the packed cache (sm_100a).
 //
 // One CTA = (view, KV head, chunk of live rows); 4 warps, each an independent
-// worker with its own ring of shared-memory tiles filled by 1-D TMA bulk copies
-// (cp.async.bulk + mbarrier).  Per 16 rows a warp
+// worker with its own ring of shared-memory tiles filled by 16-byte cp.async copies
+// (many small ranges per tile: measured here, per-lane LDGSTS sustains them better
+// than one bulk-copy instruction per range).  Per 16 rows a warp
 //   * computes q.K scores on the tensor cores (mma.sync m16n8k16, query heads on M,
 //     rows on N): packed 2/4/8-bit K codes are masked in place into fp16
 //     SUBNORMAL integers (code * 2^-24, exact), so unpacking is one AND per pair
@@ -25,7 +26,6 @@ constexpr int TILE_MAX = 64;           // rows per tile (2-bit and 4-bit phases)
 constexpr int V_STAGE = 4096;          // V payload bytes per stage
 constexpr int GH = 8;                  // query heads per CTA pass (N of the P.V product)
 constexpr int KB_MAX = 32;             // 16-channel blocks of the score product
-constexpr unsigned WAIT_LIMIT = 1u << 24;
 constexpr float TWO24 = 16777216.f;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -59,29 +59,17 @@ __host__ __device__ inline int stage_capacity(int k_row_bytes_max) {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+// 16-byte global -> shared copy (L2 only); src and dst are 16-byte aligned.
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
+// Same, reading only the first src_bytes (< 16) bytes and zero-filling the rest.
+__device__ __forceinline__ void cp16_partial(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Global -> shared bulk copy; src, dst and bytes are multiples of 16.
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(dst)),
-               "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -184,27 +172,34 @@ __device__ __forceinline__ bool blocks_inside(const unsigned char* lo, const uns
   return a >= reinterpret_cast<uintptr_t>(t_lo) && b <= reinterpret_cast<uintptr_t>(t_hi);
 }
 
-// Stage one byte range whose covering 16-byte blocks may stick out of the tensor (a
-// tensor end that is not 16-byte aligned): whole blocks inside the tensor go by bulk
-// copy, the remaining edge bytes are copied by the lanes.  The byte at global address x
-// lands at dst + (x - (src & ~15)).  Returns the bulk byte count.
-__device__ __noinline__ uint32_t stage_range_guarded(unsigned char* dst, const unsigned char* src, int len,
-                                                     const unsigned char* t_lo, const unsigned char* t_hi,
-                                                     uint64_t* bar, int lane, bool issue) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(src), e = a + len, a0 = a & ~(uintptr_t)15;
-  uintptr_t lo = a0, hi = (e + 15) & ~(uintptr_t)15;
-  const uintptr_t tl = (reinterpret_cast<uintptr_t>(t_lo) + 15) & ~(uintptr_t)15;
-  const uintptr_t th = reinterpret_cast<uintptr_t>(t_hi) & ~(uintptr_t)15;
-  if (lo < tl) lo = tl;
-  if (hi > th) hi = th;
-  if (hi <= lo) { lo = hi = a; }
-  if (!issue) return (uint32_t)(hi - lo);
-  if (lane == 0 && hi > lo) bulk_g2s(dst + (lo - a0), reinterpret_cast<const void*>(lo), (uint32_t)(hi - lo), bar);
-  const uintptr_t f1 = min(e, max(a, lo));                 // [a, f1): before the first whole block
-  const uintptr_t b0 = max(f1, min(e, hi));                // [b0, e): after the last whole block
-  for (uintptr_t x = a + lane; x < f1; x += 32) dst[x - a0] = *reinterpret_cast<const unsigned char*>(x);
-  for (uintptr_t x = b0 + lane; x < e; x += 32) dst[x - a0] = *reinterpret_cast<const unsigned char*>(x);
-  return (uint32_t)(hi - lo);
+// Stage one byte range with 16-byte copies: the byte at global address x lands at
+// dst + (x - (src & ~15)).  All covering blocks lie inside the tensor.
+__device__ __forceinline__ void stage_range(uint32_t dst, const unsigned char* src, int len, int lane) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(src), a0 = a & ~(uintptr_t)15;
+  const int nblk = (int)((((a + len + 15) & ~(uintptr_t)15) - a0) >> 4);
+  const unsigned char* s0 = reinterpret_cast<const unsigned char*>(a0);
+  for (int b = lane; b < nblk; b += 32) cp16(dst + 16 * b, s0 + 16 * b);
+}
+
+// Same for a range whose covering blocks may stick out of the tensor [t_lo, t_hi) (a
+// tensor start or end that is not 16-byte aligned): a block crossing the end is read
+// partially and zero-filled, a block crossing the start is copied byte by byte.
+__device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const unsigned char* src, int len,
+                                                 const unsigned char* t_lo, const unsigned char* t_hi, int lane) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(src), a0 = a & ~(uintptr_t)15;
+  const uintptr_t tl = reinterpret_cast<uintptr_t>(t_lo), th = reinterpret_cast<uintptr_t>(t_hi);
+  const int nblk = (int)((((a + len + 15) & ~(uintptr_t)15) - a0) >> 4);
+  const uint32_t dst = smem_u32(dst_ptr);
+  for (int b = lane; b < nblk; b += 32) {
+    const uintptr_t lo = a0 + 16 * (uintptr_t)b;
+    if (lo < tl) {
+      for (uintptr_t x = tl; x < lo + 16 && x < th; ++x) dst_ptr[x - a0] = *reinterpret_cast<const unsigned char*>(x);
+    } else if (lo + 16 > th) {
+      if (th > lo) cp16_partial(dst + 16 * b, reinterpret_cast<const void*>(lo), (int)(th - lo));
+    } else {
+      cp16(dst + 16 * b, reinterpret_cast<const void*>(lo));
+    }
+  }
 }
 
 __global__ void __launch_bounds__(FW * 32, 4)
@@ -214,7 +209,6 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ rdkv_layer_view v;
   __shared__ CtaGeom G;
-  __shared__ __align__(8) uint64_t bars[FW][FSTAGES];
   __shared__ float s_bias[GH];
   __shared__ float s_ml[FW][GH][3];               // per warp: m, l, zero-point term
 
@@ -229,8 +223,6 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     int* dst = reinterpret_cast<int*>(&v);
     for (int i = tid; i < (int)(sizeof(rdkv_layer_view) / 4); i += blockDim.x) dst[i] = src[i];
   }
-  if (tid < FW * FSTAGES) mbar_init(&bars[tid / FSTAGES][tid % FSTAGES], 1);
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
 
   const int hq0 = h * g + gh0;                             // first query head handled here
@@ -312,39 +304,24 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   unsigned char* wstage = smem_raw + (size_t)warp * FSTAGES * stage_bytes;
   uint2* qsA = reinterpret_cast<uint2*>(smem_raw + (size_t)FW * FSTAGES * stage_bytes);   // [nkb][32]
 
-  // Stage tile `tile_idx` of this worker into ring slot `stage`.
+  // Stage tile `tile_idx` of this worker into ring slot `stage` (one cp.async group).
   auto issue_tile = [&](int tile_idx, int stage) {
     const TileDesc t = tile_of(G, tile_idx);
     unsigned char* sb = wstage + (size_t)stage * stage_bytes;
-    uint64_t* bar = &bars[warp][stage];
     const int p = t.phase;
     const unsigned char* a_k2 = G.k2[p] + (int64_t)t.row0 * kd.sub2;
     const unsigned char* a_k4 = G.k4[p] + (int64_t)t.row0 * kd.sub4;
     const unsigned char* a_k8 = G.k8[p] + (int64_t)t.row0 * kd.n8;
     const unsigned char* a_v = G.vrow[p] + (int64_t)t.row0 * phase_row_bytes(p);
     if (G.fast) {
-      if (lane == 0) {
-        const unsigned char* src[6];
-        int len[6], dst[6], nr = 0;
-        if (kd.sub2) { src[nr] = a_k2; len[nr] = t.n * kd.sub2; dst[nr++] = SL.k2; }
-        if (kd.sub4) { src[nr] = a_k4; len[nr] = t.n * kd.sub4; dst[nr++] = SL.k4; }
-        if (kd.n8) { src[nr] = a_k8; len[nr] = t.n * kd.n8; dst[nr++] = SL.k8; }
-        src[nr] = a_v; len[nr] = t.n * phase_row_bytes(p); dst[nr++] = SL.v;
-        if (p < 3) {
-          src[nr] = G.sc[p] + t.row0 * 2; len[nr] = t.n * 2; dst[nr++] = SL.sc;
-          src[nr] = G.zp[p] + t.row0 * 2; len[nr] = t.n * 2; dst[nr++] = SL.zp;
-        }
-        uint32_t total = 0;
-        uintptr_t b0[6];
-        uint32_t nb[6];
-        for (int i = 0; i < nr; ++i) {
-          const uintptr_t a = reinterpret_cast<uintptr_t>(src[i]);
-          b0[i] = a & ~(uintptr_t)15;
-          nb[i] = (uint32_t)(((a + len[i] + 15) & ~(uintptr_t)15) - b0[i]);
-          total += nb[i];
-        }
-        mbar_expect_tx(bar, total);
-        for (int i = 0; i < nr; ++i) bulk_g2s(sb + dst[i], reinterpret_cast<const void*>(b0[i]), nb[i], bar);
+      const uint32_t sbu = smem_u32(sb);
+      stage_range(sbu + SL.v, a_v, t.n * phase_row_bytes(p), lane);
+      if (kd.sub2) stage_range(sbu + SL.k2, a_k2, t.n * kd.sub2, lane);
+      if (kd.sub4) stage_range(sbu + SL.k4, a_k4, t.n * kd.sub4, lane);
+      if (kd.n8) stage_range(sbu + SL.k8, a_k8, t.n * kd.n8, lane);
+      if (p < 3) {
+        stage_range(sbu + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, lane);
+        stage_range(sbu + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, lane);
       }
     } else {
       const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
@@ -352,32 +329,31 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
       const unsigned char* vlo = p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : v16b;
       const int64_t vext = p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes;
-      for (int pass = 0; pass < 2; ++pass) {               // pass 0 sums the bulk bytes, pass 1 copies
-        uint32_t total = 0;
-        const bool go = pass == 1;
-        if (kd.sub2) total += stage_range_guarded(sb + SL.k2, a_k2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, bar, lane, go);
-        if (kd.sub4) total += stage_range_guarded(sb + SL.k4, a_k4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, bar, lane, go);
-        if (kd.n8) total += stage_range_guarded(sb + SL.k8, a_k8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, bar, lane, go);
-        total += stage_range_guarded(sb + SL.v, a_v, t.n * phase_row_bytes(p), vlo, vlo + vext, bar, lane, go);
-        if (p < 3) {
-          total += stage_range_guarded(sb + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, scb, scb + v.v_meta_bytes, bar, lane, go);
-          total += stage_range_guarded(sb + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, zpb, zpb + v.v_meta_bytes, bar, lane, go);
-        }
-        if (pass == 0 && lane == 0) mbar_expect_tx(bar, total);
+      stage_range_guarded(sb + SL.v, a_v, t.n * phase_row_bytes(p), vlo, vlo + vext, lane);
+      if (kd.sub2) stage_range_guarded(sb + SL.k2, a_k2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, lane);
+      if (kd.sub4) stage_range_guarded(sb + SL.k4, a_k4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, lane);
+      if (kd.n8) stage_range_guarded(sb + SL.k8, a_k8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, lane);
+      if (p < 3) {
+        stage_range_guarded(sb + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, scb, scb + v.v_meta_bytes, lane);
+        stage_range_guarded(sb + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, zpb, zpb + v.v_meta_bytes, lane);
       }
     }
-    // rows past the tile's end must hold finite fp16 data in the fp16 phase
+    // rows past the tile's end must hold finite fp16 data in the fp16 phase: clear the
+    // rest of the last 16-row group beyond the copied blocks
     if (p == 3 && (t.n & 15)) {
       const int off = (int)(reinterpret_cast<uintptr_t>(a_v) & 15);
-      uint32_t* z = reinterpret_cast<uint32_t*>(sb + SL.v + ((off + t.n * 256 + 3) & ~3));
-      const int words = ((16 - (t.n & 15)) * 256) / 4;
-      for (int i = lane; i < words; i += 32) z[i] = 0u;
+      const int first = (off + t.n * 256 + 15) & ~15;
+      const int last = off + ((t.n + 15) & ~15) * 256;
+      for (int i = first + 4 * lane; i < last; i += 128) *reinterpret_cast<uint32_t*>(sb + SL.v + i) = 0u;
     }
   };
 
   int n_my = (total_tiles - warp + FW - 1) / FW;           // tiles warp, warp+FW, ...
   if (n_my < 0) n_my = 0;
-  for (int it = 0; it < min(n_my, FSTAGES); ++it) issue_tile(warp + it * FW, it);
+  for (int it = 0; it < FSTAGES; ++it) {                  // one group per ring slot, empty or not
+    if (it < n_my) issue_tile(warp + it * FW, it);
+    cp_commit();
+  }
 
   // ── q*scale in MMA A-fragment order and the zero-point bias (overlaps the first copies) ──
   {
@@ -422,19 +398,11 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   float m_run = -INFINITY, l_run = 0.f, zc_run = 0.f;      // for head r (partial sums over this thread's rows)
   int cur_phase = -1;
-  bool timed_out = false;
 
   for (int it = 0; it < n_my; ++it) {
     const int stage = it % FSTAGES;
-    const uint32_t parity = (it / FSTAGES) & 1;
-    {
-      unsigned spins = 0;
-      while (!mbar_try_wait(&bars[warp][stage], parity)) {
-        if (++spins > WAIT_LIMIT) { timed_out = true; break; }
-      }
-      if (__any_sync(0xffffffffu, timed_out)) { timed_out = true; break; }
-    }
-    __syncwarp();
+    cp_wait<FSTAGES - 1>();                                // this lane's copies of tile `it` have landed
+    __syncwarp();                                          // ... and every other lane's
     const TileDesc t = tile_of(G, warp + it * FW);
     const unsigned char* sb = wstage + (size_t)stage * stage_bytes;
     const int p = t.phase;
@@ -648,9 +616,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     __syncwarp();
     const int nxt = it + FSTAGES;
     if (nxt < n_my) issue_tile(warp + nxt * FW, stage);
+    cp_commit();
   }
-
-  if (timed_out && lane == 0 && status != nullptr) atomicOr(status, 1);
+  cp_wait<0>();
 
   // ── merge the four workers and write the chunk's record ─────────────────────
   if (cur_phase >= 0) {                                    // accumulators to true units
