@@ -29,6 +29,7 @@ constexpr int KB_MAX = 32;             // 16-channel blocks of the score product
 constexpr float TWO24 = 16777216.f;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
+constexpr float RESCALE_TH = 8.f;      // log2 slack before the running maximum is moved
 
 __host__ __device__ constexpr int phase_tile_rows(int p) { return p == 0 ? 64 : p == 1 ? 64 : p == 2 ? 32 : 16; }
 __host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : p == 1 ? 64 : p == 2 ? 128 : 256; }
@@ -72,7 +73,7 @@ template <int N>
 __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -84,6 +85,14 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+// Transpose of an 8x8 matrix of 16-bit elements held one row pair per thread (thread
+// 4r+j: row r, columns 2j and 2j+1): afterwards thread 4r+j holds column r, rows 2j, 2j+1.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ float pow2i(int e) { return __int_as_float((127 + e) << 23); }
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -174,11 +183,19 @@ __device__ __forceinline__ bool blocks_inside(const unsigned char* lo, const uns
 
 // Stage one byte range with 16-byte copies: the byte at global address x lands at
 // dst + (x - (src & ~15)).  All covering blocks lie inside the tensor.
+template <int MAX_IT>
 __device__ __forceinline__ void stage_range(uint32_t dst, const unsigned char* src, int len, int lane) {
   const uintptr_t a = reinterpret_cast<uintptr_t>(src), a0 = a & ~(uintptr_t)15;
   const int nblk = (int)((((a + len + 15) & ~(uintptr_t)15) - a0) >> 4);
-  const unsigned char* s0 = reinterpret_cast<const unsigned char*>(a0);
-  for (int b = lane; b < nblk; b += 32) cp16(dst + 16 * b, s0 + 16 * b);
+  const unsigned char* s0 = reinterpret_cast<const unsigned char*>(a0) + 16 * lane;
+  const uint32_t d0 = dst + 16 * lane;
+  if (MAX_IT > 0) {                                        // size known to fit MAX_IT warp-wide copies
+#pragma unroll
+    for (int i = 0; i < MAX_IT; ++i)
+      if (lane + 32 * i < nblk) cp16(d0 + 512 * i, s0 + 512 * i);
+  } else {
+    for (int b = lane; b < nblk; b += 32) cp16(dst + 16 * b, reinterpret_cast<const unsigned char*>(a0) + 16 * b);
+  }
 }
 
 // Same for a range whose covering blocks may stick out of the tensor [t_lo, t_hi) (a
@@ -315,13 +332,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     const unsigned char* a_v = G.vrow[p] + (int64_t)t.row0 * phase_row_bytes(p);
     if (G.fast) {
       const uint32_t sbu = smem_u32(sb);
-      stage_range(sbu + SL.v, a_v, t.n * phase_row_bytes(p), lane);
-      if (kd.sub2) stage_range(sbu + SL.k2, a_k2, t.n * kd.sub2, lane);
-      if (kd.sub4) stage_range(sbu + SL.k4, a_k4, t.n * kd.sub4, lane);
-      if (kd.n8) stage_range(sbu + SL.k8, a_k8, t.n * kd.n8, lane);
+      stage_range<V_STAGE / 512 + 1>(sbu + SL.v, a_v, t.n * phase_row_bytes(p), lane);
+      if (kd.sub2) stage_range<0>(sbu + SL.k2, a_k2, t.n * kd.sub2, lane);
+      if (kd.sub4) stage_range<0>(sbu + SL.k4, a_k4, t.n * kd.sub4, lane);
+      if (kd.n8) stage_range<0>(sbu + SL.k8, a_k8, t.n * kd.n8, lane);
       if (p < 3) {
-        stage_range(sbu + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, lane);
-        stage_range(sbu + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, lane);
+        stage_range<1>(sbu + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, lane);
+        stage_range<1>(sbu + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, lane);
       }
     } else {
       const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
@@ -387,16 +404,22 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   }
 
   // ── per-warp worker ─────────────────────────────────────────────────────────
-  const bool head_ok = r < gcnt;
+  // Score product orientation: rows on M (16 per MMA), query heads on N.  Thread (r, j)
+  // then holds scores of rows g16+r and g16+r+8 for heads 2j and 2j+1 — the same two
+  // heads whose output columns it accumulates in the P.V product.
+  const bool he_ok = 2 * j < gcnt, ho_ok = 2 * j + 1 < gcnt;
   const float c1 = TWO24 * INV_SQRT_D * LOG2E;             // scores are kept in base-2 units
-  const float b1 = s_bias[r] * INV_SQRT_D * LOG2E;
-  const float* mask_row = (v.mask != nullptr && head_ok) ? v.mask + (int64_t)(hq0 + r) * v.mask_row_stride : nullptr;
+  const float b1e = s_bias[2 * j] * INV_SQRT_D * LOG2E, b1o = s_bias[2 * j + 1] * INV_SQRT_D * LOG2E;
+  const float* mask_e = (v.mask != nullptr && he_ok) ? v.mask + (int64_t)(hq0 + 2 * j) * v.mask_row_stride : nullptr;
+  const float* mask_o = (v.mask != nullptr && ho_ok) ? v.mask + (int64_t)(hq0 + 2 * j + 1) * v.mask_row_stride : nullptr;
   const bool k_aligned = !(kd.sub2 & 1) && !(kd.sub4 & 3) && !(kd.n8 & 3);
+  const uint2* qs_lane = qsA + lane;
 
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f, zc_run = 0.f;      // for head r (partial sums over this thread's rows)
+  float m_e = -INFINITY, m_o = -INFINITY;                  // running maxima of heads 2j, 2j+1 (same in every r)
+  float l_e = 0.f, l_o = 0.f, zc_e = 0.f, zc_o = 0.f;      // partial sums over this thread's rows
   int cur_phase = -1;
 
   for (int it = 0; it < n_my; ++it) {
@@ -411,7 +434,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       if (cur_phase >= 0) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float f = exp2f((float)(acc_exp(cur_phase, i & 3) - acc_exp(p, i & 3)));
+          const float f = pow2i(acc_exp(cur_phase, i & 3) - acc_exp(p, i & 3));
           acc[i][0] *= f; acc[i][1] *= f; acc[i][2] *= f; acc[i][3] *= f;
         }
       }
@@ -422,12 +445,6 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     const int off_k4 = (int)((reinterpret_cast<uintptr_t>(G.k4[p]) + (uint32_t)(t.row0 * kd.sub4)) & 15);
     const int off_k8 = (int)((reinterpret_cast<uintptr_t>(G.k8[p]) + (uint32_t)(t.row0 * kd.n8)) & 15);
     const int off_v = (int)((reinterpret_cast<uintptr_t>(G.vrow[p]) + (uint32_t)(t.row0 * phase_row_bytes(p))) & 15);
-    const unsigned char* sk2 = sb + SL.k2;
-    const unsigned char* sk4 = sb + SL.k4;
-    const unsigned char* sk8 = sb + SL.k8;
-    const unsigned char* sv = sb + SL.v + off_v;
-    const unsigned char* ssc = sb + SL.sc;
-    const unsigned char* szp = sb + SL.zp;
     int off_m = 0, off_z = 0;
     if (p < 3) {
       off_m = (int)((reinterpret_cast<uintptr_t>(G.sc[p]) + (uint32_t)(t.row0 * 2)) & 15);
@@ -435,119 +452,122 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     }
     const bool kfast = k_aligned && !(off_k2 & 1) && !(off_k4 & 3) && !(off_k8 & 3);
     const int64_t krow0 = G.krow[p] + t.row0;              // stripe row of the tile's first row (mask column)
+    // per-thread cursors: K rows r (and r+8) of the current group, V rows 2j.., scale/zp rows r
+    const unsigned char* k2p = sb + SL.k2 + off_k2 + r * kd.sub2 + 2 * j;
+    const unsigned char* k4p = sb + SL.k4 + off_k4 + r * kd.sub4 + 4 * j;
+    const unsigned char* k8p = sb + SL.k8 + off_k8 + r * kd.n8 + 4 * j;
+    const uint16_t* scp = reinterpret_cast<const uint16_t*>(sb + SL.sc + off_m) + r;
+    const uint16_t* zpp = reinterpret_cast<const uint16_t*>(sb + SL.zp + off_z) + r;
+    const int vrb = phase_row_bytes(p);
+    const unsigned char* vp = sb + SL.v + off_v + (p == 3 ? 8 : 4) * r + 2 * j * vrb;
 
     for (int g16 = 0; g16 < t.n; g16 += 16) {
-      // ── scores: S[head][row] for rows g16 + {0..7} and g16 + {8..15} ──
-      float sa[2][4];
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt) sa[nt][0] = sa[nt][1] = sa[nt][2] = sa[nt][3] = 0.f;
+      // ── scores of rows g16+r (A) and g16+r+8 (B): two independent MMA chains ──
+      float sx[4] = {0.f, 0.f, 0.f, 0.f}, sy[4] = {0.f, 0.f, 0.f, 0.f};
       {
-        const int rowA = g16 + r, rowB = rowA + 8;
-        int kb = 0;
-        for (int s = 0; s < kd.nsp2; ++s, kb += 2) {
-          const uint2 a0 = qsA[kb * 32 + lane], a1 = qsA[(kb + 1) * 32 + lane];
-          uint32_t wA, wB;
-          if (kfast) {
-            wA = *reinterpret_cast<const uint16_t*>(sk2 + off_k2 + rowA * kd.sub2 + 8 * s + 2 * j);
-            wB = *reinterpret_cast<const uint16_t*>(sk2 + off_k2 + rowB * kd.sub2 + 8 * s + 2 * j);
-          } else {
-            wA = lds_unaligned(sk2, off_k2 + rowA * kd.sub2 + 8 * s + 2 * j);
-            wB = lds_unaligned(sk2, off_k2 + rowB * kd.sub2 + 8 * s + 2 * j);
+        const uint2* qp = qs_lane;
+        if (kfast) {
+          for (int s = 0; s < kd.nsp2; ++s, qp += 64) {
+            const uint2 q0 = qp[0], q1 = qp[32];
+            const uint32_t wA = *reinterpret_cast<const uint16_t*>(k2p + 8 * s);
+            const uint32_t wB = *reinterpret_cast<const uint16_t*>(k2p + 8 * kd.sub2 + 8 * s);
+            const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
+            mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
+            mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
           }
-          const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
-          mma16816(sa[0], a0.x, 0u, a0.y, 0u, yA & 0x00030003u, yA & 0x000C000Cu);
-          mma16816(sa[1], a0.x, 0u, a0.y, 0u, yB & 0x00030003u, yB & 0x000C000Cu);
-          mma16816(sa[0], a1.x, 0u, a1.y, 0u, yA & 0x00300030u, yA & 0x00C000C0u);
-          mma16816(sa[1], a1.x, 0u, a1.y, 0u, yB & 0x00300030u, yB & 0x00C000C0u);
-        }
-        for (int s = 0; s < kd.nsp4; ++s, kb += 2) {
-          const uint2 a0 = qsA[kb * 32 + lane], a1 = qsA[(kb + 1) * 32 + lane];
-          uint32_t wA, wB;
-          if (kfast) {
-            wA = *reinterpret_cast<const uint32_t*>(sk4 + off_k4 + rowA * kd.sub4 + 16 * s + 4 * j);
-            wB = *reinterpret_cast<const uint32_t*>(sk4 + off_k4 + rowB * kd.sub4 + 16 * s + 4 * j);
-          } else {
-            wA = lds_unaligned(sk4, off_k4 + rowA * kd.sub4 + 16 * s + 4 * j);
-            wB = lds_unaligned(sk4, off_k4 + rowB * kd.sub4 + 16 * s + 4 * j);
+          for (int s = 0; s < kd.nsp4; ++s, qp += 64) {
+            const uint2 q0 = qp[0], q1 = qp[32];
+            const uint32_t wA = *reinterpret_cast<const uint32_t*>(k4p + 16 * s);
+            const uint32_t wB = *reinterpret_cast<const uint32_t*>(k4p + 8 * kd.sub4 + 16 * s);
+            const uint32_t vA = wA >> 8, vB = wB >> 8;
+            mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, q0.x, q0.y);
+            mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q1.x, q1.y);
           }
-          const uint32_t vA = wA >> 8, vB = wB >> 8;
-          mma16816(sa[0], a0.x, 0u, a0.y, 0u, wA & 0x000F000Fu, wA & 0x00F000F0u);
-          mma16816(sa[1], a0.x, 0u, a0.y, 0u, wB & 0x000F000Fu, wB & 0x00F000F0u);
-          mma16816(sa[0], a1.x, 0u, a1.y, 0u, vA & 0x000F000Fu, vA & 0x00F000F0u);
-          mma16816(sa[1], a1.x, 0u, a1.y, 0u, vB & 0x000F000Fu, vB & 0x00F000F0u);
-        }
-        for (int b = 0; b < kd.nkb8; ++b, ++kb) {
-          const uint2 a0 = qsA[kb * 32 + lane];
-          uint32_t wA, wB;
-          if (kfast) {
-            wA = *reinterpret_cast<const uint32_t*>(sk8 + off_k8 + rowA * kd.n8 + 16 * b + 4 * j);
-            wB = *reinterpret_cast<const uint32_t*>(sk8 + off_k8 + rowB * kd.n8 + 16 * b + 4 * j);
-          } else {
-            wA = lds_unaligned(sk8, off_k8 + rowA * kd.n8 + 16 * b + 4 * j);
-            wB = lds_unaligned(sk8, off_k8 + rowB * kd.n8 + 16 * b + 4 * j);
+          for (int b = 0; b < kd.nkb8; ++b, qp += 32) {
+            const uint2 q0 = qp[0];
+            const uint32_t wA = *reinterpret_cast<const uint32_t*>(k8p + 16 * b);
+            const uint32_t wB = *reinterpret_cast<const uint32_t*>(k8p + 8 * kd.n8 + 16 * b);
+            mma16816((b & 1) ? sy : sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu,
+                     (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
           }
-          mma16816(sa[0], a0.x, 0u, a0.y, 0u, wA & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu);
-          mma16816(sa[1], a0.x, 0u, a0.y, 0u, wB & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu);
+        } else {                                           // rows not 2/4-byte aligned in the stage
+          const unsigned char* b2 = sb + SL.k2; const unsigned char* b4 = sb + SL.k4; const unsigned char* b8 = sb + SL.k8;
+          const int o2 = (int)(k2p - b2), o4 = (int)(k4p - b4), o8 = (int)(k8p - b8);
+          for (int s = 0; s < kd.nsp2; ++s, qp += 64) {
+            const uint2 q0 = qp[0], q1 = qp[32];
+            const uint32_t wA = lds_unaligned(b2, o2 + 8 * s), wB = lds_unaligned(b2, o2 + 8 * kd.sub2 + 8 * s);
+            const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);
+            mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
+            mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
+          }
+          for (int s = 0; s < kd.nsp4; ++s, qp += 64) {
+            const uint2 q0 = qp[0], q1 = qp[32];
+            const uint32_t wA = lds_unaligned(b4, o4 + 16 * s), wB = lds_unaligned(b4, o4 + 8 * kd.sub4 + 16 * s);
+            const uint32_t vA = wA >> 8, vB = wB >> 8;
+            mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, q0.x, q0.y);
+            mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q1.x, q1.y);
+          }
+          for (int b = 0; b < kd.nkb8; ++b, qp += 32) {
+            const uint2 q0 = qp[0];
+            const uint32_t wA = lds_unaligned(b8, o8 + 16 * b), wB = lds_unaligned(b8, o8 + 8 * kd.n8 + 16 * b);
+            mma16816((b & 1) ? sy : sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu,
+                     (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
+          }
         }
       }
-      // this thread now holds, for head r, rows g16 + {2j, 2j+1, 8+2j, 9+2j}
-      const int r0 = g16 + 2 * j;
+      // sx+sy: [0] (row A, head 2j) [1] (row A, head 2j+1) [2] (row B, head 2j) [3] (row B, head 2j+1)
       const bool full = g16 + 16 <= t.n;
+      const bool rowA_ok = full || g16 + r < t.n, rowB_ok = full || g16 + r + 8 < t.n;
       float s2[4];
-      s2[0] = fmaf(sa[0][0], c1, -b1); s2[1] = fmaf(sa[0][1], c1, -b1);
-      s2[2] = fmaf(sa[1][0], c1, -b1); s2[3] = fmaf(sa[1][1], c1, -b1);
-      if (mask_row != nullptr) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = r0 + (e & 1) + 8 * (e >> 1);
-          if (row < t.n) s2[e] += mask_row[krow0 + row] * LOG2E;
-        }
+      s2[0] = fmaf(sx[0] + sy[0], c1, -b1e); s2[1] = fmaf(sx[1] + sy[1], c1, -b1o);
+      s2[2] = fmaf(sx[2] + sy[2], c1, -b1e); s2[3] = fmaf(sx[3] + sy[3], c1, -b1o);
+      if (mask_e != nullptr || mask_o != nullptr) {
+        const int64_t ca = krow0 + g16 + r;
+        if (mask_e != nullptr) { if (rowA_ok) s2[0] += mask_e[ca] * LOG2E; if (rowB_ok) s2[2] += mask_e[ca + 8] * LOG2E; }
+        if (mask_o != nullptr) { if (rowA_ok) s2[1] += mask_o[ca] * LOG2E; if (rowB_ok) s2[3] += mask_o[ca + 8] * LOG2E; }
       }
-      if (!head_ok) { s2[0] = s2[1] = s2[2] = s2[3] = -INFINITY; }
-      if (!full) {
+      if (!he_ok || !rowA_ok) s2[0] = -INFINITY;
+      if (!ho_ok || !rowA_ok) s2[1] = -INFINITY;
+      if (!he_ok || !rowB_ok) s2[2] = -INFINITY;
+      if (!ho_ok || !rowB_ok) s2[3] = -INFINITY;
+      float me = fmaxf(s2[0], s2[2]), mo = fmaxf(s2[1], s2[3]);
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (r0 + (e & 1) + 8 * (e >> 1) >= t.n) s2[e] = -INFINITY;
+      for (int o = 4; o < 32; o <<= 1) {
+        me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
+        mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
       }
-      float mloc = fmaxf(fmaxf(s2[0], s2[1]), fmaxf(s2[2], s2[3]));
-      mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 1));
-      mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 2));
-      const float m_new = fmaxf(m_run, mloc);
-      if (__any_sync(0xffffffffu, m_new > m_run)) {        // lazy rescale: only when some head's max moved
-        const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
-        l_run *= alpha; zc_run *= alpha;
-        const float a_even = __shfl_sync(0xffffffffu, alpha, (2 * j) * 4);        // head 2j lives in lanes r = 2j
-        const float a_odd = __shfl_sync(0xffffffffu, alpha, (2 * j + 1) * 4);
+      // lazy rescale: keep the old reference maximum while the new one is within 2^RESCALE_TH of it
+      if (__any_sync(0xffffffffu, me > m_e + RESCALE_TH || mo > m_o + RESCALE_TH)) {
+        const float ne = fmaxf(m_e, me), no = fmaxf(m_o, mo);
+        const float ae = (ne == -INFINITY) ? 1.f : ex2(m_e - ne), ao = (no == -INFINITY) ? 1.f : ex2(m_o - no);
+        l_e *= ae; zc_e *= ae; l_o *= ao; zc_o *= ao;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { acc[i][0] *= a_even; acc[i][1] *= a_odd; acc[i][2] *= a_even; acc[i][3] *= a_odd; }
-        m_run = m_new;
+        for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
+        m_e = ne; m_o = no;
       }
-      const float m_safe = (m_run == -INFINITY) ? 0.f : m_run;
+      const float mse = (m_e == -INFINITY) ? 0.f : m_e, mso = (m_o == -INFINITY) ? 0.f : m_o;
       float pe[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) { pe[e] = ex2(s2[e] - m_safe); l_run += pe[e]; }
-      uint32_t pb0 = pack_h2(pe[0], pe[1]), pb1 = pack_h2(pe[2], pe[3]);
+      pe[0] = ex2(s2[0] - mse); pe[1] = ex2(s2[1] - mso); pe[2] = ex2(s2[2] - mse); pe[3] = ex2(s2[3] - mso);
+      l_e += pe[0] + pe[2]; l_o += pe[1] + pe[3];
+      uint32_t hA, hB;                                     // (row A | row B) x (head 2j, head 2j+1) as fp16 pairs
       if (p < 3) {
-        // rows r0, r0+1 and r0+8, r0+9: scale and zero point as fp16 pairs
-        uint32_t sc01 = lds_unaligned(ssc, off_m + 2 * r0), sc23 = lds_unaligned(ssc, off_m + 2 * r0 + 16);
-        uint32_t zp01 = lds_unaligned(szp, off_z + 2 * r0), zp23 = lds_unaligned(szp, off_z + 2 * r0 + 16);
-        if (!full) {                                       // dead rows may hold non-finite bytes
-          if (r0 >= t.n) { sc01 = 0u; zp01 = 0u; } else if (r0 + 1 >= t.n) { sc01 &= 0xFFFFu; zp01 &= 0xFFFFu; }
-          if (r0 + 8 >= t.n) { sc23 = 0u; zp23 = 0u; } else if (r0 + 9 >= t.n) { sc23 &= 0xFFFFu; zp23 &= 0xFFFFu; }
-        }
-        const __half2 ps01 = __hmul2(*reinterpret_cast<__half2*>(&pb0), *reinterpret_cast<__half2*>(&sc01));
-        const __half2 ps23 = __hmul2(*reinterpret_cast<__half2*>(&pb1), *reinterpret_cast<__half2*>(&sc23));
-        const float2 f01 = __half22float2(ps01), f23 = __half22float2(ps23);
-        const float2 z01 = __half22float2(*reinterpret_cast<__half2*>(&zp01));
-        const float2 z23 = __half22float2(*reinterpret_cast<__half2*>(&zp23));
-        zc_run = fmaf(f01.x, z01.x, zc_run); zc_run = fmaf(f01.y, z01.y, zc_run);
-        zc_run = fmaf(f23.x, z23.x, zc_run); zc_run = fmaf(f23.y, z23.y, zc_run);
-        pb0 = *reinterpret_cast<const uint32_t*>(&ps01);
-        pb1 = *reinterpret_cast<const uint32_t*>(&ps23);
+        float scA = h2f(scp[g16]), scB = h2f(scp[g16 + 8]), zpA = h2f(zpp[g16]), zpB = h2f(zpp[g16 + 8]);
+        if (!rowA_ok) { scA = 0.f; zpA = 0.f; }            // dead rows may hold non-finite bytes
+        if (!rowB_ok) { scB = 0.f; zpB = 0.f; }
+        hA = pack_h2(pe[0] * scA, pe[1] * scA); hB = pack_h2(pe[2] * scB, pe[3] * scB);
+        const float2 fA = __half22float2(*reinterpret_cast<__half2*>(&hA));   // the values the tensor core sees
+        const float2 fB = __half22float2(*reinterpret_cast<__half2*>(&hB));
+        zc_e = fmaf(fA.x, zpA, zc_e); zc_o = fmaf(fA.y, zpA, zc_o);
+        zc_e = fmaf(fB.x, zpB, zc_e); zc_o = fmaf(fB.y, zpB, zc_o);
+      } else {
+        hA = pack_h2(pe[0], pe[1]); hB = pack_h2(pe[2], pe[3]);
       }
+      // 8x8 transposes: thread (r, j) now holds head r at rows g16 + {2j, 2j+1} and g16 + 8 + {2j, 2j+1}
+      const uint32_t pb0 = movmatrix_trans(hA), pb1 = movmatrix_trans(hB);
+
       // ── P.V: channels on M, rows on K; this thread supplies rows g16 + {2j,2j+1,8+2j,9+2j} ──
+      const unsigned char* base = vp + g16 * vrb;
       if (p == 2) {
-        const unsigned char* base = sv + 4 * r + r0 * 128;
 #pragma unroll
         for (int vv = 0; vv < 4; ++vv) {
           const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + 32 * vv);
@@ -563,7 +583,6 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           }
         }
       } else if (p == 1) {
-        const unsigned char* base = sv + 4 * r + r0 * 64;
 #pragma unroll
         for (int vl = 0; vl < 2; ++vl) {
           const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + 32 * vl);
@@ -582,7 +601,6 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           }
         }
       } else if (p == 0) {
-        const unsigned char* base = sv + 4 * r + r0 * 32;
         const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base);
         const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + 32);
         const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + 8 * 32);
@@ -598,8 +616,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             mma16816(acc[4 * qq + vv], y01 & mk, z01 & mk, y23 & mk, z23 & mk, pb0, pb1);
           }
         }
-      } else {
-        const unsigned char* base = sv + 8 * r + r0 * 256;        // fp16 rows: channel c at byte 2c
+      } else {                                             // fp16 rows: channel c at byte 2c
 #pragma unroll
         for (int vv = 0; vv < 4; ++vv) {
           const uint2 w0 = *reinterpret_cast<const uint2*>(base + 64 * vv);
@@ -612,6 +629,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
                    prmt(w2.y, w3.y, 0x7632), pb0, pb1);
         }
       }
+      k2p += 16 * kd.sub2; k4p += 16 * kd.sub4; k8p += 16 * kd.n8;
     }
     __syncwarp();
     const int nxt = it + FSTAGES;
@@ -624,17 +642,21 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   if (cur_phase >= 0) {                                    // accumulators to true units
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float f = exp2f((float)acc_exp(cur_phase, i & 3));
+      const float f = pow2i(acc_exp(cur_phase, i & 3));
       acc[i][0] *= f; acc[i][1] *= f; acc[i][2] *= f; acc[i][3] *= f;
     }
   }
-  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-  zc_run += __shfl_xor_sync(0xffffffffu, zc_run, 1);
-  zc_run += __shfl_xor_sync(0xffffffffu, zc_run, 2);
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {                       // rows are spread over r: lanes 4r + j
+    l_e += __shfl_xor_sync(0xffffffffu, l_e, o); l_o += __shfl_xor_sync(0xffffffffu, l_o, o);
+    zc_e += __shfl_xor_sync(0xffffffffu, zc_e, o); zc_o += __shfl_xor_sync(0xffffffffu, zc_o, o);
+  }
   __syncthreads();                                         // every worker is done with its stages
   float* red = reinterpret_cast<float*>(smem_raw);         // [FW][GH][128]
-  if (j == 0) { s_ml[warp][r][0] = m_run; s_ml[warp][r][1] = l_run; s_ml[warp][r][2] = zc_run; }
+  if (r == 0) {
+    s_ml[warp][2 * j][0] = m_e; s_ml[warp][2 * j][1] = l_e; s_ml[warp][2 * j][2] = zc_e;
+    s_ml[warp][2 * j + 1][0] = m_o; s_ml[warp][2 * j + 1][1] = l_o; s_ml[warp][2 * j + 1][2] = zc_o;
+  }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int ch = 4 * r + 2 * (i >> 2) + 32 * (i & 3);
