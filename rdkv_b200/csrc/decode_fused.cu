@@ -194,6 +194,7 @@ __device__ __forceinline__ void stage_range(uint32_t dst, const unsigned char* s
     for (int i = 0; i < MAX_IT; ++i)
       if (lane + 32 * i < nblk) cp16(d0 + 512 * i, s0 + 512 * i);
   } else {
+#pragma unroll 1
     for (int b = lane; b < nblk; b += 32) cp16(dst + 16 * b, reinterpret_cast<const unsigned char*>(a0) + 16 * b);
   }
 }
@@ -207,6 +208,7 @@ __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const u
   const uintptr_t tl = reinterpret_cast<uintptr_t>(t_lo), th = reinterpret_cast<uintptr_t>(t_hi);
   const int nblk = (int)((((a + len + 15) & ~(uintptr_t)15) - a0) >> 4);
   const uint32_t dst = smem_u32(dst_ptr);
+#pragma unroll 1
   for (int b = lane; b < nblk; b += 32) {
     const uintptr_t lo = a0 + 16 * (uintptr_t)b;
     if (lo < tl) {
@@ -219,7 +221,7 @@ __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const u
   }
 }
 
-__global__ void __launch_bounds__(FW * 32, 4)
+__global__ void __launch_bounds__(FW * 32, 3)
 decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __restrict__ q, int q_dtype,
                     int H_q, int g, int chunk_rows, int n_chunks, int stage_bytes,
                     float* __restrict__ partials, float* __restrict__ out, int* __restrict__ status) {
@@ -379,6 +381,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
     const int64_t qoff = ((int64_t)view_idx * H_q + hq0 + r) * D;
     float bias_part = 0.f;                                 // thread (r = head, j) sums its own slots
+#pragma unroll 1
     for (int kb = warp; kb < kd.nkb; kb += FW) {
       float val[4];
 #pragma unroll
@@ -422,6 +425,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   float l_e = 0.f, l_o = 0.f, zc_e = 0.f, zc_o = 0.f;      // partial sums over this thread's rows
   int cur_phase = -1;
 
+#pragma unroll 1
   for (int it = 0; it < n_my; ++it) {
     const int stage = it % FSTAGES;
     cp_wait<FSTAGES - 1>();                                // this lane's copies of tile `it` have landed
@@ -461,12 +465,14 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     const int vrb = phase_row_bytes(p);
     const unsigned char* vp = sb + SL.v + off_v + (p == 3 ? 8 : 4) * r + 2 * j * vrb;
 
+#pragma unroll 1
     for (int g16 = 0; g16 < t.n; g16 += 16) {
       // ── scores of rows g16+r (A) and g16+r+8 (B): two independent MMA chains ──
       float sx[4] = {0.f, 0.f, 0.f, 0.f}, sy[4] = {0.f, 0.f, 0.f, 0.f};
       {
         const uint2* qp = qs_lane;
         if (kfast) {
+#pragma unroll 1
           for (int s = 0; s < kd.nsp2; ++s, qp += 64) {
             const uint2 q0 = qp[0], q1 = qp[32];
             const uint32_t wA = *reinterpret_cast<const uint16_t*>(k2p + 8 * s);
@@ -475,6 +481,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
             mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
           }
+#pragma unroll 1
           for (int s = 0; s < kd.nsp4; ++s, qp += 64) {
             const uint2 q0 = qp[0], q1 = qp[32];
             const uint32_t wA = *reinterpret_cast<const uint32_t*>(k4p + 16 * s);
@@ -483,16 +490,18 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, q0.x, q0.y);
             mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q1.x, q1.y);
           }
+#pragma unroll 1
           for (int b = 0; b < kd.nkb8; ++b, qp += 32) {
             const uint2 q0 = qp[0];
             const uint32_t wA = *reinterpret_cast<const uint32_t*>(k8p + 16 * b);
             const uint32_t wB = *reinterpret_cast<const uint32_t*>(k8p + 8 * kd.n8 + 16 * b);
-            mma16816((b & 1) ? sy : sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu,
-                     (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
+            if (b & 1) mma16816(sy, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
+            else mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
           }
         } else {                                           // rows not 2/4-byte aligned in the stage
           const unsigned char* b2 = sb + SL.k2; const unsigned char* b4 = sb + SL.k4; const unsigned char* b8 = sb + SL.k8;
           const int o2 = (int)(k2p - b2), o4 = (int)(k4p - b4), o8 = (int)(k8p - b8);
+#pragma unroll 1
           for (int s = 0; s < kd.nsp2; ++s, qp += 64) {
             const uint2 q0 = qp[0], q1 = qp[32];
             const uint32_t wA = lds_unaligned(b2, o2 + 8 * s), wB = lds_unaligned(b2, o2 + 8 * kd.sub2 + 8 * s);
@@ -500,6 +509,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
             mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
           }
+#pragma unroll 1
           for (int s = 0; s < kd.nsp4; ++s, qp += 64) {
             const uint2 q0 = qp[0], q1 = qp[32];
             const uint32_t wA = lds_unaligned(b4, o4 + 16 * s), wB = lds_unaligned(b4, o4 + 8 * kd.sub4 + 16 * s);
@@ -507,11 +517,12 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, q0.x, q0.y);
             mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q1.x, q1.y);
           }
+#pragma unroll 1
           for (int b = 0; b < kd.nkb8; ++b, qp += 32) {
             const uint2 q0 = qp[0];
             const uint32_t wA = lds_unaligned(b8, o8 + 16 * b), wB = lds_unaligned(b8, o8 + 8 * kd.n8 + 16 * b);
-            mma16816((b & 1) ? sy : sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu,
-                     (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
+            if (b & 1) mma16816(sy, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
+            else mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
           }
         }
       }
