@@ -223,6 +223,28 @@ int rdkv_knapsack_batched(const float* scores, int64_t row_stride, int n_rows, i
                           int n_options, int max_iters, float tol, int64_t* out, void* scratch,
                           void* stream);
 
+/* ── batched bit allocator without caller-provided scratch ────────────────────
+ * No counterpart in the reference.  Same computation and arguments as
+ * rdkv_knapsack_batched, minus `scratch`: the three words per row the two kernels
+ * hand over to each other live in a fixed array inside the library's device image
+ * (48 KiB on every GPU that loads the library, held until the process exits).  It is
+ * meant for callers that may not allocate device memory where they call from — an
+ * engine that froze its memory plan after warm-up, a host callback, a plugin that
+ * is given input and output buffers and nothing else.  The call itself performs no
+ * allocation of any kind.
+ *   - n_rows above rdkv_knapsack_static_max_rows() (4096) is refused with
+ *     RDKV_ERR_TOO_LARGE; split the batch or use rdkv_knapsack_batched.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before
+ *     any stream capture begins.
+ *   - All calls on a device share the one array.  Every call overwrites the entries of
+ *     its own rows before reading them, so nothing has to be cleared between calls, but
+ *     two calls whose kernels overlap on the GPU (different streams) race: serialise them. */
+int rdkv_knapsack_static_max_rows(void);
+int rdkv_knapsack_batched_static(const float* scores, int64_t row_stride, int n_rows, int len,
+                                 const float* budget, const float* option_bits, const float* option_eps,
+                                 int n_options, int max_iters, float tol, int64_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

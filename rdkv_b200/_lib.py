@@ -65,6 +65,8 @@ _PROTOTYPES = {
     "rdkv_pack_k": ([_p, _i64, _i64, _i, _i, _p, _i64, _p, _i64, _i, _i, _p, _i64, _p, _i64,
                      _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p], _i),
     "rdkv_knapsack_batched": ([_p, _i64, _i, _i, _p, C.POINTER(_f), C.POINTER(_f), _i, _i, _f, _p, _p, _p], _i),
+    "rdkv_knapsack_static_max_rows": ([], _i),
+    "rdkv_knapsack_batched_static": ([_p, _i64, _i, _i, _p, C.POINTER(_f), C.POINTER(_f), _i, _i, _f, _p, _p], _i),
 }
 
 EXPORTED_SYMBOLS = tuple(_PROTOTYPES)

@@ -186,3 +186,53 @@ extern "C" int rdkv_knapsack_batched(const float* scores, int64_t row_stride, in
                                                            max_iters, tol, use_smem, lam0, ndbl, out);
   return launch_status();
 }
+
+// ── allocation-free variant ──────────────────────────────────────────────────
+// Some callers cannot provide the per-row scratch of rdkv_knapsack_batched because
+// they are not allowed to allocate device memory at the point of the call: a
+// prefill step that runs inside an engine's fixed memory plan after warm-up, a
+// host callback, a plugin interface that hands over input and output buffers only.
+// For them the scratch lives in this library's own device image: a file-scope
+// array that every GPU loading the library carries until the process exits.
+constexpr int KNAP_STATIC_MAX_ROWS = 4096;                 // 3 words per row -> 48 KiB per GPU
+static __device__ __align__(256) unsigned int g_knap_static_scratch[3 * KNAP_STATIC_MAX_ROWS];
+
+#include <mutex>
+namespace {
+constexpr int KNAP_MAX_DEVICES = 64;
+std::mutex g_knap_static_mutex;
+void* g_knap_static_addr[KNAP_MAX_DEVICES] = {nullptr};   // device address of the array, per device
+}  // namespace
+
+extern "C" int rdkv_knapsack_static_max_rows(void) { return KNAP_STATIC_MAX_ROWS; }
+
+extern "C" int rdkv_knapsack_batched_static(const float* scores, int64_t row_stride, int n_rows, int len,
+                                            const float* budget, const float* option_bits,
+                                            const float* option_eps, int n_options, int max_iters, float tol,
+                                            int64_t* out, void* stream) {
+  if (n_rows > KNAP_STATIC_MAX_ROWS) return RDKV_ERR_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= KNAP_MAX_DEVICES) {
+    g_last_cuda_error = (int)e;
+    return RDKV_ERR_NO_DEVICE;
+  }
+  void* scratch = nullptr;
+  {
+    // The array's name is only a host-side handle; the address a kernel can use is
+    // looked up once per device, with that device current.
+    std::lock_guard<std::mutex> lock(g_knap_static_mutex);
+    if (g_knap_static_addr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_knap_static_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        g_last_cuda_error = (int)e;
+        return RDKV_ERR_LAUNCH;
+      }
+      g_knap_static_addr[dev] = p;
+    }
+    scratch = g_knap_static_addr[dev];
+  }
+  return rdkv_knapsack_batched(scores, row_stride, n_rows, len, budget, option_bits, option_eps, n_options,
+                               max_iters, tol, out, scratch, stream);
+}
