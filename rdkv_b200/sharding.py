@@ -1,0 +1,104 @@
+"""Sharding of the packed-KV decode path over the GPUs of one node.
+
+One process per GPU (torch.distributed, NCCL over NVLink).  Two ways to cut the work:
+
+* KV-head sharding — rank r packs and serves KV heads [r*H_kv/N, (r+1)*H_kv/N) and their
+  query heads.  Heads are independent, so attention needs no collective; an all-gather of
+  the [B, H_q_local, 128] outputs is only needed if every rank wants the full result.
+* sequence split — the ranks of a group each hold a slice of every head's kept tokens
+  (cut at pack time, each slice with its own per-head bounds and its own per-channel K
+  ranges), run the fused kernel on it and exchange one merged (m, l, o) record per query
+  head: one all-gather into local memory, then the log-sum-exp combine kernel.
+
+The reference has no distributed code; the oracle for both is the single-device result on
+the same (sharded or split) inputs.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+PARTIAL_STRIDE = 132
+
+
+def head_shard(rank: int, world: int, H_kv: int) -> Tuple[int, int]:
+    """KV heads [h0, h1) owned by `rank` when `world` ranks share H_kv heads evenly."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} for world size {world}")
+    if H_kv % world:
+        raise ValueError(f"{world} ranks cannot share {H_kv} KV heads evenly")
+    per = H_kv // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_heads(K: Tensor, V: Tensor, v_bits: Tensor, k_bits: Tensor, rank: int, world: int):
+    """Slices of one layer's inputs for this rank: K,V [1,H_kv,T,D], v_bits [H_kv,T], k_bits [H_kv,D]."""
+    h0, h1 = head_shard(rank, world, K.shape[1])
+    return K[:, h0:h1], V[:, h0:h1], v_bits[h0:h1], k_bits[h0:h1]
+
+
+def split_tokens(v_bits: Tensor, part: int, n_parts: int) -> Tensor:
+    """Token bit map of sequence slice `part`: tokens outside [part*T/n, (part+1)*T/n) are
+    marked evicted (0), so packing this map keeps only the slice's tokens."""
+    if not 0 <= part < n_parts:
+        raise ValueError(f"bad part {part} of {n_parts}")
+    T = v_bits.shape[-1]
+    lo, hi = part * T // n_parts, (part + 1) * T // n_parts
+    out = torch.zeros_like(v_bits)
+    out[..., lo:hi] = v_bits[..., lo:hi]
+    return out
+
+
+def grid(rank: int, world: int, seq_parts: int) -> Tuple[int, int, int]:
+    """(head_rank, head_world, seq_part) of a rank in a head-shards x sequence-parts grid;
+    ranks of one sequence group are adjacent."""
+    if world % seq_parts:
+        raise ValueError(f"world size {world} is not a multiple of {seq_parts} sequence parts")
+    return rank // seq_parts, world // seq_parts, rank % seq_parts
+
+
+def check_group_consistency(n_rows: int, group=None) -> None:
+    """Host-side agreement check before the first exchange: every rank of the group must
+    bring the same number of records.  Raises on every rank if they disagree."""
+    world = dist.get_world_size(group)
+    sizes = [None] * world
+    dist.all_gather_object(sizes, int(n_rows), group=group)
+    if len(set(sizes)) != 1:
+        raise ValueError(f"sequence-split group disagrees on the record count: {sizes}")
+
+
+def combine_across_ranks(local_record: Tensor, group=None, *, combine: Optional[Callable] = None,
+                         gathered: Optional[Tensor] = None) -> Tensor:
+    """All-gather the merged per-head records [n_rows,132] of the group's ranks into local
+    memory and merge them in rank order.  Returns [n_rows,128] fp32.
+
+    `combine(records [n_rows, S, 132]) -> [n_rows,128]` defaults to the CUDA combine kernel."""
+    world = dist.get_world_size(group)
+    if local_record.dim() != 2 or local_record.shape[1] != PARTIAL_STRIDE:
+        raise ValueError("local_record must be [n_rows, 132]")
+    n_rows = local_record.shape[0]
+    if gathered is None:
+        gathered = torch.empty((world * n_rows, PARTIAL_STRIDE), dtype=local_record.dtype,
+                               device=local_record.device)
+    dist.all_gather_into_tensor(gathered, local_record.contiguous(), group=group)
+    records = gathered.view(world, n_rows, PARTIAL_STRIDE).permute(1, 0, 2)   # [n_rows, S, 132] view, no copy
+    if combine is None:
+        from .decode import lse_combine
+        combine = lse_combine
+    return combine(records)
+
+
+def sequence_split_attention(q: Tensor, table, group=None, *, record: Optional[Tensor] = None,
+                             gathered: Optional[Tensor] = None) -> Tensor:
+    """Decode attention when the ranks of `group` hold different token slices of the same
+    heads: fused kernel on the local slice -> one record per query head -> all-gather ->
+    combine.  q [n_views,H_q,128]; returns [n_views,H_q,128] fp32 on every rank of the group."""
+    from .decode import packed_decode_attention
+    n_rows = table.n_views * table.H_q
+    if record is None:
+        record = torch.empty((n_rows, PARTIAL_STRIDE), dtype=torch.float32, device=q.device)
+    packed_decode_attention(q, table, out_partial=record)
+    return combine_across_ranks(record, group, gathered=gathered).view(table.n_views, table.H_q, 128)
