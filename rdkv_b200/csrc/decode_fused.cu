@@ -1,9 +1,10 @@
 // Fused split-sequence decode attention over the packed cache (sm_100a).
 //
-// One CTA = (view, KV head, chunk of live rows); 4 warps, each an independent
-// worker with its own ring of shared-memory tiles filled by 16-byte cp.async copies
-// (many small ranges per tile: measured here, per-lane LDGSTS sustains them better
-// than one bulk-copy instruction per range).  Per 16 rows a warp
+// One CTA = (view, KV head, chunk of live rows); its 128 threads stage tiles of up to
+// 256 rows into a 2-slot shared-memory ring with 16-byte cp.async copies (a tile is six
+// small byte ranges: measured here, per-lane LDGSTS sustains them better than one
+// bulk-copy instruction per range), and each of the 4 warps works through a quarter of
+// the tile's rows.  Per 16 rows a warp
 //   * computes q.K scores on the tensor cores (mma.sync m16n8k16, query heads on M,
 //     rows on N): packed 2/4/8-bit K codes are masked in place into fp16
 //     SUBNORMAL integers (code * 2^-24, exact), so unpacking is one AND per pair
@@ -21,9 +22,9 @@
 namespace rdkv {
 
 constexpr int FW = 4;                  // warps per CTA
-constexpr int FSTAGES = 2;             // ring depth per warp
-constexpr int TILE_MAX = 64;           // rows per tile (2-bit and 4-bit phases)
-constexpr int V_STAGE = 4096;          // V payload bytes per stage
+constexpr int FSTAGES = 2;             // ring depth
+constexpr int TILE_MAX = 256;          // rows per tile (2-bit and 4-bit phases)
+constexpr int V_STAGE = 16384;         // V payload bytes per stage
 constexpr int GH = 8;                  // query heads per CTA pass (N of the P.V product)
 constexpr int KB_MAX = 32;             // 16-channel blocks of the score product
 constexpr float TWO24 = 16777216.f;
@@ -31,7 +32,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float RESCALE_TH = 8.f;      // log2 slack before the running maximum is moved
 
-__host__ __device__ constexpr int phase_tile_rows(int p) { return p == 0 ? 64 : p == 1 ? 64 : p == 2 ? 32 : 16; }
+__host__ __device__ constexpr int phase_tile_rows(int p) { return p == 0 ? 256 : p == 1 ? 256 : p == 2 ? 128 : 64; }
 __host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : p == 1 ? 64 : p == 2 ? 128 : 256; }
 
 __host__ __device__ inline int align16i(int x) { return (x + 15) & ~15; }
@@ -97,6 +98,30 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// Shared-memory loads through 32-bit shared-window addresses (IMM: constant byte offset).
+template <int IMM = 0>
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(IMM));
+  return v;
+}
+template <int IMM = 0>
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(a), "n"(IMM));
+  return v;
+}
+template <int IMM = 0>
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(a), "n"(IMM));
+  return v;
+}
+// 32 bits starting at an arbitrary byte address of shared memory (two aligned loads).
+__device__ __forceinline__ uint32_t lds32_unaligned(uint32_t a) {
+  const uint32_t lo = lds32(a & ~3u), hi = lds32<4>(a & ~3u);
+  return __funnelshift_r(lo, hi, (a & 3u) * 8);
 }
 // 32 bits starting at an arbitrary byte offset of a shared-memory buffer.
 // `base` must be 4-byte aligned.
@@ -183,19 +208,20 @@ __device__ __forceinline__ bool blocks_inside(const unsigned char* lo, const uns
 
 // Stage one byte range with 16-byte copies: the byte at global address x lands at
 // dst + (x - (src & ~15)).  All covering blocks lie inside the tensor.
-template <int MAX_IT>
-__device__ __forceinline__ void stage_range(uint32_t dst, const unsigned char* src, int len, int lane) {
+// `tid` runs over the NT threads that share the copy.
+template <int MAX_IT, int NT>
+__device__ __forceinline__ void stage_range(uint32_t dst, const unsigned char* src, int len, int tid) {
   const uintptr_t a = reinterpret_cast<uintptr_t>(src), a0 = a & ~(uintptr_t)15;
   const int nblk = (int)((((a + len + 15) & ~(uintptr_t)15) - a0) >> 4);
-  const unsigned char* s0 = reinterpret_cast<const unsigned char*>(a0) + 16 * lane;
-  const uint32_t d0 = dst + 16 * lane;
-  if (MAX_IT > 0) {                                        // size known to fit MAX_IT warp-wide copies
+  const unsigned char* s0 = reinterpret_cast<const unsigned char*>(a0) + 16 * tid;
+  const uint32_t d0 = dst + 16 * tid;
+  if (MAX_IT > 0) {                                        // size known to fit MAX_IT rounds of NT copies
 #pragma unroll
     for (int i = 0; i < MAX_IT; ++i)
-      if (lane + 32 * i < nblk) cp16(d0 + 512 * i, s0 + 512 * i);
+      if (tid + NT * i < nblk) cp16(d0 + 16 * NT * i, s0 + 16 * NT * i);
   } else {
 #pragma unroll 1
-    for (int b = lane; b < nblk; b += 32) cp16(dst + 16 * b, reinterpret_cast<const unsigned char*>(a0) + 16 * b);
+    for (int b = tid; b < nblk; b += NT) cp16(dst + 16 * b, reinterpret_cast<const unsigned char*>(a0) + 16 * b);
   }
 }
 
@@ -203,13 +229,14 @@ __device__ __forceinline__ void stage_range(uint32_t dst, const unsigned char* s
 // tensor start or end that is not 16-byte aligned): a block crossing the end is read
 // partially and zero-filled, a block crossing the start is copied byte by byte.
 __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const unsigned char* src, int len,
-                                                 const unsigned char* t_lo, const unsigned char* t_hi, int lane) {
+                                                 const unsigned char* t_lo, const unsigned char* t_hi, int tid,
+                                                 int nt) {
   const uintptr_t a = reinterpret_cast<uintptr_t>(src), a0 = a & ~(uintptr_t)15;
   const uintptr_t tl = reinterpret_cast<uintptr_t>(t_lo), th = reinterpret_cast<uintptr_t>(t_hi);
   const int nblk = (int)((((a + len + 15) & ~(uintptr_t)15) - a0) >> 4);
   const uint32_t dst = smem_u32(dst_ptr);
 #pragma unroll 1
-  for (int b = lane; b < nblk; b += 32) {
+  for (int b = tid; b < nblk; b += nt) {
     const uintptr_t lo = a0 + 16 * (uintptr_t)b;
     if (lo < tl) {
       for (uintptr_t x = tl; x < lo + 16 && x < th; ++x) dst_ptr[x - a0] = *reinterpret_cast<const unsigned char*>(x);
@@ -320,27 +347,28 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     return;
   }
 
-  unsigned char* wstage = smem_raw + (size_t)warp * FSTAGES * stage_bytes;
-  uint2* qsA = reinterpret_cast<uint2*>(smem_raw + (size_t)FW * FSTAGES * stage_bytes);   // [nkb][32]
+  const uint32_t smem0 = smem_u32(smem_raw);
+  const uint32_t qs_base = smem0 + FSTAGES * stage_bytes;  // uint2 qsA[nkb][32]
+  uint2* qsA = reinterpret_cast<uint2*>(smem_raw + (size_t)FSTAGES * stage_bytes);
 
-  // Stage tile `tile_idx` of this worker into ring slot `stage` (one cp.async group).
+  // Stage tile `tile_idx` into ring slot `stage`; all threads take part (one cp.async group each).
   auto issue_tile = [&](int tile_idx, int stage) {
     const TileDesc t = tile_of(G, tile_idx);
-    unsigned char* sb = wstage + (size_t)stage * stage_bytes;
+    unsigned char* sb = smem_raw + (size_t)stage * stage_bytes;
     const int p = t.phase;
     const unsigned char* a_k2 = G.k2[p] + (int64_t)t.row0 * kd.sub2;
     const unsigned char* a_k4 = G.k4[p] + (int64_t)t.row0 * kd.sub4;
     const unsigned char* a_k8 = G.k8[p] + (int64_t)t.row0 * kd.n8;
     const unsigned char* a_v = G.vrow[p] + (int64_t)t.row0 * phase_row_bytes(p);
     if (G.fast) {
-      const uint32_t sbu = smem_u32(sb);
-      stage_range<V_STAGE / 512 + 1>(sbu + SL.v, a_v, t.n * phase_row_bytes(p), lane);
-      if (kd.sub2) stage_range<0>(sbu + SL.k2, a_k2, t.n * kd.sub2, lane);
-      if (kd.sub4) stage_range<0>(sbu + SL.k4, a_k4, t.n * kd.sub4, lane);
-      if (kd.n8) stage_range<0>(sbu + SL.k8, a_k8, t.n * kd.n8, lane);
+      const uint32_t sbu = smem0 + stage * stage_bytes;
+      stage_range<V_STAGE / (16 * FW * 32) + 1, FW * 32>(sbu + SL.v, a_v, t.n * phase_row_bytes(p), tid);
+      if (kd.sub2) stage_range<0, FW * 32>(sbu + SL.k2, a_k2, t.n * kd.sub2, tid);
+      if (kd.sub4) stage_range<0, FW * 32>(sbu + SL.k4, a_k4, t.n * kd.sub4, tid);
+      if (kd.n8) stage_range<0, FW * 32>(sbu + SL.k8, a_k8, t.n * kd.n8, tid);
       if (p < 3) {
-        stage_range<1>(sbu + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, lane);
-        stage_range<1>(sbu + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, lane);
+        stage_range<1, FW * 32>(sbu + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, tid);
+        stage_range<1, FW * 32>(sbu + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, tid);
       }
     } else {
       const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
@@ -348,13 +376,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
       const unsigned char* vlo = p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : v16b;
       const int64_t vext = p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes;
-      stage_range_guarded(sb + SL.v, a_v, t.n * phase_row_bytes(p), vlo, vlo + vext, lane);
-      if (kd.sub2) stage_range_guarded(sb + SL.k2, a_k2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, lane);
-      if (kd.sub4) stage_range_guarded(sb + SL.k4, a_k4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, lane);
-      if (kd.n8) stage_range_guarded(sb + SL.k8, a_k8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, lane);
+      stage_range_guarded(sb + SL.v, a_v, t.n * phase_row_bytes(p), vlo, vlo + vext, tid, FW * 32);
+      if (kd.sub2) stage_range_guarded(sb + SL.k2, a_k2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, tid, FW * 32);
+      if (kd.sub4) stage_range_guarded(sb + SL.k4, a_k4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, tid, FW * 32);
+      if (kd.n8) stage_range_guarded(sb + SL.k8, a_k8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, tid, FW * 32);
       if (p < 3) {
-        stage_range_guarded(sb + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, scb, scb + v.v_meta_bytes, lane);
-        stage_range_guarded(sb + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, zpb, zpb + v.v_meta_bytes, lane);
+        stage_range_guarded(sb + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, scb, scb + v.v_meta_bytes, tid, FW * 32);
+        stage_range_guarded(sb + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, zpb, zpb + v.v_meta_bytes, tid, FW * 32);
       }
     }
     // rows past the tile's end must hold finite fp16 data in the fp16 phase: clear the
@@ -363,18 +391,16 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       const int off = (int)(reinterpret_cast<uintptr_t>(a_v) & 15);
       const int first = (off + t.n * 256 + 15) & ~15;
       const int last = off + ((t.n + 15) & ~15) * 256;
-      for (int i = first + 4 * lane; i < last; i += 128) *reinterpret_cast<uint32_t*>(sb + SL.v + i) = 0u;
+      for (int i = first + 4 * tid; i < last; i += 4 * FW * 32) *reinterpret_cast<uint32_t*>(sb + SL.v + i) = 0u;
     }
   };
 
-  int n_my = (total_tiles - warp + FW - 1) / FW;           // tiles warp, warp+FW, ...
-  if (n_my < 0) n_my = 0;
   for (int it = 0; it < FSTAGES; ++it) {                  // one group per ring slot, empty or not
-    if (it < n_my) issue_tile(warp + it * FW, it);
+    if (it < total_tiles) issue_tile(it, it);
     cp_commit();
   }
 
-  // ── q*scale in MMA A-fragment order and the zero-point bias (overlaps the first copies) ──
+  // ── q*scale in MMA fragment order and the zero-point bias (overlaps the first copies) ──
   {
     const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
     const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
@@ -406,7 +432,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     __syncthreads();
   }
 
-  // ── per-warp worker ─────────────────────────────────────────────────────────
+  // ── workers ─────────────────────────────────────────────────────────────────
   // Score product orientation: rows on M (16 per MMA), query heads on N.  Thread (r, j)
   // then holds scores of rows g16+r and g16+r+8 for heads 2j and 2j+1 — the same two
   // heads whose output columns it accumulates in the P.V product.
@@ -415,236 +441,220 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   const float b1e = s_bias[2 * j] * INV_SQRT_D * LOG2E, b1o = s_bias[2 * j + 1] * INV_SQRT_D * LOG2E;
   const float* mask_e = (v.mask != nullptr && he_ok) ? v.mask + (int64_t)(hq0 + 2 * j) * v.mask_row_stride : nullptr;
   const float* mask_o = (v.mask != nullptr && ho_ok) ? v.mask + (int64_t)(hq0 + 2 * j + 1) * v.mask_row_stride : nullptr;
+  const bool has_mask = v.mask != nullptr;
   const bool k_aligned = !(kd.sub2 & 1) && !(kd.sub4 & 3) && !(kd.n8 & 3);
-  const uint2* qs_lane = qsA + lane;
+  const bool k_simple = kd.nsp2 == 1 && kd.nsp4 == 1 && kd.nkb8 == 1;   // one span per segment: straight-line code
+  const uint32_t qs_lane = qs_base + 8 * lane;
 
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  float m_e = -INFINITY, m_o = -INFINITY;                  // running maxima of heads 2j, 2j+1 (same in every r)
+  float m_e = -INFINITY, m_o = -INFINITY;                  // reference maxima of heads 2j, 2j+1 (same in every r)
   float l_e = 0.f, l_o = 0.f, zc_e = 0.f, zc_o = 0.f;      // partial sums over this thread's rows
   int cur_phase = -1;
 
 #pragma unroll 1
-  for (int it = 0; it < n_my; ++it) {
+  for (int it = 0; it < total_tiles; ++it) {
     const int stage = it % FSTAGES;
-    cp_wait<FSTAGES - 1>();                                // this lane's copies of tile `it` have landed
-    __syncwarp();                                          // ... and every other lane's
-    const TileDesc t = tile_of(G, warp + it * FW);
-    const unsigned char* sb = wstage + (size_t)stage * stage_bytes;
+    cp_wait<FSTAGES - 1>();                                // this thread's copies of tile `it` have landed
+    __syncthreads();                                       // ... and everybody else's
+    const TileDesc t = tile_of(G, it);
     const int p = t.phase;
+    const int ngroups = (t.n + 15) >> 4, gpw = (ngroups + FW - 1) / FW;
+    const int gb = warp * gpw, ge = min(ngroups, gb + gpw);      // this warp's 16-row groups of the tile
 
-    if (p != cur_phase) {                                  // change of accumulator units (powers of two)
-      if (cur_phase >= 0) {
+    if (gb < ge) {
+      if (p != cur_phase) {                                // change of accumulator units (powers of two)
+        if (cur_phase >= 0) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float f = pow2i(acc_exp(cur_phase, i & 3) - acc_exp(p, i & 3));
-          acc[i][0] *= f; acc[i][1] *= f; acc[i][2] *= f; acc[i][3] *= f;
+          for (int i = 0; i < 8; ++i) {
+            const float f = pow2i(acc_exp(cur_phase, i & 3) - acc_exp(p, i & 3));
+            acc[i][0] *= f; acc[i][1] *= f; acc[i][2] *= f; acc[i][3] *= f;
+          }
         }
+        cur_phase = p;
       }
-      cur_phase = p;
-    }
-    // in-stage byte offsets of the tile's first row (low address bits of the sources)
-    const int off_k2 = (int)((reinterpret_cast<uintptr_t>(G.k2[p]) + (uint32_t)(t.row0 * kd.sub2)) & 15);
-    const int off_k4 = (int)((reinterpret_cast<uintptr_t>(G.k4[p]) + (uint32_t)(t.row0 * kd.sub4)) & 15);
-    const int off_k8 = (int)((reinterpret_cast<uintptr_t>(G.k8[p]) + (uint32_t)(t.row0 * kd.n8)) & 15);
-    const int off_v = (int)((reinterpret_cast<uintptr_t>(G.vrow[p]) + (uint32_t)(t.row0 * phase_row_bytes(p))) & 15);
-    int off_m = 0, off_z = 0;
-    if (p < 3) {
-      off_m = (int)((reinterpret_cast<uintptr_t>(G.sc[p]) + (uint32_t)(t.row0 * 2)) & 15);
-      off_z = (int)((reinterpret_cast<uintptr_t>(G.zp[p]) + (uint32_t)(t.row0 * 2)) & 15);
-    }
-    const bool kfast = k_aligned && !(off_k2 & 1) && !(off_k4 & 3) && !(off_k8 & 3);
-    const int64_t krow0 = G.krow[p] + t.row0;              // stripe row of the tile's first row (mask column)
-    // per-thread cursors: K rows r (and r+8) of the current group, V rows 2j.., scale/zp rows r
-    const unsigned char* k2p = sb + SL.k2 + off_k2 + r * kd.sub2 + 2 * j;
-    const unsigned char* k4p = sb + SL.k4 + off_k4 + r * kd.sub4 + 4 * j;
-    const unsigned char* k8p = sb + SL.k8 + off_k8 + r * kd.n8 + 4 * j;
-    const uint16_t* scp = reinterpret_cast<const uint16_t*>(sb + SL.sc + off_m) + r;
-    const uint16_t* zpp = reinterpret_cast<const uint16_t*>(sb + SL.zp + off_z) + r;
-    const int vrb = phase_row_bytes(p);
-    const unsigned char* vp = sb + SL.v + off_v + (p == 3 ? 8 : 4) * r + 2 * j * vrb;
+      const uint32_t sbu = smem0 + stage * stage_bytes;
+      // low address bits of the sources = byte offsets of the tile's first row inside its stage area
+      const uint32_t off_k2 = ((uint32_t)reinterpret_cast<uintptr_t>(G.k2[p]) + (uint32_t)(t.row0 * kd.sub2)) & 15u;
+      const uint32_t off_k4 = ((uint32_t)reinterpret_cast<uintptr_t>(G.k4[p]) + (uint32_t)(t.row0 * kd.sub4)) & 15u;
+      const uint32_t off_k8 = ((uint32_t)reinterpret_cast<uintptr_t>(G.k8[p]) + (uint32_t)(t.row0 * kd.n8)) & 15u;
+      const int vrb = phase_row_bytes(p);
+      const uint32_t off_v = ((uint32_t)reinterpret_cast<uintptr_t>(G.vrow[p]) + (uint32_t)(t.row0 * vrb)) & 15u;
+      uint32_t off_m = 0, off_z = 0;
+      if (p < 3) {
+        off_m = ((uint32_t)reinterpret_cast<uintptr_t>(G.sc[p]) + (uint32_t)(t.row0 * 2)) & 15u;
+        off_z = ((uint32_t)reinterpret_cast<uintptr_t>(G.zp[p]) + (uint32_t)(t.row0 * 2)) & 15u;
+      }
+      const bool kfast = k_aligned && !(off_k2 & 1) && !(off_k4 & 3) && !(off_k8 & 3);
+      const int row_b = gb * 16;                           // first row of this warp inside the tile
+      // cursors (shared-window addresses): K rows r / r+8 of the group, scale/zp row r, V rows 2j..
+      uint32_t k2a = sbu + SL.k2 + off_k2 + (row_b + r) * kd.sub2 + 2 * j;
+      uint32_t k4a = sbu + SL.k4 + off_k4 + (row_b + r) * kd.sub4 + 4 * j;
+      uint32_t k8a = sbu + SL.k8 + off_k8 + (row_b + r) * kd.n8 + 4 * j;
+      uint32_t sca = sbu + SL.sc + off_m + 2 * (row_b + r);
+      uint32_t zpa = sbu + SL.zp + off_z + 2 * (row_b + r);
+      uint32_t va = sbu + SL.v + off_v + (p == 3 ? 8 : 4) * r + (row_b + 2 * j) * vrb;
+      const int64_t krow0 = G.krow[p] + t.row0;            // stripe row of the tile's first row (mask column)
 
 #pragma unroll 1
-    for (int g16 = 0; g16 < t.n; g16 += 16) {
-      // ── scores of rows g16+r (A) and g16+r+8 (B): two independent MMA chains ──
-      float sx[4] = {0.f, 0.f, 0.f, 0.f}, sy[4] = {0.f, 0.f, 0.f, 0.f};
-      {
-        const uint2* qp = qs_lane;
-        if (kfast) {
+      for (int g16 = row_b; g16 < ge * 16; g16 += 16) {
+        // ── scores of rows g16+r (A) and g16+r+8 (B): two independent MMA chains ──
+        float sx[4] = {0.f, 0.f, 0.f, 0.f}, sy[4] = {0.f, 0.f, 0.f, 0.f};
+        if (k_simple && kfast) {
+          const uint2 q0 = lds64<0>(qs_lane), q1 = lds64<256>(qs_lane), q2 = lds64<512>(qs_lane),
+                      q3 = lds64<768>(qs_lane), q4 = lds64<1024>(qs_lane);
+          const uint32_t w2A = lds16(k2a), w2B = lds16(k2a + 8 * kd.sub2);
+          const uint32_t w4A = lds32(k4a), w4B = lds32(k4a + 8 * kd.sub4);
+          const uint32_t w8A = lds32(k8a), w8B = lds32(k8a + 8 * kd.n8);
+          const uint32_t yA = prmt(w2A, 0u, 0x4140), yB = prmt(w2B, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
+          mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
+          mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
+          const uint32_t vA = w4A >> 8, vB = w4B >> 8;
+          mma16816(sx, w4A & 0x000F000Fu, w4B & 0x000F000Fu, w4A & 0x00F000F0u, w4B & 0x00F000F0u, q2.x, q2.y);
+          mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q3.x, q3.y);
+          mma16816(sx, w8A & 0x00FF00FFu, w8B & 0x00FF00FFu, prmt(w8A, 0u, 0x4341), prmt(w8B, 0u, 0x4341), q4.x, q4.y);
+        } else {
+          uint32_t qa = qs_lane;
 #pragma unroll 1
-          for (int s = 0; s < kd.nsp2; ++s, qp += 64) {
-            const uint2 q0 = qp[0], q1 = qp[32];
-            const uint32_t wA = *reinterpret_cast<const uint16_t*>(k2p + 8 * s);
-            const uint32_t wB = *reinterpret_cast<const uint16_t*>(k2p + 8 * kd.sub2 + 8 * s);
-            const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
-            mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
-            mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
-          }
-#pragma unroll 1
-          for (int s = 0; s < kd.nsp4; ++s, qp += 64) {
-            const uint2 q0 = qp[0], q1 = qp[32];
-            const uint32_t wA = *reinterpret_cast<const uint32_t*>(k4p + 16 * s);
-            const uint32_t wB = *reinterpret_cast<const uint32_t*>(k4p + 8 * kd.sub4 + 16 * s);
-            const uint32_t vA = wA >> 8, vB = wB >> 8;
-            mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, q0.x, q0.y);
-            mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q1.x, q1.y);
-          }
-#pragma unroll 1
-          for (int b = 0; b < kd.nkb8; ++b, qp += 32) {
-            const uint2 q0 = qp[0];
-            const uint32_t wA = *reinterpret_cast<const uint32_t*>(k8p + 16 * b);
-            const uint32_t wB = *reinterpret_cast<const uint32_t*>(k8p + 8 * kd.n8 + 16 * b);
-            if (b & 1) mma16816(sy, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
-            else mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
-          }
-        } else {                                           // rows not 2/4-byte aligned in the stage
-          const unsigned char* b2 = sb + SL.k2; const unsigned char* b4 = sb + SL.k4; const unsigned char* b8 = sb + SL.k8;
-          const int o2 = (int)(k2p - b2), o4 = (int)(k4p - b4), o8 = (int)(k8p - b8);
-#pragma unroll 1
-          for (int s = 0; s < kd.nsp2; ++s, qp += 64) {
-            const uint2 q0 = qp[0], q1 = qp[32];
-            const uint32_t wA = lds_unaligned(b2, o2 + 8 * s), wB = lds_unaligned(b2, o2 + 8 * kd.sub2 + 8 * s);
+          for (int s = 0; s < kd.nsp2; ++s, qa += 512) {
+            const uint2 q0 = lds64<0>(qa), q1 = lds64<256>(qa);
+            const uint32_t wA = kfast ? lds16(k2a + 8 * s) : lds32_unaligned(k2a + 8 * s);
+            const uint32_t wB = kfast ? lds16(k2a + 8 * kd.sub2 + 8 * s) : lds32_unaligned(k2a + 8 * kd.sub2 + 8 * s);
             const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);
             mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
             mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
           }
 #pragma unroll 1
-          for (int s = 0; s < kd.nsp4; ++s, qp += 64) {
-            const uint2 q0 = qp[0], q1 = qp[32];
-            const uint32_t wA = lds_unaligned(b4, o4 + 16 * s), wB = lds_unaligned(b4, o4 + 8 * kd.sub4 + 16 * s);
+          for (int s = 0; s < kd.nsp4; ++s, qa += 512) {
+            const uint2 q0 = lds64<0>(qa), q1 = lds64<256>(qa);
+            const uint32_t wA = kfast ? lds32(k4a + 16 * s) : lds32_unaligned(k4a + 16 * s);
+            const uint32_t wB = kfast ? lds32(k4a + 8 * kd.sub4 + 16 * s) : lds32_unaligned(k4a + 8 * kd.sub4 + 16 * s);
             const uint32_t vA = wA >> 8, vB = wB >> 8;
             mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, q0.x, q0.y);
             mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q1.x, q1.y);
           }
 #pragma unroll 1
-          for (int b = 0; b < kd.nkb8; ++b, qp += 32) {
-            const uint2 q0 = qp[0];
-            const uint32_t wA = lds_unaligned(b8, o8 + 16 * b), wB = lds_unaligned(b8, o8 + 8 * kd.n8 + 16 * b);
-            if (b & 1) mma16816(sy, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
-            else mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, (wA >> 8) & 0x00FF00FFu, (wB >> 8) & 0x00FF00FFu, q0.x, q0.y);
+          for (int b = 0; b < kd.nkb8; ++b, qa += 256) {
+            const uint2 q0 = lds64<0>(qa);
+            const uint32_t wA = kfast ? lds32(k8a + 16 * b) : lds32_unaligned(k8a + 16 * b);
+            const uint32_t wB = kfast ? lds32(k8a + 8 * kd.n8 + 16 * b) : lds32_unaligned(k8a + 8 * kd.n8 + 16 * b);
+            mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, prmt(wA, 0u, 0x4341), prmt(wB, 0u, 0x4341), q0.x, q0.y);
           }
         }
-      }
-      // sx+sy: [0] (row A, head 2j) [1] (row A, head 2j+1) [2] (row B, head 2j) [3] (row B, head 2j+1)
-      const bool full = g16 + 16 <= t.n;
-      const bool rowA_ok = full || g16 + r < t.n, rowB_ok = full || g16 + r + 8 < t.n;
-      float s2[4];
-      s2[0] = fmaf(sx[0] + sy[0], c1, -b1e); s2[1] = fmaf(sx[1] + sy[1], c1, -b1o);
-      s2[2] = fmaf(sx[2] + sy[2], c1, -b1e); s2[3] = fmaf(sx[3] + sy[3], c1, -b1o);
-      if (mask_e != nullptr || mask_o != nullptr) {
-        const int64_t ca = krow0 + g16 + r;
-        if (mask_e != nullptr) { if (rowA_ok) s2[0] += mask_e[ca] * LOG2E; if (rowB_ok) s2[2] += mask_e[ca + 8] * LOG2E; }
-        if (mask_o != nullptr) { if (rowA_ok) s2[1] += mask_o[ca] * LOG2E; if (rowB_ok) s2[3] += mask_o[ca + 8] * LOG2E; }
-      }
-      if (!he_ok || !rowA_ok) s2[0] = -INFINITY;
-      if (!ho_ok || !rowA_ok) s2[1] = -INFINITY;
-      if (!he_ok || !rowB_ok) s2[2] = -INFINITY;
-      if (!ho_ok || !rowB_ok) s2[3] = -INFINITY;
-      float me = fmaxf(s2[0], s2[2]), mo = fmaxf(s2[1], s2[3]);
+        // sx+sy: [0] (row A, head 2j) [1] (row A, head 2j+1) [2] (row B, head 2j) [3] (row B, head 2j+1)
+        const bool full = g16 + 16 <= t.n;
+        const bool rowA_ok = full || g16 + r < t.n, rowB_ok = full || g16 + r + 8 < t.n;
+        float s2[4];
+        s2[0] = fmaf(sx[0] + sy[0], c1, -b1e); s2[1] = fmaf(sx[1] + sy[1], c1, -b1o);
+        s2[2] = fmaf(sx[2] + sy[2], c1, -b1e); s2[3] = fmaf(sx[3] + sy[3], c1, -b1o);
+        if (has_mask) {
+          const int64_t ca = krow0 + g16 + r;
+          if (mask_e != nullptr) { if (rowA_ok) s2[0] += mask_e[ca] * LOG2E; if (rowB_ok) s2[2] += mask_e[ca + 8] * LOG2E; }
+          if (mask_o != nullptr) { if (rowA_ok) s2[1] += mask_o[ca] * LOG2E; if (rowB_ok) s2[3] += mask_o[ca + 8] * LOG2E; }
+        }
+        if (!he_ok || !rowA_ok) s2[0] = -INFINITY;
+        if (!ho_ok || !rowA_ok) s2[1] = -INFINITY;
+        if (!he_ok || !rowB_ok) s2[2] = -INFINITY;
+        if (!ho_ok || !rowB_ok) s2[3] = -INFINITY;
+        // lazy reference maximum: exact maxima are only worked out when some score of the warp
+        // exceeds its head's reference by more than RESCALE_TH (always true for the first group)
+        const float te = m_e + RESCALE_TH, to = m_o + RESCALE_TH;
+        if (__any_sync(0xffffffffu, s2[0] > te || s2[2] > te || s2[1] > to || s2[3] > to)) {
+          float me = fmaxf(s2[0], s2[2]), mo = fmaxf(s2[1], s2[3]);
 #pragma unroll
-      for (int o = 4; o < 32; o <<= 1) {
-        me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
-        mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
-      }
-      // lazy rescale: keep the old reference maximum while the new one is within 2^RESCALE_TH of it
-      if (__any_sync(0xffffffffu, me > m_e + RESCALE_TH || mo > m_o + RESCALE_TH)) {
-        const float ne = fmaxf(m_e, me), no = fmaxf(m_o, mo);
-        const float ae = (ne == -INFINITY) ? 1.f : ex2(m_e - ne), ao = (no == -INFINITY) ? 1.f : ex2(m_o - no);
-        l_e *= ae; zc_e *= ae; l_o *= ao; zc_o *= ao;
+          for (int o = 4; o < 32; o <<= 1) {
+            me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
+            mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
+          }
+          const float ne = fmaxf(m_e, me), no = fmaxf(m_o, mo);
+          const float ae = (ne == -INFINITY) ? 1.f : ex2(m_e - ne), ao = (no == -INFINITY) ? 1.f : ex2(m_o - no);
+          l_e *= ae; zc_e *= ae; l_o *= ao; zc_o *= ao;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
-        m_e = ne; m_o = no;
-      }
-      const float mse = (m_e == -INFINITY) ? 0.f : m_e, mso = (m_o == -INFINITY) ? 0.f : m_o;
-      float pe[4];
-      pe[0] = ex2(s2[0] - mse); pe[1] = ex2(s2[1] - mso); pe[2] = ex2(s2[2] - mse); pe[3] = ex2(s2[3] - mso);
-      l_e += pe[0] + pe[2]; l_o += pe[1] + pe[3];
-      uint32_t hA, hB;                                     // (row A | row B) x (head 2j, head 2j+1) as fp16 pairs
-      if (p < 3) {
-        float scA = h2f(scp[g16]), scB = h2f(scp[g16 + 8]), zpA = h2f(zpp[g16]), zpB = h2f(zpp[g16 + 8]);
-        if (!rowA_ok) { scA = 0.f; zpA = 0.f; }            // dead rows may hold non-finite bytes
-        if (!rowB_ok) { scB = 0.f; zpB = 0.f; }
-        hA = pack_h2(pe[0] * scA, pe[1] * scA); hB = pack_h2(pe[2] * scB, pe[3] * scB);
-        const float2 fA = __half22float2(*reinterpret_cast<__half2*>(&hA));   // the values the tensor core sees
-        const float2 fB = __half22float2(*reinterpret_cast<__half2*>(&hB));
-        zc_e = fmaf(fA.x, zpA, zc_e); zc_o = fmaf(fA.y, zpA, zc_o);
-        zc_e = fmaf(fB.x, zpB, zc_e); zc_o = fmaf(fB.y, zpB, zc_o);
-      } else {
-        hA = pack_h2(pe[0], pe[1]); hB = pack_h2(pe[2], pe[3]);
-      }
-      // 8x8 transposes: thread (r, j) now holds head r at rows g16 + {2j, 2j+1} and g16 + 8 + {2j, 2j+1}
-      const uint32_t pb0 = movmatrix_trans(hA), pb1 = movmatrix_trans(hB);
+          for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
+          m_e = ne; m_o = no;
+        }
+        const float mse = (m_e == -INFINITY) ? 0.f : m_e, mso = (m_o == -INFINITY) ? 0.f : m_o;
+        float pe[4];
+        pe[0] = ex2(s2[0] - mse); pe[1] = ex2(s2[1] - mso); pe[2] = ex2(s2[2] - mse); pe[3] = ex2(s2[3] - mso);
+        l_e += pe[0] + pe[2]; l_o += pe[1] + pe[3];
+        uint32_t hA, hB;                                   // (row A | row B) x (head 2j, head 2j+1) as fp16 pairs
+        if (p < 3) {
+          float scA = h2f((uint16_t)lds16(sca)), scB = h2f((uint16_t)lds16<16>(sca));
+          float zpA = h2f((uint16_t)lds16(zpa)), zpB = h2f((uint16_t)lds16<16>(zpa));
+          if (!rowA_ok) { scA = 0.f; zpA = 0.f; }          // dead rows may hold non-finite bytes
+          if (!rowB_ok) { scB = 0.f; zpB = 0.f; }
+          hA = pack_h2(pe[0] * scA, pe[1] * scA); hB = pack_h2(pe[2] * scB, pe[3] * scB);
+          const float2 fA = __half22float2(*reinterpret_cast<__half2*>(&hA));   // the values the tensor core sees
+          const float2 fB = __half22float2(*reinterpret_cast<__half2*>(&hB));
+          zc_e = fmaf(fA.x, zpA, zc_e); zc_o = fmaf(fA.y, zpA, zc_o);
+          zc_e = fmaf(fB.x, zpB, zc_e); zc_o = fmaf(fB.y, zpB, zc_o);
+        } else {
+          hA = pack_h2(pe[0], pe[1]); hB = pack_h2(pe[2], pe[3]);
+        }
+        // 8x8 transposes: thread (r, j) now holds head r at rows g16 + {2j, 2j+1} and g16 + 8 + {2j, 2j+1}
+        const uint32_t pb0 = movmatrix_trans(hA), pb1 = movmatrix_trans(hB);
 
-      // ── P.V: channels on M, rows on K; this thread supplies rows g16 + {2j,2j+1,8+2j,9+2j} ──
-      const unsigned char* base = vp + g16 * vrb;
-      if (p == 2) {
+        // ── P.V: channels on M, rows on K; this thread supplies rows g16 + {2j,2j+1,8+2j,9+2j} ──
+        if (p == 2) {
 #pragma unroll
-        for (int vv = 0; vv < 4; ++vv) {
-          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + 32 * vv);
-          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + 32 * vv + 128);
-          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + 32 * vv + 8 * 128);
-          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + 32 * vv + 9 * 128);
+          for (int vv = 0; vv < 4; ++vv) {
+            const uint32_t w0 = lds32(va + 32 * vv), w1 = lds32(va + 32 * vv + 128);
+            const uint32_t w2 = lds32(va + 32 * vv + 8 * 128), w3 = lds32(va + 32 * vv + 9 * 128);
 #pragma unroll
-          for (int qq = 0; qq < 2; ++qq) {
-            const uint32_t sel = qq ? 0x7632u : 0x5410u;
-            const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
-            mma16816(acc[4 * qq + vv], y01 & 0x00FF00FFu, (y01 >> 8) & 0x00FF00FFu, y23 & 0x00FF00FFu,
-                     (y23 >> 8) & 0x00FF00FFu, pb0, pb1);
+            for (int qq = 0; qq < 2; ++qq) {
+              const uint32_t sel = qq ? 0x7632u : 0x5410u;
+              const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
+              mma16816(acc[4 * qq + vv], y01 & 0x00FF00FFu, prmt(y01, 0u, 0x4341), y23 & 0x00FF00FFu,
+                       prmt(y23, 0u, 0x4341), pb0, pb1);
+            }
           }
-        }
-      } else if (p == 1) {
+        } else if (p == 1) {
 #pragma unroll
-        for (int vl = 0; vl < 2; ++vl) {
-          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base + 32 * vl);
-          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + 32 * vl + 64);
-          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + 32 * vl + 8 * 64);
-          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + 32 * vl + 9 * 64);
+          for (int vl = 0; vl < 2; ++vl) {
+            const uint32_t w0 = lds32(va + 32 * vl), w1 = lds32(va + 32 * vl + 64);
+            const uint32_t w2 = lds32(va + 32 * vl + 8 * 64), w3 = lds32(va + 32 * vl + 9 * 64);
+#pragma unroll
+            for (int qq = 0; qq < 2; ++qq) {
+              const uint32_t sel = qq ? 0x7632u : 0x5410u;
+              const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
+              const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
+              mma16816(acc[4 * qq + vl], y01 & 0x000F000Fu, z01 & 0x000F000Fu, y23 & 0x000F000Fu, z23 & 0x000F000Fu,
+                       pb0, pb1);
+              mma16816(acc[4 * qq + vl + 2], y01 & 0x00F000F0u, z01 & 0x00F000F0u, y23 & 0x00F000F0u,
+                       z23 & 0x00F000F0u, pb0, pb1);
+            }
+          }
+        } else if (p == 0) {
+          const uint32_t w0 = lds32(va), w1 = lds32(va + 32), w2 = lds32(va + 8 * 32), w3 = lds32(va + 9 * 32);
 #pragma unroll
           for (int qq = 0; qq < 2; ++qq) {
             const uint32_t sel = qq ? 0x7632u : 0x5410u;
             const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
             const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
-            mma16816(acc[4 * qq + vl], y01 & 0x000F000Fu, z01 & 0x000F000Fu, y23 & 0x000F000Fu, z23 & 0x000F000Fu,
-                     pb0, pb1);
-            mma16816(acc[4 * qq + vl + 2], y01 & 0x00F000F0u, z01 & 0x00F000F0u, y23 & 0x00F000F0u,
-                     z23 & 0x00F000F0u, pb0, pb1);
-          }
-        }
-      } else if (p == 0) {
-        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(base);
-        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(base + 32);
-        const uint32_t w2 = *reinterpret_cast<const uint32_t*>(base + 8 * 32);
-        const uint32_t w3 = *reinterpret_cast<const uint32_t*>(base + 9 * 32);
 #pragma unroll
-        for (int qq = 0; qq < 2; ++qq) {
-          const uint32_t sel = qq ? 0x7632u : 0x5410u;
-          const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
-          const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
+            for (int vv = 0; vv < 4; ++vv) {
+              const uint32_t mk = 0x00030003u << (2 * vv);
+              mma16816(acc[4 * qq + vv], y01 & mk, z01 & mk, y23 & mk, z23 & mk, pb0, pb1);
+            }
+          }
+        } else {                                           // fp16 rows: channel c at byte 2c
 #pragma unroll
           for (int vv = 0; vv < 4; ++vv) {
-            const uint32_t mk = 0x00030003u << (2 * vv);
-            mma16816(acc[4 * qq + vv], y01 & mk, z01 & mk, y23 & mk, z23 & mk, pb0, pb1);
+            const uint2 w0 = lds64(va + 64 * vv), w1 = lds64(va + 64 * vv + 256);
+            const uint2 w2 = lds64(va + 64 * vv + 8 * 256), w3 = lds64(va + 64 * vv + 9 * 256);
+            mma16816(acc[vv], prmt(w0.x, w1.x, 0x5410), prmt(w0.x, w1.x, 0x7632), prmt(w2.x, w3.x, 0x5410),
+                     prmt(w2.x, w3.x, 0x7632), pb0, pb1);
+            mma16816(acc[4 + vv], prmt(w0.y, w1.y, 0x5410), prmt(w0.y, w1.y, 0x7632), prmt(w2.y, w3.y, 0x5410),
+                     prmt(w2.y, w3.y, 0x7632), pb0, pb1);
           }
         }
-      } else {                                             // fp16 rows: channel c at byte 2c
-#pragma unroll
-        for (int vv = 0; vv < 4; ++vv) {
-          const uint2 w0 = *reinterpret_cast<const uint2*>(base + 64 * vv);
-          const uint2 w1 = *reinterpret_cast<const uint2*>(base + 64 * vv + 256);
-          const uint2 w2 = *reinterpret_cast<const uint2*>(base + 64 * vv + 8 * 256);
-          const uint2 w3 = *reinterpret_cast<const uint2*>(base + 64 * vv + 9 * 256);
-          mma16816(acc[vv], prmt(w0.x, w1.x, 0x5410), prmt(w0.x, w1.x, 0x7632), prmt(w2.x, w3.x, 0x5410),
-                   prmt(w2.x, w3.x, 0x7632), pb0, pb1);
-          mma16816(acc[4 + vv], prmt(w0.y, w1.y, 0x5410), prmt(w0.y, w1.y, 0x7632), prmt(w2.y, w3.y, 0x5410),
-                   prmt(w2.y, w3.y, 0x7632), pb0, pb1);
-        }
+        k2a += 16 * kd.sub2; k4a += 16 * kd.sub4; k8a += 16 * kd.n8; sca += 32; zpa += 32; va += 16 * vrb;
       }
-      k2p += 16 * kd.sub2; k4p += 16 * kd.sub4; k8p += 16 * kd.n8;
     }
-    __syncwarp();
+    __syncthreads();                                       // every warp is done with this ring slot
     const int nxt = it + FSTAGES;
-    if (nxt < n_my) issue_tile(warp + nxt * FW, stage);
+    if (nxt < total_tiles) issue_tile(nxt, stage);
     cp_commit();
   }
   cp_wait<0>();
@@ -721,7 +731,7 @@ extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_view
   const int n_hgrp = (g + GH - 1) / GH;
   if (n_views > 65535 || (int64_t)H_kv * n_hgrp > 65535) return RDKV_ERR_TOO_LARGE;
   const int stage_bytes = align16i(stage_capacity(k_row_bytes_max));
-  size_t smem = (size_t)FW * FSTAGES * stage_bytes + KB_MAX * 32 * sizeof(uint2);
+  size_t smem = (size_t)FSTAGES * stage_bytes + KB_MAX * 32 * sizeof(uint2);
   const size_t epilogue = (size_t)FW * GH * D * sizeof(float);
   if (smem < epilogue) smem = epilogue;
   if (smem > 227 * 1024) return RDKV_ERR_TOO_LARGE;
