@@ -21,7 +21,8 @@
 
 namespace rdkv {
 
-constexpr int FW = 4;                  // warps per CTA
+constexpr int FW = 4;                  // consumer (compute) warps per CTA; one more warp stages the tiles
+constexpr int CTA_THREADS = (FW + 1) * 32;
 constexpr int FSTAGES = 2;             // ring depth
 constexpr int TILE_MAX = 256;          // rows per tile (2-bit and 4-bit phases)
 constexpr int V_STAGE = 16384;         // V payload bytes per stage
@@ -70,6 +71,9 @@ __device__ __forceinline__ void cp16_partial(uint32_t dst, const void* src, int 
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Named barriers: `count` threads must arrive (bar.arrive or bar.sync) to release the waiters.
+__device__ __forceinline__ void bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void bar_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -185,6 +189,13 @@ struct CtaGeom {
 
 struct TileDesc { int phase, row0, n; };   // row0: offset from lo[phase]
 
+// What the staging warp tells the compute warps about the tile in a ring slot.
+struct TileInfo {
+  int phase, n;
+  uint32_t off_k2, off_k4, off_k8, off_v, off_m, off_z;   // byte offsets of row 0 inside each stage area
+  int64_t krow0;                                           // stripe row of row 0 (mask column)
+};
+
 __device__ __forceinline__ TileDesc tile_of(const CtaGeom& G, int idx) {
   TileDesc t;
   int p = 0;
@@ -220,7 +231,7 @@ __device__ __forceinline__ void stage_range(uint32_t dst, const unsigned char* s
     for (int i = 0; i < MAX_IT; ++i)
       if (tid + NT * i < nblk) cp16(d0 + 16 * NT * i, s0 + 16 * NT * i);
   } else {
-#pragma unroll 1
+#pragma unroll 4
     for (int b = tid; b < nblk; b += NT) cp16(dst + 16 * b, reinterpret_cast<const unsigned char*>(a0) + 16 * b);
   }
 }
@@ -248,7 +259,7 @@ __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const u
   }
 }
 
-__global__ void __launch_bounds__(FW * 32, 3)
+__global__ void __launch_bounds__(CTA_THREADS, 3)
 decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __restrict__ q, int q_dtype,
                     int H_q, int g, int chunk_rows, int n_chunks, int stage_bytes,
                     float* __restrict__ partials, float* __restrict__ out, int* __restrict__ status) {
@@ -257,6 +268,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   __shared__ CtaGeom G;
   __shared__ float s_bias[GH];
   __shared__ float s_ml[FW][GH][3];               // per warp: m, l, zero-point term
+  __shared__ TileInfo s_tile[FSTAGES];
 
   const int chunk = blockIdx.x, view_idx = blockIdx.z;
   const int n_hgrp = (g + GH - 1) / GH;
@@ -351,7 +363,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   const uint32_t qs_base = smem0 + FSTAGES * stage_bytes;  // uint2 qsA[nkb][32]
   uint2* qsA = reinterpret_cast<uint2*>(smem_raw + (size_t)FSTAGES * stage_bytes);
 
-  // Stage tile `tile_idx` into ring slot `stage`; all threads take part (one cp.async group each).
+  // Stage tile `tile_idx` into ring slot `stage`: the 32 lanes of the staging warp issue the copies
+  // (one cp.async group per tile) and lane 0 leaves the tile's description for the compute warps.
   auto issue_tile = [&](int tile_idx, int stage) {
     const TileDesc t = tile_of(G, tile_idx);
     unsigned char* sb = smem_raw + (size_t)stage * stage_bytes;
@@ -362,13 +375,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     const unsigned char* a_v = G.vrow[p] + (int64_t)t.row0 * phase_row_bytes(p);
     if (G.fast) {
       const uint32_t sbu = smem0 + stage * stage_bytes;
-      stage_range<V_STAGE / (16 * FW * 32) + 1, FW * 32>(sbu + SL.v, a_v, t.n * phase_row_bytes(p), tid);
-      if (kd.sub2) stage_range<0, FW * 32>(sbu + SL.k2, a_k2, t.n * kd.sub2, tid);
-      if (kd.sub4) stage_range<0, FW * 32>(sbu + SL.k4, a_k4, t.n * kd.sub4, tid);
-      if (kd.n8) stage_range<0, FW * 32>(sbu + SL.k8, a_k8, t.n * kd.n8, tid);
+      stage_range<0, 32>(sbu + SL.v, a_v, t.n * phase_row_bytes(p), lane);
+      if (kd.sub2) stage_range<0, 32>(sbu + SL.k2, a_k2, t.n * kd.sub2, lane);
+      if (kd.sub4) stage_range<0, 32>(sbu + SL.k4, a_k4, t.n * kd.sub4, lane);
+      if (kd.n8) stage_range<0, 32>(sbu + SL.k8, a_k8, t.n * kd.n8, lane);
       if (p < 3) {
-        stage_range<1, FW * 32>(sbu + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, tid);
-        stage_range<1, FW * 32>(sbu + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, tid);
+        stage_range<0, 32>(sbu + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, lane);
+        stage_range<0, 32>(sbu + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, lane);
       }
     } else {
       const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
@@ -376,13 +389,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
       const unsigned char* vlo = p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : v16b;
       const int64_t vext = p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes;
-      stage_range_guarded(sb + SL.v, a_v, t.n * phase_row_bytes(p), vlo, vlo + vext, tid, FW * 32);
-      if (kd.sub2) stage_range_guarded(sb + SL.k2, a_k2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, tid, FW * 32);
-      if (kd.sub4) stage_range_guarded(sb + SL.k4, a_k4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, tid, FW * 32);
-      if (kd.n8) stage_range_guarded(sb + SL.k8, a_k8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, tid, FW * 32);
+      stage_range_guarded(sb + SL.v, a_v, t.n * phase_row_bytes(p), vlo, vlo + vext, lane, 32);
+      if (kd.sub2) stage_range_guarded(sb + SL.k2, a_k2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, lane, 32);
+      if (kd.sub4) stage_range_guarded(sb + SL.k4, a_k4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, lane, 32);
+      if (kd.n8) stage_range_guarded(sb + SL.k8, a_k8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, lane, 32);
       if (p < 3) {
-        stage_range_guarded(sb + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, scb, scb + v.v_meta_bytes, tid, FW * 32);
-        stage_range_guarded(sb + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, zpb, zpb + v.v_meta_bytes, tid, FW * 32);
+        stage_range_guarded(sb + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, scb, scb + v.v_meta_bytes, lane, 32);
+        stage_range_guarded(sb + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, zpb, zpb + v.v_meta_bytes, lane, 32);
       }
     }
     // rows past the tile's end must hold finite fp16 data in the fp16 phase: clear the
@@ -391,17 +404,43 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       const int off = (int)(reinterpret_cast<uintptr_t>(a_v) & 15);
       const int first = (off + t.n * 256 + 15) & ~15;
       const int last = off + ((t.n + 15) & ~15) * 256;
-      for (int i = first + 4 * tid; i < last; i += 4 * FW * 32) *reinterpret_cast<uint32_t*>(sb + SL.v + i) = 0u;
+      for (int i = first + 4 * lane; i < last; i += 4 * 32) *reinterpret_cast<uint32_t*>(sb + SL.v + i) = 0u;
+    }
+    if (lane == 0) {
+      TileInfo& ti = s_tile[stage];
+      ti.phase = p; ti.n = t.n;
+      ti.off_k2 = (uint32_t)reinterpret_cast<uintptr_t>(a_k2) & 15u;
+      ti.off_k4 = (uint32_t)reinterpret_cast<uintptr_t>(a_k4) & 15u;
+      ti.off_k8 = (uint32_t)reinterpret_cast<uintptr_t>(a_k8) & 15u;
+      ti.off_v = (uint32_t)reinterpret_cast<uintptr_t>(a_v) & 15u;
+      ti.off_m = p < 3 ? ((uint32_t)reinterpret_cast<uintptr_t>(G.sc[p]) + 2u * t.row0) & 15u : 0u;
+      ti.off_z = p < 3 ? ((uint32_t)reinterpret_cast<uintptr_t>(G.zp[p]) + 2u * t.row0) & 15u : 0u;
+      ti.krow0 = G.krow[p] + t.row0;
     }
   };
 
-  for (int it = 0; it < FSTAGES; ++it) {                  // one group per ring slot, empty or not
-    if (it < total_tiles) issue_tile(it, it);
-    cp_commit();
+  // barrier ids: FULL[s] = 1 + s (tile in slot s has landed), FREE[s] = 1 + FSTAGES + s (slot s may be
+  // refilled), 1 + 2*FSTAGES: the compute warps among themselves
+  constexpr int BAR_FULL = 1, BAR_FREE = 1 + FSTAGES, BAR_COMPUTE = 1 + 2 * FSTAGES;
+
+  if (warp == FW) {
+    // ── staging warp ──────────────────────────────────────────────────────────
+    // A tile is announced (FULL) as soon as it has landed, before the warp waits for
+    // the next free slot, so the compute warps never wait on the staging of a later tile.
+#pragma unroll 1
+    for (int it = 0; it < total_tiles; ++it) {
+      const int stage = it % FSTAGES;
+      if (it >= FSTAGES) bar_sync(BAR_FREE + stage, CTA_THREADS);          // compute warps left the slot
+      issue_tile(it, stage);
+      cp_commit();
+      cp_wait<0>();
+      __syncwarp();
+      bar_arrive(BAR_FULL + stage, CTA_THREADS);
+    }
   }
 
   // ── q*scale in MMA fragment order and the zero-point bias (overlaps the first copies) ──
-  {
+  if (warp < FW) {
     const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
     const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
     const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
@@ -427,9 +466,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
     if (j == 0) s_ml[warp][r][0] = bias_part;
-    __syncthreads();
+    bar_sync(BAR_COMPUTE, FW * 32);
     if (tid < GH) s_bias[tid] = s_ml[0][tid][0] + s_ml[1][tid][0] + s_ml[2][tid][0] + s_ml[3][tid][0];
-    __syncthreads();
+    bar_sync(BAR_COMPUTE, FW * 32);
   }
 
   // ── workers ─────────────────────────────────────────────────────────────────
@@ -438,7 +477,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   // heads whose output columns it accumulates in the P.V product.
   const bool he_ok = 2 * j < gcnt, ho_ok = 2 * j + 1 < gcnt;
   const float c1 = TWO24 * INV_SQRT_D * LOG2E;             // scores are kept in base-2 units
-  const float b1e = s_bias[2 * j] * INV_SQRT_D * LOG2E, b1o = s_bias[2 * j + 1] * INV_SQRT_D * LOG2E;
+  // an absent head gets an infinite bias: its scores are -inf without further tests
+  const float b1e = he_ok ? s_bias[2 * j] * INV_SQRT_D * LOG2E : INFINITY;
+  const float b1o = ho_ok ? s_bias[2 * j + 1] * INV_SQRT_D * LOG2E : INFINITY;
   const float* mask_e = (v.mask != nullptr && he_ok) ? v.mask + (int64_t)(hq0 + 2 * j) * v.mask_row_stride : nullptr;
   const float* mask_o = (v.mask != nullptr && ho_ok) ? v.mask + (int64_t)(hq0 + 2 * j + 1) * v.mask_row_stride : nullptr;
   const bool has_mask = v.mask != nullptr;
@@ -454,11 +495,10 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   int cur_phase = -1;
 
 #pragma unroll 1
-  for (int it = 0; it < total_tiles; ++it) {
+  for (int it = 0; warp < FW && it < total_tiles; ++it) {
     const int stage = it % FSTAGES;
-    cp_wait<FSTAGES - 1>();                                // this thread's copies of tile `it` have landed
-    __syncthreads();                                       // ... and everybody else's
-    const TileDesc t = tile_of(G, it);
+    bar_sync(BAR_FULL + stage, CTA_THREADS);               // the tile in this slot has landed
+    const TileInfo t = s_tile[stage];
     const int p = t.phase;
     const int ngroups = (t.n + 15) >> 4, gpw = (ngroups + FW - 1) / FW;
     const int gb = warp * gpw, ge = min(ngroups, gb + gpw);      // this warp's 16-row groups of the tile
@@ -476,16 +516,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       }
       const uint32_t sbu = smem0 + stage * stage_bytes;
       // low address bits of the sources = byte offsets of the tile's first row inside its stage area
-      const uint32_t off_k2 = ((uint32_t)reinterpret_cast<uintptr_t>(G.k2[p]) + (uint32_t)(t.row0 * kd.sub2)) & 15u;
-      const uint32_t off_k4 = ((uint32_t)reinterpret_cast<uintptr_t>(G.k4[p]) + (uint32_t)(t.row0 * kd.sub4)) & 15u;
-      const uint32_t off_k8 = ((uint32_t)reinterpret_cast<uintptr_t>(G.k8[p]) + (uint32_t)(t.row0 * kd.n8)) & 15u;
+      const uint32_t off_k2 = t.off_k2, off_k4 = t.off_k4, off_k8 = t.off_k8, off_v = t.off_v;
+      const uint32_t off_m = t.off_m, off_z = t.off_z;
       const int vrb = phase_row_bytes(p);
-      const uint32_t off_v = ((uint32_t)reinterpret_cast<uintptr_t>(G.vrow[p]) + (uint32_t)(t.row0 * vrb)) & 15u;
-      uint32_t off_m = 0, off_z = 0;
-      if (p < 3) {
-        off_m = ((uint32_t)reinterpret_cast<uintptr_t>(G.sc[p]) + (uint32_t)(t.row0 * 2)) & 15u;
-        off_z = ((uint32_t)reinterpret_cast<uintptr_t>(G.zp[p]) + (uint32_t)(t.row0 * 2)) & 15u;
-      }
       const bool kfast = k_aligned && !(off_k2 & 1) && !(off_k4 & 3) && !(off_k8 & 3);
       const int row_b = gb * 16;                           // first row of this warp inside the tile
       // cursors (shared-window addresses): K rows r / r+8 of the group, scale/zp row r, V rows 2j..
@@ -495,7 +528,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       uint32_t sca = sbu + SL.sc + off_m + 2 * (row_b + r);
       uint32_t zpa = sbu + SL.zp + off_z + 2 * (row_b + r);
       uint32_t va = sbu + SL.v + off_v + (p == 3 ? 8 : 4) * r + (row_b + 2 * j) * vrb;
-      const int64_t krow0 = G.krow[p] + t.row0;            // stripe row of the tile's first row (mask column)
+      const int64_t krow0 = t.krow0;                       // stripe row of the tile's first row (mask column)
 
 #pragma unroll 1
       for (int g16 = row_b; g16 < ge * 16; g16 += 16) {
@@ -553,10 +586,10 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           if (mask_e != nullptr) { if (rowA_ok) s2[0] += mask_e[ca] * LOG2E; if (rowB_ok) s2[2] += mask_e[ca + 8] * LOG2E; }
           if (mask_o != nullptr) { if (rowA_ok) s2[1] += mask_o[ca] * LOG2E; if (rowB_ok) s2[3] += mask_o[ca + 8] * LOG2E; }
         }
-        if (!he_ok || !rowA_ok) s2[0] = -INFINITY;
-        if (!ho_ok || !rowA_ok) s2[1] = -INFINITY;
-        if (!he_ok || !rowB_ok) s2[2] = -INFINITY;
-        if (!ho_ok || !rowB_ok) s2[3] = -INFINITY;
+        if (!full) {
+          if (!rowA_ok) { s2[0] = -INFINITY; s2[1] = -INFINITY; }
+          if (!rowB_ok) { s2[2] = -INFINITY; s2[3] = -INFINITY; }
+        }
         // lazy reference maximum: exact maxima are only worked out when some score of the warp
         // exceeds its head's reference by more than RESCALE_TH (always true for the first group)
         const float te = m_e + RESCALE_TH, to = m_o + RESCALE_TH;
@@ -652,12 +685,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         k2a += 16 * kd.sub2; k4a += 16 * kd.sub4; k8a += 16 * kd.n8; sca += 32; zpa += 32; va += 16 * vrb;
       }
     }
-    __syncthreads();                                       // every warp is done with this ring slot
-    const int nxt = it + FSTAGES;
-    if (nxt < total_tiles) issue_tile(nxt, stage);
-    cp_commit();
+    if (it + FSTAGES < total_tiles) bar_arrive(BAR_FREE + stage, CTA_THREADS);   // slot may be refilled
   }
-  cp_wait<0>();
 
   // ── merge the four workers and write the chunk's record ─────────────────────
   if (cur_phase >= 0) {                                    // accumulators to true units
@@ -674,12 +703,12 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   }
   __syncthreads();                                         // every worker is done with its stages
   float* red = reinterpret_cast<float*>(smem_raw);         // [FW][GH][128]
-  if (r == 0) {
+  if (warp < FW && r == 0) {
     s_ml[warp][2 * j][0] = m_e; s_ml[warp][2 * j][1] = l_e; s_ml[warp][2 * j][2] = zc_e;
     s_ml[warp][2 * j + 1][0] = m_o; s_ml[warp][2 * j + 1][1] = l_o; s_ml[warp][2 * j + 1][2] = zc_o;
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 8 && warp < FW; ++i) {
     const int ch = 4 * r + 2 * (i >> 2) + 32 * (i & 3);
     float* o0 = red + ((warp * GH + 2 * j) * D);
     float* o1 = o0 + D;
@@ -738,7 +767,7 @@ extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_view
   cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
   dim3 grid(n_chunks, H_kv * n_hgrp, n_views);
-  decode_fused_kernel<<<grid, FW * 32, smem, (cudaStream_t)stream>>>(views, q, q_dtype, H_q, g, chunk_rows,
+  decode_fused_kernel<<<grid, CTA_THREADS, smem, (cudaStream_t)stream>>>(views, q, q_dtype, H_q, g, chunk_rows,
                                                                      n_chunks, stage_bytes, partials, out, status);
   return launch_status();
 }
