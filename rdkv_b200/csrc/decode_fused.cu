@@ -23,17 +23,24 @@ namespace rdkv {
 
 constexpr int FW = 4;                  // consumer (compute) warps per CTA; one more warp stages the tiles
 constexpr int CTA_THREADS = (FW + 1) * 32;
-constexpr int FSTAGES = 2;             // ring depth
-constexpr int TILE_MAX = 256;          // rows per tile (2-bit and 4-bit phases)
-constexpr int V_STAGE = 16384;         // V payload bytes per stage
+#ifndef RDKV_FSTAGES
+#define RDKV_FSTAGES 2
+#endif
+#ifndef RDKV_TILE_SHIFT
+#define RDKV_TILE_SHIFT 0
+#endif
+constexpr int FSTAGES = RDKV_FSTAGES;  // ring depth
+constexpr int TILE_MAX = 256 >> RDKV_TILE_SHIFT;   // rows per tile (2-bit and 4-bit phases)
+constexpr int V_STAGE = 16384 >> RDKV_TILE_SHIFT;  // V payload bytes per stage
 constexpr int GH = 8;                  // query heads per CTA pass (N of the P.V product)
 constexpr int KB_MAX = 32;             // 16-channel blocks of the score product
 constexpr float TWO24 = 16777216.f;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
+constexpr unsigned WAIT_LIMIT = 1u << 22;  // try_wait rounds before a compute warp gives up on a tile
 constexpr float RESCALE_TH = 8.f;      // log2 slack before the running maximum is moved
 
-__host__ __device__ constexpr int phase_tile_rows(int p) { return p == 0 ? 256 : p == 1 ? 256 : p == 2 ? 128 : 64; }
+__host__ __device__ constexpr int phase_tile_rows(int p) { return (p == 0 ? 256 : p == 1 ? 256 : p == 2 ? 128 : 64) >> RDKV_TILE_SHIFT; }
 __host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : p == 1 ? 64 : p == 2 ? 128 : 256; }
 
 __host__ __device__ inline int align16i(int x) { return (x + 15) & ~15; }
@@ -71,6 +78,26 @@ __device__ __forceinline__ void cp16_partial(uint32_t dst, const void* src, int 
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// mbarrier (shared memory, CTA scope).  A tile's arrival is signalled asynchronously: every
+// staging lane posts one arrival that fires when its cp.async copies have landed.
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_on_copies(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Named barriers: `count` threads must arrive (bar.arrive or bar.sync) to release the waiters.
 __device__ __forceinline__ void bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 __device__ __forceinline__ void bar_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
@@ -269,6 +296,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   __shared__ float s_bias[GH];
   __shared__ float s_ml[FW][GH][3];               // per warp: m, l, zero-point term
   __shared__ TileInfo s_tile[FSTAGES];
+  __shared__ __align__(8) uint64_t s_full[FSTAGES];   // tile in slot s has landed
 
   const int chunk = blockIdx.x, view_idx = blockIdx.z;
   const int n_hgrp = (g + GH - 1) / GH;
@@ -281,6 +309,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     int* dst = reinterpret_cast<int*>(&v);
     for (int i = tid; i < (int)(sizeof(rdkv_layer_view) / 4); i += blockDim.x) dst[i] = src[i];
   }
+  if (tid < FSTAGES) mbar_init(&s_full[tid], 64);        // per staging lane: one plain + one copy-completion arrival
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
 
   const int hq0 = h * g + gh0;                             // first query head handled here
@@ -419,24 +449,23 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     }
   };
 
-  // barrier ids: FULL[s] = 1 + s (tile in slot s has landed), FREE[s] = 1 + FSTAGES + s (slot s may be
-  // refilled), 1 + 2*FSTAGES: the compute warps among themselves
-  constexpr int BAR_FULL = 1, BAR_FREE = 1 + FSTAGES, BAR_COMPUTE = 1 + 2 * FSTAGES;
+  // named barrier ids: FREE[s] = 1 + s (slot s may be refilled), 1 + FSTAGES: the compute warps among themselves
+  constexpr int BAR_FREE = 1, BAR_COMPUTE = 1 + FSTAGES;
 
   if (warp == FW) {
     // ── staging warp ──────────────────────────────────────────────────────────
-    // A tile is announced (FULL) as soon as it has landed, before the warp waits for
-    // the next free slot, so the compute warps never wait on the staging of a later tile.
+    // It only ever waits for a free slot; a tile's landing is signalled to the compute warps
+    // by the copies themselves (mbarrier arrival on completion), so issuing the next tile
+    // overlaps the flight of the previous one.
 #pragma unroll 1
     for (int it = 0; it < total_tiles; ++it) {
       const int stage = it % FSTAGES;
       if (it >= FSTAGES) bar_sync(BAR_FREE + stage, CTA_THREADS);          // compute warps left the slot
       issue_tile(it, stage);
-      cp_commit();
-      cp_wait<0>();
-      __syncwarp();
-      bar_arrive(BAR_FULL + stage, CTA_THREADS);
+      mbar_arrive_on_copies(&s_full[stage]);                               // fires when this lane's copies land
+      mbar_arrive(&s_full[stage]);                                         // releases this lane's plain stores
     }
+    cp_wait<0>();
   }
 
   // ── q*scale in MMA fragment order and the zero-point bias (overlaps the first copies) ──
@@ -497,11 +526,22 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
 #pragma unroll 1
   for (int it = 0; warp < FW && it < total_tiles; ++it) {
     const int stage = it % FSTAGES;
-    bar_sync(BAR_FULL + stage, CTA_THREADS);               // the tile in this slot has landed
+    {                                                      // wait (bounded) until the tile in this slot has landed
+      const uint32_t parity = (it / FSTAGES) & 1;
+      unsigned spins = 0;
+      while (!mbar_try_wait(&s_full[stage], parity)) {
+        if (++spins > WAIT_LIMIT) {                        // give up: flag it and go on (results are then invalid)
+          if (lane == 0 && status != nullptr) atomicOr(status, 1);
+          break;
+        }
+      }
+    }
     const TileInfo t = s_tile[stage];
     const int p = t.phase;
-    const int ngroups = (t.n + 15) >> 4, gpw = (ngroups + FW - 1) / FW;
-    const int gb = warp * gpw, ge = min(ngroups, gb + gpw);      // this warp's 16-row groups of the tile
+    // this warp takes the tile's 16-row groups gb, gb+FW, ...; the start rotates from tile to
+    // tile so that short tiles (fewer groups than warps) do not always land on the same warps
+    const int ngroups = (t.n + 15) >> 4;
+    const int gb = (warp + FW - (it * (TILE_MAX / 64)) % FW) % FW, ge = ngroups;
 
     if (gb < ge) {
       if (p != cur_phase) {                                // change of accumulator units (powers of two)
@@ -531,7 +571,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       const int64_t krow0 = t.krow0;                       // stripe row of the tile's first row (mask column)
 
 #pragma unroll 1
-      for (int g16 = row_b; g16 < ge * 16; g16 += 16) {
+      for (int g16 = row_b; g16 < ge * 16; g16 += 16 * FW) {
         // ── scores of rows g16+r (A) and g16+r+8 (B): two independent MMA chains ──
         float sx[4] = {0.f, 0.f, 0.f, 0.f}, sy[4] = {0.f, 0.f, 0.f, 0.f};
         if (k_simple && kfast) {
@@ -682,7 +722,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
                      prmt(w2.y, w3.y, 0x7632), pb0, pb1);
           }
         }
-        k2a += 16 * kd.sub2; k4a += 16 * kd.sub4; k8a += 16 * kd.n8; sca += 32; zpa += 32; va += 16 * vrb;
+        k2a += 16 * FW * kd.sub2; k4a += 16 * FW * kd.sub4; k8a += 16 * FW * kd.n8; sca += 32 * FW; zpa += 32 * FW;
+        va += 16 * FW * vrb;
       }
     }
     if (it + FSTAGES < total_tiles) bar_arrive(BAR_FREE + stage, CTA_THREADS);   // slot may be refilled
