@@ -32,9 +32,10 @@ CFG3 = dict(layers=32, batch=16, kv_heads=8, q_heads=32, context=32768, budget=2
 L2_BYTES = 126 * 1024 * 1024
 METRIC = "packed-KV decode-attn tokens/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one fused-kernel launch from the committed ncu
-# capture (profiles/), scaled to this workload by units processed; None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = None
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one fused-kernel launch in
+# the committed ncu capture (profiles/; an 8-layer launch: 287.8 MB moved for 280.2 MB algorithmic);
+# traffic grows with the units processed, so the ratio carries over to the full launch.
+NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = 1.027
 
 
 def load_peaks():
@@ -145,11 +146,13 @@ def timed_steps(fn, steps, barrier):
     barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()          # a profiler run with --profile-from-start off sees the timed regions only
     e0.record()
     for i in range(steps):
         fn(i)
     e1.record()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     barrier()
     return e0.elapsed_time(e1)
 
@@ -164,7 +167,8 @@ def max_over_ranks(x: float, world: int, device) -> float:
 
 def run_decode(args, rank, world, device):
     from rdkv_b200._lib import lib
-    from rdkv_b200.decode import DecodeTable, decode_attention_partial, lse_combine, packed_decode_attention
+    from rdkv_b200.decode import (DecodeTable, decode_attention_partial, lse_combine, packed_decode_attention,
+                                  packed_decode_attention_host)
     cfg = dict(CFG3)
     if args.small:
         cfg.update(layers=2, batch=2, context=4096, budget=1024)
@@ -207,6 +211,7 @@ def run_decode(args, rank, world, device):
     # per-kernel duration of the fused kernel (dominant) inside the same loop, for the roofline
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     torch.cuda.synchronize()
+    torch.cuda.profiler.start()
     with sampler:
         for i in range(args.steps):
             tb = tables[i % R]
@@ -216,19 +221,19 @@ def run_decode(args, rank, world, device):
             if tb.n_chunks > 1:
                 lse_combine(part, out.view(-1, 128))
         torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     fused_ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
     fused_ms = max_over_ranks(fused_ms, world, device)
 
     # end to end through the public call with host buffers: pinned q in, pinned out back, every step
     q_host = [q.cpu().pin_memory() for q in q_pool[:min(n_q, 8)]]
-    q_dev = torch.empty_like(q_pool[0])
+    q_dev = q_pool[0]
     out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
 
     def e2e_step(i):
-        q_dev.copy_(q_host[i % len(q_host)], non_blocking=True)
-        packed_decode_attention(q_dev, tables[i % R], out=out)
-        out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()      # the caller reads the result before the next step
+        # uploads the queries, runs the kernel and downloads the results in view ranges on
+        # separate streams; returns when out_host holds the step's results
+        packed_decode_attention_host(q_host[i % len(q_host)], tables[i % R], out_host, slices=args.e2e_slices)
 
     for i in range(min(args.warmup, 3)):
         e2e_step(i)
@@ -506,6 +511,8 @@ def main():
     ap.add_argument("--small", action="store_true", help="2 layers x batch 2 (smoke-sized case)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling-sized runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-slices", type=int, default=4,
+                    help="view ranges (streams) the host-buffer call overlaps its copies and kernels over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     world = int(os.environ.get("WORLD_SIZE", "1"))

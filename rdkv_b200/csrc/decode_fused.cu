@@ -17,21 +17,29 @@
 // Zero points are handled outside the products: sum_c zp*q*scale once per CTA
 // (K side, reference "bias trick", obkv_accel/triton_k_kernel.py:14-16) and
 // sum_t p*scale*zp per head (V side).
+#include <type_traits>
+
 #include "rdkv_common.cuh"
 
 namespace rdkv {
 
-constexpr int FW = 4;                  // consumer (compute) warps per CTA; one more warp stages the tiles
-constexpr int CTA_THREADS = (FW + 1) * 32;
+#ifndef RDKV_FW
+#define RDKV_FW 4
+#endif
+#ifndef RDKV_MINB
+#define RDKV_MINB 3
+#endif
 #ifndef RDKV_FSTAGES
 #define RDKV_FSTAGES 2
 #endif
-#ifndef RDKV_TILE_SHIFT
-#define RDKV_TILE_SHIFT 0
+#ifndef RDKV_TILE_ROWS
+#define RDKV_TILE_ROWS 256
 #endif
+constexpr int FW = RDKV_FW;            // consumer (compute) warps per CTA; one more warp stages the tiles
+constexpr int CTA_THREADS = (FW + 1) * 32;
 constexpr int FSTAGES = RDKV_FSTAGES;  // ring depth
-constexpr int TILE_MAX = 256 >> RDKV_TILE_SHIFT;   // rows per tile (2-bit and 4-bit phases)
-constexpr int V_STAGE = 16384 >> RDKV_TILE_SHIFT;  // V payload bytes per stage
+constexpr int TILE_MAX = RDKV_TILE_ROWS;           // rows per tile (2-bit and 4-bit phases)
+constexpr int V_STAGE = 64 * TILE_MAX;             // V payload bytes per stage
 constexpr int GH = 8;                  // query heads per CTA pass (N of the P.V product)
 constexpr int KB_MAX = 32;             // 16-channel blocks of the score product
 constexpr float TWO24 = 16777216.f;
@@ -40,7 +48,7 @@ constexpr float LN2 = 0.6931471805599453f;
 constexpr unsigned WAIT_LIMIT = 1u << 22;  // try_wait rounds before a compute warp gives up on a tile
 constexpr float RESCALE_TH = 8.f;      // log2 slack before the running maximum is moved
 
-__host__ __device__ constexpr int phase_tile_rows(int p) { return (p == 0 ? 256 : p == 1 ? 256 : p == 2 ? 128 : 64) >> RDKV_TILE_SHIFT; }
+__host__ __device__ constexpr int phase_tile_rows(int p) { return p < 2 ? TILE_MAX : p == 2 ? TILE_MAX / 2 : TILE_MAX / 4; }
 __host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : p == 1 ? 64 : p == 2 ? 128 : 256; }
 
 __host__ __device__ inline int align16i(int x) { return (x + 15) & ~15; }
@@ -286,7 +294,11 @@ __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const u
   }
 }
 
-__global__ void __launch_bounds__(CTA_THREADS, 3)
+#ifdef RDKV_MAXNREG
+__global__ void __maxnreg__(RDKV_MAXNREG)
+#else
+__global__ void __launch_bounds__(CTA_THREADS, RDKV_MINB)
+#endif
 decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __restrict__ q, int q_dtype,
                     int H_q, int g, int chunk_rows, int n_chunks, int stage_bytes,
                     float* __restrict__ partials, float* __restrict__ out, int* __restrict__ status) {
@@ -496,7 +508,12 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
     if (j == 0) s_ml[warp][r][0] = bias_part;
     bar_sync(BAR_COMPUTE, FW * 32);
-    if (tid < GH) s_bias[tid] = s_ml[0][tid][0] + s_ml[1][tid][0] + s_ml[2][tid][0] + s_ml[3][tid][0];
+    if (tid < GH) {
+      float b = 0.f;
+#pragma unroll
+      for (int w = 0; w < FW; ++w) b += s_ml[w][tid][0];
+      s_bias[tid] = b;
+    }
     bar_sync(BAR_COMPUTE, FW * 32);
   }
 
@@ -555,176 +572,221 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         cur_phase = p;
       }
       const uint32_t sbu = smem0 + stage * stage_bytes;
-      // low address bits of the sources = byte offsets of the tile's first row inside its stage area
-      const uint32_t off_k2 = t.off_k2, off_k4 = t.off_k4, off_k8 = t.off_k8, off_v = t.off_v;
-      const uint32_t off_m = t.off_m, off_z = t.off_z;
-      const int vrb = phase_row_bytes(p);
-      const bool kfast = k_aligned && !(off_k2 & 1) && !(off_k4 & 3) && !(off_k8 & 3);
+      const bool kfast = k_aligned && !(t.off_k2 & 1) && !(t.off_k4 & 3) && !(t.off_k8 & 3);
+      const bool simple = k_simple && kfast;
       const int row_b = gb * 16;                           // first row of this warp inside the tile
-      // cursors (shared-window addresses): K rows r / r+8 of the group, scale/zp row r, V rows 2j..
-      uint32_t k2a = sbu + SL.k2 + off_k2 + (row_b + r) * kd.sub2 + 2 * j;
-      uint32_t k4a = sbu + SL.k4 + off_k4 + (row_b + r) * kd.sub4 + 4 * j;
-      uint32_t k8a = sbu + SL.k8 + off_k8 + (row_b + r) * kd.n8 + 4 * j;
-      uint32_t sca = sbu + SL.sc + off_m + 2 * (row_b + r);
-      uint32_t zpa = sbu + SL.zp + off_z + 2 * (row_b + r);
-      uint32_t va = sbu + SL.v + off_v + (p == 3 ? 8 : 4) * r + (row_b + 2 * j) * vrb;
+      // cursors (shared-window addresses): K rows r / r+8 of the group, scale/zp row r
+      // (t.off_*: low address bits of the sources = byte offsets of the tile's first row inside its stage area)
+      uint32_t k2a = sbu + SL.k2 + t.off_k2 + (row_b + r) * kd.sub2 + 2 * j;
+      uint32_t k4a = sbu + SL.k4 + t.off_k4 + (row_b + r) * kd.sub4 + 4 * j;
+      uint32_t k8a = sbu + SL.k8 + t.off_k8 + (row_b + r) * kd.n8 + 4 * j;
+      uint32_t sca = sbu + SL.sc + t.off_m + 2 * (row_b + r);
+      uint32_t zpa = sbu + SL.zp + t.off_z + 2 * (row_b + r);
+      const uint32_t v0a = sbu + SL.v + t.off_v;
       const int64_t krow0 = t.krow0;                       // stripe row of the tile's first row (mask column)
+      const int tn = t.n;
 
+      // The group loop, specialised per V phase.  Shared-memory loads are issued in program
+      // order (volatile asm), so the order below is the schedule: the K words of the NEXT
+      // group, this group's V scale/zero point and its first V words are requested while
+      // the score MMAs of this group are in flight.
+      auto run_tile = [&](auto PC) {
+        constexpr int P = decltype(PC)::value;
+        constexpr int VRB = phase_row_bytes(P);
+        uint32_t va = v0a + (P == 3 ? 8 : 4) * r + (row_b + 2 * j) * VRB;
+        uint32_t kw0 = 0, kw1 = 0, kw2 = 0, kw3 = 0, kw4 = 0, kw5 = 0;
+        if (simple) {
+          kw0 = lds16(k2a); kw1 = lds16(k2a + 8 * kd.sub2);
+          kw2 = lds32(k4a); kw3 = lds32(k4a + 8 * kd.sub4);
+          kw4 = lds32(k8a); kw5 = lds32(k8a + 8 * kd.n8);
+        }
 #pragma unroll 1
-      for (int g16 = row_b; g16 < ge * 16; g16 += 16 * FW) {
-        // ── scores of rows g16+r (A) and g16+r+8 (B): two independent MMA chains ──
-        float sx[4] = {0.f, 0.f, 0.f, 0.f}, sy[4] = {0.f, 0.f, 0.f, 0.f};
-        if (k_simple && kfast) {
-          const uint2 q0 = lds64<0>(qs_lane), q1 = lds64<256>(qs_lane), q2 = lds64<512>(qs_lane),
-                      q3 = lds64<768>(qs_lane), q4 = lds64<1024>(qs_lane);
-          const uint32_t w2A = lds16(k2a), w2B = lds16(k2a + 8 * kd.sub2);
-          const uint32_t w4A = lds32(k4a), w4B = lds32(k4a + 8 * kd.sub4);
-          const uint32_t w8A = lds32(k8a), w8B = lds32(k8a + 8 * kd.n8);
-          const uint32_t yA = prmt(w2A, 0u, 0x4140), yB = prmt(w2B, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
-          mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
-          mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
-          const uint32_t vA = w4A >> 8, vB = w4B >> 8;
-          mma16816(sx, w4A & 0x000F000Fu, w4B & 0x000F000Fu, w4A & 0x00F000F0u, w4B & 0x00F000F0u, q2.x, q2.y);
-          mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q3.x, q3.y);
-          mma16816(sx, w8A & 0x00FF00FFu, w8B & 0x00FF00FFu, prmt(w8A, 0u, 0x4341), prmt(w8B, 0u, 0x4341), q4.x, q4.y);
-        } else {
-          uint32_t qa = qs_lane;
-#pragma unroll 1
-          for (int s = 0; s < kd.nsp2; ++s, qa += 512) {
-            const uint2 q0 = lds64<0>(qa), q1 = lds64<256>(qa);
-            const uint32_t wA = kfast ? lds16(k2a + 8 * s) : lds32_unaligned(k2a + 8 * s);
-            const uint32_t wB = kfast ? lds16(k2a + 8 * kd.sub2 + 8 * s) : lds32_unaligned(k2a + 8 * kd.sub2 + 8 * s);
-            const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);
+        for (int g16 = row_b; g16 < ge * 16; g16 += 16 * FW) {
+          // ── scores of rows g16+r (A) and g16+r+8 (B): independent MMA chains ──
+          float sx[4] = {0.f, 0.f, 0.f, 0.f}, sy[4] = {0.f, 0.f, 0.f, 0.f};
+          if (simple) {
+            const uint2 q0 = lds64<0>(qs_lane), q1 = lds64<256>(qs_lane), q2 = lds64<512>(qs_lane),
+                        q3 = lds64<768>(qs_lane), q4 = lds64<1024>(qs_lane);
+            const uint32_t yA = prmt(kw0, 0u, 0x4140), yB = prmt(kw1, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
             mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
             mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
-          }
+            const uint32_t vA = kw2 >> 8, vB = kw3 >> 8;
+            mma16816(sx, kw2 & 0x000F000Fu, kw3 & 0x000F000Fu, kw2 & 0x00F000F0u, kw3 & 0x00F000F0u, q2.x, q2.y);
+            mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q3.x, q3.y);
+            mma16816(sx, kw4 & 0x00FF00FFu, kw5 & 0x00FF00FFu, prmt(kw4, 0u, 0x4341), prmt(kw5, 0u, 0x4341), q4.x, q4.y);
+            // K words of this warp's next group (past the tile's end the words are unused; the
+            // addresses stay inside the CTA's shared memory: at most 80 rows x 16 bytes further)
+            k2a += 16 * FW * kd.sub2; k4a += 16 * FW * kd.sub4; k8a += 16 * FW * kd.n8;
+            kw0 = lds16(k2a); kw1 = lds16(k2a + 8 * kd.sub2);
+            kw2 = lds32(k4a); kw3 = lds32(k4a + 8 * kd.sub4);
+            kw4 = lds32(k8a); kw5 = lds32(k8a + 8 * kd.n8);
+          } else {
+            uint32_t qa = qs_lane;
 #pragma unroll 1
-          for (int s = 0; s < kd.nsp4; ++s, qa += 512) {
-            const uint2 q0 = lds64<0>(qa), q1 = lds64<256>(qa);
-            const uint32_t wA = kfast ? lds32(k4a + 16 * s) : lds32_unaligned(k4a + 16 * s);
-            const uint32_t wB = kfast ? lds32(k4a + 8 * kd.sub4 + 16 * s) : lds32_unaligned(k4a + 8 * kd.sub4 + 16 * s);
-            const uint32_t vA = wA >> 8, vB = wB >> 8;
-            mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, q0.x, q0.y);
-            mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q1.x, q1.y);
-          }
-#pragma unroll 1
-          for (int b = 0; b < kd.nkb8; ++b, qa += 256) {
-            const uint2 q0 = lds64<0>(qa);
-            const uint32_t wA = kfast ? lds32(k8a + 16 * b) : lds32_unaligned(k8a + 16 * b);
-            const uint32_t wB = kfast ? lds32(k8a + 8 * kd.n8 + 16 * b) : lds32_unaligned(k8a + 8 * kd.n8 + 16 * b);
-            mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, prmt(wA, 0u, 0x4341), prmt(wB, 0u, 0x4341), q0.x, q0.y);
-          }
-        }
-        // sx+sy: [0] (row A, head 2j) [1] (row A, head 2j+1) [2] (row B, head 2j) [3] (row B, head 2j+1)
-        const bool full = g16 + 16 <= t.n;
-        const bool rowA_ok = full || g16 + r < t.n, rowB_ok = full || g16 + r + 8 < t.n;
-        float s2[4];
-        s2[0] = fmaf(sx[0] + sy[0], c1, -b1e); s2[1] = fmaf(sx[1] + sy[1], c1, -b1o);
-        s2[2] = fmaf(sx[2] + sy[2], c1, -b1e); s2[3] = fmaf(sx[3] + sy[3], c1, -b1o);
-        if (has_mask) {
-          const int64_t ca = krow0 + g16 + r;
-          if (mask_e != nullptr) { if (rowA_ok) s2[0] += mask_e[ca] * LOG2E; if (rowB_ok) s2[2] += mask_e[ca + 8] * LOG2E; }
-          if (mask_o != nullptr) { if (rowA_ok) s2[1] += mask_o[ca] * LOG2E; if (rowB_ok) s2[3] += mask_o[ca + 8] * LOG2E; }
-        }
-        if (!full) {
-          if (!rowA_ok) { s2[0] = -INFINITY; s2[1] = -INFINITY; }
-          if (!rowB_ok) { s2[2] = -INFINITY; s2[3] = -INFINITY; }
-        }
-        // lazy reference maximum: exact maxima are only worked out when some score of the warp
-        // exceeds its head's reference by more than RESCALE_TH (always true for the first group)
-        const float te = m_e + RESCALE_TH, to = m_o + RESCALE_TH;
-        if (__any_sync(0xffffffffu, s2[0] > te || s2[2] > te || s2[1] > to || s2[3] > to)) {
-          float me = fmaxf(s2[0], s2[2]), mo = fmaxf(s2[1], s2[3]);
-#pragma unroll
-          for (int o = 4; o < 32; o <<= 1) {
-            me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
-            mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
-          }
-          const float ne = fmaxf(m_e, me), no = fmaxf(m_o, mo);
-          const float ae = (ne == -INFINITY) ? 1.f : ex2(m_e - ne), ao = (no == -INFINITY) ? 1.f : ex2(m_o - no);
-          l_e *= ae; zc_e *= ae; l_o *= ao; zc_o *= ao;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
-          m_e = ne; m_o = no;
-        }
-        const float mse = (m_e == -INFINITY) ? 0.f : m_e, mso = (m_o == -INFINITY) ? 0.f : m_o;
-        float pe[4];
-        pe[0] = ex2(s2[0] - mse); pe[1] = ex2(s2[1] - mso); pe[2] = ex2(s2[2] - mse); pe[3] = ex2(s2[3] - mso);
-        l_e += pe[0] + pe[2]; l_o += pe[1] + pe[3];
-        uint32_t hA, hB;                                   // (row A | row B) x (head 2j, head 2j+1) as fp16 pairs
-        if (p < 3) {
-          float scA = h2f((uint16_t)lds16(sca)), scB = h2f((uint16_t)lds16<16>(sca));
-          float zpA = h2f((uint16_t)lds16(zpa)), zpB = h2f((uint16_t)lds16<16>(zpa));
-          if (!rowA_ok) { scA = 0.f; zpA = 0.f; }          // dead rows may hold non-finite bytes
-          if (!rowB_ok) { scB = 0.f; zpB = 0.f; }
-          hA = pack_h2(pe[0] * scA, pe[1] * scA); hB = pack_h2(pe[2] * scB, pe[3] * scB);
-          const float2 fA = __half22float2(*reinterpret_cast<__half2*>(&hA));   // the values the tensor core sees
-          const float2 fB = __half22float2(*reinterpret_cast<__half2*>(&hB));
-          zc_e = fmaf(fA.x, zpA, zc_e); zc_o = fmaf(fA.y, zpA, zc_o);
-          zc_e = fmaf(fB.x, zpB, zc_e); zc_o = fmaf(fB.y, zpB, zc_o);
-        } else {
-          hA = pack_h2(pe[0], pe[1]); hB = pack_h2(pe[2], pe[3]);
-        }
-        // 8x8 transposes: thread (r, j) now holds head r at rows g16 + {2j, 2j+1} and g16 + 8 + {2j, 2j+1}
-        const uint32_t pb0 = movmatrix_trans(hA), pb1 = movmatrix_trans(hB);
-
-        // ── P.V: channels on M, rows on K; this thread supplies rows g16 + {2j,2j+1,8+2j,9+2j} ──
-        if (p == 2) {
-#pragma unroll
-          for (int vv = 0; vv < 4; ++vv) {
-            const uint32_t w0 = lds32(va + 32 * vv), w1 = lds32(va + 32 * vv + 128);
-            const uint32_t w2 = lds32(va + 32 * vv + 8 * 128), w3 = lds32(va + 32 * vv + 9 * 128);
-#pragma unroll
-            for (int qq = 0; qq < 2; ++qq) {
-              const uint32_t sel = qq ? 0x7632u : 0x5410u;
-              const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
-              mma16816(acc[4 * qq + vv], y01 & 0x00FF00FFu, prmt(y01, 0u, 0x4341), y23 & 0x00FF00FFu,
-                       prmt(y23, 0u, 0x4341), pb0, pb1);
+            for (int s = 0; s < kd.nsp2; ++s, qa += 512) {
+              const uint2 q0 = lds64<0>(qa), q1 = lds64<256>(qa);
+              const uint32_t wA = kfast ? lds16(k2a + 8 * s) : lds32_unaligned(k2a + 8 * s);
+              const uint32_t wB = kfast ? lds16(k2a + 8 * kd.sub2 + 8 * s) : lds32_unaligned(k2a + 8 * kd.sub2 + 8 * s);
+              const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);
+              mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
+              mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
             }
+#pragma unroll 1
+            for (int s = 0; s < kd.nsp4; ++s, qa += 512) {
+              const uint2 q0 = lds64<0>(qa), q1 = lds64<256>(qa);
+              const uint32_t wA = kfast ? lds32(k4a + 16 * s) : lds32_unaligned(k4a + 16 * s);
+              const uint32_t wB = kfast ? lds32(k4a + 8 * kd.sub4 + 16 * s) : lds32_unaligned(k4a + 8 * kd.sub4 + 16 * s);
+              const uint32_t vA = wA >> 8, vB = wB >> 8;
+              mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, q0.x, q0.y);
+              mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q1.x, q1.y);
+            }
+#pragma unroll 1
+            for (int b = 0; b < kd.nkb8; ++b, qa += 256) {
+              const uint2 q0 = lds64<0>(qa);
+              const uint32_t wA = kfast ? lds32(k8a + 16 * b) : lds32_unaligned(k8a + 16 * b);
+              const uint32_t wB = kfast ? lds32(k8a + 8 * kd.n8 + 16 * b) : lds32_unaligned(k8a + 8 * kd.n8 + 16 * b);
+              mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, prmt(wA, 0u, 0x4341), prmt(wB, 0u, 0x4341), q0.x, q0.y);
+            }
+            k2a += 16 * FW * kd.sub2; k4a += 16 * FW * kd.sub4; k8a += 16 * FW * kd.n8;
           }
-        } else if (p == 1) {
+          // requested now, needed after the softmax: V scale / zero point of rows A and B and
+          // the first V words of the group
+          uint32_t rsA = 0, rsB = 0, rzA = 0, rzB = 0;
+          if (P < 3) { rsA = lds16(sca); rsB = lds16<16>(sca); rzA = lds16(zpa); rzB = lds16<16>(zpa); }
+          uint32_t w0, w1, w2, w3, x0 = 0, x1 = 0, x2 = 0, x3 = 0;
+          if (P == 3) {
+            const uint2 a0 = lds64(va), a1 = lds64<256>(va), a2 = lds64<8 * 256>(va), a3 = lds64<9 * 256>(va);
+            w0 = a0.x; w1 = a1.x; w2 = a2.x; w3 = a3.x; x0 = a0.y; x1 = a1.y; x2 = a2.y; x3 = a3.y;
+          } else {
+            w0 = lds32(va); w1 = lds32<VRB>(va); w2 = lds32<8 * VRB>(va); w3 = lds32<9 * VRB>(va);
+          }
+
+          // sx+sy: [0] (row A, head 2j) [1] (row A, head 2j+1) [2] (row B, head 2j) [3] (row B, head 2j+1)
+          const bool full = g16 + 16 <= tn;
+          const bool rowA_ok = full || g16 + r < tn, rowB_ok = full || g16 + r + 8 < tn;
+          float s2[4];
+          s2[0] = fmaf(sx[0] + sy[0], c1, -b1e); s2[1] = fmaf(sx[1] + sy[1], c1, -b1o);
+          s2[2] = fmaf(sx[2] + sy[2], c1, -b1e); s2[3] = fmaf(sx[3] + sy[3], c1, -b1o);
+          if (has_mask) {
+            const int64_t ca = krow0 + g16 + r;
+            if (mask_e != nullptr) { if (rowA_ok) s2[0] += mask_e[ca] * LOG2E; if (rowB_ok) s2[2] += mask_e[ca + 8] * LOG2E; }
+            if (mask_o != nullptr) { if (rowA_ok) s2[1] += mask_o[ca] * LOG2E; if (rowB_ok) s2[3] += mask_o[ca + 8] * LOG2E; }
+          }
+          if (!full) {
+            if (!rowA_ok) { s2[0] = -INFINITY; s2[1] = -INFINITY; }
+            if (!rowB_ok) { s2[2] = -INFINITY; s2[3] = -INFINITY; }
+          }
+          // lazy reference maximum: exact maxima are only worked out when some score of the warp
+          // exceeds its head's reference by more than RESCALE_TH (always true for the first group)
+          const float te = m_e + RESCALE_TH, to = m_o + RESCALE_TH;
+          if (__any_sync(0xffffffffu, s2[0] > te || s2[2] > te || s2[1] > to || s2[3] > to)) {
+            float me = fmaxf(s2[0], s2[2]), mo = fmaxf(s2[1], s2[3]);
 #pragma unroll
-          for (int vl = 0; vl < 2; ++vl) {
-            const uint32_t w0 = lds32(va + 32 * vl), w1 = lds32(va + 32 * vl + 64);
-            const uint32_t w2 = lds32(va + 32 * vl + 8 * 64), w3 = lds32(va + 32 * vl + 9 * 64);
+            for (int o = 4; o < 32; o <<= 1) {
+              me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
+              mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
+            }
+            const float ne = fmaxf(m_e, me), no = fmaxf(m_o, mo);
+            const float ae = (ne == -INFINITY) ? 1.f : ex2(m_e - ne), ao = (no == -INFINITY) ? 1.f : ex2(m_o - no);
+            l_e *= ae; zc_e *= ae; l_o *= ao; zc_o *= ao;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
+            m_e = ne; m_o = no;
+          }
+          const float mse = (m_e == -INFINITY) ? 0.f : m_e, mso = (m_o == -INFINITY) ? 0.f : m_o;
+          float pe[4];
+          pe[0] = ex2(s2[0] - mse); pe[1] = ex2(s2[1] - mso); pe[2] = ex2(s2[2] - mse); pe[3] = ex2(s2[3] - mso);
+          l_e += pe[0] + pe[2]; l_o += pe[1] + pe[3];
+          uint32_t hA, hB;                                 // (row A | row B) x (head 2j, head 2j+1) as fp16 pairs
+          if (P < 3) {
+            float scA = h2f((uint16_t)rsA), scB = h2f((uint16_t)rsB);
+            float zpA = h2f((uint16_t)rzA), zpB = h2f((uint16_t)rzB);
+            if (!rowA_ok) { scA = 0.f; zpA = 0.f; }        // dead rows may hold non-finite bytes
+            if (!rowB_ok) { scB = 0.f; zpB = 0.f; }
+            hA = pack_h2(pe[0] * scA, pe[1] * scA); hB = pack_h2(pe[2] * scB, pe[3] * scB);
+            const float2 fA = __half22float2(*reinterpret_cast<__half2*>(&hA));   // the values the tensor core sees
+            const float2 fB = __half22float2(*reinterpret_cast<__half2*>(&hB));
+            zc_e = fmaf(fA.x, zpA, zc_e); zc_o = fmaf(fA.y, zpA, zc_o);
+            zc_e = fmaf(fB.x, zpB, zc_e); zc_o = fmaf(fB.y, zpB, zc_o);
+          } else {
+            hA = pack_h2(pe[0], pe[1]); hB = pack_h2(pe[2], pe[3]);
+          }
+          // 8x8 transposes: thread (r, j) now holds head r at rows g16 + {2j, 2j+1} and g16 + 8 + {2j, 2j+1}
+          const uint32_t pb0 = movmatrix_trans(hA), pb1 = movmatrix_trans(hB);
+
+          // ── P.V: channels on M, rows on K; this thread supplies rows g16 + {2j,2j+1,8+2j,9+2j}.
+          //    The words of part vv+1 are requested before part vv is worked on. ──
+          if (P == 2) {
+#pragma unroll
+            for (int vv = 0; vv < 4; ++vv) {
+              uint32_t n0 = 0, n1 = 0, n2 = 0, n3 = 0;
+              if (vv < 3) {
+                n0 = lds32(va + 32 * (vv + 1)); n1 = lds32(va + 32 * (vv + 1) + 128);
+                n2 = lds32(va + 32 * (vv + 1) + 8 * 128); n3 = lds32(va + 32 * (vv + 1) + 9 * 128);
+              }
+#pragma unroll
+              for (int qq = 0; qq < 2; ++qq) {
+                const uint32_t sel = qq ? 0x7632u : 0x5410u;
+                const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
+                mma16816(acc[4 * qq + vv], y01 & 0x00FF00FFu, prmt(y01, 0u, 0x4341), y23 & 0x00FF00FFu,
+                         prmt(y23, 0u, 0x4341), pb0, pb1);
+              }
+              w0 = n0; w1 = n1; w2 = n2; w3 = n3;
+            }
+          } else if (P == 1) {
+#pragma unroll
+            for (int vl = 0; vl < 2; ++vl) {
+              uint32_t n0 = 0, n1 = 0, n2 = 0, n3 = 0;
+              if (vl < 1) {
+                n0 = lds32(va + 32); n1 = lds32(va + 32 + 64); n2 = lds32(va + 32 + 8 * 64); n3 = lds32(va + 32 + 9 * 64);
+              }
+#pragma unroll
+              for (int qq = 0; qq < 2; ++qq) {
+                const uint32_t sel = qq ? 0x7632u : 0x5410u;
+                const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
+                const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
+                mma16816(acc[4 * qq + vl], y01 & 0x000F000Fu, z01 & 0x000F000Fu, y23 & 0x000F000Fu, z23 & 0x000F000Fu,
+                         pb0, pb1);
+                mma16816(acc[4 * qq + vl + 2], y01 & 0x00F000F0u, z01 & 0x00F000F0u, y23 & 0x00F000F0u,
+                         z23 & 0x00F000F0u, pb0, pb1);
+              }
+              w0 = n0; w1 = n1; w2 = n2; w3 = n3;
+            }
+          } else if (P == 0) {
 #pragma unroll
             for (int qq = 0; qq < 2; ++qq) {
               const uint32_t sel = qq ? 0x7632u : 0x5410u;
               const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
               const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
-              mma16816(acc[4 * qq + vl], y01 & 0x000F000Fu, z01 & 0x000F000Fu, y23 & 0x000F000Fu, z23 & 0x000F000Fu,
-                       pb0, pb1);
-              mma16816(acc[4 * qq + vl + 2], y01 & 0x00F000F0u, z01 & 0x00F000F0u, y23 & 0x00F000F0u,
-                       z23 & 0x00F000F0u, pb0, pb1);
-            }
-          }
-        } else if (p == 0) {
-          const uint32_t w0 = lds32(va), w1 = lds32(va + 32), w2 = lds32(va + 8 * 32), w3 = lds32(va + 9 * 32);
 #pragma unroll
-          for (int qq = 0; qq < 2; ++qq) {
-            const uint32_t sel = qq ? 0x7632u : 0x5410u;
-            const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
-            const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
+              for (int vv = 0; vv < 4; ++vv) {
+                const uint32_t mk = 0x00030003u << (2 * vv);
+                mma16816(acc[4 * qq + vv], y01 & mk, z01 & mk, y23 & mk, z23 & mk, pb0, pb1);
+              }
+            }
+          } else {                                         // fp16 rows: channel c at byte 2c
 #pragma unroll
             for (int vv = 0; vv < 4; ++vv) {
-              const uint32_t mk = 0x00030003u << (2 * vv);
-              mma16816(acc[4 * qq + vv], y01 & mk, z01 & mk, y23 & mk, z23 & mk, pb0, pb1);
+              uint2 a0 = make_uint2(0u, 0u), a1 = a0, a2 = a0, a3 = a0;
+              if (vv < 3) {
+                a0 = lds64(va + 64 * (vv + 1)); a1 = lds64(va + 64 * (vv + 1) + 256);
+                a2 = lds64(va + 64 * (vv + 1) + 8 * 256); a3 = lds64(va + 64 * (vv + 1) + 9 * 256);
+              }
+              mma16816(acc[vv], prmt(w0, w1, 0x5410), prmt(w0, w1, 0x7632), prmt(w2, w3, 0x5410),
+                       prmt(w2, w3, 0x7632), pb0, pb1);
+              mma16816(acc[4 + vv], prmt(x0, x1, 0x5410), prmt(x0, x1, 0x7632), prmt(x2, x3, 0x5410),
+                       prmt(x2, x3, 0x7632), pb0, pb1);
+              w0 = a0.x; w1 = a1.x; w2 = a2.x; w3 = a3.x; x0 = a0.y; x1 = a1.y; x2 = a2.y; x3 = a3.y;
             }
           }
-        } else {                                           // fp16 rows: channel c at byte 2c
-#pragma unroll
-          for (int vv = 0; vv < 4; ++vv) {
-            const uint2 w0 = lds64(va + 64 * vv), w1 = lds64(va + 64 * vv + 256);
-            const uint2 w2 = lds64(va + 64 * vv + 8 * 256), w3 = lds64(va + 64 * vv + 9 * 256);
-            mma16816(acc[vv], prmt(w0.x, w1.x, 0x5410), prmt(w0.x, w1.x, 0x7632), prmt(w2.x, w3.x, 0x5410),
-                     prmt(w2.x, w3.x, 0x7632), pb0, pb1);
-            mma16816(acc[4 + vv], prmt(w0.y, w1.y, 0x5410), prmt(w0.y, w1.y, 0x7632), prmt(w2.y, w3.y, 0x5410),
-                     prmt(w2.y, w3.y, 0x7632), pb0, pb1);
-          }
+          sca += 32 * FW; zpa += 32 * FW;
+          va += 16 * FW * VRB;
         }
-        k2a += 16 * FW * kd.sub2; k4a += 16 * FW * kd.sub4; k8a += 16 * FW * kd.n8; sca += 32 * FW; zpa += 32 * FW;
-        va += 16 * FW * vrb;
-      }
+      };
+      if (p == 0) run_tile(std::integral_constant<int, 0>{});
+      else if (p == 1) run_tile(std::integral_constant<int, 1>{});
+      else if (p == 2) run_tile(std::integral_constant<int, 2>{});
+      else run_tile(std::integral_constant<int, 3>{});
     }
     if (it + FSTAGES < total_tiles) bar_arrive(BAR_FREE + stage, CTA_THREADS);   // slot may be refilled
   }

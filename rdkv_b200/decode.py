@@ -114,15 +114,28 @@ def lse_combine(partials: Tensor, out: Optional[Tensor] = None, *, out_ml: Optio
     return out
 
 
-def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out: Optional[Tensor]) -> None:
+def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out: Optional[Tensor],
+                  v0: int = 0, v1: Optional[int] = None) -> None:
+    """Launch the fused kernel on views [v0, v1) of the table (all of them by default);
+    q, partials and out are the full-table tensors, the range is cut by pointer offsets."""
     require_cuda(q, "q")
     if q.shape[-1] != HEAD_DIM or q.numel() != table.n_views * table.H_q * HEAD_DIM:
         raise ValueError(f"q must be [{table.n_views},{table.H_q},{HEAD_DIM}], got {tuple(q.shape)}")
     if not q.is_contiguous():
         q = q.contiguous()
-    check(lib().rdkv_decode_attn_partial(ptr(table.views), table.n_views, ptr(q), q_dtype_tag(q), table.H_q,
+    v1 = table.n_views if v1 is None else v1
+    if not 0 <= v0 <= v1 <= table.n_views:
+        raise ValueError(f"view range [{v0},{v1}) outside the table of {table.n_views} views")
+    rows = v0 * table.H_q                                  # first query-head row of the range
+
+    def off(t: Optional[Tensor], per_row: int) -> Optional[int]:
+        return None if t is None else t.data_ptr() + rows * per_row * t.element_size()
+
+    check(lib().rdkv_decode_attn_partial(table.views.data_ptr() + v0 * C.sizeof(LayerView), v1 - v0,
+                                         off(q, HEAD_DIM), q_dtype_tag(q), table.H_q,
                                          table.H_kv, table.chunk_rows, table.n_chunks, table.k_row_bytes_max,
-                                         ptr(partials), ptr(out), ptr(table.status), stream_ptr(q.device)),
+                                         off(partials, table.n_chunks * PARTIAL_STRIDE), off(out, HEAD_DIM),
+                                         ptr(table.status), stream_ptr(q.device)),
           "rdkv_decode_attn_partial")
 
 
@@ -169,6 +182,57 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
         _launch_fused(q, table, part, None)
         lse_combine(part, out.view(-1, HEAD_DIM))
     return out
+
+
+class _HostIO:
+    """Device staging buffers and streams of the host-buffer call, kept on the table."""
+
+    def __init__(self, table: DecodeTable, q_dtype: torch.dtype, n_slices: int):
+        dev = table.device
+        self.q = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=q_dtype, device=dev)
+        self.out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=dev)
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(n_slices)]
+        step = -(-table.n_views // n_slices)
+        self.ranges = [(a, min(a + step, table.n_views)) for a in range(0, table.n_views, step)]
+
+
+def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: Tensor, *, slices: int = 4) -> Tensor:
+    """Host-buffer form of :func:`packed_decode_attention`: ``q_host`` [n_views,H_q,128]
+    (fp16/bf16/fp32) and ``out_host`` [n_views,H_q,128] fp32 live in (pinned) host memory.
+
+    The views are cut into ``slices`` ranges; every range uploads its queries, runs the
+    kernel and downloads its results on a stream of its own, so the copies of one range
+    overlap the kernel of another.  Returns after the results have arrived in ``out_host``.
+    Pageable host tensors work too but serialise the copies.
+    """
+    if q_host.is_cuda or out_host.is_cuda:
+        raise ValueError("packed_decode_attention_host takes host tensors; use packed_decode_attention on the device")
+    if tuple(q_host.shape) != (table.n_views, table.H_q, HEAD_DIM) or not q_host.is_contiguous():
+        raise ValueError(f"q_host must be contiguous [{table.n_views},{table.H_q},{HEAD_DIM}]")
+    if tuple(out_host.shape) != tuple(q_host.shape) or out_host.dtype != torch.float32 or not out_host.is_contiguous():
+        raise ValueError("out_host must be contiguous float32 with q_host's shape")
+    q_dtype_tag(q_host)
+    n_slices = max(1, min(int(slices), table.n_views))
+    io: Optional[_HostIO] = getattr(table, "_host_io", None)
+    if io is None or io.q.dtype != q_host.dtype or len(io.streams) != n_slices:
+        io = _HostIO(table, q_host.dtype, n_slices)
+        table._host_io = io
+    cur = torch.cuda.current_stream(table.device)
+    part = table.workspace()
+    for (a, b), st in zip(io.ranges, io.streams):
+        st.wait_stream(cur)
+        with torch.cuda.stream(st):
+            io.q[a:b].copy_(q_host[a:b], non_blocking=True)
+            if part is None:
+                _launch_fused(io.q, table, None, io.out, a, b)
+            else:
+                _launch_fused(io.q, table, part, None, a, b)
+                lse_combine(part[a * table.H_q:b * table.H_q], io.out.view(-1, HEAD_DIM)[a * table.H_q:b * table.H_q])
+            out_host[a:b].copy_(io.out[a:b], non_blocking=True)
+    for st in io.streams[:len(io.ranges)]:
+        cur.wait_stream(st)
+    cur.synchronize()
+    return out_host
 
 
 def packed_layer_attention(q: Tensor, packed_layer: PackedKVLayer, new_v_only: Optional[Tensor] = None,

@@ -108,6 +108,39 @@ def test_fused_batch_of_views_and_partials():
     assert_attn_close(to_np(again).reshape(len(shapes), H_kv * g, 128)[0], wants[0][0], "combine identity")
 
 
+def test_host_buffer_call_equals_device_call():
+    """The host-buffer form (view ranges on separate streams, copies overlapped with the
+    kernels) returns bit-for-bit what the device call returns, for one-chunk tables and
+    for split-sequence tables, whatever the number of ranges."""
+    from rdkv_b200 import synth
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention, packed_decode_attention_host
+    from rdkv_b200.packing import pack_kv
+    H_kv, g = 4, 4
+    layers, nvs = [], []
+    for i in range(7):
+        seed = synth.unit_seed(5, i, 1)
+        T, N = 1536 + 64 * i, 640 + 32 * i
+        K, V = synth.make_kv(H_kv, T, seed=seed)
+        pl, nv = pack_kv(K.cuda(), V.cuda(), synth.make_v_bits(H_kv, T, N, seed=seed).cuda(),
+                         synth.make_k_bits(H_kv, seed=seed).cuda(), g)
+        layers.append(pl)
+        nvs.append(nv)
+    q = synth.make_q(H_kv * g, seed=2, batch=7, dtype=torch.bfloat16)
+    for n_chunks in (1, 3):                                # one chunk per head (direct write) / split sequence
+        table = DecodeTable(layers, nvs, H_kv * g)
+        table.n_chunks, table.chunk_rows = n_chunks, 64 * (-(-table.max_t_k // (64 * n_chunks)))
+        want = packed_decode_attention(q.cuda(), table).cpu()
+        q_host = q.pin_memory()
+        for slices in (1, 3, 7, 50):
+            out_host = torch.full((7, H_kv * g, 128), float("nan")).pin_memory()
+            got = packed_decode_attention_host(q_host, table, out_host, slices=slices)
+            assert got is out_host
+            assert torch.equal(out_host, want), (n_chunks, slices)
+        table.check_status()
+    with pytest.raises(ValueError):
+        packed_decode_attention_host(q.cuda(), table, out_host)
+
+
 def test_lse_combine_matches_oracle():
     from oracle import ref_attention as RA
     from rdkv_b200.decode import lse_combine
