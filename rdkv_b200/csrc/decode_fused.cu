@@ -94,6 +94,17 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Adds `bytes` to the transaction count the current phase waits for (no arrival).
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16) whose
+// completion is counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_on_copies(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -224,12 +235,16 @@ struct CtaGeom {
 
 struct TileDesc { int phase, row0, n; };   // row0: offset from lo[phase]
 
-// What the staging warp tells the compute warps about the tile in a ring slot.
-struct TileInfo {
+// What the staging warp tells the compute warps about the tile in a ring slot (16 bytes).
+struct __align__(16) TileInfo {
   int phase, n;
-  uint32_t off_k2, off_k4, off_k8, off_v, off_m, off_z;   // byte offsets of row 0 inside each stage area
-  int64_t krow0;                                           // stripe row of row 0 (mask column)
+  uint32_t offs;                       // six nibbles: byte offset (0..15) of row 0 inside the k2, k4, k8, v, scale, zp areas
+  int krow0;                           // stripe row of row 0 (mask column)
 };
+// One byte range of a tile as the staging warp plans it (16 bytes), and a planned tile.
+struct __align__(16) RangePlan { const unsigned char* src; int len; uint32_t dst_off; };
+struct __align__(16) TilePlan { RangePlan rg[6]; TileInfo info; };
+constexpr int PLAN_TILES = 32;         // tiles planned per round (one per staging lane)
 
 __device__ __forceinline__ TileDesc tile_of(const CtaGeom& G, int idx) {
   TileDesc t;
@@ -308,6 +323,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   __shared__ float s_bias[GH];
   __shared__ float s_ml[FW][GH][3];               // per warp: m, l, zero-point term
   __shared__ TileInfo s_tile[FSTAGES];
+  __shared__ TilePlan s_plan[PLAN_TILES];          // private to the staging warp
   __shared__ __align__(8) uint64_t s_full[FSTAGES];   // tile in slot s has landed
 
   const int chunk = blockIdx.x, view_idx = blockIdx.z;
@@ -336,56 +352,140 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   const int d_pad = kd.n2p + kd.n4p + kd.n8;
   const StageLayout SL = stage_layout(kd.sub2, kd.sub4, kd.n8);
 
-  // ── geometry: live rows of this head are [0,n2) 2-bit, [n2,n2+n4) 4-bit, [..,t_v) 8-bit,
-  //    [t_v, t_v+n16) fp16; the chunk takes [chunk*chunk_rows, +chunk_rows) of them ──
-  if (tid == 0) {
+  // named barrier ids: FREE[s] = 1 + s (slot s may be refilled); COMPUTE: the compute warps among
+  // themselves; GEOM: the staging warp has published the CTA's geometry
+  constexpr int BAR_FREE = 1, BAR_COMPUTE = 1 + FSTAGES, BAR_GEOM = 2 + FSTAGES;
+  const uint32_t smem0 = smem_u32(smem_raw);
+  const uint32_t qs_base = smem0 + FSTAGES * stage_bytes;  // uint2 qsA[nkb][32]
+  uint2* qsA = reinterpret_cast<uint2*>(smem_raw + (size_t)FSTAGES * stage_bytes);
+  const bool fits = SL.total <= stage_bytes && d_pad > 0 && kd.nkb <= KB_MAX;   // view fits this launch
+
+  // ── geometry (staging warp, one lane per phase): live rows of this head are [0,n2) 2-bit,
+  //    [n2,n2+n4) 4-bit, [..,t_v) 8-bit, [t_v, t_v+n16) fp16; the chunk takes
+  //    [chunk*chunk_rows, +chunk_rows) of them.  The compute warps fold the queries meanwhile. ──
+  if (warp == FW) {
     const HeadCounts hc = head_counts(v, h);
+    const int p = lane & 3;
     const int c0 = chunk * chunk_rows, c1 = c0 + chunk_rows;
-    const int b[5] = {0, hc.n2, hc.n2 + hc.n4, hc.t_v, hc.t_v + hc.n16};
-    int tiles = 0;
-    bool fast = true;
+    const int b_lo = p == 0 ? 0 : p == 1 ? hc.n2 : p == 2 ? hc.n2 + hc.n4 : hc.t_v;
+    const int b_hi = p == 0 ? hc.n2 : p == 1 ? hc.n2 + hc.n4 : p == 2 ? hc.t_v : hc.t_v + hc.n16;
+    const int lo = max(b_lo, c0);
+    const int hi = max(lo, min(b_hi, c1));
+    const int n = hi - lo;
+    const int ntile = (n + phase_tile_rows(p) - 1) / phase_tile_rows(p);
+    const int64_t krow = p < 3 ? lo : (int64_t)v.max_t_v + (lo - hc.t_v);   // stripe row
     const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
     const unsigned char* scb = reinterpret_cast<const unsigned char*>(v.v_scale);
     const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
-    for (int p = 0; p < 4; ++p) {
-      int lo = max(b[p], c0), hi = min(b[p + 1], c1);
-      if (hi < lo) hi = lo;
-      G.lo[p] = lo; G.hi[p] = hi;
-      G.first_tile[p] = tiles;
-      tiles += (hi - lo + phase_tile_rows(p) - 1) / phase_tile_rows(p);
-      const int64_t krow = p < 3 ? lo : (int64_t)v.max_t_v + (lo - hc.t_v);   // stripe row
-      const int n = hi - lo;
-      G.krow[p] = krow;
-      G.k2[p] = kd.sub2 ? v.k2 + h * v.k2_head_stride + krow * kd.sub2 : nullptr;
-      G.k4[p] = kd.sub4 ? v.k4 + h * v.k4_head_stride + krow * kd.sub4 : nullptr;
-      G.k8[p] = kd.n8 ? v.k8 + h * v.k8_head_stride + krow * kd.n8 : nullptr;
-      const unsigned char* vb; const unsigned char* vlo; int64_t vext;
-      if (p == 0) { vlo = v.v2; vext = v.v2_bytes; vb = v.v2 + h * v.v2_head_stride + (int64_t)lo * 32; }
-      else if (p == 1) { vlo = v.v4; vext = v.v4_bytes; vb = v.v4 + h * v.v4_head_stride + (int64_t)(lo - hc.n2) * 64; }
-      else if (p == 2) { vlo = v.v8; vext = v.v8_bytes; vb = v.v8 + h * v.v8_head_stride + (int64_t)(lo - hc.n2 - hc.n4) * 128; }
-      else { vlo = v16b; vext = v.v16_bytes; vb = v16b + (h * v.v16_head_stride + (int64_t)(lo - hc.t_v) * 128) * 2; }
-      G.vrow[p] = vb;
-      if (n > 0) {
-        if (kd.sub2) fast = fast && blocks_inside(G.k2[p], G.k2[p] + (int64_t)n * kd.sub2, v.k2, v.k2 + v.k2_bytes);
-        if (kd.sub4) fast = fast && blocks_inside(G.k4[p], G.k4[p] + (int64_t)n * kd.sub4, v.k4, v.k4 + v.k4_bytes);
-        if (kd.n8) fast = fast && blocks_inside(G.k8[p], G.k8[p] + (int64_t)n * kd.n8, v.k8, v.k8 + v.k8_bytes);
-        fast = fast && blocks_inside(vb, vb + (int64_t)n * phase_row_bytes(p), vlo, vlo + vext);
-      }
+    const unsigned char* gk2 = kd.sub2 ? v.k2 + h * v.k2_head_stride + krow * kd.sub2 : nullptr;
+    const unsigned char* gk4 = kd.sub4 ? v.k4 + h * v.k4_head_stride + krow * kd.sub4 : nullptr;
+    const unsigned char* gk8 = kd.n8 ? v.k8 + h * v.k8_head_stride + krow * kd.n8 : nullptr;
+    const unsigned char* vlo = p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : v16b;
+    const int64_t vext = p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes;
+    const int64_t vhs = p == 0 ? v.v2_head_stride : p == 1 ? v.v4_head_stride : p == 2 ? v.v8_head_stride
+                                                                                     : 2 * v.v16_head_stride;
+    const unsigned char* vb = vlo + h * vhs + (int64_t)(lo - b_lo) * phase_row_bytes(p);
+    const unsigned char* gsc = scb + (h * v.v_meta_head_stride + lo) * 2;
+    const unsigned char* gzp = zpb + (h * v.v_meta_head_stride + lo) * 2;
+    bool fast = true;
+    if (n > 0) {
+      if (kd.sub2) fast = fast && blocks_inside(gk2, gk2 + (int64_t)n * kd.sub2, v.k2, v.k2 + v.k2_bytes);
+      if (kd.sub4) fast = fast && blocks_inside(gk4, gk4 + (int64_t)n * kd.sub4, v.k4, v.k4 + v.k4_bytes);
+      if (kd.n8) fast = fast && blocks_inside(gk8, gk8 + (int64_t)n * kd.n8, v.k8, v.k8 + v.k8_bytes);
+      fast = fast && blocks_inside(vb, vb + (int64_t)n * phase_row_bytes(p), vlo, vlo + vext);
       if (p < 3) {
-        G.sc[p] = scb + (h * v.v_meta_head_stride + lo) * 2;
-        G.zp[p] = zpb + (h * v.v_meta_head_stride + lo) * 2;
-        if (n > 0) {
-          fast = fast && blocks_inside(G.sc[p], G.sc[p] + n * 2, scb, scb + v.v_meta_bytes);
-          fast = fast && blocks_inside(G.zp[p], G.zp[p] + n * 2, zpb, zpb + v.v_meta_bytes);
-        }
+        fast = fast && blocks_inside(gsc, gsc + n * 2, scb, scb + v.v_meta_bytes);
+        fast = fast && blocks_inside(gzp, gzp + n * 2, zpb, zpb + v.v_meta_bytes);
       }
     }
-    G.first_tile[4] = tiles;
-    G.fast = fast ? 1 : 0;
-    if (SL.total > stage_bytes || d_pad <= 0 || kd.nkb > KB_MAX || (hc.n16 > 0 && v.v16 == nullptr))
-      G.first_tile[4] = -1;                                // view does not fit this launch
+    fast = __all_sync(0xffffffffu, fast);                  // lanes 4.. repeat lanes 0..3
+    const int t0 = __shfl_sync(0xffffffffu, ntile, 0), t1 = __shfl_sync(0xffffffffu, ntile, 1);
+    const int t2 = __shfl_sync(0xffffffffu, ntile, 2), t3 = __shfl_sync(0xffffffffu, ntile, 3);
+    if (lane < 4) {
+      G.lo[p] = lo; G.hi[p] = hi;
+      G.first_tile[p] = p == 0 ? 0 : p == 1 ? t0 : p == 2 ? t0 + t1 : t0 + t1 + t2;
+      G.krow[p] = krow;
+      G.k2[p] = gk2; G.k4[p] = gk4; G.k8[p] = gk8; G.vrow[p] = vb;
+      if (p < 3) { G.sc[p] = gsc; G.zp[p] = gzp; }
+    }
+    if (lane == 0) {
+      G.fast = fast ? 1 : 0;
+      G.first_tile[4] = (!fits || (hc.n16 > 0 && v.v16 == nullptr)) ? -1 : t0 + t1 + t2 + t3;
+    }
+    __threadfence_block();
+    __syncwarp();
+    bar_arrive(BAR_GEOM, CTA_THREADS);
   }
-  __syncthreads();
+
+  // ── q*scale in MMA fragment order and the zero-point bias (compute warps, while the staging
+  //    warp works out the geometry and starts the first copies).  All loads of a round are
+  //    issued before any is used: slot -> permuted channel -> query element is a chain of two
+  //    global round trips, paid once per round of two 16-channel blocks. ──
+  if (warp < FW && fits) {
+    const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
+    const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
+    const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
+    const bool head_ok = r < gcnt;
+    const int64_t qoff = ((int64_t)view_idx * H_q + hq0 + (head_ok ? r : 0)) * D;
+    float bias_part = 0.f;                                 // thread (r = head, j) sums its own slots
+    auto fold = [&](auto loadq) {
+#pragma unroll 1
+      for (int kb0 = warp; kb0 < kd.nkb; kb0 += 2 * FW) {
+        int slot[2][4];
+        float f[2][4], scv[2][4], zpv[2][4], qv[2][4];
+        int64_t pm[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int kb = kb0 + u * FW;
+            slot[u][e] = kb < kd.nkb ? k_slot(kd, kb, j, e, &f[u][e]) : -1;
+            if (slot[u][e] < 0) f[u][e] = 1.f;
+          }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int sl = max(slot[u][e], 0);
+            pm[u][e] = perm[sl]; scv[u][e] = h2f(sc[sl]); zpv[u][e] = h2f(zp[sl]);
+          }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) qv[u][e] = loadq(qoff + pm[u][e]);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int kb = kb0 + u * FW;
+          float val[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float x = 0.f;
+            if (slot[u][e] >= 0 && head_ok) {
+              x = __half2float(__float2half_rn(qv[u][e] * scv[u][e] / f[u][e]));
+              bias_part += zpv[u][e] * (x * f[u][e]);
+            }
+            val[e] = x;
+          }
+          if (kb < kd.nkb) qsA[kb * 32 + lane] = make_uint2(pack_h2(val[0], val[1]), pack_h2(val[2], val[3]));
+        }
+      }
+    };
+    if (q_dtype == RDKV_BF16) fold([&](int64_t i) { return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(q)[i]); });
+    else if (q_dtype == RDKV_F16) fold([&](int64_t i) { return __half2float(reinterpret_cast<const __half*>(q)[i]); });
+    else fold([&](int64_t i) { return reinterpret_cast<const float*>(q)[i]; });
+    bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
+    bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
+    if (j == 0) s_ml[warp][r][0] = bias_part;
+    bar_sync(BAR_COMPUTE, FW * 32);
+    if (tid < GH) {
+      float b = 0.f;
+#pragma unroll
+      for (int w = 0; w < FW; ++w) b += s_ml[w][tid][0];
+      s_bias[tid] = b;
+    }
+    bar_sync(BAR_COMPUTE, FW * 32);
+  }
+  if (warp < FW) bar_sync(BAR_GEOM, CTA_THREADS);          // geometry published
   const int total_tiles = G.first_tile[4];
 
   if (total_tiles <= 0) {                                  // nothing live here: empty records
@@ -401,120 +501,93 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     return;
   }
 
-  const uint32_t smem0 = smem_u32(smem_raw);
-  const uint32_t qs_base = smem0 + FSTAGES * stage_bytes;  // uint2 qsA[nkb][32]
-  uint2* qsA = reinterpret_cast<uint2*>(smem_raw + (size_t)FSTAGES * stage_bytes);
-
-  // Stage tile `tile_idx` into ring slot `stage`: the 32 lanes of the staging warp issue the copies
-  // (one cp.async group per tile) and lane 0 leaves the tile's description for the compute warps.
-  auto issue_tile = [&](int tile_idx, int stage) {
-    const TileDesc t = tile_of(G, tile_idx);
-    unsigned char* sb = smem_raw + (size_t)stage * stage_bytes;
-    const int p = t.phase;
-    const unsigned char* a_k2 = G.k2[p] + (int64_t)t.row0 * kd.sub2;
-    const unsigned char* a_k4 = G.k4[p] + (int64_t)t.row0 * kd.sub4;
-    const unsigned char* a_k8 = G.k8[p] + (int64_t)t.row0 * kd.n8;
-    const unsigned char* a_v = G.vrow[p] + (int64_t)t.row0 * phase_row_bytes(p);
-    if (G.fast) {
-      const uint32_t sbu = smem0 + stage * stage_bytes;
-      stage_range<0, 32>(sbu + SL.v, a_v, t.n * phase_row_bytes(p), lane);
-      if (kd.sub2) stage_range<0, 32>(sbu + SL.k2, a_k2, t.n * kd.sub2, lane);
-      if (kd.sub4) stage_range<0, 32>(sbu + SL.k4, a_k4, t.n * kd.sub4, lane);
-      if (kd.n8) stage_range<0, 32>(sbu + SL.k8, a_k8, t.n * kd.n8, lane);
-      if (p < 3) {
-        stage_range<0, 32>(sbu + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, lane);
-        stage_range<0, 32>(sbu + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, lane);
-      }
-    } else {
-      const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
-      const unsigned char* scb = reinterpret_cast<const unsigned char*>(v.v_scale);
-      const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
-      const unsigned char* vlo = p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : v16b;
-      const int64_t vext = p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes;
-      stage_range_guarded(sb + SL.v, a_v, t.n * phase_row_bytes(p), vlo, vlo + vext, lane, 32);
-      if (kd.sub2) stage_range_guarded(sb + SL.k2, a_k2, t.n * kd.sub2, v.k2, v.k2 + v.k2_bytes, lane, 32);
-      if (kd.sub4) stage_range_guarded(sb + SL.k4, a_k4, t.n * kd.sub4, v.k4, v.k4 + v.k4_bytes, lane, 32);
-      if (kd.n8) stage_range_guarded(sb + SL.k8, a_k8, t.n * kd.n8, v.k8, v.k8 + v.k8_bytes, lane, 32);
-      if (p < 3) {
-        stage_range_guarded(sb + SL.sc, G.sc[p] + t.row0 * 2, t.n * 2, scb, scb + v.v_meta_bytes, lane, 32);
-        stage_range_guarded(sb + SL.zp, G.zp[p] + t.row0 * 2, t.n * 2, zpb, zpb + v.v_meta_bytes, lane, 32);
-      }
-    }
-    // rows past the tile's end must hold finite fp16 data in the fp16 phase: clear the
-    // rest of the last 16-row group beyond the copied blocks
-    if (p == 3 && (t.n & 15)) {
-      const int off = (int)(reinterpret_cast<uintptr_t>(a_v) & 15);
-      const int first = (off + t.n * 256 + 15) & ~15;
-      const int last = off + ((t.n + 15) & ~15) * 256;
-      for (int i = first + 4 * lane; i < last; i += 4 * 32) *reinterpret_cast<uint32_t*>(sb + SL.v + i) = 0u;
-    }
-    if (lane == 0) {
-      TileInfo& ti = s_tile[stage];
-      ti.phase = p; ti.n = t.n;
-      ti.off_k2 = (uint32_t)reinterpret_cast<uintptr_t>(a_k2) & 15u;
-      ti.off_k4 = (uint32_t)reinterpret_cast<uintptr_t>(a_k4) & 15u;
-      ti.off_k8 = (uint32_t)reinterpret_cast<uintptr_t>(a_k8) & 15u;
-      ti.off_v = (uint32_t)reinterpret_cast<uintptr_t>(a_v) & 15u;
-      ti.off_m = p < 3 ? ((uint32_t)reinterpret_cast<uintptr_t>(G.sc[p]) + 2u * t.row0) & 15u : 0u;
-      ti.off_z = p < 3 ? ((uint32_t)reinterpret_cast<uintptr_t>(G.zp[p]) + 2u * t.row0) & 15u : 0u;
-      ti.krow0 = G.krow[p] + t.row0;
-    }
-  };
-
-  // named barrier ids: FREE[s] = 1 + s (slot s may be refilled), 1 + FSTAGES: the compute warps among themselves
-  constexpr int BAR_FREE = 1, BAR_COMPUTE = 1 + FSTAGES;
-
   if (warp == FW) {
     // ── staging warp ──────────────────────────────────────────────────────────
-    // It only ever waits for a free slot; a tile's landing is signalled to the compute warps
-    // by the copies themselves (mbarrier arrival on completion), so issuing the next tile
-    // overlaps the flight of the previous one.
+    // Tiles are planned 32 at a time, one per lane (where each of a tile's six byte ranges
+    // starts, how long it is, where it goes), so that the per-tile work is a table look-up and
+    // the copy instructions.  The warp only ever waits for a free slot; a tile's landing is
+    // signalled to the compute warps by the copies themselves (mbarrier transaction bytes on
+    // the bulk-copy path, arrival on completion of the cp.async copies otherwise).
+    const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
+    const unsigned char* scb = reinterpret_cast<const unsigned char*>(v.v_scale);
+    const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
+    const bool fast = G.fast != 0;
 #pragma unroll 1
     for (int it = 0; it < total_tiles; ++it) {
+      const int slot = it % PLAN_TILES;
+      if (slot == 0) {                                     // plan tiles [it, it + 32)
+        __syncwarp();
+        if (it + lane < total_tiles) {
+          const TileDesc t = tile_of(G, it + lane);
+          const int p = t.phase;
+          TilePlan& P = s_plan[lane];
+          const unsigned char* a_k2 = G.k2[p] + (int64_t)t.row0 * kd.sub2;
+          const unsigned char* a_k4 = G.k4[p] + (int64_t)t.row0 * kd.sub4;
+          const unsigned char* a_k8 = G.k8[p] + (int64_t)t.row0 * kd.n8;
+          const unsigned char* a_v = G.vrow[p] + (int64_t)t.row0 * phase_row_bytes(p);
+          const unsigned char* a_sc = G.sc[p < 3 ? p : 0] + t.row0 * 2;
+          const unsigned char* a_zp = G.zp[p < 3 ? p : 0] + t.row0 * 2;
+          P.rg[0] = RangePlan{a_v, t.n * phase_row_bytes(p), (uint32_t)SL.v};
+          P.rg[1] = RangePlan{a_k2, t.n * kd.sub2, (uint32_t)SL.k2};
+          P.rg[2] = RangePlan{a_k4, t.n * kd.sub4, (uint32_t)SL.k4};
+          P.rg[3] = RangePlan{a_k8, t.n * kd.n8, (uint32_t)SL.k8};
+          P.rg[4] = RangePlan{a_sc, p < 3 ? t.n * 2 : 0, (uint32_t)SL.sc};
+          P.rg[5] = RangePlan{a_zp, p < 3 ? t.n * 2 : 0, (uint32_t)SL.zp};
+          auto low4 = [](const unsigned char* x) { return (uint32_t)reinterpret_cast<uintptr_t>(x) & 15u; };
+          P.info.phase = p; P.info.n = t.n;
+          P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 | low4(a_v) << 12 |
+                        (p < 3 ? low4(a_sc) << 16 | low4(a_zp) << 20 : 0u);
+          P.info.krow0 = (int)(G.krow[p] + t.row0);
+        }
+        __syncwarp();
+      }
+      // this tile's plan: lanes 0..5 take one range each (before the wait for the slot)
       const int stage = it % FSTAGES;
+      RangePlan rp = s_plan[slot].rg[lane < 6 ? lane : 0];
+      if (lane >= 6) rp.len = 0;
+      const TileInfo ti = s_plan[slot].info;
+      const uintptr_t a = reinterpret_cast<uintptr_t>(rp.src), a0 = a & ~(uintptr_t)15;
+      const uint32_t bytes = rp.len > 0 ? (uint32_t)(((a + rp.len + 15) & ~(uintptr_t)15) - a0) : 0u;   // covering 16-byte blocks
+      uint32_t total = bytes;
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+      const uint32_t sbu = smem0 + stage * stage_bytes;
+
       if (it >= FSTAGES) bar_sync(BAR_FREE + stage, CTA_THREADS);          // compute warps left the slot
-      issue_tile(it, stage);
-      mbar_arrive_on_copies(&s_full[stage]);                               // fires when this lane's copies land
+      if (fast) {
+        // every range is contiguous in its tensor: ONE bulk copy each, completion counted in bytes
+        if (lane == 0) mbar_expect_tx(&s_full[stage], total);
+        __syncwarp();
+        if (bytes) bulk_g2s(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage]);
+      } else {
+        // a range whose covering blocks stick out of its tensor: guarded 16-byte copies by all lanes
+        unsigned char* sb = smem_raw + (size_t)stage * stage_bytes;
+        const int p = ti.phase;
+#pragma unroll 1
+        for (int k = 0; k < 6; ++k) {
+          const RangePlan rk = s_plan[slot].rg[k];
+          if (rk.len <= 0) continue;
+          const unsigned char* lo = k == 0 ? (p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : v16b)
+                                  : k == 1 ? v.k2 : k == 2 ? v.k4 : k == 3 ? v.k8 : k == 4 ? scb : zpb;
+          const int64_t ext = k == 0 ? (p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes)
+                            : k == 1 ? v.k2_bytes : k == 2 ? v.k4_bytes : k == 3 ? v.k8_bytes : v.v_meta_bytes;
+          stage_range_guarded(sb + rk.dst_off, rk.src, rk.len, lo, lo + ext, lane, 32);
+        }
+      }
+      // rows past the tile's end must hold finite fp16 data in the fp16 phase: clear the
+      // rest of the last 16-row group beyond the copied blocks
+      if (ti.phase == 3 && (ti.n & 15)) {
+        const int off = (int)((ti.offs >> 12) & 15u);
+        const int first = (off + ti.n * 256 + 15) & ~15;
+        const int last = off + ((ti.n + 15) & ~15) * 256;
+        unsigned char* sv = smem_raw + (size_t)stage * stage_bytes + SL.v;
+        for (int i = first + 4 * lane; i < last; i += 4 * 32) *reinterpret_cast<uint32_t*>(sv + i) = 0u;
+      }
+      if (lane == 0) s_tile[stage] = ti;
+      mbar_arrive_on_copies(&s_full[stage]);                               // fires when this lane's cp.async copies land
       mbar_arrive(&s_full[stage]);                                         // releases this lane's plain stores
     }
     cp_wait<0>();
-  }
-
-  // ── q*scale in MMA fragment order and the zero-point bias (overlaps the first copies) ──
-  if (warp < FW) {
-    const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
-    const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
-    const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
-    const int64_t qoff = ((int64_t)view_idx * H_q + hq0 + r) * D;
-    float bias_part = 0.f;                                 // thread (r = head, j) sums its own slots
-#pragma unroll 1
-    for (int kb = warp; kb < kd.nkb; kb += FW) {
-      float val[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float f;
-        const int slot = k_slot(kd, kb, j, e, &f);
-        float x = 0.f;
-        if (slot >= 0 && r < gcnt) {
-          const float qs = load_q(q, q_dtype, qoff + perm[slot]) * h2f(sc[slot]);
-          x = __half2float(__float2half_rn(qs / f));
-          bias_part += h2f(zp[slot]) * (x * f);
-        }
-        val[e] = x;
-      }
-      qsA[kb * 32 + lane] = make_uint2(pack_h2(val[0], val[1]), pack_h2(val[2], val[3]));
-    }
-    bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
-    bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
-    if (j == 0) s_ml[warp][r][0] = bias_part;
-    bar_sync(BAR_COMPUTE, FW * 32);
-    if (tid < GH) {
-      float b = 0.f;
-#pragma unroll
-      for (int w = 0; w < FW; ++w) b += s_ml[w][tid][0];
-      s_bias[tid] = b;
-    }
-    bar_sync(BAR_COMPUTE, FW * 32);
   }
 
   // ── workers ─────────────────────────────────────────────────────────────────
@@ -572,18 +645,20 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         cur_phase = p;
       }
       const uint32_t sbu = smem0 + stage * stage_bytes;
-      const bool kfast = k_aligned && !(t.off_k2 & 1) && !(t.off_k4 & 3) && !(t.off_k8 & 3);
+      // low address bits of the sources = byte offsets of the tile's first row inside its stage area
+      const uint32_t off_k2 = t.offs & 15u, off_k4 = (t.offs >> 4) & 15u, off_k8 = (t.offs >> 8) & 15u;
+      const uint32_t off_v = (t.offs >> 12) & 15u, off_m = (t.offs >> 16) & 15u, off_z = (t.offs >> 20) & 15u;
+      const bool kfast = k_aligned && !(off_k2 & 1) && !(off_k4 & 3) && !(off_k8 & 3);
       const bool simple = k_simple && kfast;
       const int row_b = gb * 16;                           // first row of this warp inside the tile
       // cursors (shared-window addresses): K rows r / r+8 of the group, scale/zp row r
-      // (t.off_*: low address bits of the sources = byte offsets of the tile's first row inside its stage area)
-      uint32_t k2a = sbu + SL.k2 + t.off_k2 + (row_b + r) * kd.sub2 + 2 * j;
-      uint32_t k4a = sbu + SL.k4 + t.off_k4 + (row_b + r) * kd.sub4 + 4 * j;
-      uint32_t k8a = sbu + SL.k8 + t.off_k8 + (row_b + r) * kd.n8 + 4 * j;
-      uint32_t sca = sbu + SL.sc + t.off_m + 2 * (row_b + r);
-      uint32_t zpa = sbu + SL.zp + t.off_z + 2 * (row_b + r);
-      const uint32_t v0a = sbu + SL.v + t.off_v;
-      const int64_t krow0 = t.krow0;                       // stripe row of the tile's first row (mask column)
+      uint32_t k2a = sbu + SL.k2 + off_k2 + (row_b + r) * kd.sub2 + 2 * j;
+      uint32_t k4a = sbu + SL.k4 + off_k4 + (row_b + r) * kd.sub4 + 4 * j;
+      uint32_t k8a = sbu + SL.k8 + off_k8 + (row_b + r) * kd.n8 + 4 * j;
+      uint32_t sca = sbu + SL.sc + off_m + 2 * (row_b + r);
+      uint32_t zpa = sbu + SL.zp + off_z + 2 * (row_b + r);
+      const uint32_t v0a = sbu + SL.v + off_v;
+      const int64_t krow0 = t.krow0;                      // stripe row of the tile's first row (mask column)
       const int tn = t.n;
 
       // The group loop, specialised per V phase.  Shared-memory loads are issued in program
