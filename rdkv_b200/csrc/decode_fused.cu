@@ -47,6 +47,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr unsigned WAIT_LIMIT = 1u << 22;  // try_wait rounds before a compute warp gives up on a tile
 constexpr float RESCALE_TH = 8.f;      // log2 slack before the running maximum is moved
+constexpr float M_NONE = -1.0e30f;     // reference maximum of a head that has seen no live score yet (finite: no inf - inf)
 
 __host__ __device__ constexpr int phase_tile_rows(int p) { return p < 2 ? TILE_MAX : p == 2 ? TILE_MAX / 2 : TILE_MAX / 4; }
 __host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : p == 1 ? 64 : p == 2 ? 128 : 256; }
@@ -609,7 +610,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  float m_e = -INFINITY, m_o = -INFINITY;                  // reference maxima of heads 2j, 2j+1 (same in every r)
+  float m_e = M_NONE, m_o = M_NONE;                        // reference maxima of heads 2j, 2j+1 (same in every r)
   float l_e = 0.f, l_o = 0.f, zc_e = 0.f, zc_o = 0.f;      // partial sums over this thread's rows
   int cur_phase = -1;
 
@@ -665,12 +666,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       // order (volatile asm), so the order below is the schedule: the K words of the NEXT
       // group, this group's V scale/zero point and its first V words are requested while
       // the score MMAs of this group are in flight.
-      auto run_tile = [&](auto PC) {
+      auto run_tile = [&](auto PC, auto SC) {
         constexpr int P = decltype(PC)::value;
+        constexpr bool SIMPLE = decltype(SC)::value;       // one span per K segment, aligned rows: straight-line score code
         constexpr int VRB = phase_row_bytes(P);
         uint32_t va = v0a + (P == 3 ? 8 : 4) * r + (row_b + 2 * j) * VRB;
         uint32_t kw0 = 0, kw1 = 0, kw2 = 0, kw3 = 0, kw4 = 0, kw5 = 0;
-        if (simple) {
+        if (SIMPLE) {
           kw0 = lds16(k2a); kw1 = lds16(k2a + 8 * kd.sub2);
           kw2 = lds32(k4a); kw3 = lds32(k4a + 8 * kd.sub4);
           kw4 = lds32(k8a); kw5 = lds32(k8a + 8 * kd.n8);
@@ -679,7 +681,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         for (int g16 = row_b; g16 < ge * 16; g16 += 16 * FW) {
           // ── scores of rows g16+r (A) and g16+r+8 (B): independent MMA chains ──
           float sx[4] = {0.f, 0.f, 0.f, 0.f}, sy[4] = {0.f, 0.f, 0.f, 0.f};
-          if (simple) {
+          if (SIMPLE) {
             const uint2 q0 = lds64<0>(qs_lane), q1 = lds64<256>(qs_lane), q2 = lds64<512>(qs_lane),
                         q3 = lds64<768>(qs_lane), q4 = lds64<1024>(qs_lane);
             const uint32_t yA = prmt(kw0, 0u, 0x4140), yB = prmt(kw1, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
@@ -737,19 +739,18 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           }
 
           // sx+sy: [0] (row A, head 2j) [1] (row A, head 2j+1) [2] (row B, head 2j) [3] (row B, head 2j+1)
-          const bool full = g16 + 16 <= tn;
-          const bool rowA_ok = full || g16 + r < tn, rowB_ok = full || g16 + r + 8 < tn;
           float s2[4];
           s2[0] = fmaf(sx[0] + sy[0], c1, -b1e); s2[1] = fmaf(sx[1] + sy[1], c1, -b1o);
           s2[2] = fmaf(sx[2] + sy[2], c1, -b1e); s2[3] = fmaf(sx[3] + sy[3], c1, -b1o);
           if (has_mask) {
             const int64_t ca = krow0 + g16 + r;
-            if (mask_e != nullptr) { if (rowA_ok) s2[0] += mask_e[ca] * LOG2E; if (rowB_ok) s2[2] += mask_e[ca + 8] * LOG2E; }
-            if (mask_o != nullptr) { if (rowA_ok) s2[1] += mask_o[ca] * LOG2E; if (rowB_ok) s2[3] += mask_o[ca + 8] * LOG2E; }
+            const bool a_ok = g16 + r < tn, b_ok = g16 + r + 8 < tn;
+            if (mask_e != nullptr) { if (a_ok) s2[0] += mask_e[ca] * LOG2E; if (b_ok) s2[2] += mask_e[ca + 8] * LOG2E; }
+            if (mask_o != nullptr) { if (a_ok) s2[1] += mask_o[ca] * LOG2E; if (b_ok) s2[3] += mask_o[ca + 8] * LOG2E; }
           }
-          if (!full) {
-            if (!rowA_ok) { s2[0] = -INFINITY; s2[1] = -INFINITY; }
-            if (!rowB_ok) { s2[2] = -INFINITY; s2[3] = -INFINITY; }
+          if (g16 + 16 > tn) {                             // last, partial group of the tile: rows past its end are dead
+            if (g16 + r >= tn) { s2[0] = -INFINITY; s2[1] = -INFINITY; rsA = 0u; rzA = 0u; }   // (their bytes may be non-finite)
+            if (g16 + r + 8 >= tn) { s2[2] = -INFINITY; s2[3] = -INFINITY; rsB = 0u; rzB = 0u; }
           }
           // lazy reference maximum: exact maxima are only worked out when some score of the warp
           // exceeds its head's reference by more than RESCALE_TH (always true for the first group)
@@ -762,22 +763,19 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
               mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
             }
             const float ne = fmaxf(m_e, me), no = fmaxf(m_o, mo);
-            const float ae = (ne == -INFINITY) ? 1.f : ex2(m_e - ne), ao = (no == -INFINITY) ? 1.f : ex2(m_o - no);
+            const float ae = ex2(m_e - ne), ao = ex2(m_o - no);
             l_e *= ae; zc_e *= ae; l_o *= ao; zc_o *= ao;
 #pragma unroll
             for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
             m_e = ne; m_o = no;
           }
-          const float mse = (m_e == -INFINITY) ? 0.f : m_e, mso = (m_o == -INFINITY) ? 0.f : m_o;
           float pe[4];
-          pe[0] = ex2(s2[0] - mse); pe[1] = ex2(s2[1] - mso); pe[2] = ex2(s2[2] - mse); pe[3] = ex2(s2[3] - mso);
+          pe[0] = ex2(s2[0] - m_e); pe[1] = ex2(s2[1] - m_o); pe[2] = ex2(s2[2] - m_e); pe[3] = ex2(s2[3] - m_o);
           l_e += pe[0] + pe[2]; l_o += pe[1] + pe[3];
           uint32_t hA, hB;                                 // (row A | row B) x (head 2j, head 2j+1) as fp16 pairs
           if (P < 3) {
-            float scA = h2f((uint16_t)rsA), scB = h2f((uint16_t)rsB);
-            float zpA = h2f((uint16_t)rzA), zpB = h2f((uint16_t)rzB);
-            if (!rowA_ok) { scA = 0.f; zpA = 0.f; }        // dead rows may hold non-finite bytes
-            if (!rowB_ok) { scB = 0.f; zpB = 0.f; }
+            const float scA = h2f((uint16_t)rsA), scB = h2f((uint16_t)rsB);
+            const float zpA = h2f((uint16_t)rzA), zpB = h2f((uint16_t)rzB);
             hA = pack_h2(pe[0] * scA, pe[1] * scA); hB = pack_h2(pe[2] * scB, pe[3] * scB);
             const float2 fA = __half22float2(*reinterpret_cast<__half2*>(&hA));   // the values the tensor core sees
             const float2 fB = __half22float2(*reinterpret_cast<__half2*>(&hB));
@@ -858,10 +856,18 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           va += 16 * FW * VRB;
         }
       };
-      if (p == 0) run_tile(std::integral_constant<int, 0>{});
-      else if (p == 1) run_tile(std::integral_constant<int, 1>{});
-      else if (p == 2) run_tile(std::integral_constant<int, 2>{});
-      else run_tile(std::integral_constant<int, 3>{});
+      using std::integral_constant;
+      if (simple) {
+        if (p == 0) run_tile(integral_constant<int, 0>{}, std::true_type{});
+        else if (p == 1) run_tile(integral_constant<int, 1>{}, std::true_type{});
+        else if (p == 2) run_tile(integral_constant<int, 2>{}, std::true_type{});
+        else run_tile(integral_constant<int, 3>{}, std::true_type{});
+      } else {
+        if (p == 0) run_tile(integral_constant<int, 0>{}, std::false_type{});
+        else if (p == 1) run_tile(integral_constant<int, 1>{}, std::false_type{});
+        else if (p == 2) run_tile(integral_constant<int, 2>{}, std::false_type{});
+        else run_tile(integral_constant<int, 3>{}, std::false_type{});
+      }
     }
     if (it + FSTAGES < total_tiles) bar_arrive(BAR_FREE + stage, CTA_THREADS);   // slot may be refilled
   }
@@ -914,7 +920,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     } else {
       float* rec = rec0 + hq * rec_stride;
       rec[4 + d] = o;
-      if (d == 0) { rec[0] = M * LN2; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }   // m in natural-log units
+      if (d == 0) { rec[0] = M <= M_NONE ? -INFINITY : M * LN2; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }   // m in natural-log units
     }
   }
 }
