@@ -130,6 +130,14 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// Same with a zero accumulator input: starts a chain without materialising zeros in registers.
+__device__ __forceinline__ void mma16816_z(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   return __byte_perm(a, b, sel);
 }
@@ -576,11 +584,11 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         }
       }
       // rows past the tile's end must hold finite fp16 data in the fp16 phase: clear the
-      // rest of the last 16-row group beyond the copied blocks
-      if (ti.phase == 3 && (ti.n & 15)) {
+      // rest of the last 32-row block beyond the copied blocks
+      if (ti.phase == 3 && (ti.n & 31)) {
         const int off = (int)((ti.offs >> 12) & 15u);
         const int first = (off + ti.n * 256 + 15) & ~15;
-        const int last = off + ((ti.n + 15) & ~15) * 256;
+        const int last = min(off + ((ti.n + 31) & ~31) * 256, V_STAGE + 16);
         unsigned char* sv = smem_raw + (size_t)stage * stage_bytes + SL.v;
         for (int i = first + 4 * lane; i < last; i += 4 * 32) *reinterpret_cast<uint32_t*>(sv + i) = 0u;
       }
@@ -629,12 +637,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     }
     const TileInfo t = s_tile[stage];
     const int p = t.phase;
-    // this warp takes the tile's 16-row groups gb, gb+FW, ...; the start rotates from tile to
-    // tile so that short tiles (fewer groups than warps) do not always land on the same warps
-    const int ngroups = (t.n + 15) >> 4;
-    const int gb = (warp + FW - (it * (TILE_MAX / 64)) % FW) % FW, ge = ngroups;
+    // this warp takes the tile's 32-row blocks pb, pb+FW, ... (two 16-row MMA groups each, worked on
+    // together so that the two dependency chains overlap); the start rotates from tile to tile so
+    // that short tiles (fewer blocks than warps) do not always land on the same warps
+    const int nblocks = (t.n + 31) >> 5;
+    const int pb = (warp + FW - (it * (TILE_MAX / 128)) % FW) % FW;
 
-    if (gb < ge) {
+    if (pb < nblocks) {
       if (p != cur_phase) {                                // change of accumulator units (powers of two)
         if (cur_phase >= 0) {
 #pragma unroll
@@ -651,8 +660,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       const uint32_t off_v = (t.offs >> 12) & 15u, off_m = (t.offs >> 16) & 15u, off_z = (t.offs >> 20) & 15u;
       const bool kfast = k_aligned && !(off_k2 & 1) && !(off_k4 & 3) && !(off_k8 & 3);
       const bool simple = k_simple && kfast;
-      const int row_b = gb * 16;                           // first row of this warp inside the tile
-      // cursors (shared-window addresses): K rows r / r+8 of the group, scale/zp row r
+      const int row_b = pb * 32;                           // first row of this warp inside the tile
+      // cursors (shared-window addresses): K row r of the block, scale/zp row r
       uint32_t k2a = sbu + SL.k2 + off_k2 + (row_b + r) * kd.sub2 + 2 * j;
       uint32_t k4a = sbu + SL.k4 + off_k4 + (row_b + r) * kd.sub4 + 4 * j;
       uint32_t k8a = sbu + SL.k8 + off_k8 + (row_b + r) * kd.n8 + 4 * j;
@@ -661,141 +670,73 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       const uint32_t v0a = sbu + SL.v + off_v;
       const int64_t krow0 = t.krow0;                      // stripe row of the tile's first row (mask column)
       const int tn = t.n;
+      const uint32_t d2 = 8 * kd.sub2, d4 = 8 * kd.sub4, d8 = 8 * kd.n8;   // 8 rows further in each K stream
 
-      // The group loop, specialised per V phase.  Shared-memory loads are issued in program
-      // order (volatile asm), so the order below is the schedule: the K words of the NEXT
-      // group, this group's V scale/zero point and its first V words are requested while
-      // the score MMAs of this group are in flight.
+      // The block loop, specialised per V phase.  A block is rows [g32, g32+32): thread (r, j) scores
+      // rows g32 + r + {0, 8, 16, 24} for heads 2j, 2j+1 (groups A: +0/+8, B: +16/+24).
       auto run_tile = [&](auto PC, auto SC) {
         constexpr int P = decltype(PC)::value;
         constexpr bool SIMPLE = decltype(SC)::value;       // one span per K segment, aligned rows: straight-line score code
         constexpr int VRB = phase_row_bytes(P);
         uint32_t va = v0a + (P == 3 ? 8 : 4) * r + (row_b + 2 * j) * VRB;
-        uint32_t kw0 = 0, kw1 = 0, kw2 = 0, kw3 = 0, kw4 = 0, kw5 = 0;
-        if (SIMPLE) {
-          kw0 = lds16(k2a); kw1 = lds16(k2a + 8 * kd.sub2);
-          kw2 = lds32(k4a); kw3 = lds32(k4a + 8 * kd.sub4);
-          kw4 = lds32(k8a); kw5 = lds32(k8a + 8 * kd.n8);
-        }
-#pragma unroll 1
-        for (int g16 = row_b; g16 < ge * 16; g16 += 16 * FW) {
-          // ── scores of rows g16+r (A) and g16+r+8 (B): independent MMA chains ──
-          float sx[4] = {0.f, 0.f, 0.f, 0.f}, sy[4] = {0.f, 0.f, 0.f, 0.f};
+
+        // scores of one 16-row group whose row r sits at (a2, a4, a8)
+        auto k_group = [&](uint32_t a2, uint32_t a4, uint32_t a8, float (&sx)[4], float (&sy)[4], const uint2& q0,
+                           const uint2& q1, const uint2& q2, const uint2& q3, const uint2& q4) {
           if (SIMPLE) {
-            const uint2 q0 = lds64<0>(qs_lane), q1 = lds64<256>(qs_lane), q2 = lds64<512>(qs_lane),
-                        q3 = lds64<768>(qs_lane), q4 = lds64<1024>(qs_lane);
-            const uint32_t yA = prmt(kw0, 0u, 0x4140), yB = prmt(kw1, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
-            mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
-            mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
-            const uint32_t vA = kw2 >> 8, vB = kw3 >> 8;
-            mma16816(sx, kw2 & 0x000F000Fu, kw3 & 0x000F000Fu, kw2 & 0x00F000F0u, kw3 & 0x00F000F0u, q2.x, q2.y);
+            const uint32_t w2A = lds16(a2), w2B = lds16(a2 + d2);
+            const uint32_t w4A = lds32(a4), w4B = lds32(a4 + d4);
+            const uint32_t w8A = lds32(a8), w8B = lds32(a8 + d8);
+            const uint32_t yA = prmt(w2A, 0u, 0x4140), yB = prmt(w2B, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
+            mma16816_z(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
+            mma16816_z(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
+            const uint32_t vA = w4A >> 8, vB = w4B >> 8;
+            mma16816(sx, w4A & 0x000F000Fu, w4B & 0x000F000Fu, w4A & 0x00F000F0u, w4B & 0x00F000F0u, q2.x, q2.y);
             mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q3.x, q3.y);
-            mma16816(sx, kw4 & 0x00FF00FFu, kw5 & 0x00FF00FFu, prmt(kw4, 0u, 0x4341), prmt(kw5, 0u, 0x4341), q4.x, q4.y);
-            // K words of this warp's next group (past the tile's end the words are unused; the
-            // addresses stay inside the CTA's shared memory: at most 80 rows x 16 bytes further)
-            k2a += 16 * FW * kd.sub2; k4a += 16 * FW * kd.sub4; k8a += 16 * FW * kd.n8;
-            kw0 = lds16(k2a); kw1 = lds16(k2a + 8 * kd.sub2);
-            kw2 = lds32(k4a); kw3 = lds32(k4a + 8 * kd.sub4);
-            kw4 = lds32(k8a); kw5 = lds32(k8a + 8 * kd.n8);
+            mma16816(sx, w8A & 0x00FF00FFu, w8B & 0x00FF00FFu, prmt(w8A, 0u, 0x4341), prmt(w8B, 0u, 0x4341), q4.x, q4.y);
           } else {
+            sx[0] = sx[1] = sx[2] = sx[3] = 0.f; sy[0] = sy[1] = sy[2] = sy[3] = 0.f;
             uint32_t qa = qs_lane;
 #pragma unroll 1
             for (int s = 0; s < kd.nsp2; ++s, qa += 512) {
-              const uint2 q0 = lds64<0>(qa), q1 = lds64<256>(qa);
-              const uint32_t wA = kfast ? lds16(k2a + 8 * s) : lds32_unaligned(k2a + 8 * s);
-              const uint32_t wB = kfast ? lds16(k2a + 8 * kd.sub2 + 8 * s) : lds32_unaligned(k2a + 8 * kd.sub2 + 8 * s);
+              const uint2 p0 = lds64<0>(qa), p1 = lds64<256>(qa);
+              const uint32_t wA = kfast ? lds16(a2 + 8 * s) : lds32_unaligned(a2 + 8 * s);
+              const uint32_t wB = kfast ? lds16(a2 + d2 + 8 * s) : lds32_unaligned(a2 + d2 + 8 * s);
               const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);
-              mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
-              mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
+              mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, p0.x, p0.y);
+              mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, p1.x, p1.y);
             }
 #pragma unroll 1
             for (int s = 0; s < kd.nsp4; ++s, qa += 512) {
-              const uint2 q0 = lds64<0>(qa), q1 = lds64<256>(qa);
-              const uint32_t wA = kfast ? lds32(k4a + 16 * s) : lds32_unaligned(k4a + 16 * s);
-              const uint32_t wB = kfast ? lds32(k4a + 8 * kd.sub4 + 16 * s) : lds32_unaligned(k4a + 8 * kd.sub4 + 16 * s);
+              const uint2 p0 = lds64<0>(qa), p1 = lds64<256>(qa);
+              const uint32_t wA = kfast ? lds32(a4 + 16 * s) : lds32_unaligned(a4 + 16 * s);
+              const uint32_t wB = kfast ? lds32(a4 + d4 + 16 * s) : lds32_unaligned(a4 + d4 + 16 * s);
               const uint32_t vA = wA >> 8, vB = wB >> 8;
-              mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, q0.x, q0.y);
-              mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q1.x, q1.y);
+              mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, p0.x, p0.y);
+              mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, p1.x, p1.y);
             }
 #pragma unroll 1
             for (int b = 0; b < kd.nkb8; ++b, qa += 256) {
-              const uint2 q0 = lds64<0>(qa);
-              const uint32_t wA = kfast ? lds32(k8a + 16 * b) : lds32_unaligned(k8a + 16 * b);
-              const uint32_t wB = kfast ? lds32(k8a + 8 * kd.n8 + 16 * b) : lds32_unaligned(k8a + 8 * kd.n8 + 16 * b);
-              mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, prmt(wA, 0u, 0x4341), prmt(wB, 0u, 0x4341), q0.x, q0.y);
+              const uint2 p0 = lds64<0>(qa);
+              const uint32_t wA = kfast ? lds32(a8 + 16 * b) : lds32_unaligned(a8 + 16 * b);
+              const uint32_t wB = kfast ? lds32(a8 + d8 + 16 * b) : lds32_unaligned(a8 + d8 + 16 * b);
+              mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, prmt(wA, 0u, 0x4341), prmt(wB, 0u, 0x4341), p0.x, p0.y);
             }
-            k2a += 16 * FW * kd.sub2; k4a += 16 * FW * kd.sub4; k8a += 16 * FW * kd.n8;
           }
-          // requested now, needed after the softmax: V scale / zero point of rows A and B and
-          // the first V words of the group
-          uint32_t rsA = 0, rsB = 0, rzA = 0, rzB = 0;
-          if (P < 3) { rsA = lds16(sca); rsB = lds16<16>(sca); rzA = lds16(zpa); rzB = lds16<16>(zpa); }
-          uint32_t w0, w1, w2, w3, x0 = 0, x1 = 0, x2 = 0, x3 = 0;
-          if (P == 3) {
-            const uint2 a0 = lds64(va), a1 = lds64<256>(va), a2 = lds64<8 * 256>(va), a3 = lds64<9 * 256>(va);
-            w0 = a0.x; w1 = a1.x; w2 = a2.x; w3 = a3.x; x0 = a0.y; x1 = a1.y; x2 = a2.y; x3 = a3.y;
-          } else {
-            w0 = lds32(va); w1 = lds32<VRB>(va); w2 = lds32<8 * VRB>(va); w3 = lds32<9 * VRB>(va);
-          }
+        };
 
-          // sx+sy: [0] (row A, head 2j) [1] (row A, head 2j+1) [2] (row B, head 2j) [3] (row B, head 2j+1)
-          float s2[4];
-          s2[0] = fmaf(sx[0] + sy[0], c1, -b1e); s2[1] = fmaf(sx[1] + sy[1], c1, -b1o);
-          s2[2] = fmaf(sx[2] + sy[2], c1, -b1e); s2[3] = fmaf(sx[3] + sy[3], c1, -b1o);
-          if (has_mask) {
-            const int64_t ca = krow0 + g16 + r;
-            const bool a_ok = g16 + r < tn, b_ok = g16 + r + 8 < tn;
-            if (mask_e != nullptr) { if (a_ok) s2[0] += mask_e[ca] * LOG2E; if (b_ok) s2[2] += mask_e[ca + 8] * LOG2E; }
-            if (mask_o != nullptr) { if (a_ok) s2[1] += mask_o[ca] * LOG2E; if (b_ok) s2[3] += mask_o[ca + 8] * LOG2E; }
-          }
-          if (g16 + 16 > tn) {                             // last, partial group of the tile: rows past its end are dead
-            if (g16 + r >= tn) { s2[0] = -INFINITY; s2[1] = -INFINITY; rsA = 0u; rzA = 0u; }   // (their bytes may be non-finite)
-            if (g16 + r + 8 >= tn) { s2[2] = -INFINITY; s2[3] = -INFINITY; rsB = 0u; rzB = 0u; }
-          }
-          // lazy reference maximum: exact maxima are only worked out when some score of the warp
-          // exceeds its head's reference by more than RESCALE_TH (always true for the first group)
-          const float te = m_e + RESCALE_TH, to = m_o + RESCALE_TH;
-          if (__any_sync(0xffffffffu, s2[0] > te || s2[2] > te || s2[1] > to || s2[3] > to)) {
-            float me = fmaxf(s2[0], s2[2]), mo = fmaxf(s2[1], s2[3]);
-#pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
-              me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
-              mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
-            }
-            const float ne = fmaxf(m_e, me), no = fmaxf(m_o, mo);
-            const float ae = ex2(m_e - ne), ao = ex2(m_o - no);
-            l_e *= ae; zc_e *= ae; l_o *= ao; zc_o *= ao;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
-            m_e = ne; m_o = no;
-          }
-          float pe[4];
-          pe[0] = ex2(s2[0] - m_e); pe[1] = ex2(s2[1] - m_o); pe[2] = ex2(s2[2] - m_e); pe[3] = ex2(s2[3] - m_o);
-          l_e += pe[0] + pe[2]; l_o += pe[1] + pe[3];
-          uint32_t hA, hB;                                 // (row A | row B) x (head 2j, head 2j+1) as fp16 pairs
-          if (P < 3) {
-            const float scA = h2f((uint16_t)rsA), scB = h2f((uint16_t)rsB);
-            const float zpA = h2f((uint16_t)rzA), zpB = h2f((uint16_t)rzB);
-            hA = pack_h2(pe[0] * scA, pe[1] * scA); hB = pack_h2(pe[2] * scB, pe[3] * scB);
-            const float2 fA = __half22float2(*reinterpret_cast<__half2*>(&hA));   // the values the tensor core sees
-            const float2 fB = __half22float2(*reinterpret_cast<__half2*>(&hB));
-            zc_e = fmaf(fA.x, zpA, zc_e); zc_o = fmaf(fA.y, zpA, zc_o);
-            zc_e = fmaf(fB.x, zpB, zc_e); zc_o = fmaf(fB.y, zpB, zc_o);
-          } else {
-            hA = pack_h2(pe[0], pe[1]); hB = pack_h2(pe[2], pe[3]);
-          }
-          // 8x8 transposes: thread (r, j) now holds head r at rows g16 + {2j, 2j+1} and g16 + 8 + {2j, 2j+1}
-          const uint32_t pb0 = movmatrix_trans(hA), pb1 = movmatrix_trans(hB);
-
-          // ── P.V: channels on M, rows on K; this thread supplies rows g16 + {2j,2j+1,8+2j,9+2j}.
-          //    The words of part vv+1 are requested before part vv is worked on. ──
+        // P.V of one 16-row group: channels on M, rows on K; this thread supplies rows {2j, 2j+1, 8+2j, 9+2j}
+        // of the group whose rows start at shared address `vg`.  (w0..w3: the first words, already loaded;
+        // the words of part vv+1 are requested before part vv is worked on.)
+        auto pv_group = [&](uint32_t vg, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t x0, uint32_t x1,
+                            uint32_t x2, uint32_t x3, uint32_t pb0, uint32_t pb1) {
           if (P == 2) {
 #pragma unroll
             for (int vv = 0; vv < 4; ++vv) {
               uint32_t n0 = 0, n1 = 0, n2 = 0, n3 = 0;
               if (vv < 3) {
-                n0 = lds32(va + 32 * (vv + 1)); n1 = lds32(va + 32 * (vv + 1) + 128);
-                n2 = lds32(va + 32 * (vv + 1) + 8 * 128); n3 = lds32(va + 32 * (vv + 1) + 9 * 128);
+                n0 = lds32(vg + 32 * (vv + 1)); n1 = lds32(vg + 32 * (vv + 1) + 128);
+                n2 = lds32(vg + 32 * (vv + 1) + 8 * 128); n3 = lds32(vg + 32 * (vv + 1) + 9 * 128);
               }
 #pragma unroll
               for (int qq = 0; qq < 2; ++qq) {
@@ -811,7 +752,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             for (int vl = 0; vl < 2; ++vl) {
               uint32_t n0 = 0, n1 = 0, n2 = 0, n3 = 0;
               if (vl < 1) {
-                n0 = lds32(va + 32); n1 = lds32(va + 32 + 64); n2 = lds32(va + 32 + 8 * 64); n3 = lds32(va + 32 + 9 * 64);
+                n0 = lds32(vg + 32); n1 = lds32(vg + 32 + 64); n2 = lds32(vg + 32 + 8 * 64); n3 = lds32(vg + 32 + 9 * 64);
               }
 #pragma unroll
               for (int qq = 0; qq < 2; ++qq) {
@@ -842,8 +783,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             for (int vv = 0; vv < 4; ++vv) {
               uint2 a0 = make_uint2(0u, 0u), a1 = a0, a2 = a0, a3 = a0;
               if (vv < 3) {
-                a0 = lds64(va + 64 * (vv + 1)); a1 = lds64(va + 64 * (vv + 1) + 256);
-                a2 = lds64(va + 64 * (vv + 1) + 8 * 256); a3 = lds64(va + 64 * (vv + 1) + 9 * 256);
+                a0 = lds64(vg + 64 * (vv + 1)); a1 = lds64(vg + 64 * (vv + 1) + 256);
+                a2 = lds64(vg + 64 * (vv + 1) + 8 * 256); a3 = lds64(vg + 64 * (vv + 1) + 9 * 256);
               }
               mma16816(acc[vv], prmt(w0, w1, 0x5410), prmt(w0, w1, 0x7632), prmt(w2, w3, 0x5410),
                        prmt(w2, w3, 0x7632), pb0, pb1);
@@ -852,8 +793,107 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
               w0 = a0.x; w1 = a1.x; w2 = a2.x; w3 = a3.x; x0 = a0.y; x1 = a1.y; x2 = a2.y; x3 = a3.y;
             }
           }
-          sca += 32 * FW; zpa += 32 * FW;
-          va += 16 * FW * VRB;
+        };
+
+#pragma unroll 1
+        for (int g32 = row_b; g32 < nblocks * 32; g32 += 32 * FW) {
+          // ── scores: two independent groups, two MMA chains each ──
+          float sxA[4], syA[4], sxB[4], syB[4];
+          {
+            uint2 q0 = make_uint2(0u, 0u), q1 = q0, q2 = q0, q3 = q0, q4 = q0;
+            if (SIMPLE) {
+              q0 = lds64<0>(qs_lane); q1 = lds64<256>(qs_lane); q2 = lds64<512>(qs_lane);
+              q3 = lds64<768>(qs_lane); q4 = lds64<1024>(qs_lane);
+            }
+            k_group(k2a, k4a, k8a, sxA, syA, q0, q1, q2, q3, q4);
+            k_group(k2a + 2 * d2, k4a + 2 * d4, k8a + 2 * d8, sxB, syB, q0, q1, q2, q3, q4);
+          }
+          // requested now, needed after the softmax: V scale / zero point of the four rows and the
+          // first V words of both groups
+          uint32_t rs[4] = {0u, 0u, 0u, 0u}, rz[4] = {0u, 0u, 0u, 0u};
+          if (P < 3) {
+            rs[0] = lds16(sca); rs[1] = lds16<16>(sca); rs[2] = lds16<32>(sca); rs[3] = lds16<48>(sca);
+            rz[0] = lds16(zpa); rz[1] = lds16<16>(zpa); rz[2] = lds16<32>(zpa); rz[3] = lds16<48>(zpa);
+          }
+          uint32_t wA0, wA1, wA2, wA3, xA0 = 0, xA1 = 0, xA2 = 0, xA3 = 0;
+          uint32_t wB0, wB1, wB2, wB3, xB0 = 0, xB1 = 0, xB2 = 0, xB3 = 0;
+          if (P == 3) {
+            const uint2 a0 = lds64(va), a1 = lds64<256>(va), a2 = lds64<8 * 256>(va), a3 = lds64<9 * 256>(va);
+            wA0 = a0.x; wA1 = a1.x; wA2 = a2.x; wA3 = a3.x; xA0 = a0.y; xA1 = a1.y; xA2 = a2.y; xA3 = a3.y;
+            const uint2 b0 = lds64<16 * 256>(va), b1 = lds64<17 * 256>(va), b2 = lds64<24 * 256>(va), b3 = lds64<25 * 256>(va);
+            wB0 = b0.x; wB1 = b1.x; wB2 = b2.x; wB3 = b3.x; xB0 = b0.y; xB1 = b1.y; xB2 = b2.y; xB3 = b3.y;
+          } else {
+            wA0 = lds32(va); wA1 = lds32<VRB>(va); wA2 = lds32<8 * VRB>(va); wA3 = lds32<9 * VRB>(va);
+            wB0 = lds32<16 * VRB>(va); wB1 = lds32<17 * VRB>(va); wB2 = lds32<24 * VRB>(va); wB3 = lds32<25 * VRB>(va);
+          }
+
+          // s2[k]: rows g32 + r + 8*(k>>1)... laid out [2k] head 2j, [2k+1] head 2j+1 for row slot k = 0..3
+          float s2[8];
+          s2[0] = fmaf(sxA[0] + syA[0], c1, -b1e); s2[1] = fmaf(sxA[1] + syA[1], c1, -b1o);
+          s2[2] = fmaf(sxA[2] + syA[2], c1, -b1e); s2[3] = fmaf(sxA[3] + syA[3], c1, -b1o);
+          s2[4] = fmaf(sxB[0] + syB[0], c1, -b1e); s2[5] = fmaf(sxB[1] + syB[1], c1, -b1o);
+          s2[6] = fmaf(sxB[2] + syB[2], c1, -b1e); s2[7] = fmaf(sxB[3] + syB[3], c1, -b1o);
+          if (has_mask) {
+            const int64_t ca = krow0 + g32 + r;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (g32 + r + 8 * k < tn) {
+                if (mask_e != nullptr) s2[2 * k] += mask_e[ca + 8 * k] * LOG2E;
+                if (mask_o != nullptr) s2[2 * k + 1] += mask_o[ca + 8 * k] * LOG2E;
+              }
+            }
+          }
+          if (g32 + 32 > tn) {                             // last, partial block of the tile: rows past its end are dead
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              if (g32 + r + 8 * k >= tn) { s2[2 * k] = -INFINITY; s2[2 * k + 1] = -INFINITY; rs[k] = 0u; rz[k] = 0u; }   // (their bytes may be non-finite)
+          }
+          // lazy reference maximum: exact maxima are only worked out when some score of the warp
+          // exceeds its head's reference by more than RESCALE_TH (always true for the first block)
+          const float te = m_e + RESCALE_TH, to = m_o + RESCALE_TH;
+          const float mxe = fmaxf(fmaxf(s2[0], s2[2]), fmaxf(s2[4], s2[6]));
+          const float mxo = fmaxf(fmaxf(s2[1], s2[3]), fmaxf(s2[5], s2[7]));
+          if (__any_sync(0xffffffffu, mxe > te || mxo > to)) {
+            float me = mxe, mo = mxo;
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+              me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
+              mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
+            }
+            const float ne = fmaxf(m_e, me), no = fmaxf(m_o, mo);
+            const float ae = ex2(m_e - ne), ao = ex2(m_o - no);
+            l_e *= ae; zc_e *= ae; l_o *= ao; zc_o *= ao;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
+            m_e = ne; m_o = no;
+          }
+          float pe[8];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { pe[2 * k] = ex2(s2[2 * k] - m_e); pe[2 * k + 1] = ex2(s2[2 * k + 1] - m_o); }
+          l_e += (pe[0] + pe[2]) + (pe[4] + pe[6]); l_o += (pe[1] + pe[3]) + (pe[5] + pe[7]);
+          uint32_t hh[4];                                  // row slot k x (head 2j, head 2j+1) as fp16 pairs
+          if (P < 3) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float sck = h2f((uint16_t)rs[k]), zpk = h2f((uint16_t)rz[k]);
+              hh[k] = pack_h2(pe[2 * k] * sck, pe[2 * k + 1] * sck);
+              const float2 fk = __half22float2(*reinterpret_cast<__half2*>(&hh[k]));   // the values the tensor core sees
+              zc_e = fmaf(fk.x, zpk, zc_e); zc_o = fmaf(fk.y, zpk, zc_o);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) hh[k] = pack_h2(pe[2 * k], pe[2 * k + 1]);
+          }
+          // 8x8 transposes: thread (r, j) now holds head r at rows {2j, 2j+1} and 8 + {2j, 2j+1} of each group
+          const uint32_t pA0 = movmatrix_trans(hh[0]), pA1 = movmatrix_trans(hh[1]);
+          const uint32_t pB0 = movmatrix_trans(hh[2]), pB1 = movmatrix_trans(hh[3]);
+
+          pv_group(va, wA0, wA1, wA2, wA3, xA0, xA1, xA2, xA3, pA0, pA1);
+          pv_group(va + 16 * VRB, wB0, wB1, wB2, wB3, xB0, xB1, xB2, xB3, pB0, pB1);
+
+          k2a += 4 * FW * d2; k4a += 4 * FW * d4; k8a += 4 * FW * d8;
+          sca += 64 * FW; zpa += 64 * FW;
+          va += 32 * FW * VRB;
         }
       };
       using std::integral_constant;
