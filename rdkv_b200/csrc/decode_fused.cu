@@ -608,8 +608,6 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   // an absent head gets an infinite bias: its scores are -inf without further tests
   const float b1e = he_ok ? s_bias[2 * j] * INV_SQRT_D * LOG2E : INFINITY;
   const float b1o = ho_ok ? s_bias[2 * j + 1] * INV_SQRT_D * LOG2E : INFINITY;
-  const float* mask_e = (v.mask != nullptr && he_ok) ? v.mask + (int64_t)(hq0 + 2 * j) * v.mask_row_stride : nullptr;
-  const float* mask_o = (v.mask != nullptr && ho_ok) ? v.mask + (int64_t)(hq0 + 2 * j + 1) * v.mask_row_stride : nullptr;
   const bool has_mask = v.mask != nullptr;
   const bool k_aligned = !(kd.sub2 & 1) && !(kd.sub4 & 3) && !(kd.n8 & 3);
   const bool k_simple = kd.nsp2 == 1 && kd.nsp4 == 1 && kd.nkb8 == 1;   // one span per segment: straight-line code
@@ -668,7 +666,6 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       uint32_t sca = sbu + SL.sc + off_m + 2 * (row_b + r);
       uint32_t zpa = sbu + SL.zp + off_z + 2 * (row_b + r);
       const uint32_t v0a = sbu + SL.v + off_v;
-      const int64_t krow0 = t.krow0;                      // stripe row of the tile's first row (mask column)
       const int tn = t.n;
       const uint32_t d2 = 8 * kd.sub2, d4 = 8 * kd.sub4, d8 = 8 * kd.n8;   // 8 rows further in each K stream
 
@@ -833,13 +830,15 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           s2[2] = fmaf(sxA[2] + syA[2], c1, -b1e); s2[3] = fmaf(sxA[3] + syA[3], c1, -b1o);
           s2[4] = fmaf(sxB[0] + syB[0], c1, -b1e); s2[5] = fmaf(sxB[1] + syB[1], c1, -b1o);
           s2[6] = fmaf(sxB[2] + syB[2], c1, -b1e); s2[7] = fmaf(sxB[3] + syB[3], c1, -b1o);
-          if (has_mask) {
-            const int64_t ca = krow0 + g32 + r;
+          if (has_mask) {                                  // additive softmax mask (rarely given: everything it needs is re-read here)
+            const int64_t ca = (int64_t)s_tile[stage].krow0 + g32 + r;   // stripe row = mask column
+            const float* mask_e = v.mask + (int64_t)(hq0 + 2 * j) * v.mask_row_stride;
+            const float* mask_o = mask_e + v.mask_row_stride;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               if (g32 + r + 8 * k < tn) {
-                if (mask_e != nullptr) s2[2 * k] += mask_e[ca + 8 * k] * LOG2E;
-                if (mask_o != nullptr) s2[2 * k + 1] += mask_o[ca + 8 * k] * LOG2E;
+                if (he_ok) s2[2 * k] += mask_e[ca + 8 * k] * LOG2E;
+                if (ho_ok) s2[2 * k + 1] += mask_o[ca + 8 * k] * LOG2E;
               }
             }
           }
