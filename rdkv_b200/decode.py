@@ -117,7 +117,8 @@ def lse_combine(partials: Tensor, out: Optional[Tensor] = None, *, out_ml: Optio
 def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out: Optional[Tensor],
                   v0: int = 0, v1: Optional[int] = None) -> None:
     """Launch the fused kernel on views [v0, v1) of the table (all of them by default);
-    q, partials and out are the full-table tensors, the range is cut by pointer offsets."""
+    q, partials and out are the full-table tensors, the range is cut by pointer offsets.
+    ``out`` may be a pinned host tensor (device-addressable)."""
     require_cuda(q, "q")
     if q.shape[-1] != HEAD_DIM or q.numel() != table.n_views * table.H_q * HEAD_DIM:
         raise ValueError(f"q must be [{table.n_views},{table.H_q},{HEAD_DIM}], got {tuple(q.shape)}")
@@ -185,12 +186,12 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
 
 
 class _HostIO:
-    """Device staging buffers and streams of the host-buffer call, kept on the table."""
+    """Device staging buffer for the queries and the streams of the host-buffer call, kept on the table."""
 
     def __init__(self, table: DecodeTable, q_dtype: torch.dtype, n_slices: int):
         dev = table.device
         self.q = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=q_dtype, device=dev)
-        self.out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=dev)
+        self.out: Optional[Tensor] = None                  # device-side results; only for pageable out_host
         self.streams = [torch.cuda.Stream(device=dev) for _ in range(n_slices)]
         step = -(-table.n_views // n_slices)
         self.ranges = [(a, min(a + step, table.n_views)) for a in range(0, table.n_views, step)]
@@ -198,12 +199,14 @@ class _HostIO:
 
 def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: Tensor, *, slices: int = 4) -> Tensor:
     """Host-buffer form of :func:`packed_decode_attention`: ``q_host`` [n_views,H_q,128]
-    (fp16/bf16/fp32) and ``out_host`` [n_views,H_q,128] fp32 live in (pinned) host memory.
+    (fp16/bf16/fp32) and ``out_host`` [n_views,H_q,128] fp32 live in host memory.
 
-    The views are cut into ``slices`` ranges; every range uploads its queries, runs the
-    kernel and downloads its results on a stream of its own, so the copies of one range
-    overlap the kernel of another.  Returns after the results have arrived in ``out_host``.
-    Pageable host tensors work too but serialise the copies.
+    The views are cut into ``slices`` ranges; every range uploads its queries and runs the
+    kernel on a stream of its own, so the upload of one range overlaps the kernel of another.
+    With a pinned ``out_host`` the kernels write their results straight into it (pinned host
+    memory is addressable from the device), so the results cross the bus while the kernels
+    run and no separate download is needed; a pageable ``out_host`` gets a copy per range.
+    Returns after the results have arrived in ``out_host``.
     """
     if q_host.is_cuda or out_host.is_cuda:
         raise ValueError("packed_decode_attention_host takes host tensors; use packed_decode_attention on the device")
@@ -217,6 +220,10 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
     if io is None or io.q.dtype != q_host.dtype or len(io.streams) != n_slices:
         io = _HostIO(table, q_host.dtype, n_slices)
         table._host_io = io
+    direct = out_host.is_pinned()
+    if not direct and io.out is None:
+        io.out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=table.device)
+    out = out_host if direct else io.out
     cur = torch.cuda.current_stream(table.device)
     part = table.workspace()
     for (a, b), st in zip(io.ranges, io.streams):
@@ -224,11 +231,15 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
         with torch.cuda.stream(st):
             io.q[a:b].copy_(q_host[a:b], non_blocking=True)
             if part is None:
-                _launch_fused(io.q, table, None, io.out, a, b)
+                _launch_fused(io.q, table, None, out, a, b)
             else:
                 _launch_fused(io.q, table, part, None, a, b)
-                lse_combine(part[a * table.H_q:b * table.H_q], io.out.view(-1, HEAD_DIM)[a * table.H_q:b * table.H_q])
-            out_host[a:b].copy_(io.out[a:b], non_blocking=True)
+                rows = slice(a * table.H_q, b * table.H_q)
+                check(lib().rdkv_lse_combine(part[rows].data_ptr(), (b - a) * table.H_q, table.n_chunks,
+                                             part.stride(0), part.stride(1), out.view(-1, HEAD_DIM)[rows].data_ptr(),
+                                             None, None, stream_ptr(table.device)), "rdkv_lse_combine")
+            if not direct:
+                out_host[a:b].copy_(io.out[a:b], non_blocking=True)
     for st in io.streams[:len(io.ranges)]:
         cur.wait_stream(st)
     cur.synchronize()

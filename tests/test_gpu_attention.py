@@ -132,10 +132,13 @@ def test_host_buffer_call_equals_device_call():
         want = packed_decode_attention(q.cuda(), table).cpu()
         q_host = q.pin_memory()
         for slices in (1, 3, 7, 50):
-            out_host = torch.full((7, H_kv * g, 128), float("nan")).pin_memory()
-            got = packed_decode_attention_host(q_host, table, out_host, slices=slices)
-            assert got is out_host
-            assert torch.equal(out_host, want), (n_chunks, slices)
+            for pinned in (True, False):                   # pinned: written by the kernels; pageable: copied per range
+                out_host = torch.full((7, H_kv * g, 128), float("nan"))
+                if pinned:
+                    out_host = out_host.pin_memory()
+                got = packed_decode_attention_host(q_host, table, out_host, slices=slices)
+                assert got is out_host
+                assert torch.equal(out_host, want), (n_chunks, slices, pinned)
         table.check_status()
     with pytest.raises(ValueError):
         packed_decode_attention_host(q.cuda(), table, out_host)
