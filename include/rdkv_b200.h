@@ -193,7 +193,9 @@ int rdkv_pack_v(const uint16_t* V, int64_t v_head_stride, int64_t v_row_stride, 
  * identity over t_k rows.  ch_order/ch_counts: channel partition (mode 1).
  * Channel slot layout is [n_ch2_pad | n_ch4_pad | n_ch8]; a head's kept
  * channels fill a prefix of each block, the rest are zero columns.
- * scratch: fp32 [H][n_slabs][2][d_pad] (n_slabs = rdkv_pack_k_slabs(t_k)).
+ * scratch: fp32 [H][rdkv_pack_k_slabs(t_k)][2][d_pad] (per head: one block of
+ * (min, max) per slab of stripe rows, then one block holding the final scale and
+ * zero point in fp32).
  * Outputs: k2 [H][t_k][n_ch2_pad/4], k4 [H][t_k][n_ch4_pad/2], k8 [H][t_k][n_ch8],
  * scale/zp fp16 [H][d_pad], sort_idx int64 [H][d_kept_max] (0-padded),
  * perm int64 [H][d_pad] (pad -> 0), perm_q int64 [H*g][d_pad] or NULL,
@@ -210,6 +212,36 @@ int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_row_stride, 
                 uint8_t* k2, uint8_t* k4, uint8_t* k8, uint16_t* out_scale, uint16_t* out_zp,
                 int64_t* sort_idx, int64_t* perm, int64_t* perm_q, int32_t* seg_bounds,
                 int quant_bits_override, void* stream);
+
+/* ── prefill: every layer of a cache in one pass ──────────────────────────────
+ * The reference packs a whole cache layer by layer (build_packed_cache,
+ * obkv_accel/packing.py:1323-1421; driver loop obkv_fast.py:1098-1166); here the
+ * layers' V and K passes run as three launches whose third grid dimension is the
+ * layer.  One job per layer, in device memory; a job's fields have the meaning
+ * of the like-named arguments of rdkv_pack_v / rdkv_pack_k.  rows2..rows16,
+ * rows_meta, rows_k: rows allocated per head in the outputs (the per-layer
+ * outputs may be slices of tensors that are taller than this layer needs).
+ * scratch: fp32 [H][rdkv_pack_k_slabs(t_k)][2][d_pad] of the job. */
+typedef struct rdkv_pack_job {
+  const uint16_t* K; const uint16_t* V;               /* fp16 [H][T][D] of the layer */
+  int64_t k_head_stride, k_row_stride, v_head_stride, v_row_stride;   /* elements */
+  const int32_t* tok_order; const int32_t* tok_counts; /* [H][tok_order_row_stride], [H][4] */
+  const int32_t* ch_order;  const int32_t* ch_counts;  /* [H][ch_order_row_stride],  [H][4] */
+  int64_t tok_order_row_stride, ch_order_row_stride;
+  int32_t D, gqa;
+  int32_t max_n2, max_n4, max_n8, max_n16, max_t_v, t_k;
+  int32_t rows2, rows4, rows8, rows16, rows_meta, rows_k;
+  int32_t n_ch2_pad, n_ch4_pad, n_ch8, d_kept_max;
+  uint8_t *v2, *v4, *v8; uint16_t *v16, *v_scale, *v_zp;
+  uint8_t *k2, *k4, *k8; uint16_t *k_scale, *k_zp;
+  int64_t *sort_idx, *perm, *perm_q; int32_t* seg_bounds;
+  float* scratch;
+} rdkv_pack_job;
+
+int rdkv_sizeof_pack_job(void);
+/* max_slots: max over jobs of max_n2+max_n4+max_n8+max_n16; max_t_k, max_d_pad: max over jobs. */
+int rdkv_pack_kv_batched(const rdkv_pack_job* jobs, int n_jobs, int H, int D, int max_slots,
+                         int max_t_k, int max_d_pad, void* stream);
 
 /* ── prefill: batched Lagrangian bit allocator ────────────────────────────────
  * Replaces knapsack_bit_allocation_batched (knapsack_solver.py:121-248).

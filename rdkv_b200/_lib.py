@@ -44,6 +44,30 @@ class LayerView(C.Structure):
     ]
 
 
+class PackJob(C.Structure):
+    """Mirror of ``rdkv_pack_job`` (one layer of a batched pack); field order and types must match the header."""
+    _fields_ = [
+        ("K", C.c_void_p), ("V", C.c_void_p),
+        ("k_head_stride", C.c_int64), ("k_row_stride", C.c_int64),
+        ("v_head_stride", C.c_int64), ("v_row_stride", C.c_int64),
+        ("tok_order", C.c_void_p), ("tok_counts", C.c_void_p),
+        ("ch_order", C.c_void_p), ("ch_counts", C.c_void_p),
+        ("tok_order_row_stride", C.c_int64), ("ch_order_row_stride", C.c_int64),
+        ("D", C.c_int32), ("gqa", C.c_int32),
+        ("max_n2", C.c_int32), ("max_n4", C.c_int32), ("max_n8", C.c_int32), ("max_n16", C.c_int32),
+        ("max_t_v", C.c_int32), ("t_k", C.c_int32),
+        ("rows2", C.c_int32), ("rows4", C.c_int32), ("rows8", C.c_int32), ("rows16", C.c_int32),
+        ("rows_meta", C.c_int32), ("rows_k", C.c_int32),
+        ("n_ch2_pad", C.c_int32), ("n_ch4_pad", C.c_int32), ("n_ch8", C.c_int32), ("d_kept_max", C.c_int32),
+        ("v2", C.c_void_p), ("v4", C.c_void_p), ("v8", C.c_void_p),
+        ("v16", C.c_void_p), ("v_scale", C.c_void_p), ("v_zp", C.c_void_p),
+        ("k2", C.c_void_p), ("k4", C.c_void_p), ("k8", C.c_void_p),
+        ("k_scale", C.c_void_p), ("k_zp", C.c_void_p),
+        ("sort_idx", C.c_void_p), ("perm", C.c_void_p), ("perm_q", C.c_void_p), ("seg_bounds", C.c_void_p),
+        ("scratch", C.c_void_p),
+    ]
+
+
 _lib: Optional[C.CDLL] = None
 
 _i, _i64, _p, _f = C.c_int, C.c_int64, C.c_void_p, C.c_float
@@ -64,6 +88,8 @@ _PROTOTYPES = {
     "rdkv_pack_k_slabs": ([_i], _i),
     "rdkv_pack_k": ([_p, _i64, _i64, _i, _i, _p, _i64, _p, _i64, _i, _i, _p, _i64, _p, _i64,
                      _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p], _i),
+    "rdkv_sizeof_pack_job": ([], _i),
+    "rdkv_pack_kv_batched": ([_p, _i, _i, _i, _i, _i, _i, _p], _i),
     "rdkv_knapsack_batched": ([_p, _i64, _i, _i, _p, C.POINTER(_f), C.POINTER(_f), _i, _i, _f, _p, _p, _p], _i),
     "rdkv_knapsack_static_max_rows": ([], _i),
     "rdkv_knapsack_batched_static": ([_p, _i64, _i, _i, _p, C.POINTER(_f), C.POINTER(_f), _i, _i, _f, _p, _p], _i),
@@ -89,6 +115,8 @@ def lib() -> C.CDLL:
             raise RuntimeError("rdkv_b200: library ABI version mismatch; rebuild it")
         if handle.rdkv_sizeof_layer_view() != C.sizeof(LayerView):
             raise RuntimeError("rdkv_b200: rdkv_layer_view layout mismatch between header and binding")
+        if handle.rdkv_sizeof_pack_job() != C.sizeof(PackJob):
+            raise RuntimeError("rdkv_b200: rdkv_pack_job layout mismatch between header and binding")
         _lib = handle
     return _lib
 

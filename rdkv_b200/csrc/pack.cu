@@ -111,16 +111,31 @@ __device__ __forceinline__ uint16_t f2h_bits(float x) { return __half_as_ushort(
 constexpr int PACKV_WARPS = 8;
 constexpr int PACK_MAX_D = 512;
 
-__global__ void __launch_bounds__(PACKV_WARPS * 32)
-pack_v_kernel(const uint16_t* __restrict__ V, int64_t v_head_stride, int64_t v_row_stride, int D,
-              const int32_t* __restrict__ order, int64_t order_row_stride,
-              const int32_t* __restrict__ counts, int64_t counts_row_stride, int n_identity,
-              int identity_bits, int max_n2, int max_n4, int max_n8, int max_n16,
-              uint8_t* out2, uint8_t* out4, uint8_t* out8, uint16_t* out16, uint16_t* out_scale,
-              uint16_t* out_zp, int max_t_v, int qbits_override) {
-  __shared__ float xs[PACKV_WARPS][PACK_MAX_D];
-  __shared__ uint8_t cs[PACKV_WARPS][PACK_MAX_D];
-  const int h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+// Arguments of one V packing pass (one layer).  rows2..rows16 / rows_meta: rows allocated per
+// head in the output tensors (>= max_n*, max_t_v: the outputs may be slices of taller tensors).
+struct PackVArgs {
+  const uint16_t* V; int64_t v_head_stride, v_row_stride; int D;
+  const int32_t* order; int64_t order_row_stride;
+  const int32_t* counts; int64_t counts_row_stride;
+  int n_identity, identity_bits, max_n2, max_n4, max_n8, max_n16;
+  int rows2, rows4, rows8, rows16, rows_meta;
+  uint8_t *out2, *out4, *out8; uint16_t *out16, *out_scale, *out_zp;
+  int max_t_v, qbits_override;
+};
+
+__device__ __forceinline__ void pack_v_body(const PackVArgs& A, int h, int block_x,
+                                            float (*xs)[PACK_MAX_D], uint8_t (*cs)[PACK_MAX_D]) {
+  const uint16_t* __restrict__ V = A.V;
+  const int64_t v_head_stride = A.v_head_stride, v_row_stride = A.v_row_stride, order_row_stride = A.order_row_stride;
+  const int64_t counts_row_stride = A.counts_row_stride;
+  const int D = A.D, n_identity = A.n_identity, identity_bits = A.identity_bits;
+  const int max_n2 = A.max_n2, max_n4 = A.max_n4, max_n8 = A.max_n8, max_n16 = A.max_n16, max_t_v = A.max_t_v;
+  const int qbits_override = A.qbits_override;
+  const int32_t* __restrict__ order = A.order;
+  const int32_t* __restrict__ counts = A.counts;
+  uint8_t *out2 = A.out2, *out4 = A.out4, *out8 = A.out8;
+  uint16_t *out16 = A.out16, *out_scale = A.out_scale, *out_zp = A.out_zp;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int n[4];
   if (order != nullptr) {
     const int32_t* c = counts + h * counts_row_stride;
@@ -133,14 +148,14 @@ pack_v_kernel(const uint16_t* __restrict__ V, int64_t v_head_stride, int64_t v_r
   }
   const int t_v = n[0] + n[1] + n[2];
   // zero the tail of the per-row metadata
-  if (blockIdx.x == 0 && out_scale != nullptr) {
+  if (block_x == 0 && out_scale != nullptr) {
     for (int r = t_v + threadIdx.x; r < max_t_v; r += blockDim.x) {
-      out_scale[(int64_t)h * max_t_v + r] = 0;
-      out_zp[(int64_t)h * max_t_v + r] = 0;
+      out_scale[(int64_t)h * A.rows_meta + r] = 0;
+      out_zp[(int64_t)h * A.rows_meta + r] = 0;
     }
   }
   const int slots = max_n2 + max_n4 + max_n8 + max_n16;
-  const int slot = blockIdx.x * PACKV_WARPS + warp;
+  const int slot = block_x * PACKV_WARPS + warp;
   if (slot >= slots) return;
   int seg, j;
   if (slot < max_n2) { seg = 0; j = slot; }
@@ -151,7 +166,7 @@ pack_v_kernel(const uint16_t* __restrict__ V, int64_t v_head_stride, int64_t v_r
   const bool live = j < n[seg];
   const int width = seg == 0 ? D / 4 : seg == 1 ? D / 2 : D;
   if (seg == 3) {                                   // fp16 rows are copied through
-    uint16_t* dst = out16 + ((int64_t)h * max_n16 + j) * D;
+    uint16_t* dst = out16 + ((int64_t)h * A.rows16 + j) * D;
     if (live) {
       const int src = order != nullptr ? order[h * order_row_stride + base + j] : j;
       const uint16_t* row = V + h * v_head_stride + (int64_t)src * v_row_stride;
@@ -161,9 +176,9 @@ pack_v_kernel(const uint16_t* __restrict__ V, int64_t v_head_stride, int64_t v_r
     }
     return;
   }
-  uint8_t* dst = seg == 0 ? out2 + ((int64_t)h * max_n2 + j) * width
-               : seg == 1 ? out4 + ((int64_t)h * max_n4 + j) * width
-                          : out8 + ((int64_t)h * max_n8 + j) * width;
+  uint8_t* dst = seg == 0 ? out2 + ((int64_t)h * A.rows2 + j) * width
+               : seg == 1 ? out4 + ((int64_t)h * A.rows4 + j) * width
+                          : out8 + ((int64_t)h * A.rows8 + j) * width;
   if (!live) {
     for (int c = lane; c < width; c += 32) dst[c] = 0;
     return;
@@ -192,9 +207,117 @@ pack_v_kernel(const uint16_t* __restrict__ V, int64_t v_head_stride, int64_t v_r
     for (int i = lane; i < D; i += 32) dst[i] = cs[warp][i];
   }
   if (lane == 0) {
-    out_scale[(int64_t)h * max_t_v + base + j] = f2h_bits(qp.scale);
-    out_zp[(int64_t)h * max_t_v + base + j] = f2h_bits(qp.zp);
+    out_scale[(int64_t)h * A.rows_meta + base + j] = f2h_bits(qp.scale);
+    out_zp[(int64_t)h * A.rows_meta + base + j] = f2h_bits(qp.zp);
   }
+}
+
+// D == 128: a warp packs PACKV_ROWS128 slots at once, everything in registers.  Lane l holds
+// channels l, l+32, l+64, l+96 of a row — exactly the four codes of byte l of a quarter-split
+// 2-bit row and the code pairs of bytes l and l+32 of a half-split 4-bit row — so no data moves
+// between lanes; the loads of all rows are in flight together.
+constexpr int PACKV_ROWS128 = 4;
+
+__device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int block_x) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int D = 128;
+  int n[4];
+  {
+    const int32_t* c = A.counts + h * A.counts_row_stride;
+    n[0] = c[0]; n[1] = c[1]; n[2] = c[2]; n[3] = c[3];
+  }
+  const int t_v = n[0] + n[1] + n[2];
+  if (block_x == 0 && A.out_scale != nullptr) {               // zero the tail of the per-row metadata
+    for (int r = t_v + threadIdx.x; r < A.max_t_v; r += blockDim.x) {
+      A.out_scale[(int64_t)h * A.rows_meta + r] = 0;
+      A.out_zp[(int64_t)h * A.rows_meta + r] = 0;
+    }
+  }
+  const int slots = A.max_n2 + A.max_n4 + A.max_n8 + A.max_n16;
+  const int slot0 = (block_x * PACKV_WARPS + warp) * PACKV_ROWS128;
+  if (slot0 >= slots) return;
+  int seg[PACKV_ROWS128], jj[PACKV_ROWS128], base[PACKV_ROWS128];
+  bool live[PACKV_ROWS128];
+  const uint16_t* row[PACKV_ROWS128];
+#pragma unroll
+  for (int k = 0; k < PACKV_ROWS128; ++k) {
+    const int slot = slot0 + k;
+    int sg, j;
+    if (slot < A.max_n2) { sg = 0; j = slot; }
+    else if (slot < A.max_n2 + A.max_n4) { sg = 1; j = slot - A.max_n2; }
+    else if (slot < A.max_n2 + A.max_n4 + A.max_n8) { sg = 2; j = slot - A.max_n2 - A.max_n4; }
+    else { sg = 3; j = slot - A.max_n2 - A.max_n4 - A.max_n8; }
+    seg[k] = slot < slots ? sg : -1; jj[k] = j;
+    base[k] = sg == 0 ? 0 : sg == 1 ? n[0] : sg == 2 ? n[0] + n[1] : t_v;
+    live[k] = slot < slots && j < n[sg];
+    const int src = live[k] ? A.order[h * A.order_row_stride + base[k] + j] : 0;
+    row[k] = A.V + h * A.v_head_stride + (int64_t)src * A.v_row_stride;
+  }
+  uint16_t raw[PACKV_ROWS128][4];
+#pragma unroll
+  for (int k = 0; k < PACKV_ROWS128; ++k)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) raw[k][q] = live[k] ? row[k][lane + 32 * q] : (uint16_t)0;
+#pragma unroll
+  for (int k = 0; k < PACKV_ROWS128; ++k) {
+    if (seg[k] < 0) continue;
+    const int j = jj[k];
+    if (seg[k] == 3) {                                        // fp16 rows are copied through (zeros when dead)
+      uint16_t* dst = A.out16 + ((int64_t)h * A.rows16 + j) * D;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = raw[k][q];
+      continue;
+    }
+    const int width = seg[k] == 0 ? D / 4 : seg[k] == 1 ? D / 2 : D;
+    uint8_t* dst = seg[k] == 0 ? A.out2 + ((int64_t)h * A.rows2 + j) * width
+                 : seg[k] == 1 ? A.out4 + ((int64_t)h * A.rows4 + j) * width
+                               : A.out8 + ((int64_t)h * A.rows8 + j) * width;
+    if (!live[k]) {
+      for (int c = lane; c < width; c += 32) dst[c] = 0;
+      continue;
+    }
+    float x[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) x[q] = h2f(raw[k][q]);
+    const float lo = warp_min(fminf(fminf(x[0], x[1]), fminf(x[2], x[3])));
+    const float hi = warp_max(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])));
+    const int qbits = seg[k] == 0 ? 2 : seg[k] == 1 ? 4 : 8;
+    const QParam qp = make_qparam(lo, hi, (float)((1 << qbits) - 1));
+    unsigned c[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) c[q] = quant_code(x[q], qp);
+    if (seg[k] == 0) {
+      dst[lane] = (uint8_t)(c[0] | (c[1] << 2) | (c[2] << 4) | (c[3] << 6));
+    } else if (seg[k] == 1) {
+      dst[lane] = (uint8_t)(c[0] | (c[2] << 4));
+      dst[lane + 32] = (uint8_t)(c[1] | (c[3] << 4));
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = (uint8_t)c[q];
+    }
+    if (lane == 0) {
+      A.out_scale[(int64_t)h * A.rows_meta + base[k] + j] = f2h_bits(qp.scale);
+      A.out_zp[(int64_t)h * A.rows_meta + base[k] + j] = f2h_bits(qp.zp);
+    }
+  }
+}
+
+__host__ __device__ inline bool pack_v_fast(int D, int qbits_override, const void* order) {
+  return D == 128 && qbits_override == 0 && order != nullptr;
+}
+__host__ __device__ inline int pack_v_blocks(int slots, bool fast) {
+  const int per = PACKV_WARPS * (fast ? PACKV_ROWS128 : 1);
+  return slots > 0 ? (slots + per - 1) / per : 1;
+}
+
+__global__ void __launch_bounds__(PACKV_WARPS * 32)
+pack_v128_kernel(PackVArgs A) { pack_v_body128(A, blockIdx.y, blockIdx.x); }
+
+__global__ void __launch_bounds__(PACKV_WARPS * 32)
+pack_v_kernel(PackVArgs A) {
+  __shared__ float xs[PACKV_WARPS][PACK_MAX_D];
+  __shared__ uint8_t cs[PACKV_WARPS][PACK_MAX_D];
+  pack_v_body(A, blockIdx.y, blockIdx.x, xs, cs);
 }
 
 // ───────────────────────────── K: stripe maps ────────────────────────────────
@@ -250,16 +373,29 @@ __host__ __device__ inline int pack_k_slabs(int t_k) {
   return s < 1 ? 1 : (s > PACKK_MAX_SLABS ? PACKK_MAX_SLABS : s);
 }
 
+// Arguments of one K packing pass (one layer).  rows_k: stripe rows allocated per head in
+// k2/k4/k8 (>= t_k: the outputs may be slices of taller tensors).
+struct PackKArgs {
+  const uint16_t* K; int64_t k_head_stride, k_row_stride;
+  const int32_t* tok_order; int64_t tok_order_rs; const int32_t* tok_counts; int64_t tok_counts_rs;
+  int max_t_v, t_k, rows_k;
+  const int32_t* ch_order; int64_t ch_order_rs; const int32_t* ch_counts; int64_t ch_counts_rs;
+  int n2p, n4p, n8p, d_kept_max, gqa, n_slabs;
+  float* scratch;
+  uint8_t *k2, *k4, *k8; uint16_t *out_scale, *out_zp;
+  int64_t *sort_idx, *perm, *perm_q; int32_t* seg_bounds;
+  int qbits_override;
+};
+
 // Pass 1: per-slab min/max of every channel slot over its stripe rows.
-__global__ void __launch_bounds__(128)
-pack_k_minmax_kernel(const uint16_t* __restrict__ K, int64_t k_head_stride, int64_t k_row_stride,
-                     const int32_t* tok_order, int64_t tok_order_rs, const int32_t* tok_counts,
-                     int64_t tok_counts_rs, int max_t_v, int t_k, const int32_t* ch_order,
-                     int64_t ch_order_rs, const int32_t* ch_counts, int64_t ch_counts_rs, int n2p,
-                     int n4p, int n8p, float* __restrict__ scratch) {
-  const int h = blockIdx.y, slab = blockIdx.x, n_slabs = gridDim.x;
-  const KMaps m = load_maps(h, tok_order, tok_order_rs, tok_counts, tok_counts_rs, max_t_v, t_k,
-                            ch_order, ch_order_rs, ch_counts, ch_counts_rs, n2p, n4p, n8p);
+__device__ __forceinline__ void pack_k_minmax_body(const PackKArgs& A, int h, int slab) {
+  const uint16_t* __restrict__ K = A.K;
+  const int64_t k_head_stride = A.k_head_stride, k_row_stride = A.k_row_stride;
+  const int t_k = A.t_k, n2p = A.n2p, n4p = A.n4p, n8p = A.n8p, n_slabs = A.n_slabs;
+  float* __restrict__ scratch = A.scratch;
+  if (slab >= n_slabs) return;
+  const KMaps m = load_maps(h, A.tok_order, A.tok_order_rs, A.tok_counts, A.tok_counts_rs, A.max_t_v, t_k,
+                            A.ch_order, A.ch_order_rs, A.ch_counts, A.ch_counts_rs, n2p, n4p, n8p);
   const int d_pad = n2p + n4p + n8p;
   const int rows_per = (t_k + n_slabs - 1) / n_slabs;
   const int r0 = min(t_k, slab * rows_per), r1 = min(t_k, r0 + rows_per);
@@ -271,92 +407,195 @@ pack_k_minmax_kernel(const uint16_t* __restrict__ K, int64_t k_head_stride, int6
       const float x = (tok < 0 || ch < 0) ? 0.f : h2f(K[h * k_head_stride + (int64_t)tok * k_row_stride + ch]);
       lo = fminf(lo, x); hi = fmaxf(hi, x);
     }
-    float* dst = scratch + ((int64_t)(h * n_slabs + slab) * 2) * d_pad;
+    float* dst = scratch + ((int64_t)(h * (n_slabs + 1) + slab) * 2) * d_pad;
     dst[p] = lo; dst[d_pad + p] = hi;
   }
 }
 
-// Pass 2: reduce slab extrema, quantise and bit-pack PACKK_ROWS stripe rows per CTA.
+__global__ void __launch_bounds__(128)
+pack_k_minmax_kernel(PackKArgs A) { pack_k_minmax_body(A, blockIdx.y, blockIdx.x); }
+
+// Pass 2 (one CTA per head): reduce the slab extrema to scale / zero point per channel slot
+// (kept in fp32 in the head's last scratch block for pass 3) and write the per-head tables.
+__device__ __forceinline__ void pack_k_params_body(const PackKArgs& A, int h) {
+  const int n2p = A.n2p, n4p = A.n4p, n8p = A.n8p, n_slabs = A.n_slabs, gqa = A.gqa;
+  const int d_pad = n2p + n4p + n8p;
+  const KMaps m = load_maps(h, A.tok_order, A.tok_order_rs, A.tok_counts, A.tok_counts_rs, A.max_t_v, A.t_k,
+                            A.ch_order, A.ch_order_rs, A.ch_counts, A.ch_counts_rs, n2p, n4p, n8p);
+  float* fin = A.scratch + ((int64_t)(h * (n_slabs + 1) + n_slabs) * 2) * d_pad;
+  for (int p = threadIdx.x; p < d_pad; p += blockDim.x) {
+    float lo = INFINITY, hi = -INFINITY;
+    for (int s = 0; s < n_slabs; ++s) {
+      const float* src = A.scratch + ((int64_t)(h * (n_slabs + 1) + s) * 2) * d_pad;
+      lo = fminf(lo, src[p]); hi = fmaxf(hi, src[d_pad + p]);
+    }
+    const int qbits = A.qbits_override > 0 ? A.qbits_override : (p < n2p ? 2 : p < n2p + n4p ? 4 : 8);
+    const QParam qp = make_qparam(lo, hi, (float)((1 << qbits) - 1));
+    fin[p] = qp.scale; fin[d_pad + p] = qp.zp;
+    A.out_scale[(int64_t)h * d_pad + p] = f2h_bits(qp.scale);
+    A.out_zp[(int64_t)h * d_pad + p] = f2h_bits(qp.zp);
+    const int ch = slot_channel(m, p);
+    const int64_t pc = ch < 0 ? 0 : ch;
+    if (A.perm != nullptr) A.perm[(int64_t)h * d_pad + p] = pc;
+    if (A.perm_q != nullptr)
+      for (int i = 0; i < gqa; ++i) A.perm_q[((int64_t)h * gqa + i) * d_pad + p] = pc;
+  }
+  const int kept = m.n2c + m.n4c + m.n8c;
+  if (A.sort_idx != nullptr)
+    for (int j = threadIdx.x; j < A.d_kept_max; j += blockDim.x)
+      A.sort_idx[(int64_t)h * A.d_kept_max + j] = j < kept ? m.ch_order[j] : 0;
+  if (A.seg_bounds != nullptr && threadIdx.x == 0) {
+    A.seg_bounds[h * 3 + 0] = m.n2c; A.seg_bounds[h * 3 + 1] = m.n4c; A.seg_bounds[h * 3 + 2] = m.n8c;
+  }
+}
+
+__global__ void __launch_bounds__(128)
+pack_k_params_kernel(PackKArgs A) { pack_k_params_body(A, blockIdx.x); }
+
+// Pass 3: quantise and bit-pack PACKK_ROWS stripe rows per CTA, four rows per warp at once.  A
+// lane owns output bytes (lane, lane+32, ...) of a row and gathers the 4 / 2 / 1 channel slots
+// that make up each of them, so codes never move between lanes.
 constexpr int PACKK_WARPS = 8;
 constexpr int PACKK_ROWS = 32;
+constexpr int PACKK_RPW = PACKK_ROWS / PACKK_WARPS;          // rows per warp
 
-__global__ void __launch_bounds__(PACKK_WARPS * 32)
-pack_k_quant_kernel(const uint16_t* __restrict__ K, int64_t k_head_stride, int64_t k_row_stride,
-                    const int32_t* tok_order, int64_t tok_order_rs, const int32_t* tok_counts,
-                    int64_t tok_counts_rs, int max_t_v, int t_k, const int32_t* ch_order,
-                    int64_t ch_order_rs, const int32_t* ch_counts, int64_t ch_counts_rs, int n2p,
-                    int n4p, int n8p, int d_kept_max, int gqa, int n_slabs,
-                    const float* __restrict__ scratch, uint8_t* k2, uint8_t* k4, uint8_t* k8,
-                    uint16_t* out_scale, uint16_t* out_zp, int64_t* sort_idx, int64_t* perm,
-                    int64_t* perm_q, int32_t* seg_bounds, int qbits_override) {
-  extern __shared__ unsigned char smem_raw[];
+__device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int block_x, unsigned char* smem_raw) {
+  const uint16_t* __restrict__ K = A.K;
+  const int t_k = A.t_k, n2p = A.n2p, n4p = A.n4p, n8p = A.n8p, n_slabs = A.n_slabs, ov = A.qbits_override;
+  const int64_t rows_k = A.rows_k;
+  if (block_x * PACKK_ROWS >= t_k) return;
   const int d_pad = n2p + n4p + n8p;
   float* s_scale = reinterpret_cast<float*>(smem_raw);          // [d_pad]
   float* s_zp = s_scale + d_pad;                                 // [d_pad]
   int* s_ch = reinterpret_cast<int*>(s_zp + d_pad);             // [d_pad]
-  uint8_t* s_codes = reinterpret_cast<uint8_t*>(s_ch + d_pad);  // [PACKK_WARPS][d_pad]
-  const int h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const KMaps m = load_maps(h, tok_order, tok_order_rs, tok_counts, tok_counts_rs, max_t_v, t_k,
-                            ch_order, ch_order_rs, ch_counts, ch_counts_rs, n2p, n4p, n8p);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const KMaps m = load_maps(h, A.tok_order, A.tok_order_rs, A.tok_counts, A.tok_counts_rs, A.max_t_v, t_k,
+                            A.ch_order, A.ch_order_rs, A.ch_counts, A.ch_counts_rs, n2p, n4p, n8p);
+  const float* fin = A.scratch + ((int64_t)(h * (n_slabs + 1) + n_slabs) * 2) * d_pad;
   for (int p = threadIdx.x; p < d_pad; p += blockDim.x) {
-    float lo = INFINITY, hi = -INFINITY;
-    for (int s = 0; s < n_slabs; ++s) {
-      const float* src = scratch + ((int64_t)(h * n_slabs + s) * 2) * d_pad;
-      lo = fminf(lo, src[p]); hi = fmaxf(hi, src[d_pad + p]);
-    }
-    const int qbits = qbits_override > 0 ? qbits_override : (p < n2p ? 2 : p < n2p + n4p ? 4 : 8);
-    const QParam qp = make_qparam(lo, hi, (float)((1 << qbits) - 1));
-    s_scale[p] = qp.scale; s_zp[p] = qp.zp;
-    const int ch = slot_channel(m, p);
-    s_ch[p] = ch;
-    if (blockIdx.x == 0) {
-      out_scale[(int64_t)h * d_pad + p] = f2h_bits(qp.scale);
-      out_zp[(int64_t)h * d_pad + p] = f2h_bits(qp.zp);
-      const int64_t pc = ch < 0 ? 0 : ch;
-      if (perm != nullptr) perm[(int64_t)h * d_pad + p] = pc;
-      if (perm_q != nullptr)
-        for (int i = 0; i < gqa; ++i) perm_q[((int64_t)h * gqa + i) * d_pad + p] = pc;
-    }
-  }
-  if (blockIdx.x == 0) {
-    const int kept = m.n2c + m.n4c + m.n8c;
-    if (sort_idx != nullptr)
-      for (int j = threadIdx.x; j < d_kept_max; j += blockDim.x)
-        sort_idx[(int64_t)h * d_kept_max + j] = j < kept ? m.ch_order[j] : 0;
-    if (seg_bounds != nullptr && threadIdx.x == 0) {
-      seg_bounds[h * 3 + 0] = m.n2c; seg_bounds[h * 3 + 1] = m.n4c; seg_bounds[h * 3 + 2] = m.n8c;
-    }
+    s_scale[p] = fin[p]; s_zp[p] = fin[d_pad + p]; s_ch[p] = slot_channel(m, p);
   }
   __syncthreads();
   const int sub2 = n2p / 4, sub4 = n4p / 2;
-  uint8_t* codes = s_codes + warp * d_pad;
-  const int row0 = blockIdx.x * PACKK_ROWS;
-  for (int rr = warp; rr < PACKK_ROWS; rr += PACKK_WARPS) {
-    const int s = row0 + rr;
-    if (s >= t_k) break;
-    const int tok = stripe_token(m, s);
-    const uint16_t* row = K + h * k_head_stride + (int64_t)(tok < 0 ? 0 : tok) * k_row_stride;
-    for (int p = lane; p < d_pad; p += 32) {
-      const int ch = s_ch[p];
-      const float x = (tok < 0 || ch < 0) ? 0.f : h2f(row[ch]);
-      QParam qp;
-      qp.scale = s_scale[p]; qp.zp = s_zp[p];
-      qp.qmax = (float)((1 << (qbits_override > 0 ? qbits_override : (p < n2p ? 2 : p < n2p + n4p ? 4 : 8))) - 1);
-      codes[p] = (uint8_t)quant_code(x, qp);
-    }
-    __syncwarp();
-    if (qbits_override > 0) {
-      for (int i = lane; i < d_pad; i += 32) k8[((int64_t)h * t_k + s) * d_pad + i] = codes[i];
-    } else {
-      for (int i = lane; i < sub2; i += 32)
-        k2[((int64_t)h * t_k + s) * sub2 + i] =
-            codes[i] | (codes[i + sub2] << 2) | (codes[i + 2 * sub2] << 4) | (codes[i + 3 * sub2] << 6);
-      for (int i = lane; i < sub4; i += 32)
-        k4[((int64_t)h * t_k + s) * sub4 + i] = codes[n2p + i] | (codes[n2p + i + sub4] << 4);
-      for (int i = lane; i < n8p; i += 32) k8[((int64_t)h * t_k + s) * n8p + i] = codes[n2p + n4p + i];
-    }
-    __syncwarp();
+  const int row_bytes = ov > 0 ? d_pad : sub2 + sub4 + n8p;
+  const int s0 = block_x * PACKK_ROWS + warp * PACKK_RPW;
+  int tok[PACKK_RPW];
+  const uint16_t* row[PACKK_RPW];
+#pragma unroll
+  for (int k = 0; k < PACKK_RPW; ++k) {
+    tok[k] = s0 + k < t_k ? stripe_token(m, s0 + k) : -1;
+    row[k] = K + h * A.k_head_stride + (int64_t)(tok[k] < 0 ? 0 : tok[k]) * A.k_row_stride;
   }
+  for (int b = lane; b < row_bytes; b += 32) {
+    int ns, sl0, step, shift;                                   // slots sl0 + v*step, code v at bit v*shift
+    float qmax;
+    uint8_t* dst; int width, col;
+    if (ov > 0) { ns = 1; sl0 = b; step = 0; shift = 0; qmax = (float)((1 << ov) - 1); dst = A.k8; width = d_pad; col = b; }
+    else if (b < sub2) { ns = 4; sl0 = b; step = sub2; shift = 2; qmax = 3.f; dst = A.k2; width = sub2; col = b; }
+    else if (b < sub2 + sub4) { ns = 2; sl0 = n2p + b - sub2; step = sub4; shift = 4; qmax = 15.f; dst = A.k4; width = sub4; col = b - sub2; }
+    else { ns = 1; sl0 = n2p + n4p + b - sub2 - sub4; step = 0; shift = 0; qmax = 255.f; dst = A.k8; width = n8p; col = b - sub2 - sub4; }
+    int ch[4]; float sc[4], zp[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int sl = sl0 + (v < ns ? v : 0) * step;
+      ch[v] = s_ch[sl]; sc[v] = s_scale[sl]; zp[v] = s_zp[sl];
+    }
+    uint16_t raw[PACKK_RPW][4];
+#pragma unroll
+    for (int k = 0; k < PACKK_RPW; ++k)
+#pragma unroll
+      for (int v = 0; v < 4; ++v) raw[k][v] = (v < ns && tok[k] >= 0 && ch[v] >= 0) ? row[k][ch[v]] : (uint16_t)0;
+#pragma unroll
+    for (int k = 0; k < PACKK_RPW; ++k) {
+      if (s0 + k >= t_k) break;
+      unsigned byte = 0;
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        if (v < ns) {
+          QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
+          byte |= quant_code(h2f(raw[k][v]), qp) << (v * shift);
+        }
+      }
+      dst[((int64_t)h * rows_k + s0 + k) * width + col] = (uint8_t)byte;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(PACKK_WARPS * 32)
+pack_k_quant_kernel(PackKArgs A) {
+  extern __shared__ unsigned char pk_smem[];
+  pack_k_quant_body(A, blockIdx.y, blockIdx.x, pk_smem);
+}
+
+// ───────────────────────────── all layers in one launch ──────────────────────
+// blockIdx.z = layer; the per-layer arguments come from a device array of jobs.
+__device__ __forceinline__ void job_to_vargs(const rdkv_pack_job& J, PackVArgs& A) {
+  A.V = J.V; A.v_head_stride = J.v_head_stride; A.v_row_stride = J.v_row_stride; A.D = J.D;
+  A.order = J.tok_order; A.order_row_stride = J.tok_order_row_stride;
+  A.counts = J.tok_counts; A.counts_row_stride = 4;
+  A.n_identity = 0; A.identity_bits = 0;
+  A.max_n2 = J.max_n2; A.max_n4 = J.max_n4; A.max_n8 = J.max_n8; A.max_n16 = J.max_n16;
+  A.rows2 = J.rows2; A.rows4 = J.rows4; A.rows8 = J.rows8; A.rows16 = J.rows16; A.rows_meta = J.rows_meta;
+  A.out2 = J.v2; A.out4 = J.v4; A.out8 = J.v8; A.out16 = J.v16; A.out_scale = J.v_scale; A.out_zp = J.v_zp;
+  A.max_t_v = J.max_t_v; A.qbits_override = 0;
+}
+
+__global__ void __launch_bounds__(PACKV_WARPS * 32)
+pack_v_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
+  __shared__ float xs[PACKV_WARPS][PACK_MAX_D];
+  __shared__ uint8_t cs[PACKV_WARPS][PACK_MAX_D];
+  __shared__ PackVArgs A;
+  if (threadIdx.x == 0) job_to_vargs(jobs[blockIdx.z], A);
+  __syncthreads();
+  pack_v_body(A, blockIdx.y, blockIdx.x, xs, cs);
+}
+
+__global__ void __launch_bounds__(PACKV_WARPS * 32)
+pack_v128_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
+  __shared__ PackVArgs A;
+  if (threadIdx.x == 0) job_to_vargs(jobs[blockIdx.z], A);
+  __syncthreads();
+  pack_v_body128(A, blockIdx.y, blockIdx.x);
+}
+
+__device__ __forceinline__ void job_to_kargs(const rdkv_pack_job& J, PackKArgs& A) {
+  A.K = J.K; A.k_head_stride = J.k_head_stride; A.k_row_stride = J.k_row_stride;
+  A.tok_order = J.tok_order; A.tok_order_rs = J.tok_order_row_stride; A.tok_counts = J.tok_counts; A.tok_counts_rs = 4;
+  A.max_t_v = J.max_t_v; A.t_k = J.t_k; A.rows_k = J.rows_k;
+  A.ch_order = J.ch_order; A.ch_order_rs = J.ch_order_row_stride; A.ch_counts = J.ch_counts; A.ch_counts_rs = 4;
+  A.n2p = J.n_ch2_pad; A.n4p = J.n_ch4_pad; A.n8p = J.n_ch8; A.d_kept_max = J.d_kept_max; A.gqa = J.gqa;
+  A.n_slabs = pack_k_slabs(J.t_k); A.scratch = J.scratch;
+  A.k2 = J.k2; A.k4 = J.k4; A.k8 = J.k8; A.out_scale = J.k_scale; A.out_zp = J.k_zp;
+  A.sort_idx = J.sort_idx; A.perm = J.perm; A.perm_q = J.perm_q; A.seg_bounds = J.seg_bounds;
+  A.qbits_override = 0;
+}
+
+__global__ void __launch_bounds__(128)
+pack_k_minmax_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
+  __shared__ PackKArgs A;
+  if (threadIdx.x == 0) job_to_kargs(jobs[blockIdx.z], A);
+  __syncthreads();
+  if (A.t_k <= 0 || A.n2p + A.n4p + A.n8p == 0) return;
+  pack_k_minmax_body(A, blockIdx.y, blockIdx.x);
+}
+
+__global__ void __launch_bounds__(128)
+pack_k_params_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
+  __shared__ PackKArgs A;
+  if (threadIdx.x == 0) job_to_kargs(jobs[blockIdx.y], A);
+  __syncthreads();
+  if (A.t_k <= 0 || A.n2p + A.n4p + A.n8p == 0) return;
+  pack_k_params_body(A, blockIdx.x);
+}
+
+__global__ void __launch_bounds__(PACKK_WARPS * 32)
+pack_k_quant_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
+  extern __shared__ unsigned char pk_smem[];
+  __shared__ PackKArgs A;
+  if (threadIdx.x == 0) job_to_kargs(jobs[blockIdx.z], A);
+  __syncthreads();
+  if (A.t_k <= 0 || A.n2p + A.n4p + A.n8p == 0) return;
+  pack_k_quant_body(A, blockIdx.y, blockIdx.x, pk_smem);
 }
 
 }  // namespace rdkv
@@ -389,15 +628,22 @@ extern "C" int rdkv_pack_v(const uint16_t* V, int64_t v_head_stride, int64_t v_r
   if (quant_bits_override < 0 || quant_bits_override > 8) return RDKV_ERR_BAD_ARG;
   const int slots = max_n2 + max_n4 + max_n8 + max_n16;
   if (slots == 0 && max_t_v == 0) return RDKV_OK;
-  dim3 grid(slots > 0 ? (slots + PACKV_WARPS - 1) / PACKV_WARPS : 1, H);
-  pack_v_kernel<<<grid, PACKV_WARPS * 32, 0, (cudaStream_t)stream>>>(
-      V, v_head_stride, v_row_stride, D, order, order_row_stride, counts, counts_row_stride, n_identity,
-      identity_bits, max_n2, max_n4, max_n8, max_n16, out2, out4, out8, out16, out_scale, out_zp,
-      max_t_v, quant_bits_override);
+  const bool fast = pack_v_fast(D, quant_bits_override, order);
+  dim3 grid(pack_v_blocks(slots, fast), H);
+  PackVArgs A;
+  A.V = V; A.v_head_stride = v_head_stride; A.v_row_stride = v_row_stride; A.D = D;
+  A.order = order; A.order_row_stride = order_row_stride; A.counts = counts; A.counts_row_stride = counts_row_stride;
+  A.n_identity = n_identity; A.identity_bits = identity_bits;
+  A.max_n2 = max_n2; A.max_n4 = max_n4; A.max_n8 = max_n8; A.max_n16 = max_n16;
+  A.rows2 = max_n2; A.rows4 = max_n4; A.rows8 = max_n8; A.rows16 = max_n16; A.rows_meta = max_t_v;
+  A.out2 = out2; A.out4 = out4; A.out8 = out8; A.out16 = out16; A.out_scale = out_scale; A.out_zp = out_zp;
+  A.max_t_v = max_t_v; A.qbits_override = quant_bits_override;
+  if (fast) pack_v128_kernel<<<grid, PACKV_WARPS * 32, 0, (cudaStream_t)stream>>>(A);
+  else pack_v_kernel<<<grid, PACKV_WARPS * 32, 0, (cudaStream_t)stream>>>(A);
   return launch_status();
 }
 
-extern "C" int rdkv_pack_k_slabs(int t_k) { return pack_k_slabs(t_k); }
+extern "C" int rdkv_pack_k_slabs(int t_k) { return pack_k_slabs(t_k) + 1; }
 
 extern "C" int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_row_stride, int H, int D,
                            const int32_t* tok_order, int64_t tok_order_row_stride,
@@ -425,17 +671,49 @@ extern "C" int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_r
   if (perm_q != nullptr && gqa <= 0) return RDKV_ERR_BAD_ARG;
   const int n_slabs = pack_k_slabs(t_k);
   cudaStream_t st = (cudaStream_t)stream;
-  pack_k_minmax_kernel<<<dim3(n_slabs, H), 128, 0, st>>>(
-      K, k_head_stride, k_row_stride, tok_order, tok_order_row_stride, tok_counts, tok_counts_row_stride,
-      max_t_v, t_k, ch_order, ch_order_row_stride, ch_counts, ch_counts_row_stride, n_ch2_pad, n_ch4_pad,
-      n_ch8, scratch);
+  PackKArgs A;
+  A.K = K; A.k_head_stride = k_head_stride; A.k_row_stride = k_row_stride;
+  A.tok_order = tok_order; A.tok_order_rs = tok_order_row_stride; A.tok_counts = tok_counts; A.tok_counts_rs = tok_counts_row_stride;
+  A.max_t_v = max_t_v; A.t_k = t_k; A.rows_k = t_k;
+  A.ch_order = ch_order; A.ch_order_rs = ch_order_row_stride; A.ch_counts = ch_counts; A.ch_counts_rs = ch_counts_row_stride;
+  A.n2p = n_ch2_pad; A.n4p = n_ch4_pad; A.n8p = n_ch8; A.d_kept_max = d_kept_max; A.gqa = gqa; A.n_slabs = n_slabs;
+  A.scratch = scratch; A.k2 = k2; A.k4 = k4; A.k8 = k8; A.out_scale = out_scale; A.out_zp = out_zp;
+  A.sort_idx = sort_idx; A.perm = perm; A.perm_q = perm_q; A.seg_bounds = seg_bounds; A.qbits_override = quant_bits_override;
+  pack_k_minmax_kernel<<<dim3(n_slabs, H), 128, 0, st>>>(A);
   int rc = launch_status();
   if (rc != RDKV_OK) return rc;
-  const size_t smem = (size_t)d_pad * (3 * sizeof(float)) + (size_t)PACKK_WARPS * d_pad;
-  pack_k_quant_kernel<<<dim3((t_k + PACKK_ROWS - 1) / PACKK_ROWS, H), PACKK_WARPS * 32, smem, st>>>(
-      K, k_head_stride, k_row_stride, tok_order, tok_order_row_stride, tok_counts, tok_counts_row_stride,
-      max_t_v, t_k, ch_order, ch_order_row_stride, ch_counts, ch_counts_row_stride, n_ch2_pad, n_ch4_pad,
-      n_ch8, d_kept_max, gqa, n_slabs, scratch, k2, k4, k8, out_scale, out_zp, sort_idx, perm, perm_q,
-      seg_bounds, quant_bits_override);
+  pack_k_params_kernel<<<H, 128, 0, st>>>(A);
+  rc = launch_status();
+  if (rc != RDKV_OK) return rc;
+  const size_t smem = (size_t)d_pad * (3 * sizeof(float));
+  pack_k_quant_kernel<<<dim3((t_k + PACKK_ROWS - 1) / PACKK_ROWS, H), PACKK_WARPS * 32, smem, st>>>(A);
+  return launch_status();
+}
+
+extern "C" int rdkv_sizeof_pack_job(void) { return (int)sizeof(rdkv_pack_job); }
+
+extern "C" int rdkv_pack_kv_batched(const rdkv_pack_job* jobs, int n_jobs, int H, int D, int max_slots,
+                                    int max_t_k, int max_d_pad, void* stream) {
+  if (jobs == nullptr || n_jobs < 0 || H <= 0 || D <= 0 || max_slots < 0 || max_t_k < 0 || max_d_pad < 0)
+    return RDKV_ERR_BAD_ARG;
+  if (D > PACK_MAX_D || (D & 3)) return RDKV_ERR_BAD_SHAPE;
+  if (max_d_pad > PACKK_MAX_DPAD) return RDKV_ERR_TOO_LARGE;
+  if (n_jobs == 0) return RDKV_OK;
+  if (n_jobs > 65535 || H > 65535) return RDKV_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool fast = D == 128;
+  dim3 gv(pack_v_blocks(max_slots, fast), H, n_jobs);
+  if (fast) pack_v128_batched_kernel<<<gv, PACKV_WARPS * 32, 0, st>>>(jobs);
+  else pack_v_batched_kernel<<<gv, PACKV_WARPS * 32, 0, st>>>(jobs);
+  int rc = launch_status();
+  if (rc != RDKV_OK || max_t_k == 0 || max_d_pad == 0) return rc;
+  pack_k_minmax_batched_kernel<<<dim3(pack_k_slabs(max_t_k), H, n_jobs), 128, 0, st>>>(jobs);
+  rc = launch_status();
+  if (rc != RDKV_OK) return rc;
+  pack_k_params_batched_kernel<<<dim3(H, n_jobs), 128, 0, st>>>(jobs);
+  rc = launch_status();
+  if (rc != RDKV_OK) return rc;
+  const size_t smem = (size_t)max_d_pad * (3 * sizeof(float));
+  pack_k_quant_batched_kernel<<<dim3((max_t_k + PACKK_ROWS - 1) / PACKK_ROWS, H, n_jobs), PACKK_WARPS * 32, smem, st>>>(jobs);
   return launch_status();
 }

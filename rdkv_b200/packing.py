@@ -388,6 +388,181 @@ def pack_kv(K: Tensor, V: Tensor, v_bits: Tensor, k_bits: Tensor, gqa_factor: in
     return layer, v16
 
 
+class PackedLayerBatch:
+    """Result of :func:`pack_kv_layers`: every layer of a cache packed in one pass.
+
+    The packed bytes of all layers live in a few tall tensors (one per field, leading
+    dimension = layer); ``batch[i]`` / ``batch.layer(i)`` gives layer ``i`` as the
+    ``(PackedKVLayer, new_v_only)`` pair :func:`pack_kv` would have returned, made of
+    views into them (same shapes, same bytes; the views are strided along the head axis
+    when another layer needed more rows).
+    """
+
+    def __init__(self, n_layers: int):
+        self.n_layers = n_layers
+        self._cache: dict = {}
+        self._make = None
+
+    def __len__(self) -> int:
+        return self.n_layers
+
+    def layer(self, i: int) -> Tuple[PackedKVLayer, Optional[Tensor]]:
+        if not 0 <= i < self.n_layers:
+            raise IndexError(i)
+        if i not in self._cache:
+            self._cache[i] = self._make(i)
+        return self._cache[i]
+
+    __getitem__ = layer
+
+    def __iter__(self):
+        return (self.layer(i) for i in range(self.n_layers))
+
+
+def pack_kv_layers(Ks: Sequence[Tensor], Vs: Sequence[Tensor], v_bits: Tensor, k_bits: Tensor, gqa_factor: int, *,
+                   build_mask: bool = True, launch_events: Optional[list] = None) -> PackedLayerBatch:
+    """:func:`pack_kv` for all layers of a cache at once (the reference packs a prefilled
+    cache layer by layer: obkv_accel/packing.py:1323-1421, obkv_fast.py:1098-1166).
+
+    Ks, Vs: per-layer [1,H_kv,T,D] fp16 tensors; v_bits [L,H_kv,T], k_bits [L,H_kv,D] in
+    {0,2,4,8,16}.  Two partition launches, ONE host read of all segment counts, three
+    packing launches whose third grid dimension is the layer.  Layer ``i`` of the result
+    is bit-identical to ``pack_kv(Ks[i], Vs[i], v_bits[i], k_bits[i], gqa_factor)``.
+    Layers whose K bit maps lead to different padded channel widths cannot share tall
+    tensors; they are then packed one by one.  ``launch_events``: a list that receives a
+    (start, end) pair of CUDA events around the three packing launches (for measurements).
+    """
+    import ctypes as C
+    from ._lib import PackJob
+    L = len(Ks)
+    if L == 0 or len(Vs) != L:
+        raise ValueError("pack_kv_layers needs as many V as K tensors, at least one")
+    Ks = [_as_fp16_rows(k, "K") for k in Ks]
+    Vs = [_as_fp16_rows(v, "V") for v in Vs]
+    H, T, D = Ks[0].shape[1], Ks[0].shape[2], Ks[0].shape[3]
+    dev = Ks[0].device
+    if any(tuple(k.shape) != (1, H, T, D) for k in Ks) or any(tuple(v.shape) != (1, H, T, D) for v in Vs):
+        raise ValueError("every layer must have the same [1,H_kv,T,D] shape")
+    if tuple(v_bits.shape) != (L, H, T) or tuple(k_bits.shape) != (L, H, D):
+        raise ValueError(f"v_bits must be [{L},{H},{T}] and k_bits [{L},{H},{D}]")
+    v_bits, k_bits = v_bits.to(dev), k_bits.to(dev)
+    tok_order, tok_counts = partition_by_bits(v_bits.reshape(L * H, T), 0)
+    ch_order, ch_counts = partition_by_bits(k_bits.reshape(L * H, D), 1)
+    host = torch.cat([tok_counts, ch_counts], dim=0).cpu().numpy()          # the one host read
+    tok_h = host[:L * H].reshape(L, H, 4)
+    ch_h = host[L * H:].reshape(L, H, 4)
+    mx = tok_h.max(axis=1)                                                   # [L,4] per-layer segment maxima
+    t_v_h = tok_h[:, :, :3].sum(axis=2)                                      # [L,H]
+    max_t_v = t_v_h.max(axis=1)
+    t_k = max_t_v + mx[:, 3]
+    if int(t_k.min()) == 0:
+        raise RuntimeError("pack_kv_layers: a layer kept zero tokens in every head")
+    cm = ch_h[:, :, :3].max(axis=1)                                          # [L,3]
+    n2p = (cm[:, 0] + 3) // 4 * 4
+    n4p = (cm[:, 1] + 1) // 2 * 2
+    n8p = cm[:, 2]
+    dk = ch_h[:, :, :3].sum(axis=2).max(axis=1)
+    batch = PackedLayerBatch(L)
+    uniform = (n2p == n2p[0]).all() and (n4p == n4p[0]).all() and (n8p == n8p[0]).all() and (dk == dk[0]).all()
+    if not uniform or int(n2p[0] + n4p[0] + n8p[0]) == 0:
+        done = [pack_kv(Ks[i], Vs[i], v_bits[i], k_bits[i], gqa_factor, build_mask=build_mask) for i in range(L)]
+        batch._make = lambda i: done[i]
+        return batch
+    N2P, N4P, N8P, DK = int(n2p[0]), int(n4p[0]), int(n8p[0]), int(dk[0])
+    d_pad = N2P + N4P + N8P
+    R2, R4, R8, R16 = (int(x) for x in mx.max(axis=0))
+    RM, RK = int(max_t_v.max()), int(t_k.max())
+    u8 = dict(dtype=torch.uint8, device=dev)
+    f16 = dict(dtype=torch.float16, device=dev)
+    i64 = dict(dtype=torch.int64, device=dev)
+    V2 = torch.empty((L, H, R2, D // 4), **u8) if R2 else None
+    V4 = torch.empty((L, H, R4, D // 2), **u8) if R4 else None
+    V8 = torch.empty((L, H, R8, D), **u8) if R8 else None
+    V16 = torch.empty((L, H, R16, D), **f16) if R16 else None
+    VS = torch.empty((L, H, max(RM, 1), 1), **f16)
+    VZ = torch.empty_like(VS)
+    K2 = torch.empty((L, H, RK, N2P // 4), **u8) if N2P else None
+    K4 = torch.empty((L, H, RK, N4P // 2), **u8) if N4P else None
+    K8 = torch.empty((L, H, RK, N8P), **u8) if N8P else None
+    KS = torch.empty((L, H, 1, d_pad), **f16)
+    KZ = torch.empty_like(KS)
+    SORT = torch.empty((L, H, DK), **i64)
+    PERM = torch.empty((L, H, d_pad), **i64)
+    PERMQ = torch.empty((L, H * gqa_factor, d_pad), **i64)
+    SEG = torch.empty((L, H, 3), dtype=torch.int32, device=dev)
+    slabs = [lib().rdkv_pack_k_slabs(int(x)) for x in t_k]
+    max_slabs = max(slabs)
+    SCR = torch.empty((L, H * max_slabs * 2 * d_pad), dtype=torch.float32, device=dev)
+
+    def base(t: Optional[Tensor], i: int) -> Optional[int]:
+        return None if t is None else t.data_ptr() + i * t.stride(0) * t.element_size()
+
+    jobs = (PackJob * L)()
+    for i in range(L):
+        J = jobs[i]
+        K, V = Ks[i], Vs[i]
+        J.K, J.V = K.data_ptr(), V.data_ptr()
+        J.k_head_stride, J.k_row_stride, J.v_head_stride, J.v_row_stride = K.stride(1), K.stride(2), V.stride(1), V.stride(2)
+        J.tok_order = tok_order.data_ptr() + i * H * T * 4
+        J.tok_counts = tok_counts.data_ptr() + i * H * 16
+        J.ch_order = ch_order.data_ptr() + i * H * D * 4
+        J.ch_counts = ch_counts.data_ptr() + i * H * 16
+        J.tok_order_row_stride, J.ch_order_row_stride = T, D
+        J.D, J.gqa = D, gqa_factor
+        J.max_n2, J.max_n4, J.max_n8, J.max_n16 = (int(x) for x in mx[i])
+        J.max_t_v, J.t_k = int(max_t_v[i]), int(t_k[i])
+        J.rows2, J.rows4, J.rows8, J.rows16, J.rows_meta, J.rows_k = R2, R4, R8, R16, max(RM, 1), RK
+        J.n_ch2_pad, J.n_ch4_pad, J.n_ch8, J.d_kept_max = N2P, N4P, N8P, DK
+        J.v2, J.v4, J.v8, J.v16 = base(V2, i), base(V4, i), base(V8, i), base(V16, i)
+        J.v_scale, J.v_zp = base(VS, i), base(VZ, i)
+        J.k2, J.k4, J.k8, J.k_scale, J.k_zp = base(K2, i), base(K4, i), base(K8, i), base(KS, i), base(KZ, i)
+        J.sort_idx, J.perm, J.perm_q, J.seg_bounds = base(SORT, i), base(PERM, i), base(PERMQ, i), base(SEG, i)
+        J.scratch = base(SCR, i)
+    jobs_dev = torch.frombuffer(bytearray(bytes(jobs)), dtype=torch.uint8).to(dev)
+    if launch_events is not None:
+        ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        ev[0].record()
+    check(lib().rdkv_pack_kv_batched(jobs_dev.data_ptr(), L, H, D, int(mx.sum(axis=1).max()), RK, d_pad,
+                                     stream_ptr(dev)), "rdkv_pack_kv_batched")
+    if launch_events is not None:
+        ev[1].record()
+        launch_events.append(ev)
+    keep = (jobs_dev, Ks, Vs, SCR)                                           # alive until the kernels have run
+
+    def make(i: int) -> Tuple[PackedKVLayer, Optional[Tensor]]:
+        _ = keep
+        m2, m4, m8, m16 = (int(x) for x in mx[i])
+        tv, tk = int(max_t_v[i]), int(t_k[i])
+
+        def cut(t: Optional[Tensor], rows: int) -> Optional[Tensor]:
+            return None if (t is None or rows == 0) else t[i:i + 1, :, :rows]
+
+        cnt = tok_counts[i * H:(i + 1) * H]
+        t_v = cnt[:, :3].sum(dim=1).to(torch.int32)
+        n16 = cnt[:, 3].contiguous()
+        order_i = tok_order[i * H:(i + 1) * H]
+        h0 = next((h for h in range(H) if int(t_v_h[i, h]) + int(tok_h[i, h, 3]) > 0), 0)
+        is_comp = (v_bits[i, h0] > 0) & (v_bits[i, h0] != 16)
+        rank = torch.cumsum(is_comp.to(torch.int64), 0) - 1
+        sort_idx = rank[order_i[h0, :int(t_v_h[i, h0])].to(torch.int64)]
+        layer = PackedKVLayer(
+            K_2bit=cut(K2, tk), K_4bit=cut(K4, tk), K_8bit=cut(K8, tk), K_ch_scale=KS[i:i + 1], K_ch_zp=KZ[i:i + 1],
+            K_ch_sort_idx=SORT[i, 0], K_ch_seg_bounds=(int(cm[i, 0]), int(cm[i, 1]), int(cm[i, 2])),
+            K_ch_perm_padded_idx=PERM[i, 0],
+            V_2bit=cut(V2, m2), V_4bit=cut(V4, m4), V_8bit=cut(V8, m8), V_scale=VS[i:i + 1, :, :tv], V_zp=VZ[i:i + 1, :, :tv],
+            sort_idx=sort_idx, seg_bounds=(m2, m4, m8), T_eff=tv,
+            seg_bounds_per_head=cnt[:, :3].contiguous(), T_eff_per_head=t_v,
+            softmax_mask=_softmax_mask(t_v, n16, tv, tk, gqa_factor) if build_mask else None,
+            K_ch_sort_idx_per_head=SORT[i], K_ch_perm_padded_idx_per_head=PERM[i],
+            K_ch_seg_bounds_per_head=SEG[i], K_ch_perm_padded_idx_for_Q=PERMQ[i],
+            T_eff_k=tk, n_v16=m16, T_eff_k_per_head=(t_v + n16).to(torch.int32), n_v16_per_head=n16,
+        )
+        return layer, cut(V16, m16)
+
+    batch._make = make
+    return batch
+
+
 def build_packed_layer(K: Tensor, V: Tensor, v_bits: Tensor, k_bits: Tensor, *,
                        gqa_factor: Optional[int] = None,
                        v_segment_counts: Optional[Tuple[int, int, int]] = None,

@@ -132,6 +132,48 @@ def test_config0_layer_matches_oracle():
     assert tuple(packed.K_2bit.shape) == (1, 8, 1024, 6) and tuple(packed.V_4bit.shape) == (1, 8, 384, 64)
 
 
+def test_pack_kv_layers_equals_per_layer_packing():
+    """All layers in one pass: every layer bit-identical to pack_kv on that layer (tall
+    shared tensors, ragged and per-layer different segment counts, strided head views),
+    the decode kernel reads the views, and differing K widths fall back to per-layer packing."""
+    from rdkv_b200 import synth
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention
+    from rdkv_b200.packing import pack_kv, pack_kv_layers
+    H, T, g = 4, 1536, 4
+    Ks, Vs, vbs, kbs = [], [], [], []
+    budgets = [(512, None), (384, [384, 200, 0, 333]), (640, [640, 640, 17, 512]), (64, None)]
+    for i, (N, ragged) in enumerate(budgets):
+        seed = synth.unit_seed(7, i)
+        K, V = synth.make_kv(H, T, seed=seed)
+        Ks.append(K.cuda()); Vs.append(V.cuda())
+        vbs.append(synth.make_v_bits(H, T, N, seed=seed, per_head_N=ragged))
+        kbs.append(synth.make_k_bits(H, seed=seed))
+    v_bits, k_bits = torch.stack(vbs).cuda(), torch.stack(kbs).cuda()
+    batch = pack_kv_layers(Ks, Vs, v_bits, k_bits, g)
+    assert len(batch) == 4
+    singles = [pack_kv(Ks[i], Vs[i], v_bits[i], k_bits[i], g) for i in range(4)]
+    for i, ((pl, nv), (wl, wnv)) in enumerate(zip(batch, singles)):
+        assert_layer_equal(layer_to_np(pl), layer_to_np(wl), f"layer {i}.")
+        for f in ("K_ch_sort_idx", "K_ch_perm_padded_idx", "sort_idx"):
+            assert torch.equal(getattr(pl, f), getattr(wl, f)), f
+        assert (nv is None) == (wnv is None) and (nv is None or torch.equal(nv, wnv))
+    # the fused kernel reads the (strided) views of the batch exactly as it reads single layers
+    q = synth.make_q(H * g, seed=3, batch=4, dtype=torch.float16).cuda()
+    got = packed_decode_attention(q, DecodeTable([b[0] for b in batch], [b[1] for b in batch], H * g))
+    want = packed_decode_attention(q, DecodeTable([b[0] for b in singles], [b[1] for b in singles], H * g))
+    assert torch.equal(got, want)
+    # a layer whose K bit map pads to other widths: per-layer fallback, same results
+    kb2 = k_bits.clone()
+    kb2[1, :, :] = 0
+    kb2[1, :, :40] = 8
+    batch2 = pack_kv_layers(Ks, Vs, v_bits, kb2, g, build_mask=False)
+    for i in range(4):
+        wl, wnv = pack_kv(Ks[i], Vs[i], v_bits[i], kb2[i], g, build_mask=False)
+        assert_layer_equal(layer_to_np(batch2[i][0]), layer_to_np(wl), f"fallback layer {i}.")
+    with pytest.raises(ValueError):
+        pack_kv_layers(Ks, Vs[:3], v_bits, k_bits, g)
+
+
 def test_edge_cases():
     from oracle import ref_packing as RP
     from rdkv_b200 import synth
