@@ -35,7 +35,7 @@ def test_struct_layout_and_version():
     assert b"argument" in lib.rdkv_last_error_string(1)
     assert lib.rdkv_decode_stage_bytes(34) >= 4096 + 64 * 34
     assert lib.rdkv_pack_k_slabs(1) == 2 and lib.rdkv_pack_k_slabs(10 ** 6) <= 65   # slabs + the block of final parameters
-        assert lib.rdkv_sizeof_pack_job() == ctypes.sizeof(_lib.PackJob)
+    assert lib.rdkv_sizeof_pack_job() == ctypes.sizeof(_lib.PackJob)
 
 
 def test_argument_validation_needs_no_gpu():
