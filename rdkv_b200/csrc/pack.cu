@@ -385,6 +385,7 @@ struct PackKArgs {
   uint8_t *k2, *k4, *k8; uint16_t *out_scale, *out_zp;
   int64_t *sort_idx, *perm, *perm_q; int32_t* seg_bounds;
   int qbits_override;
+  int stage_rows;                      // pass 3 reads whole 128-channel rows through shared memory
 };
 
 // Pass 1: per-slab min/max of every channel slot over its stripe rows.
@@ -412,8 +413,72 @@ __device__ __forceinline__ void pack_k_minmax_body(const PackKArgs& A, int h, in
   }
 }
 
+// D == 128: the slab's rows are read whole (one 8-byte load per lane and row, several rows in
+// flight per warp) and the extrema of ALL 128 channels are kept in registers; the kept channels
+// are picked out at the end.  Rows without a token and slots without a channel count as zeros,
+// as on the zero-padded canvas the reference quantises.
+__device__ __forceinline__ void pack_k_minmax_body128(const PackKArgs& A, int h, int slab) {
+  __shared__ float s_lo[4][128], s_hi[4][128];
+  __shared__ int s_pad[4];
+  const int t_k = A.t_k, n_slabs = A.n_slabs;
+  if (slab >= n_slabs) return;
+  const int n2p = A.n2p, n4p = A.n4p, n8p = A.n8p, d_pad = n2p + n4p + n8p;
+  const KMaps m = load_maps(h, A.tok_order, A.tok_order_rs, A.tok_counts, A.tok_counts_rs, A.max_t_v, t_k,
+                            A.ch_order, A.ch_order_rs, A.ch_counts, A.ch_counts_rs, n2p, n4p, n8p);
+  const int rows_per = (t_k + n_slabs - 1) / n_slabs;
+  const int r0 = min(t_k, slab * rows_per), r1 = min(t_k, r0 + rows_per);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float lo[4] = {INFINITY, INFINITY, INFINITY, INFINITY}, hi[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  bool pad = false;
+  const uint16_t* Kh = A.K + h * A.k_head_stride;
+  for (int s = r0 + warp * 4; s < r1; s += 16) {              // 4 warps x 4 rows per round
+    int tok[4];
+    uint2 w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) tok[k] = s + k < r1 ? stripe_token(m, s + k) : -2;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      w[k] = tok[k] >= 0 ? *reinterpret_cast<const uint2*>(Kh + (int64_t)tok[k] * A.k_row_stride + 4 * lane) : make_uint2(0u, 0u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (tok[k] == -2) continue;
+      if (tok[k] < 0) { pad = true; continue; }
+      const float x0 = h2f((uint16_t)(w[k].x & 0xffffu)), x1 = h2f((uint16_t)(w[k].x >> 16));
+      const float x2 = h2f((uint16_t)(w[k].y & 0xffffu)), x3 = h2f((uint16_t)(w[k].y >> 16));
+      lo[0] = fminf(lo[0], x0); hi[0] = fmaxf(hi[0], x0); lo[1] = fminf(lo[1], x1); hi[1] = fmaxf(hi[1], x1);
+      lo[2] = fminf(lo[2], x2); hi[2] = fmaxf(hi[2], x2); lo[3] = fminf(lo[3], x3); hi[3] = fmaxf(hi[3], x3);
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) { s_lo[warp][4 * lane + q] = lo[q]; s_hi[warp][4 * lane + q] = hi[q]; }
+  if (lane == 0) s_pad[warp] = pad ? 1 : 0;
+  __syncthreads();
+  const bool any_pad = (s_pad[0] | s_pad[1] | s_pad[2] | s_pad[3]) != 0;
+  float* dst = A.scratch + ((int64_t)(h * (n_slabs + 1) + slab) * 2) * d_pad;
+  for (int p = threadIdx.x; p < d_pad; p += blockDim.x) {
+    const int ch = slot_channel(m, p);
+    float l = INFINITY, u = -INFINITY;
+    if (r1 > r0) {
+      if (ch < 0) { l = 0.f; u = 0.f; }
+      else {
+        l = fminf(fminf(s_lo[0][ch], s_lo[1][ch]), fminf(s_lo[2][ch], s_lo[3][ch]));
+        u = fmaxf(fmaxf(s_hi[0][ch], s_hi[1][ch]), fmaxf(s_hi[2][ch], s_hi[3][ch]));
+        if (any_pad) { l = fminf(l, 0.f); u = fmaxf(u, 0.f); }
+      }
+    }
+    dst[p] = l; dst[d_pad + p] = u;
+  }
+}
+
+__host__ __device__ inline bool pack_k_fast(int D, int64_t k_row_stride, const void* K) {
+  return D == 128 && (k_row_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(K) & 7) == 0;
+}
+
 __global__ void __launch_bounds__(128)
 pack_k_minmax_kernel(PackKArgs A) { pack_k_minmax_body(A, blockIdx.y, blockIdx.x); }
+
+__global__ void __launch_bounds__(128)
+pack_k_minmax128_kernel(PackKArgs A) { pack_k_minmax_body128(A, blockIdx.y, blockIdx.x); }
 
 // Pass 2 (one CTA per head): reduce the slab extrema to scale / zero point per channel slot
 // (kept in fp32 in the head's last scratch block for pass 3) and write the per-head tables.
@@ -486,6 +551,21 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
     tok[k] = s0 + k < t_k ? stripe_token(m, s0 + k) : -1;
     row[k] = K + h * A.k_head_stride + (int64_t)(tok[k] < 0 ? 0 : tok[k]) * A.k_row_stride;
   }
+  // D == 128: the warp's rows are read whole (one 8-byte load per lane and row, all in flight
+  // together) into shared memory and the channels are gathered from there
+  if (A.stage_rows) {
+    uint16_t* s_rows = reinterpret_cast<uint16_t*>(smem_raw + (((size_t)d_pad * 12 + 15) & ~(size_t)15)) + warp * (PACKK_RPW * 128);
+    uint2 w[PACKK_RPW];
+#pragma unroll
+    for (int k = 0; k < PACKK_RPW; ++k)
+      w[k] = tok[k] >= 0 ? *reinterpret_cast<const uint2*>(row[k] + 4 * lane) : make_uint2(0u, 0u);
+#pragma unroll
+    for (int k = 0; k < PACKK_RPW; ++k) {
+      *reinterpret_cast<uint2*>(s_rows + k * 128 + 4 * lane) = w[k];
+      row[k] = s_rows + k * 128;
+    }
+    __syncwarp();
+  }
   for (int b = lane; b < row_bytes; b += 32) {
     int ns, sl0, step, shift;                                   // slots sl0 + v*step, code v at bit v*shift
     float qmax;
@@ -523,7 +603,7 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
 
 __global__ void __launch_bounds__(PACKK_WARPS * 32)
 pack_k_quant_kernel(PackKArgs A) {
-  extern __shared__ unsigned char pk_smem[];
+  extern __shared__ __align__(16) unsigned char pk_smem[];
   pack_k_quant_body(A, blockIdx.y, blockIdx.x, pk_smem);
 }
 
@@ -568,6 +648,7 @@ __device__ __forceinline__ void job_to_kargs(const rdkv_pack_job& J, PackKArgs& 
   A.k2 = J.k2; A.k4 = J.k4; A.k8 = J.k8; A.out_scale = J.k_scale; A.out_zp = J.k_zp;
   A.sort_idx = J.sort_idx; A.perm = J.perm; A.perm_q = J.perm_q; A.seg_bounds = J.seg_bounds;
   A.qbits_override = 0;
+  A.stage_rows = (pack_k_fast(J.D, J.k_row_stride, J.K) && (J.k_head_stride & 3) == 0) ? 1 : 0;
 }
 
 __global__ void __launch_bounds__(128)
@@ -577,6 +658,18 @@ pack_k_minmax_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
   __syncthreads();
   if (A.t_k <= 0 || A.n2p + A.n4p + A.n8p == 0) return;
   pack_k_minmax_body(A, blockIdx.y, blockIdx.x);
+}
+
+__global__ void __launch_bounds__(128)
+pack_k_minmax128_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
+  __shared__ PackKArgs A;
+  if (threadIdx.x == 0) job_to_kargs(jobs[blockIdx.z], A);
+  __syncthreads();
+  if (A.t_k <= 0 || A.n2p + A.n4p + A.n8p == 0) return;
+  if (pack_k_fast(128, A.k_row_stride, A.K + blockIdx.y * A.k_head_stride) && (A.k_head_stride & 3) == 0)
+    pack_k_minmax_body128(A, blockIdx.y, blockIdx.x);
+  else
+    pack_k_minmax_body(A, blockIdx.y, blockIdx.x);
 }
 
 __global__ void __launch_bounds__(128)
@@ -590,7 +683,7 @@ pack_k_params_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
 
 __global__ void __launch_bounds__(PACKK_WARPS * 32)
 pack_k_quant_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
-  extern __shared__ unsigned char pk_smem[];
+  extern __shared__ __align__(16) unsigned char pk_smem[];
   __shared__ PackKArgs A;
   if (threadIdx.x == 0) job_to_kargs(jobs[blockIdx.z], A);
   __syncthreads();
@@ -679,13 +772,17 @@ extern "C" int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_r
   A.n2p = n_ch2_pad; A.n4p = n_ch4_pad; A.n8p = n_ch8; A.d_kept_max = d_kept_max; A.gqa = gqa; A.n_slabs = n_slabs;
   A.scratch = scratch; A.k2 = k2; A.k4 = k4; A.k8 = k8; A.out_scale = out_scale; A.out_zp = out_zp;
   A.sort_idx = sort_idx; A.perm = perm; A.perm_q = perm_q; A.seg_bounds = seg_bounds; A.qbits_override = quant_bits_override;
-  pack_k_minmax_kernel<<<dim3(n_slabs, H), 128, 0, st>>>(A);
+  A.stage_rows = (pack_k_fast(D, k_row_stride, K) && (k_head_stride & 3) == 0) ? 1 : 0;
+  if (pack_k_fast(D, k_row_stride, K) && (k_head_stride & 3) == 0)
+    pack_k_minmax128_kernel<<<dim3(n_slabs, H), 128, 0, st>>>(A);
+  else
+    pack_k_minmax_kernel<<<dim3(n_slabs, H), 128, 0, st>>>(A);
   int rc = launch_status();
   if (rc != RDKV_OK) return rc;
   pack_k_params_kernel<<<H, 128, 0, st>>>(A);
   rc = launch_status();
   if (rc != RDKV_OK) return rc;
-  const size_t smem = (size_t)d_pad * (3 * sizeof(float));
+  const size_t smem = (size_t)d_pad * (3 * sizeof(float)) + (A.stage_rows ? 16 + PACKK_ROWS * 128 * sizeof(uint16_t) : 0);
   pack_k_quant_kernel<<<dim3((t_k + PACKK_ROWS - 1) / PACKK_ROWS, H), PACKK_WARPS * 32, smem, st>>>(A);
   return launch_status();
 }
@@ -707,13 +804,14 @@ extern "C" int rdkv_pack_kv_batched(const rdkv_pack_job* jobs, int n_jobs, int H
   else pack_v_batched_kernel<<<gv, PACKV_WARPS * 32, 0, st>>>(jobs);
   int rc = launch_status();
   if (rc != RDKV_OK || max_t_k == 0 || max_d_pad == 0) return rc;
-  pack_k_minmax_batched_kernel<<<dim3(pack_k_slabs(max_t_k), H, n_jobs), 128, 0, st>>>(jobs);
+  if (D == 128) pack_k_minmax128_batched_kernel<<<dim3(pack_k_slabs(max_t_k), H, n_jobs), 128, 0, st>>>(jobs);
+  else pack_k_minmax_batched_kernel<<<dim3(pack_k_slabs(max_t_k), H, n_jobs), 128, 0, st>>>(jobs);
   rc = launch_status();
   if (rc != RDKV_OK) return rc;
   pack_k_params_batched_kernel<<<dim3(H, n_jobs), 128, 0, st>>>(jobs);
   rc = launch_status();
   if (rc != RDKV_OK) return rc;
-  const size_t smem = (size_t)max_d_pad * (3 * sizeof(float));
+  const size_t smem = (size_t)max_d_pad * (3 * sizeof(float)) + (D == 128 ? 16 + PACKK_ROWS * 128 * sizeof(uint16_t) : 0);
   pack_k_quant_batched_kernel<<<dim3((max_t_k + PACKK_ROWS - 1) / PACKK_ROWS, H, n_jobs), PACKK_WARPS * 32, smem, st>>>(jobs);
   return launch_status();
 }

@@ -494,30 +494,32 @@ def pack_kv_layers(Ks: Sequence[Tensor], Vs: Sequence[Tensor], v_bits: Tensor, k
     max_slabs = max(slabs)
     SCR = torch.empty((L, H * max_slabs * 2 * d_pad), dtype=torch.float32, device=dev)
 
-    def base(t: Optional[Tensor], i: int) -> Optional[int]:
-        return None if t is None else t.data_ptr() + i * t.stride(0) * t.element_size()
+    # base address and per-layer byte stride of every tall tensor, read once
+    def span(t: Optional[Tensor]):
+        return (0, 0) if t is None else (t.data_ptr(), t.stride(0) * t.element_size())
 
+    outs = {"v2": span(V2), "v4": span(V4), "v8": span(V8), "v16": span(V16), "v_scale": span(VS), "v_zp": span(VZ),
+            "k2": span(K2), "k4": span(K4), "k8": span(K8), "k_scale": span(KS), "k_zp": span(KZ),
+            "sort_idx": span(SORT), "perm": span(PERM), "perm_q": span(PERMQ), "seg_bounds": span(SEG),
+            "scratch": span(SCR)}
+    to_p, tc_p, co_p, cc_p = tok_order.data_ptr(), tok_counts.data_ptr(), ch_order.data_ptr(), ch_counts.data_ptr()
+    mx_l, tv_l, tk_l = mx.tolist(), max_t_v.tolist(), t_k.tolist()
     jobs = (PackJob * L)()
     for i in range(L):
         J = jobs[i]
         K, V = Ks[i], Vs[i]
         J.K, J.V = K.data_ptr(), V.data_ptr()
         J.k_head_stride, J.k_row_stride, J.v_head_stride, J.v_row_stride = K.stride(1), K.stride(2), V.stride(1), V.stride(2)
-        J.tok_order = tok_order.data_ptr() + i * H * T * 4
-        J.tok_counts = tok_counts.data_ptr() + i * H * 16
-        J.ch_order = ch_order.data_ptr() + i * H * D * 4
-        J.ch_counts = ch_counts.data_ptr() + i * H * 16
+        J.tok_order, J.tok_counts = to_p + i * H * T * 4, tc_p + i * H * 16
+        J.ch_order, J.ch_counts = co_p + i * H * D * 4, cc_p + i * H * 16
         J.tok_order_row_stride, J.ch_order_row_stride = T, D
         J.D, J.gqa = D, gqa_factor
-        J.max_n2, J.max_n4, J.max_n8, J.max_n16 = (int(x) for x in mx[i])
-        J.max_t_v, J.t_k = int(max_t_v[i]), int(t_k[i])
+        J.max_n2, J.max_n4, J.max_n8, J.max_n16 = mx_l[i]
+        J.max_t_v, J.t_k = tv_l[i], tk_l[i]
         J.rows2, J.rows4, J.rows8, J.rows16, J.rows_meta, J.rows_k = R2, R4, R8, R16, max(RM, 1), RK
         J.n_ch2_pad, J.n_ch4_pad, J.n_ch8, J.d_kept_max = N2P, N4P, N8P, DK
-        J.v2, J.v4, J.v8, J.v16 = base(V2, i), base(V4, i), base(V8, i), base(V16, i)
-        J.v_scale, J.v_zp = base(VS, i), base(VZ, i)
-        J.k2, J.k4, J.k8, J.k_scale, J.k_zp = base(K2, i), base(K4, i), base(K8, i), base(KS, i), base(KZ, i)
-        J.sort_idx, J.perm, J.perm_q, J.seg_bounds = base(SORT, i), base(PERM, i), base(PERMQ, i), base(SEG, i)
-        J.scratch = base(SCR, i)
+        for name, (p0, step) in outs.items():
+            setattr(J, name, (p0 + i * step) if p0 else None)
     jobs_dev = torch.frombuffer(bytearray(bytes(jobs)), dtype=torch.uint8).to(dev)
     if launch_events is not None:
         ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
