@@ -216,7 +216,8 @@ __device__ __forceinline__ void pack_v_body(const PackVArgs& A, int h, int block
 // channels l, l+32, l+64, l+96 of a row — exactly the four codes of byte l of a quarter-split
 // 2-bit row and the code pairs of bytes l and l+32 of a half-split 4-bit row — so no data moves
 // between lanes; the loads of all rows are in flight together.
-constexpr int PACKV_ROWS128 = 4;
+constexpr int PACKV_ROWS128 = 4;                             // rows in flight per warp
+constexpr int PACKV_ROUNDS128 = 4;                           // rounds per warp: a CTA packs 8 x 4 x 4 = 128 slots
 
 __device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int block_x) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -234,7 +235,9 @@ __device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int bl
     }
   }
   const int slots = A.max_n2 + A.max_n4 + A.max_n8 + A.max_n16;
-  const int slot0 = (block_x * PACKV_WARPS + warp) * PACKV_ROWS128;
+#pragma unroll 1
+  for (int round = 0; round < PACKV_ROUNDS128; ++round) {
+  const int slot0 = ((block_x * PACKV_ROUNDS128 + round) * PACKV_WARPS + warp) * PACKV_ROWS128;
   if (slot0 >= slots) return;
   int seg[PACKV_ROWS128], jj[PACKV_ROWS128], base[PACKV_ROWS128];
   bool live[PACKV_ROWS128];
@@ -300,13 +303,14 @@ __device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int bl
       A.out_zp[(int64_t)h * A.rows_meta + base[k] + j] = f2h_bits(qp.zp);
     }
   }
+  }
 }
 
 __host__ __device__ inline bool pack_v_fast(int D, int qbits_override, const void* order) {
   return D == 128 && qbits_override == 0 && order != nullptr;
 }
 __host__ __device__ inline int pack_v_blocks(int slots, bool fast) {
-  const int per = PACKV_WARPS * (fast ? PACKV_ROWS128 : 1);
+  const int per = PACKV_WARPS * (fast ? PACKV_ROWS128 * PACKV_ROUNDS128 : 1);
   return slots > 0 ? (slots + per - 1) / per : 1;
 }
 
@@ -521,8 +525,9 @@ pack_k_params_kernel(PackKArgs A) { pack_k_params_body(A, blockIdx.x); }
 // lane owns output bytes (lane, lane+32, ...) of a row and gathers the 4 / 2 / 1 channel slots
 // that make up each of them, so codes never move between lanes.
 constexpr int PACKK_WARPS = 8;
-constexpr int PACKK_ROWS = 32;
-constexpr int PACKK_RPW = PACKK_ROWS / PACKK_WARPS;          // rows per warp
+constexpr int PACKK_RPW = 4;                                 // rows in flight per warp
+constexpr int PACKK_ROUNDS = 4;                              // rounds per warp
+constexpr int PACKK_ROWS = PACKK_WARPS * PACKK_RPW * PACKK_ROUNDS;   // stripe rows per CTA
 
 __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int block_x, unsigned char* smem_raw) {
   const uint16_t* __restrict__ K = A.K;
@@ -543,7 +548,10 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
   __syncthreads();
   const int sub2 = n2p / 4, sub4 = n4p / 2;
   const int row_bytes = ov > 0 ? d_pad : sub2 + sub4 + n8p;
-  const int s0 = block_x * PACKK_ROWS + warp * PACKK_RPW;
+#pragma unroll 1
+  for (int round = 0; round < PACKK_ROUNDS; ++round) {
+  const int s0 = block_x * PACKK_ROWS + (round * PACKK_WARPS + warp) * PACKK_RPW;
+  if (s0 >= t_k) break;
   int tok[PACKK_RPW];
   const uint16_t* row[PACKK_RPW];
 #pragma unroll
@@ -598,6 +606,8 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
       }
       dst[((int64_t)h * rows_k + s0 + k) * width + col] = (uint8_t)byte;
     }
+  }
+  __syncwarp();                                              // the staged rows are overwritten in the next round
   }
 }
 
@@ -782,7 +792,7 @@ extern "C" int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_r
   pack_k_params_kernel<<<H, 128, 0, st>>>(A);
   rc = launch_status();
   if (rc != RDKV_OK) return rc;
-  const size_t smem = (size_t)d_pad * (3 * sizeof(float)) + (A.stage_rows ? 16 + PACKK_ROWS * 128 * sizeof(uint16_t) : 0);
+  const size_t smem = (size_t)d_pad * (3 * sizeof(float)) + (A.stage_rows ? 16 + PACKK_WARPS * PACKK_RPW * 128 * sizeof(uint16_t) : 0);
   pack_k_quant_kernel<<<dim3((t_k + PACKK_ROWS - 1) / PACKK_ROWS, H), PACKK_WARPS * 32, smem, st>>>(A);
   return launch_status();
 }
@@ -811,7 +821,7 @@ extern "C" int rdkv_pack_kv_batched(const rdkv_pack_job* jobs, int n_jobs, int H
   pack_k_params_batched_kernel<<<dim3(H, n_jobs), 128, 0, st>>>(jobs);
   rc = launch_status();
   if (rc != RDKV_OK) return rc;
-  const size_t smem = (size_t)max_d_pad * (3 * sizeof(float)) + (D == 128 ? 16 + PACKK_ROWS * 128 * sizeof(uint16_t) : 0);
+  const size_t smem = (size_t)max_d_pad * (3 * sizeof(float)) + (D == 128 ? 16 + PACKK_WARPS * PACKK_RPW * 128 * sizeof(uint16_t) : 0);
   pack_k_quant_batched_kernel<<<dim3((max_t_k + PACKK_ROWS - 1) / PACKK_ROWS, H, n_jobs), PACKK_WARPS * 32, smem, st>>>(jobs);
   return launch_status();
 }
