@@ -213,6 +213,20 @@ int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_row_stride, 
                 int64_t* sort_idx, int64_t* perm, int64_t* perm_q, int32_t* seg_bounds,
                 int quant_bits_override, void* stream);
 
+/* ── decode: the uncompressed tail (Zone C) ───────────────────────────────────
+ * Tokens appended during decoding stay as plain K / V rows (the reference's
+ * new-token buffer, obkv_accel/fast_decode.py:863-866; its scores and weighted
+ * sum, :1719-1784: softmax over [packed zones || tail]).  Writes one
+ * (m, l, -, -, o[128]) record per (view, query head), m in natural-log units,
+ * for rdkv_lse_combine to merge with the record of the packed zones.
+ * new_k / new_v: [n_views][H_kv][cap][128] fp16, bf16 or fp32 with the given
+ * element strides (rows 16- resp. 8-byte aligned); the first n_new rows of every
+ * head are live, or n_new_per_view[view] rows when that device array is given. */
+int rdkv_tail_attn_partial(const void* q, int q_dtype, int64_t n_views, int H_q, int H_kv,
+                           const void* new_k, const void* new_v, int kv_dtype,
+                           int64_t kv_view_stride, int64_t kv_head_stride, int64_t kv_row_stride,
+                           int n_new, const int32_t* n_new_per_view, float* partial, void* stream);
+
 /* ── prefill: every layer of a cache in one pass ──────────────────────────────
  * The reference packs a whole cache layer by layer (build_packed_cache,
  * obkv_accel/packing.py:1323-1421; driver loop obkv_fast.py:1098-1166); here the

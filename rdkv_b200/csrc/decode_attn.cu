@@ -230,6 +230,60 @@ lse_combine_kernel(const float* __restrict__ partials, int n_splits, int64_t row
   }
 }
 
+// ───────────────────────────── Zone C: uncompressed tail ─────────────────────
+// Decode-appended tokens kept as plain K / V rows (reference: the new-token buffer of
+// obkv_accel/fast_decode.py:863-866 and its scores / weighted sum, :1719-1784).  One warp per
+// query head walks the tail with an online softmax and writes an (m, l, o[128]) record that
+// the log-sum-exp combine merges with the packed zones' record: one softmax over all zones.
+constexpr int TAIL_WARPS = 4;
+
+__device__ __forceinline__ float4 load_row4(const void* base, int dtype, int64_t elem_off) {
+  if (dtype == RDKV_F32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + elem_off);
+  const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + elem_off);
+  if (dtype == RDKV_F16) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+__global__ void __launch_bounds__(TAIL_WARPS * 32)
+tail_attn_partial_kernel(const void* __restrict__ q, int q_dtype, int64_t n_rows, int H_q, int g,
+                         const void* __restrict__ new_k, const void* __restrict__ new_v, int kv_dtype,
+                         int64_t kv_view_stride, int64_t kv_head_stride, int64_t kv_row_stride, int n_new,
+                         const int32_t* __restrict__ n_new_per_view, float* __restrict__ partial) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * TAIL_WARPS + warp;    // (view, query head)
+  if (row >= n_rows) return;
+  const int64_t view = row / H_q;
+  const int hq = (int)(row % H_q), h = hq / g;
+  const int n = n_new_per_view != nullptr ? n_new_per_view[view] : n_new;
+  float4 qv;
+  qv.x = load_q(q, q_dtype, row * D + 4 * lane) * INV_SQRT_D; qv.y = load_q(q, q_dtype, row * D + 4 * lane + 1) * INV_SQRT_D;
+  qv.z = load_q(q, q_dtype, row * D + 4 * lane + 2) * INV_SQRT_D; qv.w = load_q(q, q_dtype, row * D + 4 * lane + 3) * INV_SQRT_D;
+  const int64_t base = view * kv_view_stride + h * kv_head_stride + 4 * lane;
+  float m = -INFINITY, l = 0.f;
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int t = 0; t < n; ++t) {
+    const float4 k = load_row4(new_k, kv_dtype, base + t * kv_row_stride);
+    const float4 vv = load_row4(new_v, kv_dtype, base + t * kv_row_stride);
+    float sdot = warp_sum(qv.x * k.x + qv.y * k.y + qv.z * k.z + qv.w * k.w);
+    sdot = __shfl_sync(0xffffffffu, sdot, 0);               // the same value in every lane
+    const float mn = fmaxf(m, sdot);
+    const float a = m == -INFINITY ? 0.f : __expf(m - mn), pw = __expf(sdot - mn);
+    l = fmaf(l, a, pw);
+    o.x = fmaf(o.x, a, pw * vv.x); o.y = fmaf(o.y, a, pw * vv.y);
+    o.z = fmaf(o.z, a, pw * vv.z); o.w = fmaf(o.w, a, pw * vv.w);
+    m = mn;
+  }
+  float* rec = partial + row * RDKV_PARTIAL_STRIDE;
+  *reinterpret_cast<float4*>(rec + 4 + 4 * lane) = o;
+  if (lane == 0) { rec[0] = m; rec[1] = l; rec[2] = 0.f; rec[3] = 0.f; }
+}
+
 static int check_view_dims(int H_q, int H_kv) {
   if (H_q <= 0 || H_kv <= 0) return RDKV_ERR_BAD_ARG;
   if (H_q % H_kv != 0 || H_q / H_kv > MAX_GROUP) return RDKV_ERR_BAD_SHAPE;
@@ -290,5 +344,29 @@ extern "C" int rdkv_lse_combine(const float* partials, int64_t n_rows, int n_spl
   lse_combine_kernel<<<(unsigned)n_rows, D, 0, (cudaStream_t)stream>>>(partials, n_splits, row_stride,
                                                                       split_stride, out, out_ml,
                                                                       out_partial);
+  return launch_status();
+}
+
+extern "C" int rdkv_tail_attn_partial(const void* q, int q_dtype, int64_t n_views, int H_q, int H_kv,
+                                      const void* new_k, const void* new_v, int kv_dtype,
+                                      int64_t kv_view_stride, int64_t kv_head_stride, int64_t kv_row_stride,
+                                      int n_new, const int32_t* n_new_per_view, float* partial, void* stream) {
+  if (q == nullptr || new_k == nullptr || new_v == nullptr || partial == nullptr || n_views < 0 || n_new < 0)
+    return RDKV_ERR_BAD_ARG;
+  if (q_dtype < RDKV_F16 || q_dtype > RDKV_F32 || kv_dtype < RDKV_F16 || kv_dtype > RDKV_F32) return RDKV_ERR_BAD_ARG;
+  if (H_q <= 0 || H_kv <= 0 || H_q % H_kv != 0) return RDKV_ERR_BAD_SHAPE;
+  const int align = kv_dtype == RDKV_F32 ? 4 : 4;            // rows are read 4 elements per lane
+  if ((kv_view_stride % align) || (kv_head_stride % align) || (kv_row_stride % align)) return RDKV_ERR_BAD_SHAPE;
+  const size_t bytes = kv_dtype == RDKV_F32 ? 16 : 8;
+  if ((reinterpret_cast<uintptr_t>(new_k) % bytes) || (reinterpret_cast<uintptr_t>(new_v) % bytes) ||
+      (reinterpret_cast<uintptr_t>(partial) % 16))
+    return RDKV_ERR_BAD_ARG;
+  const int64_t n_rows = n_views * H_q;
+  if (n_rows == 0) return RDKV_OK;
+  const int64_t blocks = (n_rows + TAIL_WARPS - 1) / TAIL_WARPS;
+  if (blocks > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
+  tail_attn_partial_kernel<<<(unsigned)blocks, TAIL_WARPS * 32, 0, (cudaStream_t)stream>>>(
+      q, q_dtype, n_rows, H_q, H_q / H_kv, new_k, new_v, kv_dtype, kv_view_stride, kv_head_stride, kv_row_stride,
+      n_new, n_new_per_view, partial);
   return launch_status();
 }

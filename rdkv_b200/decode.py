@@ -153,17 +153,80 @@ def decode_attention_partial(q: Tensor, table: DecodeTable, out: Optional[Tensor
     return part
 
 
+def tail_attention_partial(q: Tensor, new_k: Tensor, new_v: Tensor, n_new, H_kv: int,
+                           out_partial: Optional[Tensor] = None) -> Tensor:
+    """(m, l, o) records of plain attention over the uncompressed tail (Zone C: tokens
+    appended while decoding; reference obkv_accel/fast_decode.py:863-866, 1719-1784).
+
+    q [n_views,H_q,128]; new_k, new_v [n_views,H_kv,cap,128] fp16/bf16/fp32 (same dtype and
+    strides); n_new: live rows per head, an int or an int32 device tensor [n_views].
+    Returns [n_views*H_q, 132] fp32 records for :func:`lse_combine`.
+    """
+    require_cuda(q, "q"); require_cuda(new_k, "new_k"); require_cuda(new_v, "new_v")
+    if q.dim() != 3 or q.shape[-1] != HEAD_DIM:
+        raise ValueError("q must be [n_views,H_q,128]")
+    n_views, H_q = int(q.shape[0]), int(q.shape[1])
+    if new_k.dim() != 4 or tuple(new_k.shape[:2]) != (n_views, H_kv) or new_k.shape[-1] != HEAD_DIM:
+        raise ValueError(f"new_k must be [{n_views},{H_kv},cap,{HEAD_DIM}], got {tuple(new_k.shape)}")
+    if new_v.shape != new_k.shape or new_v.dtype != new_k.dtype or new_v.stride() != new_k.stride():
+        raise ValueError("new_v must match new_k in shape, dtype and strides")
+    if new_k.stride(-1) != 1:
+        raise ValueError("tail rows must be contiguous along the channel axis")
+    if not q.is_contiguous():
+        q = q.contiguous()
+    cap = int(new_k.shape[2])
+    per_view = None
+    if isinstance(n_new, Tensor):
+        require_cuda(n_new, "n_new")
+        if n_new.dtype != torch.int32 or n_new.numel() != n_views or not n_new.is_contiguous():
+            raise ValueError("n_new tensor must be contiguous int32 [n_views]")
+        per_view, n_int = n_new, 0
+    else:
+        n_int = int(n_new)
+        if not 0 <= n_int <= cap:
+            raise ValueError(f"n_new={n_int} outside [0, {cap}]")
+    if out_partial is None:
+        out_partial = torch.empty((n_views * H_q, PARTIAL_STRIDE), dtype=torch.float32, device=q.device)
+    check(lib().rdkv_tail_attn_partial(ptr(q), q_dtype_tag(q), n_views, H_q, H_kv, ptr(new_k), ptr(new_v),
+                                       q_dtype_tag(new_k), new_k.stride(0), new_k.stride(1), new_k.stride(2),
+                                       n_int, ptr(per_view), ptr(out_partial), stream_ptr(q.device)),
+          "rdkv_tail_attn_partial")
+    return out_partial
+
+
 def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tensor] = None,
-                            out_partial: Optional[Tensor] = None) -> Tensor:
+                            out_partial: Optional[Tensor] = None, new_k: Optional[Tensor] = None,
+                            new_v: Optional[Tensor] = None, n_new=0) -> Tensor:
     """softmax(q·K̂ᵀ/√128)·V̂ over every view of ``table``.
 
     q [n_views,H_q,128] fp16/bf16/fp32 -> out [n_views,H_q,128] fp32.  With
     ``out_partial`` ([n_views*H_q,132] fp32) the merged un-normalised (m, l, o)
     record per query head is written instead, for a later combine across
-    sequence shards.  One launch when a single chunk covers every head, else the
+    sequence shards.  ``new_k`` / ``new_v`` [n_views,H_kv,cap,128] with ``n_new`` live
+    rows add the uncompressed tail of decode-appended tokens (Zone C) to the same
+    softmax, as the reference's attention block does (fast_decode.py:1719-1784).
+    One launch when a single chunk covers every head and there is no tail, else the
     fused kernel plus the combine; no allocation after the first call, no host
     synchronisation.
     """
+    if new_k is not None:
+        if new_v is None:
+            raise ValueError("new_k needs new_v")
+        n_rows = table.n_views * table.H_q
+        ws = getattr(table, "_tail_ws", None)
+        if ws is None:
+            ws = torch.empty((2, n_rows, PARTIAL_STRIDE), dtype=torch.float32, device=table.device)
+            table._tail_ws = ws
+        packed_decode_attention(q, table, out_partial=ws[0])          # packed zones: merged record
+        tail_attention_partial(q.reshape(table.n_views, table.H_q, HEAD_DIM), new_k, new_v, n_new, table.H_kv, ws[1])
+        both = ws.permute(1, 0, 2)                                       # [n_rows, 2, 132]
+        if out_partial is not None:
+            lse_combine(both, None, out_partial=out_partial)
+            return out_partial
+        if out is None:
+            out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
+        lse_combine(both, out.view(-1, HEAD_DIM))
+        return out
     if out_partial is not None:
         if table.n_chunks == 1:
             _launch_fused(q, table, out_partial, None)

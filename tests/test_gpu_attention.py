@@ -108,6 +108,56 @@ def test_fused_batch_of_views_and_partials():
     assert_attn_close(to_np(again).reshape(len(shapes), H_kv * g, 128)[0], wants[0][0], "combine identity")
 
 
+@pytest.mark.parametrize("kv_dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_uncompressed_tail_joins_the_softmax(kv_dtype):
+    """Zone C (decode-appended fp rows) is part of the same softmax as the packed zones:
+    several views with different tail lengths (per-view count tensor and shared int),
+    single-chunk and split-sequence tables, against the oracle."""
+    from oracle import ref_attention as RA
+    from oracle import ref_packing as RP
+    from rdkv_b200 import synth
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention, tail_attention_partial
+    from rdkv_b200.packing import pack_kv
+    H_kv, g, cap = 4, 4, 40
+    shapes = [(1024, 384, None), (640, 256, [256, 100, 7, 200]), (512, 128, None)]
+    tails = [33, 0, 40]
+    qs = synth.make_q(H_kv * g, seed=21, batch=len(shapes), dtype=torch.float16)
+    gen = torch.Generator().manual_seed(77)
+    new_k = torch.randn(len(shapes), H_kv, cap, 128, generator=gen).to(kv_dtype)
+    new_v = torch.randn(len(shapes), H_kv, cap, 128, generator=gen).to(kv_dtype)
+    layers, nvs, wants, ols = [], [], [], []
+    for i, (T, N, ragged) in enumerate(shapes):
+        seed = synth.unit_seed(3, i, 9)
+        K, V = synth.make_kv(H_kv, T, seed=seed)
+        vb = synth.make_v_bits(H_kv, T, N, seed=seed, per_head_N=ragged)
+        kb = synth.make_k_bits(H_kv, seed=seed)
+        pl, nv = pack_kv(K.cuda(), V.cuda(), vb.cuda(), kb.cuda(), g)
+        layers.append(pl); nvs.append(nv)
+        ol, onv = RP.pack_kv(K.numpy(), V.numpy(), vb.numpy(), kb.numpy(), g)
+        ols.append((ol, onv))
+        wants.append(RA.decode_attention(qs[i].float().numpy(), ol, onv,
+                                         new_k[i, :, :tails[i]].float().numpy(), new_v[i, :, :tails[i]].float().numpy())[0])
+    n_dev = torch.tensor(tails, dtype=torch.int32, device="cuda")
+    for n_chunks in (1, 3):
+        table = DecodeTable(layers, nvs, H_kv * g)
+        table.n_chunks, table.chunk_rows = n_chunks, 64 * (-(-table.max_t_k // (64 * n_chunks)))
+        out = packed_decode_attention(qs.cuda(), table, new_k=new_k.cuda(), new_v=new_v.cuda(), n_new=n_dev)
+        for i, w in enumerate(wants):
+            assert_attn_close(to_np(out[i]), w, f"chunks {n_chunks} view {i}")
+        table.check_status()
+    # shared integer count: every view uses the first 12 tail rows
+    table = DecodeTable(layers[:1], nvs[:1], H_kv * g)
+    out = packed_decode_attention(qs[:1].cuda(), table, new_k=new_k[:1].cuda(), new_v=new_v[:1].cuda(), n_new=12)
+    ol, onv = ols[0]
+    want = RA.decode_attention(qs[0].float().numpy(), ol, onv, new_k[0, :, :12].float().numpy(), new_v[0, :, :12].float().numpy())[0]
+    assert_attn_close(to_np(out[0]), want, "shared count")
+    # an empty tail record is (-inf, 0, 0): combining it changes nothing
+    rec = tail_attention_partial(qs[:1].cuda(), new_k[:1].cuda(), new_v[:1].cuda(), 0, H_kv)
+    assert torch.all(rec[:, 0] == float("-inf")) and torch.all(rec[:, 1] == 0) and torch.all(rec[:, 4:] == 0)
+    with pytest.raises(ValueError):
+        packed_decode_attention(qs[:1].cuda(), table, new_k=new_k[:1].cuda())
+
+
 def test_host_buffer_call_equals_device_call():
     """The host-buffer form (view ranges on separate streams, copies overlapped with the
     kernels) returns bit-for-bit what the device call returns, for one-chunk tables and
