@@ -216,10 +216,14 @@ __device__ __forceinline__ void pack_v_body(const PackVArgs& A, int h, int block
 // channels l, l+32, l+64, l+96 of a row — exactly the four codes of byte l of a quarter-split
 // 2-bit row and the code pairs of bytes l and l+32 of a half-split 4-bit row — so no data moves
 // between lanes; the loads of all rows are in flight together.
-constexpr int PACKV_ROWS128 = 4;                             // rows in flight per warp
-constexpr int PACKV_ROUNDS128 = 4;                           // rounds per warp: a CTA packs 8 x 4 x 4 = 128 slots
+constexpr int PACKV_CTA_ROWS128 = 128;                       // slots per CTA
+constexpr int PACKV_RPW128 = PACKV_CTA_ROWS128 / PACKV_WARPS;   // rows per warp (all loaded at once)
 
-__device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int block_x) {
+// Needs `rows`: PACKV_CTA_ROWS128 x 128 fp16 of shared memory, 8-byte aligned.  Rows of V that do
+// not start on 8-byte boundaries are read element by element.
+__device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int block_x, uint16_t* rows) {
+  __shared__ int s_src[PACKV_CTA_ROWS128];                    // source token, -1: pad row, -2: beyond the last slot
+  __shared__ int s_seg[PACKV_CTA_ROWS128], s_j[PACKV_CTA_ROWS128], s_base[PACKV_CTA_ROWS128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int D = 128;
   int n[4];
@@ -235,63 +239,74 @@ __device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int bl
     }
   }
   const int slots = A.max_n2 + A.max_n4 + A.max_n8 + A.max_n16;
-#pragma unroll 1
-  for (int round = 0; round < PACKV_ROUNDS128; ++round) {
-  const int slot0 = ((block_x * PACKV_ROUNDS128 + round) * PACKV_WARPS + warp) * PACKV_ROWS128;
+  const int slot0 = block_x * PACKV_CTA_ROWS128;
   if (slot0 >= slots) return;
-  int seg[PACKV_ROWS128], jj[PACKV_ROWS128], base[PACKV_ROWS128];
-  bool live[PACKV_ROWS128];
-  const uint16_t* row[PACKV_ROWS128];
-#pragma unroll
-  for (int k = 0; k < PACKV_ROWS128; ++k) {
-    const int slot = slot0 + k;
+  if (threadIdx.x < PACKV_CTA_ROWS128) {                      // one slot per thread: where its row comes from
+    const int slot = slot0 + threadIdx.x;
     int sg, j;
     if (slot < A.max_n2) { sg = 0; j = slot; }
     else if (slot < A.max_n2 + A.max_n4) { sg = 1; j = slot - A.max_n2; }
     else if (slot < A.max_n2 + A.max_n4 + A.max_n8) { sg = 2; j = slot - A.max_n2 - A.max_n4; }
     else { sg = 3; j = slot - A.max_n2 - A.max_n4 - A.max_n8; }
-    seg[k] = slot < slots ? sg : -1; jj[k] = j;
-    base[k] = sg == 0 ? 0 : sg == 1 ? n[0] : sg == 2 ? n[0] + n[1] : t_v;
-    live[k] = slot < slots && j < n[sg];
-    const int src = live[k] ? A.order[h * A.order_row_stride + base[k] + j] : 0;
-    row[k] = A.V + h * A.v_head_stride + (int64_t)src * A.v_row_stride;
+    const int base = sg == 0 ? 0 : sg == 1 ? n[0] : sg == 2 ? n[0] + n[1] : t_v;
+    int src = -2;
+    if (slot < slots) src = j < n[sg] ? A.order[h * A.order_row_stride + base + j] : -1;
+    s_src[threadIdx.x] = src; s_seg[threadIdx.x] = sg; s_j[threadIdx.x] = j; s_base[threadIdx.x] = base;
   }
-  uint16_t raw[PACKV_ROWS128][4];
+  __syncthreads();
+  {                                                           // the warp's rows, whole, all loads in flight together
+    uint2 w[PACKV_RPW128];
+    const uint16_t* Vh = A.V + h * A.v_head_stride + 4 * lane;
+    const bool aligned = (reinterpret_cast<uintptr_t>(A.V) & 7) == 0 && (A.v_head_stride & 3) == 0 && (A.v_row_stride & 3) == 0;
 #pragma unroll
-  for (int k = 0; k < PACKV_ROWS128; ++k)
+    for (int k = 0; k < PACKV_RPW128; ++k) {
+      const int src = s_src[warp * PACKV_RPW128 + k];
+      const uint16_t* p = Vh + (int64_t)(src >= 0 ? src : 0) * A.v_row_stride;
+      if (src < 0) w[k] = make_uint2(0u, 0u);
+      else if (aligned) w[k] = *reinterpret_cast<const uint2*>(p);
+      else w[k] = make_uint2((uint32_t)p[0] | ((uint32_t)p[1] << 16), (uint32_t)p[2] | ((uint32_t)p[3] << 16));
+    }
 #pragma unroll
-    for (int q = 0; q < 4; ++q) raw[k][q] = live[k] ? row[k][lane + 32 * q] : (uint16_t)0;
-#pragma unroll
-  for (int k = 0; k < PACKV_ROWS128; ++k) {
-    if (seg[k] < 0) continue;
-    const int j = jj[k];
-    if (seg[k] == 3) {                                        // fp16 rows are copied through (zeros when dead)
+    for (int k = 0; k < PACKV_RPW128; ++k)
+      *reinterpret_cast<uint2*>(rows + (warp * PACKV_RPW128 + k) * D + 4 * lane) = w[k];
+  }
+  __syncwarp();
+  // lane l takes channels l, l+32, l+64, l+96 of a row: the four codes of byte l of a quarter-split
+  // 2-bit row, the code pairs of bytes l and l+32 of a half-split 4-bit row
+#pragma unroll 1
+  for (int k = 0; k < PACKV_RPW128; ++k) {
+    const int i = warp * PACKV_RPW128 + k;
+    const int src = s_src[i];
+    if (src == -2) break;
+    const int seg = s_seg[i], j = s_j[i];
+    const uint16_t* row = rows + i * D;
+    if (seg == 3) {                                           // fp16 rows are copied through (zeros when dead)
       uint16_t* dst = A.out16 + ((int64_t)h * A.rows16 + j) * D;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = raw[k][q];
+      for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = row[lane + 32 * q];
       continue;
     }
-    const int width = seg[k] == 0 ? D / 4 : seg[k] == 1 ? D / 2 : D;
-    uint8_t* dst = seg[k] == 0 ? A.out2 + ((int64_t)h * A.rows2 + j) * width
-                 : seg[k] == 1 ? A.out4 + ((int64_t)h * A.rows4 + j) * width
-                               : A.out8 + ((int64_t)h * A.rows8 + j) * width;
-    if (!live[k]) {
+    const int width = seg == 0 ? D / 4 : seg == 1 ? D / 2 : D;
+    uint8_t* dst = seg == 0 ? A.out2 + ((int64_t)h * A.rows2 + j) * width
+                 : seg == 1 ? A.out4 + ((int64_t)h * A.rows4 + j) * width
+                            : A.out8 + ((int64_t)h * A.rows8 + j) * width;
+    if (src < 0) {
       for (int c = lane; c < width; c += 32) dst[c] = 0;
       continue;
     }
     float x[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) x[q] = h2f(raw[k][q]);
+    for (int q = 0; q < 4; ++q) x[q] = h2f(row[lane + 32 * q]);
     const float lo = warp_min(fminf(fminf(x[0], x[1]), fminf(x[2], x[3])));
     const float hi = warp_max(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])));
-    const int qbits = seg[k] == 0 ? 2 : seg[k] == 1 ? 4 : 8;
+    const int qbits = seg == 0 ? 2 : seg == 1 ? 4 : 8;
     const QParam qp = make_qparam(lo, hi, (float)((1 << qbits) - 1));
     unsigned c[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) c[q] = quant_code(x[q], qp);
-    if (seg[k] == 0) {
+    if (seg == 0) {
       dst[lane] = (uint8_t)(c[0] | (c[1] << 2) | (c[2] << 4) | (c[3] << 6));
-    } else if (seg[k] == 1) {
+    } else if (seg == 1) {
       dst[lane] = (uint8_t)(c[0] | (c[2] << 4));
       dst[lane + 32] = (uint8_t)(c[1] | (c[3] << 4));
     } else {
@@ -299,10 +314,9 @@ __device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int bl
       for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = (uint8_t)c[q];
     }
     if (lane == 0) {
-      A.out_scale[(int64_t)h * A.rows_meta + base[k] + j] = f2h_bits(qp.scale);
-      A.out_zp[(int64_t)h * A.rows_meta + base[k] + j] = f2h_bits(qp.zp);
+      A.out_scale[(int64_t)h * A.rows_meta + s_base[i] + j] = f2h_bits(qp.scale);
+      A.out_zp[(int64_t)h * A.rows_meta + s_base[i] + j] = f2h_bits(qp.zp);
     }
-  }
   }
 }
 
@@ -310,12 +324,15 @@ __host__ __device__ inline bool pack_v_fast(int D, int qbits_override, const voi
   return D == 128 && qbits_override == 0 && order != nullptr;
 }
 __host__ __device__ inline int pack_v_blocks(int slots, bool fast) {
-  const int per = PACKV_WARPS * (fast ? PACKV_ROWS128 * PACKV_ROUNDS128 : 1);
+  const int per = fast ? PACKV_CTA_ROWS128 : PACKV_WARPS;
   return slots > 0 ? (slots + per - 1) / per : 1;
 }
 
 __global__ void __launch_bounds__(PACKV_WARPS * 32)
-pack_v128_kernel(PackVArgs A) { pack_v_body128(A, blockIdx.y, blockIdx.x); }
+pack_v128_kernel(PackVArgs A) {
+  __shared__ __align__(16) uint16_t rows[PACKV_CTA_ROWS128 * 128];
+  pack_v_body128(A, blockIdx.y, blockIdx.x, rows);
+}
 
 __global__ void __launch_bounds__(PACKV_WARPS * 32)
 pack_v_kernel(PackVArgs A) {
@@ -525,11 +542,13 @@ pack_k_params_kernel(PackKArgs A) { pack_k_params_body(A, blockIdx.x); }
 // lane owns output bytes (lane, lane+32, ...) of a row and gathers the 4 / 2 / 1 channel slots
 // that make up each of them, so codes never move between lanes.
 constexpr int PACKK_WARPS = 8;
-constexpr int PACKK_RPW = 4;                                 // rows in flight per warp
-constexpr int PACKK_ROUNDS = 4;                              // rounds per warp
-constexpr int PACKK_ROWS = PACKK_WARPS * PACKK_RPW * PACKK_ROUNDS;   // stripe rows per CTA
+constexpr int PACKK_ROWS = 128;                              // stripe rows per CTA
+constexpr int PACKK_RPW = PACKK_ROWS / PACKK_WARPS;          // rows per warp
 
+// Dynamic shared memory: scale, zp (fp32) and channel (int) per slot, then — when rows are staged
+// (128 channels, 8-byte aligned rows) — the CTA's PACKK_ROWS rows whole, all loads in flight at once.
 __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int block_x, unsigned char* smem_raw) {
+  __shared__ int s_tok[PACKK_ROWS];
   const uint16_t* __restrict__ K = A.K;
   const int t_k = A.t_k, n2p = A.n2p, n4p = A.n4p, n8p = A.n8p, n_slabs = A.n_slabs, ov = A.qbits_override;
   const int64_t rows_k = A.rows_k;
@@ -538,6 +557,7 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
   float* s_scale = reinterpret_cast<float*>(smem_raw);          // [d_pad]
   float* s_zp = s_scale + d_pad;                                 // [d_pad]
   int* s_ch = reinterpret_cast<int*>(s_zp + d_pad);             // [d_pad]
+  uint16_t* s_rows = reinterpret_cast<uint16_t*>(smem_raw + (((size_t)d_pad * 12 + 15) & ~(size_t)15));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const KMaps m = load_maps(h, A.tok_order, A.tok_order_rs, A.tok_counts, A.tok_counts_rs, A.max_t_v, t_k,
                             A.ch_order, A.ch_order_rs, A.ch_counts, A.ch_counts_rs, n2p, n4p, n8p);
@@ -545,35 +565,26 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
   for (int p = threadIdx.x; p < d_pad; p += blockDim.x) {
     s_scale[p] = fin[p]; s_zp[p] = fin[d_pad + p]; s_ch[p] = slot_channel(m, p);
   }
+  const int row0 = block_x * PACKK_ROWS;
+  if (threadIdx.x < PACKK_ROWS) s_tok[threadIdx.x] = row0 + threadIdx.x < t_k ? stripe_token(m, row0 + threadIdx.x) : -1;
   __syncthreads();
-  const int sub2 = n2p / 4, sub4 = n4p / 2;
-  const int row_bytes = ov > 0 ? d_pad : sub2 + sub4 + n8p;
-#pragma unroll 1
-  for (int round = 0; round < PACKK_ROUNDS; ++round) {
-  const int s0 = block_x * PACKK_ROWS + (round * PACKK_WARPS + warp) * PACKK_RPW;
-  if (s0 >= t_k) break;
-  int tok[PACKK_RPW];
-  const uint16_t* row[PACKK_RPW];
-#pragma unroll
-  for (int k = 0; k < PACKK_RPW; ++k) {
-    tok[k] = s0 + k < t_k ? stripe_token(m, s0 + k) : -1;
-    row[k] = K + h * A.k_head_stride + (int64_t)(tok[k] < 0 ? 0 : tok[k]) * A.k_row_stride;
-  }
-  // D == 128: the warp's rows are read whole (one 8-byte load per lane and row, all in flight
-  // together) into shared memory and the channels are gathered from there
+  const uint16_t* Kh = K + h * A.k_head_stride;
   if (A.stage_rows) {
-    uint16_t* s_rows = reinterpret_cast<uint16_t*>(smem_raw + (((size_t)d_pad * 12 + 15) & ~(size_t)15)) + warp * (PACKK_RPW * 128);
     uint2 w[PACKK_RPW];
 #pragma unroll
-    for (int k = 0; k < PACKK_RPW; ++k)
-      w[k] = tok[k] >= 0 ? *reinterpret_cast<const uint2*>(row[k] + 4 * lane) : make_uint2(0u, 0u);
-#pragma unroll
     for (int k = 0; k < PACKK_RPW; ++k) {
-      *reinterpret_cast<uint2*>(s_rows + k * 128 + 4 * lane) = w[k];
-      row[k] = s_rows + k * 128;
+      const int tok = s_tok[warp * PACKK_RPW + k];
+      w[k] = tok >= 0 ? *reinterpret_cast<const uint2*>(Kh + (int64_t)tok * A.k_row_stride + 4 * lane) : make_uint2(0u, 0u);
     }
+#pragma unroll
+    for (int k = 0; k < PACKK_RPW; ++k)
+      *reinterpret_cast<uint2*>(s_rows + (warp * PACKK_RPW + k) * 128 + 4 * lane) = w[k];
     __syncwarp();
   }
+  // a lane owns output bytes (lane, lane+32, ...) of a row and gathers the 4 / 2 / 1 channel slots
+  // that make up each of them, so codes never move between lanes
+  const int sub2 = n2p / 4, sub4 = n4p / 2;
+  const int row_bytes = ov > 0 ? d_pad : sub2 + sub4 + n8p;
   for (int b = lane; b < row_bytes; b += 32) {
     int ns, sl0, step, shift;                                   // slots sl0 + v*step, code v at bit v*shift
     float qmax;
@@ -588,26 +599,24 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
       const int sl = sl0 + (v < ns ? v : 0) * step;
       ch[v] = s_ch[sl]; sc[v] = s_scale[sl]; zp[v] = s_zp[sl];
     }
-    uint16_t raw[PACKK_RPW][4];
-#pragma unroll
-    for (int k = 0; k < PACKK_RPW; ++k)
-#pragma unroll
-      for (int v = 0; v < 4; ++v) raw[k][v] = (v < ns && tok[k] >= 0 && ch[v] >= 0) ? row[k][ch[v]] : (uint16_t)0;
-#pragma unroll
+    uint8_t* out = dst + ((int64_t)h * rows_k + row0 + warp * PACKK_RPW) * width + col;
+#pragma unroll 4
     for (int k = 0; k < PACKK_RPW; ++k) {
-      if (s0 + k >= t_k) break;
+      const int i = warp * PACKK_RPW + k;
+      if (row0 + i >= t_k) break;
+      const int tok = s_tok[i];
+      const uint16_t* row = A.stage_rows ? s_rows + i * 128 : Kh + (int64_t)(tok < 0 ? 0 : tok) * A.k_row_stride;
       unsigned byte = 0;
 #pragma unroll
       for (int v = 0; v < 4; ++v) {
         if (v < ns) {
+          const float x = (tok >= 0 && ch[v] >= 0) ? h2f(row[ch[v]]) : 0.f;
           QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
-          byte |= quant_code(h2f(raw[k][v]), qp) << (v * shift);
+          byte |= quant_code(x, qp) << (v * shift);
         }
       }
-      dst[((int64_t)h * rows_k + s0 + k) * width + col] = (uint8_t)byte;
+      out[(int64_t)k * width] = (uint8_t)byte;
     }
-  }
-  __syncwarp();                                              // the staged rows are overwritten in the next round
   }
 }
 
@@ -642,10 +651,11 @@ pack_v_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
 
 __global__ void __launch_bounds__(PACKV_WARPS * 32)
 pack_v128_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
+  __shared__ __align__(16) uint16_t rows[PACKV_CTA_ROWS128 * 128];
   __shared__ PackVArgs A;
   if (threadIdx.x == 0) job_to_vargs(jobs[blockIdx.z], A);
   __syncthreads();
-  pack_v_body128(A, blockIdx.y, blockIdx.x);
+  pack_v_body128(A, blockIdx.y, blockIdx.x, rows);
 }
 
 __device__ __forceinline__ void job_to_kargs(const rdkv_pack_job& J, PackKArgs& A) {
@@ -792,7 +802,7 @@ extern "C" int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_r
   pack_k_params_kernel<<<H, 128, 0, st>>>(A);
   rc = launch_status();
   if (rc != RDKV_OK) return rc;
-  const size_t smem = (size_t)d_pad * (3 * sizeof(float)) + (A.stage_rows ? 16 + PACKK_WARPS * PACKK_RPW * 128 * sizeof(uint16_t) : 0);
+  const size_t smem = (size_t)d_pad * (3 * sizeof(float)) + (A.stage_rows ? 16 + PACKK_ROWS * 128 * sizeof(uint16_t) : 0);
   pack_k_quant_kernel<<<dim3((t_k + PACKK_ROWS - 1) / PACKK_ROWS, H), PACKK_WARPS * 32, smem, st>>>(A);
   return launch_status();
 }
@@ -821,7 +831,7 @@ extern "C" int rdkv_pack_kv_batched(const rdkv_pack_job* jobs, int n_jobs, int H
   pack_k_params_batched_kernel<<<dim3(H, n_jobs), 128, 0, st>>>(jobs);
   rc = launch_status();
   if (rc != RDKV_OK) return rc;
-  const size_t smem = (size_t)max_d_pad * (3 * sizeof(float)) + (D == 128 ? 16 + PACKK_WARPS * PACKK_RPW * 128 * sizeof(uint16_t) : 0);
+  const size_t smem = (size_t)max_d_pad * (3 * sizeof(float)) + (D == 128 ? 16 + PACKK_ROWS * 128 * sizeof(uint16_t) : 0);
   pack_k_quant_batched_kernel<<<dim3((max_t_k + PACKK_ROWS - 1) / PACKK_ROWS, H, n_jobs), PACKK_WARPS * 32, smem, st>>>(jobs);
   return launch_status();
 }
