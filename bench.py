@@ -167,7 +167,7 @@ def max_over_ranks(x: float, world: int, device) -> float:
 
 def run_decode(args, rank, world, device):
     from rdkv_b200._lib import lib
-    from rdkv_b200.decode import (DecodeTable, decode_attention_partial, lse_combine, packed_decode_attention,
+    from rdkv_b200.decode import (DecodeTable, decode_attention_phases, packed_decode_attention,
                                   packed_decode_attention_host)
     cfg = dict(CFG3)
     if args.small:
@@ -216,10 +216,9 @@ def run_decode(args, rank, world, device):
         for i in range(args.steps):
             tb = tables[i % R]
             ev[i][0].record()
-            part = decode_attention_partial(q_pool[i % n_q], tb, out)
+            decode_attention_phases(q_pool[i % n_q], tb, out, phases=1)
             ev[i][1].record()
-            if tb.n_chunks > 1:
-                lse_combine(part, out.view(-1, 128))
+            decode_attention_phases(q_pool[i % n_q], tb, out, phases=2)
         torch.cuda.synchronize()
     torch.cuda.profiler.stop()
     fused_ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
@@ -243,7 +242,9 @@ def run_decode(args, rank, world, device):
 
     for tb in tables:
         tb.check_status()
-    launches = 1 if tables[0].n_chunks == 1 else 2
+    t0 = tables[0]
+    v_main, k_rest, rows_rest = t0.unit_plan(t0.n_views)
+    launches = (1 if v_main > 0 else 0) + (0 if v_main == t0.n_views else (1 if k_rest == 1 else 2))
     if rank != 0:
         return None
     peak, peak_kind = load_peaks()
@@ -267,7 +268,9 @@ def run_decode(args, rank, world, device):
             "launches_per_step": launches,
             "l2": f"{R} cache replica(s) rotated per step, {R * step_bytes / 2**20:.0f} MiB per GPU "
                   f"> 2 x 126 MiB L2; no flush needed",
-            "small": bool(args.small or args.layers), "chunk_rows": tables[0].chunk_rows, "n_chunks": tables[0].n_chunks,
+            "small": bool(args.small or args.layers),
+            "launch_shape": ("one CTA per (view, KV head)" if v_main == t0.n_views
+                             else f"{k_rest} chunks of {rows_rest} rows per (view, KV head) + merge"),
         },
         "hbm_gbs": total_step_bytes * args.steps / sec / 1e9,
         "hbm_frac_of_8tbs": total_step_bytes * args.steps / sec / 1e9 / (8000.0 * world),

@@ -29,7 +29,7 @@ class DecodeTable:
     """
 
     def __init__(self, layers: Sequence[PackedKVLayer], new_v_only: Sequence[Optional[Tensor]], H_q: int,
-                 *, use_mask: bool = False, device=None):
+                 *, use_mask: bool = False, device=None, n_chunks: Optional[int] = None):
         if len(layers) == 0:
             raise ValueError("DecodeTable needs at least one layer")
         if len(new_v_only) != len(layers):
@@ -62,13 +62,13 @@ class DecodeTable:
             for t, align in ((pl.V_2bit, 4), (pl.V_4bit, 4), (pl.V_8bit, 4), (nv, 8)):
                 if t is not None and t.numel() and t.data_ptr() % align:
                     raise ValueError(f"packed V tensors must be {align}-byte aligned")
-        # chunking: enough CTAs to fill the GPU a few times over, chunks as long as possible
-        # (every chunk costs one partial record per query head)
+        # uniform chunks of the partial-record calls: only when there are fewer units than CTA slots
+        # (a chunk pays the per-CTA prologue and merge again; see unit_plan)
         n_hgrp = (self.H_q // self.H_kv + 7) // 8
         units = self.n_views * self.H_kv * n_hgrp
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        want = max(1, -(-4 * sms // units))
-        n_chunks = max(1, min(want, -(-max(max_t_k, 1) // 128)))
+        want = max(1, min(4, (self.CTAS_PER_SM * sms) // units))
+        n_chunks = max(1, min(want if n_chunks is None else int(n_chunks), -(-max(max_t_k, 1) // 128)))
         self.chunk_rows = max(64, ((-(-max(max_t_k, 1) // n_chunks) + 63) // 64) * 64)
         self.n_chunks = max(1, -(-max(max_t_k, 1) // self.chunk_rows))
         raw = bytes(views)
@@ -76,6 +76,38 @@ class DecodeTable:
         self.views = host.to(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._partials: Optional[Tensor] = None
+        self.unit_rows = ((max(max_t_k, 1) + 63) // 64) * 64
+        self._sms = sms
+        self._n_hgrp = n_hgrp
+
+    CTAS_PER_SM = 3                      # resident CTAs of the fused kernel per SM
+
+    def unit_plan(self, n_views: int):
+        """(v_main, k, rows): of a launch over ``n_views`` views the first ``v_main`` views run one CTA
+        per unit, the units of the remaining views are cut into ``k`` uniform chunks of ``rows`` rows.
+        Measured on B200: a CTA per whole unit is the most efficient shape (a chunk pays the per-CTA
+        prologue and merge again), so units are cut — all of them, uniformly — only when there are
+        fewer units than CTA slots.  Tried and dropped: cutting just the units of a mostly empty last
+        wave (on a stream of lower priority), and equal segments of one flat row axis over all units
+        with a loop over items in the CTA — both slower than the idle tail they remove."""
+        slots = self._sms * self.CTAS_PER_SM
+        hy = self.H_kv * self._n_hgrp
+        units = n_views * hy
+        k_max = max(1, min(4, self.unit_rows // 256))
+        if units <= slots:
+            k = max(1, min(k_max, slots // max(units, 1)))
+            return (n_views, 1, self.unit_rows) if k == 1 else (0, k, self._chunk_rows_for(k))
+        return n_views, 1, self.unit_rows
+
+    def _chunk_rows_for(self, k: int) -> int:
+        return max(64, ((-(-self.unit_rows // k) + 63) // 64) * 64)
+
+    def chunk_workspace(self, k: int) -> Tensor:
+        """Records of chunked units: [n_views*H_q, k, 132] fp32 (grown on demand)."""
+        cache = self.__dict__.setdefault("_chunk_ws", {})
+        if k not in cache:
+            cache[k] = torch.empty((self.n_views * self.H_q, k, PARTIAL_STRIDE), dtype=torch.float32, device=self.device)
+        return cache[k]
 
     def workspace(self) -> Optional[Tensor]:
         """Split-sequence partial records [n_views*H_q, n_chunks, 132] fp32 (allocated once);
@@ -115,10 +147,12 @@ def lse_combine(partials: Tensor, out: Optional[Tensor] = None, *, out_ml: Optio
 
 
 def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out: Optional[Tensor],
-                  v0: int = 0, v1: Optional[int] = None) -> None:
-    """Launch the fused kernel on views [v0, v1) of the table (all of them by default);
-    q, partials and out are the full-table tensors, the range is cut by pointer offsets.
-    ``out`` may be a pinned host tensor (device-addressable)."""
+                  v0: int = 0, v1: Optional[int] = None, n_chunks: Optional[int] = None,
+                  chunk_rows: Optional[int] = None) -> None:
+    """Launch the fused kernel on views [v0, v1) of the table (all of them by default) with uniform
+    chunks (the table's, or the given ones); q, partials ([n_views*H_q, n_chunks, 132]) and out are
+    the full-table tensors, the range is cut by pointer offsets.  ``out`` may be a pinned host
+    tensor (device-addressable)."""
     require_cuda(q, "q")
     if q.shape[-1] != HEAD_DIM or q.numel() != table.n_views * table.H_q * HEAD_DIM:
         raise ValueError(f"q must be [{table.n_views},{table.H_q},{HEAD_DIM}], got {tuple(q.shape)}")
@@ -132,17 +166,53 @@ def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out
     def off(t: Optional[Tensor], per_row: int) -> Optional[int]:
         return None if t is None else t.data_ptr() + rows * per_row * t.element_size()
 
+    n_chunks = table.n_chunks if n_chunks is None else n_chunks
+    chunk_rows = table.chunk_rows if chunk_rows is None else chunk_rows
     check(lib().rdkv_decode_attn_partial(table.views.data_ptr() + v0 * C.sizeof(LayerView), v1 - v0,
                                          off(q, HEAD_DIM), q_dtype_tag(q), table.H_q,
-                                         table.H_kv, table.chunk_rows, table.n_chunks, table.k_row_bytes_max,
-                                         off(partials, table.n_chunks * PARTIAL_STRIDE), off(out, HEAD_DIM),
+                                         table.H_kv, chunk_rows, n_chunks, table.k_row_bytes_max,
+                                         off(partials, n_chunks * PARTIAL_STRIDE), off(out, HEAD_DIM),
                                          ptr(table.status), stream_ptr(q.device)),
           "rdkv_decode_attn_partial")
 
 
+def _launch_units(q: Tensor, table: DecodeTable, out: Tensor, v0: int = 0, v1: Optional[int] = None,
+                  phases: int = 3) -> None:
+    """One CTA per unit on views [v0, v1), or uniform chunks of every unit when there are fewer
+    units than CTA slots (DecodeTable.unit_plan); chunk records are merged by the combine kernel.
+    phases: 1 = fused launches, 2 = merge, 3 = both."""
+    v1 = table.n_views if v1 is None else v1
+    v_main, k, rows_k = table.unit_plan(v1 - v0)
+    if phases & 1 and v_main > 0:
+        _launch_fused(q, table, None, out, v0, v0 + v_main, 1, table.unit_rows)
+    if v_main < v1 - v0:
+        a = v0 + v_main
+        if k == 1:
+            if phases & 1:
+                _launch_fused(q, table, None, out, a, v1, 1, table.unit_rows)
+            return
+        ws = table.chunk_workspace(k)
+        if phases & 1:
+            _launch_fused(q, table, ws, None, a, v1, k, rows_k)
+        if phases & 2:
+            rows = slice(a * table.H_q, v1 * table.H_q)
+            check(lib().rdkv_lse_combine(ws[rows].data_ptr(), (v1 - a) * table.H_q, k, ws.stride(0), ws.stride(1),
+                                         out.data_ptr() + a * table.H_q * HEAD_DIM * 4, None, None,
+                                         stream_ptr(q.device)), "rdkv_lse_combine")
+
+
+
+def decode_attention_phases(q: Tensor, table: DecodeTable, out: Tensor, *, phases: int = 3) -> Tensor:
+    """The two phases of :func:`packed_decode_attention` separately (for measurements):
+    ``phases=1`` runs the fused kernel alone, ``phases=2`` the merge of the records of split
+    units / chunks (if the table's launch shape has any), 3 both."""
+    _launch_units(q, table, out, phases=phases)
+    return out
+
+
 def decode_attention_partial(q: Tensor, table: DecodeTable, out: Optional[Tensor] = None) -> Tensor:
-    """The fused kernel alone: returns the per-chunk records, or ``out`` itself when a
-    single chunk covers every head (the kernel then writes normalised results)."""
+    """The fused kernel alone in uniform-chunk mode: returns the per-chunk records, or ``out``
+    itself when a single chunk covers every head (the kernel then writes normalised results)."""
     if table.n_chunks == 1:
         if out is None:
             out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
@@ -239,12 +309,7 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
         out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
     if not out.is_contiguous() or out.dtype != torch.float32:
         raise ValueError("out must be contiguous float32 [n_views,H_q,128]")
-    if table.n_chunks == 1:
-        _launch_fused(q, table, None, out)
-    else:
-        part = table.workspace()
-        _launch_fused(q, table, part, None)
-        lse_combine(part, out.view(-1, HEAD_DIM))
+    _launch_units(q, table, out)
     return out
 
 
@@ -278,7 +343,9 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
     if tuple(out_host.shape) != tuple(q_host.shape) or out_host.dtype != torch.float32 or not out_host.is_contiguous():
         raise ValueError("out_host must be contiguous float32 with q_host's shape")
     q_dtype_tag(q_host)
-    n_slices = max(1, min(int(slices), table.n_views))
+    # no more ranges than keep every range's launch at least one full wave of CTAs
+    units = table.n_views * table.H_kv * table._n_hgrp
+    n_slices = max(1, min(int(slices), table.n_views, units // (table._sms * table.CTAS_PER_SM)))
     io: Optional[_HostIO] = getattr(table, "_host_io", None)
     if io is None or io.q.dtype != q_host.dtype or len(io.streams) != n_slices:
         io = _HostIO(table, q_host.dtype, n_slices)
@@ -288,19 +355,11 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
         io.out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=table.device)
     out = out_host if direct else io.out
     cur = torch.cuda.current_stream(table.device)
-    part = table.workspace()
     for (a, b), st in zip(io.ranges, io.streams):
         st.wait_stream(cur)
         with torch.cuda.stream(st):
             io.q[a:b].copy_(q_host[a:b], non_blocking=True)
-            if part is None:
-                _launch_fused(io.q, table, None, out, a, b)
-            else:
-                _launch_fused(io.q, table, part, None, a, b)
-                rows = slice(a * table.H_q, b * table.H_q)
-                check(lib().rdkv_lse_combine(part[rows].data_ptr(), (b - a) * table.H_q, table.n_chunks,
-                                             part.stride(0), part.stride(1), out.view(-1, HEAD_DIM)[rows].data_ptr(),
-                                             None, None, stream_ptr(table.device)), "rdkv_lse_combine")
+            _launch_units(io.q, table, out, a, b)
             if not direct:
                 out_host[a:b].copy_(io.out[a:b], non_blocking=True)
     for st in io.streams[:len(io.ranges)]:

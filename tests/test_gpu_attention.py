@@ -158,6 +158,41 @@ def test_uncompressed_tail_joins_the_softmax(kv_dtype):
         packed_decode_attention(qs[:1].cuda(), table, new_k=new_k[:1].cuda())
 
 
+def test_whole_units_and_uniform_chunks():
+    """More units than CTA slots: one CTA per unit; fewer: every unit in uniform chunks merged by
+    the combine kernel.  Both launch shapes against each other and the oracle."""
+    from oracle import ref_attention as RA
+    from oracle import ref_packing as RP
+    from rdkv_b200 import synth
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention
+    from rdkv_b200.packing import pack_kv
+    H_kv, g, T, N = 4, 4, 1024, 560
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    n_views = (3 * sms) // H_kv + 9                        # a few units more than one wave of CTAs
+    layers, nvs = [], []
+    for i in range(n_views):
+        seed = synth.unit_seed(6, i % 7, i)
+        K, V = synth.make_kv(H_kv, T, seed=seed)
+        vb = synth.make_v_bits(H_kv, T, N, seed=seed)
+        kb = synth.make_k_bits(H_kv, seed=seed)
+        pl, nv = pack_kv(K.cuda(), V.cuda(), vb.cuda(), kb.cuda(), g, build_mask=False)
+        layers.append(pl); nvs.append(nv)
+        if i == n_views - 1:
+            last = RP.pack_kv(K.numpy(), V.numpy(), vb.numpy(), kb.numpy(), g)
+    q = synth.make_q(H_kv * g, seed=5, batch=n_views, dtype=torch.float16)
+    want_last = RA.decode_attention(q[n_views - 1].float().numpy(), *last)[0]
+    outs = []
+    for lo in (0, n_views - 20):                           # all views (whole units) / 20 views (chunks)
+        table = DecodeTable(layers[lo:], nvs[lo:], H_kv * g)
+        v_main, k, rows = table.unit_plan(n_views - lo)
+        assert (v_main == n_views and k == 1) if lo == 0 else (v_main == 0 and k > 1)
+        out = packed_decode_attention(q[lo:].cuda(), table)
+        assert_attn_close(to_np(out[-1]), want_last, "last view")
+        outs.append(out[-20:])
+        table.check_status()
+    assert_attn_close(to_np(outs[0]), to_np(outs[1]), "whole units vs chunks")
+
+
 def test_host_buffer_call_equals_device_call():
     """The host-buffer form (view ranges on separate streams, copies overlapped with the
     kernels) returns bit-for-bit what the device call returns, for one-chunk tables and
