@@ -527,7 +527,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="2 layers x batch 2 (smoke-sized case)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling-sized runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-slices", type=int, default=4,
+    ap.add_argument("--e2e-slices", type=int, default=None,
                     help="view ranges (streams) the host-buffer call overlaps its copies and kernels over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -325,11 +325,13 @@ class _HostIO:
         self.ranges = [(a, min(a + step, table.n_views)) for a in range(0, table.n_views, step)]
 
 
-def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: Tensor, *, slices: int = 4) -> Tensor:
+def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: Tensor, *,
+                                 slices: Optional[int] = None) -> Tensor:
     """Host-buffer form of :func:`packed_decode_attention`: ``q_host`` [n_views,H_q,128]
     (fp16/bf16/fp32) and ``out_host`` [n_views,H_q,128] fp32 live in host memory.
 
-    The views are cut into ``slices`` ranges; every range uploads its queries and runs the
+    The views are cut into ``slices`` ranges (default: up to 4, each at least one full wave of
+    CTAs); every range uploads its queries and runs the
     kernel on a stream of its own, so the upload of one range overlaps the kernel of another.
     With a pinned ``out_host`` the kernels write their results straight into it (pinned host
     memory is addressable from the device), so the results cross the bus while the kernels
@@ -343,9 +345,10 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
     if tuple(out_host.shape) != tuple(q_host.shape) or out_host.dtype != torch.float32 or not out_host.is_contiguous():
         raise ValueError("out_host must be contiguous float32 with q_host's shape")
     q_dtype_tag(q_host)
-    # no more ranges than keep every range's launch at least one full wave of CTAs
-    units = table.n_views * table.H_kv * table._n_hgrp
-    n_slices = max(1, min(int(slices), table.n_views, units // (table._sms * table.CTAS_PER_SM)))
+    if slices is None:                                     # up to 4 ranges, each at least one full wave of CTAs
+        units = table.n_views * table.H_kv * table._n_hgrp
+        slices = min(4, units // (table._sms * table.CTAS_PER_SM))
+    n_slices = max(1, min(int(slices), table.n_views))
     io: Optional[_HostIO] = getattr(table, "_host_io", None)
     if io is None or io.q.dtype != q_host.dtype or len(io.streams) != n_slices:
         io = _HostIO(table, q_host.dtype, n_slices)
