@@ -133,6 +133,23 @@ int rdkv_v_weighted_sum(const rdkv_layer_view* view, const float* w, int64_t w_r
  * if a view did not fit the launch (k_row_bytes_max too small, or more than 512
  * padded channels); the affected records are then invalid.
  * Alignment: V code tensors 4-byte, fp16 V tensor 8-byte, scale/zp 2-byte aligned. */
+/* The two halves of the same kernel behind the reference's two-stage interface
+ * (views: DEVICE array of ONE view):
+ * rdkv_decode_scores — what k_mixed_qk_dot_into computes
+ * (obkv_accel/triton_k_kernel.py:1211-1427): scores[h][t] for every stripe row
+ * t < t_eff (rows that belong to no token hold the zero point and score 0 up to
+ * rounding, as in the reference); q [H_q][128] contiguous; V is not read.
+ * rdkv_decode_weighted_sum — what v_dequant_weighted_sum_dispatch_into computes
+ * (obkv_accel/triton_v_kernel.py:1729-1760): out[h][:] = sum_t weights[h][t] * V^[t]
+ * with weight columns = stripe rows; out fp32 [H_q][128] contiguous; K is not read;
+ * unit_rows >= the longest head's live rows (one CTA per KV head, fixed summation
+ * order). */
+int rdkv_decode_scores(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,
+                       int H_kv, int chunk_rows, int n_chunks, int k_row_bytes_max, int t_eff,
+                       float* scores, int64_t scores_row_stride, int32_t* status, void* stream);
+int rdkv_decode_weighted_sum(const rdkv_layer_view* views, int n_views, int H_q, int H_kv, int unit_rows,
+                             int k_row_bytes_max, const float* weights, int64_t weights_row_stride,
+                             float* out, int32_t* status, void* stream);
 int rdkv_decode_stage_bytes(int k_row_bytes_max);
 int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,
                              int H_q, int H_kv, int chunk_rows, int n_chunks, int k_row_bytes_max,

@@ -80,6 +80,8 @@ _PROTOTYPES = {
     "rdkv_k_scores": ([C.POINTER(LayerView), _p, _i, _i64, _i, _i, _i, _p, _i64, _p], _i),
     "rdkv_v_weighted_sum": ([C.POINTER(LayerView), _p, _i64, _i, _i, _p, _i64, _p], _i),
     "rdkv_decode_stage_bytes": ([_i], _i),
+    "rdkv_decode_scores": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p, _i64, _p, _p], _i),
+    "rdkv_decode_weighted_sum": ([_p, _i, _i, _i, _i, _i, _p, _i64, _p, _p, _p], _i),
     "rdkv_decode_attn_partial": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p], _i),
     "rdkv_tail_attn_partial": ([_p, _i, _i64, _i, _i, _p, _p, _i, _i64, _i64, _i64, _i, _p, _p, _p], _i),
     "rdkv_lse_combine": ([_p, _i64, _i, _i64, _i64, _p, _p, _p, _p], _i),

@@ -318,6 +318,15 @@ __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const u
   }
 }
 
+// MODE_ATTN: the whole attention block.  MODE_SCORES: only the q.K scores of the live rows, written
+// to aux[(query head) * aux_stride + stripe row] for stripe rows < t_eff (the K kernel of the
+// two-stage interface; V is not read).  MODE_WEIGHTS: the softmax weights are given in
+// aux[(query head) * aux_stride + stripe row]; only sum_t w.V is computed (the V kernel of the
+// two-stage interface; K is not read), records carry m = 0 and l = 1 in chunk 0 so that the
+// combine kernel adds the chunks up.
+constexpr int MODE_ATTN = 0, MODE_SCORES = 1, MODE_WEIGHTS = 2;
+
+template <int MODE>
 #ifdef RDKV_MAXNREG
 __global__ void __maxnreg__(RDKV_MAXNREG)
 #else
@@ -325,7 +334,8 @@ __global__ void __launch_bounds__(CTA_THREADS, RDKV_MINB)
 #endif
 decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __restrict__ q, int q_dtype,
                     int H_q, int g, int chunk_rows, int n_chunks, int stage_bytes,
-                    float* __restrict__ partials, float* __restrict__ out, int* __restrict__ status) {
+                    float* __restrict__ partials, float* __restrict__ out, int* __restrict__ status,
+                    float* __restrict__ aux, int64_t aux_stride, int t_eff) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ rdkv_layer_view v;
   __shared__ CtaGeom G;
@@ -376,13 +386,16 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     const HeadCounts hc = head_counts(v, h);
     const int p = lane & 3;
     const int c0 = chunk * chunk_rows, c1 = c0 + chunk_rows;
-    const int b_lo = p == 0 ? 0 : p == 1 ? hc.n2 : p == 2 ? hc.n2 + hc.n4 : hc.t_v;
-    const int b_hi = p == 0 ? hc.n2 : p == 1 ? hc.n2 + hc.n4 : p == 2 ? hc.t_v : hc.t_v + hc.n16;
+    // (MODE_SCORES: every stripe row below t_eff is scored, as one run of rows; the rows that
+    //  belong to no token hold the zero point and score 0, as in the reference)
+    const int b_lo = MODE == MODE_SCORES ? 0 : p == 0 ? 0 : p == 1 ? hc.n2 : p == 2 ? hc.n2 + hc.n4 : hc.t_v;
+    const int b_hi = MODE == MODE_SCORES ? (p == 0 ? t_eff : 0)
+                                         : p == 0 ? hc.n2 : p == 1 ? hc.n2 + hc.n4 : p == 2 ? hc.t_v : hc.t_v + hc.n16;
     const int lo = max(b_lo, c0);
     const int hi = max(lo, min(b_hi, c1));
     const int n = hi - lo;
     const int ntile = (n + phase_tile_rows(p) - 1) / phase_tile_rows(p);
-    const int64_t krow = p < 3 ? lo : (int64_t)v.max_t_v + (lo - hc.t_v);   // stripe row
+    const int64_t krow = (p < 3 || MODE == MODE_SCORES) ? lo : (int64_t)v.max_t_v + (lo - hc.t_v);   // stripe row
     const unsigned char* v16b = reinterpret_cast<const unsigned char*>(v.v16);
     const unsigned char* scb = reinterpret_cast<const unsigned char*>(v.v_scale);
     const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
@@ -401,8 +414,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       if (kd.sub2) fast = fast && blocks_inside(gk2, gk2 + (int64_t)n * kd.sub2, v.k2, v.k2 + v.k2_bytes);
       if (kd.sub4) fast = fast && blocks_inside(gk4, gk4 + (int64_t)n * kd.sub4, v.k4, v.k4 + v.k4_bytes);
       if (kd.n8) fast = fast && blocks_inside(gk8, gk8 + (int64_t)n * kd.n8, v.k8, v.k8 + v.k8_bytes);
-      fast = fast && blocks_inside(vb, vb + (int64_t)n * phase_row_bytes(p), vlo, vlo + vext);
-      if (p < 3) {
+      if (MODE != MODE_SCORES) fast = fast && blocks_inside(vb, vb + (int64_t)n * phase_row_bytes(p), vlo, vlo + vext);
+      if (p < 3 && MODE != MODE_SCORES) {
         fast = fast && blocks_inside(gsc, gsc + n * 2, scb, scb + v.v_meta_bytes);
         fast = fast && blocks_inside(gzp, gzp + n * 2, zpb, zpb + v.v_meta_bytes);
       }
@@ -419,7 +432,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     }
     if (lane == 0) {
       G.fast = fast ? 1 : 0;
-      G.first_tile[4] = (!fits || (hc.n16 > 0 && v.v16 == nullptr)) ? -1 : t0 + t1 + t2 + t3;
+      G.first_tile[4] = (!fits || (MODE != MODE_SCORES && hc.n16 > 0 && v.v16 == nullptr)) ? -1 : t0 + t1 + t2 + t3;
     }
     __threadfence_block();
     __syncwarp();
@@ -430,7 +443,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   //    warp works out the geometry and starts the first copies).  All loads of a round are
   //    issued before any is used: slot -> permuted channel -> query element is a chain of two
   //    global round trips, paid once per round of two 16-channel blocks. ──
-  if (warp < FW && fits) {
+  if (MODE != MODE_WEIGHTS && warp < FW && fits) {
     const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
     const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
     const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
@@ -499,6 +512,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
 
   if (total_tiles <= 0) {                                  // nothing live here: empty records
     if (total_tiles < 0 && tid == 0 && status != nullptr) atomicOr(status, 2);
+    if (MODE == MODE_SCORES) return;
     if (direct) {
       for (int i = tid; i < gcnt * D; i += blockDim.x) out[((int64_t)view_idx * H_q + hq0) * D + i] = 0.f;
     } else {
@@ -536,12 +550,12 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           const unsigned char* a_v = G.vrow[p] + (int64_t)t.row0 * phase_row_bytes(p);
           const unsigned char* a_sc = G.sc[p < 3 ? p : 0] + t.row0 * 2;
           const unsigned char* a_zp = G.zp[p < 3 ? p : 0] + t.row0 * 2;
-          P.rg[0] = RangePlan{a_v, t.n * phase_row_bytes(p), (uint32_t)SL.v};
-          P.rg[1] = RangePlan{a_k2, t.n * kd.sub2, (uint32_t)SL.k2};
-          P.rg[2] = RangePlan{a_k4, t.n * kd.sub4, (uint32_t)SL.k4};
-          P.rg[3] = RangePlan{a_k8, t.n * kd.n8, (uint32_t)SL.k8};
-          P.rg[4] = RangePlan{a_sc, p < 3 ? t.n * 2 : 0, (uint32_t)SL.sc};
-          P.rg[5] = RangePlan{a_zp, p < 3 ? t.n * 2 : 0, (uint32_t)SL.zp};
+          P.rg[0] = RangePlan{a_v, MODE == MODE_SCORES ? 0 : t.n * phase_row_bytes(p), (uint32_t)SL.v};
+          P.rg[1] = RangePlan{a_k2, MODE == MODE_WEIGHTS ? 0 : t.n * kd.sub2, (uint32_t)SL.k2};
+          P.rg[2] = RangePlan{a_k4, MODE == MODE_WEIGHTS ? 0 : t.n * kd.sub4, (uint32_t)SL.k4};
+          P.rg[3] = RangePlan{a_k8, MODE == MODE_WEIGHTS ? 0 : t.n * kd.n8, (uint32_t)SL.k8};
+          P.rg[4] = RangePlan{a_sc, (p < 3 && MODE != MODE_SCORES) ? t.n * 2 : 0, (uint32_t)SL.sc};
+          P.rg[5] = RangePlan{a_zp, (p < 3 && MODE != MODE_SCORES) ? t.n * 2 : 0, (uint32_t)SL.zp};
           auto low4 = [](const unsigned char* x) { return (uint32_t)reinterpret_cast<uintptr_t>(x) & 15u; };
           P.info.phase = p; P.info.n = t.n;
           P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 | low4(a_v) << 12 |
@@ -604,10 +618,12 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   // then holds scores of rows g16+r and g16+r+8 for heads 2j and 2j+1 — the same two
   // heads whose output columns it accumulates in the P.V product.
   const bool he_ok = 2 * j < gcnt, ho_ok = 2 * j + 1 < gcnt;
-  const float c1 = TWO24 * INV_SQRT_D * LOG2E;             // scores are kept in base-2 units
+  // scores are kept in base-2 units (natural units when they are the result)
+  const float c1 = MODE == MODE_SCORES ? TWO24 * INV_SQRT_D : TWO24 * INV_SQRT_D * LOG2E;
   // an absent head gets an infinite bias: its scores are -inf without further tests
-  const float b1e = he_ok ? s_bias[2 * j] * INV_SQRT_D * LOG2E : INFINITY;
-  const float b1o = ho_ok ? s_bias[2 * j + 1] * INV_SQRT_D * LOG2E : INFINITY;
+  const float bsc = MODE == MODE_SCORES ? INV_SQRT_D : INV_SQRT_D * LOG2E;
+  const float b1e = (he_ok && MODE != MODE_WEIGHTS) ? s_bias[2 * j] * bsc : INFINITY;
+  const float b1o = (ho_ok && MODE != MODE_WEIGHTS) ? s_bias[2 * j + 1] * bsc : INFINITY;
   const bool has_mask = v.mask != nullptr;
   const bool k_aligned = !(kd.sub2 & 1) && !(kd.sub4 & 3) && !(kd.n8 & 3);
   const bool k_simple = kd.nsp2 == 1 && kd.nsp4 == 1 && kd.nkb8 == 1;   // one span per segment: straight-line code
@@ -616,7 +632,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  float m_e = M_NONE, m_o = M_NONE;                        // reference maxima of heads 2j, 2j+1 (same in every r)
+  // reference maxima of heads 2j, 2j+1 (same in every r); given weights are used as they are
+  float m_e = MODE == MODE_WEIGHTS ? 0.f : M_NONE, m_o = MODE == MODE_WEIGHTS ? 0.f : M_NONE;
   float l_e = 0.f, l_o = 0.f, zc_e = 0.f, zc_o = 0.f;      // partial sums over this thread's rows
   int cur_phase = -1;
 
@@ -795,8 +812,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
 #pragma unroll 1
         for (int g32 = row_b; g32 < nblocks * 32; g32 += 32 * FW) {
           // ── scores: two independent groups, two MMA chains each ──
-          float sxA[4], syA[4], sxB[4], syB[4];
-          {
+          float sxA[4] = {0.f, 0.f, 0.f, 0.f}, syA[4] = {0.f, 0.f, 0.f, 0.f}, sxB[4] = {0.f, 0.f, 0.f, 0.f},
+                syB[4] = {0.f, 0.f, 0.f, 0.f};
+          if (MODE != MODE_WEIGHTS) {
             uint2 q0 = make_uint2(0u, 0u), q1 = q0, q2 = q0, q3 = q0, q4 = q0;
             if (SIMPLE) {
               q0 = lds64<0>(qs_lane); q1 = lds64<256>(qs_lane); q2 = lds64<512>(qs_lane);
@@ -808,13 +826,14 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           // requested now, needed after the softmax: V scale / zero point of the four rows and the
           // first V words of both groups
           uint32_t rs[4] = {0u, 0u, 0u, 0u}, rz[4] = {0u, 0u, 0u, 0u};
-          if (P < 3) {
+          if (P < 3 && MODE != MODE_SCORES) {
             rs[0] = lds16(sca); rs[1] = lds16<16>(sca); rs[2] = lds16<32>(sca); rs[3] = lds16<48>(sca);
             rz[0] = lds16(zpa); rz[1] = lds16<16>(zpa); rz[2] = lds16<32>(zpa); rz[3] = lds16<48>(zpa);
           }
-          uint32_t wA0, wA1, wA2, wA3, xA0 = 0, xA1 = 0, xA2 = 0, xA3 = 0;
-          uint32_t wB0, wB1, wB2, wB3, xB0 = 0, xB1 = 0, xB2 = 0, xB3 = 0;
-          if (P == 3) {
+          uint32_t wA0 = 0, wA1 = 0, wA2 = 0, wA3 = 0, xA0 = 0, xA1 = 0, xA2 = 0, xA3 = 0;
+          uint32_t wB0 = 0, wB1 = 0, wB2 = 0, wB3 = 0, xB0 = 0, xB1 = 0, xB2 = 0, xB3 = 0;
+          if (MODE == MODE_SCORES) {
+          } else if (P == 3) {
             const uint2 a0 = lds64(va), a1 = lds64<256>(va), a2 = lds64<8 * 256>(va), a3 = lds64<9 * 256>(va);
             wA0 = a0.x; wA1 = a1.x; wA2 = a2.x; wA3 = a3.x; xA0 = a0.y; xA1 = a1.y; xA2 = a2.y; xA3 = a3.y;
             const uint2 b0 = lds64<16 * 256>(va), b1 = lds64<17 * 256>(va), b2 = lds64<24 * 256>(va), b3 = lds64<25 * 256>(va);
@@ -830,7 +849,31 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           s2[2] = fmaf(sxA[2] + syA[2], c1, -b1e); s2[3] = fmaf(sxA[3] + syA[3], c1, -b1o);
           s2[4] = fmaf(sxB[0] + syB[0], c1, -b1e); s2[5] = fmaf(sxB[1] + syB[1], c1, -b1o);
           s2[6] = fmaf(sxB[2] + syB[2], c1, -b1e); s2[7] = fmaf(sxB[3] + syB[3], c1, -b1o);
-          if (has_mask) {                                  // additive softmax mask (rarely given: everything it needs is re-read here)
+          if (MODE == MODE_SCORES) {                       // the scores are the result
+            const int64_t col0 = (int64_t)s_tile[stage].krow0 + g32 + r;    // stripe row = output column
+            float* oe = aux + (int64_t)(hq0 + 2 * j) * aux_stride + col0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (g32 + r + 8 * k < tn && col0 + 8 * k < t_eff) {
+                if (he_ok) oe[8 * k] = s2[2 * k];
+                if (ho_ok) oe[aux_stride + 8 * k] = s2[2 * k + 1];
+              }
+            }
+            k2a += 4 * FW * d2; k4a += 4 * FW * d4; k8a += 4 * FW * d8;
+            continue;
+          }
+          if (MODE == MODE_WEIGHTS) {                      // the weights are given
+            const int64_t col0 = (int64_t)s_tile[stage].krow0 + g32 + r;
+            const float* we = aux + (int64_t)(hq0 + 2 * j) * aux_stride + col0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const bool ok = g32 + r + 8 * k < tn;
+              s2[2 * k] = (ok && he_ok) ? we[8 * k] : 0.f;
+              s2[2 * k + 1] = (ok && ho_ok) ? we[aux_stride + 8 * k] : 0.f;
+              if (!ok) { rs[k] = 0u; rz[k] = 0u; }
+            }
+          }
+          if (MODE == MODE_ATTN && has_mask) {                                  // additive softmax mask (rarely given: everything it needs is re-read here)
             const int64_t ca = (int64_t)s_tile[stage].krow0 + g32 + r;   // stripe row = mask column
             const float* mask_e = v.mask + (int64_t)(hq0 + 2 * j) * v.mask_row_stride;
             const float* mask_o = mask_e + v.mask_row_stride;
@@ -842,7 +885,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
               }
             }
           }
-          if (g32 + 32 > tn) {                             // last, partial block of the tile: rows past its end are dead
+          if (MODE == MODE_ATTN && g32 + 32 > tn) {        // last, partial block of the tile: rows past its end are dead
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               if (g32 + r + 8 * k >= tn) { s2[2 * k] = -INFINITY; s2[2 * k + 1] = -INFINITY; rs[k] = 0u; rz[k] = 0u; }   // (their bytes may be non-finite)
@@ -852,7 +895,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           const float te = m_e + RESCALE_TH, to = m_o + RESCALE_TH;
           const float mxe = fmaxf(fmaxf(s2[0], s2[2]), fmaxf(s2[4], s2[6]));
           const float mxo = fmaxf(fmaxf(s2[1], s2[3]), fmaxf(s2[5], s2[7]));
-          if (__any_sync(0xffffffffu, mxe > te || mxo > to)) {
+          if (MODE == MODE_ATTN && __any_sync(0xffffffffu, mxe > te || mxo > to)) {
             float me = mxe, mo = mxo;
 #pragma unroll
             for (int o = 4; o < 32; o <<= 1) {
@@ -867,9 +910,14 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             m_e = ne; m_o = no;
           }
           float pe[8];
+          if (MODE == MODE_WEIGHTS) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) { pe[2 * k] = ex2(s2[2 * k] - m_e); pe[2 * k + 1] = ex2(s2[2 * k + 1] - m_o); }
-          l_e += (pe[0] + pe[2]) + (pe[4] + pe[6]); l_o += (pe[1] + pe[3]) + (pe[5] + pe[7]);
+            for (int k = 0; k < 8; ++k) pe[k] = s2[k];
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { pe[2 * k] = ex2(s2[2 * k] - m_e); pe[2 * k + 1] = ex2(s2[2 * k + 1] - m_o); }
+            l_e += (pe[0] + pe[2]) + (pe[4] + pe[6]); l_o += (pe[1] + pe[3]) + (pe[5] + pe[7]);
+          }
           uint32_t hh[4];                                  // row slot k x (head 2j, head 2j+1) as fp16 pairs
           if (P < 3) {
 #pragma unroll
@@ -911,6 +959,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     if (it + FSTAGES < total_tiles) bar_arrive(BAR_FREE + stage, CTA_THREADS);   // slot may be refilled
   }
 
+  if (MODE == MODE_SCORES) return;
   // ── merge the four workers and write the chunk's record ─────────────────────
   if (cur_phase >= 0) {                                    // accumulators to true units
 #pragma unroll
@@ -954,7 +1003,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         o = fmaf(red[(w * GH + hq) * D + d] - s_ml[w][hq][2], wgt, o);
       }
     }
-    if (direct) {
+    if (MODE == MODE_WEIGHTS) {                            // a plain weighted sum: nothing to normalise
+      out[((int64_t)view_idx * H_q + hq0 + hq) * D + d] = o;
+    } else if (direct) {
       out[((int64_t)view_idx * H_q + hq0 + hq) * D + d] = L > 0.f ? o / L : 0.f;
     } else {
       float* rec = rec0 + hq * rec_stride;
@@ -970,15 +1021,10 @@ using namespace rdkv;
 
 extern "C" int rdkv_decode_stage_bytes(int k_row_bytes_max) { return stage_capacity(k_row_bytes_max); }
 
-extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,
-                                        int H_q, int H_kv, int chunk_rows, int n_chunks, int k_row_bytes_max,
-                                        float* partials, float* out, int* status, void* stream) {
-  if (views == nullptr || q == nullptr || n_views < 0 || n_chunks <= 0 || chunk_rows <= 0) return RDKV_ERR_BAD_ARG;
-  if (partials == nullptr && !(n_chunks == 1 && out != nullptr)) return RDKV_ERR_BAD_ARG;
-  if (q_dtype < RDKV_F16 || q_dtype > RDKV_F32) return RDKV_ERR_BAD_ARG;
-  if (H_q <= 0 || H_kv <= 0 || H_q % H_kv != 0) return RDKV_ERR_BAD_SHAPE;
-  if (k_row_bytes_max <= 0 || k_row_bytes_max > 224) return RDKV_ERR_BAD_SHAPE;
-  if (n_views == 0) return RDKV_OK;
+template <int MODE>
+static int launch_fused(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q, int H_kv,
+                        int chunk_rows, int n_chunks, int k_row_bytes_max, float* partials, float* out, int* status,
+                        float* aux, int64_t aux_stride, int t_eff, void* stream) {
   const int g = H_q / H_kv;
   const int n_hgrp = (g + GH - 1) / GH;
   if (n_views > 65535 || (int64_t)H_kv * n_hgrp > 65535) return RDKV_ERR_TOO_LARGE;
@@ -987,10 +1033,53 @@ extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_view
   const size_t epilogue = (size_t)FW * GH * D * sizeof(float);
   if (smem < epilogue) smem = epilogue;
   if (smem > 227 * 1024) return RDKV_ERR_TOO_LARGE;
-  cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
   dim3 grid(n_chunks, H_kv * n_hgrp, n_views);
-  decode_fused_kernel<<<grid, CTA_THREADS, smem, (cudaStream_t)stream>>>(views, q, q_dtype, H_q, g, chunk_rows,
-                                                                     n_chunks, stage_bytes, partials, out, status);
+  decode_fused_kernel<MODE><<<grid, CTA_THREADS, smem, (cudaStream_t)stream>>>(
+      views, q, q_dtype, H_q, g, chunk_rows, n_chunks, stage_bytes, partials, out, status, aux, aux_stride, t_eff);
   return launch_status();
+}
+
+static int check_fused_args(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q, int H_kv,
+                            int k_row_bytes_max) {
+  if (views == nullptr || q == nullptr || n_views < 0) return RDKV_ERR_BAD_ARG;
+  if (q_dtype < RDKV_F16 || q_dtype > RDKV_F32) return RDKV_ERR_BAD_ARG;
+  if (H_q <= 0 || H_kv <= 0 || H_q % H_kv != 0) return RDKV_ERR_BAD_SHAPE;
+  if (k_row_bytes_max <= 0 || k_row_bytes_max > 224) return RDKV_ERR_BAD_SHAPE;
+  return RDKV_OK;
+}
+
+extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,
+                                        int H_q, int H_kv, int chunk_rows, int n_chunks, int k_row_bytes_max,
+                                        float* partials, float* out, int* status, void* stream) {
+  if (n_chunks <= 0 || chunk_rows <= 0) return RDKV_ERR_BAD_ARG;
+  if (partials == nullptr && !(n_chunks == 1 && out != nullptr)) return RDKV_ERR_BAD_ARG;
+  const int rc = check_fused_args(views, n_views, q, q_dtype, H_q, H_kv, k_row_bytes_max);
+  if (rc != RDKV_OK || n_views == 0) return rc;
+  return launch_fused<MODE_ATTN>(views, n_views, q, q_dtype, H_q, H_kv, chunk_rows, n_chunks, k_row_bytes_max,
+                                 partials, out, status, nullptr, 0, 0, stream);
+}
+
+extern "C" int rdkv_decode_scores(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,
+                                  int H_kv, int chunk_rows, int n_chunks, int k_row_bytes_max, int t_eff,
+                                  float* scores, int64_t scores_row_stride, int* status, void* stream) {
+  if (n_chunks <= 0 || chunk_rows <= 0 || scores == nullptr || t_eff < 0 || scores_row_stride < t_eff)
+    return RDKV_ERR_BAD_ARG;
+  if (n_views > 1) return RDKV_ERR_BAD_ARG;                 // one score matrix per call
+  const int rc = check_fused_args(views, n_views, q, q_dtype, H_q, H_kv, k_row_bytes_max);
+  if (rc != RDKV_OK || n_views == 0 || t_eff == 0) return rc;
+  return launch_fused<MODE_SCORES>(views, n_views, q, q_dtype, H_q, H_kv, chunk_rows, n_chunks, k_row_bytes_max,
+                                   nullptr, nullptr, status, scores, scores_row_stride, t_eff, stream);
+}
+
+extern "C" int rdkv_decode_weighted_sum(const rdkv_layer_view* views, int n_views, int H_q, int H_kv, int unit_rows,
+                                        int k_row_bytes_max, const float* weights, int64_t weights_row_stride,
+                                        float* out, int* status, void* stream) {
+  if (unit_rows <= 0 || weights == nullptr || out == nullptr || weights_row_stride < 0) return RDKV_ERR_BAD_ARG;
+  if (n_views > 1) return RDKV_ERR_BAD_ARG;                 // one weight matrix per call
+  const int rc = check_fused_args(views, n_views, weights, RDKV_F32, H_q, H_kv, k_row_bytes_max);
+  if (rc != RDKV_OK || n_views == 0) return rc;
+  return launch_fused<MODE_WEIGHTS>(views, n_views, weights, RDKV_F32, H_q, H_kv, unit_rows, 1, k_row_bytes_max,
+                                    nullptr, out, status, const_cast<float*>(weights), weights_row_stride, 0, stream);
 }

@@ -29,7 +29,8 @@ class DecodeTable:
     """
 
     def __init__(self, layers: Sequence[PackedKVLayer], new_v_only: Sequence[Optional[Tensor]], H_q: int,
-                 *, use_mask: bool = False, device=None, n_chunks: Optional[int] = None):
+                 *, use_mask: bool = False, device=None, n_chunks: Optional[int] = None,
+                 k_only: bool = False):
         if len(layers) == 0:
             raise ValueError("DecodeTable needs at least one layer")
         if len(new_v_only) != len(layers):
@@ -48,7 +49,7 @@ class DecodeTable:
             n2, n4, n8 = pl.K_ch_seg_bounds
             if n2 + n4 + n8 == 0 or n2 > 128 or n4 > 128 or n8 > 128:
                 raise ValueError("layer has no kept K channels or more than 128 in a segment")
-            if int(pl.n_v16) > 0 and nv is None:
+            if int(pl.n_v16) > 0 and nv is None and not k_only:
                 raise ValueError(f"layer {i} has fp16 rows but no new_v_only tensor")
             v, keep = layer_view(pl, nv if (nv is not None and int(pl.n_v16) > 0) else None, use_mask=use_mask)
             views[i] = v

@@ -44,11 +44,45 @@ def k_mixed_qk_dot_into(Q: torch.Tensor, packed_layer, T_eff: int, out: torch.Te
         return
     if T_eff <= 0:
         return
+    table = _scores_table(packed_layer, H_q)
+    if table is not None and int(T_eff) <= table.max_t_k:
+        # the score half of the fused tensor-core kernel; its one-view table is kept on the layer
+        # object, as the reference keeps its pre-squeezed views on the cache object
+        # (obkv_accel/fast_decode.py:813-816)
+        if not Q.is_contiguous():
+            Q = Q.contiguous()
+        rows = 256
+        check(lib().rdkv_decode_scores(ptr(table.views), 1, ptr(Q), q_dtype_tag(Q), H_q, table.H_kv, rows,
+                                       -(-int(T_eff) // rows), table.k_row_bytes_max, int(T_eff), ptr(out),
+                                       out.stride(0), ptr(table.status), stream_ptr(Q.device)), "rdkv_decode_scores")
+        return
     if Q.stride(1) != 1:
         Q = Q.contiguous()
     view, _keep = layer_view(packed_layer)
     check(lib().rdkv_k_scores(C.byref(view), ptr(Q), q_dtype_tag(Q), Q.stride(0), H_q, _num_kv_heads(packed_layer),
                               int(T_eff), ptr(out), out.stride(0), stream_ptr(Q.device)), "rdkv_k_scores")
+
+
+def _scores_table(packed_layer, H_q: int):
+    """One-view table of the layer for the fused kernel's score mode, cached on the layer; None
+    when the layer's shape is outside what that kernel takes (the scalar kernel then runs)."""
+    from .decode import DecodeTable
+    cached = getattr(packed_layer, "_rdkv_k_table", None)
+    if cached is not None and cached[0] == H_q:
+        return cached[1]
+    table = None
+    try:
+        if H_q % _num_kv_heads(packed_layer) == 0:
+            table = DecodeTable([packed_layer], [None], H_q, k_only=True)
+            if table.k_row_bytes_max > 224:
+                table = None
+    except (ValueError, AttributeError):
+        table = None
+    try:
+        packed_layer._rdkv_k_table = (H_q, table)
+    except AttributeError:
+        pass
+    return table
 
 
 def k_mixed_qk_dot(Q: torch.Tensor, packed_layer, T_eff: int) -> torch.Tensor:

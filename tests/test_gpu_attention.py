@@ -278,7 +278,9 @@ def test_full_size_linearity_and_permutation():
         b = v_dequant_weighted_sum_dispatch(w2, pl, V16=nv[0], n_v16_per_head=pl.n_v16_per_head, max_T_v=pl.T_eff)
         ab = v_dequant_weighted_sum_dispatch(0.25 * w + 0.75 * w2, pl, V16=nv[0],
                                              n_v16_per_head=pl.n_v16_per_head, max_T_v=pl.T_eff)
-        np.testing.assert_allclose(to_np(ab), to_np(0.25 * a + 0.75 * b), atol=1e-5, rtol=1e-4)
+        # (the weights enter the tensor-core product as fp16 pairs, as in the reference's V kernel:
+        #  linear up to that rounding)
+        assert_attn_close(to_np(ab), to_np(0.25 * a + 0.75 * b), f"linearity g={g}")
         # an exact reference for this size on the GPU-resident dequantised values of one head
         from oracle import ref_packing as RP
         layer = {k: to_np(v) if torch.is_tensor(v) else v for k, v in vars(pl).items()}
