@@ -317,13 +317,26 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
 class _HostIO:
     """Device staging buffer for the queries and the streams of the host-buffer call, kept on the table."""
 
-    def __init__(self, table: DecodeTable, q_dtype: torch.dtype, n_slices: int):
+    def __init__(self, table: DecodeTable, q_dtype: torch.dtype, n_slices: int, growing: bool):
         dev = table.device
         self.q = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=q_dtype, device=dev)
         self.out: Optional[Tensor] = None                  # device-side results; only for pageable out_host
-        self.streams = [torch.cuda.Stream(device=dev) for _ in range(n_slices)]
-        step = -(-table.n_views // n_slices)
-        self.ranges = [(a, min(a + step, table.n_views)) for a in range(0, table.n_views, step)]
+        self.key = (q_dtype, n_slices, growing)
+        n = table.n_views
+        if growing and n_slices > 1:
+            # ranges of 1 : 2 : 4 : ... : rest — the first upload, the only one no kernel hides, is short
+            unit = max(1, n // (2 ** n_slices - 1))
+            sizes = [unit * 2 ** i for i in range(n_slices - 1)]
+            sizes.append(n - sum(sizes))
+        else:
+            step = -(-n // n_slices)
+            sizes = [min(step, n - a) for a in range(0, n, step)]
+        self.ranges, a = [], 0
+        for sz in sizes:
+            if sz > 0:
+                self.ranges.append((a, a + sz))
+                a += sz
+        self.streams = [torch.cuda.Stream(device=dev) for _ in self.ranges]
 
 
 def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: Tensor, *,
@@ -331,7 +344,7 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
     """Host-buffer form of :func:`packed_decode_attention`: ``q_host`` [n_views,H_q,128]
     (fp16/bf16/fp32) and ``out_host`` [n_views,H_q,128] fp32 live in host memory.
 
-    The views are cut into ``slices`` ranges (default: up to 4, each at least one full wave of
+    The views are cut into ``slices`` ranges (default: two when each is at least one full wave of
     CTAs); every range uploads its queries and runs the
     kernel on a stream of its own, so the upload of one range overlaps the kernel of another.
     With a pinned ``out_host`` the kernels write their results straight into it (pinned host
@@ -346,13 +359,14 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
     if tuple(out_host.shape) != tuple(q_host.shape) or out_host.dtype != torch.float32 or not out_host.is_contiguous():
         raise ValueError("out_host must be contiguous float32 with q_host's shape")
     q_dtype_tag(q_host)
-    if slices is None:                                     # up to 4 ranges, each at least one full wave of CTAs
-        units = table.n_views * table.H_kv * table._n_hgrp
-        slices = min(4, units // (table._sms * table.CTAS_PER_SM))
+    growing = False
+    if slices is None:                                     # two ranges when each is at least a full wave of CTAs (measured best)
+        waves = (table.n_views * table.H_kv * table._n_hgrp) // (table._sms * table.CTAS_PER_SM)
+        slices = 2 if waves >= 2 else 1
     n_slices = max(1, min(int(slices), table.n_views))
     io: Optional[_HostIO] = getattr(table, "_host_io", None)
-    if io is None or io.q.dtype != q_host.dtype or len(io.streams) != n_slices:
-        io = _HostIO(table, q_host.dtype, n_slices)
+    if io is None or io.key != (q_host.dtype, n_slices, growing):
+        io = _HostIO(table, q_host.dtype, n_slices, growing)
         table._host_io = io
     direct = out_host.is_pinned()
     if not direct and io.out is None:
