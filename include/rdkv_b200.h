@@ -244,6 +244,28 @@ int rdkv_tail_attn_partial(const void* q, int q_dtype, int64_t n_views, int H_q,
                            int64_t kv_view_stride, int64_t kv_head_stride, int64_t kv_row_stride,
                            int n_new, const int32_t* n_new_per_view, float* partial, void* stream);
 
+/* ── prefill: importance scores that feed the allocator ───────────────────────
+ * Replaces _score_one_layer (obkv_fast.py:854-896) and apply_score_pooling
+ * (obkv_fast.py:208-246).
+ * rdkv_score_layer: aw [BH][R][T] attention weights of the observation window
+ * (BH = batch x KV heads, R = query heads per KV head x window positions), q
+ * [BH][R][D], k [BH][T][D] (element strides given) ->
+ *   layer_token   fp32 [BH][T] = sum_r aw (rounded to aw's dtype, as the reference's
+ *                                 aw.sum(...).float() is),
+ *   layer_channel fp32 [BH][D] = mean_r(q^2) * mean_t(k^2).
+ * scratch: fp32 [BH][rdkv_score_chunks(T)][D].
+ * rdkv_score_pool: sliding-window pooling (stride 1) of `rows` rows of `len` fp32
+ * scores; pool_max 0 = average, 1 = maximum; reflect 0 = zero padding with
+ * kernel_size taps, 1 = reflection padding with min(kernel_size, 2*len-1) taps;
+ * out_len must be len + 2*(taps/2) - taps + 1. */
+int rdkv_score_chunks(int T);
+int rdkv_score_layer(const void* aw, int aw_dtype, const void* q, int q_dtype, const void* k, int k_dtype,
+                     int64_t k_head_stride, int64_t k_row_stride, int BH, int R, int T, int D,
+                     float* scratch, float* layer_token, float* layer_channel, void* stream);
+int rdkv_score_pool(const float* scores, int64_t row_stride, int rows, int len, int pool_max,
+                    int kernel_size, int reflect, float* out, int64_t out_row_stride, int out_len,
+                    void* stream);
+
 /* ── prefill: every layer of a cache in one pass ──────────────────────────────
  * The reference packs a whole cache layer by layer (build_packed_cache,
  * obkv_accel/packing.py:1323-1421; driver loop obkv_fast.py:1098-1166); here the

@@ -1,0 +1,66 @@
+"""Importance scores that feed the bit allocator.
+
+Drop-ins for the reference's ``_score_one_layer`` (obkv_fast.py:854-896) and
+``apply_score_pooling`` (obkv_fast.py:208-246): same names, arguments and return shapes.
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from ._lib import check, lib, ptr, q_dtype_tag, require_cuda, stream_ptr
+
+
+def _score_one_layer(aw: Tensor, q: Tensor, o, v: Tensor, head_dim: int, v_score_type: str = "attn_linear",
+                     k: Tensor = None, k_score_type: str = "think"):
+    """aw [B,H_kv,g,W,T], q [B,H_kv,g,W,D], v / k [B,H_kv,T,D] ->
+    (layer_token [B,H_kv,T] = sum_{g,w} aw, layer_channel [B,H_kv,D] = mean(q^2) * mean_t(k^2)), fp32.
+    ``o`` and ``v`` are accepted for signature compatibility (unused, as in the reference)."""
+    if v_score_type != "attn_linear":
+        raise ValueError(f"Unsupported v_score_type={v_score_type!r}; expected 'attn_linear'.")
+    if k_score_type != "think":
+        raise ValueError(f"Unsupported k_score_type={k_score_type!r}; expected 'think'.")
+    if k is None:
+        raise ValueError("k_score_type='think' requires the keys tensor (k=...).")
+    require_cuda(aw, "aw"); require_cuda(q, "q"); require_cuda(k, "k")
+    B, H, g, W, T = aw.shape
+    D = int(q.shape[-1])
+    if tuple(q.shape) != (B, H, g, W, D) or tuple(k.shape) != (B, H, T, D) or D != int(head_dim):
+        raise ValueError("q must be [B,H_kv,g,W,D] and k [B,H_kv,T,D]")
+    aw, q = aw.contiguous(), q.contiguous()
+    if k.stride(3) != 1 or k.stride(0) != H * k.stride(1):
+        k = k.contiguous()
+    dev = aw.device
+    token = torch.empty((B, H, T), dtype=torch.float32, device=dev)
+    channel = torch.empty((B, H, D), dtype=torch.float32, device=dev)
+    scratch = torch.empty((B * H, lib().rdkv_score_chunks(T), D), dtype=torch.float32, device=dev)
+    check(lib().rdkv_score_layer(ptr(aw), q_dtype_tag(aw), ptr(q), q_dtype_tag(q), ptr(k), q_dtype_tag(k),
+                                 k.stride(1), k.stride(2), B * H, g * W, T, D, ptr(scratch), ptr(token),
+                                 ptr(channel), stream_ptr(dev)), "rdkv_score_layer")
+    return token, channel
+
+
+def apply_score_pooling(scores: Tensor, pool_type: str, kernel_size: int, padding_mode: str = "zero") -> Tensor:
+    """Sliding-window average (``pool_type == "avg"``) or maximum of a score row / of the rows of a
+    2-D score tensor; ``padding_mode`` "zero" or "reflect" (the window shrinks to ``2*len-1`` taps
+    on very short rows, as in the reference)."""
+    require_cuda(scores, "scores")
+    if scores.dim() not in (1, 2):
+        raise ValueError(f"Expected score tensor rank 1 or 2, got shape={tuple(scores.shape)}.")
+    x = scores.reshape(1, -1) if scores.dim() == 1 else scores
+    if x.dtype != torch.float32:
+        x = x.float()
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    rows, n = int(x.shape[0]), int(x.shape[1])
+    reflect = padding_mode == "reflect"
+    if reflect and n <= 0:
+        raise ValueError("Cannot reflect-pool an empty score sequence.")
+    taps = min(int(kernel_size), 2 * n - 1) if reflect else int(kernel_size)
+    out_len = n + 2 * (taps // 2) - taps + 1
+    out = torch.empty((rows, out_len), dtype=torch.float32, device=x.device)
+    check(lib().rdkv_score_pool(ptr(x), x.stride(0), rows, n, 0 if pool_type == "avg" else 1, int(kernel_size),
+                                1 if reflect else 0, ptr(out), out.stride(0), out_len, stream_ptr(x.device)),
+          "rdkv_score_pool")
+    out = out.to(scores.dtype) if scores.dtype != torch.float32 else out
+    return out[0] if scores.dim() == 1 else out

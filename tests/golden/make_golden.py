@@ -186,5 +186,36 @@ def main():
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 
+def make_scoring():
+    """Scoring / pooling vectors from the reference's own functions (obkv_fast.py:208-246, 854-896)."""
+    import obkv_fast as ref_fast
+    out = {}
+    g = torch.Generator().manual_seed(1234)
+    B, H, gq, W, T, D = 1, 2, 4, 8, 203, 128
+    for tag, dt in (("f32", torch.float32), ("f16", torch.float16)):
+        aw = torch.softmax(torch.randn(B, H, gq, W, T, generator=g) * 3, dim=-1).to(dt)
+        q = torch.randn(B, H, gq, W, D, generator=g).to(dt)
+        k = torch.randn(B, H, T, D, generator=g).to(dt)
+        v = torch.randn(B, H, T, D, generator=g).to(dt)
+        tok, ch = ref_fast._score_one_layer(aw, q, None, v, D, k=k)
+        out[f"score_{tag}_aw"] = aw.float().numpy(); out[f"score_{tag}_q"] = q.float().numpy()
+        out[f"score_{tag}_k"] = k.float().numpy()
+        out[f"score_{tag}_token"] = tok.numpy(); out[f"score_{tag}_channel"] = ch.numpy()
+    x = torch.randn(3, 57, generator=g)
+    out["pool_x"] = x.numpy()
+    for pt in ("avg", "max"):
+        for mode in ("zero", "reflect"):
+            for ks in (5, 4, 1):
+                out[f"pool_{pt}_{mode}_{ks}"] = ref_fast.apply_score_pooling(x, pt, ks, mode).numpy()
+    short = torch.randn(2, generator=g)
+    out["pool_short_x"] = short.numpy()
+    out["pool_short_avg_reflect_5"] = ref_fast.apply_score_pooling(short, "avg", 5, "reflect").numpy()
+    one = torch.randn(1, generator=g)
+    out["pool_one_x"] = one.numpy()
+    out["pool_one_avg_reflect_5"] = ref_fast.apply_score_pooling(one, "avg", 5, "reflect").numpy()
+    np.savez_compressed(os.path.join(HERE, "scoring.npz"), **out)
+
+
 if __name__ == "__main__":
     main()
+    make_scoring()

@@ -98,3 +98,24 @@ def test_knapsack_default_epsilon(golden_knapsack):
     from rdkv_b200.knapsack_solver import DEFAULT_EPSILON
     got = RK.knapsack_batched(golden_knapsack["defeps_scores"], 2.0, DEFAULT_EPSILON)
     assert np.array_equal(got, golden_knapsack["defeps_bits"])
+
+
+def test_scoring_oracle_matches_reference_vectors():
+    """Importance scoring and score pooling: the numpy restatement against vectors produced by the
+    reference's own functions (pooling bit for bit; the score sums to fp32 summation-order noise)."""
+    from conftest import load_golden
+    from oracle import ref_scoring as RS
+    g = load_golden("scoring.npz")
+    for tag, dt in (("f32", np.float32), ("f16", np.float16)):
+        tok, ch = RS.score_one_layer(g[f"score_{tag}_aw"].astype(dt), g[f"score_{tag}_q"].astype(dt),
+                                     g[f"score_{tag}_k"].astype(dt))
+        np.testing.assert_allclose(tok, g[f"score_{tag}_token"], rtol=2e-3 if dt == np.float16 else 1e-5, atol=1e-6)
+        np.testing.assert_allclose(ch, g[f"score_{tag}_channel"], rtol=1e-5)
+    for key in g:
+        if key.startswith("pool_") and not key.endswith("_x"):
+            parts = key.split("_")
+            src = g["pool_x"] if parts[1] in ("avg", "max") else g[f"pool_{parts[1]}_x"]
+            pt, mode, ks = parts[-3], parts[-2], int(parts[-1])
+            got = RS.score_pooling(src, pt, ks, mode)
+            assert got.shape == g[key].shape, key
+            assert np.array_equal(got, g[key]), key
