@@ -471,6 +471,45 @@ def run_pack(args, rank, world, device):
     return line
 
 
+def run_score(args, rank, world, device):
+    """Importance scoring of one layer in config-1 shape (8 KV heads x 4 query heads x 32-position
+    observation window over 32768 tokens, fp16) followed by the default pooling (avg, 5, reflect)."""
+    if rank != 0:
+        return None
+    from rdkv_b200.scoring import _score_one_layer, apply_score_pooling
+    B, H, g, W, T, D = 1, 8, 4, 32, 32768, 128
+    gen = torch.Generator(device=device)
+    gen.manual_seed(77)
+    n_rep = 4                                               # rotate inputs: 4 x 201 MB > L2
+    aws = [torch.softmax(torch.randn(B, H, g, W, T, generator=gen, device=device) * 2, dim=-1).half() for _ in range(n_rep)]
+    qs = [torch.randn(B, H, g, W, D, generator=gen, device=device).half() for _ in range(n_rep)]
+    ks = [torch.randn(B, H, T, D, generator=gen, device=device).half() for _ in range(n_rep)]
+
+    def step(i):
+        j = i % n_rep
+        tok, ch = _score_one_layer(aws[j], qs[j], None, ks[j], D, k=ks[j])
+        apply_score_pooling(tok[0], "avg", 5, "reflect")
+
+    for i in range(args.warmup):
+        step(i)
+    sampler = ClockSampler(device.index or 0)
+    with sampler:
+        ms = timed_steps(step, args.steps, lambda: None)
+    sec = ms / 1e3 / args.steps
+    moved = aws[0].numel() * 2 + ks[0].numel() * 2 + qs[0].numel() * 2 + H * T * 4 * 3
+    peak, kind = load_peaks()
+    return {"metric": "importance scoring + pooling, layers/s", "value": 1.0 / sec, "unit": "layers/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp16 in, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": "score one layer: aw [1,8,4,32,32768] fp16, K [1,8,32768,128] fp16, avg-5 reflect pooling",
+                       "l2": "4 input sets of 201 MB rotated > L2"},
+            "roofline": {"bound": "hbm", "achieved": moved / sec / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": moved / sec / 1e9 / peak, "traffic": None, "peak_kind": kind,
+                         "kernel": "token_score_kernel + channel_ksq_kernel + pool_kernel (whole step, 5 launches)",
+                         "algorithmic_bytes_per_step": moved},
+            "gpu_launches": 4 * args.steps, "clocks": sampler.summary()}
+
+
 def run_alloc(args, rank, world, device):
     """Config 2: 256 V rows of 32768 token scores + 256 K rows of 128 channel scores, lognormal(0,1.5),
     budget 2.0 bits/token for V, per-head K budget derived from the V result; 60 bisection steps."""
@@ -523,7 +562,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="rdkv_b200", choices=["rdkv_b200", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "pack", "alloc"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "pack", "alloc", "score"])
     ap.add_argument("--small", action="store_true", help="2 layers x batch 2 (smoke-sized case)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling-sized runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -553,6 +592,8 @@ def main():
             line = run_decode(args, rank, world, device)
         elif args.workload == "pack":
             line = run_pack(args, rank, world, device)
+        elif args.workload == "score":
+            line = run_score(args, rank, world, device)
         else:
             line = run_alloc(args, rank, world, device)
         if rank == 0 and line is not None:
