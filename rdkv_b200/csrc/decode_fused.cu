@@ -318,6 +318,52 @@ __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const u
   }
 }
 
+// Last step of a CTA: the partial results of the compute warps (o in `red` [FW][GH][128], and per
+// warp and head m, l and the zero-point term in `ml` [FW][GH][3]) become the CTA's result.  Kept
+// out of line so that its registers do not weigh on the main loop.  how: 0 = (m, l, o) record,
+// 1 = normalised output, 2 = plain sum (weights were given).
+__device__ __noinline__ void final_merge(const float* red, const float* ml, float (*fin)[FW + 3], int gcnt, int how,
+                                         float* out_rows, float* rec0, int64_t rec_stride) {
+  const int tid = threadIdx.x;
+  if (tid < GH) {                                          // per head: maximum, weight of every warp, l, zero-point term
+    const int hq = tid;
+    float M = M_NONE;
+#pragma unroll
+    for (int w = 0; w < FW; ++w) M = fmaxf(M, ml[(w * GH + hq) * 3]);
+    float L = 0.f, Z = 0.f;
+#pragma unroll
+    for (int w = 0; w < FW; ++w) {
+      const float wgt = ex2(ml[(w * GH + hq) * 3] - M);
+      L = fmaf(ml[(w * GH + hq) * 3 + 1], wgt, L);
+      Z = fmaf(ml[(w * GH + hq) * 3 + 2], wgt, Z);
+      fin[hq][w] = wgt;
+    }
+    fin[hq][FW] = M; fin[hq][FW + 1] = L; fin[hq][FW + 2] = Z;
+  }
+  __syncthreads();
+  if (tid < D) {                                           // thread = channel; heads in turn
+    const int d = tid;
+    for (int hq = 0; hq < gcnt; ++hq) {
+      float o = -fin[hq][FW + 2];
+#pragma unroll
+      for (int w = 0; w < FW; ++w) o = fmaf(red[(w * GH + hq) * D + d], fin[hq][w], o);
+      const float L = fin[hq][FW + 1];
+      if (how == 2) {
+        out_rows[hq * D + d] = o;
+      } else if (how == 1) {
+        out_rows[hq * D + d] = L > 0.f ? o / L : 0.f;
+      } else {
+        float* rec = rec0 + hq * rec_stride;
+        rec[4 + d] = o;
+        if (d == 0) {                                      // m in natural-log units; -inf marks an empty record
+          const float M = fin[hq][FW];
+          rec[0] = M <= M_NONE ? -INFINITY : M * LN2; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f;
+        }
+      }
+    }
+  }
+}
+
 // MODE_ATTN: the whole attention block.  MODE_SCORES: only the q.K scores of the live rows, written
 // to aux[(query head) * aux_stride + stripe row] for stripe rows < t_eff (the K kernel of the
 // two-stage interface; V is not read).  MODE_WEIGHTS: the softmax weights are given in
@@ -341,6 +387,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   __shared__ CtaGeom G;
   __shared__ float s_bias[GH];
   __shared__ float s_ml[FW][GH][3];               // per warp: m, l, zero-point term
+  __shared__ float s_fin[GH][FW + 3];             // final merge: weight of each warp's partial; M, L, zero-point term
   __shared__ TileInfo s_tile[FSTAGES];
   __shared__ TilePlan s_plan[PLAN_TILES];          // private to the staging warp
   __shared__ __align__(8) uint64_t s_full[FSTAGES];   // tile in slot s has landed
@@ -987,32 +1034,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     o0[ch] = acc[i][0]; o1[ch] = acc[i][1]; o0[ch + 1] = acc[i][2]; o1[ch + 1] = acc[i][3];
   }
   __syncthreads();
-  for (int i = tid; i < gcnt * D; i += blockDim.x) {
-    const int hq = i / D, d = i % D;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < FW; ++w) M = fmaxf(M, s_ml[w][hq][0]);
-    float L = 0.f, o = 0.f;
-    if (M != -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < FW; ++w) {
-        const float mw = s_ml[w][hq][0];
-        if (mw == -INFINITY) continue;
-        const float wgt = ex2(mw - M);
-        L = fmaf(s_ml[w][hq][1], wgt, L);
-        o = fmaf(red[(w * GH + hq) * D + d] - s_ml[w][hq][2], wgt, o);
-      }
-    }
-    if (MODE == MODE_WEIGHTS) {                            // a plain weighted sum: nothing to normalise
-      out[((int64_t)view_idx * H_q + hq0 + hq) * D + d] = o;
-    } else if (direct) {
-      out[((int64_t)view_idx * H_q + hq0 + hq) * D + d] = L > 0.f ? o / L : 0.f;
-    } else {
-      float* rec = rec0 + hq * rec_stride;
-      rec[4 + d] = o;
-      if (d == 0) { rec[0] = M <= M_NONE ? -INFINITY : M * LN2; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }   // m in natural-log units
-    }
-  }
+  final_merge(red, &s_ml[0][0][0], s_fin, gcnt, MODE == MODE_WEIGHTS ? 2 : direct ? 1 : 0,
+              out + ((int64_t)view_idx * H_q + hq0) * D, rec0, rec_stride);
 }
 
 }  // namespace rdkv
