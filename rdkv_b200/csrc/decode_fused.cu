@@ -1,22 +1,19 @@
 // Fused split-sequence decode attention over the packed cache (sm_100a).
 //
-// One CTA = (view, KV head, chunk of live rows); its 128 threads stage tiles of up to
-// 256 rows into a 2-slot shared-memory ring with 16-byte cp.async copies (a tile is six
-// small byte ranges: measured here, per-lane LDGSTS sustains them better than one
-// bulk-copy instruction per range), and each of the 4 warps works through a quarter of
-// the tile's rows.  Per 16 rows a warp
-//   * computes q.K scores on the tensor cores (mma.sync m16n8k16, query heads on M,
-//     rows on N): packed 2/4/8-bit K codes are masked in place into fp16
-//     SUBNORMAL integers (code * 2^-24, exact), so unpacking is one AND per pair
-//     of codes; bit-position factors (4^v, 16) are folded into q*scale;
-//   * keeps an online softmax per query head in base 2 (lazy rescale);
-//   * feeds exp2(s-m)*v_scale as the B operand of the P.V product with V codes,
-//     again masked in place, as the A operand (channels on M, rows on K).
-// The score fragments of the first product are, element for element, the B
-// fragments of the second, so probabilities never leave registers.
-// Zero points are handled outside the products: sum_c zp*q*scale once per CTA
-// (K side, reference "bias trick", obkv_accel/triton_k_kernel.py:14-16) and
-// sum_t p*scale*zp per head (V side).
+// One CTA = (view, KV head, chunk of live rows), 160 threads.  Warp 4 (the staging warp) works out
+// the CTA's geometry, plans its tiles (up to 256 rows: six contiguous byte ranges each) and streams
+// them into a 2-slot shared-memory ring with one bulk copy per range, completion counted on an
+// mbarrier.  Warps 0-3 (the compute warps) fold the queries meanwhile and then work through the
+// tiles, 32 rows (two 16-row MMA groups) per warp and step:
+//   * q.K scores on the tensor cores (mma.sync m16n8k16, rows on M, query heads on N): packed
+//     2/4/8-bit K codes are masked in place into fp16 SUBNORMAL integers (code * 2^-24, exact), so
+//     unpacking is one AND per pair of codes; bit-position factors (4^v, 16) are folded into q*scale;
+//   * an online softmax per query head in base 2 with a lazily moved reference maximum;
+//   * exp2(s-m)*v_scale, transposed in registers (movmatrix), as the B operand of the P.V product
+//     with V codes, again masked in place, as the A operand (channels on M, rows on K).
+// Probabilities never leave registers.  Zero points are handled outside the products:
+// sum_c zp*q*scale once per CTA (K side, reference "bias trick",
+// obkv_accel/triton_k_kernel.py:14-16) and sum_t p*scale*zp per head (V side).
 #include <type_traits>
 
 #include "rdkv_common.cuh"
@@ -86,7 +83,6 @@ __device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp16_partial(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 // mbarrier (shared memory, CTA scope).  A tile's arrival is signalled asynchronously: every
 // staging lane posts one arrival that fires when its cp.async copies have landed.
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -182,13 +178,6 @@ __device__ __forceinline__ uint32_t lds32_unaligned(uint32_t a) {
   const uint32_t lo = lds32(a & ~3u), hi = lds32<4>(a & ~3u);
   return __funnelshift_r(lo, hi, (a & 3u) * 8);
 }
-// 32 bits starting at an arbitrary byte offset of a shared-memory buffer.
-// `base` must be 4-byte aligned.
-__device__ __forceinline__ uint32_t lds_unaligned(const unsigned char* base, int off) {
-  const uint32_t* p = reinterpret_cast<const uint32_t*>(base + (off & ~3));
-  return __funnelshift_r(p[0], p[1], (off & 3) * 8);
-}
-
 // ── K channel-slot map: which padded channel slot feeds MMA k-index e of thread j ──
 // e = 0..3 stands for k = 2j, 2j+1, 2j+8, 2j+9.  Returns the slot or -1, and the
 // power-of-two factor the masked code carries (folded into q*scale).
@@ -276,27 +265,9 @@ __device__ __forceinline__ bool blocks_inside(const unsigned char* lo, const uns
   return a >= reinterpret_cast<uintptr_t>(t_lo) && b <= reinterpret_cast<uintptr_t>(t_hi);
 }
 
-// Stage one byte range with 16-byte copies: the byte at global address x lands at
-// dst + (x - (src & ~15)).  All covering blocks lie inside the tensor.
-// `tid` runs over the NT threads that share the copy.
-template <int MAX_IT, int NT>
-__device__ __forceinline__ void stage_range(uint32_t dst, const unsigned char* src, int len, int tid) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(src), a0 = a & ~(uintptr_t)15;
-  const int nblk = (int)((((a + len + 15) & ~(uintptr_t)15) - a0) >> 4);
-  const unsigned char* s0 = reinterpret_cast<const unsigned char*>(a0) + 16 * tid;
-  const uint32_t d0 = dst + 16 * tid;
-  if (MAX_IT > 0) {                                        // size known to fit MAX_IT rounds of NT copies
-#pragma unroll
-    for (int i = 0; i < MAX_IT; ++i)
-      if (tid + NT * i < nblk) cp16(d0 + 16 * NT * i, s0 + 16 * NT * i);
-  } else {
-#pragma unroll 4
-    for (int b = tid; b < nblk; b += NT) cp16(dst + 16 * b, reinterpret_cast<const unsigned char*>(a0) + 16 * b);
-  }
-}
-
-// Same for a range whose covering blocks may stick out of the tensor [t_lo, t_hi) (a
-// tensor start or end that is not 16-byte aligned): a block crossing the end is read
+// Stage one byte range whose covering 16-byte blocks may stick out of its tensor [t_lo, t_hi) (a
+// tensor start or end that is not 16-byte aligned) with per-lane 16-byte cp.async copies: the
+// byte at global address x lands at dst + (x - (src & ~15)); a block crossing the end is read
 // partially and zero-filled, a block crossing the start is copied byte by byte.
 __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const unsigned char* src, int len,
                                                  const unsigned char* t_lo, const unsigned char* t_hi, int tid,

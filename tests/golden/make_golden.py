@@ -1,7 +1,8 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own
 Python code (PyTorch CPU kernels) on seeded inputs.
 
-    python tests/golden/make_golden.py [/path/to/reference/checkout]
+    python tests/golden/make_golden.py /path/to/reference/checkout
+    (or RDKV_REFERENCE=/path/to/reference/checkout in the environment)
 
 The reference checkout is only needed to (re)generate the files; the tests read
 the committed .npz files and never import the reference.  Inputs are stored
@@ -17,7 +18,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RDKV_REFERENCE", "")
+if not os.path.isdir(REF):
+    raise SystemExit("give the path of the reference checkout (argument or RDKV_REFERENCE)")
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
 sys.path.insert(0, ROOT)
