@@ -105,6 +105,32 @@ __device__ __forceinline__ unsigned quant_code(float x, const QParam& p) {
   return (unsigned)rintf(fminf(fmaxf(y, 0.f), p.qmax));
 }
 
+// quant_code without the division in the common case.  rinv = RN(1/scale).  x*rinv differs from the
+// rounded quotient by less than 2^-14 wherever the code is not decided by the clamp (|quotient| <= 256
+// there), so after adding the zero point the two sums differ by < 1.3e-4 and round to the same
+// integer unless the sum lies that close to a half-integer; those cases take the exact path.
+// Non-finite inputs behave as in quant_code (NaN -> code 0, +-inf -> the clamp).
+__device__ __forceinline__ unsigned quant_code_fast(float x, float rinv, const QParam& p) {
+  const float y = __fadd_rn(__fmul_rn(x, rinv), p.zp);
+  const float yc = fminf(fmaxf(y, 0.f), p.qmax);
+  const float c = __fadd_rn(__fadd_rn(yc, 12582912.f), -12582912.f);   // round half to even for 0 <= yc < 2^22
+  if (fabsf(__fadd_rn(fabsf(__fsub_rn(y, c)), -0.5f)) < 2.5e-4f) return quant_code(x, p);
+  return (unsigned)c;
+}
+
+// min / max over the 32 lanes of a full warp in one instruction each (NaN operands are ignored,
+// as by fminf / fmaxf)
+__device__ __forceinline__ float warp_min_redux(float v) {
+  float r;
+  asm volatile("redux.sync.min.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float warp_max_redux(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+
 __device__ __forceinline__ uint16_t f2h_bits(float x) { return __half_as_ushort(__float2half_rn(x)); }
 
 // ───────────────────────────── V: one warp per row ───────────────────────────
@@ -297,13 +323,14 @@ __device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int bl
     float x[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) x[q] = h2f(row[lane + 32 * q]);
-    const float lo = warp_min(fminf(fminf(x[0], x[1]), fminf(x[2], x[3])));
-    const float hi = warp_max(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])));
+    const float lo = warp_min_redux(fminf(fminf(x[0], x[1]), fminf(x[2], x[3])));
+    const float hi = warp_max_redux(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])));
     const int qbits = seg == 0 ? 2 : seg == 1 ? 4 : 8;
     const QParam qp = make_qparam(lo, hi, (float)((1 << qbits) - 1));
+    const float rinv = __frcp_rn(qp.scale);
     unsigned c[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) c[q] = quant_code(x[q], qp);
+    for (int q = 0; q < 4; ++q) c[q] = quant_code_fast(x[q], rinv, qp);
     if (seg == 0) {
       dst[lane] = (uint8_t)(c[0] | (c[1] << 2) | (c[2] << 4) | (c[3] << 6));
     } else if (seg == 1) {
@@ -593,11 +620,12 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
     else if (b < sub2) { ns = 4; sl0 = b; step = sub2; shift = 2; qmax = 3.f; dst = A.k2; width = sub2; col = b; }
     else if (b < sub2 + sub4) { ns = 2; sl0 = n2p + b - sub2; step = sub4; shift = 4; qmax = 15.f; dst = A.k4; width = sub4; col = b - sub2; }
     else { ns = 1; sl0 = n2p + n4p + b - sub2 - sub4; step = 0; shift = 0; qmax = 255.f; dst = A.k8; width = n8p; col = b - sub2 - sub4; }
-    int ch[4]; float sc[4], zp[4];
+    int ch[4]; float sc[4], zp[4], rinv[4];
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
       const int sl = sl0 + (v < ns ? v : 0) * step;
       ch[v] = s_ch[sl]; sc[v] = s_scale[sl]; zp[v] = s_zp[sl];
+      rinv[v] = __frcp_rn(sc[v]);
     }
     uint8_t* out = dst + ((int64_t)h * rows_k + row0 + warp * PACKK_RPW) * width + col;
 #pragma unroll 4
@@ -612,7 +640,7 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
         if (v < ns) {
           const float x = (tok >= 0 && ch[v] >= 0) ? h2f(row[ch[v]]) : 0.f;
           QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
-          byte |= quant_code(x, qp) << (v * shift);
+          byte |= quant_code_fast(x, rinv[v], qp) << (v * shift);
         }
       }
       out[(int64_t)k * width] = (uint8_t)byte;

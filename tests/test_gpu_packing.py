@@ -132,6 +132,40 @@ def test_config0_layer_matches_oracle():
     assert tuple(packed.K_2bit.shape) == (1, 8, 1024, 6) and tuple(packed.V_4bit.shape) == (1, 8, 384, 64)
 
 
+def test_quotients_on_and_next_to_half_integers():
+    """Values built so that (x - lo) / scale lands exactly on, or one fp16 step off, a half-integer for
+    most elements: the rounding then depends on the last bit of the IEEE quotient.  Integer-valued rows
+    with a power-of-two-ish range give exact ties; fp16 neighbours of those give the near misses."""
+    from oracle import ref_packing as RP
+    from rdkv_b200 import synth
+    rng = np.random.default_rng(20250607)
+    H, T, D = 2, 512, 128
+    seed = synth.unit_seed(11)
+    v_bits = synth.make_v_bits(H, T, 384, seed=seed).numpy()
+    k_bits = synth.make_k_bits(H, seed=seed).numpy()
+
+    def tie_tensor():
+        # per (head, token): integers in [0, 2*qmax] for some qmax -> scale 2 (8-bit: 510/255), quotient k/2
+        base = rng.integers(0, 511, size=(1, H, T, D)).astype(np.float32)
+        base[..., 0] = 0.0
+        base[..., 1] = 510.0          # V rows: lo 0, hi 510 -> scale 2 at 8 bits, 34 at 4 bits, 170 at 2 bits
+        base[:, :, 0, :] = 0.0
+        base[:, :, 1, :] = 510.0        # K channels: same range along the token axis
+        x = base.astype(np.float16)
+        nudge = rng.integers(-1, 2, size=x.shape).astype(np.int16)          # one fp16 step down / none / up
+        nudge[..., :2] = 0
+        nudge[:, :, :2, :] = 0
+        nudge[base == 0.0] = 0        # (0 minus one step would be a NaN pattern)
+        y = (x.view(np.int16) + nudge).view(np.float16)
+        return np.ascontiguousarray(y)
+
+    K, V = tie_tensor(), tie_tensor()
+    packed, nv = _pack_kv_gpu(K, V, v_bits, k_bits, 4)
+    want, want_nv = RP.pack_kv(K, V, v_bits, k_bits, 4)
+    assert_layer_equal(layer_to_np(packed), want, "ties.")
+    assert np.array_equal(to_np(nv), want_nv)
+
+
 def test_pack_kv_layers_equals_per_layer_packing():
     """All layers in one pass: every layer bit-identical to pack_kv on that layer (tall
     shared tensors, ragged and per-layer different segment counts, strided head views),
