@@ -238,20 +238,25 @@ __device__ __forceinline__ void pack_v_body(const PackVArgs& A, int h, int block
   }
 }
 
-// D == 128: a warp packs PACKV_ROWS128 slots at once, everything in registers.  Lane l holds
-// channels l, l+32, l+64, l+96 of a row — exactly the four codes of byte l of a quarter-split
-// 2-bit row and the code pairs of bytes l and l+32 of a half-split 4-bit row — so no data moves
-// between lanes; the loads of all rows are in flight together.
-constexpr int PACKV_CTA_ROWS128 = 128;                       // slots per CTA
-constexpr int PACKV_RPW128 = PACKV_CTA_ROWS128 / PACKV_WARPS;   // rows per warp (all loaded at once)
+// D == 128: four lanes per slot, eight slots per warp, everything in registers.  Lane s of a
+// slot's four loads channels 32i + 8s .. +7 (i = 0..3) as 16-byte words and quantises them into four
+// "planes" of eight one-byte codes; the packed row is then a few shifts and ORs of whole planes:
+//   2-bit (byte b = channels b, b+32, b+64, b+96):  bytes 8s..8s+7  = P0 | P1<<2 | P2<<4 | P3<<6
+//   4-bit (byte b = channels b, b+64):              bytes 32i+8s..  = P[i] | P[i+2]<<4   (i = 0, 1)
+//   8-bit:                                          bytes 32i+8s..  = P[i]
+// so codes never move between lanes and every store is 8 bytes.  The per-row work (where the row
+// comes from, its extrema, scale and zero point) is paid once per eight rows of a warp instruction.
+constexpr int PACKV_CTA_ROWS128 = PACKV_WARPS * 8;           // slots per CTA
 
-// Needs `rows`: PACKV_CTA_ROWS128 x 128 fp16 of shared memory, 8-byte aligned.  Rows of V that do
-// not start on 8-byte boundaries are read element by element.
-__device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int block_x, uint16_t* rows) {
-  __shared__ int s_src[PACKV_CTA_ROWS128];                    // source token, -1: pad row, -2: beyond the last slot
-  __shared__ int s_seg[PACKV_CTA_ROWS128], s_j[PACKV_CTA_ROWS128], s_base[PACKV_CTA_ROWS128];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+__device__ __forceinline__ void store8(uint8_t* dst, uint2 v, bool aligned) {
+  if (aligned) { *reinterpret_cast<uint2*>(dst) = v; return; }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) dst[e] = (uint8_t)((e < 4 ? v.x : v.y) >> (8 * (e & 3)));
+}
+
+__device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int block_x) {
   constexpr int D = 128;
+  const int s = threadIdx.x & 3;
   int n[4];
   {
     const int32_t* c = A.counts + h * A.counts_row_stride;
@@ -265,85 +270,106 @@ __device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int bl
     }
   }
   const int slots = A.max_n2 + A.max_n4 + A.max_n8 + A.max_n16;
-  const int slot0 = block_x * PACKV_CTA_ROWS128;
-  if (slot0 >= slots) return;
-  if (threadIdx.x < PACKV_CTA_ROWS128) {                      // one slot per thread: where its row comes from
-    const int slot = slot0 + threadIdx.x;
-    int sg, j;
-    if (slot < A.max_n2) { sg = 0; j = slot; }
-    else if (slot < A.max_n2 + A.max_n4) { sg = 1; j = slot - A.max_n2; }
-    else if (slot < A.max_n2 + A.max_n4 + A.max_n8) { sg = 2; j = slot - A.max_n2 - A.max_n4; }
-    else { sg = 3; j = slot - A.max_n2 - A.max_n4 - A.max_n8; }
-    const int base = sg == 0 ? 0 : sg == 1 ? n[0] : sg == 2 ? n[0] + n[1] : t_v;
-    int src = -2;
-    if (slot < slots) src = j < n[sg] ? A.order[h * A.order_row_stride + base + j] : -1;
-    s_src[threadIdx.x] = src; s_seg[threadIdx.x] = sg; s_j[threadIdx.x] = j; s_base[threadIdx.x] = base;
+  const int slot = block_x * PACKV_CTA_ROWS128 + (threadIdx.x >> 2);
+  const bool in_range = slot < slots;                         // (lanes of idle slots still join the shuffles)
+  int sg, j;
+  if (slot < A.max_n2) { sg = 0; j = slot; }
+  else if (slot < A.max_n2 + A.max_n4) { sg = 1; j = slot - A.max_n2; }
+  else if (slot < A.max_n2 + A.max_n4 + A.max_n8) { sg = 2; j = slot - A.max_n2 - A.max_n4; }
+  else { sg = 3; j = slot - A.max_n2 - A.max_n4 - A.max_n8; }
+  const int base = sg == 0 ? 0 : sg == 1 ? n[0] : sg == 2 ? n[0] + n[1] : t_v;
+  int src = -1;                                               // source token; -1: pad row (written as zeros)
+  if (in_range && j < n[sg]) src = A.order[h * A.order_row_stride + base + j];
+  const bool in_al = (reinterpret_cast<uintptr_t>(A.V) & 15) == 0 && (A.v_head_stride & 7) == 0 && (A.v_row_stride & 7) == 0;
+  uint4 w[4];
+  if (src >= 0) {
+    const uint16_t* row = A.V + h * A.v_head_stride + (int64_t)src * A.v_row_stride + 8 * s;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (in_al) {
+        w[i] = *reinterpret_cast<const uint4*>(row + 32 * i);
+      } else {                                                // rows off 16-byte boundaries: element by element
+        const uint16_t* e = row + 32 * i;
+        w[i] = make_uint4((uint32_t)e[0] | (uint32_t)e[1] << 16, (uint32_t)e[2] | (uint32_t)e[3] << 16,
+                          (uint32_t)e[4] | (uint32_t)e[5] << 16, (uint32_t)e[6] | (uint32_t)e[7] << 16);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = make_uint4(0u, 0u, 0u, 0u);
   }
-  __syncthreads();
-  {                                                           // the warp's rows, whole, all loads in flight together
-    uint2 w[PACKV_RPW128];
-    const uint16_t* Vh = A.V + h * A.v_head_stride + 4 * lane;
-    const bool aligned = (reinterpret_cast<uintptr_t>(A.V) & 7) == 0 && (A.v_head_stride & 3) == 0 && (A.v_row_stride & 3) == 0;
+  if (sg == 3) {                                              // fp16 rows are copied through (zeros when dead)
+    if (in_range) {
+      uint16_t* dst = A.out16 + ((int64_t)h * A.rows16 + j) * D + 8 * s;
+      const bool al = (reinterpret_cast<uintptr_t>(A.out16) & 15) == 0;
 #pragma unroll
-    for (int k = 0; k < PACKV_RPW128; ++k) {
-      const int src = s_src[warp * PACKV_RPW128 + k];
-      const uint16_t* p = Vh + (int64_t)(src >= 0 ? src : 0) * A.v_row_stride;
-      if (src < 0) w[k] = make_uint2(0u, 0u);
-      else if (aligned) w[k] = *reinterpret_cast<const uint2*>(p);
-      else w[k] = make_uint2((uint32_t)p[0] | ((uint32_t)p[1] << 16), (uint32_t)p[2] | ((uint32_t)p[3] << 16));
+      for (int i = 0; i < 4; ++i) {
+        if (al) {
+          *reinterpret_cast<uint4*>(dst + 32 * i) = w[i];
+        } else {
+          const uint32_t q[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dst[32 * i + e] = (uint16_t)(q[e >> 1] >> (16 * (e & 1)));
+        }
+      }
     }
-#pragma unroll
-    for (int k = 0; k < PACKV_RPW128; ++k)
-      *reinterpret_cast<uint2*>(rows + (warp * PACKV_RPW128 + k) * D + 4 * lane) = w[k];
   }
-  __syncwarp();
-  // lane l takes channels l, l+32, l+64, l+96 of a row: the four codes of byte l of a quarter-split
-  // 2-bit row, the code pairs of bytes l and l+32 of a half-split 4-bit row
-#pragma unroll 1
-  for (int k = 0; k < PACKV_RPW128; ++k) {
-    const int i = warp * PACKV_RPW128 + k;
-    const int src = s_src[i];
-    if (src == -2) break;
-    const int seg = s_seg[i], j = s_j[i];
-    const uint16_t* row = rows + i * D;
-    if (seg == 3) {                                           // fp16 rows are copied through (zeros when dead)
-      uint16_t* dst = A.out16 + ((int64_t)h * A.rows16 + j) * D;
+  // extrema of the row: exact in fp16, over this lane's 32 channels and then the slot's four lanes
+  __half2 lo2, hi2;
+  {
+    const uint32_t q0[4] = {w[0].x, w[0].y, w[0].z, w[0].w};
+    lo2 = hi2 = *reinterpret_cast<const __half2*>(&q0[0]);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = row[lane + 32 * q];
-      continue;
-    }
-    const int width = seg == 0 ? D / 4 : seg == 1 ? D / 2 : D;
-    uint8_t* dst = seg == 0 ? A.out2 + ((int64_t)h * A.rows2 + j) * width
-                 : seg == 1 ? A.out4 + ((int64_t)h * A.rows4 + j) * width
-                            : A.out8 + ((int64_t)h * A.rows8 + j) * width;
-    if (src < 0) {
-      for (int c = lane; c < width; c += 32) dst[c] = 0;
-      continue;
-    }
-    float x[4];
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t q[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
 #pragma unroll
-    for (int q = 0; q < 4; ++q) x[q] = h2f(row[lane + 32 * q]);
-    const float lo = warp_min_redux(fminf(fminf(x[0], x[1]), fminf(x[2], x[3])));
-    const float hi = warp_max_redux(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])));
-    const int qbits = seg == 0 ? 2 : seg == 1 ? 4 : 8;
-    const QParam qp = make_qparam(lo, hi, (float)((1 << qbits) - 1));
+      for (int e = 0; e < 4; ++e) {
+        const __half2 v = *reinterpret_cast<const __half2*>(&q[e]);
+        lo2 = __hmin2(lo2, v); hi2 = __hmax2(hi2, v);
+      }
+    }
+  }
+  float lo = fminf(__low2float(lo2), __high2float(lo2)), hi = fmaxf(__low2float(hi2), __high2float(hi2));
+  lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, 1)); hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, 1));
+  lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, 2)); hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, 2));
+  if (!in_range || sg == 3) return;
+  const int width = sg == 0 ? D / 4 : sg == 1 ? D / 2 : D;
+  uint8_t* out = sg == 0 ? A.out2 : sg == 1 ? A.out4 : A.out8;
+  const int64_t rows_out = sg == 0 ? A.rows2 : sg == 1 ? A.rows4 : A.rows8;
+  const bool al = (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+  uint8_t* dst = out + ((int64_t)h * rows_out + j) * width + 8 * s;
+  uint2 P[4];
+  if (src >= 0) {
+    const QParam qp = make_qparam(lo, hi, sg == 0 ? 3.f : sg == 1 ? 15.f : 255.f);
     const float rinv = __frcp_rn(qp.scale);
-    unsigned c[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) c[q] = quant_code_fast(x[q], rinv, qp);
-    if (seg == 0) {
-      dst[lane] = (uint8_t)(c[0] | (c[1] << 2) | (c[2] << 4) | (c[3] << 6));
-    } else if (seg == 1) {
-      dst[lane] = (uint8_t)(c[0] | (c[2] << 4));
-      dst[lane + 32] = (uint8_t)(c[1] | (c[3] << 4));
-    } else {
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t q[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+      uint32_t pl[2] = {0u, 0u};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = (uint8_t)c[q];
+      for (int e = 0; e < 8; ++e) {
+        const float x = h2f((uint16_t)(q[e >> 1] >> (16 * (e & 1))));
+        pl[e >> 2] |= quant_code_fast(x, rinv, qp) << (8 * (e & 3));
+      }
+      P[i] = make_uint2(pl[0], pl[1]);
     }
-    if (lane == 0) {
-      A.out_scale[(int64_t)h * A.rows_meta + s_base[i] + j] = f2h_bits(qp.scale);
-      A.out_zp[(int64_t)h * A.rows_meta + s_base[i] + j] = f2h_bits(qp.zp);
+    if (s == 0) {
+      A.out_scale[(int64_t)h * A.rows_meta + base + j] = f2h_bits(qp.scale);
+      A.out_zp[(int64_t)h * A.rows_meta + base + j] = f2h_bits(qp.zp);
     }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) P[i] = make_uint2(0u, 0u);
+  }
+  if (sg == 0) {
+    store8(dst, make_uint2(P[0].x | P[1].x << 2 | P[2].x << 4 | P[3].x << 6,
+                           P[0].y | P[1].y << 2 | P[2].y << 4 | P[3].y << 6), al);
+  } else if (sg == 1) {
+    store8(dst, make_uint2(P[0].x | P[2].x << 4, P[0].y | P[2].y << 4), al);
+    store8(dst + 32, make_uint2(P[1].x | P[3].x << 4, P[1].y | P[3].y << 4), al);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) store8(dst + 32 * i, P[i], al);
   }
 }
 
@@ -357,8 +383,7 @@ __host__ __device__ inline int pack_v_blocks(int slots, bool fast) {
 
 __global__ void __launch_bounds__(PACKV_WARPS * 32)
 pack_v128_kernel(PackVArgs A) {
-  __shared__ __align__(16) uint16_t rows[PACKV_CTA_ROWS128 * 128];
-  pack_v_body128(A, blockIdx.y, blockIdx.x, rows);
+  pack_v_body128(A, blockIdx.y, blockIdx.x);
 }
 
 __global__ void __launch_bounds__(PACKV_WARPS * 32)
@@ -608,42 +633,65 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
       *reinterpret_cast<uint2*>(s_rows + (warp * PACKK_RPW + k) * 128 + 4 * lane) = w[k];
     __syncwarp();
   }
-  // a lane owns output bytes (lane, lane+32, ...) of a row and gathers the 4 / 2 / 1 channel slots
-  // that make up each of them, so codes never move between lanes
+  // A lane owns a "quad" of a row: four channel slots whose codes land in one output byte (2-bit),
+  // two adjacent bytes (4-bit) or four adjacent bytes (8-bit), so codes never move between lanes
+  // and all lanes carry the same number of codes.  Slots that do not exist (odd tails) get a zero
+  // reciprocal and zero point, which quantises to code 0.
   const int sub2 = n2p / 4, sub4 = n4p / 2;
-  const int row_bytes = ov > 0 ? d_pad : sub2 + sub4 + n8p;
-  for (int b = lane; b < row_bytes; b += 32) {
-    int ns, sl0, step, shift;                                   // slots sl0 + v*step, code v at bit v*shift
+  const int nq2 = ov > 0 ? 0 : sub2, nq4 = ov > 0 ? 0 : (sub4 + 1) / 2;
+  const int n8 = ov > 0 ? d_pad : n8p, nq8 = (n8 + 3) / 4, base8 = ov > 0 ? 0 : n2p + n4p;
+  for (int q = lane; q < nq2 + nq4 + nq8; q += 32) {
+    int sl[4], nv, nb, shift, width, col;
     float qmax;
-    uint8_t* dst; int width, col;
-    if (ov > 0) { ns = 1; sl0 = b; step = 0; shift = 0; qmax = (float)((1 << ov) - 1); dst = A.k8; width = d_pad; col = b; }
-    else if (b < sub2) { ns = 4; sl0 = b; step = sub2; shift = 2; qmax = 3.f; dst = A.k2; width = sub2; col = b; }
-    else if (b < sub2 + sub4) { ns = 2; sl0 = n2p + b - sub2; step = sub4; shift = 4; qmax = 15.f; dst = A.k4; width = sub4; col = b - sub2; }
-    else { ns = 1; sl0 = n2p + n4p + b - sub2 - sub4; step = 0; shift = 0; qmax = 255.f; dst = A.k8; width = n8p; col = b - sub2 - sub4; }
+    uint8_t* dst;
+    if (q < nq2) {
+      nv = 4; nb = 1; shift = 2; qmax = 3.f; dst = A.k2; width = sub2; col = q;
+#pragma unroll
+      for (int v = 0; v < 4; ++v) sl[v] = q + v * sub2;
+    } else if (q < nq2 + nq4) {
+      const int b0 = 2 * (q - nq2);
+      nb = b0 + 1 < sub4 ? 2 : 1; nv = 2 * nb; shift = 4; qmax = 15.f; dst = A.k4; width = sub4; col = b0;
+      sl[0] = n2p + b0; sl[1] = n2p + b0 + sub4; sl[2] = n2p + b0 + 1; sl[3] = n2p + b0 + 1 + sub4;
+    } else {
+      const int b0 = 4 * (q - nq2 - nq4);
+      nb = min(4, n8 - b0); nv = nb; shift = 8; qmax = ov > 0 ? (float)((1 << ov) - 1) : 255.f;
+      dst = A.k8; width = n8; col = b0;
+#pragma unroll
+      for (int v = 0; v < 4; ++v) sl[v] = base8 + b0 + v;
+    }
     int ch[4]; float sc[4], zp[4], rinv[4];
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
-      const int sl = sl0 + (v < ns ? v : 0) * step;
-      ch[v] = s_ch[sl]; sc[v] = s_scale[sl]; zp[v] = s_zp[sl];
-      rinv[v] = __frcp_rn(sc[v]);
+      const bool on = v < nv;
+      const int x = on ? sl[v] : sl[0];
+      ch[v] = s_ch[x]; sc[v] = s_scale[x];
+      zp[v] = on ? s_zp[x] : 0.f;
+      rinv[v] = on ? __frcp_rn(sc[v]) : 0.f;
     }
     uint8_t* out = dst + ((int64_t)h * rows_k + row0 + warp * PACKK_RPW) * width + col;
+    // whole-word stores where every row's address allows it
+    const int am = nb == 2 ? 1 : 3;
+    const bool al = (nb == 2 || nb == 4) && (reinterpret_cast<uintptr_t>(out) & am) == 0 && (width & am) == 0;
 #pragma unroll 4
     for (int k = 0; k < PACKK_RPW; ++k) {
       const int i = warp * PACKK_RPW + k;
       if (row0 + i >= t_k) break;
       const int tok = s_tok[i];
       const uint16_t* row = A.stage_rows ? s_rows + i * 128 : Kh + (int64_t)(tok < 0 ? 0 : tok) * A.k_row_stride;
-      unsigned byte = 0;
+      unsigned word = 0;
 #pragma unroll
       for (int v = 0; v < 4; ++v) {
-        if (v < ns) {
-          const float x = (tok >= 0 && ch[v] >= 0) ? h2f(row[ch[v]]) : 0.f;
-          QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
-          byte |= quant_code_fast(x, rinv[v], qp) << (v * shift);
-        }
+        const float x = (tok >= 0 && ch[v] >= 0) ? h2f(row[ch[v]]) : 0.f;
+        QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
+        word |= quant_code_fast(x, rinv[v], qp) << (v * shift);
       }
-      out[(int64_t)k * width] = (uint8_t)byte;
+      uint8_t* o = out + (int64_t)k * width;
+      if (nb == 1) o[0] = (uint8_t)word;
+      else if (al && nb == 2) *reinterpret_cast<uint16_t*>(o) = (uint16_t)word;
+      else if (al && nb == 4) *reinterpret_cast<uint32_t*>(o) = word;
+      else {
+        for (int e = 0; e < nb; ++e) o[e] = (uint8_t)(word >> (8 * e));
+      }
     }
   }
 }
@@ -679,11 +727,10 @@ pack_v_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
 
 __global__ void __launch_bounds__(PACKV_WARPS * 32)
 pack_v128_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
-  __shared__ __align__(16) uint16_t rows[PACKV_CTA_ROWS128 * 128];
   __shared__ PackVArgs A;
   if (threadIdx.x == 0) job_to_vargs(jobs[blockIdx.z], A);
   __syncthreads();
-  pack_v_body128(A, blockIdx.y, blockIdx.x, rows);
+  pack_v_body128(A, blockIdx.y, blockIdx.x);
 }
 
 __device__ __forceinline__ void job_to_kargs(const rdkv_pack_job& J, PackKArgs& A) {
