@@ -110,12 +110,19 @@ __device__ __forceinline__ unsigned quant_code(float x, const QParam& p) {
 // there), so after adding the zero point the two sums differ by < 1.3e-4 and round to the same
 // integer unless the sum lies that close to a half-integer; those cases take the exact path.
 // Non-finite inputs behave as in quant_code (NaN -> code 0, +-inf -> the clamp).
-__device__ __forceinline__ unsigned quant_code_fast(float x, float rinv, const QParam& p) {
+// The code comes back as a float (an exact small integer), so that callers can assemble bytes
+// with exact fp32 multiply-adds and convert once per pair of bytes.  A sum outside the clamp range
+// is decided by the clamp on both paths (its error is far below its distance to the range unless
+// it is within 1.3e-4 of an end, where both round to that end), so the test looks at the clamped sum.
+__device__ __forceinline__ float quant_code_fast_f(float x, float rinv, const QParam& p) {
   const float y = __fadd_rn(__fmul_rn(x, rinv), p.zp);
   const float yc = fminf(fmaxf(y, 0.f), p.qmax);
   const float c = __fadd_rn(__fadd_rn(yc, 12582912.f), -12582912.f);   // round half to even for 0 <= yc < 2^22
-  if (fabsf(__fadd_rn(fabsf(__fsub_rn(y, c)), -0.5f)) < 2.5e-4f) return quant_code(x, p);
-  return (unsigned)c;
+  if (fabsf(__fsub_rn(yc, c)) > 0.5f - 2.5e-4f) return (float)quant_code(x, p);
+  return c;
+}
+__device__ __forceinline__ unsigned quant_code_fast(float x, float rinv, const QParam& p) {
+  return (unsigned)quant_code_fast_f(x, rinv, p);
 }
 
 // min / max over the 32 lanes of a full warp in one instruction each (NaN operands are ignored,
@@ -345,13 +352,14 @@ __device__ __forceinline__ void pack_v_body128(const PackVArgs& A, int h, int bl
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t q[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
-      uint32_t pl[2] = {0u, 0u};
+      uint32_t pr[4];                                         // two one-byte codes each, from one fp16 pair
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float x = h2f((uint16_t)(q[e >> 1] >> (16 * (e & 1))));
-        pl[e >> 2] |= quant_code_fast(x, rinv, qp) << (8 * (e & 3));
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&q[e]));
+        const float c0 = quant_code_fast_f(x.x, rinv, qp), c1 = quant_code_fast_f(x.y, rinv, qp);
+        pr[e] = (uint32_t)__fmaf_rn(c1, 256.f, c0);           // exact: both codes are integers <= 255
       }
-      P[i] = make_uint2(pl[0], pl[1]);
+      P[i] = make_uint2(pr[0] | pr[1] << 16, pr[2] | pr[3] << 16);
     }
     if (s == 0) {
       A.out_scale[(int64_t)h * A.rows_meta + base + j] = f2h_bits(qp.scale);
@@ -590,21 +598,40 @@ __device__ __forceinline__ void pack_k_params_body(const PackKArgs& A, int h) {
 __global__ void __launch_bounds__(128)
 pack_k_params_kernel(PackKArgs A) { pack_k_params_body(A, blockIdx.x); }
 
-// Pass 3: quantise and bit-pack PACKK_ROWS stripe rows per CTA, four rows per warp at once.  A
-// lane owns output bytes (lane, lane+32, ...) of a row and gathers the 4 / 2 / 1 channel slots
-// that make up each of them, so codes never move between lanes.
+// Pass 3: quantise and bit-pack.  A CTA takes PACKK_BPC consecutive blocks of PACKK_ROWS stripe rows,
+// so the per-head set-up (channel parameters, stripe-row -> token map) is paid once for all of
+// them; each warp stages its own rows of the next block with cp.async while it quantises the
+// current one (two buffers, no CTA-wide barrier in the loop).
 constexpr int PACKK_WARPS = 8;
-constexpr int PACKK_ROWS = 128;                              // stripe rows per CTA
-constexpr int PACKK_RPW = PACKK_ROWS / PACKK_WARPS;          // rows per warp
+constexpr int PACKK_ROWS = 128;                              // stripe rows per block
+constexpr int PACKK_RPW = PACKK_ROWS / PACKK_WARPS;          // rows per warp and block
+constexpr int PACKK_BPC = 4;                                 // blocks per CTA
+
+__host__ __device__ inline int pack_k_quant_ctas(int t_k) {
+  return (t_k + PACKK_ROWS * PACKK_BPC - 1) / (PACKK_ROWS * PACKK_BPC);
+}
+__host__ __device__ inline size_t pack_k_quant_smem(int d_pad, bool staged) {
+  return (size_t)d_pad * (3 * sizeof(float)) + (staged ? 16 + 2 * PACKK_ROWS * 128 * sizeof(uint16_t) : 0);
+}
+
+__device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;"
+               :: "r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
 // Dynamic shared memory: scale, zp (fp32) and channel (int) per slot, then — when rows are staged
-// (128 channels, 8-byte aligned rows) — the CTA's PACKK_ROWS rows whole, all loads in flight at once.
+// (128 channels, 8-byte aligned rows) — two buffers of PACKK_ROWS whole rows.
 __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int block_x, unsigned char* smem_raw) {
-  __shared__ int s_tok[PACKK_ROWS];
+  __shared__ int s_tok[PACKK_ROWS * PACKK_BPC];
   const uint16_t* __restrict__ K = A.K;
   const int t_k = A.t_k, n2p = A.n2p, n4p = A.n4p, n8p = A.n8p, n_slabs = A.n_slabs, ov = A.qbits_override;
   const int64_t rows_k = A.rows_k;
-  if (block_x * PACKK_ROWS >= t_k) return;
+  const int row_base = block_x * PACKK_ROWS * PACKK_BPC;
+  if (row_base >= t_k) return;
+  const int n_blocks = min(PACKK_BPC, (t_k - row_base + PACKK_ROWS - 1) / PACKK_ROWS);
   const int d_pad = n2p + n4p + n8p;
   float* s_scale = reinterpret_cast<float*>(smem_raw);          // [d_pad]
   float* s_zp = s_scale + d_pad;                                 // [d_pad]
@@ -617,22 +644,24 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
   for (int p = threadIdx.x; p < d_pad; p += blockDim.x) {
     s_scale[p] = fin[p]; s_zp[p] = fin[d_pad + p]; s_ch[p] = slot_channel(m, p);
   }
-  const int row0 = block_x * PACKK_ROWS;
-  if (threadIdx.x < PACKK_ROWS) s_tok[threadIdx.x] = row0 + threadIdx.x < t_k ? stripe_token(m, row0 + threadIdx.x) : -1;
+  for (int i = threadIdx.x; i < n_blocks * PACKK_ROWS; i += blockDim.x)
+    s_tok[i] = row_base + i < t_k ? stripe_token(m, row_base + i) : -1;
   __syncthreads();
   const uint16_t* Kh = K + h * A.k_head_stride;
-  if (A.stage_rows) {
-    uint2 w[PACKK_RPW];
+  const bool staged = A.stage_rows != 0;
+  auto stage = [&](int blk) {                                  // this warp's rows of block blk -> buffer blk & 1
+    uint16_t* buf = s_rows + (blk & 1) * PACKK_ROWS * 128;
 #pragma unroll
     for (int k = 0; k < PACKK_RPW; ++k) {
-      const int tok = s_tok[warp * PACKK_RPW + k];
-      w[k] = tok >= 0 ? *reinterpret_cast<const uint2*>(Kh + (int64_t)tok * A.k_row_stride + 4 * lane) : make_uint2(0u, 0u);
+      const int i = warp * PACKK_RPW + k;
+      const int tok = s_tok[blk * PACKK_ROWS + i];
+      uint16_t* dst = buf + i * 128 + 4 * lane;
+      if (tok >= 0) cp_async8(dst, Kh + (int64_t)tok * A.k_row_stride + 4 * lane);
+      else *reinterpret_cast<uint2*>(dst) = make_uint2(0u, 0u);
     }
-#pragma unroll
-    for (int k = 0; k < PACKK_RPW; ++k)
-      *reinterpret_cast<uint2*>(s_rows + (warp * PACKK_RPW + k) * 128 + 4 * lane) = w[k];
-    __syncwarp();
-  }
+    cp_async_commit();
+  };
+  if (staged) stage(0);
   // A lane owns a "quad" of a row: four channel slots whose codes land in one output byte (2-bit),
   // two adjacent bytes (4-bit) or four adjacent bytes (8-bit), so codes never move between lanes
   // and all lanes carry the same number of codes.  Slots that do not exist (odd tails) get a zero
@@ -640,7 +669,20 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
   const int sub2 = n2p / 4, sub4 = n4p / 2;
   const int nq2 = ov > 0 ? 0 : sub2, nq4 = ov > 0 ? 0 : (sub4 + 1) / 2;
   const int n8 = ov > 0 ? d_pad : n8p, nq8 = (n8 + 3) / 4, base8 = ov > 0 ? 0 : n2p + n4p;
-  for (int q = lane; q < nq2 + nq4 + nq8; q += 32) {
+  // few quads per row (few kept channels): a warp works on 2 or 4 rows at once
+  const int n_quads = nq2 + nq4 + nq8;
+  const int qn = n_quads <= 8 ? 8 : n_quads <= 16 ? 16 : 32;   // lanes per row
+  const int rpp = 32 / qn, rsub = lane / qn;                   // rows per pass, this lane's row of a pass
+#pragma unroll 1
+  for (int blk = 0; blk < n_blocks; ++blk) {
+  if (staged) {
+    if (blk + 1 < n_blocks) { stage(blk + 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncwarp();
+  }
+  const int row0 = row_base + blk * PACKK_ROWS;
+  const uint16_t* rows_blk = s_rows + (blk & 1) * PACKK_ROWS * 128;
+  for (int q = lane % qn; q < n_quads; q += qn) {
     int sl[4], nv, nb, shift, width, col;
     float qmax;
     uint8_t* dst;
@@ -660,6 +702,7 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
       for (int v = 0; v < 4; ++v) sl[v] = base8 + b0 + v;
     }
     int ch[4]; float sc[4], zp[4], rinv[4];
+    bool live[4];                                              // the slot holds a kept channel
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
       const bool on = v < nv;
@@ -667,24 +710,30 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
       ch[v] = s_ch[x]; sc[v] = s_scale[x];
       zp[v] = on ? s_zp[x] : 0.f;
       rinv[v] = on ? __frcp_rn(sc[v]) : 0.f;
+      live[v] = ch[v] >= 0;
+      ch[v] = max(ch[v], 0);
     }
+    const float mult = (float)(1 << shift);
     uint8_t* out = dst + ((int64_t)h * rows_k + row0 + warp * PACKK_RPW) * width + col;
     // whole-word stores where every row's address allows it
     const int am = nb == 2 ? 1 : 3;
     const bool al = (nb == 2 || nb == 4) && (reinterpret_cast<uintptr_t>(out) & am) == 0 && (width & am) == 0;
 #pragma unroll 4
-    for (int k = 0; k < PACKK_RPW; ++k) {
+    for (int k = rsub; k < PACKK_RPW; k += rpp) {
       const int i = warp * PACKK_RPW + k;
       if (row0 + i >= t_k) break;
-      const int tok = s_tok[i];
-      const uint16_t* row = A.stage_rows ? s_rows + i * 128 : Kh + (int64_t)(tok < 0 ? 0 : tok) * A.k_row_stride;
-      unsigned word = 0;
+      // (staged rows of pad tokens were written as zeros)
+      const int tok = staged ? 0 : s_tok[blk * PACKK_ROWS + i];
+      const uint16_t* row = staged ? rows_blk + i * 128 : Kh + (int64_t)(tok < 0 ? 0 : tok) * A.k_row_stride;
+      float c[4];
 #pragma unroll
       for (int v = 0; v < 4; ++v) {
-        const float x = (tok >= 0 && ch[v] >= 0) ? h2f(row[ch[v]]) : 0.f;
+        const float x = (tok >= 0 && live[v]) ? h2f(row[ch[v]]) : 0.f;
         QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
-        word |= quant_code_fast(x, rinv[v], qp) << (v * shift);
+        c[v] = quant_code_fast_f(x, rinv[v], qp);
       }
+      // codes are small integers: bytes assemble exactly in fp32 (at most 16 bits per half)
+      const unsigned word = (unsigned)__fmaf_rn(c[1], mult, c[0]) | (unsigned)__fmaf_rn(c[3], mult, c[2]) << (2 * shift);
       uint8_t* o = out + (int64_t)k * width;
       if (nb == 1) o[0] = (uint8_t)word;
       else if (al && nb == 2) *reinterpret_cast<uint16_t*>(o) = (uint16_t)word;
@@ -693,6 +742,8 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
         for (int e = 0; e < nb; ++e) o[e] = (uint8_t)(word >> (8 * e));
       }
     }
+  }
+  __syncwarp();                                                // the buffer may be restaged from here on
   }
 }
 
@@ -877,8 +928,10 @@ extern "C" int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_r
   pack_k_params_kernel<<<H, 128, 0, st>>>(A);
   rc = launch_status();
   if (rc != RDKV_OK) return rc;
-  const size_t smem = (size_t)d_pad * (3 * sizeof(float)) + (A.stage_rows ? 16 + PACKK_ROWS * 128 * sizeof(uint16_t) : 0);
-  pack_k_quant_kernel<<<dim3((t_k + PACKK_ROWS - 1) / PACKK_ROWS, H), PACKK_WARPS * 32, smem, st>>>(A);
+  const size_t smem = pack_k_quant_smem(d_pad, A.stage_rows != 0);
+  if (cudaFuncSetAttribute(pack_k_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return launch_status();
+  pack_k_quant_kernel<<<dim3(pack_k_quant_ctas(t_k), H), PACKK_WARPS * 32, smem, st>>>(A);
   return launch_status();
 }
 
@@ -906,7 +959,9 @@ extern "C" int rdkv_pack_kv_batched(const rdkv_pack_job* jobs, int n_jobs, int H
   pack_k_params_batched_kernel<<<dim3(H, n_jobs), 128, 0, st>>>(jobs);
   rc = launch_status();
   if (rc != RDKV_OK) return rc;
-  const size_t smem = (size_t)max_d_pad * (3 * sizeof(float)) + (D == 128 ? 16 + PACKK_ROWS * 128 * sizeof(uint16_t) : 0);
-  pack_k_quant_batched_kernel<<<dim3((max_t_k + PACKK_ROWS - 1) / PACKK_ROWS, H, n_jobs), PACKK_WARPS * 32, smem, st>>>(jobs);
+  const size_t smem = pack_k_quant_smem(max_d_pad, D == 128);
+  if (cudaFuncSetAttribute(pack_k_quant_batched_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return launch_status();
+  pack_k_quant_batched_kernel<<<dim3(pack_k_quant_ctas(max_t_k), H, n_jobs), PACKK_WARPS * 32, smem, st>>>(jobs);
   return launch_status();
 }
