@@ -106,19 +106,20 @@ __device__ __forceinline__ unsigned quant_code(float x, const QParam& p) {
 }
 
 // quant_code without the division in the common case.  rinv = RN(1/scale).  x*rinv differs from the
-// rounded quotient by less than 2^-14 wherever the code is not decided by the clamp (|quotient| <= 256
-// there), so after adding the zero point the two sums differ by < 1.3e-4 and round to the same
-// integer unless the sum lies that close to a half-integer; those cases take the exact path.
+// rounded quotient by less than 2^-14.5 wherever the code is not decided by the clamp (|quotient| <= 256
+// there: 2^-15 from the product, 2^-16 from the quotient's own rounding), so after adding the zero
+// point (2^-17 per sum) the two sums differ by < 6.2e-5 and round to the same integer unless the
+// sum lies within 1.3e-4 of a half-integer; those cases take the exact path.
 // Non-finite inputs behave as in quant_code (NaN -> code 0, +-inf -> the clamp).
 // The code comes back as a float (an exact small integer), so that callers can assemble bytes
 // with exact fp32 multiply-adds and convert once per pair of bytes.  A sum outside the clamp range
 // is decided by the clamp on both paths (its error is far below its distance to the range unless
 // it is within 1.3e-4 of an end, where both round to that end), so the test looks at the clamped sum.
 __device__ __forceinline__ float quant_code_fast_f(float x, float rinv, const QParam& p) {
-  const float y = __fadd_rn(__fmul_rn(x, rinv), p.zp);
+  const float y = __fmaf_rn(x, rinv, p.zp);                 // (one rounding fewer than the bound allows for)
   const float yc = fminf(fmaxf(y, 0.f), p.qmax);
   const float c = __fadd_rn(__fadd_rn(yc, 12582912.f), -12582912.f);   // round half to even for 0 <= yc < 2^22
-  if (fabsf(__fsub_rn(yc, c)) > 0.5f - 2.5e-4f) return (float)quant_code(x, p);
+  if (fabsf(__fsub_rn(yc, c)) > 0.5f - 1.3e-4f) return (float)quant_code(x, p);
   return c;
 }
 __device__ __forceinline__ unsigned quant_code_fast(float x, float rinv, const QParam& p) {
@@ -509,29 +510,41 @@ __device__ __forceinline__ void pack_k_minmax_body128(const PackKArgs& A, int h,
   const int rows_per = (t_k + n_slabs - 1) / n_slabs;
   const int r0 = min(t_k, slab * rows_per), r1 = min(t_k, r0 + rows_per);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float lo[4] = {INFINITY, INFINITY, INFINITY, INFINITY}, hi[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  // extrema in fp16 pairs (exact: the data are fp16), two pairs per lane = channels 4*lane .. +3;
+  // the tokens of 16 stripe rows are looked up one per lane and handed round by shuffle, and the
+  // 16 rows are loaded together
+  const __half2 inf2 = __float2half2_rn(INFINITY), ninf2 = __float2half2_rn(-INFINITY);
+  __half2 lo2[2] = {inf2, inf2}, hi2[2] = {ninf2, ninf2};
   bool pad = false;
-  const uint16_t* Kh = A.K + h * A.k_head_stride;
-  for (int s = r0 + warp * 4; s < r1; s += 16) {              // 4 warps x 4 rows per round
-    int tok[4];
-    uint2 w[4];
+  const uint16_t* Kh = A.K + h * A.k_head_stride + 4 * lane;
+  for (int s0 = r0 + warp * 16; s0 < r1; s0 += 64) {          // 4 warps x 16 rows per round
+    const int tok_l = (lane < 16 && s0 + lane < r1) ? stripe_token(m, s0 + lane) : -2;
+    pad = pad || __any_sync(0xffffffffu, tok_l == -1);
+    {
+      uint2 w[16];
+      bool on[16];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) tok[k] = s + k < r1 ? stripe_token(m, s + k) : -2;
+      for (int k = 0; k < 16; ++k) {
+        const int tok = __shfl_sync(0xffffffffu, tok_l, k);
+        on[k] = tok >= 0;
+        w[k] = make_uint2(0u, 0u);
+        if (on[k]) w[k] = *reinterpret_cast<const uint2*>(Kh + (int64_t)tok * A.k_row_stride);
+      }
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-      w[k] = tok[k] >= 0 ? *reinterpret_cast<const uint2*>(Kh + (int64_t)tok[k] * A.k_row_stride + 4 * lane) : make_uint2(0u, 0u);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      if (tok[k] == -2) continue;
-      if (tok[k] < 0) { pad = true; continue; }
-      const float x0 = h2f((uint16_t)(w[k].x & 0xffffu)), x1 = h2f((uint16_t)(w[k].x >> 16));
-      const float x2 = h2f((uint16_t)(w[k].y & 0xffffu)), x3 = h2f((uint16_t)(w[k].y >> 16));
-      lo[0] = fminf(lo[0], x0); hi[0] = fmaxf(hi[0], x0); lo[1] = fminf(lo[1], x1); hi[1] = fmaxf(hi[1], x1);
-      lo[2] = fminf(lo[2], x2); hi[2] = fmaxf(hi[2], x2); lo[3] = fminf(lo[3], x3); hi[3] = fmaxf(hi[3], x3);
+      for (int k = 0; k < 16; ++k) {
+        if (!on[k]) continue;                                  // (warp-uniform)
+        const __half2 a = *reinterpret_cast<const __half2*>(&w[k].x), c = *reinterpret_cast<const __half2*>(&w[k].y);
+        lo2[0] = __hmin2(lo2[0], a); hi2[0] = __hmax2(hi2[0], a);
+        lo2[1] = __hmin2(lo2[1], c); hi2[1] = __hmax2(hi2[1], c);
+      }
     }
   }
-#pragma unroll
-  for (int q = 0; q < 4; ++q) { s_lo[warp][4 * lane + q] = lo[q]; s_hi[warp][4 * lane + q] = hi[q]; }
+  {
+    const float2 l0 = __half22float2(lo2[0]), l1 = __half22float2(lo2[1]);
+    const float2 h0 = __half22float2(hi2[0]), h1 = __half22float2(hi2[1]);
+    s_lo[warp][4 * lane + 0] = l0.x; s_lo[warp][4 * lane + 1] = l0.y; s_lo[warp][4 * lane + 2] = l1.x; s_lo[warp][4 * lane + 3] = l1.y;
+    s_hi[warp][4 * lane + 0] = h0.x; s_hi[warp][4 * lane + 1] = h0.y; s_hi[warp][4 * lane + 2] = h1.x; s_hi[warp][4 * lane + 3] = h1.y;
+  }
   if (lane == 0) s_pad[warp] = pad ? 1 : 0;
   __syncthreads();
   const bool any_pad = (s_pad[0] | s_pad[1] | s_pad[2] | s_pad[3]) != 0;
