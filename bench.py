@@ -457,7 +457,7 @@ def run_pack(args, rank, world, device):
                        "l2": "4.3 GB of inputs per step > L2"},
             "roofline": {"bound": "hbm", "achieved": moved / (kern_ms / 1e3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": moved / (kern_ms / 1e3) / 1e9 / peak, "traffic": None, "peak_kind": kind,
-                         "kernel": "pack_v_batched_kernel + pack_k_minmax_batched_kernel + pack_k_quant_batched_kernel",
+                         "kernel": "pack_v128_batched_kernel + pack_k_minmax128_batched_kernel + pack_k_params_batched_kernel + pack_k_quant_batched_kernel",
                          "kernel_ms": kern_ms, "algorithmic_bytes_per_step": moved},
             "gpu_launches": 5 * args.steps, "clocks": sampler.summary()}
     if not args.no_cpu_baseline:
