@@ -731,27 +731,48 @@ __device__ __forceinline__ void pack_k_quant_body(const PackKArgs& A, int h, int
     // whole-word stores where every row's address allows it
     const int am = nb == 2 ? 1 : 3;
     const bool al = (nb == 2 || nb == 4) && (reinterpret_cast<uintptr_t>(out) & am) == 0 && (width & am) == 0;
-#pragma unroll 4
-    for (int k = rsub; k < PACKK_RPW; k += rpp) {
-      const int i = warp * PACKK_RPW + k;
-      if (row0 + i >= t_k) break;
-      // (staged rows of pad tokens were written as zeros)
-      const int tok = staged ? 0 : s_tok[blk * PACKK_ROWS + i];
-      const uint16_t* row = staged ? rows_blk + i * 128 : Kh + (int64_t)(tok < 0 ? 0 : tok) * A.k_row_stride;
-      float c[4];
+    const int kmax = min(PACKK_RPW, t_k - row0 - warp * PACKK_RPW);     // rows of this warp that exist
+    if (staged) {
+      // shared-memory byte addresses of the four gathered elements in the warp's first row
+      const uint32_t rw = (uint32_t)__cvta_generic_to_shared(rows_blk + warp * PACKK_RPW * 128);
+      uint32_t ea[4];
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        const float x = (tok >= 0 && live[v]) ? h2f(row[ch[v]]) : 0.f;
-        QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
-        c[v] = quant_code_fast_f(x, rinv[v], qp);
+      for (int v = 0; v < 4; ++v) ea[v] = rw + 2 * ch[v];
+#pragma unroll 2
+      for (int k = rsub; k < kmax; k += rpp) {
+        float c[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint16_t bits;
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(bits) : "r"(ea[v] + k * 256));
+          const float x = live[v] ? h2f(bits) : 0.f;          // (staged rows of pad tokens were written as zeros)
+          QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
+          c[v] = quant_code_fast_f(x, rinv[v], qp);
+        }
+        // codes are small integers: bytes assemble exactly in fp32 (at most 16 bits per half)
+        const unsigned word = (unsigned)__fmaf_rn(c[1], mult, c[0]) | (unsigned)__fmaf_rn(c[3], mult, c[2]) << (2 * shift);
+        uint8_t* o = out + (int64_t)k * width;
+        if (nb == 1) o[0] = (uint8_t)word;
+        else if (al && nb == 2) *reinterpret_cast<uint16_t*>(o) = (uint16_t)word;
+        else if (al && nb == 4) *reinterpret_cast<uint32_t*>(o) = word;
+        else {
+          for (int e = 0; e < nb; ++e) o[e] = (uint8_t)(word >> (8 * e));
+        }
       }
-      // codes are small integers: bytes assemble exactly in fp32 (at most 16 bits per half)
-      const unsigned word = (unsigned)__fmaf_rn(c[1], mult, c[0]) | (unsigned)__fmaf_rn(c[3], mult, c[2]) << (2 * shift);
-      uint8_t* o = out + (int64_t)k * width;
-      if (nb == 1) o[0] = (uint8_t)word;
-      else if (al && nb == 2) *reinterpret_cast<uint16_t*>(o) = (uint16_t)word;
-      else if (al && nb == 4) *reinterpret_cast<uint32_t*>(o) = word;
-      else {
+    } else {
+#pragma unroll 2
+      for (int k = rsub; k < kmax; k += rpp) {
+        const int tok = s_tok[blk * PACKK_ROWS + warp * PACKK_RPW + k];
+        const uint16_t* row = Kh + (int64_t)(tok < 0 ? 0 : tok) * A.k_row_stride;
+        float c[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const float x = (tok >= 0 && live[v]) ? h2f(row[ch[v]]) : 0.f;
+          QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
+          c[v] = quant_code_fast_f(x, rinv[v], qp);
+        }
+        const unsigned word = (unsigned)__fmaf_rn(c[1], mult, c[0]) | (unsigned)__fmaf_rn(c[3], mult, c[2]) << (2 * shift);
+        uint8_t* o = out + (int64_t)k * width;
         for (int e = 0; e < nb; ++e) o[e] = (uint8_t)(word >> (8 * e));
       }
     }
