@@ -582,11 +582,34 @@ __device__ __forceinline__ void pack_k_params_body(const PackKArgs& A, int h) {
   const KMaps m = load_maps(h, A.tok_order, A.tok_order_rs, A.tok_counts, A.tok_counts_rs, A.max_t_v, A.t_k,
                             A.ch_order, A.ch_order_rs, A.ch_counts, A.ch_counts_rs, n2p, n4p, n8p);
   float* fin = A.scratch + ((int64_t)(h * (n_slabs + 1) + n_slabs) * 2) * d_pad;
+  // narrow heads: the slabs of a slot are reduced by PARAM_PARTS threads side by side first
+  constexpr int PARAM_PARTS = 8, PARAM_DMAX = 128;
+  __shared__ float s_part[2][PARAM_PARTS][PARAM_DMAX];
+  const bool split = d_pad <= PARAM_DMAX;
+  if (split) {
+    for (int idx = threadIdx.x; idx < d_pad * PARAM_PARTS; idx += blockDim.x) {
+      const int p = idx % d_pad, part = idx / d_pad;
+      float lo = INFINITY, hi = -INFINITY;
+      for (int s = part; s < n_slabs; s += PARAM_PARTS) {
+        const float* src = A.scratch + ((int64_t)(h * (n_slabs + 1) + s) * 2) * d_pad;
+        lo = fminf(lo, src[p]); hi = fmaxf(hi, src[d_pad + p]);
+      }
+      s_part[0][part][p] = lo; s_part[1][part][p] = hi;
+    }
+    __syncthreads();
+  }
   for (int p = threadIdx.x; p < d_pad; p += blockDim.x) {
     float lo = INFINITY, hi = -INFINITY;
-    for (int s = 0; s < n_slabs; ++s) {
-      const float* src = A.scratch + ((int64_t)(h * (n_slabs + 1) + s) * 2) * d_pad;
-      lo = fminf(lo, src[p]); hi = fmaxf(hi, src[d_pad + p]);
+    if (split) {
+#pragma unroll
+      for (int part = 0; part < PARAM_PARTS; ++part) {
+        lo = fminf(lo, s_part[0][part][p]); hi = fmaxf(hi, s_part[1][part][p]);
+      }
+    } else {
+      for (int s = 0; s < n_slabs; ++s) {
+        const float* src = A.scratch + ((int64_t)(h * (n_slabs + 1) + s) * 2) * d_pad;
+        lo = fminf(lo, src[p]); hi = fmaxf(hi, src[d_pad + p]);
+      }
     }
     const int qbits = A.qbits_override > 0 ? A.qbits_override : (p < n2p ? 2 : p < n2p + n4p ? 4 : 8);
     const QParam qp = make_qparam(lo, hi, (float)((1 << qbits) - 1));
