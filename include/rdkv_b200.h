@@ -266,6 +266,23 @@ int rdkv_score_pool(const float* scores, int64_t row_stride, int rows, int len, 
                     int kernel_size, int reflect, float* out, int64_t out_row_stride, int out_len,
                     void* stream);
 
+/* ── packed layer -> fp16 K, V ────────────────────────────────────────────────
+ * Replaces unpack_k_mixed (obkv_accel/packing.py:581-709), unpack_v_segment (:1427-1444) and the
+ * per-layer body of unpack_trizone_to_past_kv (obkv_accel/trizone_decompress.py:43-183, 247-290):
+ * value = fp16((float(code) - float(zp)) * float(scale)), bit-identical to the reference.
+ * `view` is a HOST pointer (copied into the launch).  k_out / v_out: fp16 [H_kv][rows_out][D] with
+ * out_head_stride elements between heads; either may be NULL (that side is skipped).
+ *   K: slot j of a head's sorted kept channels (2-bit | 4-bit | 8-bit, counts from
+ *      k_ch_counts[h][3], or n_ch2 / n_ch4 / n_ch8 for every head when it is NULL) goes to original
+ *      channel k_sort_idx[h * k_sort_idx_head_stride + j]; all other channels and rows >= view->t_k
+ *      are zeros.
+ *   V: rows [0, n2+n4+n8) of a head are its dequantised segments in head-local order, rows
+ *      [view->max_t_v, + n_v16[h]) its fp16 Zone-B rows, every other row zeros. */
+int rdkv_unpack_layer(const rdkv_layer_view* view, int H_kv, int D, const int64_t* k_sort_idx,
+                      int64_t k_sort_idx_head_stride, const int32_t* k_ch_counts, int n_ch2, int n_ch4,
+                      int n_ch8, uint16_t* k_out, uint16_t* v_out, int64_t out_head_stride, int rows_out,
+                      void* stream);
+
 /* ── prefill: every layer of a cache in one pass ──────────────────────────────
  * The reference packs a whole cache layer by layer (build_packed_cache,
  * obkv_accel/packing.py:1323-1421; driver loop obkv_fast.py:1098-1166); here the

@@ -1,8 +1,8 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own
 Python code (PyTorch CPU kernels) on seeded inputs.
 
-    python tests/golden/make_golden.py /path/to/reference/checkout
-    (or RDKV_REFERENCE=/path/to/reference/checkout in the environment)
+    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack]
+    (or RDKV_REFERENCE=/path/to/reference/checkout in the environment; no part named = all)
 
 The reference checkout is only needed to (re)generate the files; the tests read
 the committed .npz files and never import the reference.  Inputs are stored
@@ -219,6 +219,44 @@ def make_scoring():
     np.savez_compressed(os.path.join(HERE, "scoring.npz"), **out)
 
 
+LAYER_CASES = {
+    "even": dict(H_kv=2, g=4, T=384, N=128, seed=synth.unit_seed(0, 0, 1)),
+    "ragged": dict(H_kv=3, g=2, T=320, N=96, seed=synth.unit_seed(0, 1, 2), per_head_N=[96, 84, 72],
+                   k_mix=((8, 9), (4, 21), (2, 30))),
+    "gqa8": dict(H_kv=1, g=8, T=200, N=64, seed=synth.unit_seed(4, 0, 0), k_mix=((8, 128),)),
+}
+
+
+def make_unpack():
+    """Decompressor vectors: the reference's unpack_trizone_to_past_kv (trizone_decompress.py:185) on the
+    layers of layers.npz (same seeds), and unpack_v_segment (packing.py:1427) on one segment of each width."""
+    out = {}
+    for tag, c in LAYER_CASES.items():
+        K, V = synth.make_kv(c["H_kv"], c["T"], seed=c["seed"])
+        v_bits = synth.make_v_bits(c["H_kv"], c["T"], c["N"], seed=c["seed"], per_head_N=c.get("per_head_N"))
+        k_bits = synth.make_k_bits(c["H_kv"], seed=c["seed"], mix=c.get("k_mix", ((8, 16), (4, 24), (2, 24))))
+        pl, nv = ref_pack_kv(K, V, v_bits, k_bits, c["g"])
+        cache = P.TriZoneCache(packed=(pl,), new_v_only=[nv], new_both_k=[None], new_both_v=[None], original_seq_len=0)
+        ((K_hat, V_hat),), masks = TD.unpack_trizone_to_past_kv(cache, head_dim=128, return_masks=True, max_new_tokens=3)
+        out[f"{tag}_K_hat"] = npy(K_hat); out[f"{tag}_V_hat"] = npy(V_hat)
+        out[f"{tag}_zone_a"] = npy(TD._unpack_v_perhead(pl, head_dim=128))
+        if masks[0] is not None:
+            out[f"{tag}_mask"] = npy(masks[0].float())
+    g = torch.Generator().manual_seed(99)
+    x = torch.randn(1, 2, 37, 128, generator=g).half()
+    for bits in (2, 4, 8):
+        codes, sc, zp = P.quantize_and_pack(x, bits, 3)
+        out[f"seg{bits}_codes"] = npy(codes); out[f"seg{bits}_scale"] = npy(sc); out[f"seg{bits}_zp"] = npy(zp)
+        out[f"seg{bits}_out"] = npy(P.unpack_v_segment(codes, sc, zp, bits))
+    np.savez_compressed(os.path.join(HERE, "unpack.npz"), **out)
+    print("unpack.npz", os.path.getsize(os.path.join(HERE, "unpack.npz")), "bytes")
+
+
 if __name__ == "__main__":
-    main()
-    make_scoring()
+    parts = sys.argv[2:] or ["layers", "scoring", "unpack"]
+    if "layers" in parts:
+        main()
+    if "scoring" in parts:
+        make_scoring()
+    if "unpack" in parts:
+        make_unpack()

@@ -119,3 +119,16 @@ def test_scoring_oracle_matches_reference_vectors():
             got = RS.score_pooling(src, pt, ks, mode)
             assert got.shape == g[key].shape, key
             assert np.array_equal(got, g[key]), key
+
+
+@pytest.mark.parametrize("tag", ["even", "ragged", "gqa8"])
+def test_dequantise_matches_reference(golden_layers, tag):
+    """Oracle dequantisation against the reference's unpack_trizone_to_past_kv outputs (bit-exact fp16)."""
+    from conftest import load_golden
+    u = sub(load_golden("unpack.npz"), tag)
+    g = sub(golden_layers, tag)
+    layer, nv = RP.pack_kv(g["K"], g["V"], g["v_bits"], g["k_bits"], int(g["g"]))
+    assert np.array_equal(RP.unpack_k(layer, 128).view(np.uint16), u["K_hat"].view(np.uint16))
+    v_hat = RP.unpack_v(layer, nv, 128)
+    assert np.array_equal(v_hat.view(np.uint16), u["V_hat"].view(np.uint16))
+    assert np.array_equal(v_hat[:, :, :layer["T_eff"]].view(np.uint16), u["zone_a"].view(np.uint16))
