@@ -36,6 +36,9 @@ METRIC = "packed-KV decode-attn tokens/s"
 # the committed ncu capture (profiles/; an 8-layer launch: 286.4 MB moved for 280.2 MB algorithmic);
 # traffic grows with the units processed, so the ratio carries over to the full launch.
 NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = 1.022
+# the same ratio for the four packing launches of config 1 (profiles/: 934.7 MB moved for 945.4 MB
+# algorithmic; the launch list is a one-pass capture of the full workload)
+PACK_NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = 0.989
 
 
 def load_peaks():
@@ -456,10 +459,11 @@ def run_pack(args, rank, world, device):
                                    "all layers in one pass (pack_kv_layers)",
                        "l2": "4.3 GB of inputs per step > L2"},
             "roofline": {"bound": "hbm", "achieved": moved / (kern_ms / 1e3) / 1e9, "peak": peak, "unit": "GB/s",
-                         "frac": moved / (kern_ms / 1e3) / 1e9 / peak, "traffic": None, "peak_kind": kind,
+                         "frac": moved / (kern_ms / 1e3) / 1e9 / peak,
+                         "traffic": moved * PACK_NCU_TRAFFIC_BYTES_PER_ALGO_BYTE, "peak_kind": kind,
                          "kernel": "pack_v128_batched_kernel + pack_k_minmax128_batched_kernel + pack_k_params_batched_kernel + pack_k_quant_batched_kernel",
                          "kernel_ms": kern_ms, "algorithmic_bytes_per_step": moved},
-            "gpu_launches": 5 * args.steps, "clocks": sampler.summary()}
+            "gpu_launches": 6 * args.steps, "clocks": sampler.summary()}
     if not args.no_cpu_baseline:
         from oracle import ref_packing as RP
         K, V, vb, kb = Ks[0].cpu().numpy(), Vs[0].cpu().numpy(), v_bits[0].cpu().numpy(), k_bits[0].cpu().numpy()
