@@ -232,6 +232,37 @@ def test_edge_cases():
     assert packed.K_2bit is None and packed.K_8bit is None and packed.K_ch_scale.shape[-1] == 0
 
 
+def test_unaligned_strided_inputs():
+    """K and V as views into wider buffers (rows start 6 bytes off, row stride not a multiple of 8
+    bytes): the element-wise load paths and the unstaged K pass, per layer and all layers at once."""
+    from oracle import ref_packing as RP
+    from rdkv_b200 import synth
+    from rdkv_b200.packing import pack_kv, pack_kv_layers
+    H, T = 3, 300
+    Ks, Vs, vbs, kbs, wants = [], [], [], [], []
+    for layer in range(2):
+        seed = synth.unit_seed(12, layer)
+        K, V = synth.make_kv(H, T, seed=seed)
+        vb = synth.make_v_bits(H, T, 120, seed=seed, per_head_N=[120, 90, 77])
+        kb = synth.make_k_bits(H, seed=seed)
+        views = []
+        for x in (K, V):
+            wide = torch.zeros(1, H, T, 128 + 6, dtype=x.dtype, device="cuda")
+            wide[..., 3:131] = x.cuda()
+            views.append(wide[..., 3:131])
+            assert views[-1].data_ptr() % 8 == 6 and views[-1].stride(2) == 134
+        Ks.append(views[0]); Vs.append(views[1]); vbs.append(vb.cuda()); kbs.append(kb.cuda())
+        wants.append(RP.pack_kv(K.numpy(), V.numpy(), vb.numpy(), kb.numpy(), 2))
+        packed, nv = pack_kv(views[0], views[1], vbs[-1], kbs[-1], 2)
+        assert_layer_equal(layer_to_np(packed), wants[-1][0], f"unaligned{layer}.")
+        assert np.array_equal(to_np(nv), wants[-1][1])
+    batch = pack_kv_layers(Ks, Vs, torch.stack(vbs), torch.stack(kbs), 2)
+    for layer in range(2):
+        packed, nv = batch[layer]
+        assert_layer_equal(layer_to_np(packed), wants[layer][0], f"unaligned.batched{layer}.")
+        assert np.array_equal(to_np(nv), wants[layer][1])
+
+
 def test_full_size_properties():
     """Config-1 layer (8 heads x 32768 tokens, budget 4096): size-independent checks —
     byte-exact round trip of the codes through dequantise/requantise and range bounds."""
