@@ -170,8 +170,7 @@ def max_over_ranks(x: float, world: int, device) -> float:
 
 def run_decode(args, rank, world, device):
     from rdkv_b200._lib import lib
-    from rdkv_b200.decode import (DecodeTable, decode_attention_phases, packed_decode_attention,
-                                  packed_decode_attention_host)
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention, packed_decode_attention_host
     cfg = dict(CFG3)
     if args.small:
         cfg.update(layers=2, batch=2, context=4096, budget=1024)
@@ -189,7 +188,7 @@ def run_decode(args, rank, world, device):
     tables, step_bytes = [], None
     while True:
         layers, nvs, nbytes = build_decode_cache(cfg, h0, h1, len(tables), device)
-        tables.append(DecodeTable(layers, nvs, Hq_loc))
+        tables.append(DecodeTable(layers, nvs, Hq_loc, n_chunks=args.chunks))
         step_bytes = nbytes
         if len(tables) * nbytes >= 2.2 * L2_BYTES or args.small:
             break
@@ -219,9 +218,8 @@ def run_decode(args, rank, world, device):
         for i in range(args.steps):
             tb = tables[i % R]
             ev[i][0].record()
-            decode_attention_phases(q_pool[i % n_q], tb, out, phases=1)
+            packed_decode_attention(q_pool[i % n_q], tb, out=out)
             ev[i][1].record()
-            decode_attention_phases(q_pool[i % n_q], tb, out, phases=2)
         torch.cuda.synchronize()
     torch.cuda.profiler.stop()
     fused_ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
@@ -247,7 +245,7 @@ def run_decode(args, rank, world, device):
         tb.check_status()
     t0 = tables[0]
     v_main, k_rest, rows_rest = t0.unit_plan(t0.n_views)
-    launches = (1 if v_main > 0 else 0) + (0 if v_main == t0.n_views else (1 if k_rest == 1 else 2))
+    launches = 1
     if rank != 0:
         return None
     peak, peak_kind = load_peaks()
@@ -272,8 +270,10 @@ def run_decode(args, rank, world, device):
             "l2": f"{R} cache replica(s) rotated per step, {R * step_bytes / 2**20:.0f} MiB per GPU "
                   f"> 2 x 126 MiB L2; no flush needed",
             "small": bool(args.small or args.layers),
-            "launch_shape": ("one CTA per (view, KV head)" if v_main == t0.n_views
-                             else f"{k_rest} chunks of {rows_rest} rows per (view, KV head) + merge"),
+            "launch_shape": ("one CTA per (view, KV head)" if k_rest == 1
+                             else f"{t0.plan(t0.n_views)[2]} (view, KV head) units whole, the other "
+                                  f"{t0.n_views * (h1 - h0) - t0.plan(t0.n_views)[2]} in {k_rest} chunks of {rows_rest} "
+                                  "rows merged in the kernel"),
         },
         "hbm_gbs": total_step_bytes * args.steps / sec / 1e9,
         "hbm_frac_of_8tbs": total_step_bytes * args.steps / sec / 1e9 / (8000.0 * world),
@@ -570,6 +570,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="2 layers x batch 2 (smoke-sized case)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling-sized runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--chunks", type=int, default=None, help="force this many chunks per (view, KV head) (default: planned)")
     ap.add_argument("--e2e-slices", type=int, default=None,
                     help="view ranges (streams) the host-buffer call overlaps its copies and kernels over")
     args = ap.parse_args()

@@ -130,7 +130,7 @@ int rdkv_v_weighted_sum(const rdkv_layer_view* view, const float* w, int64_t w_r
  * may be NULL.  k_row_bytes_max: largest K bytes per row (sub_2 + sub_4 + n_ch_8)
  * over the views; it sizes the shared-memory stages (rdkv_decode_stage_bytes).
  * status: optional device int32, OR-ed with 1 if a staging wait ran out and with 2
- * if a view did not fit the launch (k_row_bytes_max too small, or more than 512
+ * if a view did not fit the launch (k_row_bytes_max too small, or more than 384
  * padded channels); the affected records are then invalid.
  * Alignment: V code tensors 4-byte, fp16 V tensor 8-byte, scale/zp 2-byte aligned. */
 /* The two halves of the same kernel behind the reference's two-stage interface
@@ -154,6 +154,52 @@ int rdkv_decode_stage_bytes(int k_row_bytes_max);
 int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,
                              int H_q, int H_kv, int chunk_rows, int n_chunks, int k_row_bytes_max,
                              float* partials, float* out, int32_t* status, void* stream);
+
+/* The same kernel with everything a decode step needs in ONE launch (new; same reference
+ * block, obkv_accel/fast_decode.py:1701-1784):
+ *   - row_begin / row_end: only the live rows [row_begin, row_end) of every head are attended
+ *     over (0 / INT32_MAX = all of them); chunk c covers rows [row_begin + c*chunk_rows, +chunk_rows)
+ *     cut at row_end.  A sequence-split rank passes its row window of the shared packed layer and
+ *     asks for out_record.
+ *   - unit_recs / k_slots / nkb_max: optional prepared table of the views (rdkv_decode_prepare
+ *     below); NULL / NULL / 0 = the kernel reads counts, scales, zero points and permutations from
+ *     the views' own tensors (a second, dependent round trip per CTA).
+ *   - n_whole_units: of the launch's units (view, KV head, group of 8 query heads; in that order)
+ *     the first n_whole_units are attended over by one CTA each whatever n_chunks says; only the
+ *     remaining ones are cut into n_chunks chunks.  CTAs start in launch order, so a launch whose
+ *     units do not fill the last round of CTAs evenly can keep full rounds of whole units and cut
+ *     just the leftover ones finely enough to fill the last round (0 = cut every unit).
+ *   - n_chunks > 1: chunk records go to partials ([n_views*H_q][n_chunks][132]) and the last CTA of
+ *     each (view, KV head, group of 8 query heads) to finish merges them in chunk order; nobody
+ *     waits.  unit_counters: int32 [n_views][H_kv * ceil(g/8)], zero before the first launch; the
+ *     kernel leaves them zero again.  Launches that share counters or partials must not overlap.
+ *   - exactly one of out (normalised fp32 [n_views][H_q][128]) and out_record (un-normalised
+ *     (m, l, -, -, o[128]) per (view, query head), input of rdkv_lse_combine across shards). */
+int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,
+                     int H_kv, int chunk_rows, int n_chunks, int n_whole_units, int row_begin, int row_end,
+                     int k_row_bytes_max, const void* unit_recs, const void* k_slots, int nkb_max,
+                     float* partials, int32_t* unit_counters, float* out, float* out_record,
+                     int32_t* status, void* stream);
+
+/* Prepared table of a set of views (new; the reference re-derives the same per-head quantities
+ * in Python before every kernel call, obkv_accel/triton_k_kernel.py:1236-1285).  Per (view, KV
+ * head): the head's V row counts (n2, n4, n8, n16), where the rows of each V phase start in every
+ * tensor, a flag saying that every byte range of the head can be staged in whole 16-byte blocks,
+ * and the head's kept K channels as the fused kernel's threads consume them (original channel,
+ * zero point, scale per padded slot, in MMA fragment order).
+ * It is a snapshot of the view records and of their count, K scale, K zero-point and permutation
+ * tensors: a caller that rewrites any of those in place runs rdkv_decode_prepare again (one small launch, capturable)
+ * before the next rdkv_decode_attn that is given the table.  Packed payloads and V scales / zero
+ * points are never copied.
+ *   nkb_max: max over the views of rdkv_decode_k_blocks(n_ch2_pad, n_ch4_pad, n_ch8) (<= 24);
+ *   unit_recs: rdkv_decode_prepared_bytes(n_views*H_kv, nkb_max, 0) bytes, 16-byte aligned;
+ *   k_slots:   rdkv_decode_prepared_bytes(n_views*H_kv, nkb_max, 1) bytes, 16-byte aligned.
+ * A launch over a sub-range of the views starting at view v0 offsets the two pointers by
+ * v0*H_kv units (rdkv_decode_prepared_bytes(1, nkb_max, 0) resp. (1, nkb_max, 1) bytes per unit). */
+int rdkv_decode_k_blocks(int n_ch2_pad, int n_ch4_pad, int n_ch8);
+int64_t rdkv_decode_prepared_bytes(int64_t n_units, int nkb_max, int which);
+int rdkv_decode_prepare(const rdkv_layer_view* views, int n_views, int H_kv, int nkb_max, void* unit_recs,
+                        void* k_slots, void* stream);
 
 /* Log-sum-exp merge of split-sequence partials (new; the reference has no
  * split path — it is the combine step of the fused call above and of the

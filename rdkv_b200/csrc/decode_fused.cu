@@ -38,7 +38,20 @@ constexpr int FSTAGES = RDKV_FSTAGES;  // ring depth
 constexpr int TILE_MAX = RDKV_TILE_ROWS;           // rows per tile (2-bit and 4-bit phases)
 constexpr int V_STAGE = 64 * TILE_MAX;             // V payload bytes per stage
 constexpr int GH = 8;                  // query heads per CTA pass (N of the P.V product)
-constexpr int KB_MAX = 32;             // 16-channel blocks of the score product
+#ifndef RDKV_KB_MAX
+#define RDKV_KB_MAX 24
+#endif
+#ifndef RDKV_DPAD_MAX
+#define RDKV_DPAD_MAX 384
+#endif
+constexpr int KB_MAX = RDKV_KB_MAX;    // 16-channel blocks of the score product (3 segments x 128 channels at most)
+constexpr int DPAD_MAX = RDKV_DPAD_MAX;  // padded channel slots of a view (n_ch2_pad + n_ch4_pad + n_ch8)
+// dynamic shared memory behind the ring: folded queries in MMA fragment order, then the scratch the
+// fold reads (the group's query rows as fp32, the head's K scales, zero points and channel permutation)
+constexpr int QS_BYTES = KB_MAX * 32 * 8;
+constexpr int FOLD_Q_BYTES = GH * 128 * 4;
+constexpr int FOLD_META_BYTES = 3 * DPAD_MAX * 2;
+constexpr int TAIL_BYTES = QS_BYTES + FOLD_Q_BYTES + FOLD_META_BYTES;
 constexpr float TWO24 = 16777216.f;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -102,6 +115,12 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// Same with an L2 eviction policy for the lines it reads.
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+               : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_on_copies(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -147,6 +166,46 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   uint32_t y;
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
   return y;
+}
+// Loads of the small per-launch tables (view records, prepared tables) ask L2 to keep their lines
+// over the packed payload that streams through it (evict_last); the payload's bulk copies ask for
+// evict_first.
+#ifndef RDKV_L2HINT
+#define RDKV_L2HINT 1
+#endif
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+  uint64_t p;
+  asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_stream() {
+  uint64_t p;
+  asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ int ldg_keep(const int* a) {
+#if RDKV_L2HINT
+  int x;
+  asm volatile("ld.global.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(x) : "l"(a), "l"(l2_policy_keep()));
+  return x;
+#else
+  return *a;
+#endif
+}
+__device__ __forceinline__ int4 ldg_keep4(const int4* a) {
+#if RDKV_L2HINT
+  int4 x;
+  asm volatile("ld.global.L2::cache_hint.v4.b32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w)
+               : "l"(a), "l"(l2_policy_keep()));
+  return x;
+#else
+  return *a;
+#endif
+}
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+  const __half2 c = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&c);
 }
 __device__ __forceinline__ float pow2i(int e) { return __int_as_float((127 + e) << 23); }
 __device__ __forceinline__ float ex2(float x) {
@@ -211,6 +270,26 @@ __device__ inline int k_slot(const KDims& d, int kb, int j, int e, float* factor
   *factor = 1.f;
   return i < d.n8 ? d.n2p + d.n4p + i : -1;
 }
+
+// Per (view, KV head) record of a prepared table (rdkv_decode_prepare): the head's row counts and
+// whether every byte range of the whole head lies on 16-byte blocks inside its tensor (then so
+// does every sub-range a chunk may take), and per V phase where its rows start in every tensor, so
+// that a chunk's geometry is a few integer operations on one record.  16-byte aligned.
+struct __align__(16) PhaseRec {                 // one V phase (2-bit, 4-bit, 8-bit, fp16 rows) of the head
+  int b_lo, b_hi, pad0, pad1;                    // its live-row range
+  const unsigned char *k2, *k4, *k8, *vrow, *sc, *zp;   // addresses of row b_lo in the K streams, the V tensor, V scale / zero point
+};
+struct __align__(16) UnitRec {
+  int n2, n4, n8, n16;
+  int flags, nkb, n_ch2_pad, n_ch4_pad;
+  int n_ch8, max_t_v, pad0, pad1;
+  PhaseRec ph[4];
+};
+static_assert(sizeof(PhaseRec) == 64 && sizeof(UnitRec) == 304, "prepared-table records are read as int4 words");
+// One slot quadruple of the prepared K table: what thread `lane` of 16-channel block `kb` needs to
+// fold its four query elements — original channels, zero points (integers 0..255) and fp16 scales
+// (0 for a pad slot).  16 bytes; [unit][kb][lane].
+struct __align__(16) KSlotRec { uint32_t perm4, zp4, sc01, sc23; };
 
 // Accumulator unit exponent: true value = acc * 2^E(phase, v), v = m-tile & 3.
 __device__ __forceinline__ int acc_exp(int phase, int v) {
@@ -335,6 +414,78 @@ __device__ __noinline__ void final_merge(const float* red, const float* ml, floa
   }
 }
 
+// Chunked units without a second launch: every CTA of a unit (view, KV head, head group) calls
+// this after it has written its chunk's records.  The CTAs count themselves on the unit's arrival
+// counter; the one that finds it has arrived last merges the unit's n_chunks records per query
+// head, in chunk order (so the result does not depend on who arrived last), into the normalised
+// output or one un-normalised record, and puts the counter back to zero for the next launch.
+// Nobody waits for anybody.  (Measured against a variant in which the CTA of the last chunk
+// polls the counter and the others leave without reading it: no difference.)
+// row0: index of the unit's first query head among all (view, head) rows.
+__device__ __noinline__ void chunk_merge(const float* partials, int* counter, int n_chunks, int gcnt,
+                                         int64_t row0, float* out, float* merged) {
+  __shared__ int s_last;
+  const int tid = threadIdx.x;
+  __syncthreads();                                         // the CTA's record stores are ordered before thread 0's fence
+  if (tid == 0) {
+    __threadfence();
+    const int old = atomicAdd(counter, 1);
+    s_last = old == n_chunks - 1;
+    if (s_last) { *counter = 0; __threadfence(); }         // acquire side: the other CTAs' records
+  }
+  __syncthreads();
+  if (!s_last) return;
+  // thread = (query head slot, channel quarter): every load of the unit's records is in flight at once
+  for (int base_hq = 0; base_hq < gcnt; base_hq += 4) {
+    const int hq = base_hq + (tid >> 5);
+    if (tid >= 128 || hq >= gcnt) continue;
+    const int d0 = (tid & 31) * 4;
+    const float* base = partials + (row0 + hq) * n_chunks * RDKV_PARTIAL_STRIDE;
+    float M = -INFINITY, L = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+    for (int s0 = 0; s0 < n_chunks; s0 += 4) {             // four records in flight at a time, merged in chunk order
+      float m[4], l[4];
+      float4 x[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool ok = s0 + i < n_chunks;
+        const float* rec = base + (s0 + i) * RDKV_PARTIAL_STRIDE;
+        m[i] = ok ? __ldcg(rec) : -INFINITY;
+        l[i] = ok ? __ldcg(rec + 1) : 0.f;
+        x[i] = ok ? __ldcg(reinterpret_cast<const float4*>(rec + 4 + d0)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (m[i] == -INFINITY) continue;
+        const float Mn = fmaxf(M, m[i]);
+        const float a = exp2f((M - Mn) * LOG2E), b = exp2f((m[i] - Mn) * LOG2E);
+        L = L * a + l[i] * b;
+        o.x = o.x * a + x[i].x * b; o.y = o.y * a + x[i].y * b; o.z = o.z * a + x[i].z * b; o.w = o.w * a + x[i].w * b;
+        M = Mn;
+      }
+    }
+    if (out != nullptr) {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      *reinterpret_cast<float4*>(out + (row0 + hq) * D + d0) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+    } else {
+      float* rec = merged + (row0 + hq) * RDKV_PARTIAL_STRIDE;
+      *reinterpret_cast<float4*>(rec + 4 + d0) = o;
+      if (d0 == 0) *reinterpret_cast<float4*>(rec) = make_float4(M, L, 0.f, 0.f);
+    }
+  }
+}
+
+// What a CTA's last step needs, parked in shared memory at its start so that it does not occupy
+// registers across the tile loop.
+struct EpiInfo {
+  float* out_rows;                     // normalised output rows of this CTA's query heads
+  float* rec0;                         // record of its first query head (records of the next heads rec_stride floats on)
+  int64_t rec_stride;
+  int64_t row0;                        // index of its first query head among all (view, head) rows
+  int how, gcnt, n_chunks, unit_y;
+};
+
 // MODE_ATTN: the whole attention block.  MODE_SCORES: only the q.K scores of the live rows, written
 // to aux[(query head) * aux_stride + stripe row] for stripe rows < t_eff (the K kernel of the
 // two-stage interface; V is not read).  MODE_WEIGHTS: the softmax weights are given in
@@ -350,60 +501,181 @@ __global__ void __maxnreg__(RDKV_MAXNREG)
 __global__ void __launch_bounds__(CTA_THREADS, RDKV_MINB)
 #endif
 decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __restrict__ q, int q_dtype,
-                    int H_q, int g, int chunk_rows, int n_chunks, int stage_bytes,
+                    int H_q, int g, int chunk_rows, int k_chunks, int n_whole, int stage_bytes,
                     float* __restrict__ partials, float* __restrict__ out, int* __restrict__ status,
-                    float* __restrict__ aux, int64_t aux_stride, int t_eff) {
+                    float* __restrict__ aux, int64_t aux_stride, int t_eff,
+                    const UnitRec* __restrict__ unit_recs, const KSlotRec* __restrict__ kslots, int nkb_max,
+                    int* __restrict__ unit_ctr, float* __restrict__ merged, int row_begin, int row_end) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ rdkv_layer_view v;
   __shared__ CtaGeom G;
-  __shared__ float s_bias[GH];
   __shared__ float s_ml[FW][GH][3];               // per warp: m, l, zero-point term
   __shared__ float s_fin[GH][FW + 3];             // final merge: weight of each warp's partial; M, L, zero-point term
+  __shared__ EpiInfo s_epi;
   __shared__ TileInfo s_tile[FSTAGES];
   __shared__ TilePlan s_plan[PLAN_TILES];          // private to the staging warp
   __shared__ __align__(8) uint64_t s_full[FSTAGES];   // tile in slot s has landed
 
-  const int chunk = blockIdx.x, view_idx = blockIdx.z;
+  // Work items, one per CTA, in launch order: the first n_whole units (view, KV head, group of
+  // query heads) whole, then every remaining unit as k_chunks chunks of chunk_rows live rows.
+  // (Whole units first: the chunks fill the last, partly empty round of CTAs.)
   const int n_hgrp = (g + GH - 1) / GH;
-  const int h = blockIdx.y / n_hgrp, hgrp = blockIdx.y % n_hgrp;
+  const int hy = (H_q / g) * n_hgrp;
+  int unit_y, chunk, n_chunks;
+  if ((int)blockIdx.x < n_whole) {
+    unit_y = blockIdx.x; chunk = 0; n_chunks = 1;
+  } else {
+    const int jj = blockIdx.x - n_whole;
+    unit_y = n_whole + jj / k_chunks; chunk = jj % k_chunks; n_chunks = k_chunks;
+  }
+  const int view_idx = unit_y / hy;
+  const int h = (unit_y % hy) / n_hgrp, hgrp = (unit_y % hy) % n_hgrp;
   const int gh0 = hgrp * GH, gcnt = min(GH, g - gh0);     // query heads [gh0, gh0+gcnt) of this KV head
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, j = lane & 3;
-
-  {
-    const int* src = reinterpret_cast<const int*>(views + view_idx);
-    int* dst = reinterpret_cast<int*>(&v);
-    for (int i = tid; i < (int)(sizeof(rdkv_layer_view) / 4); i += blockDim.x) dst[i] = src[i];
-  }
-  if (tid < FSTAGES) mbar_init(&s_full[tid], 64);        // per staging lane: one plain + one copy-completion arrival
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  __syncthreads();
-
   const int hq0 = h * g + gh0;                             // first query head handled here
-  float* rec0 = partials != nullptr
-                    ? partials + ((int64_t)(view_idx * H_q + hq0) * n_chunks + chunk) * RDKV_PARTIAL_STRIDE
+
+  const uint32_t smem0 = smem_u32(smem_raw);
+  const uint32_t qs_base = smem0 + FSTAGES * stage_bytes;  // uint2 qsA[nkb][32]
+  unsigned char* tail = smem_raw + (size_t)FSTAGES * stage_bytes;
+  const int qs_bytes = QS_BYTES;
+  uint2* qsA = reinterpret_cast<uint2*>(tail);
+  float* f_q = reinterpret_cast<float*>(tail + qs_bytes);                   // [gcnt][128] query rows as fp32
+  uint16_t* f_sc = reinterpret_cast<uint16_t*>(tail + qs_bytes + FOLD_Q_BYTES);   // [d_pad] K scales (fp16 bits; launches without a prepared table)
+  uint16_t* f_zp = f_sc + DPAD_MAX;                                         // [d_pad] K zero points (fp16 bits)
+  uint16_t* f_pm = f_zp + DPAD_MAX;                                         // [d_pad] original channel of each slot
+
+  // ── first round trip.  Compute warps: the view record, this thread's K slots of the prepared
+  //    table and the group's query rows.  Staging warp: the unit's record of the prepared table,
+  //    from which it works out the CTA's geometry without waiting for anything else.  Nothing
+  //    here depends on anything but the launch arguments. ──
+  // named barrier ids: FREE[s] = 1 + s (slot s may be refilled); COMPUTE: the compute warps among
+  // themselves; GEOM: the staging warp has published the CTA's geometry; VIEW: the view record
+  // and the query rows are in shared memory
+  constexpr int BAR_FREE = 1, BAR_COMPUTE = 1 + FSTAGES, BAR_GEOM = 2 + FSTAGES, BAR_VIEW = 3 + FSTAGES;
+  const bool prepared = unit_recs != nullptr;
+  const int64_t unit = (int64_t)view_idx * (H_q / g) + h;
+  KSlotRec km0 = {0u, 0u, 0u, 0u}, km1 = km0;              // this thread's slots of blocks warp, warp + FW
+  int n2p = 0, n4p = 0, n8c = 0;                           // padded channel counts of the view
+  bool geom_done = false;
+  if (warp == FW) {
+    if (lane < FSTAGES) mbar_init(&s_full[lane], 64);      // per staging lane: one plain + one copy-completion arrival
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+    if (prepared) {
+      const int4* up = reinterpret_cast<const int4*>(unit_recs + unit);
+      const int p = lane & 3;
+      const int4 h1 = ldg_keep4(up + 1), h2 = ldg_keep4(up + 2);
+      const int4 a0 = ldg_keep4(up + 3 + 4 * p), a1 = ldg_keep4(up + 4 + 4 * p), a2 = ldg_keep4(up + 5 + 4 * p),
+                 a3 = ldg_keep4(up + 6 + 4 * p);
+      if (h1.x & 1) {                                      // every range of the head lies on whole 16-byte blocks
+        bar_arrive(BAR_VIEW, CTA_THREADS);
+        n2p = h1.z; n4p = h1.w; n8c = h2.x;
+        const KDims kq = k_dims(n2p, n4p, n8c);
+        const StageLayout SQ = stage_layout(kq.sub2, kq.sub4, kq.n8);
+        const bool fits_q = SQ.total <= stage_bytes && kq.n2p + kq.n4p + kq.n8 > 0 &&
+                            kq.n2p + kq.n4p + kq.n8 <= DPAD_MAX && kq.nkb <= KB_MAX;
+        const int c0 = row_begin + chunk * chunk_rows, c1 = n_chunks == 1 ? row_end : min(c0 + chunk_rows, row_end);
+        const int lo = max(a0.x, c0), hi = max(lo, min(a0.y, c1));
+        const int n = hi - lo, d = lo - a0.x;
+        const int ntile = p == 0   ? (n + phase_tile_rows(0) - 1) / phase_tile_rows(0)
+                          : p == 1 ? (n + phase_tile_rows(1) - 1) / phase_tile_rows(1)
+                          : p == 2 ? (n + phase_tile_rows(2) - 1) / phase_tile_rows(2)
+                                   : (n + phase_tile_rows(3) - 1) / phase_tile_rows(3);
+        auto ptr_of = [](int x, int y) {
+          return reinterpret_cast<const unsigned char*>((uintptr_t)(uint32_t)x | ((uintptr_t)(uint32_t)y << 32));
+        };
+        const int t0 = __shfl_sync(0xffffffffu, ntile, 0), t1 = __shfl_sync(0xffffffffu, ntile, 1);
+        const int t2 = __shfl_sync(0xffffffffu, ntile, 2), t3 = __shfl_sync(0xffffffffu, ntile, 3);
+        if (lane < 4) {
+          G.lo[p] = lo; G.hi[p] = hi;
+          G.first_tile[p] = p == 0 ? 0 : p == 1 ? t0 : p == 2 ? t0 + t1 : t0 + t1 + t2;
+          G.krow[p] = p < 3 ? (int64_t)lo : (int64_t)h2.y + d;
+          G.k2[p] = ptr_of(a1.x, a1.y) + (int64_t)d * kq.sub2;
+          G.k4[p] = ptr_of(a1.z, a1.w) + (int64_t)d * kq.sub4;
+          G.k8[p] = ptr_of(a2.x, a2.y) + (int64_t)d * kq.n8;
+          G.vrow[p] = ptr_of(a2.z, a2.w) + (int64_t)d * phase_row_bytes(p);
+          if (p < 3) { G.sc[p] = ptr_of(a3.x, a3.y) + 2 * d; G.zp[p] = ptr_of(a3.z, a3.w) + 2 * d; }
+        }
+        if (lane == 0) {
+          G.fast = 1;
+          G.first_tile[4] = fits_q ? t0 + t1 + t2 + t3 : -1;
+        }
+        __threadfence_block();
+        __syncwarp();
+        bar_arrive(BAR_GEOM, CTA_THREADS);
+        geom_done = true;
+      }
+    }
+    if (!geom_done) bar_sync(BAR_VIEW, CTA_THREADS);       // the general path reads the view record
+  } else {
+    {
+      const int* src = reinterpret_cast<const int*>(views + view_idx);
+      int* dst = reinterpret_cast<int*>(&v);
+      for (int i = tid; i < (int)(sizeof(rdkv_layer_view) / 4); i += FW * 32) dst[i] = ldg_keep(src + i);
+    }
+    if (prepared && MODE != MODE_WEIGHTS) {
+      const int4* kp = reinterpret_cast<const int4*>(kslots + unit * nkb_max * 32 + lane);
+      if (warp < nkb_max) { const int4 t = ldg_keep4(kp + warp * 32); km0 = {(uint32_t)t.x, (uint32_t)t.y, (uint32_t)t.z, (uint32_t)t.w}; }
+      if (warp + FW < nkb_max) { const int4 t = ldg_keep4(kp + (warp + FW) * 32); km1 = {(uint32_t)t.x, (uint32_t)t.y, (uint32_t)t.z, (uint32_t)t.w}; }
+    }
+    if (MODE != MODE_WEIGHTS) {
+      const int64_t q0 = ((int64_t)view_idx * H_q + hq0) * D;
+      const int n = gcnt * D;
+      if (q_dtype == RDKV_F32) {
+        const float* qp = reinterpret_cast<const float*>(q) + q0;
+        if ((reinterpret_cast<uintptr_t>(qp) & 15) == 0) {
+          for (int i = 4 * tid; i < n; i += 4 * FW * 32) *reinterpret_cast<float4*>(f_q + i) = *reinterpret_cast<const float4*>(qp + i);
+        } else {
+          for (int i = tid; i < n; i += FW * 32) f_q[i] = qp[i];
+        }
+      } else {
+        const uint16_t* qp = reinterpret_cast<const uint16_t*>(q) + q0;
+        const bool bf = q_dtype == RDKV_BF16;
+        auto cvt = [&](uint16_t x) { return bf ? __uint_as_float((uint32_t)x << 16) : h2f(x); };
+        if ((reinterpret_cast<uintptr_t>(qp) & 7) == 0) {
+          for (int i = 4 * tid; i < n; i += 4 * FW * 32) {
+            const uint2 w = *reinterpret_cast<const uint2*>(qp + i);
+            *reinterpret_cast<float4*>(f_q + i) = make_float4(cvt((uint16_t)w.x), cvt((uint16_t)(w.x >> 16)),
+                                                              cvt((uint16_t)w.y), cvt((uint16_t)(w.y >> 16)));
+          }
+        } else {
+          for (int i = tid; i < n; i += FW * 32) f_q[i] = cvt(qp[i]);
+        }
+      }
+    }
+    bar_sync(BAR_VIEW, CTA_THREADS);
+  }
+  if (!geom_done) { n2p = v.n_ch2_pad; n4p = v.n_ch4_pad; n8c = v.n_ch8; }
+
+  // where this CTA's result goes: chunked units write one record per chunk (merged by the last
+  // CTA of the unit to finish when the launch brings arrival counters, else by the combine kernel);
+  // a whole unit writes the normalised result or one un-normalised record
+  float* rec_base = (n_chunks > 1 || merged == nullptr) ? partials : merged;
+  float* rec0 = rec_base != nullptr
+                    ? rec_base + ((int64_t)(view_idx * H_q + hq0) * n_chunks + chunk) * RDKV_PARTIAL_STRIDE
                     : nullptr;
   const int64_t rec_stride = (int64_t)n_chunks * RDKV_PARTIAL_STRIDE;
   const bool direct = (n_chunks == 1 && out != nullptr);
+  if (tid == 0) {
+    s_epi.out_rows = out != nullptr ? out + ((int64_t)view_idx * H_q + hq0) * D : nullptr;
+    s_epi.rec0 = rec0; s_epi.rec_stride = rec_stride; s_epi.row0 = (int64_t)view_idx * H_q + hq0;
+    s_epi.how = MODE == MODE_WEIGHTS ? 2 : direct ? 1 : 0;
+    s_epi.gcnt = gcnt; s_epi.n_chunks = n_chunks; s_epi.unit_y = unit_y;
+  }
 
-  const KDims kd = k_dims(v.n_ch2_pad, v.n_ch4_pad, v.n_ch8);
+  const KDims kd = k_dims(n2p, n4p, n8c);
   const int d_pad = kd.n2p + kd.n4p + kd.n8;
   const StageLayout SL = stage_layout(kd.sub2, kd.sub4, kd.n8);
+  const bool fits = SL.total <= stage_bytes && d_pad > 0 && d_pad <= DPAD_MAX && kd.nkb <= KB_MAX;   // view fits this launch
 
-  // named barrier ids: FREE[s] = 1 + s (slot s may be refilled); COMPUTE: the compute warps among
-  // themselves; GEOM: the staging warp has published the CTA's geometry
-  constexpr int BAR_FREE = 1, BAR_COMPUTE = 1 + FSTAGES, BAR_GEOM = 2 + FSTAGES;
-  const uint32_t smem0 = smem_u32(smem_raw);
-  const uint32_t qs_base = smem0 + FSTAGES * stage_bytes;  // uint2 qsA[nkb][32]
-  uint2* qsA = reinterpret_cast<uint2*>(smem_raw + (size_t)FSTAGES * stage_bytes);
-  const bool fits = SL.total <= stage_bytes && d_pad > 0 && kd.nkb <= KB_MAX;   // view fits this launch
-
-  // ── geometry (staging warp, one lane per phase): live rows of this head are [0,n2) 2-bit,
-  //    [n2,n2+n4) 4-bit, [..,t_v) 8-bit, [t_v, t_v+n16) fp16; the chunk takes
-  //    [chunk*chunk_rows, +chunk_rows) of them.  The compute warps fold the queries meanwhile. ──
-  if (warp == FW) {
+  // ── geometry, general path (staging warp, one lane per phase): live rows of this head are
+  //    [0,n2) 2-bit, [n2,n2+n4) 4-bit, [..,t_v) 8-bit, [t_v, t_v+n16) fp16; the chunk takes
+  //    [row_begin + chunk*chunk_rows, +chunk_rows) of them, cut at row_end.  The compute warps
+  //    fold the queries meanwhile. ──
+  if (warp == FW && !geom_done) {
     const HeadCounts hc = head_counts(v, h);
     const int p = lane & 3;
-    const int c0 = chunk * chunk_rows, c1 = c0 + chunk_rows;
+    const int c0 = row_begin + chunk * chunk_rows, c1 = n_chunks == 1 ? row_end : min(c0 + chunk_rows, row_end);
     // (MODE_SCORES: every stripe row below t_eff is scored, as one run of rows; the rows that
     //  belong to no token hold the zero point and score 0, as in the reference)
     const int b_lo = MODE == MODE_SCORES ? 0 : p == 0 ? 0 : p == 1 ? hc.n2 : p == 2 ? hc.n2 + hc.n4 : hc.t_v;
@@ -458,71 +730,80 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   }
 
   // ── q*scale in MMA fragment order and the zero-point bias (compute warps, while the staging
-  //    warp works out the geometry and starts the first copies).  All loads of a round are
-  //    issued before any is used: slot -> permuted channel -> query element is a chain of two
-  //    global round trips, paid once per round of two 16-channel blocks. ──
-  if (MODE != MODE_WEIGHTS && warp < FW && fits) {
-    const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
-    const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
-    const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
+  //    warp works out the geometry and starts the first copies).  The head's scales, zero points
+  //    and channel permutation come into shared memory with one coalesced read each; the fold
+  //    itself then gathers from shared memory only. ──
+  if (MODE != MODE_WEIGHTS && warp < FW && fits && prepared) {
+    // prepared table: this thread's slot quadruples were requested at entry, together with the
+    // view record; nothing else comes from global memory.  Blocks warp and warp + FW are folded
+    // side by side (independent chains), any further ones in a loop.
     const bool head_ok = r < gcnt;
-    const int64_t qoff = ((int64_t)view_idx * H_q + hq0 + (head_ok ? r : 0)) * D;
-    float bias_part = 0.f;                                 // thread (r = head, j) sums its own slots
-    auto fold = [&](auto loadq) {
-#pragma unroll 1
-      for (int kb0 = warp; kb0 < kd.nkb; kb0 += 2 * FW) {
-        int slot[2][4];
-        float f[2][4], scv[2][4], zpv[2][4], qv[2][4];
-        int64_t pm[2][4];
+    const float* qrow = f_q + (head_ok ? r : 0) * D;
+    float bias_part = 0.f;
+    auto fold_block = [&](const KSlotRec& km, int kb, float& bias) {
+      const int ex2b = kb < 2 * kd.nsp2 ? 4 * (kb & 1) : 0;            // exponent of the factor of e = 0, 1
+      const int exs = kb < 2 * kd.nsp2 ? 2 : kb < 2 * kd.nsp2 + 2 * kd.nsp4 ? 4 : 0;   // added for e = 2, 3
+      float val[4];
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int kb = kb0 + u * FW;
-            slot[u][e] = kb < kd.nkb ? k_slot(kd, kb, j, e, &f[u][e]) : -1;
-            if (slot[u][e] < 0) f[u][e] = 1.f;
-          }
-#pragma unroll
-        for (int u = 0; u < 2; ++u)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int sl = max(slot[u][e], 0);
-            pm[u][e] = perm[sl]; scv[u][e] = h2f(sc[sl]); zpv[u][e] = h2f(zp[sl]);
-          }
-#pragma unroll
-        for (int u = 0; u < 2; ++u)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) qv[u][e] = loadq(qoff + pm[u][e]);
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int kb = kb0 + u * FW;
-          float val[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float x = 0.f;
-            if (slot[u][e] >= 0 && head_ok) {
-              x = __half2float(__float2half_rn(qv[u][e] * scv[u][e] / f[u][e]));
-              bias_part += zpv[u][e] * (x * f[u][e]);
-            }
-            val[e] = x;
-          }
-          if (kb < kd.nkb) qsA[kb * 32 + lane] = make_uint2(pack_h2(val[0], val[1]), pack_h2(val[2], val[3]));
-        }
+      for (int e = 0; e < 4; ++e) {
+        const int ex = ex2b + (e >> 1) * exs;
+        const float scv = h2f((uint16_t)((e < 2 ? km.sc01 : km.sc23) >> (16 * (e & 1))));
+        const float zpv = (float)((km.zp4 >> (8 * e)) & 255u);
+        float x = __half2float(__float2half_rn(qrow[(km.perm4 >> (8 * e)) & 127u] * scv * pow2i(-ex)));
+        if (!head_ok) x = 0.f;
+        bias += zpv * (x * pow2i(ex));
+        val[e] = x;
       }
+      qsA[kb * 32 + lane] = make_uint2(pack_h2(val[0], val[1]), pack_h2(val[2], val[3]));
     };
-    if (q_dtype == RDKV_BF16) fold([&](int64_t i) { return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(q)[i]); });
-    else if (q_dtype == RDKV_F16) fold([&](int64_t i) { return __half2float(reinterpret_cast<const __half*>(q)[i]); });
-    else fold([&](int64_t i) { return reinterpret_cast<const float*>(q)[i]; });
+    {
+      float b0 = 0.f, b1 = 0.f;
+      if (warp < kd.nkb) fold_block(km0, warp, b0);
+      if (warp + FW < kd.nkb) fold_block(km1, warp + FW, b1);
+      bias_part = b0 + b1;
+    }
+#pragma unroll 1
+    for (int kb = warp + 2 * FW; kb < kd.nkb; kb += FW) {
+      const int4 t = *(reinterpret_cast<const int4*>(kslots + unit * nkb_max * 32 + lane) + kb * 32);
+      const KSlotRec km = {(uint32_t)t.x, (uint32_t)t.y, (uint32_t)t.z, (uint32_t)t.w};
+      fold_block(km, kb, bias_part);
+    }
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
-    if (j == 0) s_ml[warp][r][0] = bias_part;
+    if (j == 0) s_ml[warp][r][0] = bias_part;            // summed over the warps where it is used
     bar_sync(BAR_COMPUTE, FW * 32);
-    if (tid < GH) {
-      float b = 0.f;
-#pragma unroll
-      for (int w = 0; w < FW; ++w) b += s_ml[w][tid][0];
-      s_bias[tid] = b;
+  } else if (MODE != MODE_WEIGHTS && warp < FW && fits) {
+    {
+      const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
+      const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
+      const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
+      for (int i = tid; i < d_pad; i += FW * 32) {
+        f_sc[i] = sc[i]; f_zp[i] = zp[i]; f_pm[i] = (uint16_t)(perm[i] & (D - 1));
+      }
     }
+    bar_sync(BAR_COMPUTE, FW * 32);
+    const bool head_ok = r < gcnt;
+    const float* qrow = f_q + (head_ok ? r : 0) * D;
+    float bias_part = 0.f;                                 // thread (r = head, j) sums its own slots
+#pragma unroll 1
+    for (int kb = warp; kb < kd.nkb; kb += FW) {
+      float val[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float f;
+        const int slot = k_slot(kd, kb, j, e, &f);
+        float x = 0.f;
+        if (slot >= 0 && head_ok) {
+          x = __half2float(__float2half_rn(qrow[f_pm[slot]] * h2f(f_sc[slot]) / f));
+          bias_part += h2f(f_zp[slot]) * (x * f);
+        }
+        val[e] = x;
+      }
+      qsA[kb * 32 + lane] = make_uint2(pack_h2(val[0], val[1]), pack_h2(val[2], val[3]));
+    }
+    bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
+    bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
+    if (j == 0) s_ml[warp][r][0] = bias_part;            // summed over the warps where it is used
     bar_sync(BAR_COMPUTE, FW * 32);
   }
   if (warp < FW) bar_sync(BAR_GEOM, CTA_THREADS);          // geometry published
@@ -539,6 +820,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         rec0[hq * rec_stride + e] = (e == 0) ? -INFINITY : 0.f;
       }
     }
+    if (MODE == MODE_ATTN && n_chunks > 1 && unit_ctr != nullptr)
+      chunk_merge(partials, unit_ctr + unit_y, n_chunks, gcnt,
+                  (int64_t)view_idx * H_q + hq0, out, merged);
     return;
   }
 
@@ -553,6 +837,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     const unsigned char* scb = reinterpret_cast<const unsigned char*>(v.v_scale);
     const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
     const bool fast = G.fast != 0;
+    const uint64_t pol_stream = l2_policy_stream();
 #pragma unroll 1
     for (int it = 0; it < total_tiles; ++it) {
       const int slot = it % PLAN_TILES;
@@ -575,7 +860,12 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           P.rg[4] = RangePlan{a_sc, (p < 3 && MODE != MODE_SCORES) ? t.n * 2 : 0, (uint32_t)SL.sc};
           P.rg[5] = RangePlan{a_zp, (p < 3 && MODE != MODE_SCORES) ? t.n * 2 : 0, (uint32_t)SL.zp};
           auto low4 = [](const unsigned char* x) { return (uint32_t)reinterpret_cast<uintptr_t>(x) & 15u; };
-          P.info.phase = p; P.info.n = t.n;
+          int blocks_before = 0;                          // 32-row blocks of the chunk ahead of this tile: the tile's first block goes to warp (that % FW)
+#pragma unroll
+          for (int qq = 0; qq < 3; ++qq)
+            if (qq < p) blocks_before += (G.hi[qq] - G.lo[qq] + 31) >> 5;
+          blocks_before += t.row0 >> 5;
+          P.info.phase = p | (blocks_before & (FW - 1)) << 8; P.info.n = t.n;
           P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 | low4(a_v) << 12 |
                         (p < 3 ? low4(a_sc) << 16 | low4(a_zp) << 20 : 0u);
           P.info.krow0 = (int)(G.krow[p] + t.row0);
@@ -599,11 +889,15 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         // every range is contiguous in its tensor: ONE bulk copy each, completion counted in bytes
         if (lane == 0) mbar_expect_tx(&s_full[stage], total);
         __syncwarp();
+#if RDKV_L2HINT
+        if (bytes) bulk_g2s_hint(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage], pol_stream);
+#else
         if (bytes) bulk_g2s(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage]);
+#endif
       } else {
         // a range whose covering blocks stick out of its tensor: guarded 16-byte copies by all lanes
         unsigned char* sb = smem_raw + (size_t)stage * stage_bytes;
-        const int p = ti.phase;
+        const int p = ti.phase & 3;
 #pragma unroll 1
         for (int k = 0; k < 6; ++k) {
           const RangePlan rk = s_plan[slot].rg[k];
@@ -617,7 +911,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       }
       // rows past the tile's end must hold finite fp16 data in the fp16 phase: clear the
       // rest of the last 32-row block beyond the copied blocks
-      if (ti.phase == 3 && (ti.n & 31)) {
+      if ((ti.phase & 3) == 3 && (ti.n & 31)) {
         const int off = (int)((ti.offs >> 12) & 15u);
         const int first = (off + ti.n * 256 + 15) & ~15;
         const int last = min(off + ((ti.n + 31) & ~31) * 256, V_STAGE + 16);
@@ -640,8 +934,14 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   const float c1 = MODE == MODE_SCORES ? TWO24 * INV_SQRT_D : TWO24 * INV_SQRT_D * LOG2E;
   // an absent head gets an infinite bias: its scores are -inf without further tests
   const float bsc = MODE == MODE_SCORES ? INV_SQRT_D : INV_SQRT_D * LOG2E;
-  const float b1e = (he_ok && MODE != MODE_WEIGHTS) ? s_bias[2 * j] * bsc : INFINITY;
-  const float b1o = (ho_ok && MODE != MODE_WEIGHTS) ? s_bias[2 * j + 1] * bsc : INFINITY;
+  auto bias_of = [&](int hq) {                             // zero-point bias of a query head: the warps' partial sums
+    float b = 0.f;
+#pragma unroll
+    for (int w = 0; w < FW; ++w) b += s_ml[w][hq][0];
+    return b;
+  };
+  const float b1e = (he_ok && MODE != MODE_WEIGHTS && warp < FW) ? bias_of(2 * j) * bsc : INFINITY;
+  const float b1o = (ho_ok && MODE != MODE_WEIGHTS && warp < FW) ? bias_of(2 * j + 1) * bsc : INFINITY;
   const bool has_mask = v.mask != nullptr;
   const bool k_aligned = !(kd.sub2 & 1) && !(kd.sub4 & 3) && !(kd.n8 & 3);
   const bool k_simple = kd.nsp2 == 1 && kd.nsp4 == 1 && kd.nkb8 == 1;   // one span per segment: straight-line code
@@ -651,8 +951,15 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   // reference maxima of heads 2j, 2j+1 (same in every r); given weights are used as they are
-  float m_e = MODE == MODE_WEIGHTS ? 0.f : M_NONE, m_o = MODE == MODE_WEIGHTS ? 0.f : M_NONE;
-  float l_e = 0.f, l_o = 0.f, zc_e = 0.f, zc_o = 0.f;      // partial sums over this thread's rows
+  float m_e = MODE == MODE_ATTN ? M_NONE : 0.f, m_o = m_e;
+  // Scores are formed relative to the reference maximum: s = acc*c1 - cb with cb = bias + m (a head
+  // that has no reference yet counts from 0 and moves it at its first finite score: thr = -1e29).
+  float cb_e = b1e, cb_o = b1o;
+  float thr_e = MODE == MODE_ATTN ? -1.0e29f : INFINITY, thr_o = thr_e;
+  float l_e = 0.f, l_o = 0.f;                              // partial sums over this thread's rows
+  // zero-point term sum_t p*scale*zp of heads 2j, 2j+1 ([0], [1]; complete in every lane): an extra
+  // m-tile of the P.V product whose A rows all hold the rows' zero points
+  float zacc[4] = {0.f, 0.f, 0.f, 0.f};
   int cur_phase = -1;
 
 #pragma unroll 1
@@ -669,7 +976,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       }
     }
     const TileInfo t = s_tile[stage];
-    const int p = t.phase;
+    const int p = t.phase & 3;
     // this warp takes the tile's 32-row blocks pb, pb+FW, ... (two 16-row MMA groups each, worked on
     // together so that the two dependency chains overlap); the start rotates from tile to tile so
     // that short tiles (fewer blocks than warps) do not always land on the same warps
@@ -698,8 +1005,12 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       uint32_t k2a = sbu + SL.k2 + off_k2 + (row_b + r) * kd.sub2 + 2 * j;
       uint32_t k4a = sbu + SL.k4 + off_k4 + (row_b + r) * kd.sub4 + 4 * j;
       uint32_t k8a = sbu + SL.k8 + off_k8 + (row_b + r) * kd.n8 + 4 * j;
-      uint32_t sca = sbu + SL.sc + off_m + 2 * (row_b + r);
-      uint32_t zpa = sbu + SL.zp + off_z + 2 * (row_b + r);
+      // V scale / zero point of rows 2j, 2j+1 of the block as one fp16 pair (the rows a thread
+      // holds after the transpose); a tile whose first row sits at an odd fp16 position takes
+      // the two-load form
+      uint32_t sca = sbu + SL.sc + off_m + 2 * (row_b + 2 * j);
+      uint32_t zpa = sbu + SL.zp + off_z + 2 * (row_b + 2 * j);
+      const bool m_al = !((off_m | off_z) & 2u);
       const uint32_t v0a = sbu + SL.v + off_v;
       const int tn = t.n;
       const uint32_t d2 = 8 * kd.sub2, d4 = 8 * kd.sub4, d8 = 8 * kd.n8;   // 8 rows further in each K stream
@@ -843,10 +1154,17 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           }
           // requested now, needed after the softmax: V scale / zero point of the four rows and the
           // first V words of both groups
-          uint32_t rs[4] = {0u, 0u, 0u, 0u}, rz[4] = {0u, 0u, 0u, 0u};
+          uint32_t rs[4] = {0u, 0u, 0u, 0u}, rz[4] = {0u, 0u, 0u, 0u};   // [k]: rows 8k + {2j, 2j+1}
           if (P < 3 && MODE != MODE_SCORES) {
-            rs[0] = lds16(sca); rs[1] = lds16<16>(sca); rs[2] = lds16<32>(sca); rs[3] = lds16<48>(sca);
-            rz[0] = lds16(zpa); rz[1] = lds16<16>(zpa); rz[2] = lds16<32>(zpa); rz[3] = lds16<48>(zpa);
+            if (m_al) {
+              rs[0] = lds32(sca); rs[1] = lds32<16>(sca); rs[2] = lds32<32>(sca); rs[3] = lds32<48>(sca);
+              rz[0] = lds32(zpa); rz[1] = lds32<16>(zpa); rz[2] = lds32<32>(zpa); rz[3] = lds32<48>(zpa);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                rs[k] = lds32_unaligned(sca + 16 * k); rz[k] = lds32_unaligned(zpa + 16 * k);
+              }
+            }
           }
           uint32_t wA0 = 0, wA1 = 0, wA2 = 0, wA3 = 0, xA0 = 0, xA1 = 0, xA2 = 0, xA3 = 0;
           uint32_t wB0 = 0, wB1 = 0, wB2 = 0, wB3 = 0, xB0 = 0, xB1 = 0, xB2 = 0, xB3 = 0;
@@ -863,10 +1181,10 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
 
           // s2[k]: rows g32 + r + 8*(k>>1)... laid out [2k] head 2j, [2k+1] head 2j+1 for row slot k = 0..3
           float s2[8];
-          s2[0] = fmaf(sxA[0] + syA[0], c1, -b1e); s2[1] = fmaf(sxA[1] + syA[1], c1, -b1o);
-          s2[2] = fmaf(sxA[2] + syA[2], c1, -b1e); s2[3] = fmaf(sxA[3] + syA[3], c1, -b1o);
-          s2[4] = fmaf(sxB[0] + syB[0], c1, -b1e); s2[5] = fmaf(sxB[1] + syB[1], c1, -b1o);
-          s2[6] = fmaf(sxB[2] + syB[2], c1, -b1e); s2[7] = fmaf(sxB[3] + syB[3], c1, -b1o);
+          s2[0] = fmaf(sxA[0] + syA[0], c1, -cb_e); s2[1] = fmaf(sxA[1] + syA[1], c1, -cb_o);
+          s2[2] = fmaf(sxA[2] + syA[2], c1, -cb_e); s2[3] = fmaf(sxA[3] + syA[3], c1, -cb_o);
+          s2[4] = fmaf(sxB[0] + syB[0], c1, -cb_e); s2[5] = fmaf(sxB[1] + syB[1], c1, -cb_o);
+          s2[6] = fmaf(sxB[2] + syB[2], c1, -cb_e); s2[7] = fmaf(sxB[3] + syB[3], c1, -cb_o);
           if (MODE == MODE_SCORES) {                       // the scores are the result
             const int64_t col0 = (int64_t)s_tile[stage].krow0 + g32 + r;    // stripe row = output column
             float* oe = aux + (int64_t)(hq0 + 2 * j) * aux_stride + col0;
@@ -888,7 +1206,6 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
               const bool ok = g32 + r + 8 * k < tn;
               s2[2 * k] = (ok && he_ok) ? we[8 * k] : 0.f;
               s2[2 * k + 1] = (ok && ho_ok) ? we[aux_stride + 8 * k] : 0.f;
-              if (!ok) { rs[k] = 0u; rz[k] = 0u; }
             }
           }
           if (MODE == MODE_ATTN && has_mask) {                                  // additive softmax mask (rarely given: everything it needs is re-read here)
@@ -903,29 +1220,41 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
               }
             }
           }
-          if (MODE == MODE_ATTN && g32 + 32 > tn) {        // last, partial block of the tile: rows past its end are dead
+          if (MODE != MODE_SCORES && g32 + 32 > tn) {      // last, partial block of the tile: rows past its end are dead
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              if (g32 + r + 8 * k >= tn) { s2[2 * k] = -INFINITY; s2[2 * k + 1] = -INFINITY; rs[k] = 0u; rz[k] = 0u; }   // (their bytes may be non-finite)
+            for (int k = 0; k < 4; ++k) {
+              if (MODE == MODE_ATTN && g32 + r + 8 * k >= tn) { s2[2 * k] = -INFINITY; s2[2 * k + 1] = -INFINITY; }
+              // (their scale / zero-point bytes may be anything: clear the halves of dead rows)
+              const int row = g32 + 8 * k + 2 * j;
+              const uint32_t keep = row + 1 < tn ? 0xFFFFFFFFu : row < tn ? 0x0000FFFFu : 0u;
+              rs[k] &= keep; rz[k] &= keep;
+            }
           }
           // lazy reference maximum: exact maxima are only worked out when some score of the warp
-          // exceeds its head's reference by more than RESCALE_TH (always true for the first block)
-          const float te = m_e + RESCALE_TH, to = m_o + RESCALE_TH;
+          // exceeds its head's reference by more than RESCALE_TH (or is the head's first finite one)
           const float mxe = fmaxf(fmaxf(s2[0], s2[2]), fmaxf(s2[4], s2[6]));
           const float mxo = fmaxf(fmaxf(s2[1], s2[3]), fmaxf(s2[5], s2[7]));
-          if (MODE == MODE_ATTN && __any_sync(0xffffffffu, mxe > te || mxo > to)) {
+          if (MODE == MODE_ATTN && __any_sync(0xffffffffu, mxe > thr_e || mxo > thr_o)) {
             float me = mxe, mo = mxo;
 #pragma unroll
             for (int o = 4; o < 32; o <<= 1) {
               me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
               mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
             }
-            const float ne = fmaxf(m_e, me), no = fmaxf(m_o, mo);
+            // (scores are relative to the reference in use: 0 for a head without one)
+            const float ue = m_e <= M_NONE ? 0.f : m_e, uo = m_o <= M_NONE ? 0.f : m_o;
+            const float ne = fmaxf(m_e, me + ue), no = fmaxf(m_o, mo + uo);
             const float ae = ex2(m_e - ne), ao = ex2(m_o - no);
-            l_e *= ae; zc_e *= ae; l_o *= ao; zc_o *= ao;
+            l_e *= ae; zacc[0] *= ae; l_o *= ao; zacc[1] *= ao;
 #pragma unroll
             for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
+            const float we = ne <= M_NONE ? 0.f : ne, wo = no <= M_NONE ? 0.f : no;
+            const float de = we - ue, dd = wo - uo;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { s2[2 * k] -= de; s2[2 * k + 1] -= dd; }
             m_e = ne; m_o = no;
+            cb_e = b1e + we; cb_o = b1o + wo;
+            thr_e = ne <= M_NONE ? -1.0e29f : RESCALE_TH; thr_o = no <= M_NONE ? -1.0e29f : RESCALE_TH;
           }
           float pe[8];
           if (MODE == MODE_WEIGHTS) {
@@ -933,25 +1262,20 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             for (int k = 0; k < 8; ++k) pe[k] = s2[k];
           } else {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) { pe[2 * k] = ex2(s2[2 * k] - m_e); pe[2 * k + 1] = ex2(s2[2 * k + 1] - m_o); }
+            for (int k = 0; k < 8; ++k) pe[k] = ex2(s2[k]);
             l_e += (pe[0] + pe[2]) + (pe[4] + pe[6]); l_o += (pe[1] + pe[3]) + (pe[5] + pe[7]);
           }
-          uint32_t hh[4];                                  // row slot k x (head 2j, head 2j+1) as fp16 pairs
+          // row slot k x (head 2j, head 2j+1) as fp16 pairs, then 8x8 transposes: thread (r, j) now
+          // holds head r at rows {2j, 2j+1} and 8 + {2j, 2j+1} of each group
+          uint32_t pA0 = movmatrix_trans(pack_h2(pe[0], pe[1])), pA1 = movmatrix_trans(pack_h2(pe[2], pe[3]));
+          uint32_t pB0 = movmatrix_trans(pack_h2(pe[4], pe[5])), pB1 = movmatrix_trans(pack_h2(pe[6], pe[7]));
           if (P < 3) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const float sck = h2f((uint16_t)rs[k]), zpk = h2f((uint16_t)rz[k]);
-              hh[k] = pack_h2(pe[2 * k] * sck, pe[2 * k + 1] * sck);
-              const float2 fk = __half22float2(*reinterpret_cast<__half2*>(&hh[k]));   // the values the tensor core sees
-              zc_e = fmaf(fk.x, zpk, zc_e); zc_o = fmaf(fk.y, zpk, zc_o);
-            }
-          } else {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) hh[k] = pack_h2(pe[2 * k], pe[2 * k + 1]);
+            // per-row V scale, applied to the row pairs this thread now holds; the zero-point term
+            // takes the same (rounded) factors through the tensor core
+            pA0 = hmul2(pA0, rs[0]); pA1 = hmul2(pA1, rs[1]); pB0 = hmul2(pB0, rs[2]); pB1 = hmul2(pB1, rs[3]);
+            mma16816(zacc, rz[0], 0u, rz[1], 0u, pA0, pA1);
+            mma16816(zacc, rz[2], 0u, rz[3], 0u, pB0, pB1);
           }
-          // 8x8 transposes: thread (r, j) now holds head r at rows {2j, 2j+1} and 8 + {2j, 2j+1} of each group
-          const uint32_t pA0 = movmatrix_trans(hh[0]), pA1 = movmatrix_trans(hh[1]);
-          const uint32_t pB0 = movmatrix_trans(hh[2]), pB1 = movmatrix_trans(hh[3]);
 
           pv_group(va, wA0, wA1, wA2, wA3, xA0, xA1, xA2, xA3, pA0, pA1);
           pv_group(va + 16 * VRB, wB0, wB1, wB2, wB3, xB0, xB1, xB2, xB3, pB0, pB1);
@@ -989,13 +1313,12 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
 #pragma unroll
   for (int o = 4; o < 32; o <<= 1) {                       // rows are spread over r: lanes 4r + j
     l_e += __shfl_xor_sync(0xffffffffu, l_e, o); l_o += __shfl_xor_sync(0xffffffffu, l_o, o);
-    zc_e += __shfl_xor_sync(0xffffffffu, zc_e, o); zc_o += __shfl_xor_sync(0xffffffffu, zc_o, o);
   }
   __syncthreads();                                         // every worker is done with its stages
   float* red = reinterpret_cast<float*>(smem_raw);         // [FW][GH][128]
   if (warp < FW && r == 0) {
-    s_ml[warp][2 * j][0] = m_e; s_ml[warp][2 * j][1] = l_e; s_ml[warp][2 * j][2] = zc_e;
-    s_ml[warp][2 * j + 1][0] = m_o; s_ml[warp][2 * j + 1][1] = l_o; s_ml[warp][2 * j + 1][2] = zc_o;
+    s_ml[warp][2 * j][0] = m_e; s_ml[warp][2 * j][1] = l_e; s_ml[warp][2 * j][2] = zacc[0];
+    s_ml[warp][2 * j + 1][0] = m_o; s_ml[warp][2 * j + 1][1] = l_o; s_ml[warp][2 * j + 1][2] = zacc[1];
   }
 #pragma unroll
   for (int i = 0; i < 8 && warp < FW; ++i) {
@@ -1005,8 +1328,10 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     o0[ch] = acc[i][0]; o1[ch] = acc[i][1]; o0[ch + 1] = acc[i][2]; o1[ch + 1] = acc[i][3];
   }
   __syncthreads();
-  final_merge(red, &s_ml[0][0][0], s_fin, gcnt, MODE == MODE_WEIGHTS ? 2 : direct ? 1 : 0,
-              out + ((int64_t)view_idx * H_q + hq0) * D, rec0, rec_stride);
+  const EpiInfo ep = s_epi;
+  final_merge(red, &s_ml[0][0][0], s_fin, ep.gcnt, ep.how, ep.out_rows, ep.rec0, ep.rec_stride);
+  if (MODE == MODE_ATTN && ep.n_chunks > 1 && unit_ctr != nullptr)
+    chunk_merge(partials, unit_ctr + ep.unit_y, ep.n_chunks, ep.gcnt, ep.row0, out, merged);
 }
 
 }  // namespace rdkv
@@ -1015,23 +1340,106 @@ using namespace rdkv;
 
 extern "C" int rdkv_decode_stage_bytes(int k_row_bytes_max) { return stage_capacity(k_row_bytes_max); }
 
+// Prepared table of a set of views: per (view, KV head) a UnitRec (row counts, whole-head
+// alignment flag) and the K slot quadruples in the order the fused kernel's threads consume them.
+// With it a CTA needs ONE round trip to global memory (view record, unit record, slots and query
+// rows together) before its staging warp can plan copies and its compute warps can fold the
+// queries; without it the counts, scales, zero points and permutation cost a second, dependent
+// round trip and the slot arithmetic is redone by every CTA.  One block per unit.
+__global__ void __launch_bounds__(128)
+decode_prepare_kernel(const rdkv_layer_view* __restrict__ views, int H_kv, int nkb_max,
+                      UnitRec* __restrict__ recs, KSlotRec* __restrict__ kslots) {
+  const int64_t unit = blockIdx.x;
+  const rdkv_layer_view& v = views[unit / H_kv];
+  const int h = (int)(unit % H_kv);
+  const KDims kd = k_dims(v.n_ch2_pad, v.n_ch4_pad, v.n_ch8);
+  const int d_pad = kd.n2p + kd.n4p + kd.n8;
+  const uint16_t* sc = v.k_scale + (int64_t)h * d_pad;
+  const uint16_t* zp = v.k_zp + (int64_t)h * d_pad;
+  const int64_t* perm = v.k_perm + (int64_t)h * v.k_perm_head_stride;
+  for (int i = threadIdx.x; i < nkb_max * 32; i += blockDim.x) {
+    const int kb = i >> 5, j = i & 3;
+    KSlotRec rec = {0u, 0u, 0u, 0u};
+    if (kb < kd.nkb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float f;
+        const int slot = k_slot(kd, kb, j, e, &f);
+        if (slot < 0) continue;
+        const uint32_t pm = (uint32_t)(perm[slot] & (D - 1));
+        const uint32_t z = (uint32_t)min(255.f, fmaxf(0.f, h2f(zp[slot])));
+        rec.perm4 |= pm << (8 * e);
+        rec.zp4 |= z << (8 * e);
+        if (e < 2) rec.sc01 |= (uint32_t)sc[slot] << (16 * e); else rec.sc23 |= (uint32_t)sc[slot] << (16 * (e - 2));
+      }
+    }
+    kslots[unit * nkb_max * 32 + i] = rec;
+  }
+  if (threadIdx.x == 0) {
+    const HeadCounts hc = head_counts(v, h);
+    bool fast = true;
+    UnitRec u;
+    for (int p = 0; p < 4; ++p) {                          // the whole head, phase by phase (as the kernel's geometry does per chunk)
+      const int lo = p == 0 ? 0 : p == 1 ? hc.n2 : p == 2 ? hc.n2 + hc.n4 : hc.t_v;
+      const int hi = p == 0 ? hc.n2 : p == 1 ? hc.n2 + hc.n4 : p == 2 ? hc.t_v : hc.t_v + hc.n16;
+      const int n = hi - lo;
+      const int64_t krow = p < 3 ? lo : (int64_t)v.max_t_v;
+      const unsigned char* a2 = kd.sub2 ? v.k2 + h * v.k2_head_stride + krow * kd.sub2 : nullptr;
+      const unsigned char* a4 = kd.sub4 ? v.k4 + h * v.k4_head_stride + krow * kd.sub4 : nullptr;
+      const unsigned char* a8 = kd.n8 ? v.k8 + h * v.k8_head_stride + krow * kd.n8 : nullptr;
+      const unsigned char* vlo = p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : reinterpret_cast<const unsigned char*>(v.v16);
+      const int64_t vext = p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes;
+      const int64_t vhs = p == 0 ? v.v2_head_stride : p == 1 ? v.v4_head_stride : p == 2 ? v.v8_head_stride : 2 * v.v16_head_stride;
+      const unsigned char* vb = vlo != nullptr ? vlo + h * vhs : nullptr;
+      const unsigned char* scb = reinterpret_cast<const unsigned char*>(v.v_scale);
+      const unsigned char* zpb = reinterpret_cast<const unsigned char*>(v.v_zp);
+      const unsigned char* gsc = p < 3 && scb != nullptr ? scb + (h * v.v_meta_head_stride + lo) * 2 : nullptr;
+      const unsigned char* gzp = p < 3 && zpb != nullptr ? zpb + (h * v.v_meta_head_stride + lo) * 2 : nullptr;
+      if (n > 0) {
+        if (kd.sub2) fast = fast && blocks_inside(a2, a2 + (int64_t)n * kd.sub2, v.k2, v.k2 + v.k2_bytes);
+        if (kd.sub4) fast = fast && blocks_inside(a4, a4 + (int64_t)n * kd.sub4, v.k4, v.k4 + v.k4_bytes);
+        if (kd.n8) fast = fast && blocks_inside(a8, a8 + (int64_t)n * kd.n8, v.k8, v.k8 + v.k8_bytes);
+        fast = fast && vb != nullptr && blocks_inside(vb, vb + (int64_t)n * phase_row_bytes(p), vlo, vlo + vext);
+        if (p < 3) {
+          fast = fast && gsc != nullptr && gzp != nullptr;
+          fast = fast && blocks_inside(gsc, gsc + n * 2, scb, scb + v.v_meta_bytes);
+          fast = fast && blocks_inside(gzp, gzp + n * 2, zpb, zpb + v.v_meta_bytes);
+        }
+      }
+      u.ph[p].b_lo = lo; u.ph[p].b_hi = hi; u.ph[p].pad0 = 0; u.ph[p].pad1 = 0;
+      u.ph[p].k2 = a2; u.ph[p].k4 = a4; u.ph[p].k8 = a8; u.ph[p].vrow = vb; u.ph[p].sc = gsc; u.ph[p].zp = gzp;
+    }
+    u.n2 = hc.n2; u.n4 = hc.n4; u.n8 = hc.n8; u.n16 = hc.n16;
+    u.flags = fast ? 1 : 0; u.nkb = kd.nkb; u.n_ch2_pad = kd.n2p; u.n_ch4_pad = kd.n4p;
+    u.n_ch8 = kd.n8; u.max_t_v = v.max_t_v; u.pad0 = 0; u.pad1 = 0;
+    recs[unit] = u;
+  }
+}
+
 template <int MODE>
 static int launch_fused(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q, int H_kv,
                         int chunk_rows, int n_chunks, int k_row_bytes_max, float* partials, float* out, int* status,
-                        float* aux, int64_t aux_stride, int t_eff, void* stream) {
+                        float* aux, int64_t aux_stride, int t_eff, void* stream,
+                        const void* unit_recs = nullptr, const void* kslots = nullptr, int nkb_max = 0,
+                        int* unit_ctr = nullptr, float* merged = nullptr,
+                        int row_begin = 0, int row_end = 0x7fffffff, int n_whole = 0) {
   const int g = H_q / H_kv;
   const int n_hgrp = (g + GH - 1) / GH;
-  if (n_views > 65535 || (int64_t)H_kv * n_hgrp > 65535) return RDKV_ERR_TOO_LARGE;
+  const int64_t units = (int64_t)n_views * H_kv * n_hgrp;
+  if (n_whole < 0 || n_whole > units) return RDKV_ERR_BAD_ARG;
+  const int64_t items = n_whole + (units - n_whole) * n_chunks;
+  if (items > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
   const int stage_bytes = align16i(stage_capacity(k_row_bytes_max));
-  size_t smem = (size_t)FSTAGES * stage_bytes + KB_MAX * 32 * sizeof(uint2);
+  size_t smem = (size_t)FSTAGES * stage_bytes + TAIL_BYTES;
   const size_t epilogue = (size_t)FW * GH * D * sizeof(float);
   if (smem < epilogue) smem = epilogue;
   if (smem > 227 * 1024) return RDKV_ERR_TOO_LARGE;
   cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
-  dim3 grid(n_chunks, H_kv * n_hgrp, n_views);
-  decode_fused_kernel<MODE><<<grid, CTA_THREADS, smem, (cudaStream_t)stream>>>(
-      views, q, q_dtype, H_q, g, chunk_rows, n_chunks, stage_bytes, partials, out, status, aux, aux_stride, t_eff);
+  decode_fused_kernel<MODE><<<(unsigned)items, CTA_THREADS, smem, (cudaStream_t)stream>>>(
+      views, q, q_dtype, H_q, g, chunk_rows, n_chunks, n_whole, stage_bytes, partials, out, status, aux, aux_stride, t_eff,
+      reinterpret_cast<const UnitRec*>(unit_recs), reinterpret_cast<const KSlotRec*>(kslots), nkb_max, unit_ctr, merged,
+      row_begin, row_end);
   return launch_status();
 }
 
@@ -1053,6 +1461,47 @@ extern "C" int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_view
   if (rc != RDKV_OK || n_views == 0) return rc;
   return launch_fused<MODE_ATTN>(views, n_views, q, q_dtype, H_q, H_kv, chunk_rows, n_chunks, k_row_bytes_max,
                                  partials, out, status, nullptr, 0, 0, stream);
+}
+
+extern "C" int rdkv_decode_k_blocks(int n_ch2_pad, int n_ch4_pad, int n_ch8) {
+  return k_dims(n_ch2_pad, n_ch4_pad, n_ch8).nkb;
+}
+
+extern "C" int64_t rdkv_decode_prepared_bytes(int64_t n_units, int nkb_max, int which) {
+  if (n_units < 0 || nkb_max < 0) return -1;
+  return which == 0 ? n_units * (int64_t)sizeof(UnitRec) : n_units * nkb_max * 32 * (int64_t)sizeof(KSlotRec);
+}
+
+extern "C" int rdkv_decode_prepare(const rdkv_layer_view* views, int n_views, int H_kv, int nkb_max, void* unit_recs,
+                                   void* k_slots, void* stream) {
+  if (views == nullptr || unit_recs == nullptr || k_slots == nullptr || n_views < 0 || H_kv <= 0) return RDKV_ERR_BAD_ARG;
+  if (nkb_max <= 0 || nkb_max > KB_MAX) return RDKV_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(unit_recs) & 15) || (reinterpret_cast<uintptr_t>(k_slots) & 15)) return RDKV_ERR_BAD_ARG;
+  const int64_t n = (int64_t)n_views * H_kv;
+  if (n == 0) return RDKV_OK;
+  if (n > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
+  decode_prepare_kernel<<<(unsigned)n, 128, 0, (cudaStream_t)stream>>>(
+      views, H_kv, nkb_max, reinterpret_cast<UnitRec*>(unit_recs), reinterpret_cast<KSlotRec*>(k_slots));
+  return launch_status();
+}
+
+extern "C" int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,
+                                int H_kv, int chunk_rows, int n_chunks, int n_whole_units, int row_begin, int row_end,
+                                int k_row_bytes_max, const void* unit_recs, const void* k_slots, int nkb_max,
+                                float* partials, int32_t* unit_counters, float* out, float* out_record,
+                                int32_t* status, void* stream) {
+  if (n_chunks <= 0 || chunk_rows <= 0 || row_begin < 0 || row_end < row_begin) return RDKV_ERR_BAD_ARG;
+  if ((out == nullptr) == (out_record == nullptr)) return RDKV_ERR_BAD_ARG;          // exactly one result form
+  if (n_chunks > 1 && (partials == nullptr || unit_counters == nullptr)) return RDKV_ERR_BAD_ARG;
+  if ((unit_recs == nullptr) != (k_slots == nullptr)) return RDKV_ERR_BAD_ARG;
+  if (unit_recs != nullptr && ((reinterpret_cast<uintptr_t>(unit_recs) & 15) || (reinterpret_cast<uintptr_t>(k_slots) & 15) ||
+                               nkb_max <= 0 || nkb_max > KB_MAX))
+    return RDKV_ERR_BAD_ARG;
+  const int rc = check_fused_args(views, n_views, q, q_dtype, H_q, H_kv, k_row_bytes_max);
+  if (rc != RDKV_OK || n_views == 0) return rc;
+  return launch_fused<MODE_ATTN>(views, n_views, q, q_dtype, H_q, H_kv, chunk_rows, n_chunks, k_row_bytes_max,
+                                 partials, out, status, nullptr, 0, 0, stream, unit_recs, k_slots, nkb_max,
+                                 unit_counters, out_record, row_begin, row_end, n_whole_units);
 }
 
 extern "C" int rdkv_decode_scores(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,

@@ -3,7 +3,7 @@
 Replaces the attention block of the reference decode loop
 (obkv_accel/fast_decode.py:1701-1784: K kernel -> mask add -> softmax -> V kernel)
 with one split-sequence kernel launch over any number of (sequence, layer)
-pairs followed by a log-sum-exp combine.  Softmax semantics are the
+pairs (units cut into chunks are merged by the last of their CTAs to finish).  Softmax semantics are the
 reference's: one softmax per query head over its live Zone-A and Zone-B rows;
 stripe padding is excluded through the per-head row counts read on the device
 (and through ``softmax_mask`` too when ``use_mask`` is set).
@@ -11,26 +11,29 @@ stripe padding is excluded through the per-head row counts read on the device
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Optional, Sequence
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 from torch import Tensor
 
 from ._lib import HEAD_DIM, PARTIAL_STRIDE, LayerView, check, lib, ptr, q_dtype_tag, require_cuda, stream_ptr
-from .packing import PackedKVLayer, layer_view
+from .packing import PackedKVLayer, layer_identity, layer_view
 
 
 class DecodeTable:
     """Device-resident array of ``rdkv_layer_view`` records, one per (sequence, layer).
 
-    The table holds references to every tensor it points into.  Per-head row
-    counts stay in the layers' own int32 device tensors, so a caller may rewrite
-    payloads and counts in place between launches.
+    The table holds references to every tensor it points into.  Payloads, scales, zero
+    points of V are read from the layers' own tensors at every launch, so a caller may
+    rewrite them in place between launches.  The per-head row counts and the K scales,
+    zero points and channel permutation are read from a snapshot the table keeps on the
+    device: call :meth:`refresh` after rewriting those in place (or build the table with
+    ``live_counts=True``, which makes every CTA read the layers' own tensors for them).
     """
 
     def __init__(self, layers: Sequence[PackedKVLayer], new_v_only: Sequence[Optional[Tensor]], H_q: int,
                  *, use_mask: bool = False, device=None, n_chunks: Optional[int] = None,
-                 k_only: bool = False):
+                 k_only: bool = False, live_counts: bool = False):
         if len(layers) == 0:
             raise ValueError("DecodeTable needs at least one layer")
         if len(new_v_only) != len(layers):
@@ -63,62 +66,109 @@ class DecodeTable:
             for t, align in ((pl.V_2bit, 4), (pl.V_4bit, 4), (pl.V_8bit, 4), (nv, 8)):
                 if t is not None and t.numel() and t.data_ptr() % align:
                     raise ValueError(f"packed V tensors must be {align}-byte aligned")
-        # uniform chunks of the partial-record calls: only when there are fewer units than CTA slots
-        # (a chunk pays the per-CTA prologue and merge again; see unit_plan)
         n_hgrp = (self.H_q // self.H_kv + 7) // 8
-        units = self.n_views * self.H_kv * n_hgrp
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        want = max(1, min(4, (self.CTAS_PER_SM * sms) // units))
-        n_chunks = max(1, min(want if n_chunks is None else int(n_chunks), -(-max(max_t_k, 1) // 128)))
-        self.chunk_rows = max(64, ((-(-max(max_t_k, 1) // n_chunks) + 63) // 64) * 64)
-        self.n_chunks = max(1, -(-max(max_t_k, 1) // self.chunk_rows))
+        self.unit_rows = ((max(max_t_k, 1) + 63) // 64) * 64
+        self._sms = sms
+        self._n_hgrp = n_hgrp
+        # chunks per unit: None = chosen per launch by plan(); an int forces uniform chunks
+        self.n_chunks: Optional[int] = None if n_chunks is None else max(1, int(n_chunks))
+        self.chunk_rows: Optional[int] = None
         raw = bytes(views)
         host = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
         self.views = host.to(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._partials: Optional[Tensor] = None
-        self.unit_rows = ((max(max_t_k, 1) + 63) // 64) * 64
-        self._sms = sms
-        self._n_hgrp = n_hgrp
+        # snapshot of every head's row counts (one round trip less in the kernel's prologue) and the
+        # arrival counters of chunked units (zero between launches)
+        L = lib()
+        self.nkb_max = max(L.rdkv_decode_k_blocks(int(vw.n_ch2_pad), int(vw.n_ch4_pad), int(vw.n_ch8)) for vw in views)
+        n_units = self.n_views * self.H_kv
+        self._unit_rec_bytes = int(L.rdkv_decode_prepared_bytes(1, self.nkb_max, 0))
+        self.unit_recs = torch.empty(L.rdkv_decode_prepared_bytes(n_units, self.nkb_max, 0), dtype=torch.uint8, device=self.device)
+        self.k_slots = torch.empty(L.rdkv_decode_prepared_bytes(n_units, self.nkb_max, 1), dtype=torch.uint8, device=self.device)
+        self.unit_ctr = torch.zeros(self.n_views * self.H_kv * n_hgrp, dtype=torch.int32, device=self.device)
+        self._ws = {}
+        # live_counts: the kernel reads the layers' count / scale / permutation tensors itself at every
+        # launch (no snapshot to refresh; one more round trip per CTA)
+        self.live_counts = bool(live_counts)
+        self.refresh()
 
     CTAS_PER_SM = 3                      # resident CTAs of the fused kernel per SM
+    # cost model of a launch (SM cycles, measured on B200): a CTA spends ROW_COST per live row it
+    # attends over plus a fixed cost (prologue, first tile, merge of its warps, result): FIXED_WHOLE
+    # when it has a whole unit, FIXED_CHUNK when it has a chunk (record + arrival counter on top)
+    ROW_COST = 17.6
+    FIXED_WHOLE = 13000.0
+    FIXED_CHUNK = 17000.0
+
+    def refresh(self) -> None:
+        """Rebuild the table's snapshot of the per-head quantities (one small launch on the current
+        stream, capturable): V row counts, K scales, zero points and channel permutation.  Call it
+        after rewriting a layer's ``seg_bounds_per_head`` / ``n_v16_per_head`` / ``K_ch_scale`` /
+        ``K_ch_zp`` / ``K_ch_perm_padded_idx_for_Q`` in place; packed payloads and V scales / zero
+        points are always read from the layers' own tensors."""
+        if self.live_counts or self.nkb_max > 24:
+            self.live_counts = True
+            return
+        with torch.cuda.device(self.device):
+            check(lib().rdkv_decode_prepare(self.views.data_ptr(), self.n_views, self.H_kv, self.nkb_max,
+                                            self.unit_recs.data_ptr(), self.k_slots.data_ptr(),
+                                            stream_ptr(self.device)), "rdkv_decode_prepare")
+
+    def plan(self, n_views: int, rows: Optional[int] = None):
+        """(k, chunk_rows, n_whole) for a launch over ``n_views`` views whose heads have up to ``rows``
+        live rows to attend over (default: whole heads): the first ``n_whole`` units (view, KV head,
+        group of query heads) get one CTA each, every other unit is cut into ``k`` chunks of
+        ``chunk_rows`` rows, merged by the last of its CTAs to finish.
+
+        A CTA per whole unit is the most efficient shape (a chunk pays the fixed cost again), but
+        units that do not fill the last round of CTA slots leave SMs idle.  Three shapes are
+        costed with the measured constants and the cheapest is taken: all units whole; all units
+        in k chunks (few units); full rounds of whole units followed by the leftover units cut
+        finely enough to fill one more round."""
+        rows = self.unit_rows if rows is None else max(64, ((rows + 63) // 64) * 64)
+        units = max(1, n_views * self.H_kv * self._n_hgrp)
+        if self.n_chunks is not None:
+            k = max(1, min(self.n_chunks, -(-rows // 64)))
+            cr = self.chunk_rows if (self.chunk_rows and self.chunk_rows * k >= rows) else self._chunk_rows_for(k, rows)
+            return k, cr, (units if k == 1 else 0)
+        slots = self._sms * self.CTAS_PER_SM
+        k_max = max(1, min(16, rows // 128))
+        whole = rows * self.ROW_COST + self.FIXED_WHOLE
+
+        def chunk_cost(k):
+            return self._chunk_rows_for(k, rows) * self.ROW_COST + self.FIXED_CHUNK
+
+        best = (-(-units // slots) * whole, 1, units)                       # all whole
+        full, left = divmod(units, slots)
+        if left and k_max > 1:
+            for k in range(2, k_max + 1):                                   # full rounds whole + leftover in k chunks
+                cost = full * whole + -(-left * k // slots) * chunk_cost(k)
+                if cost < best[0] * 0.98:
+                    best = (cost, k, full * slots)
+        _, k, n_whole = best
+        return k, self._chunk_rows_for(k, rows), n_whole
 
     def unit_plan(self, n_views: int):
-        """(v_main, k, rows): of a launch over ``n_views`` views the first ``v_main`` views run one CTA
-        per unit, the units of the remaining views are cut into ``k`` uniform chunks of ``rows`` rows.
-        Measured on B200: a CTA per whole unit is the most efficient shape (a chunk pays the per-CTA
-        prologue and merge again), so units are cut — all of them, uniformly — only when there are
-        fewer units than CTA slots.  Tried and dropped: cutting just the units of a mostly empty last
-        wave (on a stream of lower priority), and equal segments of one flat row axis over all units
-        with a loop over items in the CTA — both slower than the idle tail they remove."""
-        slots = self._sms * self.CTAS_PER_SM
-        hy = self.H_kv * self._n_hgrp
-        units = n_views * hy
-        k_max = max(1, min(4, self.unit_rows // 256))
-        if units <= slots:
-            k = max(1, min(k_max, slots // max(units, 1)))
-            return (n_views, 1, self.unit_rows) if k == 1 else (0, k, self._chunk_rows_for(k))
-        return n_views, 1, self.unit_rows
+        """(v_main, k, rows) form of :meth:`plan`: ``v_main`` = views whose units all stay whole."""
+        k, rows, n_whole = self.plan(n_views)
+        return n_whole // (self.H_kv * self._n_hgrp), k, rows
 
-    def _chunk_rows_for(self, k: int) -> int:
-        return max(64, ((-(-self.unit_rows // k) + 63) // 64) * 64)
+    def _chunk_rows_for(self, k: int, rows: Optional[int] = None) -> int:
+        rows = self.unit_rows if rows is None else rows
+        return max(64, ((-(-rows // k) + 63) // 64) * 64)
 
     def chunk_workspace(self, k: int) -> Tensor:
         """Records of chunked units: [n_views*H_q, k, 132] fp32 (grown on demand)."""
-        cache = self.__dict__.setdefault("_chunk_ws", {})
-        if k not in cache:
-            cache[k] = torch.empty((self.n_views * self.H_q, k, PARTIAL_STRIDE), dtype=torch.float32, device=self.device)
-        return cache[k]
+        if k not in self._ws:
+            self._ws[k] = torch.empty((self.n_views * self.H_q, k, PARTIAL_STRIDE), dtype=torch.float32, device=self.device)
+        return self._ws[k]
 
     def workspace(self) -> Optional[Tensor]:
-        """Split-sequence partial records [n_views*H_q, n_chunks, 132] fp32 (allocated once);
-        None when one chunk covers every head (results are written directly)."""
-        if self.n_chunks == 1:
-            return None
-        if self._partials is None:
-            self._partials = torch.empty((self.n_views * self.H_q, self.n_chunks, PARTIAL_STRIDE),
-                                         dtype=torch.float32, device=self.device)
-        return self._partials
+        """Split-sequence partial records [n_views*H_q, n_chunks, 132] fp32 of the table's launch
+        shape (allocated once); None when one chunk covers every head."""
+        k = self.plan(self.n_views)[0]
+        return None if k == 1 else self.chunk_workspace(k)
 
     def check_status(self) -> None:
         """Host read (synchronises) of the kernel's status word; raises if a launch reported a problem."""
@@ -167,8 +217,8 @@ def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out
     def off(t: Optional[Tensor], per_row: int) -> Optional[int]:
         return None if t is None else t.data_ptr() + rows * per_row * t.element_size()
 
-    n_chunks = table.n_chunks if n_chunks is None else n_chunks
-    chunk_rows = table.chunk_rows if chunk_rows is None else chunk_rows
+    if n_chunks is None or chunk_rows is None:
+        n_chunks, chunk_rows = table.plan(v1 - v0)[:2]
     check(lib().rdkv_decode_attn_partial(table.views.data_ptr() + v0 * C.sizeof(LayerView), v1 - v0,
                                          off(q, HEAD_DIM), q_dtype_tag(q), table.H_q,
                                          table.H_kv, chunk_rows, n_chunks, table.k_row_bytes_max,
@@ -177,50 +227,63 @@ def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out
           "rdkv_decode_attn_partial")
 
 
-def _launch_units(q: Tensor, table: DecodeTable, out: Tensor, v0: int = 0, v1: Optional[int] = None,
-                  phases: int = 3) -> None:
-    """One CTA per unit on views [v0, v1), or uniform chunks of every unit when there are fewer
-    units than CTA slots (DecodeTable.unit_plan); chunk records are merged by the combine kernel.
-    phases: 1 = fused launches, 2 = merge, 3 = both."""
+def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int = 0, v1: Optional[int] = None,
+                  *, out_record: Optional[Tensor] = None, rows: Optional[Tuple[int, int]] = None,
+                  plan: Optional[Tuple[int, int, int]] = None) -> None:
+    """ONE launch of the fused kernel on views [v0, v1): whole units, or uniform chunks merged inside
+    the kernel (DecodeTable.plan).  The result is the normalised ``out`` [n_views,H_q,128] or the
+    un-normalised record per query head ``out_record`` [n_views*H_q,132]; ``rows`` = (begin, end)
+    restricts every head to that window of its live rows.  q, out, out_record are the full-table
+    tensors, the view range is cut by pointer offsets; ``out`` may be pinned host memory."""
+    require_cuda(q, "q")
+    if q.shape[-1] != HEAD_DIM or q.numel() != table.n_views * table.H_q * HEAD_DIM:
+        raise ValueError(f"q must be [{table.n_views},{table.H_q},{HEAD_DIM}], got {tuple(q.shape)}")
+    if not q.is_contiguous():
+        q = q.contiguous()
     v1 = table.n_views if v1 is None else v1
-    v_main, k, rows_k = table.unit_plan(v1 - v0)
-    if phases & 1 and v_main > 0:
-        _launch_fused(q, table, None, out, v0, v0 + v_main, 1, table.unit_rows)
-    if v_main < v1 - v0:
-        a = v0 + v_main
-        if k == 1:
-            if phases & 1:
-                _launch_fused(q, table, None, out, a, v1, 1, table.unit_rows)
-            return
-        ws = table.chunk_workspace(k)
-        if phases & 1:
-            _launch_fused(q, table, ws, None, a, v1, k, rows_k)
-        if phases & 2:
-            rows = slice(a * table.H_q, v1 * table.H_q)
-            check(lib().rdkv_lse_combine(ws[rows].data_ptr(), (v1 - a) * table.H_q, k, ws.stride(0), ws.stride(1),
-                                         out.data_ptr() + a * table.H_q * HEAD_DIM * 4, None, None,
-                                         stream_ptr(q.device)), "rdkv_lse_combine")
+    if not 0 <= v0 <= v1 <= table.n_views:
+        raise ValueError(f"view range [{v0},{v1}) outside the table of {table.n_views} views")
+    if (out is None) == (out_record is None):
+        raise ValueError("exactly one of out and out_record")
+    r0, r1 = (0, 0x7fffffff) if rows is None else (int(rows[0]), int(rows[1]))
+    if not 0 <= r0 <= r1:
+        raise ValueError(f"bad row window [{r0},{r1})")
+    k, rows_k, n_whole = plan if plan is not None else table.plan(v1 - v0, None if rows is None else min(r1, table.unit_rows) - r0)
+    hy = table.H_kv * table._n_hgrp
+    if plan is not None:                                   # a plan of the whole table: its whole units are the table's first
+        n_whole -= v0 * hy
+    n_whole = min(max(n_whole, 0), (v1 - v0) * hy)
+    qrow = v0 * table.H_q                                  # first query-head row of the range
 
+    def off(t: Optional[Tensor], per_row: int) -> Optional[int]:
+        return None if t is None else t.data_ptr() + qrow * per_row * t.element_size()
 
-
-def decode_attention_phases(q: Tensor, table: DecodeTable, out: Tensor, *, phases: int = 3) -> Tensor:
-    """The two phases of :func:`packed_decode_attention` separately (for measurements):
-    ``phases=1`` runs the fused kernel alone, ``phases=2`` the merge of the records of split
-    units / chunks (if the table's launch shape has any), 3 both."""
-    _launch_units(q, table, out, phases=phases)
-    return out
+    ws = table.chunk_workspace(k) if k > 1 else None
+    with torch.cuda.device(table.device):
+        check(lib().rdkv_decode_attn(table.views.data_ptr() + v0 * C.sizeof(LayerView), v1 - v0,
+                                     off(q, HEAD_DIM), q_dtype_tag(q), table.H_q, table.H_kv, rows_k, k, n_whole, r0, r1,
+                                     table.k_row_bytes_max,
+                                     None if table.live_counts else table.unit_recs.data_ptr() + v0 * table.H_kv * table._unit_rec_bytes,
+                                     None if table.live_counts else table.k_slots.data_ptr() + v0 * table.H_kv * table.nkb_max * 512,
+                                     0 if table.live_counts else table.nkb_max,
+                                     off(ws, k * PARTIAL_STRIDE), table.unit_ctr.data_ptr() + v0 * hy * 4,
+                                     off(out, HEAD_DIM), off(out_record, PARTIAL_STRIDE),
+                                     ptr(table.status), stream_ptr(q.device)),
+              "rdkv_decode_attn")
 
 
 def decode_attention_partial(q: Tensor, table: DecodeTable, out: Optional[Tensor] = None) -> Tensor:
-    """The fused kernel alone in uniform-chunk mode: returns the per-chunk records, or ``out``
-    itself when a single chunk covers every head (the kernel then writes normalised results)."""
-    if table.n_chunks == 1:
+    """The fused kernel alone, writing per-chunk records and leaving them unmerged (the input of
+    :func:`lse_combine`): returns ``[n_views*H_q, k, 132]``, or ``out`` itself when a single chunk
+    covers every head (the kernel then writes normalised results)."""
+    k, rows_k = table.plan(table.n_views)[:2]
+    if k == 1:
         if out is None:
             out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
-        _launch_fused(q, table, None, out)
+        _launch_fused(q, table, None, out, n_chunks=1, chunk_rows=rows_k)
         return out
-    part = table.workspace()
-    _launch_fused(q, table, part, None)
+    part = table.chunk_workspace(k)
+    _launch_fused(q, table, part, None, n_chunks=k, chunk_rows=rows_k)
     return part
 
 
@@ -267,18 +330,21 @@ def tail_attention_partial(q: Tensor, new_k: Tensor, new_v: Tensor, n_new, H_kv:
 
 def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tensor] = None,
                             out_partial: Optional[Tensor] = None, new_k: Optional[Tensor] = None,
-                            new_v: Optional[Tensor] = None, n_new=0) -> Tensor:
+                            new_v: Optional[Tensor] = None, n_new=0,
+                            rows: Optional[Tuple[int, int]] = None) -> Tensor:
     """softmax(q·K̂ᵀ/√128)·V̂ over every view of ``table``.
 
     q [n_views,H_q,128] fp16/bf16/fp32 -> out [n_views,H_q,128] fp32.  With
     ``out_partial`` ([n_views*H_q,132] fp32) the merged un-normalised (m, l, o)
     record per query head is written instead, for a later combine across
-    sequence shards.  ``new_k`` / ``new_v`` [n_views,H_kv,cap,128] with ``n_new`` live
-    rows add the uncompressed tail of decode-appended tokens (Zone C) to the same
-    softmax, as the reference's attention block does (fast_decode.py:1719-1784).
-    One launch when a single chunk covers every head and there is no tail, else the
-    fused kernel plus the combine; no allocation after the first call, no host
-    synchronisation.
+    sequence shards; ``rows`` = (begin, end) restricts every head to that window of
+    its live rows (the share of one sequence-split rank).  ``new_k`` / ``new_v``
+    [n_views,H_kv,cap,128] with ``n_new`` live rows add the uncompressed tail of
+    decode-appended tokens (Zone C) to the same softmax, as the reference's attention
+    block does (fast_decode.py:1719-1784).
+    One launch without a tail (chunked units are merged inside the kernel), else the
+    fused kernel, the tail kernel and the combine; no allocation after the first
+    call, no host synchronisation.
     """
     if new_k is not None:
         if new_v is None:
@@ -288,7 +354,7 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
         if ws is None:
             ws = torch.empty((2, n_rows, PARTIAL_STRIDE), dtype=torch.float32, device=table.device)
             table._tail_ws = ws
-        packed_decode_attention(q, table, out_partial=ws[0])          # packed zones: merged record
+        _launch_units(q, table, None, out_record=ws[0], rows=rows)      # packed zones: merged record
         tail_attention_partial(q.reshape(table.n_views, table.H_q, HEAD_DIM), new_k, new_v, n_new, table.H_kv, ws[1])
         both = ws.permute(1, 0, 2)                                       # [n_rows, 2, 132]
         if out_partial is not None:
@@ -299,18 +365,17 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
         lse_combine(both, out.view(-1, HEAD_DIM))
         return out
     if out_partial is not None:
-        if table.n_chunks == 1:
-            _launch_fused(q, table, out_partial, None)
-        else:
-            part = table.workspace()
-            _launch_fused(q, table, part, None)
-            lse_combine(part, None, out_partial=out_partial)
+        if (out_partial.dtype != torch.float32 or not out_partial.is_contiguous()
+                or out_partial.numel() != table.n_views * table.H_q * PARTIAL_STRIDE):
+            raise ValueError(f"out_partial must be contiguous float32 [{table.n_views * table.H_q},{PARTIAL_STRIDE}]")
+        _launch_units(q, table, None, out_record=out_partial, rows=rows)
         return out_partial
     if out is None:
         out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
-    if not out.is_contiguous() or out.dtype != torch.float32:
-        raise ValueError("out must be contiguous float32 [n_views,H_q,128]")
-    _launch_units(q, table, out)
+    if (not out.is_contiguous() or out.dtype != torch.float32
+            or out.numel() != table.n_views * table.H_q * HEAD_DIM):
+        raise ValueError(f"out must be contiguous float32 [{table.n_views},{table.H_q},{HEAD_DIM}]")
+    _launch_units(q, table, out, rows=rows)
     return out
 
 
@@ -373,11 +438,12 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
         io.out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=table.device)
     out = out_host if direct else io.out
     cur = torch.cuda.current_stream(table.device)
+    plan = table.plan(table.n_views)                       # the device call's launch shape: same results bit for bit
     for (a, b), st in zip(io.ranges, io.streams):
         st.wait_stream(cur)
         with torch.cuda.stream(st):
             io.q[a:b].copy_(q_host[a:b], non_blocking=True)
-            _launch_units(io.q, table, out, a, b)
+            _launch_units(io.q, table, out, a, b, plan=plan)
             if not direct:
                 out_host[a:b].copy_(io.out[a:b], non_blocking=True)
     for st in io.streams[:len(io.ranges)]:
@@ -394,9 +460,11 @@ def packed_layer_attention(q: Tensor, packed_layer: PackedKVLayer, new_v_only: O
     loop caches its pre-squeezed views on the cache object
     (obkv_accel/fast_decode.py:813-816).
     """
-    key = (q.shape[0], None if new_v_only is None else new_v_only.data_ptr(), use_mask)
+    key = (q.shape[0], use_mask, layer_identity(packed_layer),
+           None if new_v_only is None else (new_v_only.data_ptr(), tuple(new_v_only.shape), tuple(new_v_only.stride())))
     cached = getattr(packed_layer, "_rdkv_table", None)
     if cached is None or cached[0] != key:
-        cached = (key, DecodeTable([packed_layer], [new_v_only], q.shape[0], use_mask=use_mask))
+        # (live_counts: a caller may rewrite the per-head counts in place between calls)
+        cached = (key, DecodeTable([packed_layer], [new_v_only], q.shape[0], use_mask=use_mask, live_counts=True))
         packed_layer._rdkv_table = cached
     return packed_decode_attention(q.reshape(1, q.shape[0], HEAD_DIM), cached[1])[0]

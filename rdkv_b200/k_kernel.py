@@ -14,7 +14,7 @@ import math
 import torch
 
 from ._lib import check, lib, ptr, q_dtype_tag, require_cuda, stream_ptr
-from .packing import _pad_to, layer_view
+from .packing import _pad_to, layer_identity, layer_view
 
 D = 128
 SQRT_D = math.sqrt(float(D))
@@ -67,8 +67,9 @@ def _scores_table(packed_layer, H_q: int):
     """One-view table of the layer for the fused kernel's score mode, cached on the layer; None
     when the layer's shape is outside what that kernel takes (the scalar kernel then runs)."""
     from .decode import DecodeTable
+    key = (H_q, layer_identity(packed_layer))
     cached = getattr(packed_layer, "_rdkv_k_table", None)
-    if cached is not None and cached[0] == H_q:
+    if cached is not None and cached[0] == key:
         return cached[1]
     table = None
     try:
@@ -79,7 +80,7 @@ def _scores_table(packed_layer, H_q: int):
     except (ValueError, AttributeError):
         table = None
     try:
-        packed_layer._rdkv_k_table = (H_q, table)
+        packed_layer._rdkv_k_table = (key, table)
     except AttributeError:
         pass
     return table

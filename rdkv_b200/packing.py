@@ -749,6 +749,22 @@ def _squeeze_h(t: Optional[Tensor]) -> Optional[Tensor]:
     return t
 
 
+def layer_identity(pl) -> tuple:
+    """Identity of everything a cached ``rdkv_layer_view`` of this layer captures: address and
+    shape of every tensor field it points into and the host scalars it copies.  A cache of views
+    keyed by this notices a field that was re-assigned (a deferred K filled in later, a re-pack, a
+    grown ``T_eff``); values rewritten in place keep the key, and are read by the kernels anyway."""
+    def ident(t):
+        return None if t is None else (t.data_ptr(), tuple(t.shape), tuple(t.stride()))
+    tensors = tuple(ident(getattr(pl, f, None)) for f in (
+        "K_2bit", "K_4bit", "K_8bit", "K_ch_scale", "K_ch_zp", "K_ch_perm_padded_idx_for_Q",
+        "K_ch_perm_padded_idx_per_head", "K_ch_perm_padded_idx", "V_2bit", "V_4bit", "V_8bit", "V_scale", "V_zp",
+        "seg_bounds_per_head", "n_v16_per_head", "softmax_mask"))
+    scalars = (tuple(int(x) for x in pl.K_ch_seg_bounds), tuple(int(x) for x in pl.seg_bounds),
+               int(pl.T_eff), int(pl.T_eff_k), int(pl.n_v16))
+    return tensors + scalars
+
+
 def layer_view(pl: PackedKVLayer, V16: Optional[Tensor] = None, n_v16_per_head: Optional[Tensor] = None,
                max_T_v: Optional[int] = None, *, use_mask: bool = False, t_k: Optional[int] = None
                ) -> Tuple[LayerView, list]:

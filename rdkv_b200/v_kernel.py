@@ -13,7 +13,7 @@ import ctypes as C
 import torch
 
 from ._lib import check, lib, ptr, require_cuda, stream_ptr
-from .packing import layer_view
+from .packing import layer_identity, layer_view
 
 D = 128
 
@@ -64,7 +64,8 @@ def _weights_table(packed_layer, V16, n_v16_per_head, max_T_v, H_q: int):
         return None                                        # caller-supplied counts: scalar kernel
     if V16 is not None and int(max_T_v) != int(packed_layer.T_eff):
         return None
-    key = (H_q, None if V16 is None else (V16.data_ptr(), tuple(V16.shape)))
+    key = (H_q, None if V16 is None else (V16.data_ptr(), tuple(V16.shape), tuple(V16.stride())),
+           layer_identity(packed_layer))
     cached = getattr(packed_layer, "_rdkv_v_table", None)
     if cached is not None and cached[0] == key:
         return cached[1]

@@ -159,8 +159,9 @@ def test_uncompressed_tail_joins_the_softmax(kv_dtype):
 
 
 def test_whole_units_and_uniform_chunks():
-    """More units than CTA slots: one CTA per unit; fewer: every unit in uniform chunks merged by
-    the combine kernel.  Both launch shapes against each other and the oracle."""
+    """One CTA per unit against uniform chunks of every unit merged inside the kernel by the last
+    CTA of the unit to finish (two and three chunks, more CTAs than one wave), and what the launch
+    plan picks by itself for many and for few units.  All shapes against each other and the oracle."""
     from oracle import ref_attention as RA
     from oracle import ref_packing as RP
     from rdkv_b200 import synth
@@ -182,15 +183,21 @@ def test_whole_units_and_uniform_chunks():
     q = synth.make_q(H_kv * g, seed=5, batch=n_views, dtype=torch.float16)
     want_last = RA.decode_attention(q[n_views - 1].float().numpy(), *last)[0]
     outs = []
-    for lo in (0, n_views - 20):                           # all views (whole units) / 20 views (chunks)
-        table = DecodeTable(layers[lo:], nvs[lo:], H_kv * g)
-        v_main, k, rows = table.unit_plan(n_views - lo)
-        assert (v_main == n_views and k == 1) if lo == 0 else (v_main == 0 and k > 1)
-        out = packed_decode_attention(q[lo:].cuda(), table)
-        assert_attn_close(to_np(out[-1]), want_last, "last view")
+    for lo, forced in ((0, 1), (0, 2), (0, 3), (0, None), (n_views - 20, None)):
+        table = DecodeTable(layers[lo:], nvs[lo:], H_kv * g, n_chunks=forced)
+        k, rows, n_whole = table.plan(n_views - lo)
+        assert k == forced if forced else (k > 1 if lo else k >= 1)
+        assert k * rows >= table.unit_rows and 0 <= n_whole <= (n_views - lo) * H_kv
+        if forced is None and lo == 0:                     # a few units more than one round of CTAs: only those are cut
+            assert k > 1 and n_whole == 3 * sms
+        for rep in range(2):                               # twice: the arrival counters must be back at zero
+            out = packed_decode_attention(q[lo:].cuda(), table)
+            assert_attn_close(to_np(out[-1]), want_last, f"last view, {k} chunks, call {rep}")
+        assert int(table.unit_ctr.abs().sum().item()) == 0
         outs.append(out[-20:])
         table.check_status()
-    assert_attn_close(to_np(outs[0]), to_np(outs[1]), "whole units vs chunks")
+    for o in outs[1:]:
+        assert_attn_close(to_np(outs[0]), to_np(o), "whole units vs chunks")
 
 
 def test_host_buffer_call_equals_device_call():
