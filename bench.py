@@ -28,17 +28,24 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
-CFG3 = dict(layers=32, batch=16, kv_heads=8, q_heads=32, context=32768, budget=2048, config_id=3)
+CFG3 = dict(name="config 3", layers=32, batch=16, kv_heads=8, q_heads=32, context=32768, budget=2048, config_id=3,
+            workload="config 3: full-depth decode, Llama-3.1-8B attention shape — 32 layers x batch 16 x 8 KV heads "
+                     "(32 q heads, head_dim 128), context 32768, 2048 kept tokens/head (1/8 fp16, 1/4 8b, 3/8 4b, 1/4 2b), "
+                     "64 K channels kept (16@8b,24@4b,24@2b), bf16 q per step")
+CFG4 = dict(name="config 4", layers=80, batch=4, kv_heads=8, q_heads=64, context=131072, budget=8192, config_id=4,
+            workload="config 4: long-context decode, Qwen2.5-72B attention shape — 80 layers x batch 4 x 8 KV heads "
+                     "(64 q heads, head_dim 128), context 131072, 8192 kept tokens/head (config-0 bit mix), "
+                     "64 K channels kept, bf16 q per step")
 L2_BYTES = 126 * 1024 * 1024
 METRIC = "packed-KV decode-attn tokens/s"
 
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one fused-kernel launch in
-# the committed ncu capture (profiles/; an 8-layer launch: 286.4 MB moved for 280.2 MB algorithmic);
-# traffic grows with the units processed, so the ratio carries over to the full launch.
+# the committed ncu capture (profiles/; an 8-layer launch); traffic grows with the units processed,
+# so the ratio carries over to the full launch.
 NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = 1.022
-# the same ratio for the four packing launches of config 1 (profiles/: 934.7 MB moved for 945.4 MB
-# algorithmic; the launch list is a one-pass capture of the full workload)
-PACK_NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = 0.989
+# dram__bytes_read.sum + dram__bytes_write.sum of the packing launches of one config-1 step in the
+# committed ncu launch list (profiles/; a one-pass capture of the full workload)
+PACK_NCU_TRAFFIC_BYTES = 943.4e6
 
 
 def load_peaks():
@@ -47,6 +54,12 @@ def load_peaks():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def config_dict(cfg, small):
+    """The workload description both arms (CUDA and CPU reference) print, key for key."""
+    return {"workload": cfg["workload"], "batch": cfg["batch"], "layers": cfg["layers"], "kv_heads": cfg["kv_heads"],
+            "q_heads": cfg["q_heads"], "token_budget": cfg["budget"], "context": cfg["context"], "small": bool(small)}
 
 
 # ── clocks: sampled through NVML (read-only) while the timed regions run ─────
@@ -109,16 +122,21 @@ class ClockSampler:
 
 
 # ── workload construction ────────────────────────────────────────────────────
-def unit_bytes(pl, nv) -> int:
-    """Algorithmic bytes of one packed (sequence, layer): live packed K and V rows, scale/zp, fp16 rows."""
+def unit_bytes(pl, nv, seq_part=None) -> int:
+    """Algorithmic bytes of one packed (sequence, layer): packed K and V rows of every head's live
+    rows (those of `seq_part` = (i, n), part i of n of each of the head's phases; default all), their
+    V scale / zero point, fp16 rows, and the K scale / zero point of the head."""
+    from rdkv_b200.sharding import part_rows
     sb = pl.seg_bounds_per_head.cpu().tolist()
     n16 = pl.n_v16_per_head.cpu().tolist()
     k_row = sum(t.shape[-1] for t in (pl.K_2bit, pl.K_4bit, pl.K_8bit) if t is not None)
+    part, parts = (0, 1) if seq_part is None else seq_part
+    per_row = [32 + 4, 64 + 4, 128 + 4, 256]
     total = 0
     for (n2, n4, n8), n in zip(sb, n16):
-        rows = n2 + n4 + n8 + n
-        total += rows * k_row + 2 * 2 * pl.K_ch_scale.shape[-1]
-        total += n2 * 32 + n4 * 64 + n8 * 128 + (n2 + n4 + n8) * 4 + n * 256
+        for p, (lo, hi) in enumerate(part_rows((n2, n4, n8, n), part, parts)):
+            total += (hi - lo) * (k_row + per_row[p])
+        total += 2 * 2 * pl.K_ch_scale.shape[-1]
     return total
 
 
@@ -129,7 +147,7 @@ def build_decode_cache(cfg, h0, h1, replica, device):
     from rdkv_b200 import synth
     from rdkv_b200.packing import pack_kv
     g = cfg["q_heads"] // cfg["kv_heads"]
-    layers, nvs, nbytes = [], [], 0
+    layers, nvs = [], []
     for layer in range(cfg["layers"]):
         for seq in range(cfg["batch"]):
             seed = synth.unit_seed(cfg["config_id"], layer, seq) + 100003 * replica
@@ -139,9 +157,8 @@ def build_decode_cache(cfg, h0, h1, replica, device):
             pl, nv = pack_kv(K[:, h0:h1], V[:, h0:h1], vb[h0:h1], kb[h0:h1], g, build_mask=False)
             layers.append(pl)
             nvs.append(nv)
-            nbytes += unit_bytes(pl, nv)
             del K, V
-    return layers, nvs, nbytes
+    return layers, nvs
 
 
 def timed_steps(fn, steps, barrier):
@@ -168,129 +185,261 @@ def max_over_ranks(x: float, world: int, device) -> float:
     return float(t.item())
 
 
-def run_decode(args, rank, world, device):
-    from rdkv_b200._lib import lib
+def repeated_regions(fn, steps, barrier, world, device, *, min_reps=10, target_ms=60.0, max_reps=60):
+    """The `steps`-step region timed several times (each bracketed by barrier + synchronize, max over
+    ranks): at least `min_reps` times and until the timed GPU work adds up to `target_ms`.
+    Returns (median ms of a region, dict with reps / min / max / total)."""
+    first = max_over_ranks(timed_steps(fn, steps, barrier), world, device)
+    reps = int(min(max_reps, max(min_reps, -(-target_ms // max(first, 1e-3)))))
+    times = [first] + [max_over_ranks(timed_steps(fn, steps, barrier), world, device) for _ in range(reps - 1)]
+    return statistics.median(times), {"reps": len(times), "ms_min": min(times), "ms_max": max(times),
+                                      "timed_region_s": sum(times) / 1e3}
+
+
+def measure_decode(cfg, rank, world, device, *, steps, warmup, seq_parts=1, chunks=None, want_e2e=False,
+                   e2e_slices=None, small=False):
+    """One decode workload on this rank's share: KV heads sharded over world/seq_parts head groups,
+    the live rows of every head split over seq_parts ranks (row windows of the same packed layer,
+    records merged after one all-gather per step).  Returns a dict of timings and byte counts
+    (identical on every rank after the max over ranks), plus the tables for the CPU baseline."""
+    from rdkv_b200 import sharding
     from rdkv_b200.decode import DecodeTable, packed_decode_attention, packed_decode_attention_host
+    H_kv = cfg["kv_heads"]
+    head_rank, head_world, part = sharding.grid(rank, world, seq_parts)
+    assert H_kv % head_world == 0, "KV heads are sharded across head groups: their number must divide 8"
+    h0, h1 = sharding.head_shard(head_rank, head_world, H_kv)
+    g = cfg["q_heads"] // H_kv
+    Hq_loc = (h1 - h0) * g
+    n_views = cfg["layers"] * cfg["batch"]
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    group = None
+    if seq_parts > 1:                                        # one process group per set of ranks that share heads
+        for hr in range(head_world):
+            gr = dist.new_group(list(range(hr * seq_parts, (hr + 1) * seq_parts)))
+            if hr == head_rank:
+                group = gr
+
+    # enough distinct cache replicas that consecutive steps cannot be served from L2
+    tables, step_bytes, seq_part = [], None, None
+    while True:
+        layers, nvs = build_decode_cache(cfg, h0, h1, len(tables), device)
+        tb = DecodeTable(layers, nvs, Hq_loc, n_chunks=chunks)
+        seq_part = (part, seq_parts) if seq_parts > 1 else None
+        step_bytes = sum(unit_bytes(pl, nv, seq_part) for pl, nv in zip(layers, nvs))
+        tables.append(tb)
+        if len(tables) * step_bytes >= 2.2 * L2_BYTES or small:
+            break
+    R = len(tables)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4242 + head_rank)                        # ranks that share heads draw the same queries
+    n_q = min(steps + warmup, 16 if cfg["q_heads"] > 32 else 64)
+    q_pool = [(torch.randn(n_views, Hq_loc, 128, generator=gen, device=device) / 128 ** 0.5).to(torch.bfloat16)
+              for _ in range(n_q)]
+    out = torch.empty((n_views, Hq_loc, 128), dtype=torch.float32, device=device)
+    n_rows = n_views * Hq_loc
+    if seq_parts > 1:
+        rec = torch.empty((n_rows, 132), dtype=torch.float32, device=device)
+        gathered = torch.empty((seq_parts * n_rows, 132), dtype=torch.float32, device=device)
+
+    def step(i):
+        if seq_parts == 1:
+            packed_decode_attention(q_pool[i % n_q], tables[i % R], out=out)
+        else:
+            sharding.sequence_split_attention(q_pool[i % n_q], tables[i % R], group, part=part, n_parts=seq_parts,
+                                              record=rec, gathered=gathered)
+
+    for i in range(warmup):
+        step(i)
+    sampler = ClockSampler(device.index if device.index is not None else 0)
+    with sampler:
+        ms, timing = repeated_regions(step, steps, barrier, world, device)
+
+    # the fused kernel alone (dominant) inside the same loop, and what follows it in a sequence split
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.profiler.start()
+    with sampler:
+        for i in range(steps):
+            tb = tables[i % R]
+            ev[i][0].record()
+            if seq_parts == 1:
+                packed_decode_attention(q_pool[i % n_q], tb, out=out)
+                ev[i][1].record()
+            else:
+                packed_decode_attention(q_pool[i % n_q], tb, out_partial=rec, seq_part=seq_part)
+                ev[i][1].record()
+                sharding.combine_across_ranks(rec, group, gathered=gathered)
+            ev[i][2].record()
+        torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    fused_ms = max_over_ranks(statistics.mean(e[0].elapsed_time(e[1]) for e in ev), world, device)
+    if seq_parts == 1:
+        # a step is exactly one launch of the fused kernel and the launches run back to back: the timed
+        # region per step is the kernel's average duration too (the per-launch event pairs of the pass
+        # above add their own gaps; the smaller of the two is reported)
+        fused_ms = min(fused_ms, ms / steps)
+    after_ms = max_over_ranks(statistics.mean(e[1].elapsed_time(e[2]) for e in ev), world, device)
+
+    res = {"ms_region": ms, "timing": timing, "fused_ms": fused_ms, "after_ms": after_ms, "step_bytes": step_bytes,
+           "replicas": R, "tables": tables, "out": out, "q0": q_pool[0], "sampler": sampler, "h": (h0, h1),
+           "n_views": n_views, "Hq_loc": Hq_loc}
+    if want_e2e:
+        # end to end through the public call with host buffers: pinned q in, pinned out back, every step
+        q_host = [q.cpu().pin_memory() for q in q_pool[:min(n_q, 8)]]
+        out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+        def e2e_step(i):
+            packed_decode_attention_host(q_host[i % len(q_host)], tables[i % R], out_host, slices=e2e_slices)
+
+        for i in range(min(warmup, 3)):
+            e2e_step(i)
+        with sampler:
+            e2e_ms, e2e_timing = repeated_regions(e2e_step, steps, barrier, world, device, min_reps=5, target_ms=30.0)
+        res["e2e_ms_region"], res["e2e_timing"] = e2e_ms, e2e_timing
+    for tb in tables:
+        tb.check_status()
+    return res
+
+
+def grid_name(world, seq_parts):
+    return f"{world // seq_parts}x{seq_parts}"
+
+
+def run_decode(args, rank, world, device):
     cfg = dict(CFG3)
     if args.small:
         cfg.update(layers=2, batch=2, context=4096, budget=1024)
     if args.layers:
         cfg.update(layers=args.layers)
-    H_kv = cfg["kv_heads"]
-    assert H_kv % world == 0, "KV heads are sharded across ranks: world size must divide 8"
-    h0, h1 = rank * H_kv // world, (rank + 1) * H_kv // world
-    g = cfg["q_heads"] // H_kv
-    Hq_loc = (h1 - h0) * g
-    n_views = cfg["layers"] * cfg["batch"]
-    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    m = measure_decode(cfg, rank, world, device, steps=args.steps, warmup=args.warmup, chunks=args.chunks,
+                       want_e2e=True, e2e_slices=args.e2e_slices, small=args.small)
+    t0 = m["tables"][0]
+    k_rest, rows_rest, n_whole = t0.plan(t0.n_views)
+    h0, h1 = m["h"]
+    line = None
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        ms = m["ms_region"]
+        tokens = cfg["batch"] * args.steps
+        sec = ms / 1e3
+        step_bytes = m["step_bytes"]
+        total_step_bytes = step_bytes * world            # every rank holds the same number of heads
+        achieved = step_bytes / (m["fused_ms"] / 1e3) / 1e9   # per-GPU GB/s of the dominant kernel
+        e2e_ms = m["e2e_ms_region"]
+        line = {
+            "metric": METRIC, "value": tokens / sec, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "u8 codes / fp16 scales, fp32 accumulate",
+            "data": "synthetic",
+            "config": config_dict(cfg, args.small or args.layers),
+            "detail": {
+                "parallelism": f"kv-head sharding x{world} (no data-path collective)",
+                "launches_per_step": 1,
+                "l2": f"{m['replicas']} cache replica(s) rotated per step, {m['replicas'] * step_bytes / 2**20:.0f} MiB per GPU "
+                      f"> 2 x 126 MiB L2; no flush needed",
+                "launch_shape": ("one CTA per (view, KV head)" if k_rest == 1
+                                 else f"{n_whole} (view, KV head) units whole, the other "
+                                      f"{t0.n_views * (h1 - h0) - n_whole} in {k_rest} chunks of {rows_rest} "
+                                      "rows merged in the kernel"),
+                "timing": dict(m["timing"], note="value = median over the repeated regions of `steps` steps each"),
+            },
+            "hbm_gbs": total_step_bytes * args.steps / sec / 1e9,
+            "hbm_frac_of_8tbs": total_step_bytes * args.steps / sec / 1e9 / (8000.0 * world),
+            "algorithmic_bytes_per_step": total_step_bytes,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_ALGO_BYTE * step_bytes,
+                         "peak_kind": peak_kind, "kernel": "decode_fused_kernel", "kernel_ms": m["fused_ms"],
+                         "algorithmic_bytes_per_launch": step_bytes},
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": m["q0"].numel() * m["q0"].element_size() * world,
+                    "d2h_bytes_per_step": m["out"].numel() * m["out"].element_size() * world,
+                    "ms_per_step": e2e_ms / args.steps, "reps": m["e2e_timing"]["reps"]},
+            "gpu_launches": args.steps * (m["timing"]["reps"] + 1) + args.steps * m["e2e_timing"]["reps"] * (2 if world == 1 else 1),
+            "clocks": m["sampler"].summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_decode_baseline(cfg, m["tables"][0], layers_per_sample=1, steps=2)
+    tables0 = m["tables"]
+    del m
+    if args.no_also or args.small or args.layers:
+        return line
+    # the other configurations, measured briefly in the same run and carried under "also"
+    del tables0
+    torch.cuda.empty_cache()
+    also = {}
+    grids = [1] + ([2] if world % 2 == 0 and world >= 2 else [])
+    c4 = []
+    for sp in grids:
+        r4 = measure_decode(dict(CFG4), rank, world, device, steps=min(args.steps, 16), warmup=3, seq_parts=sp)
+        if rank == 0:
+            peak, _ = load_peaks()
+            per_step = r4["ms_region"] / min(args.steps, 16)
+            c4.append({"grid": grid_name(world, sp) + " (head groups x sequence parts)",
+                       "value": CFG4["batch"] / (per_step / 1e3), "unit": "tokens/s", "ms_per_step": per_step,
+                       "kernel_ms": r4["fused_ms"], "allgather_plus_combine_us": r4["after_ms"] * 1e3 if sp > 1 else 0.0,
+                       "algorithmic_bytes_per_gpu": r4["step_bytes"],
+                       "roofline_frac_per_gpu": r4["step_bytes"] / (r4["fused_ms"] / 1e3) / 1e9 / peak,
+                       "timing": r4["timing"]})
+        del r4
+        torch.cuda.empty_cache()
+    if rank == 0:
+        also["config4"] = {"config": config_dict(CFG4, False), "grids": c4,
+                           "note": "sequence parts = row windows of the same packed layer per rank; one NCCL all-gather "
+                                   "of [rows,132] fp32 records per step, then the log-sum-exp combine kernel"}
+    if world == 1:
+        short = argparse.Namespace(**vars(args))
+        short.steps, short.warmup, short.no_cpu_baseline, short.layers = min(args.steps, 10), 3, True, None
+        pk = run_pack(short, rank, world, device)
+        torch.cuda.empty_cache()
+        al = run_alloc(short, rank, world, device)
+        if rank == 0:
+            also["pack"] = {k: pk[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "roofline")}
+            also["alloc"] = {k: al[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "roofline")}
+    if rank == 0:
+        line["also"] = also
+    return line
 
-    # enough distinct cache replicas that consecutive steps cannot be served from L2
-    tables, step_bytes = [], None
-    while True:
-        layers, nvs, nbytes = build_decode_cache(cfg, h0, h1, len(tables), device)
-        tables.append(DecodeTable(layers, nvs, Hq_loc, n_chunks=args.chunks))
-        step_bytes = nbytes
-        if len(tables) * nbytes >= 2.2 * L2_BYTES or args.small:
-            break
-    R = len(tables)
-    gen = torch.Generator(device=device)
-    gen.manual_seed(4242 + rank)
-    n_q = min(args.steps + args.warmup, 64)
-    q_pool = [(torch.randn(n_views, Hq_loc, 128, generator=gen, device=device) / 128 ** 0.5).to(torch.bfloat16)
-              for _ in range(n_q)]
-    out = torch.empty((n_views, Hq_loc, 128), dtype=torch.float32, device=device)
 
-    def step(i):
-        packed_decode_attention(q_pool[i % n_q], tables[i % R], out=out)
-
-    for i in range(args.warmup):
-        step(i)
-    sampler = ClockSampler(device.index if device.index is not None else 0)
-    with sampler:
-        ms = timed_steps(step, args.steps, barrier)
-    ms = max_over_ranks(ms, world, device)
-
-    # per-kernel duration of the fused kernel (dominant) inside the same loop, for the roofline
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    torch.cuda.synchronize()
-    torch.cuda.profiler.start()
-    with sampler:
-        for i in range(args.steps):
-            tb = tables[i % R]
-            ev[i][0].record()
-            packed_decode_attention(q_pool[i % n_q], tb, out=out)
-            ev[i][1].record()
-        torch.cuda.synchronize()
-    torch.cuda.profiler.stop()
-    fused_ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
-    fused_ms = max_over_ranks(fused_ms, world, device)
-
-    # end to end through the public call with host buffers: pinned q in, pinned out back, every step
-    q_host = [q.cpu().pin_memory() for q in q_pool[:min(n_q, 8)]]
-    q_dev = q_pool[0]
-    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-
-    def e2e_step(i):
-        # uploads the queries, runs the kernel and downloads the results in view ranges on
-        # separate streams; returns when out_host holds the step's results
-        packed_decode_attention_host(q_host[i % len(q_host)], tables[i % R], out_host, slices=args.e2e_slices)
-
-    for i in range(min(args.warmup, 3)):
-        e2e_step(i)
-    with sampler:
-        e2e_ms = timed_steps(e2e_step, args.steps, barrier)
-    e2e_ms = max_over_ranks(e2e_ms, world, device)
-
-    for tb in tables:
-        tb.check_status()
-    t0 = tables[0]
-    v_main, k_rest, rows_rest = t0.unit_plan(t0.n_views)
-    launches = 1
+def run_decode_long(args, rank, world, device):
+    """Config 4 as a workload of its own: KV heads over world/seq_parts head groups, the live rows
+    of every head over seq_parts ranks (NCCL all-gather of the records + combine per step)."""
+    cfg = dict(CFG4)
+    if args.small:
+        cfg.update(layers=2, batch=2, context=8192, budget=2048)
+    if args.layers:
+        cfg.update(layers=args.layers)
+    sp = args.seq_parts
+    m = measure_decode(cfg, rank, world, device, steps=args.steps, warmup=args.warmup, seq_parts=sp,
+                       chunks=args.chunks, small=args.small)
     if rank != 0:
         return None
     peak, peak_kind = load_peaks()
-    tokens = cfg["batch"] * args.steps
+    ms = m["ms_region"]
     sec = ms / 1e3
-    total_step_bytes = step_bytes * world            # every rank holds the same number of heads
-    achieved = step_bytes / (fused_ms / 1e3) / 1e9   # per-GPU GB/s of the dominant kernel
-    traffic = None if NCU_TRAFFIC_BYTES_PER_ALGO_BYTE is None else NCU_TRAFFIC_BYTES_PER_ALGO_BYTE * step_bytes
+    tokens = cfg["batch"] * args.steps
+    step_bytes = m["step_bytes"]
+    achieved = step_bytes / (m["fused_ms"] / 1e3) / 1e9
     line = {
         "metric": METRIC, "value": tokens / sec, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "u8 codes / fp16 scales, fp32 accumulate",
-        "data": "synthetic",
-        "config": {
-            "workload": "config 3: full-depth decode, Llama-3.1-8B attention shape — 32 layers x batch 16 x "
-                        "8 KV heads (32 q heads, head_dim 128), context 32768, 2048 kept tokens/head "
-                        "(1/8 fp16, 1/4 8b, 3/8 4b, 1/4 2b), 64 K channels kept (16@8b,24@4b,24@2b), bf16 q per step",
-            "batch": cfg["batch"], "layers": cfg["layers"], "kv_heads": H_kv, "q_heads": cfg["q_heads"],
-            "token_budget": cfg["budget"], "context": cfg["context"],
-            "parallelism": f"kv-head sharding x{world} (no data-path collective)",
-            "launches_per_step": launches,
-            "l2": f"{R} cache replica(s) rotated per step, {R * step_bytes / 2**20:.0f} MiB per GPU "
-                  f"> 2 x 126 MiB L2; no flush needed",
-            "small": bool(args.small or args.layers),
-            "launch_shape": ("one CTA per (view, KV head)" if k_rest == 1
-                             else f"{t0.plan(t0.n_views)[2]} (view, KV head) units whole, the other "
-                                  f"{t0.n_views * (h1 - h0) - t0.plan(t0.n_views)[2]} in {k_rest} chunks of {rows_rest} "
-                                  "rows merged in the kernel"),
-        },
-        "hbm_gbs": total_step_bytes * args.steps / sec / 1e9,
-        "hbm_frac_of_8tbs": total_step_bytes * args.steps / sec / 1e9 / (8000.0 * world),
-        "algorithmic_bytes_per_step": total_step_bytes,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
-                     "kernel": "decode_fused_kernel", "kernel_ms": fused_ms,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "u8 codes / fp16 scales, fp32 accumulate", "data": "synthetic",
+        "config": config_dict(cfg, args.small or args.layers),
+        "detail": {"parallelism": f"{grid_name(world, sp)} (KV-head groups x sequence parts)",
+                   "collective": ("none on the data path" if sp == 1 else
+                                  "one NCCL all-gather of [rows,132] fp32 records per step + log-sum-exp combine kernel"),
+                   "allgather_plus_combine_us": m["after_ms"] * 1e3 if sp > 1 else 0.0,
+                   "l2": f"{m['replicas']} cache replica(s), {m['replicas'] * step_bytes / 2**20:.0f} MiB read per GPU and rotation",
+                   "timing": m["timing"]},
+        "hbm_gbs": step_bytes * world * args.steps / sec / 1e9,
+        "algorithmic_bytes_per_step": step_bytes * world,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_ALGO_BYTE * step_bytes, "peak_kind": peak_kind,
+                     "kernel": "decode_fused_kernel", "kernel_ms": m["fused_ms"],
                      "algorithmic_bytes_per_launch": step_bytes},
-        "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s",
-                "h2d_bytes_per_step": q_dev.numel() * q_dev.element_size() * world,
-                "d2h_bytes_per_step": out.numel() * out.element_size() * world,
-                "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": launches * args.steps,
-        "clocks": sampler.summary(),
+        "gpu_launches": args.steps * (m["timing"]["reps"] + 1) * (1 if sp == 1 else 2),
+        "clocks": m["sampler"].summary(),
     }
-    if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_decode_baseline(cfg, tables[0], layers_per_sample=1, steps=2)
     return line
 
 
@@ -363,15 +512,20 @@ def cpu_decode_baseline(cfg, table, layers_per_sample, steps):
 
 
 def run_reference_arm(args, rank, world):
-    """The reference's CPU path (numpy restatement under oracle/) on the host cores, rank 0 only."""
+    """The reference's CPU path — dequantise the packed cache, then plain attention
+    (obkv_accel/trizone_decompress.py:185-333 + softmax attention) — as restated in numpy under
+    oracle/, on all host cores, rank 0 only.  The reference is Python on torch; its sources are not
+    on the benchmark machine, so the restatement is what is timed everywhere (kind "port")."""
     if rank != 0:
         return None
     import numpy as np
     from oracle import ref_packing as RP
     from rdkv_b200 import synth
-    cfg = dict(CFG3)
+    cfg = dict(CFG4 if args.workload == "decode-long" else CFG3)
     if args.small:
         cfg.update(layers=2, batch=2, context=4096, budget=1024)
+    if args.layers:
+        cfg.update(layers=args.layers)
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     g = cfg["q_heads"] // cfg["kv_heads"]
@@ -395,9 +549,7 @@ def run_reference_arm(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": full_step * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (numpy)", "data": "synthetic",
-        "config": {"workload": "config 3 decode (same as the CUDA arm)", "batch": cfg["batch"],
-                   "layers": cfg["layers"], "kv_heads": cfg["kv_heads"], "q_heads": cfg["q_heads"],
-                   "token_budget": cfg["budget"], "context": cfg["context"], "small": bool(args.small)},
+        "config": config_dict(cfg, args.small or args.layers),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -441,15 +593,17 @@ def run_pack(args, rank, world, device):
         state["batch"] = pack_kv_layers(Ks, Vs, v_bits, k_bits, 4, build_mask=False, launch_events=spans)
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
-    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in spans)
+    # per call two spans: the two partition launches, the four packing launches
+    kern_ms = sum(a.elapsed_time(b) for a, b in spans) / args.steps
     out_bytes = 0
     for pl, nv in state["batch"]:
         out_bytes += sum(t.numel() * t.element_size() for t in
                          (pl.K_2bit, pl.K_4bit, pl.K_8bit, pl.V_2bit, pl.V_4bit, pl.V_8bit, pl.V_scale,
                           pl.V_zp, pl.K_ch_scale, pl.K_ch_zp, nv) if t is not None)
     nominal = L * H * T * 128 * 2 * 2                       # all fp16 K and V bytes of the context
-    # kept rows of V read once, kept rows of K read twice (extrema pass, quantise pass), packed bytes written
-    moved = L * H * N * 256 * 3 + out_bytes
+    # what has to move: kept rows of K and of V read once, the bit maps read once, packed bytes written
+    # (the second reading of the kept K rows by the quantise pass is the kernels' own choice, not counted)
+    moved = L * H * N * 256 * 2 + v_bits.numel() * v_bits.element_size() + k_bits.numel() * k_bits.element_size() + out_bytes
     peak, kind = load_peaks()
     line = {"metric": "prefill quantise-and-bitpack GB/s of fp16 input consumed", "value": nominal / sec / 1e9,
             "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
@@ -460,8 +614,8 @@ def run_pack(args, rank, world, device):
                        "l2": "4.3 GB of inputs per step > L2"},
             "roofline": {"bound": "hbm", "achieved": moved / (kern_ms / 1e3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": moved / (kern_ms / 1e3) / 1e9 / peak,
-                         "traffic": moved * PACK_NCU_TRAFFIC_BYTES_PER_ALGO_BYTE, "peak_kind": kind,
-                         "kernel": "pack_v128_batched_kernel + pack_k_minmax128_batched_kernel + pack_k_params_batched_kernel + pack_k_quant_batched_kernel",
+                         "traffic": PACK_NCU_TRAFFIC_BYTES, "peak_kind": kind,
+                         "kernel": "2 x partition_kernel + pack_v128_batched_kernel + pack_k_minmax128_batched_kernel + pack_k_params_batched_kernel + pack_k_quant_batched_kernel",
                          "kernel_ms": kern_ms, "algorithmic_bytes_per_step": moved},
             "gpu_launches": 6 * args.steps, "clocks": sampler.summary()}
     if not args.no_cpu_baseline:
@@ -566,7 +720,10 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="rdkv_b200", choices=["rdkv_b200", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "pack", "alloc", "score"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode-long", "pack", "alloc", "score"])
+    ap.add_argument("--seq-parts", type=int, default=1,
+                    help="decode-long: ranks that split the live rows of the same heads (1 = KV-head sharding only)")
+    ap.add_argument("--no-also", action="store_true", help="default workload: skip the brief runs of the other configurations")
     ap.add_argument("--small", action="store_true", help="2 layers x batch 2 (smoke-sized case)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling-sized runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -595,6 +752,8 @@ def main():
     try:
         if args.workload == "decode":
             line = run_decode(args, rank, world, device)
+        elif args.workload == "decode-long":
+            line = run_decode_long(args, rank, world, device)
         elif args.workload == "pack":
             line = run_pack(args, rank, world, device)
         elif args.workload == "score":

@@ -157,10 +157,14 @@ int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const vo
 
 /* The same kernel with everything a decode step needs in ONE launch (new; same reference
  * block, obkv_accel/fast_decode.py:1701-1784):
- *   - row_begin / row_end: only the live rows [row_begin, row_end) of every head are attended
- *     over (0 / INT32_MAX = all of them); chunk c covers rows [row_begin + c*chunk_rows, +chunk_rows)
- *     cut at row_end.  A sequence-split rank passes its row window of the shared packed layer and
- *     asks for out_record.
+ *   - seq_part / seq_parts: the sequence split.  Part i of n takes, of every head, rows
+ *     [n_p*i/n, n_p*(i+1)/n) (rounded down to multiples of 32) of each of its four V phases (its
+ *     n_p 2-bit rows, its 4-bit rows, its 8-bit rows, its fp16 rows), so the parts read about the
+ *     same bytes; the ranks that share a head pass their part of the same packed layer and ask
+ *     for out_record (0 / 1 = everything).
+ *   - row_begin / row_end: of the rows left by the part, numbered phase after phase, only
+ *     [row_begin, row_end) are attended over (0 / INT32_MAX = all of them); chunk c covers rows
+ *     [row_begin + c*chunk_rows, +chunk_rows) cut at row_end.
  *   - unit_recs / k_slots / nkb_max: optional prepared table of the views (rdkv_decode_prepare
  *     below); NULL / NULL / 0 = the kernel reads counts, scales, zero points and permutations from
  *     the views' own tensors (a second, dependent round trip per CTA).
@@ -177,7 +181,7 @@ int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const vo
  *     (m, l, -, -, o[128]) per (view, query head), input of rdkv_lse_combine across shards). */
 int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,
                      int H_kv, int chunk_rows, int n_chunks, int n_whole_units, int row_begin, int row_end,
-                     int k_row_bytes_max, const void* unit_recs, const void* k_slots, int nkb_max,
+                     int seq_part, int seq_parts, int k_row_bytes_max, const void* unit_recs, const void* k_slots, int nkb_max,
                      float* partials, int32_t* unit_counters, float* out, float* out_record,
                      int32_t* status, void* stream);
 

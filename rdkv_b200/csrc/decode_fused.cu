@@ -291,6 +291,13 @@ static_assert(sizeof(PhaseRec) == 64 && sizeof(UnitRec) == 304, "prepared-table 
 // (0 for a pad slot).  16 bytes; [unit][kb][lane].
 struct __align__(16) KSlotRec { uint32_t perm4, zp4, sc01, sc23; };
 
+// Sequence parts: a head's rows are shared out phase by phase (every part gets its share of the
+// 2-bit, of the 4-bit, of the 8-bit and of the fp16 rows, so the parts read about the same bytes);
+// part i of `parts` takes rows [part_cut(n, i), part_cut(n, i + 1)) of a phase of n rows.
+__host__ __device__ inline int part_cut(int n, int i, int parts) {
+  return i >= parts ? n : (int)(((int64_t)n * i / parts) & ~31);
+}
+
 // Accumulator unit exponent: true value = acc * 2^E(phase, v), v = m-tile & 3.
 __device__ __forceinline__ int acc_exp(int phase, int v) {
   return phase == 0 ? 24 - 2 * v : phase == 1 ? 24 - 4 * (v >> 1) : phase == 2 ? 24 : 0;
@@ -505,7 +512,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
                     float* __restrict__ partials, float* __restrict__ out, int* __restrict__ status,
                     float* __restrict__ aux, int64_t aux_stride, int t_eff,
                     const UnitRec* __restrict__ unit_recs, const KSlotRec* __restrict__ kslots, int nkb_max,
-                    int* __restrict__ unit_ctr, float* __restrict__ merged, int row_begin, int row_end) {
+                    int* __restrict__ unit_ctr, float* __restrict__ merged, int row_begin, int row_end,
+                    int part, int parts) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ rdkv_layer_view v;
   __shared__ CtaGeom G;
@@ -575,8 +583,14 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         const bool fits_q = SQ.total <= stage_bytes && kq.n2p + kq.n4p + kq.n8 > 0 &&
                             kq.n2p + kq.n4p + kq.n8 <= DPAD_MAX && kq.nkb <= KB_MAX;
         const int c0 = row_begin + chunk * chunk_rows, c1 = n_chunks == 1 ? row_end : min(c0 + chunk_rows, row_end);
-        const int lo = max(a0.x, c0), hi = max(lo, min(a0.y, c1));
-        const int n = hi - lo, d = lo - a0.x;
+        // this part's share of the phase, then the chunk's window of the part's rows (numbered phase
+        // after phase): lo, hi in that numbering; d = first row's offset from the phase's first row
+        const int np = a0.y - a0.x, ps = part_cut(np, part, parts), pn = part_cut(np, part + 1, parts) - ps;
+        const int pn0 = __shfl_sync(0xffffffffu, pn, 0), pn1 = __shfl_sync(0xffffffffu, pn, 1);
+        const int pn2 = __shfl_sync(0xffffffffu, pn, 2);
+        const int lb = (p > 0 ? pn0 : 0) + (p > 1 ? pn1 : 0) + (p > 2 ? pn2 : 0);
+        const int lo = max(lb, c0), hi = max(lo, min(lb + pn, c1));
+        const int n = hi - lo, d = ps + (lo - lb);
         const int ntile = p == 0   ? (n + phase_tile_rows(0) - 1) / phase_tile_rows(0)
                           : p == 1 ? (n + phase_tile_rows(1) - 1) / phase_tile_rows(1)
                           : p == 2 ? (n + phase_tile_rows(2) - 1) / phase_tile_rows(2)
@@ -589,7 +603,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         if (lane < 4) {
           G.lo[p] = lo; G.hi[p] = hi;
           G.first_tile[p] = p == 0 ? 0 : p == 1 ? t0 : p == 2 ? t0 + t1 : t0 + t1 + t2;
-          G.krow[p] = p < 3 ? (int64_t)lo : (int64_t)h2.y + d;
+          G.krow[p] = p < 3 ? (int64_t)a0.x + d : (int64_t)h2.y + d;
           G.k2[p] = ptr_of(a1.x, a1.y) + (int64_t)d * kq.sub2;
           G.k4[p] = ptr_of(a1.z, a1.w) + (int64_t)d * kq.sub4;
           G.k8[p] = ptr_of(a2.x, a2.y) + (int64_t)d * kq.n8;
@@ -681,8 +695,15 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     const int b_lo = MODE == MODE_SCORES ? 0 : p == 0 ? 0 : p == 1 ? hc.n2 : p == 2 ? hc.n2 + hc.n4 : hc.t_v;
     const int b_hi = MODE == MODE_SCORES ? (p == 0 ? t_eff : 0)
                                          : p == 0 ? hc.n2 : p == 1 ? hc.n2 + hc.n4 : p == 2 ? hc.t_v : hc.t_v + hc.n16;
-    const int lo = max(b_lo, c0);
-    const int hi = max(lo, min(b_hi, c1));
+    // this part's share of the phase, then the chunk's window of the part's rows (numbered phase
+    // after phase); lo, hi: the rows of the head it comes to
+    const int np = b_hi - b_lo, ps = part_cut(np, part, parts), pn = part_cut(np, part + 1, parts) - ps;
+    const int pn0 = __shfl_sync(0xffffffffu, pn, 0), pn1 = __shfl_sync(0xffffffffu, pn, 1);
+    const int pn2 = __shfl_sync(0xffffffffu, pn, 2);
+    const int lb = (p > 0 ? pn0 : 0) + (p > 1 ? pn1 : 0) + (p > 2 ? pn2 : 0);
+    const int wl = max(lb, c0), wh = max(wl, min(lb + pn, c1));
+    const int lo = b_lo + ps + (wl - lb);
+    const int hi = lo + (wh - wl);
     const int n = hi - lo;
     const int ntile = (n + phase_tile_rows(p) - 1) / phase_tile_rows(p);
     const int64_t krow = (p < 3 || MODE == MODE_SCORES) ? lo : (int64_t)v.max_t_v + (lo - hc.t_v);   // stripe row
@@ -1422,7 +1443,7 @@ static int launch_fused(const rdkv_layer_view* views, int n_views, const void* q
                         float* aux, int64_t aux_stride, int t_eff, void* stream,
                         const void* unit_recs = nullptr, const void* kslots = nullptr, int nkb_max = 0,
                         int* unit_ctr = nullptr, float* merged = nullptr,
-                        int row_begin = 0, int row_end = 0x7fffffff, int n_whole = 0) {
+                        int row_begin = 0, int row_end = 0x7fffffff, int n_whole = 0, int part = 0, int parts = 1) {
   const int g = H_q / H_kv;
   const int n_hgrp = (g + GH - 1) / GH;
   const int64_t units = (int64_t)n_views * H_kv * n_hgrp;
@@ -1439,7 +1460,7 @@ static int launch_fused(const rdkv_layer_view* views, int n_views, const void* q
   decode_fused_kernel<MODE><<<(unsigned)items, CTA_THREADS, smem, (cudaStream_t)stream>>>(
       views, q, q_dtype, H_q, g, chunk_rows, n_chunks, n_whole, stage_bytes, partials, out, status, aux, aux_stride, t_eff,
       reinterpret_cast<const UnitRec*>(unit_recs), reinterpret_cast<const KSlotRec*>(kslots), nkb_max, unit_ctr, merged,
-      row_begin, row_end);
+      row_begin, row_end, part, parts);
   return launch_status();
 }
 
@@ -1487,10 +1508,11 @@ extern "C" int rdkv_decode_prepare(const rdkv_layer_view* views, int n_views, in
 
 extern "C" int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,
                                 int H_kv, int chunk_rows, int n_chunks, int n_whole_units, int row_begin, int row_end,
-                                int k_row_bytes_max, const void* unit_recs, const void* k_slots, int nkb_max,
+                                int seq_part, int seq_parts, int k_row_bytes_max, const void* unit_recs, const void* k_slots, int nkb_max,
                                 float* partials, int32_t* unit_counters, float* out, float* out_record,
                                 int32_t* status, void* stream) {
   if (n_chunks <= 0 || chunk_rows <= 0 || row_begin < 0 || row_end < row_begin) return RDKV_ERR_BAD_ARG;
+  if (seq_parts < 1 || seq_part < 0 || seq_part >= seq_parts) return RDKV_ERR_BAD_ARG;
   if ((out == nullptr) == (out_record == nullptr)) return RDKV_ERR_BAD_ARG;          // exactly one result form
   if (n_chunks > 1 && (partials == nullptr || unit_counters == nullptr)) return RDKV_ERR_BAD_ARG;
   if ((unit_recs == nullptr) != (k_slots == nullptr)) return RDKV_ERR_BAD_ARG;
@@ -1501,7 +1523,7 @@ extern "C" int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const
   if (rc != RDKV_OK || n_views == 0) return rc;
   return launch_fused<MODE_ATTN>(views, n_views, q, q_dtype, H_q, H_kv, chunk_rows, n_chunks, k_row_bytes_max,
                                  partials, out, status, nullptr, 0, 0, stream, unit_recs, k_slots, nkb_max,
-                                 unit_counters, out_record, row_begin, row_end, n_whole_units);
+                                 unit_counters, out_record, row_begin, row_end, n_whole_units, seq_part, seq_parts);
 }
 
 extern "C" int rdkv_decode_scores(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,

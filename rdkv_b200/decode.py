@@ -229,11 +229,12 @@ def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out
 
 def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int = 0, v1: Optional[int] = None,
                   *, out_record: Optional[Tensor] = None, rows: Optional[Tuple[int, int]] = None,
-                  plan: Optional[Tuple[int, int, int]] = None) -> None:
+                  seq_part: Optional[Tuple[int, int]] = None, plan: Optional[Tuple[int, int, int]] = None) -> None:
     """ONE launch of the fused kernel on views [v0, v1): whole units, or uniform chunks merged inside
     the kernel (DecodeTable.plan).  The result is the normalised ``out`` [n_views,H_q,128] or the
-    un-normalised record per query head ``out_record`` [n_views*H_q,132]; ``rows`` = (begin, end)
-    restricts every head to that window of its live rows.  q, out, out_record are the full-table
+    un-normalised record per query head ``out_record`` [n_views*H_q,132]; ``seq_part`` = (i, n)
+    restricts every head to part i of n of its rows (phase by phase), ``rows`` = (begin, end) to
+    that window of the rows that leaves.  q, out, out_record are the full-table
     tensors, the view range is cut by pointer offsets; ``out`` may be pinned host memory."""
     require_cuda(q, "q")
     if q.shape[-1] != HEAD_DIM or q.numel() != table.n_views * table.H_q * HEAD_DIM:
@@ -248,7 +249,12 @@ def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int 
     r0, r1 = (0, 0x7fffffff) if rows is None else (int(rows[0]), int(rows[1]))
     if not 0 <= r0 <= r1:
         raise ValueError(f"bad row window [{r0},{r1})")
-    k, rows_k, n_whole = plan if plan is not None else table.plan(v1 - v0, None if rows is None else min(r1, table.unit_rows) - r0)
+    sp_i, sp_n = (0, 1) if seq_part is None else (int(seq_part[0]), int(seq_part[1]))
+    if sp_n < 1 or not 0 <= sp_i < sp_n:
+        raise ValueError(f"bad sequence part {sp_i} of {sp_n}")
+    part_rows = table.unit_rows if sp_n == 1 else -(-table.unit_rows // sp_n) + 128   # a part's rows, at most
+    live = min(r1, part_rows) - r0
+    k, rows_k, n_whole = plan if plan is not None else table.plan(v1 - v0, None if (rows is None and sp_n == 1) else live)
     hy = table.H_kv * table._n_hgrp
     if plan is not None:                                   # a plan of the whole table: its whole units are the table's first
         n_whole -= v0 * hy
@@ -261,7 +267,7 @@ def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int 
     ws = table.chunk_workspace(k) if k > 1 else None
     with torch.cuda.device(table.device):
         check(lib().rdkv_decode_attn(table.views.data_ptr() + v0 * C.sizeof(LayerView), v1 - v0,
-                                     off(q, HEAD_DIM), q_dtype_tag(q), table.H_q, table.H_kv, rows_k, k, n_whole, r0, r1,
+                                     off(q, HEAD_DIM), q_dtype_tag(q), table.H_q, table.H_kv, rows_k, k, n_whole, r0, r1, sp_i, sp_n,
                                      table.k_row_bytes_max,
                                      None if table.live_counts else table.unit_recs.data_ptr() + v0 * table.H_kv * table._unit_rec_bytes,
                                      None if table.live_counts else table.k_slots.data_ptr() + v0 * table.H_kv * table.nkb_max * 512,
@@ -331,14 +337,16 @@ def tail_attention_partial(q: Tensor, new_k: Tensor, new_v: Tensor, n_new, H_kv:
 def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tensor] = None,
                             out_partial: Optional[Tensor] = None, new_k: Optional[Tensor] = None,
                             new_v: Optional[Tensor] = None, n_new=0,
-                            rows: Optional[Tuple[int, int]] = None) -> Tensor:
+                            rows: Optional[Tuple[int, int]] = None,
+                            seq_part: Optional[Tuple[int, int]] = None) -> Tensor:
     """softmax(q·K̂ᵀ/√128)·V̂ over every view of ``table``.
 
     q [n_views,H_q,128] fp16/bf16/fp32 -> out [n_views,H_q,128] fp32.  With
     ``out_partial`` ([n_views*H_q,132] fp32) the merged un-normalised (m, l, o)
     record per query head is written instead, for a later combine across
-    sequence shards; ``rows`` = (begin, end) restricts every head to that window of
-    its live rows (the share of one sequence-split rank).  ``new_k`` / ``new_v``
+    sequence shards; ``seq_part`` = (i, n) restricts every head to part i of n of its
+    rows, shared out phase by phase (the share of one sequence-split rank), ``rows`` =
+    (begin, end) to that window of the rows that leaves.  ``new_k`` / ``new_v``
     [n_views,H_kv,cap,128] with ``n_new`` live rows add the uncompressed tail of
     decode-appended tokens (Zone C) to the same softmax, as the reference's attention
     block does (fast_decode.py:1719-1784).
@@ -354,7 +362,7 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
         if ws is None:
             ws = torch.empty((2, n_rows, PARTIAL_STRIDE), dtype=torch.float32, device=table.device)
             table._tail_ws = ws
-        _launch_units(q, table, None, out_record=ws[0], rows=rows)      # packed zones: merged record
+        _launch_units(q, table, None, out_record=ws[0], rows=rows, seq_part=seq_part)      # packed zones: merged record
         tail_attention_partial(q.reshape(table.n_views, table.H_q, HEAD_DIM), new_k, new_v, n_new, table.H_kv, ws[1])
         both = ws.permute(1, 0, 2)                                       # [n_rows, 2, 132]
         if out_partial is not None:
@@ -368,14 +376,14 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
         if (out_partial.dtype != torch.float32 or not out_partial.is_contiguous()
                 or out_partial.numel() != table.n_views * table.H_q * PARTIAL_STRIDE):
             raise ValueError(f"out_partial must be contiguous float32 [{table.n_views * table.H_q},{PARTIAL_STRIDE}]")
-        _launch_units(q, table, None, out_record=out_partial, rows=rows)
+        _launch_units(q, table, None, out_record=out_partial, rows=rows, seq_part=seq_part)
         return out_partial
     if out is None:
         out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
     if (not out.is_contiguous() or out.dtype != torch.float32
             or out.numel() != table.n_views * table.H_q * HEAD_DIM):
         raise ValueError(f"out must be contiguous float32 [{table.n_views},{table.H_q},{HEAD_DIM}]")
-    _launch_units(q, table, out, rows=rows)
+    _launch_units(q, table, out, rows=rows, seq_part=seq_part)
     return out
 
 

@@ -429,8 +429,9 @@ def pack_kv_layers(Ks: Sequence[Tensor], Vs: Sequence[Tensor], v_bits: Tensor, k
     packing launches whose third grid dimension is the layer.  Layer ``i`` of the result
     is bit-identical to ``pack_kv(Ks[i], Vs[i], v_bits[i], k_bits[i], gqa_factor)``.
     Layers whose K bit maps lead to different padded channel widths cannot share tall
-    tensors; they are then packed one by one.  ``launch_events``: a list that receives a
-    (start, end) pair of CUDA events around the three packing launches (for measurements).
+    tensors; they are then packed one by one.  ``launch_events``: a list that receives two
+    (start, end) pairs of CUDA events per call, around the two partition launches and around
+    the packing launches (for measurements).
     """
     import ctypes as C
     from ._lib import PackJob
@@ -446,8 +447,14 @@ def pack_kv_layers(Ks: Sequence[Tensor], Vs: Sequence[Tensor], v_bits: Tensor, k
     if tuple(v_bits.shape) != (L, H, T) or tuple(k_bits.shape) != (L, H, D):
         raise ValueError(f"v_bits must be [{L},{H},{T}] and k_bits [{L},{H},{D}]")
     v_bits, k_bits = v_bits.to(dev), k_bits.to(dev)
+    if launch_events is not None:
+        pev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        pev[0].record()
     tok_order, tok_counts = partition_by_bits(v_bits.reshape(L * H, T), 0)
     ch_order, ch_counts = partition_by_bits(k_bits.reshape(L * H, D), 1)
+    if launch_events is not None:
+        pev[1].record()
+        launch_events.append(pev)
     host = torch.cat([tok_counts, ch_counts], dim=0).cpu().numpy()          # the one host read
     tok_h = host[:L * H].reshape(L, H, 4)
     ch_h = host[L * H:].reshape(L, H, 4)

@@ -5,13 +5,17 @@ One process per GPU (torch.distributed, NCCL over NVLink).  Two ways to cut the 
 * KV-head sharding — rank r packs and serves KV heads [r*H_kv/N, (r+1)*H_kv/N) and their
   query heads.  Heads are independent, so attention needs no collective; an all-gather of
   the [B, H_q_local, 128] outputs is only needed if every rank wants the full result.
-* sequence split — the ranks of a group each hold a slice of every head's kept tokens
-  (cut at pack time, each slice with its own per-head bounds and its own per-channel K
-  ranges), run the fused kernel on it and exchange one merged (m, l, o) record per query
-  head: one all-gather into local memory, then the log-sum-exp combine kernel.
+* sequence split — the ranks of a group serve the same heads of the SAME packed layer (packed
+  once, exactly as the reference packs it) and each attends over its own part of every head's
+  rows — its share of the head's 2-bit, 4-bit, 8-bit and fp16 rows, so that the parts read about
+  the same bytes (`part_rows`); the fused kernel writes one merged (m, l, o) record per query head,
+  the ranks exchange the records with one all-gather into local memory per decode step (all
+  layers and sequences together) and the log-sum-exp combine kernel merges them.  A rank reads
+  only its window's bytes; in this implementation every rank of the group keeps the whole packed
+  layer in memory.
 
 The reference has no distributed code; the oracle for both is the single-device result on
-the same (sharded or split) inputs.
+the same (sharded, unsplit) inputs.
 """
 from __future__ import annotations
 
@@ -40,15 +44,35 @@ def shard_heads(K: Tensor, V: Tensor, v_bits: Tensor, k_bits: Tensor, rank: int,
     return K[:, h0:h1], V[:, h0:h1], v_bits[h0:h1], k_bits[h0:h1]
 
 
-def split_tokens(v_bits: Tensor, part: int, n_parts: int) -> Tensor:
-    """Token bit map of sequence slice `part`: tokens outside [part*T/n, (part+1)*T/n) are
-    marked evicted (0), so packing this map keeps only the slice's tokens."""
-    if not 0 <= part < n_parts:
+def row_window(part: int, n_parts: int, rows: int) -> Tuple[int, int]:
+    """Live-row window [lo, hi) of sequence part `part` when heads of up to `rows` live rows are
+    split into `n_parts` equal parts (multiples of 64 rows, so that windows start on tile-friendly
+    boundaries; the last part takes what is left)."""
+    if n_parts <= 0 or not 0 <= part < n_parts:
         raise ValueError(f"bad part {part} of {n_parts}")
-    T = v_bits.shape[-1]
-    lo, hi = part * T // n_parts, (part + 1) * T // n_parts
-    out = torch.zeros_like(v_bits)
-    out[..., lo:hi] = v_bits[..., lo:hi]
+    per = max(64, ((-(-max(rows, 1) // n_parts) + 63) // 64) * 64)
+    lo = min(part * per, rows)
+    hi = rows if part == n_parts - 1 else min((part + 1) * per, rows)
+    return lo, max(lo, hi)
+
+
+def part_cut(n: int, i: int, parts: int) -> int:
+    """First row of part i when a phase of n rows is shared out over `parts` parts (multiples of
+    32 rows; the last part takes what is left).  The kernel computes the same."""
+    return n if i >= parts else (n * i // parts) & ~31
+
+
+def part_rows(counts: Sequence[int], part: int, parts: int):
+    """Rows of a head that part `part` of `parts` attends over: for each of the head's phases
+    (counts = its 2-bit, 4-bit, 8-bit, fp16 row counts) the (first, end) rows in the head's own
+    row order."""
+    if parts < 1 or not 0 <= part < parts:
+        raise ValueError(f"bad part {part} of {parts}")
+    out, base = [], 0
+    for n in counts:
+        n = int(n)
+        out.append((base + part_cut(n, part, parts), base + part_cut(n, part + 1, parts)))
+        base += n
     return out
 
 
@@ -91,14 +115,19 @@ def combine_across_ranks(local_record: Tensor, group=None, *, combine: Optional[
     return combine(records)
 
 
-def sequence_split_attention(q: Tensor, table, group=None, *, record: Optional[Tensor] = None,
+def sequence_split_attention(q: Tensor, table, group=None, *, part: Optional[int] = None,
+                             n_parts: Optional[int] = None, record: Optional[Tensor] = None,
                              gathered: Optional[Tensor] = None) -> Tensor:
-    """Decode attention when the ranks of `group` hold different token slices of the same
-    heads: fused kernel on the local slice -> one record per query head -> all-gather ->
-    combine.  q [n_views,H_q,128]; returns [n_views,H_q,128] fp32 on every rank of the group."""
+    """Decode attention when the ranks of `group` split the live rows of the same heads: fused
+    kernel on this rank's part of every (view, head) -> one record per query head ->
+    ONE all-gather for the whole step -> combine.  q [n_views,H_q,128]; returns
+    [n_views,H_q,128] fp32 on every rank of the group.  `part` / `n_parts` default to the
+    rank and size of the group."""
     from .decode import packed_decode_attention
+    n_parts = dist.get_world_size(group) if n_parts is None else n_parts
+    part = dist.get_rank(group) if part is None else part
     n_rows = table.n_views * table.H_q
     if record is None:
         record = torch.empty((n_rows, PARTIAL_STRIDE), dtype=torch.float32, device=q.device)
-    packed_decode_attention(q, table, out_partial=record)
+    packed_decode_attention(q, table, out_partial=record, seq_part=(part, n_parts))
     return combine_across_ranks(record, group, gathered=gathered).view(table.n_views, table.H_q, 128)

@@ -200,6 +200,74 @@ def test_whole_units_and_uniform_chunks():
         assert_attn_close(to_np(outs[0]), to_np(o), "whole units vs chunks")
 
 
+def test_row_windows_merge_to_the_unsplit_result():
+    """Sequence split on one GPU: every window of the heads' live rows gives the oracle's record for
+    that window, and the windows' records merge to the unsplit result (ragged heads, windows that
+    cut phases anywhere, windows past a short head's end)."""
+    from oracle import ref_attention as RA
+    from oracle import ref_packing as RP
+    from rdkv_b200 import sharding, synth
+    from rdkv_b200.decode import DecodeTable, lse_combine, packed_decode_attention
+    from rdkv_b200.packing import pack_kv
+    H_kv, g, T = 4, 4, 2048
+    layers, nvs, ols = [], [], []
+    for i, ragged in enumerate(([700, 333, 512, 64], None)):
+        seed = synth.unit_seed(7, i, 3)
+        K, V = synth.make_kv(H_kv, T, seed=seed)
+        vb = synth.make_v_bits(H_kv, T, 640, seed=seed, per_head_N=ragged)
+        kb = synth.make_k_bits(H_kv, seed=seed)
+        pl, nv = pack_kv(K.cuda(), V.cuda(), vb.cuda(), kb.cuda(), g, build_mask=False)
+        layers.append(pl); nvs.append(nv)
+        ols.append(RP.pack_kv(K.numpy(), V.numpy(), vb.numpy(), kb.numpy(), g))
+    q = synth.make_q(H_kv * g, seed=11, batch=2, dtype=torch.float16)
+    table = DecodeTable(layers, nvs, H_kv * g)
+    want = packed_decode_attention(q.cuda(), table)
+    for i, (ol, onv) in enumerate(ols):
+        assert_attn_close(to_np(want[i]), RA.decode_attention(q[i].float().numpy(), ol, onv)[0], f"unsplit view {i}")
+    for parts in (2, 3):
+        recs = []
+        for part in range(parts):
+            win = sharding.row_window(part, parts, table.unit_rows)
+            rec = torch.empty((2 * H_kv * g, 132), device="cuda")
+            packed_decode_attention(q.cuda(), table, out_partial=rec, rows=win)
+            recs.append(rec)
+            for i, (ol, onv) in enumerate(ols):                # the window alone against the oracle's window
+                o, m, l = RA.decode_attention(q[i].float().numpy(), ol, onv, rows=win)
+                r = to_np(rec).reshape(2, H_kv * g, 132)[i]
+                live = l > 0
+                got = np.where(live[:, None], r[:, 4:] / np.maximum(r[:, 1], 1e-30)[:, None], 0)
+                assert_attn_close(got[live], o[live], f"window {win} view {i}")
+                assert np.array_equal(np.isfinite(r[:, 0]), live)
+        got = lse_combine(torch.stack(recs, dim=1)).view(2, H_kv * g, 128)
+        assert float((got - want).abs().max()) < 2e-4, parts
+        # the sequence split proper: part i of n of every phase of every head, alone against the
+        # oracle's part, with and without a row window inside the part, and merged
+        recs = []
+        for part in range(parts):
+            rec = torch.empty((2 * H_kv * g, 132), device="cuda")
+            packed_decode_attention(q.cuda(), table, out_partial=rec, seq_part=(part, parts))
+            recs.append(rec)
+            for i, (ol, onv) in enumerate(ols):
+                o, m, l = RA.decode_attention(q[i].float().numpy(), ol, onv, seq_part=(part, parts))
+                r = to_np(rec).reshape(2, H_kv * g, 132)[i]
+                live = l > 0
+                got_i = np.where(live[:, None], r[:, 4:] / np.maximum(r[:, 1], 1e-30)[:, None], 0)
+                assert_attn_close(got_i[live], o[live], f"part {part}/{parts} view {i}")
+                assert np.array_equal(np.isfinite(r[:, 0]), live)
+        got = lse_combine(torch.stack(recs, dim=1)).view(2, H_kv * g, 128)
+        assert float((got - want).abs().max()) < 2e-4, parts
+        halves = [torch.empty((2 * H_kv * g, 132), device="cuda") for _ in range(2)]
+        packed_decode_attention(q.cuda(), table, out_partial=halves[0], seq_part=(0, parts), rows=(0, 128))
+        packed_decode_attention(q.cuda(), table, out_partial=halves[1], seq_part=(0, parts), rows=(128, 1 << 20))
+        both = lse_combine(torch.stack(halves, dim=1))     # two windows of part 0 = part 0
+        r0 = recs[0]
+        alone = torch.where(r0[:, 1:2] > 0, r0[:, 4:] / r0[:, 1:2].clamp_min(1e-30), torch.zeros_like(r0[:, 4:]))
+        assert float((both - alone).abs().max()) < 2e-4, parts
+    table.check_status()
+    with pytest.raises(ValueError):
+        packed_decode_attention(q.cuda(), table, rows=(5, 2))
+
+
 def test_host_buffer_call_equals_device_call():
     """The host-buffer form (view ranges on separate streams, copies overlapped with the
     kernels) returns bit-for-bit what the device call returns, for one-chunk tables and

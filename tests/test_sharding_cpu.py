@@ -1,6 +1,7 @@
 """Host-side sharding logic on 2 gloo ranks (CPU): head slices, token slices, the
 all-gather + log-sum-exp combine of sequence-split records (oracle as the compute),
 and the group consistency check."""
+import datetime
 import os
 import socket
 
@@ -23,9 +24,24 @@ def test_head_shard_and_grid():
     assert sharding.grid(5, 8, 2) == (2, 4, 1)
     with pytest.raises(ValueError):
         sharding.grid(0, 6, 4)
-    vb = synth.make_v_bits(2, 64, 32, seed=3)
-    parts = [sharding.split_tokens(vb, p, 2) for p in range(2)]
-    assert torch.equal(parts[0] + parts[1], vb) and int((parts[0][:, 32:] != 0).sum()) == 0
+    # row windows: disjoint, in order, covering [0, rows), starting on multiples of 64
+    for rows, parts in ((2048, 2), (1000, 3), (77, 1), (60, 4), (8192, 8)):
+        w = [sharding.row_window(p, parts, rows) for p in range(parts)]
+        assert w[0][0] == 0 and w[-1][1] == rows
+        assert all(a[1] == b[0] for a, b in zip(w, w[1:])) and all(lo % 64 == 0 or lo == rows for lo, _ in w)
+    with pytest.raises(ValueError):
+        sharding.row_window(2, 2, 100)
+    # parts of a head: every phase shared out, cut points on multiples of 32 rows, nothing lost
+    for counts in ((512, 768, 512, 256), (100, 0, 37, 5), (31, 33, 64, 1)):
+        for parts in (1, 2, 3):
+            got = [sharding.part_rows(counts, p, parts) for p in range(parts)]
+            base = 0
+            for ph, n in enumerate(counts):
+                spans = [got[p][ph] for p in range(parts)]
+                assert spans[0][0] == base and spans[-1][1] == base + n
+                assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+                assert all((lo - base) % 32 == 0 for lo, _ in spans)
+                base += n
 
 
 def _free_port():
@@ -38,7 +54,7 @@ def _free_port():
 
 def _worker(rank, world, port, mode, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
     try:
         from oracle import ref_attention as RA
         from oracle import ref_packing as RP
@@ -49,10 +65,11 @@ def _worker(rank, world, port, mode, ret):
         kb = synth.make_k_bits(H_kv, seed=seed)
         q = synth.make_q(H_kv * g, seed=seed + 1).numpy()
         if mode == "sequence":
-            # every rank packs its token slice of all heads, then the records are merged
-            mine = sharding.split_tokens(vb, rank, world)
-            layer, nv = RP.pack_kv(K.numpy(), V.numpy(), mine.numpy(), kb.numpy(), g)
-            o, m, l = RA.decode_attention(q, layer, nv)
+            # ONE packed layer (the reference's); every rank attends over its window of each head's
+            # live rows (ragged heads: the windows cut them at different places), then the records are merged
+            vb = synth.make_v_bits(H_kv, T, N, seed=seed, per_head_N=[96, 40, 77, 64])
+            layer, nv = RP.pack_kv(K.numpy(), V.numpy(), vb.numpy(), kb.numpy(), g)
+            o, m, l = RA.decode_attention(q, layer, nv, seq_part=(rank, world))
             rec = np.zeros((H_kv * g, 132), np.float32)
             rec[:, 0], rec[:, 1], rec[:, 4:] = m, l, o * l[:, None]
 
@@ -63,13 +80,7 @@ def _worker(rank, world, port, mode, ret):
 
             sharding.check_group_consistency(rec.shape[0])
             got = sharding.combine_across_ranks(torch.from_numpy(rec), combine=combine).numpy()
-            # expected: attention over the union of both slices' dequantised rows
-            halves = []
-            for p in range(world):
-                lp, nvp = RP.pack_kv(K.numpy(), V.numpy(), sharding.split_tokens(vb, p, world).numpy(), kb.numpy(), g)
-                halves.append(RA.decode_attention(q, lp, nvp))
-            want, _, _ = RA.lse_combine(np.stack([h[1] for h in halves]), np.stack([h[2] for h in halves]),
-                                        np.stack([h[0] * h[2][:, None] for h in halves]))
+            want = RA.decode_attention(q, layer, nv)[0]      # the unsplit result
             ret[rank] = float(np.abs(got - want).max())
         elif mode == "heads":
             Ks, Vs, vbs, kbs = sharding.shard_heads(K, V, vb, kb, rank, world)
@@ -104,10 +115,15 @@ def test_two_rank_gloo(mode):
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, world, port, mode, ret)) for r in range(world)]
     for p in procs:
+        p.daemon = True
         p.start()
     for p in procs:
         p.join(120)
-        assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:                                        # never leave a rank behind
+        p.kill()
+        p.join()
+    assert not alive and all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     if mode == "mismatch":
         assert all(ret[r] == "ValueError" for r in range(world))
     else:
