@@ -37,6 +37,7 @@ CFG4 = dict(name="config 4", layers=80, batch=4, kv_heads=8, q_heads=64, context
                      "(64 q heads, head_dim 128), context 131072, 8192 kept tokens/head (config-0 bit mix), "
                      "64 K channels kept, bf16 q per step")
 L2_BYTES = 126 * 1024 * 1024
+PERSISTENT = None                        # --persistent 0/1 forces the kernel form (default: the library's choice)
 METRIC = "packed-KV decode-attn tokens/s"
 
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one fused-kernel launch in
@@ -223,7 +224,7 @@ def measure_decode(cfg, rank, world, device, *, steps, warmup, seq_parts=1, chun
     tables, step_bytes, seq_part = [], None, None
     while True:
         layers, nvs = build_decode_cache(cfg, h0, h1, len(tables), device)
-        tb = DecodeTable(layers, nvs, Hq_loc, n_chunks=chunks)
+        tb = DecodeTable(layers, nvs, Hq_loc, n_chunks=chunks, persistent=PERSISTENT)
         seq_part = (part, seq_parts) if seq_parts > 1 else None
         step_bytes = sum(unit_bytes(pl, nv, seq_part) for pl, nv in zip(layers, nvs))
         tables.append(tb)
@@ -336,6 +337,10 @@ def run_decode(args, rank, world, device):
             "detail": {
                 "parallelism": f"kv-head sharding x{world} (no data-path collective)",
                 "launches_per_step": 1,
+                "kernel_form": ("persistent (resident CTAs draw the items from a counter)"
+                                if (t0.persistent if t0.persistent is not None else
+                                    (k_rest == 1 and t0.n_views * (h1 - h0) >= t0.PERSISTENT_MIN_ROUNDS * t0._sms * t0.CTAS_PER_SM))
+                                and t0._can_persist() else "one CTA per item"),
                 "l2": f"{m['replicas']} cache replica(s) rotated per step, {m['replicas'] * step_bytes / 2**20:.0f} MiB per GPU "
                       f"> 2 x 126 MiB L2; no flush needed",
                 "launch_shape": ("one CTA per (view, KV head)" if k_rest == 1
@@ -723,6 +728,8 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "decode-long", "pack", "alloc", "score"])
     ap.add_argument("--seq-parts", type=int, default=1,
                     help="decode-long: ranks that split the live rows of the same heads (1 = KV-head sharding only)")
+    ap.add_argument("--persistent", type=int, default=None, choices=[0, 1],
+                    help="force the per-item (0) or the persistent (1) form of the fused kernel")
     ap.add_argument("--no-also", action="store_true", help="default workload: skip the brief runs of the other configurations")
     ap.add_argument("--small", action="store_true", help="2 layers x batch 2 (smoke-sized case)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling-sized runs)")
@@ -732,6 +739,8 @@ def main():
                     help="view ranges (streams) the host-buffer call overlaps its copies and kernels over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global PERSISTENT
+    PERSISTENT = None if args.persistent is None else bool(args.persistent)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -185,6 +185,23 @@ int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const void* q, i
                      float* partials, int32_t* unit_counters, float* out, float* out_record,
                      int32_t* status, void* stream);
 
+/* Persistent form of rdkv_decode_attn (same arguments and results): one resident CTA per slot
+ * of the GPU goes through the launch's work items (whole units first, then chunks) in steps of the
+ * grid size, its staging warp running ahead across item boundaries, so that the start-up round
+ * trips and the pipeline drain are paid once per CTA instead of once per (view, KV head).
+ * Requirements beyond rdkv_decode_attn's: a prepared table (unit_recs, k_slots) in which every
+ * unit's byte ranges lie on whole 16-byte blocks (flag bit 0 of its record; a unit without it is
+ * reported through status bit 2 and left empty), no mask in the views, q 16-byte aligned, and
+ * work_counters: int32 [2], zero before the first launch (the CTAs draw their items from it and
+ * the last one to finish puts it back to zero; launches that share it must not overlap). */
+int rdkv_decode_attn_persistent(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,
+                                int H_q, int H_kv, int chunk_rows, int n_chunks, int n_whole_units,
+                                int row_begin, int row_end, int seq_part, int seq_parts,
+                                int k_row_bytes_max, const void* unit_recs, const void* k_slots,
+                                int nkb_max, float* partials, int32_t* unit_counters,
+                                int32_t* work_counters, float* out, float* out_record, int32_t* status,
+                                void* stream);
+
 /* Prepared table of a set of views (new; the reference re-derives the same per-head quantities
  * in Python before every kernel call, obkv_accel/triton_k_kernel.py:1236-1285).  Per (view, KV
  * head): the head's V row counts (n2, n4, n8, n16), where the rows of each V phase start in every

@@ -87,6 +87,7 @@ _PROTOTYPES = {
     "rdkv_decode_prepared_bytes": ([_i64, _i, _i], _i64),
     "rdkv_decode_prepare": ([_p, _i, _i, _i, _p, _p, _p], _i),
     "rdkv_decode_attn": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p], _i),
+    "rdkv_decode_attn_persistent": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p], _i),
     "rdkv_tail_attn_partial": ([_p, _i, _i64, _i, _i, _p, _p, _i, _i64, _i64, _i64, _i, _p, _p, _p], _i),
     "rdkv_lse_combine": ([_p, _i64, _i, _i64, _i64, _p, _p, _p, _p], _i),
     "rdkv_partition_by_bits": ([_p, _i, _i64, _i, _i, _i, _p, _p, _p], _i),

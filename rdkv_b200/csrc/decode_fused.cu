@@ -379,6 +379,13 @@ __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const u
 // warp and head m, l and the zero-point term in `ml` [FW][GH][3]) become the CTA's result.  Kept
 // out of line so that its registers do not weigh on the main loop.  how: 0 = (m, l, o) record,
 // 1 = normalised output, 2 = plain sum (weights were given).
+// (COMPUTE_ONLY: called by the compute warps alone — their named barrier instead of __syncthreads.)
+template <bool COMPUTE_ONLY>
+__device__ __forceinline__ void epi_sync() {
+  if (COMPUTE_ONLY) bar_sync(1 + FSTAGES, FW * 32); else __syncthreads();
+}
+
+template <bool COMPUTE_ONLY>
 __device__ __noinline__ void final_merge(const float* red, const float* ml, float (*fin)[FW + 3], int gcnt, int how,
                                          float* out_rows, float* rec0, int64_t rec_stride) {
   const int tid = threadIdx.x;
@@ -397,7 +404,7 @@ __device__ __noinline__ void final_merge(const float* red, const float* ml, floa
     }
     fin[hq][FW] = M; fin[hq][FW + 1] = L; fin[hq][FW + 2] = Z;
   }
-  __syncthreads();
+  epi_sync<COMPUTE_ONLY>();
   if (tid < D) {                                           // thread = channel; heads in turn
     const int d = tid;
     for (int hq = 0; hq < gcnt; ++hq) {
@@ -429,18 +436,19 @@ __device__ __noinline__ void final_merge(const float* red, const float* ml, floa
 // Nobody waits for anybody.  (Measured against a variant in which the CTA of the last chunk
 // polls the counter and the others leave without reading it: no difference.)
 // row0: index of the unit's first query head among all (view, head) rows.
+template <bool COMPUTE_ONLY>
 __device__ __noinline__ void chunk_merge(const float* partials, int* counter, int n_chunks, int gcnt,
                                          int64_t row0, float* out, float* merged) {
   __shared__ int s_last;
   const int tid = threadIdx.x;
-  __syncthreads();                                         // the CTA's record stores are ordered before thread 0's fence
+  epi_sync<COMPUTE_ONLY>();                                         // the CTA's record stores are ordered before thread 0's fence
   if (tid == 0) {
     __threadfence();
     const int old = atomicAdd(counter, 1);
     s_last = old == n_chunks - 1;
     if (s_last) { *counter = 0; __threadfence(); }         // acquire side: the other CTAs' records
   }
-  __syncthreads();
+  epi_sync<COMPUTE_ONLY>();
   if (!s_last) return;
   // thread = (query head slot, channel quarter): every load of the unit's records is in flight at once
   for (int base_hq = 0; base_hq < gcnt; base_hq += 4) {
@@ -842,8 +850,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       }
     }
     if (MODE == MODE_ATTN && n_chunks > 1 && unit_ctr != nullptr)
-      chunk_merge(partials, unit_ctr + unit_y, n_chunks, gcnt,
-                  (int64_t)view_idx * H_q + hq0, out, merged);
+      chunk_merge<false>(partials, unit_ctr + unit_y, n_chunks, gcnt,
+                         (int64_t)view_idx * H_q + hq0, out, merged);
     return;
   }
 
@@ -950,38 +958,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   // Score product orientation: rows on M (16 per MMA), query heads on N.  Thread (r, j)
   // then holds scores of rows g16+r and g16+r+8 for heads 2j and 2j+1 — the same two
   // heads whose output columns it accumulates in the P.V product.
-  const bool he_ok = 2 * j < gcnt, ho_ok = 2 * j + 1 < gcnt;
-  // scores are kept in base-2 units (natural units when they are the result)
-  const float c1 = MODE == MODE_SCORES ? TWO24 * INV_SQRT_D : TWO24 * INV_SQRT_D * LOG2E;
-  // an absent head gets an infinite bias: its scores are -inf without further tests
-  const float bsc = MODE == MODE_SCORES ? INV_SQRT_D : INV_SQRT_D * LOG2E;
-  auto bias_of = [&](int hq) {                             // zero-point bias of a query head: the warps' partial sums
-    float b = 0.f;
-#pragma unroll
-    for (int w = 0; w < FW; ++w) b += s_ml[w][hq][0];
-    return b;
-  };
-  const float b1e = (he_ok && MODE != MODE_WEIGHTS && warp < FW) ? bias_of(2 * j) * bsc : INFINITY;
-  const float b1o = (ho_ok && MODE != MODE_WEIGHTS && warp < FW) ? bias_of(2 * j + 1) * bsc : INFINITY;
-  const bool has_mask = v.mask != nullptr;
-  const bool k_aligned = !(kd.sub2 & 1) && !(kd.sub4 & 3) && !(kd.n8 & 3);
-  const bool k_simple = kd.nsp2 == 1 && kd.nsp4 == 1 && kd.nkb8 == 1;   // one span per segment: straight-line code
-  const uint32_t qs_lane = qs_base + 8 * lane;
-
-  float acc[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  // reference maxima of heads 2j, 2j+1 (same in every r); given weights are used as they are
-  float m_e = MODE == MODE_ATTN ? M_NONE : 0.f, m_o = m_e;
-  // Scores are formed relative to the reference maximum: s = acc*c1 - cb with cb = bias + m (a head
-  // that has no reference yet counts from 0 and moves it at its first finite score: thr = -1e29).
-  float cb_e = b1e, cb_o = b1o;
-  float thr_e = MODE == MODE_ATTN ? -1.0e29f : INFINITY, thr_o = thr_e;
-  float l_e = 0.f, l_o = 0.f;                              // partial sums over this thread's rows
-  // zero-point term sum_t p*scale*zp of heads 2j, 2j+1 ([0], [1]; complete in every lane): an extra
-  // m-tile of the P.V product whose A rows all hold the rows' zero points
-  float zacc[4] = {0.f, 0.f, 0.f, 0.f};
-  int cur_phase = -1;
+#include "decode_state.inc"
 
 #pragma unroll 1
   for (int it = 0; warp < FW && it < total_tiles; ++it) {
@@ -1004,321 +981,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     const int nblocks = (t.n + 31) >> 5;
     const int pb = (warp + FW - (it * (TILE_MAX / 128)) % FW) % FW;
 
-    if (pb < nblocks) {
-      if (p != cur_phase) {                                // change of accumulator units (powers of two)
-        if (cur_phase >= 0) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float f = pow2i(acc_exp(cur_phase, i & 3) - acc_exp(p, i & 3));
-            acc[i][0] *= f; acc[i][1] *= f; acc[i][2] *= f; acc[i][3] *= f;
-          }
-        }
-        cur_phase = p;
-      }
-      const uint32_t sbu = smem0 + stage * stage_bytes;
-      // low address bits of the sources = byte offsets of the tile's first row inside its stage area
-      const uint32_t off_k2 = t.offs & 15u, off_k4 = (t.offs >> 4) & 15u, off_k8 = (t.offs >> 8) & 15u;
-      const uint32_t off_v = (t.offs >> 12) & 15u, off_m = (t.offs >> 16) & 15u, off_z = (t.offs >> 20) & 15u;
-      const bool kfast = k_aligned && !(off_k2 & 1) && !(off_k4 & 3) && !(off_k8 & 3);
-      const bool simple = k_simple && kfast;
-      const int row_b = pb * 32;                           // first row of this warp inside the tile
-      // cursors (shared-window addresses): K row r of the block, scale/zp row r
-      uint32_t k2a = sbu + SL.k2 + off_k2 + (row_b + r) * kd.sub2 + 2 * j;
-      uint32_t k4a = sbu + SL.k4 + off_k4 + (row_b + r) * kd.sub4 + 4 * j;
-      uint32_t k8a = sbu + SL.k8 + off_k8 + (row_b + r) * kd.n8 + 4 * j;
-      // V scale / zero point of rows 2j, 2j+1 of the block as one fp16 pair (the rows a thread
-      // holds after the transpose); a tile whose first row sits at an odd fp16 position takes
-      // the two-load form
-      uint32_t sca = sbu + SL.sc + off_m + 2 * (row_b + 2 * j);
-      uint32_t zpa = sbu + SL.zp + off_z + 2 * (row_b + 2 * j);
-      const bool m_al = !((off_m | off_z) & 2u);
-      const uint32_t v0a = sbu + SL.v + off_v;
-      const int tn = t.n;
-      const uint32_t d2 = 8 * kd.sub2, d4 = 8 * kd.sub4, d8 = 8 * kd.n8;   // 8 rows further in each K stream
-
-      // The block loop, specialised per V phase.  A block is rows [g32, g32+32): thread (r, j) scores
-      // rows g32 + r + {0, 8, 16, 24} for heads 2j, 2j+1 (groups A: +0/+8, B: +16/+24).
-      auto run_tile = [&](auto PC, auto SC) {
-        constexpr int P = decltype(PC)::value;
-        constexpr bool SIMPLE = decltype(SC)::value;       // one span per K segment, aligned rows: straight-line score code
-        constexpr int VRB = phase_row_bytes(P);
-        uint32_t va = v0a + (P == 3 ? 8 : 4) * r + (row_b + 2 * j) * VRB;
-
-        // scores of one 16-row group whose row r sits at (a2, a4, a8)
-        auto k_group = [&](uint32_t a2, uint32_t a4, uint32_t a8, float (&sx)[4], float (&sy)[4], const uint2& q0,
-                           const uint2& q1, const uint2& q2, const uint2& q3, const uint2& q4) {
-          if (SIMPLE) {
-            const uint32_t w2A = lds16(a2), w2B = lds16(a2 + d2);
-            const uint32_t w4A = lds32(a4), w4B = lds32(a4 + d4);
-            const uint32_t w8A = lds32(a8), w8B = lds32(a8 + d8);
-            const uint32_t yA = prmt(w2A, 0u, 0x4140), yB = prmt(w2B, 0u, 0x4140);   // byte0 -> bits 0..7, byte1 -> 16..23
-            mma16816_z(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, q0.x, q0.y);
-            mma16816_z(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, q1.x, q1.y);
-            const uint32_t vA = w4A >> 8, vB = w4B >> 8;
-            mma16816(sx, w4A & 0x000F000Fu, w4B & 0x000F000Fu, w4A & 0x00F000F0u, w4B & 0x00F000F0u, q2.x, q2.y);
-            mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, q3.x, q3.y);
-            mma16816(sx, w8A & 0x00FF00FFu, w8B & 0x00FF00FFu, prmt(w8A, 0u, 0x4341), prmt(w8B, 0u, 0x4341), q4.x, q4.y);
-          } else {
-            sx[0] = sx[1] = sx[2] = sx[3] = 0.f; sy[0] = sy[1] = sy[2] = sy[3] = 0.f;
-            uint32_t qa = qs_lane;
-#pragma unroll 1
-            for (int s = 0; s < kd.nsp2; ++s, qa += 512) {
-              const uint2 p0 = lds64<0>(qa), p1 = lds64<256>(qa);
-              const uint32_t wA = kfast ? lds16(a2 + 8 * s) : lds32_unaligned(a2 + 8 * s);
-              const uint32_t wB = kfast ? lds16(a2 + d2 + 8 * s) : lds32_unaligned(a2 + d2 + 8 * s);
-              const uint32_t yA = prmt(wA, 0u, 0x4140), yB = prmt(wB, 0u, 0x4140);
-              mma16816(sx, yA & 0x00030003u, yB & 0x00030003u, yA & 0x000C000Cu, yB & 0x000C000Cu, p0.x, p0.y);
-              mma16816(sy, yA & 0x00300030u, yB & 0x00300030u, yA & 0x00C000C0u, yB & 0x00C000C0u, p1.x, p1.y);
-            }
-#pragma unroll 1
-            for (int s = 0; s < kd.nsp4; ++s, qa += 512) {
-              const uint2 p0 = lds64<0>(qa), p1 = lds64<256>(qa);
-              const uint32_t wA = kfast ? lds32(a4 + 16 * s) : lds32_unaligned(a4 + 16 * s);
-              const uint32_t wB = kfast ? lds32(a4 + d4 + 16 * s) : lds32_unaligned(a4 + d4 + 16 * s);
-              const uint32_t vA = wA >> 8, vB = wB >> 8;
-              mma16816(sx, wA & 0x000F000Fu, wB & 0x000F000Fu, wA & 0x00F000F0u, wB & 0x00F000F0u, p0.x, p0.y);
-              mma16816(sy, vA & 0x000F000Fu, vB & 0x000F000Fu, vA & 0x00F000F0u, vB & 0x00F000F0u, p1.x, p1.y);
-            }
-#pragma unroll 1
-            for (int b = 0; b < kd.nkb8; ++b, qa += 256) {
-              const uint2 p0 = lds64<0>(qa);
-              const uint32_t wA = kfast ? lds32(a8 + 16 * b) : lds32_unaligned(a8 + 16 * b);
-              const uint32_t wB = kfast ? lds32(a8 + d8 + 16 * b) : lds32_unaligned(a8 + d8 + 16 * b);
-              mma16816(sx, wA & 0x00FF00FFu, wB & 0x00FF00FFu, prmt(wA, 0u, 0x4341), prmt(wB, 0u, 0x4341), p0.x, p0.y);
-            }
-          }
-        };
-
-        // P.V of one 16-row group: channels on M, rows on K; this thread supplies rows {2j, 2j+1, 8+2j, 9+2j}
-        // of the group whose rows start at shared address `vg`.  (w0..w3: the first words, already loaded;
-        // the words of part vv+1 are requested before part vv is worked on.)
-        auto pv_group = [&](uint32_t vg, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t x0, uint32_t x1,
-                            uint32_t x2, uint32_t x3, uint32_t pb0, uint32_t pb1) {
-          if (P == 2) {
-#pragma unroll
-            for (int vv = 0; vv < 4; ++vv) {
-              uint32_t n0 = 0, n1 = 0, n2 = 0, n3 = 0;
-              if (vv < 3) {
-                n0 = lds32(vg + 32 * (vv + 1)); n1 = lds32(vg + 32 * (vv + 1) + 128);
-                n2 = lds32(vg + 32 * (vv + 1) + 8 * 128); n3 = lds32(vg + 32 * (vv + 1) + 9 * 128);
-              }
-#pragma unroll
-              for (int qq = 0; qq < 2; ++qq) {
-                const uint32_t sel = qq ? 0x7632u : 0x5410u;
-                const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
-                mma16816(acc[4 * qq + vv], y01 & 0x00FF00FFu, prmt(y01, 0u, 0x4341), y23 & 0x00FF00FFu,
-                         prmt(y23, 0u, 0x4341), pb0, pb1);
-              }
-              w0 = n0; w1 = n1; w2 = n2; w3 = n3;
-            }
-          } else if (P == 1) {
-#pragma unroll
-            for (int vl = 0; vl < 2; ++vl) {
-              uint32_t n0 = 0, n1 = 0, n2 = 0, n3 = 0;
-              if (vl < 1) {
-                n0 = lds32(vg + 32); n1 = lds32(vg + 32 + 64); n2 = lds32(vg + 32 + 8 * 64); n3 = lds32(vg + 32 + 9 * 64);
-              }
-#pragma unroll
-              for (int qq = 0; qq < 2; ++qq) {
-                const uint32_t sel = qq ? 0x7632u : 0x5410u;
-                const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
-                const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
-                mma16816(acc[4 * qq + vl], y01 & 0x000F000Fu, z01 & 0x000F000Fu, y23 & 0x000F000Fu, z23 & 0x000F000Fu,
-                         pb0, pb1);
-                mma16816(acc[4 * qq + vl + 2], y01 & 0x00F000F0u, z01 & 0x00F000F0u, y23 & 0x00F000F0u,
-                         z23 & 0x00F000F0u, pb0, pb1);
-              }
-              w0 = n0; w1 = n1; w2 = n2; w3 = n3;
-            }
-          } else if (P == 0) {
-#pragma unroll
-            for (int qq = 0; qq < 2; ++qq) {
-              const uint32_t sel = qq ? 0x7632u : 0x5410u;
-              const uint32_t y01 = prmt(w0, w1, sel), y23 = prmt(w2, w3, sel);
-              const uint32_t z01 = y01 >> 8, z23 = y23 >> 8;
-#pragma unroll
-              for (int vv = 0; vv < 4; ++vv) {
-                const uint32_t mk = 0x00030003u << (2 * vv);
-                mma16816(acc[4 * qq + vv], y01 & mk, z01 & mk, y23 & mk, z23 & mk, pb0, pb1);
-              }
-            }
-          } else {                                         // fp16 rows: channel c at byte 2c
-#pragma unroll
-            for (int vv = 0; vv < 4; ++vv) {
-              uint2 a0 = make_uint2(0u, 0u), a1 = a0, a2 = a0, a3 = a0;
-              if (vv < 3) {
-                a0 = lds64(vg + 64 * (vv + 1)); a1 = lds64(vg + 64 * (vv + 1) + 256);
-                a2 = lds64(vg + 64 * (vv + 1) + 8 * 256); a3 = lds64(vg + 64 * (vv + 1) + 9 * 256);
-              }
-              mma16816(acc[vv], prmt(w0, w1, 0x5410), prmt(w0, w1, 0x7632), prmt(w2, w3, 0x5410),
-                       prmt(w2, w3, 0x7632), pb0, pb1);
-              mma16816(acc[4 + vv], prmt(x0, x1, 0x5410), prmt(x0, x1, 0x7632), prmt(x2, x3, 0x5410),
-                       prmt(x2, x3, 0x7632), pb0, pb1);
-              w0 = a0.x; w1 = a1.x; w2 = a2.x; w3 = a3.x; x0 = a0.y; x1 = a1.y; x2 = a2.y; x3 = a3.y;
-            }
-          }
-        };
-
-#pragma unroll 1
-        for (int g32 = row_b; g32 < nblocks * 32; g32 += 32 * FW) {
-          // ── scores: two independent groups, two MMA chains each ──
-          float sxA[4] = {0.f, 0.f, 0.f, 0.f}, syA[4] = {0.f, 0.f, 0.f, 0.f}, sxB[4] = {0.f, 0.f, 0.f, 0.f},
-                syB[4] = {0.f, 0.f, 0.f, 0.f};
-          if (MODE != MODE_WEIGHTS) {
-            uint2 q0 = make_uint2(0u, 0u), q1 = q0, q2 = q0, q3 = q0, q4 = q0;
-            if (SIMPLE) {
-              q0 = lds64<0>(qs_lane); q1 = lds64<256>(qs_lane); q2 = lds64<512>(qs_lane);
-              q3 = lds64<768>(qs_lane); q4 = lds64<1024>(qs_lane);
-            }
-            k_group(k2a, k4a, k8a, sxA, syA, q0, q1, q2, q3, q4);
-            k_group(k2a + 2 * d2, k4a + 2 * d4, k8a + 2 * d8, sxB, syB, q0, q1, q2, q3, q4);
-          }
-          // requested now, needed after the softmax: V scale / zero point of the four rows and the
-          // first V words of both groups
-          uint32_t rs[4] = {0u, 0u, 0u, 0u}, rz[4] = {0u, 0u, 0u, 0u};   // [k]: rows 8k + {2j, 2j+1}
-          if (P < 3 && MODE != MODE_SCORES) {
-            if (m_al) {
-              rs[0] = lds32(sca); rs[1] = lds32<16>(sca); rs[2] = lds32<32>(sca); rs[3] = lds32<48>(sca);
-              rz[0] = lds32(zpa); rz[1] = lds32<16>(zpa); rz[2] = lds32<32>(zpa); rz[3] = lds32<48>(zpa);
-            } else {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                rs[k] = lds32_unaligned(sca + 16 * k); rz[k] = lds32_unaligned(zpa + 16 * k);
-              }
-            }
-          }
-          uint32_t wA0 = 0, wA1 = 0, wA2 = 0, wA3 = 0, xA0 = 0, xA1 = 0, xA2 = 0, xA3 = 0;
-          uint32_t wB0 = 0, wB1 = 0, wB2 = 0, wB3 = 0, xB0 = 0, xB1 = 0, xB2 = 0, xB3 = 0;
-          if (MODE == MODE_SCORES) {
-          } else if (P == 3) {
-            const uint2 a0 = lds64(va), a1 = lds64<256>(va), a2 = lds64<8 * 256>(va), a3 = lds64<9 * 256>(va);
-            wA0 = a0.x; wA1 = a1.x; wA2 = a2.x; wA3 = a3.x; xA0 = a0.y; xA1 = a1.y; xA2 = a2.y; xA3 = a3.y;
-            const uint2 b0 = lds64<16 * 256>(va), b1 = lds64<17 * 256>(va), b2 = lds64<24 * 256>(va), b3 = lds64<25 * 256>(va);
-            wB0 = b0.x; wB1 = b1.x; wB2 = b2.x; wB3 = b3.x; xB0 = b0.y; xB1 = b1.y; xB2 = b2.y; xB3 = b3.y;
-          } else {
-            wA0 = lds32(va); wA1 = lds32<VRB>(va); wA2 = lds32<8 * VRB>(va); wA3 = lds32<9 * VRB>(va);
-            wB0 = lds32<16 * VRB>(va); wB1 = lds32<17 * VRB>(va); wB2 = lds32<24 * VRB>(va); wB3 = lds32<25 * VRB>(va);
-          }
-
-          // s2[k]: rows g32 + r + 8*(k>>1)... laid out [2k] head 2j, [2k+1] head 2j+1 for row slot k = 0..3
-          float s2[8];
-          s2[0] = fmaf(sxA[0] + syA[0], c1, -cb_e); s2[1] = fmaf(sxA[1] + syA[1], c1, -cb_o);
-          s2[2] = fmaf(sxA[2] + syA[2], c1, -cb_e); s2[3] = fmaf(sxA[3] + syA[3], c1, -cb_o);
-          s2[4] = fmaf(sxB[0] + syB[0], c1, -cb_e); s2[5] = fmaf(sxB[1] + syB[1], c1, -cb_o);
-          s2[6] = fmaf(sxB[2] + syB[2], c1, -cb_e); s2[7] = fmaf(sxB[3] + syB[3], c1, -cb_o);
-          if (MODE == MODE_SCORES) {                       // the scores are the result
-            const int64_t col0 = (int64_t)s_tile[stage].krow0 + g32 + r;    // stripe row = output column
-            float* oe = aux + (int64_t)(hq0 + 2 * j) * aux_stride + col0;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              if (g32 + r + 8 * k < tn && col0 + 8 * k < t_eff) {
-                if (he_ok) oe[8 * k] = s2[2 * k];
-                if (ho_ok) oe[aux_stride + 8 * k] = s2[2 * k + 1];
-              }
-            }
-            k2a += 4 * FW * d2; k4a += 4 * FW * d4; k8a += 4 * FW * d8;
-            continue;
-          }
-          if (MODE == MODE_WEIGHTS) {                      // the weights are given
-            const int64_t col0 = (int64_t)s_tile[stage].krow0 + g32 + r;
-            const float* we = aux + (int64_t)(hq0 + 2 * j) * aux_stride + col0;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const bool ok = g32 + r + 8 * k < tn;
-              s2[2 * k] = (ok && he_ok) ? we[8 * k] : 0.f;
-              s2[2 * k + 1] = (ok && ho_ok) ? we[aux_stride + 8 * k] : 0.f;
-            }
-          }
-          if (MODE == MODE_ATTN && has_mask) {                                  // additive softmax mask (rarely given: everything it needs is re-read here)
-            const int64_t ca = (int64_t)s_tile[stage].krow0 + g32 + r;   // stripe row = mask column
-            const float* mask_e = v.mask + (int64_t)(hq0 + 2 * j) * v.mask_row_stride;
-            const float* mask_o = mask_e + v.mask_row_stride;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              if (g32 + r + 8 * k < tn) {
-                if (he_ok) s2[2 * k] += mask_e[ca + 8 * k] * LOG2E;
-                if (ho_ok) s2[2 * k + 1] += mask_o[ca + 8 * k] * LOG2E;
-              }
-            }
-          }
-          if (MODE != MODE_SCORES && g32 + 32 > tn) {      // last, partial block of the tile: rows past its end are dead
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              if (MODE == MODE_ATTN && g32 + r + 8 * k >= tn) { s2[2 * k] = -INFINITY; s2[2 * k + 1] = -INFINITY; }
-              // (their scale / zero-point bytes may be anything: clear the halves of dead rows)
-              const int row = g32 + 8 * k + 2 * j;
-              const uint32_t keep = row + 1 < tn ? 0xFFFFFFFFu : row < tn ? 0x0000FFFFu : 0u;
-              rs[k] &= keep; rz[k] &= keep;
-            }
-          }
-          // lazy reference maximum: exact maxima are only worked out when some score of the warp
-          // exceeds its head's reference by more than RESCALE_TH (or is the head's first finite one)
-          const float mxe = fmaxf(fmaxf(s2[0], s2[2]), fmaxf(s2[4], s2[6]));
-          const float mxo = fmaxf(fmaxf(s2[1], s2[3]), fmaxf(s2[5], s2[7]));
-          if (MODE == MODE_ATTN && __any_sync(0xffffffffu, mxe > thr_e || mxo > thr_o)) {
-            float me = mxe, mo = mxo;
-#pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
-              me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
-              mo = fmaxf(mo, __shfl_xor_sync(0xffffffffu, mo, o));
-            }
-            // (scores are relative to the reference in use: 0 for a head without one)
-            const float ue = m_e <= M_NONE ? 0.f : m_e, uo = m_o <= M_NONE ? 0.f : m_o;
-            const float ne = fmaxf(m_e, me + ue), no = fmaxf(m_o, mo + uo);
-            const float ae = ex2(m_e - ne), ao = ex2(m_o - no);
-            l_e *= ae; zacc[0] *= ae; l_o *= ao; zacc[1] *= ao;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { acc[i][0] *= ae; acc[i][1] *= ao; acc[i][2] *= ae; acc[i][3] *= ao; }
-            const float we = ne <= M_NONE ? 0.f : ne, wo = no <= M_NONE ? 0.f : no;
-            const float de = we - ue, dd = wo - uo;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) { s2[2 * k] -= de; s2[2 * k + 1] -= dd; }
-            m_e = ne; m_o = no;
-            cb_e = b1e + we; cb_o = b1o + wo;
-            thr_e = ne <= M_NONE ? -1.0e29f : RESCALE_TH; thr_o = no <= M_NONE ? -1.0e29f : RESCALE_TH;
-          }
-          float pe[8];
-          if (MODE == MODE_WEIGHTS) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) pe[k] = s2[k];
-          } else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) pe[k] = ex2(s2[k]);
-            l_e += (pe[0] + pe[2]) + (pe[4] + pe[6]); l_o += (pe[1] + pe[3]) + (pe[5] + pe[7]);
-          }
-          // row slot k x (head 2j, head 2j+1) as fp16 pairs, then 8x8 transposes: thread (r, j) now
-          // holds head r at rows {2j, 2j+1} and 8 + {2j, 2j+1} of each group
-          uint32_t pA0 = movmatrix_trans(pack_h2(pe[0], pe[1])), pA1 = movmatrix_trans(pack_h2(pe[2], pe[3]));
-          uint32_t pB0 = movmatrix_trans(pack_h2(pe[4], pe[5])), pB1 = movmatrix_trans(pack_h2(pe[6], pe[7]));
-          if (P < 3) {
-            // per-row V scale, applied to the row pairs this thread now holds; the zero-point term
-            // takes the same (rounded) factors through the tensor core
-            pA0 = hmul2(pA0, rs[0]); pA1 = hmul2(pA1, rs[1]); pB0 = hmul2(pB0, rs[2]); pB1 = hmul2(pB1, rs[3]);
-            mma16816(zacc, rz[0], 0u, rz[1], 0u, pA0, pA1);
-            mma16816(zacc, rz[2], 0u, rz[3], 0u, pB0, pB1);
-          }
-
-          pv_group(va, wA0, wA1, wA2, wA3, xA0, xA1, xA2, xA3, pA0, pA1);
-          pv_group(va + 16 * VRB, wB0, wB1, wB2, wB3, xB0, xB1, xB2, xB3, pB0, pB1);
-
-          k2a += 4 * FW * d2; k4a += 4 * FW * d4; k8a += 4 * FW * d8;
-          sca += 64 * FW; zpa += 64 * FW;
-          va += 32 * FW * VRB;
-        }
-      };
-      using std::integral_constant;
-      if (simple) {
-        if (p == 0) run_tile(integral_constant<int, 0>{}, std::true_type{});
-        else if (p == 1) run_tile(integral_constant<int, 1>{}, std::true_type{});
-        else if (p == 2) run_tile(integral_constant<int, 2>{}, std::true_type{});
-        else run_tile(integral_constant<int, 3>{}, std::true_type{});
-      } else {
-        if (p == 0) run_tile(integral_constant<int, 0>{}, std::false_type{});
-        else if (p == 1) run_tile(integral_constant<int, 1>{}, std::false_type{});
-        else if (p == 2) run_tile(integral_constant<int, 2>{}, std::false_type{});
-        else run_tile(integral_constant<int, 3>{}, std::false_type{});
-      }
-    }
+#include "decode_tile.inc"
     if (it + FSTAGES < total_tiles) bar_arrive(BAR_FREE + stage, CTA_THREADS);   // slot may be refilled
   }
 
@@ -1350,9 +1013,385 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   }
   __syncthreads();
   const EpiInfo ep = s_epi;
-  final_merge(red, &s_ml[0][0][0], s_fin, ep.gcnt, ep.how, ep.out_rows, ep.rec0, ep.rec_stride);
+  final_merge<false>(red, &s_ml[0][0][0], s_fin, ep.gcnt, ep.how, ep.out_rows, ep.rec0, ep.rec_stride);
   if (MODE == MODE_ATTN && ep.n_chunks > 1 && unit_ctr != nullptr)
-    chunk_merge(partials, unit_ctr + ep.unit_y, ep.n_chunks, ep.gcnt, ep.row0, out, merged);
+    chunk_merge<false>(partials, unit_ctr + ep.unit_y, ep.n_chunks, ep.gcnt, ep.row0, out, merged);
+}
+
+
+// ── persistent form ──────────────────────────────────────────────────────────
+// The same work with ONE resident CTA per slot that goes through work items item, item + grid, ...
+// (the item order of decode_fused_kernel: whole units first, then chunks).  The staging warp
+// runs ahead of the compute warps across item boundaries — while they merge an item and fold the
+// next item's queries, its first tiles are already on their way — so the round trips of a CTA's
+// start (unit record, first tile) and the drain of its pipeline are paid once per CTA, not once
+// per item.  Needs a prepared table whose units all lie on whole 16-byte blocks, no mask, 16-byte
+// aligned queries.
+//   * ring slots are handed back through mbarriers (s_empty: one arrival per compute warp), so the
+//     staging warp needs no knowledge of the compute warps' position; every wait is bounded;
+//   * an item's first tile brings the item's header along on the same mbarrier: its raw query rows
+//     and its K slot table (two header buffers, alternating), and the staging warp publishes the
+//     item's dimensions next to the tile's descriptor; an item without live rows gets an empty tile;
+//   * the compute warps merge in the ring slot of the item's last tile and hand that slot back only
+//     after the merge.
+//   * items are handed out dynamically: a CTA starts with item blockIdx.x and draws every further one
+//     from a counter in global memory (work[0]) when its staging warp has sent the current item's
+//     last tile — the compute warps are two tiles behind, which hides the round trip; the last CTA
+//     to run dry puts the counters (work[0], work[1]) back to zero for the next launch.
+struct ItemInfo { int n2p, n4p, n8c, total, item, pad0, pad1, pad2; };
+
+template <int MODE>
+__global__ void __launch_bounds__(CTA_THREADS, RDKV_MINB)
+decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, int chunk_rows, int k_chunks,
+                      int n_whole, int n_items, int stage_bytes, float* __restrict__ partials,
+                      float* __restrict__ out, int* __restrict__ status, const UnitRec* __restrict__ unit_recs,
+                      const KSlotRec* __restrict__ kslots, int nkb_max, int* __restrict__ unit_ctr,
+                      float* __restrict__ merged, int row_begin, int row_end, int part, int parts,
+                      int* __restrict__ work) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ CtaGeom G;                            // private to the staging warp
+  __shared__ float s_ml[FW][GH][3];
+  __shared__ float s_fin[GH][FW + 3];
+  __shared__ EpiInfo s_epi;
+  __shared__ TileInfo s_tile[FSTAGES];
+  __shared__ ItemInfo s_item[2];
+  __shared__ TilePlan s_plan[PLAN_TILES];
+  __shared__ __align__(8) uint64_t s_full[FSTAGES];    // tile in slot s has landed
+  __shared__ __align__(8) uint64_t s_empty[FSTAGES];   // the compute warps are done with slot s
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, j = lane & 3;
+  const int n_hgrp = (g + GH - 1) / GH;
+  const int hy = (H_q / g) * n_hgrp;
+  const uint32_t smem0 = smem_u32(smem_raw);
+  const uint32_t qs_base = smem0 + FSTAGES * stage_bytes;  // uint2 qsA[nkb][32]
+  unsigned char* tail = smem_raw + (size_t)FSTAGES * stage_bytes;
+  uint2* qsA = reinterpret_cast<uint2*>(tail);
+  const int q_elt = q_dtype == RDKV_F32 ? 4 : 2;
+  const int hdr_q_bytes = GH * D * q_elt;                  // raw query rows of an item
+  const int hdr_bytes = hdr_q_bytes + nkb_max * 32 * (int)sizeof(KSlotRec);
+  unsigned char* hdr0 = tail + nkb_max * 256;
+  constexpr int BAR_COMPUTE = 1 + FSTAGES;
+  const struct { const float* mask; int64_t mask_row_stride; } v = {nullptr, 0};   // (no mask in this form)
+  float* const aux = nullptr;
+  const int64_t aux_stride = 0;
+  const int t_eff = 0;
+
+  if (warp == FW) {
+    if (lane < FSTAGES) { mbar_init(&s_full[lane], 64); mbar_init(&s_empty[lane], FW); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  int git = 0;                                             // tiles this CTA has been through (empty items count one)
+  int li = 0;                                              // items this CTA has been through
+  int item = blockIdx.x;                                   // staging warp: the item in hand; compute warps: as told with its first tile
+#pragma unroll 1
+  for (;; ++li) {
+    int next_item = 0;
+    if (warp == FW) {
+      if (item >= n_items) {                               // nothing left: tell the compute warps (an empty tile without an item) and leave
+        const int stage = git % FSTAGES;
+        if (git >= FSTAGES) {
+          const uint32_t parity = ((git / FSTAGES) - 1) & 1;
+          unsigned spins = 0;
+          while (!mbar_try_wait(&s_empty[stage], parity)) {
+            if (++spins > WAIT_LIMIT) {
+              if (lane == 0 && status != nullptr) atomicOr(status, 1);
+              break;
+            }
+          }
+        }
+        if (lane == 0) {
+          s_tile[stage] = TileInfo{0, 0, 0u, 0};
+          s_item[li & 1] = ItemInfo{0, 0, 0, 0, -1, 0, 0, 0};
+          const int done = atomicAdd(work + 1, 1);         // the last CTA to run dry resets the counters
+          if (done == (int)gridDim.x - 1) { work[0] = 0; work[1] = 0; }
+        }
+        mbar_arrive_on_copies(&s_full[stage]);
+        mbar_arrive(&s_full[stage]);
+        break;
+      }
+    } else {
+      // compute warps: the item comes with its first tile
+      const int st = git % FSTAGES;
+      const uint32_t parity = (git / FSTAGES) & 1;
+      unsigned spins = 0;
+      while (!mbar_try_wait(&s_full[st], parity)) {
+        if (++spins > WAIT_LIMIT) {
+          if (lane == 0 && status != nullptr) atomicOr(status, 1);
+          break;
+        }
+      }
+      item = s_item[li & 1].item;
+      if (item < 0 || item >= n_items) break;
+    }
+    int unit_y, chunk, n_chunks;
+    if (item < n_whole) {
+      unit_y = item; chunk = 0; n_chunks = 1;
+    } else {
+      const int jj = item - n_whole;
+      unit_y = n_whole + jj / k_chunks; chunk = jj % k_chunks; n_chunks = k_chunks;
+    }
+    const int view_idx = unit_y / hy;
+    const int h = (unit_y % hy) / n_hgrp, hgrp = (unit_y % hy) % n_hgrp;
+    const int gh0 = hgrp * GH, gcnt = min(GH, g - gh0);
+    const int hq0 = h * g + gh0;
+    const int64_t unit = (int64_t)view_idx * (H_q / g) + h;
+    unsigned char* hdr = hdr0 + (li & 1) * hdr_bytes;
+
+    if (warp == FW) {
+      // ── staging warp: geometry of the item from its unit record, then its tiles ──
+      const int4* up = reinterpret_cast<const int4*>(unit_recs + unit);
+      const int p = lane & 3;
+      const int4 h1 = ldg_keep4(up + 1), h2 = ldg_keep4(up + 2);
+      const int4 a0 = ldg_keep4(up + 3 + 4 * p), a1 = ldg_keep4(up + 4 + 4 * p), a2 = ldg_keep4(up + 5 + 4 * p),
+                 a3 = ldg_keep4(up + 6 + 4 * p);
+      const int n2p = h1.z, n4p = h1.w, n8c = h2.x;
+      const KDims kd = k_dims(n2p, n4p, n8c);
+      const StageLayout SL = stage_layout(kd.sub2, kd.sub4, kd.n8);
+      const bool fits = (h1.x & 1) && SL.total <= stage_bytes && kd.n2p + kd.n4p + kd.n8 > 0 &&
+                        kd.n2p + kd.n4p + kd.n8 <= DPAD_MAX && kd.nkb <= KB_MAX && kd.nkb <= nkb_max;
+      const int c0 = row_begin + chunk * chunk_rows, c1 = n_chunks == 1 ? row_end : min(c0 + chunk_rows, row_end);
+      const int np = a0.y - a0.x, ps = part_cut(np, part, parts), pn = part_cut(np, part + 1, parts) - ps;
+      const int pn0 = __shfl_sync(0xffffffffu, pn, 0), pn1 = __shfl_sync(0xffffffffu, pn, 1);
+      const int pn2 = __shfl_sync(0xffffffffu, pn, 2);
+      const int lb = (p > 0 ? pn0 : 0) + (p > 1 ? pn1 : 0) + (p > 2 ? pn2 : 0);
+      const int lo = max(lb, c0), hi = max(lo, min(lb + pn, c1));
+      const int n = hi - lo, d = ps + (lo - lb);
+      const int ntile = p == 0   ? (n + phase_tile_rows(0) - 1) / phase_tile_rows(0)
+                        : p == 1 ? (n + phase_tile_rows(1) - 1) / phase_tile_rows(1)
+                        : p == 2 ? (n + phase_tile_rows(2) - 1) / phase_tile_rows(2)
+                                 : (n + phase_tile_rows(3) - 1) / phase_tile_rows(3);
+      auto ptr_of = [](int x, int y) {
+        return reinterpret_cast<const unsigned char*>((uintptr_t)(uint32_t)x | ((uintptr_t)(uint32_t)y << 32));
+      };
+      const int t0 = __shfl_sync(0xffffffffu, ntile, 0), t1 = __shfl_sync(0xffffffffu, ntile, 1);
+      const int t2 = __shfl_sync(0xffffffffu, ntile, 2), t3 = __shfl_sync(0xffffffffu, ntile, 3);
+      __syncwarp();                                        // (the plan of the previous item has been read)
+      if (lane < 4) {
+        G.lo[p] = lo; G.hi[p] = hi;
+        G.first_tile[p] = p == 0 ? 0 : p == 1 ? t0 : p == 2 ? t0 + t1 : t0 + t1 + t2;
+        G.krow[p] = p < 3 ? (int64_t)a0.x + d : (int64_t)h2.y + d;
+        G.k2[p] = ptr_of(a1.x, a1.y) + (int64_t)d * kd.sub2;
+        G.k4[p] = ptr_of(a1.z, a1.w) + (int64_t)d * kd.sub4;
+        G.k8[p] = ptr_of(a2.x, a2.y) + (int64_t)d * kd.n8;
+        G.vrow[p] = ptr_of(a2.z, a2.w) + (int64_t)d * phase_row_bytes(p);
+        if (p < 3) { G.sc[p] = ptr_of(a3.x, a3.y) + 2 * d; G.zp[p] = ptr_of(a3.z, a3.w) + 2 * d; }
+      }
+      __syncwarp();
+      const int total = fits ? t0 + t1 + t2 + t3 : 0;
+      if (!fits && lane == 0 && status != nullptr) atomicOr(status, 2);
+      const int n_it = max(total, 1);
+      const uint64_t pol_stream = l2_policy_stream();
+#pragma unroll 1
+      for (int it = 0; it < n_it; ++it) {
+        const int slot = it % PLAN_TILES;
+        if (slot == 0) {                                   // plan tiles [it, it + 32)
+          __syncwarp();
+          if (it + lane < total) {
+            const TileDesc t = tile_of(G, it + lane);
+            const int tp = t.phase;
+            TilePlan& P = s_plan[lane];
+            const unsigned char* a_k2 = G.k2[tp] + (int64_t)t.row0 * kd.sub2;
+            const unsigned char* a_k4 = G.k4[tp] + (int64_t)t.row0 * kd.sub4;
+            const unsigned char* a_k8 = G.k8[tp] + (int64_t)t.row0 * kd.n8;
+            const unsigned char* a_v = G.vrow[tp] + (int64_t)t.row0 * phase_row_bytes(tp);
+            const unsigned char* a_sc = G.sc[tp < 3 ? tp : 0] + t.row0 * 2;
+            const unsigned char* a_zp = G.zp[tp < 3 ? tp : 0] + t.row0 * 2;
+            P.rg[0] = RangePlan{a_v, t.n * phase_row_bytes(tp), (uint32_t)SL.v};
+            P.rg[1] = RangePlan{a_k2, t.n * kd.sub2, (uint32_t)SL.k2};
+            P.rg[2] = RangePlan{a_k4, t.n * kd.sub4, (uint32_t)SL.k4};
+            P.rg[3] = RangePlan{a_k8, t.n * kd.n8, (uint32_t)SL.k8};
+            P.rg[4] = RangePlan{a_sc, tp < 3 ? t.n * 2 : 0, (uint32_t)SL.sc};
+            P.rg[5] = RangePlan{a_zp, tp < 3 ? t.n * 2 : 0, (uint32_t)SL.zp};
+            auto low4 = [](const unsigned char* x) { return (uint32_t)reinterpret_cast<uintptr_t>(x) & 15u; };
+            int blocks_before = 0;
+#pragma unroll
+            for (int qq = 0; qq < 3; ++qq)
+              if (qq < tp) blocks_before += (G.hi[qq] - G.lo[qq] + 31) >> 5;
+            blocks_before += t.row0 >> 5;
+            P.info.phase = tp | (blocks_before & (FW - 1)) << 8; P.info.n = t.n;
+            P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 | low4(a_v) << 12 |
+                          (tp < 3 ? low4(a_sc) << 16 | low4(a_zp) << 20 : 0u);
+            P.info.krow0 = (int)(G.krow[tp] + t.row0);
+          }
+          __syncwarp();
+        }
+        const int gi = git + it, stage = gi % FSTAGES;
+        const uint32_t sbu = smem0 + stage * stage_bytes;
+        // lanes 0..5: the tile's six ranges; lanes 6, 7 with the item's first tile: its header
+        RangePlan rp = {nullptr, 0, 0u};
+        uint32_t dst = 0;
+        TileInfo ti = {0, 0, 0u, 0};
+        if (it < total) {
+          ti = s_plan[slot].info;
+          if (lane < 6) { rp = s_plan[slot].rg[lane]; dst = sbu + rp.dst_off; }
+        }
+        if (it == 0 && lane == 6) {
+          rp.src = reinterpret_cast<const unsigned char*>(q) + ((int64_t)view_idx * H_q + hq0) * D * q_elt;
+          rp.len = gcnt * D * q_elt; dst = smem_u32(hdr);
+        }
+        if (it == 0 && lane == 7) {
+          rp.src = reinterpret_cast<const unsigned char*>(kslots + unit * nkb_max * 32);
+          rp.len = nkb_max * 32 * (int)sizeof(KSlotRec); dst = smem_u32(hdr + hdr_q_bytes);
+        }
+        const uintptr_t a = reinterpret_cast<uintptr_t>(rp.src), al = a & ~(uintptr_t)15;
+        const uint32_t bytes = rp.len > 0 ? (uint32_t)(((a + rp.len + 15) & ~(uintptr_t)15) - al) : 0u;
+        uint32_t tx = bytes;
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
+        if (gi >= FSTAGES) {                               // wait (bounded) until the compute warps have left the slot
+          const uint32_t parity = ((gi / FSTAGES) - 1) & 1;
+          unsigned spins = 0;
+          while (!mbar_try_wait(&s_empty[stage], parity)) {
+            if (++spins > WAIT_LIMIT) {
+              if (lane == 0 && status != nullptr) atomicOr(status, 1);
+              break;
+            }
+          }
+        }
+        if (lane == 0) mbar_expect_tx(&s_full[stage], tx);
+        __syncwarp();
+        if (bytes) bulk_g2s_hint(dst, reinterpret_cast<const void*>(al), bytes, &s_full[stage], pol_stream);
+        if ((ti.phase & 3) == 3 && (ti.n & 31)) {          // fp16 phase: finite data past the tile's end
+          const int off = (int)((ti.offs >> 12) & 15u);
+          const int first = (off + ti.n * 256 + 15) & ~15;
+          const int last = min(off + ((ti.n + 31) & ~31) * 256, V_STAGE + 16);
+          unsigned char* sv = smem_raw + (size_t)stage * stage_bytes + SL.v;
+          for (int i = first + 4 * lane; i < last; i += 4 * 32) *reinterpret_cast<uint32_t*>(sv + i) = 0u;
+        }
+        if (lane == 0) {
+          s_tile[stage] = ti;
+          if (it == 0) s_item[li & 1] = ItemInfo{n2p, n4p, n8c, total, item, 0, 0, 0};
+        }
+        mbar_arrive_on_copies(&s_full[stage]);
+        mbar_arrive(&s_full[stage]);
+      }
+      git += n_it;
+      // the next item: drawn now, when this one's tiles are all on their way (the compute warps are
+      // still two tiles behind), so that whichever CTA gets through its items first takes the next
+      if (lane == 0) next_item = atomicAdd(work, 1) + (int)gridDim.x;
+      item = __shfl_sync(0xffffffffu, next_item, 0);
+    } else {
+      // ── compute warps ──
+      auto wait_tile = [&](int gi) {
+        const int st = gi % FSTAGES;
+        const uint32_t parity = (gi / FSTAGES) & 1;
+        unsigned spins = 0;
+        while (!mbar_try_wait(&s_full[st], parity)) {
+          if (++spins > WAIT_LIMIT) {
+            if (lane == 0 && status != nullptr) atomicOr(status, 1);
+            break;
+          }
+        }
+      };
+      const ItemInfo ii = s_item[li & 1];                  // (the item's first tile, and with it its header, has landed)
+      const int total_tiles = ii.total, n_it = max(total_tiles, 1);
+      const KDims kd = k_dims(ii.n2p, ii.n4p, ii.n8c);
+      const StageLayout SL = stage_layout(kd.sub2, kd.sub4, kd.n8);
+      {
+        const int n_chunks_ = n_chunks;
+        float* rec_base = (n_chunks_ > 1 || merged == nullptr) ? partials : merged;
+        if (tid == 0) {
+          s_epi.out_rows = out != nullptr ? out + ((int64_t)view_idx * H_q + hq0) * D : nullptr;
+          s_epi.rec0 = rec_base != nullptr
+                           ? rec_base + ((int64_t)(view_idx * H_q + hq0) * n_chunks_ + chunk) * RDKV_PARTIAL_STRIDE
+                           : nullptr;
+          s_epi.rec_stride = (int64_t)n_chunks_ * RDKV_PARTIAL_STRIDE;
+          s_epi.row0 = (int64_t)view_idx * H_q + hq0;
+          s_epi.how = (n_chunks_ == 1 && out != nullptr) ? 1 : 0;
+          s_epi.gcnt = gcnt; s_epi.n_chunks = n_chunks_; s_epi.unit_y = unit_y;
+        }
+      }
+      // fold the item's queries from its header: q*scale in MMA fragment order, zero-point bias
+      {
+        const KSlotRec* hk = reinterpret_cast<const KSlotRec*>(hdr + hdr_q_bytes);
+        const bool head_ok = r < gcnt;
+        const int qrow = (head_ok ? r : 0) * D;
+        auto qload = [&](uint32_t ch) -> float {
+          if (q_dtype == RDKV_F32) return reinterpret_cast<const float*>(hdr)[qrow + ch];
+          const uint16_t x = reinterpret_cast<const uint16_t*>(hdr)[qrow + ch];
+          return q_dtype == RDKV_BF16 ? __uint_as_float((uint32_t)x << 16) : h2f(x);
+        };
+        auto fold_block = [&](const KSlotRec& km, int kb, float& bias) {
+          const int ex2b = kb < 2 * kd.nsp2 ? 4 * (kb & 1) : 0;
+          const int exs = kb < 2 * kd.nsp2 ? 2 : kb < 2 * kd.nsp2 + 2 * kd.nsp4 ? 4 : 0;
+          float val[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int ex = ex2b + (e >> 1) * exs;
+            const float scv = h2f((uint16_t)((e < 2 ? km.sc01 : km.sc23) >> (16 * (e & 1))));
+            const float zpv = (float)((km.zp4 >> (8 * e)) & 255u);
+            float x = __half2float(__float2half_rn(qload((km.perm4 >> (8 * e)) & 127u) * scv * pow2i(-ex)));
+            if (!head_ok) x = 0.f;
+            bias += zpv * (x * pow2i(ex));
+            val[e] = x;
+          }
+          qsA[kb * 32 + lane] = make_uint2(pack_h2(val[0], val[1]), pack_h2(val[2], val[3]));
+        };
+        float b0 = 0.f, b1 = 0.f;
+        if (warp < kd.nkb) fold_block(hk[warp * 32 + lane], warp, b0);
+        if (warp + FW < kd.nkb) fold_block(hk[(warp + FW) * 32 + lane], warp + FW, b1);
+        float bias_part = b0 + b1;
+#pragma unroll 1
+        for (int kb = warp + 2 * FW; kb < kd.nkb; kb += FW) fold_block(hk[kb * 32 + lane], kb, bias_part);
+        bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
+        bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
+        if (j == 0) s_ml[warp][r][0] = bias_part;
+        bar_sync(BAR_COMPUTE, FW * 32);
+      }
+#include "decode_state.inc"
+#pragma unroll 1
+      for (int it = 0; it < n_it; ++it) {
+        const int stage = (git + it) % FSTAGES;
+        if (it > 0) wait_tile(git + it);
+        const TileInfo t = s_tile[stage];
+        const int p = t.phase & 3;
+        const int nblocks = (t.n + 31) >> 5;
+        const int pb = (warp + FW - (it * (TILE_MAX / 128)) % FW) % FW;
+#include "decode_tile.inc"
+        if (it + 1 < n_it) {                               // (the item's last slot is handed back after the merge)
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_empty[stage]);
+        }
+      }
+      const int last_stage = (git + n_it - 1) % FSTAGES;
+      // ── merge the four workers and write the item's result (in the ring slot of its last tile) ──
+      if (cur_phase >= 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float f = pow2i(acc_exp(cur_phase, i & 3));
+          acc[i][0] *= f; acc[i][1] *= f; acc[i][2] *= f; acc[i][3] *= f;
+        }
+      }
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        l_e += __shfl_xor_sync(0xffffffffu, l_e, o); l_o += __shfl_xor_sync(0xffffffffu, l_o, o);
+      }
+      bar_sync(BAR_COMPUTE, FW * 32);                      // every worker is done with its stages
+      float* red = reinterpret_cast<float*>(smem_raw + (size_t)last_stage * stage_bytes);   // [FW][GH][128]
+      if (r == 0) {
+        s_ml[warp][2 * j][0] = m_e; s_ml[warp][2 * j][1] = l_e; s_ml[warp][2 * j][2] = zacc[0];
+        s_ml[warp][2 * j + 1][0] = m_o; s_ml[warp][2 * j + 1][1] = l_o; s_ml[warp][2 * j + 1][2] = zacc[1];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int ch = 4 * r + 2 * (i >> 2) + 32 * (i & 3);
+        float* o0 = red + ((warp * GH + 2 * j) * D);
+        float* o1 = o0 + D;
+        o0[ch] = acc[i][0]; o1[ch] = acc[i][1]; o0[ch + 1] = acc[i][2]; o1[ch + 1] = acc[i][3];
+      }
+      bar_sync(BAR_COMPUTE, FW * 32);
+      const EpiInfo ep = s_epi;
+      final_merge<true>(red, &s_ml[0][0][0], s_fin, ep.gcnt, ep.how, ep.out_rows, ep.rec0, ep.rec_stride);
+      if (ep.n_chunks > 1 && unit_ctr != nullptr)
+        chunk_merge<true>(partials, unit_ctr + ep.unit_y, ep.n_chunks, ep.gcnt, ep.row0, out, merged);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[last_stage]);    // only now may the staging warp refill the slot
+      git += n_it;
+    }
+  }
+  if (warp == FW) cp_wait<0>();
 }
 
 }  // namespace rdkv
@@ -1524,6 +1563,55 @@ extern "C" int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const
   return launch_fused<MODE_ATTN>(views, n_views, q, q_dtype, H_q, H_kv, chunk_rows, n_chunks, k_row_bytes_max,
                                  partials, out, status, nullptr, 0, 0, stream, unit_recs, k_slots, nkb_max,
                                  unit_counters, out_record, row_begin, row_end, n_whole_units, seq_part, seq_parts);
+}
+
+extern "C" int rdkv_decode_attn_persistent(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,
+                                           int H_q, int H_kv, int chunk_rows, int n_chunks, int n_whole_units,
+                                           int row_begin, int row_end, int seq_part, int seq_parts,
+                                           int k_row_bytes_max, const void* unit_recs, const void* k_slots,
+                                           int nkb_max, float* partials, int32_t* unit_counters,
+                                           int32_t* work_counters, float* out, float* out_record, int32_t* status,
+                                           void* stream) {
+  if (work_counters == nullptr) return RDKV_ERR_BAD_ARG;
+  if (n_chunks <= 0 || chunk_rows <= 0 || row_begin < 0 || row_end < row_begin) return RDKV_ERR_BAD_ARG;
+  if (seq_parts < 1 || seq_part < 0 || seq_part >= seq_parts) return RDKV_ERR_BAD_ARG;
+  if ((out == nullptr) == (out_record == nullptr)) return RDKV_ERR_BAD_ARG;
+  if (n_chunks > 1 && (partials == nullptr || unit_counters == nullptr)) return RDKV_ERR_BAD_ARG;
+  if (unit_recs == nullptr || k_slots == nullptr || nkb_max <= 0 || nkb_max > KB_MAX) return RDKV_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(unit_recs) & 15) || (reinterpret_cast<uintptr_t>(k_slots) & 15) ||
+      (reinterpret_cast<uintptr_t>(q) & 15))
+    return RDKV_ERR_BAD_ARG;
+  const int rc = check_fused_args(views, n_views, q, q_dtype, H_q, H_kv, k_row_bytes_max);
+  if (rc != RDKV_OK || n_views == 0) return rc;
+  const int g = H_q / H_kv;
+  const int n_hgrp = (g + GH - 1) / GH;
+  const int64_t units = (int64_t)n_views * H_kv * n_hgrp;
+  if (n_whole_units < 0 || n_whole_units > units) return RDKV_ERR_BAD_ARG;
+  const int64_t items = n_whole_units + (units - n_whole_units) * n_chunks;
+  if (items > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
+  const int stage_bytes = align16i(stage_capacity(k_row_bytes_max));
+  const int q_elt = q_dtype == RDKV_F32 ? 4 : 2;
+  size_t smem = (size_t)FSTAGES * stage_bytes + (size_t)nkb_max * 256 +
+                2 * ((size_t)GH * D * q_elt + (size_t)nkb_max * 32 * sizeof(KSlotRec));
+  const size_t epilogue = (size_t)FW * GH * D * sizeof(float);
+  if ((size_t)stage_bytes < epilogue) return RDKV_ERR_BAD_SHAPE;     // the merge works inside one ring slot
+  if (smem > 227 * 1024) return RDKV_ERR_TOO_LARGE;
+  cudaError_t e = cudaFuncSetAttribute(decode_persist_kernel<MODE_ATTN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
+  int dev = 0, sms = 0, per_sm = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_persist_kernel<MODE_ATTN>, CTA_THREADS, smem) != cudaSuccess ||
+      per_sm <= 0) {
+    g_last_cuda_error = (int)cudaGetLastError();
+    return RDKV_ERR_LAUNCH;
+  }
+  const int64_t slots = (int64_t)sms * per_sm;
+  const unsigned grid = (unsigned)(items < slots ? items : slots);
+  decode_persist_kernel<MODE_ATTN><<<grid, CTA_THREADS, smem, (cudaStream_t)stream>>>(
+      q, q_dtype, H_q, g, chunk_rows, n_chunks, n_whole_units, (int)items, stage_bytes, partials, out, status,
+      reinterpret_cast<const UnitRec*>(unit_recs), reinterpret_cast<const KSlotRec*>(k_slots), nkb_max, unit_counters,
+      out_record, row_begin, row_end, seq_part, seq_parts, work_counters);
+  return launch_status();
 }
 
 extern "C" int rdkv_decode_scores(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,

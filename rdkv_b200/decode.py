@@ -33,7 +33,7 @@ class DecodeTable:
 
     def __init__(self, layers: Sequence[PackedKVLayer], new_v_only: Sequence[Optional[Tensor]], H_q: int,
                  *, use_mask: bool = False, device=None, n_chunks: Optional[int] = None,
-                 k_only: bool = False, live_counts: bool = False):
+                 k_only: bool = False, live_counts: bool = False, persistent: Optional[bool] = None):
         if len(layers) == 0:
             raise ValueError("DecodeTable needs at least one layer")
         if len(new_v_only) != len(layers):
@@ -87,13 +87,28 @@ class DecodeTable:
         self.unit_recs = torch.empty(L.rdkv_decode_prepared_bytes(n_units, self.nkb_max, 0), dtype=torch.uint8, device=self.device)
         self.k_slots = torch.empty(L.rdkv_decode_prepared_bytes(n_units, self.nkb_max, 1), dtype=torch.uint8, device=self.device)
         self.unit_ctr = torch.zeros(self.n_views * self.H_kv * n_hgrp, dtype=torch.int32, device=self.device)
+        # item counters of the persistent form: a pair per launch that may be in flight at the same time
+        self.work_ctr = torch.zeros(2 * self.WORK_CTR_SLOTS, dtype=torch.int32, device=self.device)
         self._ws = {}
         # live_counts: the kernel reads the layers' count / scale / permutation tensors itself at every
         # launch (no snapshot to refresh; one more round trip per CTA)
         self.live_counts = bool(live_counts)
+        self.use_mask = bool(use_mask)
         self.refresh()
+        # the persistent form of the kernel needs every unit's byte ranges on whole 16-byte blocks
+        # (flag bit 0 of its prepared record; read back once, here)
+        self.persistent = None if persistent is None else bool(persistent)
+        self._all_fast = False
+        if not self.live_counts:
+            recs = self.unit_recs.view(torch.int32).view(n_units, self._unit_rec_bytes // 4)
+            self._all_fast = bool((recs[:, 4] & 1).all().item())
 
     CTAS_PER_SM = 3                      # resident CTAs of the fused kernel per SM
+    WORK_CTR_SLOTS = 64                  # launches of one table that may overlap (view ranges on streams of their own)
+    # The persistent form (one resident CTA per slot draws items from a counter) is used for launches
+    # of whole units that fill the CTA slots at least this many times over; measured on B200 it is
+    # about 2 % faster there and slower than one CTA per item when whole units and chunks are mixed.
+    PERSISTENT_MIN_ROUNDS = 4
     # cost model of a launch (SM cycles, measured on B200): a CTA spends ROW_COST per live row it
     # attends over plus a fixed cost (prologue, first tile, merge of its warps, result): FIXED_WHOLE
     # when it has a whole unit, FIXED_CHUNK when it has a chunk (record + arrival counter on top)
@@ -141,6 +156,8 @@ class DecodeTable:
 
         best = (-(-units // slots) * whole, 1, units)                       # all whole
         full, left = divmod(units, slots)
+        if full >= self.PERSISTENT_MIN_ROUNDS and self.persistent is not False and self._can_persist():
+            return 1, self._chunk_rows_for(1, rows), units                  # many rounds: whole units, persistent form
         if left and k_max > 1:
             for k in range(2, k_max + 1):                                   # full rounds whole + leftover in k chunks
                 cost = full * whole + -(-left * k // slots) * chunk_cost(k)
@@ -148,6 +165,9 @@ class DecodeTable:
                     best = (cost, k, full * slots)
         _, k, n_whole = best
         return k, self._chunk_rows_for(k, rows), n_whole
+
+    def _can_persist(self) -> bool:
+        return (not self.live_counts) and self._all_fast and not self.use_mask
 
     def unit_plan(self, n_views: int):
         """(v_main, k, rows) form of :meth:`plan`: ``v_main`` = views whose units all stay whole."""
@@ -229,7 +249,8 @@ def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out
 
 def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int = 0, v1: Optional[int] = None,
                   *, out_record: Optional[Tensor] = None, rows: Optional[Tuple[int, int]] = None,
-                  seq_part: Optional[Tuple[int, int]] = None, plan: Optional[Tuple[int, int, int]] = None) -> None:
+                  seq_part: Optional[Tuple[int, int]] = None, plan: Optional[Tuple[int, int, int]] = None,
+                  ctr_slot: int = 0) -> None:
     """ONE launch of the fused kernel on views [v0, v1): whole units, or uniform chunks merged inside
     the kernel (DecodeTable.plan).  The result is the normalised ``out`` [n_views,H_q,128] or the
     un-normalised record per query head ``out_record`` [n_views*H_q,132]; ``seq_part`` = (i, n)
@@ -265,14 +286,23 @@ def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int 
         return None if t is None else t.data_ptr() + qrow * per_row * t.element_size()
 
     ws = table.chunk_workspace(k) if k > 1 else None
+    # persistent form (one resident CTA per slot draws the items): when the table allows it and the
+    # launch is whole units filling the CTA slots several times over (or the table asks for it)
+    items = n_whole + ((v1 - v0) * hy - n_whole) * k
+    can = table._can_persist() and (q.data_ptr() + qrow * HEAD_DIM * q.element_size()) % 16 == 0
+    want = (table.persistent if table.persistent is not None
+            else (k == 1 and items >= table.PERSISTENT_MIN_ROUNDS * table._sms * table.CTAS_PER_SM))
+    persistent = can and want and ctr_slot < table.WORK_CTR_SLOTS
+    fn = lib().rdkv_decode_attn_persistent if persistent else lib().rdkv_decode_attn
+    extra = (table.work_ctr.data_ptr() + 8 * ctr_slot,) if persistent else ()
     with torch.cuda.device(table.device):
-        check(lib().rdkv_decode_attn(table.views.data_ptr() + v0 * C.sizeof(LayerView), v1 - v0,
+        check(fn(table.views.data_ptr() + v0 * C.sizeof(LayerView), v1 - v0,
                                      off(q, HEAD_DIM), q_dtype_tag(q), table.H_q, table.H_kv, rows_k, k, n_whole, r0, r1, sp_i, sp_n,
                                      table.k_row_bytes_max,
                                      None if table.live_counts else table.unit_recs.data_ptr() + v0 * table.H_kv * table._unit_rec_bytes,
                                      None if table.live_counts else table.k_slots.data_ptr() + v0 * table.H_kv * table.nkb_max * 512,
                                      0 if table.live_counts else table.nkb_max,
-                                     off(ws, k * PARTIAL_STRIDE), table.unit_ctr.data_ptr() + v0 * hy * 4,
+                                     off(ws, k * PARTIAL_STRIDE), table.unit_ctr.data_ptr() + v0 * hy * 4, *extra,
                                      off(out, HEAD_DIM), off(out_record, PARTIAL_STRIDE),
                                      ptr(table.status), stream_ptr(q.device)),
               "rdkv_decode_attn")
@@ -447,11 +477,11 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
     out = out_host if direct else io.out
     cur = torch.cuda.current_stream(table.device)
     plan = table.plan(table.n_views)                       # the device call's launch shape: same results bit for bit
-    for (a, b), st in zip(io.ranges, io.streams):
+    for slot, ((a, b), st) in enumerate(zip(io.ranges, io.streams)):
         st.wait_stream(cur)
         with torch.cuda.stream(st):
             io.q[a:b].copy_(q_host[a:b], non_blocking=True)
-            _launch_units(io.q, table, out, a, b, plan=plan)
+            _launch_units(io.q, table, out, a, b, plan=plan, ctr_slot=slot)
             if not direct:
                 out_host[a:b].copy_(io.out[a:b], non_blocking=True)
     for st in io.streams[:len(io.ranges)]:

@@ -268,6 +268,43 @@ def test_row_windows_merge_to_the_unsplit_result():
         packed_decode_attention(q.cuda(), table, rows=(5, 2))
 
 
+def test_persistent_form_equals_the_one_item_form():
+    """One resident CTA per slot walking the work items gives bit for bit what one CTA per item
+    gives: whole units, chunked units, a mix, sequence parts and un-normalised records, ragged heads
+    and heads without rows, few items and more items than CTA slots, called twice."""
+    from rdkv_b200 import synth
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention
+    from rdkv_b200.packing import pack_kv
+    H_kv, g, T = 4, 4, 1024
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    base = []
+    for i, ragged in enumerate((None, [400, 64, 0, 333], [17, 512, 256, 1], None, [0, 0, 480, 480])):
+        seed = synth.unit_seed(8, i, 5)
+        K, V = synth.make_kv(H_kv, T, seed=seed)
+        vb = synth.make_v_bits(H_kv, T, 512, seed=seed, per_head_N=ragged)
+        kb = synth.make_k_bits(H_kv, seed=seed)
+        base.append(pack_kv(K.cuda(), V.cuda(), vb.cuda(), kb.cuda(), g, build_mask=False))
+    for n_views in (3, (3 * sms) // H_kv + 7):
+        layers = [base[i % len(base)][0] for i in range(n_views)]
+        nvs = [base[i % len(base)][1] for i in range(n_views)]
+        q = synth.make_q(H_kv * g, seed=13, batch=n_views, dtype=torch.bfloat16).cuda()
+        for forced in (None, 1, 3):
+            one = DecodeTable(layers, nvs, H_kv * g, n_chunks=forced, persistent=False)
+            per = DecodeTable(layers, nvs, H_kv * g, n_chunks=forced, persistent=True)
+            assert per._all_fast
+            for rep in range(2):
+                a = packed_decode_attention(q, one)
+                b = packed_decode_attention(q, per)
+                assert torch.equal(a, b), (n_views, forced, rep, float((a - b).abs().max()))
+            ra = torch.empty((n_views * H_kv * g, 132), device="cuda")
+            rb = torch.empty_like(ra)
+            packed_decode_attention(q, one, out_partial=ra, seq_part=(1, 2))
+            packed_decode_attention(q, per, out_partial=rb, seq_part=(1, 2))
+            assert torch.equal(ra, rb), (n_views, forced)
+            one.check_status(); per.check_status()
+            assert int(per.unit_ctr.abs().sum().item()) == 0
+
+
 def test_host_buffer_call_equals_device_call():
     """The host-buffer form (view ranges on separate streams, copies overlapped with the
     kernels) returns bit-for-bit what the device call returns, for one-chunk tables and
