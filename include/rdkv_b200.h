@@ -305,11 +305,12 @@ int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_row_stride, 
  * for rdkv_lse_combine to merge with the record of the packed zones.
  * new_k / new_v: [n_views][H_kv][cap][128] fp16, bf16 or fp32 with the given
  * element strides (rows 16- resp. 8-byte aligned); the first n_new rows of every
- * head are live, or n_new_per_view[view] rows when that device array is given. */
+ * head are live, or n_new_per_view[view] rows when that device array is given; cap = rows each
+ * head's buffer holds (counts read on the device are clamped to [0, cap]). */
 int rdkv_tail_attn_partial(const void* q, int q_dtype, int64_t n_views, int H_q, int H_kv,
                            const void* new_k, const void* new_v, int kv_dtype,
                            int64_t kv_view_stride, int64_t kv_head_stride, int64_t kv_row_stride,
-                           int n_new, const int32_t* n_new_per_view, float* partial, void* stream);
+                           int n_new, const int32_t* n_new_per_view, int cap, float* partial, void* stream);
 
 /* ── prefill: importance scores that feed the allocator ───────────────────────
  * Replaces _score_one_layer (obkv_fast.py:854-896) and apply_score_pooling
@@ -392,15 +393,27 @@ int rdkv_knapsack_batched(const float* scores, int64_t row_stride, int n_rows, i
                           int n_options, int max_iters, float tol, int64_t* out, void* scratch,
                           void* stream);
 
+/* Single-row form, for any number of independent rows.  Replaces knapsack_bit_allocation
+ * (knapsack_solver.py:39-118), whose arithmetic differs from the batched solver's: the multiplier
+ * is bisected in double precision and enters the cost as its fp32 rounding, means and the
+ * tolerance test are compared in double, lambda_hi has no floor and is doubled row by row until the
+ * mean fits or it reaches 1e12.  budget: DEVICE array of doubles [n_rows]; no scratch. */
+int rdkv_knapsack_rows(const float* scores, int64_t row_stride, int n_rows, int len, const double* budget,
+                       const float* option_bits, const float* option_eps, int n_options, int max_iters,
+                       double tol, int64_t* out, void* stream);
+
 /* ── batched bit allocator without caller-provided scratch ────────────────────
  * No counterpart in the reference.  Same computation and arguments as
  * rdkv_knapsack_batched, minus `scratch`: the three words per row the two kernels
  * hand over to each other live in a fixed array inside the library's device image
  * (48 KiB on every GPU that loads the library, held until the process exits).  It is
  * meant for callers that may not allocate device memory where they call from — an
- * engine that froze its memory plan after warm-up, a host callback, a plugin that
- * is given input and output buffers and nothing else.  The call itself performs no
- * allocation of any kind.
+ * engine that froze its memory plan after warm-up, or a plugin that is given input
+ * and output buffers and nothing else.  After one warm-up call per device the call
+ * performs no allocation of any kind (the first call on a device makes the runtime
+ * load the library's module there, which reserves device memory, and opts the
+ * kernels into large shared memory if the row is longer than 48 KiB: warm up before
+ * the memory plan is frozen, with a row as long as the longest that will follow).
  *   - n_rows above rdkv_knapsack_static_max_rows() (4096) is refused with
  *     RDKV_ERR_TOO_LARGE; split the batch or use rdkv_knapsack_batched.
  *   - The first call on each device looks up the array's device address

@@ -76,3 +76,43 @@ def knapsack_batched(scores, budget, epsilon: dict, max_iters: int = 64, tol: fl
         lam_hi = np.where(high, lam_hi, lam_mid).astype(F32)
     final[~converged] = bits_mid[~converged]
     return final.astype(np.int64)
+
+
+def knapsack_scalar(scores, budget: float, epsilon: dict, max_iters: int = 64, tol: float = 0.01,
+                    bit_options=DEFAULT_BITS) -> np.ndarray:
+    """The reference's single-row solver (knapsack_solver.py:39-118): same cost and argmin as the
+    batched one, but the multiplier is a Python float (double) that enters the cost as its fp32
+    rounding, the means (fp32) are compared with the budget in double, lambda_hi starts at
+    max(score)*0.375 without a floor and is doubled while the mean exceeds the budget and it is
+    below 1e12, and the tolerance test runs in double."""
+    s = np.ascontiguousarray(scores, dtype=F32).reshape(1, -1)
+    bits = np.asarray(bit_options, dtype=F32)
+    eps = np.asarray([epsilon[int(b)] for b in bits], dtype=F32)
+    budget = float(budget)
+
+    def solve(lam: float) -> np.ndarray:
+        return _solve(s, np.asarray([lam], dtype=F32), eps, bits)
+
+    def mean(b: np.ndarray) -> float:
+        return float(_mean(b)[0])
+
+    lam_lo, lam_hi = 0.0, float(s.max()) * 0.375
+    rounds = 0
+    while mean(solve(lam_hi)) > budget and lam_hi < 1e12 and rounds < 200:
+        lam_hi *= 2.0
+        rounds += 1
+    lo = solve(lam_lo)
+    if mean(lo) <= budget:
+        return lo[0].astype(np.int64)
+    mid = lo
+    for _ in range(max_iters):
+        lam_mid = (lam_lo + lam_hi) / 2.0
+        mid = solve(lam_mid)
+        avg = mean(mid)
+        if abs(avg - budget) / max(budget, 1e-8) < tol:
+            break
+        if avg > budget:
+            lam_lo = lam_mid
+        else:
+            lam_hi = lam_mid
+    return mid[0].astype(np.int64)

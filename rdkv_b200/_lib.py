@@ -88,7 +88,7 @@ _PROTOTYPES = {
     "rdkv_decode_prepare": ([_p, _i, _i, _i, _p, _p, _p], _i),
     "rdkv_decode_attn": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p], _i),
     "rdkv_decode_attn_persistent": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p], _i),
-    "rdkv_tail_attn_partial": ([_p, _i, _i64, _i, _i, _p, _p, _i, _i64, _i64, _i64, _i, _p, _p, _p], _i),
+    "rdkv_tail_attn_partial": ([_p, _i, _i64, _i, _i, _p, _p, _i, _i64, _i64, _i64, _i, _p, _i, _p, _p], _i),
     "rdkv_lse_combine": ([_p, _i64, _i, _i64, _i64, _p, _p, _p, _p], _i),
     "rdkv_partition_by_bits": ([_p, _i, _i64, _i, _i, _i, _p, _p, _p], _i),
     "rdkv_pack_v": ([_p, _i64, _i64, _i, _i, _p, _i64, _p, _i64, _i, _i, _i, _i, _i, _i,
@@ -103,6 +103,7 @@ _PROTOTYPES = {
     "rdkv_sizeof_pack_job": ([], _i),
     "rdkv_pack_kv_batched": ([_p, _i, _i, _i, _i, _i, _i, _p], _i),
     "rdkv_knapsack_batched": ([_p, _i64, _i, _i, _p, C.POINTER(_f), C.POINTER(_f), _i, _i, _f, _p, _p, _p], _i),
+    "rdkv_knapsack_rows": ([_p, _i64, _i, _i, _p, C.POINTER(_f), C.POINTER(_f), _i, _i, C.c_double, _p, _p], _i),
     "rdkv_knapsack_static_max_rows": ([], _i),
     "rdkv_knapsack_batched_static": ([_p, _i64, _i, _i, _p, C.POINTER(_f), C.POINTER(_f), _i, _i, _f, _p, _p], _i),
 }
@@ -152,6 +153,13 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def stream_ptr(device=None) -> int:
+    """The current stream of ``device`` for a launch.  The library launches on the CURRENT device, so
+    a tensor that lives on another GPU is refused here (wrap the call in ``torch.cuda.device``)."""
+    if device is not None:
+        idx = torch.device(device).index
+        if idx is not None and idx != torch.cuda.current_device():
+            raise RuntimeError(f"rdkv_b200: tensors live on cuda:{idx} but the current device is "
+                               f"cuda:{torch.cuda.current_device()}; make their device current for the call")
     return torch.cuda.current_stream(device).cuda_stream
 
 

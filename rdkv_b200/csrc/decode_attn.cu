@@ -254,13 +254,13 @@ __global__ void __launch_bounds__(TAIL_WARPS * 32)
 tail_attn_partial_kernel(const void* __restrict__ q, int q_dtype, int64_t n_rows, int H_q, int g,
                          const void* __restrict__ new_k, const void* __restrict__ new_v, int kv_dtype,
                          int64_t kv_view_stride, int64_t kv_head_stride, int64_t kv_row_stride, int n_new,
-                         const int32_t* __restrict__ n_new_per_view, float* __restrict__ partial) {
+                         const int32_t* __restrict__ n_new_per_view, int cap, float* __restrict__ partial) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * TAIL_WARPS + warp;    // (view, query head)
   if (row >= n_rows) return;
   const int64_t view = row / H_q;
   const int hq = (int)(row % H_q), h = hq / g;
-  const int n = n_new_per_view != nullptr ? n_new_per_view[view] : n_new;
+  const int n = min(max(n_new_per_view != nullptr ? n_new_per_view[view] : n_new, 0), cap);   // never past the buffer
   float4 qv;
   qv.x = load_q(q, q_dtype, row * D + 4 * lane) * INV_SQRT_D; qv.y = load_q(q, q_dtype, row * D + 4 * lane + 1) * INV_SQRT_D;
   qv.z = load_q(q, q_dtype, row * D + 4 * lane + 2) * INV_SQRT_D; qv.w = load_q(q, q_dtype, row * D + 4 * lane + 3) * INV_SQRT_D;
@@ -324,11 +324,9 @@ extern "C" int rdkv_v_weighted_sum(const rdkv_layer_view* view, const float* w, 
   if (view->v_scale == nullptr || view->v_zp == nullptr) return RDKV_ERR_BAD_ARG;
   const int g = H_q / H_kv;
   const size_t smem = sizeof(float) * (VSUM_THREADS / 32) * GP * D;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(v_weighted_sum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attr_done = true;
-  }
+  // (per device, not per process: set on every call, as the fused kernel's launcher does)
+  cudaError_t e = cudaFuncSetAttribute(v_weighted_sum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
   v_weighted_sum_kernel<<<H_kv, VSUM_THREADS, smem, (cudaStream_t)stream>>>(*view, w, w_row_stride, g, out,
                                                                            out_row_stride);
   return launch_status();
@@ -350,8 +348,9 @@ extern "C" int rdkv_lse_combine(const float* partials, int64_t n_rows, int n_spl
 extern "C" int rdkv_tail_attn_partial(const void* q, int q_dtype, int64_t n_views, int H_q, int H_kv,
                                       const void* new_k, const void* new_v, int kv_dtype,
                                       int64_t kv_view_stride, int64_t kv_head_stride, int64_t kv_row_stride,
-                                      int n_new, const int32_t* n_new_per_view, float* partial, void* stream) {
-  if (q == nullptr || new_k == nullptr || new_v == nullptr || partial == nullptr || n_views < 0 || n_new < 0)
+                                      int n_new, const int32_t* n_new_per_view, int cap, float* partial, void* stream) {
+  if (q == nullptr || new_k == nullptr || new_v == nullptr || partial == nullptr || n_views < 0 || n_new < 0 ||
+      cap < 0 || n_new > cap)
     return RDKV_ERR_BAD_ARG;
   if (q_dtype < RDKV_F16 || q_dtype > RDKV_F32 || kv_dtype < RDKV_F16 || kv_dtype > RDKV_F32) return RDKV_ERR_BAD_ARG;
   if (H_q <= 0 || H_kv <= 0 || H_q % H_kv != 0) return RDKV_ERR_BAD_SHAPE;
@@ -367,6 +366,6 @@ extern "C" int rdkv_tail_attn_partial(const void* q, int q_dtype, int64_t n_view
   if (blocks > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
   tail_attn_partial_kernel<<<(unsigned)blocks, TAIL_WARPS * 32, 0, (cudaStream_t)stream>>>(
       q, q_dtype, n_rows, H_q, H_q / H_kv, new_k, new_v, kv_dtype, kv_view_stride, kv_head_stride, kv_row_stride,
-      n_new, n_new_per_view, partial);
+      n_new, n_new_per_view, cap, partial);
   return launch_status();
 }

@@ -142,21 +142,55 @@ knapsack_solve_kernel(const float* __restrict__ scores, int64_t row_stride, int 
   for (int i = threadIdx.x; i < len; i += KNAP_THREADS) orow[i] = (int64_t)o.ibits[choose(row[i], nullptr, o, lb)];
 }
 
+// The single-row form of the reference (knapsack_solver.py:39-118) differs from the batched one in
+// its arithmetic: the multiplier is bisected in double precision (Python floats) and enters the cost
+// as its fp32 rounding, means and the tolerance test are compared in double, lambda_hi has no 1e-8
+// floor and is doubled row by row until the mean fits or it reaches 1e12.  One CTA per row, rows
+// independent.  (The reference does not terminate on a row whose scores are all zero while its
+// cheapest option is above the budget — lambda_hi stays 0; the doubling here stops after 200 rounds.)
+__global__ void __launch_bounds__(KNAP_THREADS)
+knapsack_scalar_kernel(const float* __restrict__ scores, int64_t row_stride, int len,
+                       const double* __restrict__ budget, KnapOpts o, int max_iters, double tol,
+                       int use_smem, int64_t* __restrict__ out) {
+  extern __shared__ float smem_row[];
+  __shared__ unsigned long long s_red[KNAP_THREADS / 32];
+  __shared__ float s_max[KNAP_THREADS / 32];
+  const int b = blockIdx.x;
+  const float* row = stage_row(scores + (int64_t)b * row_stride, len, smem_row, use_smem != 0);
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < len; i += KNAP_THREADS) mx = fmaxf(mx, row[i]);
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = -INFINITY;
+  for (int w = 0; w < KNAP_THREADS / 32; ++w) mx = fmaxf(mx, s_max[w]);
+  const double bud = budget[b];
+  auto avg_at = [&](double lam) { return (double)mean_of(sweep_sum(row, len, (float)lam, o, s_red), len); };
+  double lam_lo = 0.0, lam_hi = (double)mx * 0.375;
+  for (int k = 0; k < 200 && avg_at(lam_hi) > bud && lam_hi < 1e12; ++k) lam_hi *= 2.0;
+  double lam_final = 0.0;
+  if (!(avg_at(0.0) <= bud)) {
+    double lam_mid = 0.0;
+    for (int it = 0; it < max_iters; ++it) {
+      lam_mid = (lam_lo + lam_hi) / 2.0;
+      const double avg = avg_at(lam_mid);
+      if (fabs(avg - bud) / fmax(bud, 1e-8) < tol) break;
+      if (avg > bud) lam_lo = lam_mid; else lam_hi = lam_mid;
+    }
+    lam_final = lam_mid;
+  }
+  float lb[KNAP_MAX_OPT];
+#pragma unroll
+  for (int n = 0; n < KNAP_MAX_OPT; ++n) lb[n] = n < o.n ? __fmul_rn((float)lam_final, o.bits[n]) : 0.f;
+  int64_t* orow = out + (int64_t)b * len;
+  for (int i = threadIdx.x; i < len; i += KNAP_THREADS) orow[i] = (int64_t)o.ibits[choose(row[i], nullptr, o, lb)];
+}
+
 }  // namespace rdkv
 
 using namespace rdkv;
 
-extern "C" int rdkv_knapsack_batched(const float* scores, int64_t row_stride, int n_rows, int len,
-                                     const float* budget, const float* option_bits,
-                                     const float* option_eps, int n_options, int max_iters, float tol,
-                                     int64_t* out, void* scratch, void* stream) {
-  if (scores == nullptr || budget == nullptr || option_bits == nullptr || option_eps == nullptr ||
-      out == nullptr || scratch == nullptr)
-    return RDKV_ERR_BAD_ARG;
-  if (n_rows < 0 || len <= 0 || max_iters < 0) return RDKV_ERR_BAD_ARG;
-  if (n_options <= 0 || n_options > KNAP_MAX_OPT) return RDKV_ERR_BAD_SHAPE;
-  if (n_rows == 0) return RDKV_OK;
-  KnapOpts o;
+static int fill_options(KnapOpts& o, const float* option_bits, const float* option_eps, int n_options, int len) {
   o.n = n_options;
   float max_bit = 0.f;
   for (int n = 0; n < KNAP_MAX_OPT; ++n) {
@@ -169,6 +203,43 @@ extern "C" int rdkv_knapsack_batched(const float* scores, int64_t row_stride, in
     }
   }
   if ((double)len * (double)max_bit >= 16777216.0) return RDKV_ERR_TOO_LARGE;
+  return RDKV_OK;
+}
+
+extern "C" int rdkv_knapsack_rows(const float* scores, int64_t row_stride, int n_rows, int len, const double* budget,
+                                  const float* option_bits, const float* option_eps, int n_options, int max_iters,
+                                  double tol, int64_t* out, void* stream) {
+  if (scores == nullptr || budget == nullptr || option_bits == nullptr || option_eps == nullptr || out == nullptr)
+    return RDKV_ERR_BAD_ARG;
+  if (n_rows < 0 || len <= 0 || max_iters < 0) return RDKV_ERR_BAD_ARG;
+  if (n_options <= 0 || n_options > KNAP_MAX_OPT) return RDKV_ERR_BAD_SHAPE;
+  if (n_rows == 0) return RDKV_OK;
+  KnapOpts o;
+  const int rc = fill_options(o, option_bits, option_eps, n_options, len);
+  if (rc != RDKV_OK) return rc;
+  const size_t row_bytes = (size_t)len * sizeof(float);
+  const int use_smem = row_bytes <= (size_t)KNAP_SMEM_ROW_BYTES ? 1 : 0;
+  const size_t smem = use_smem ? row_bytes : 0;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(knapsack_scalar_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KNAP_SMEM_ROW_BYTES);
+  knapsack_scalar_kernel<<<n_rows, KNAP_THREADS, smem, (cudaStream_t)stream>>>(scores, row_stride, len, budget, o,
+                                                                              max_iters, tol, use_smem, out);
+  return launch_status();
+}
+
+extern "C" int rdkv_knapsack_batched(const float* scores, int64_t row_stride, int n_rows, int len,
+                                     const float* budget, const float* option_bits,
+                                     const float* option_eps, int n_options, int max_iters, float tol,
+                                     int64_t* out, void* scratch, void* stream) {
+  if (scores == nullptr || budget == nullptr || option_bits == nullptr || option_eps == nullptr ||
+      out == nullptr || scratch == nullptr)
+    return RDKV_ERR_BAD_ARG;
+  if (n_rows < 0 || len <= 0 || max_iters < 0) return RDKV_ERR_BAD_ARG;
+  if (n_options <= 0 || n_options > KNAP_MAX_OPT) return RDKV_ERR_BAD_SHAPE;
+  if (n_rows == 0) return RDKV_OK;
+  KnapOpts o;
+  const int orc = fill_options(o, option_bits, option_eps, n_options, len);
+  if (orc != RDKV_OK) return orc;
   const size_t row_bytes = (size_t)len * sizeof(float);
   const int use_smem = row_bytes <= (size_t)KNAP_SMEM_ROW_BYTES ? 1 : 0;
   const size_t smem = use_smem ? row_bytes : 0;
@@ -190,10 +261,14 @@ extern "C" int rdkv_knapsack_batched(const float* scores, int64_t row_stride, in
 // ── allocation-free variant ──────────────────────────────────────────────────
 // Some callers cannot provide the per-row scratch of rdkv_knapsack_batched because
 // they are not allowed to allocate device memory at the point of the call: a
-// prefill step that runs inside an engine's fixed memory plan after warm-up, a
-// host callback, a plugin interface that hands over input and output buffers only.
+// prefill step that runs inside an engine's fixed memory plan after warm-up, or a
+// plugin interface that hands over input and output buffers only.
 // For them the scratch lives in this library's own device image: a file-scope
 // array that every GPU loading the library carries until the process exits.
+// (One warm-up call per device, made before the memory plan is frozen and before any
+// stream capture, looks the array's address up and lets the runtime load the module;
+// rows longer than 48 KiB also opt the kernels into large shared memory on that call,
+// so the warm-up should use a row as long as the longest that will follow.)
 constexpr int KNAP_STATIC_MAX_ROWS = 4096;                 // 3 words per row -> 48 KiB per GPU
 static __device__ __align__(256) unsigned int g_knap_static_scratch[3 * KNAP_STATIC_MAX_ROWS];
 

@@ -359,7 +359,7 @@ def tail_attention_partial(q: Tensor, new_k: Tensor, new_v: Tensor, n_new, H_kv:
         out_partial = torch.empty((n_views * H_q, PARTIAL_STRIDE), dtype=torch.float32, device=q.device)
     check(lib().rdkv_tail_attn_partial(ptr(q), q_dtype_tag(q), n_views, H_q, H_kv, ptr(new_k), ptr(new_v),
                                        q_dtype_tag(new_k), new_k.stride(0), new_k.stride(1), new_k.stride(2),
-                                       n_int, ptr(per_view), ptr(out_partial), stream_ptr(q.device)),
+                                       n_int, ptr(per_view), cap, ptr(out_partial), stream_ptr(q.device)),
           "rdkv_tail_attn_partial")
     return out_partial
 

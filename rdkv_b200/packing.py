@@ -419,6 +419,45 @@ class PackedLayerBatch:
         return (self.layer(i) for i in range(self.n_layers))
 
 
+def select_and_pack(K: Tensor, V: Tensor, layer_scores: Tensor, channel_scores: Tensor, *, gqa_factor: int,
+                    token_budget: int, k_budget_ratio: float, obs_window: int = 0, pool_kernel_size: int = 5,
+                    pool_padding: str = "reflect", pool_type: str = "avg", v_bit_options: Optional[Tensor] = None,
+                    k_bit_options: Optional[Tensor] = None, eps_V: Optional[dict] = None,
+                    eps_K: Optional[dict] = None, build_mask: bool = True
+                    ) -> Tuple[PackedKVLayer, Optional[Tensor], int]:
+    """One layer of the prefill: pool the token scores, allocate V bits per head, derive every head's
+    K budget from the tokens it kept, allocate K bits, drop the evicted channels and pack — the
+    reference's per-layer composite ``_perhead_select_and_pack_joint`` (obkv_fast.py:899-1186) with
+    its arguments and its return ``(packed_layer, new_v_only, T_eff)``.
+
+    K, V [1,H_kv,T,D] fp16, layer_scores [H_kv,T], channel_scores [H_kv,D], all on the GPU.
+    Everything stays on the device: the only host read is the one of the segment counts inside
+    :func:`pack_kv` (the reference reads them too: the shared-max bounds are Python ints).
+    ``obs_window`` is accepted for signature compatibility (unused, as in the reference).
+    """
+    from .knapsack_solver import (DEFAULT_EPSILON_K, DEFAULT_EPSILON_V, k_average_bits_per_head,
+                                  knapsack_bit_allocation_batched, v_average_bits)
+    from .scoring import apply_score_pooling
+    assert K.dim() == 4 and V.dim() == 4, f"K/V must be [1,H_kv,T,D], got {tuple(K.shape)}/{tuple(V.shape)}"
+    assert layer_scores.dim() == 2, f"layer_scores must be [H_kv,T], got {tuple(layer_scores.shape)}"
+    assert channel_scores.dim() == 2, f"channel_scores must be [H_kv, D], got {tuple(channel_scores.shape)}"
+    require_cuda(K, "K"); require_cuda(layer_scores, "layer_scores"); require_cuda(channel_scores, "channel_scores")
+    H_kv, T = int(layer_scores.shape[0]), int(layer_scores.shape[1])
+    head_dim = int(K.shape[3])
+    pooled = (apply_score_pooling(layer_scores, pool_type, pool_kernel_size, pool_padding)
+              if pool_kernel_size > 1 else layer_scores).float()
+    v_bits = knapsack_bit_allocation_batched(
+        pooled, v_average_bits(token_budget, head_dim, T, k_budget_ratio),
+        epsilon=DEFAULT_EPSILON_V if eps_V is None else eps_V, bit_options=v_bit_options)       # [H_kv,T]
+    kept = (v_bits > 0).sum(dim=1)                                                               # stays on the device
+    k_bits = knapsack_bit_allocation_batched(
+        channel_scores.float(), k_average_bits_per_head(token_budget, head_dim, k_budget_ratio, kept),
+        epsilon=DEFAULT_EPSILON_K if eps_K is None else eps_K, bit_options=k_bit_options)       # [H_kv,D]
+    K = torch.where((k_bits == 0)[None, :, None, :], torch.zeros_like(K), K)                   # evicted channels
+    layer, new_v_only = pack_kv(K, V, v_bits, k_bits, gqa_factor, build_mask=build_mask)
+    return layer, new_v_only, int(layer.T_eff)
+
+
 def pack_kv_layers(Ks: Sequence[Tensor], Vs: Sequence[Tensor], v_bits: Tensor, k_bits: Tensor, gqa_factor: int, *,
                    build_mask: bool = True, launch_events: Optional[list] = None) -> PackedLayerBatch:
     """:func:`pack_kv` for all layers of a cache at once (the reference packs a prefilled

@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own
 Python code (PyTorch CPU kernels) on seeded inputs.
 
-    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack]
+    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack] [select]
     (or RDKV_REFERENCE=/path/to/reference/checkout in the environment; no part named = all)
 
 The reference checkout is only needed to (re)generate the files; the tests read
@@ -80,8 +80,12 @@ def ref_pack_kv(K, V, v_bits, k_bits, g):
         k_bits_per_head=k_bits)
 
 
-def ref_attend(q, pl, new_v_only, D):
-    """Reference dequantise-then-attend (trizone_decompress.py:185 + fp32 softmax attention)."""
+def ref_attend(q, pl, new_v_only, D, tail_k=None, tail_v=None):
+    """Reference dequantise-then-attend (trizone_decompress.py:185 + fp32 softmax attention).  With
+    tail_k / tail_v [H_kv,n,D] (tokens appended while decoding, kept uncompressed) the softmax runs
+    over the packed zones and the tail together, as the reference's attention block computes it
+    (fast_decode.py:1719-1784: scores of the tail use q/sqrt(D), one softmax over the concatenation,
+    out = weights_old . V_old + weights_new . V_new)."""
     cache = P.TriZoneCache(packed=(pl,), new_v_only=[new_v_only], new_both_k=[None], new_both_v=[None],
                            original_seq_len=0)
     (K_hat, V_hat), = TD.unpack_trizone_to_past_kv(cache, head_dim=D)
@@ -89,6 +93,12 @@ def ref_attend(q, pl, new_v_only, D):
     Kx = K_hat[0].float().repeat_interleave(g, 0)
     Vx = V_hat[0].float().repeat_interleave(g, 0)
     s = torch.einsum("hd,htd->ht", q.float(), Kx) / (D ** 0.5) + pl.softmax_mask
+    if tail_k is not None:
+        s_new = torch.bmm((q.float() / (D ** 0.5)).unsqueeze(1), tail_k.float().repeat_interleave(g, 0).transpose(1, 2)).squeeze(1)
+        w = torch.softmax(torch.cat([s, s_new], dim=-1), dim=-1)
+        w_old, w_new = w[:, :s.shape[1]], w[:, s.shape[1]:]
+        out = torch.einsum("ht,htd->hd", w_old, Vx) + torch.bmm(w_new.unsqueeze(1), tail_v.float().repeat_interleave(g, 0)).squeeze(1)
+        return out, K_hat, V_hat
     w = torch.softmax(s, dim=-1)
     return torch.einsum("ht,htd->hd", w, Vx), K_hat, V_hat
 
@@ -132,8 +142,13 @@ def case_layer(tag, H_kv, g, T, N, seed, per_head_N=None, k_mix=((8, 16), (4, 24
     pl, nv = ref_pack_kv(K, V, v_bits, k_bits, g)
     att, _, _ = ref_attend(q, pl, nv, 128)
     scores = k_mixed_qk_dot_ref(q, pl, pl.T_eff_k)
+    gen = torch.Generator().manual_seed(seed + 5)
+    tail_k = torch.randn(H_kv, 19, 128, generator=gen).half()       # decode-appended tokens (Zone C)
+    tail_v = torch.randn(H_kv, 19, 128, generator=gen).half()
+    att_tail, _, _ = ref_attend(q, pl, nv, 128, tail_k, tail_v)
     out = {f"{tag}_K": npy(K), f"{tag}_V": npy(V), f"{tag}_v_bits": npy(v_bits), f"{tag}_k_bits": npy(k_bits),
            f"{tag}_q": npy(q), f"{tag}_attn_out": npy(att), f"{tag}_k_scores": npy(scores),
+           f"{tag}_tail_k": npy(tail_k), f"{tag}_tail_v": npy(tail_v), f"{tag}_attn_out_tail": npy(att_tail),
            f"{tag}_g": np.asarray(g)}
     if nv is not None:
         out[f"{tag}_new_v_only"] = npy(nv)
@@ -167,6 +182,16 @@ def case_knapsack():
         out[f"{name}_tol"] = np.asarray(c.get("tol", 0.01), dtype=np.float64)
         out[f"{name}_bit_options"] = npy(c.get("bit_options", torch.tensor([0., 2., 4., 8., 16.])))
         out[f"{name}_bits"] = npy(res)
+    # the scalar form (knapsack_solver.py:39-118: bisection in Python floats, no clamp of lambda_hi),
+    # row by row, on rows that converge early, late, never, and on an all-zero row
+    sc = torch.cat([synth.make_scores(3, 512, seed=2010), torch.zeros(1, 512), synth.make_scores(2, 512, seed=2011, sigma=0.3)])
+    budgets = [2.0, 0.7, 9.0, 2.0, 2.0, 15.5]
+    out["scalar_scores"] = npy(sc)
+    out["scalar_budget"] = np.asarray(budgets, np.float32)
+    out["scalar_bits"] = np.stack([npy(KS.knapsack_bit_allocation(sc[i], budgets[i], epsilon=eps, max_iters=60))
+                                   for i in range(sc.shape[0])])
+    out["scalar_tight_bits"] = np.stack([npy(KS.knapsack_bit_allocation(sc[i], budgets[i], epsilon=eps, max_iters=60, tol=1e-6))
+                                         for i in range(sc.shape[0])])
     # default-epsilon call, as the reference's smoke test makes it
     s = synth.make_scores(2, 512, seed=2007, sigma=1.0)
     out["defeps_scores"] = npy(s)
@@ -252,8 +277,40 @@ def make_unpack():
     print("unpack.npz", os.path.getsize(os.path.join(HERE, "unpack.npz")), "bytes")
 
 
+def make_select():
+    """The reference's per-layer composite _perhead_select_and_pack_joint (obkv_fast.py:899-1186) on CPU:
+    pooling -> V allocation -> per-head K budget -> K allocation -> channel eviction -> pack."""
+    import obkv_fast as ref_fast
+    out = {}
+    cases = {
+        "a": dict(H_kv=2, g=4, T=512, budget=128, kr=0.5, pool=5, seed=7001),
+        "b": dict(H_kv=3, g=2, T=384, budget=64, kr=0.35, pool=1, seed=7002),
+    }
+    for tag, c in cases.items():
+        K, V = synth.make_kv(c["H_kv"], c["T"], seed=c["seed"])
+        gen = torch.Generator().manual_seed(c["seed"] + 1)
+        tok = torch.exp(1.2 * torch.randn(c["H_kv"], c["T"], generator=gen))
+        if tag == "b":
+            tok[1] *= 1e-3                                  # a head that keeps much less: another K budget
+        ch = torch.exp(torch.randn(c["H_kv"], 128, generator=gen))
+        pl, nv, t_eff = ref_fast._perhead_select_and_pack_joint(
+            K, V, tok, ch, gqa_factor=c["g"], token_budget=c["budget"], k_budget_ratio=c["kr"], obs_window=32,
+            pool_kernel_size=c["pool"], pool_padding="reflect", pool_type="avg", v_bit_options=None,
+            k_bit_options=None, eps_V=dict(KS.DEFAULT_EPSILON_V), eps_K=dict(KS.DEFAULT_EPSILON_K))
+        out.update({f"{tag}_K": npy(K), f"{tag}_V": npy(V), f"{tag}_token_scores": npy(tok), f"{tag}_channel_scores": npy(ch),
+                    f"{tag}_args": np.asarray([c["g"], c["budget"], c["pool"]], np.int64),
+                    f"{tag}_k_budget_ratio": np.asarray(c["kr"], np.float64), f"{tag}_t_eff": np.asarray(t_eff, np.int64)})
+        if nv is not None:
+            out[f"{tag}_new_v_only"] = npy(nv)
+        out.update(layer_to_dict(pl, tag + "_"))
+    np.savez_compressed(os.path.join(HERE, "select.npz"), **out)
+    print("select.npz", os.path.getsize(os.path.join(HERE, "select.npz")), "bytes")
+
+
 if __name__ == "__main__":
-    parts = sys.argv[2:] or ["layers", "scoring", "unpack"]
+    parts = sys.argv[2:] or ["layers", "scoring", "unpack", "select"]
+    if "select" in parts:
+        make_select()
     if "layers" in parts:
         main()
     if "scoring" in parts:

@@ -108,6 +108,29 @@ def test_fused_batch_of_views_and_partials():
     assert_attn_close(to_np(again).reshape(len(shapes), H_kv * g, 128)[0], wants[0][0], "combine identity")
 
 
+@pytest.mark.parametrize("tag", ["even", "ragged", "gqa8"])
+def test_uncompressed_tail_matches_reference_vectors(golden_layers, tag):
+    """One softmax over the packed zones and the tokens appended while decoding, against the
+    reference's formula (fast_decode.py:1719-1784) evaluated on the reference's own dequantised
+    cache: fp16 and fp32 tail buffers, the tail as a row count and as a per-view tensor."""
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention
+    g = sub(golden_layers, tag)
+    H_q = g["q"].shape[0]
+    pl, nv = _packed(g)
+    n = g["tail_k"].shape[1]
+    for dt in (torch.float16, torch.float32):
+        cap = n + 5
+        new_k = torch.zeros((1, g["tail_k"].shape[0], cap, 128), dtype=dt, device="cuda")
+        new_v = torch.zeros_like(new_k)
+        new_k[0, :, :n] = cuda(g["tail_k"]).to(dt)
+        new_v[0, :, :n] = cuda(g["tail_v"]).to(dt)
+        table = DecodeTable([pl], [nv], H_q)
+        for count in (n, torch.tensor([n], dtype=torch.int32, device="cuda")):
+            out = packed_decode_attention(cuda(g["q"]).reshape(1, H_q, 128), table, new_k=new_k, new_v=new_v, n_new=count)
+            assert_attn_close(to_np(out[0]), g["attn_out_tail"], f"{tag} tail {dt}")
+        table.check_status()
+
+
 @pytest.mark.parametrize("kv_dtype", [torch.float32, torch.float16, torch.bfloat16])
 def test_uncompressed_tail_joins_the_softmax(kv_dtype):
     """Zone C (decode-appended fp rows) is part of the same softmax as the packed zones:
@@ -303,6 +326,52 @@ def test_persistent_form_equals_the_one_item_form():
             assert torch.equal(ra, rb), (n_views, forced)
             one.check_status(); per.check_status()
             assert int(per.unit_ctr.abs().sum().item()) == 0
+
+
+def test_cached_views_follow_reassigned_fields_and_counts_rewritten_in_place():
+    """The one-view tables that the layer-level operators cache on the layer object are keyed by the
+    identity of every tensor they point into: a field that is re-assigned (another packing of the
+    same shape) is seen by the next call; per-head counts rewritten in place are read at launch."""
+    import dataclasses
+    from rdkv_b200 import synth
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention, packed_layer_attention
+    from rdkv_b200.k_kernel import k_mixed_qk_dot
+    from rdkv_b200.packing import pack_kv
+    from rdkv_b200.v_kernel import v_dequant_weighted_sum_dispatch
+    H_kv, g, T, N = 2, 4, 512, 256
+    packs = []
+    for i in range(2):
+        seed = synth.unit_seed(9, i, 1)
+        K, V = synth.make_kv(H_kv, T, seed=seed)
+        packs.append(pack_kv(K.cuda(), V.cuda(), synth.make_v_bits(H_kv, T, N, seed=seed).cuda(),
+                             synth.make_k_bits(H_kv, seed=seed).cuda(), g))
+    (pa, nva), (pb, nvb) = packs
+    q = synth.make_q(H_kv * g, seed=3).cuda()
+    w = torch.softmax(torch.randn(H_kv * g, pa.T_eff_k, device="cuda"), dim=-1)
+    want_b = packed_layer_attention(q, pb, nvb).clone()
+    want_sb = k_mixed_qk_dot(q, pb, pb.T_eff_k).clone()
+    want_vb = v_dequant_weighted_sum_dispatch(w, pb, V16=nvb[0], n_v16_per_head=pb.n_v16_per_head, max_T_v=pb.T_eff).clone()
+    out_a = packed_layer_attention(q, pa, nva).clone()
+    k_mixed_qk_dot(q, pa, pa.T_eff_k)
+    v_dequant_weighted_sum_dispatch(w, pa, V16=nva[0], n_v16_per_head=pa.n_v16_per_head, max_T_v=pa.T_eff)
+    assert not torch.equal(out_a, want_b)
+    for f in dataclasses.fields(pb):                        # the same object now holds the other packing
+        setattr(pa, f.name, getattr(pb, f.name))
+    assert torch.equal(packed_layer_attention(q, pa, nvb), want_b)
+    assert torch.equal(k_mixed_qk_dot(q, pa, pa.T_eff_k), want_sb)
+    assert torch.equal(v_dequant_weighted_sum_dispatch(w, pa, V16=nvb[0], n_v16_per_head=pa.n_v16_per_head,
+                                                       max_T_v=pa.T_eff), want_vb)
+    # counts rewritten in place: the layer-level call reads them at every launch; a table snapshots
+    # them and follows after refresh()
+    table = DecodeTable([pb], [nvb], H_kv * g)
+    before = packed_decode_attention(q[None], table).clone()
+    pb.seg_bounds_per_head[0, 2] -= 32                      # head 0 loses its last 32 8-bit rows
+    layer_level = packed_layer_attention(q, pb, nvb).clone()
+    assert not torch.equal(layer_level, before[0])
+    assert torch.equal(packed_decode_attention(q[None], table), before)        # snapshot: unchanged until refreshed
+    table.refresh()
+    assert torch.equal(packed_decode_attention(q[None], table)[0], layer_level)
+    pb.seg_bounds_per_head[0, 2] += 32
 
 
 def test_host_buffer_call_equals_device_call():

@@ -83,3 +83,24 @@ def test_long_rows_and_budget_property():
     # monotone in the score: a higher score never gets fewer bits within a row
     order = torch.argsort(s[0])
     assert torch.all(bits[0][order][1:] >= bits[0][order][:-1])
+
+
+def test_scalar_form_matches_the_reference_scalar_solver(golden_knapsack):
+    """knapsack_bit_allocation (one row, double-precision bisection) against rows solved by the
+    reference's own scalar function: early, late and never converging rows, an all-zero row, and
+    the same rows with a tolerance that is never met; and against the oracle on a config-2 row."""
+    from oracle.ref_knapsack import knapsack_scalar
+    from rdkv_b200 import synth
+    from rdkv_b200.knapsack_solver import knapsack_bit_allocation
+    g = golden_knapsack
+    eps = synth.ALLOC_EPSILON
+    for i in range(g["scalar_scores"].shape[0]):
+        s = cuda(g["scalar_scores"][i])
+        got = knapsack_bit_allocation(s, float(g["scalar_budget"][i]), epsilon=eps, max_iters=60)
+        assert got.dtype == torch.int64 and np.array_equal(to_np(got), g["scalar_bits"][i]), i
+        got = knapsack_bit_allocation(s, float(g["scalar_budget"][i]), epsilon=eps, max_iters=60, tol=1e-6)
+        assert np.array_equal(to_np(got), g["scalar_tight_bits"][i]), i
+    row = synth.make_scores(1, 32768, seed=synth.unit_seed(2, 3))[0]
+    for budget in (2.0, 0.3, 11.0):
+        got = knapsack_bit_allocation(row.cuda(), budget, epsilon=eps, max_iters=60, tol=1e-4)
+        assert np.array_equal(to_np(got), knapsack_scalar(row.numpy(), budget, eps, max_iters=60, tol=1e-4)), budget

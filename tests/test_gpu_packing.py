@@ -297,3 +297,26 @@ def test_full_size_properties():
     for f in ["K_2bit", "K_4bit", "K_8bit"]:
         assert np.array_equal(to_np(getattr(packed, f))[:, 2:4], want[f]), f
     assert np.array_equal(to_np(packed.V_scale)[:, 2:4], want["V_scale"])
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_select_and_pack_matches_the_reference_composite(tag):
+    """select_and_pack (pooling -> V allocation -> per-head K budget -> K allocation -> eviction ->
+    pack, all on the device) against the reference's own _perhead_select_and_pack_joint run on CPU:
+    every field of the packed layer, the fp16 rows and T_eff, bit for bit."""
+    from conftest import load_golden
+    from rdkv_b200.knapsack_solver import DEFAULT_EPSILON_K, DEFAULT_EPSILON_V
+    from rdkv_b200.packing import select_and_pack
+    g = sub(load_golden("select.npz"), tag)
+    gq, budget, pool = (int(x) for x in g["args"])
+    pl, nv, t_eff = select_and_pack(
+        cuda(g["K"]), cuda(g["V"]), cuda(g["token_scores"]), cuda(g["channel_scores"]), gqa_factor=gq,
+        token_budget=budget, k_budget_ratio=float(g["k_budget_ratio"]), obs_window=32, pool_kernel_size=pool,
+        pool_padding="reflect", pool_type="avg", v_bit_options=None, k_bit_options=None,
+        eps_V=DEFAULT_EPSILON_V, eps_K=DEFAULT_EPSILON_K)
+    assert_layer_equal(layer_to_np(pl), g, tag + ".")
+    assert t_eff == int(g["t_eff"])
+    if "new_v_only" in g:
+        assert np.array_equal(to_np(nv), g["new_v_only"])
+    else:
+        assert nv is None

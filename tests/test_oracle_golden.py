@@ -132,3 +132,45 @@ def test_dequantise_matches_reference(golden_layers, tag):
     v_hat = RP.unpack_v(layer, nv, 128)
     assert np.array_equal(v_hat.view(np.uint16), u["V_hat"].view(np.uint16))
     assert np.array_equal(v_hat[:, :, :layer["T_eff"]].view(np.uint16), u["zone_a"].view(np.uint16))
+
+
+def test_scalar_knapsack_matches_reference(golden_knapsack):
+    """The single-row solver (double-precision bisection): rows that converge early, late and never, an
+    all-zero row, and the same rows with a tolerance that is never met."""
+    from rdkv_b200.synth import ALLOC_EPSILON
+    g = golden_knapsack
+    for i in range(g["scalar_scores"].shape[0]):
+        got = RK.knapsack_scalar(g["scalar_scores"][i], float(g["scalar_budget"][i]), ALLOC_EPSILON, max_iters=60)
+        assert np.array_equal(got, g["scalar_bits"][i]), i
+        got = RK.knapsack_scalar(g["scalar_scores"][i], float(g["scalar_budget"][i]), ALLOC_EPSILON, max_iters=60, tol=1e-6)
+        assert np.array_equal(got, g["scalar_tight_bits"][i]), i
+
+
+@pytest.mark.parametrize("tag", ["even", "ragged", "gqa8"])
+def test_attention_with_uncompressed_tail_matches_reference(golden_layers, tag):
+    """One softmax over the packed zones and the tokens appended while decoding (Zone C): the oracle
+    against the reference's formula evaluated on the reference's own dequantised cache."""
+    g = sub(golden_layers, tag)
+    layer, nv = RP.pack_kv(g["K"], g["V"], g["v_bits"], g["k_bits"], int(g["g"]))
+    out, _, _ = RA.decode_attention(g["q"], layer, nv, g["tail_k"], g["tail_v"])
+    np.testing.assert_allclose(out, g["attn_out_tail"], rtol=1e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_select_and_pack_matches_reference(tag):
+    """Pooling -> V allocation -> per-head K budget -> K allocation -> eviction -> pack: every field of
+    the packed layer bit for bit against the reference's own per-layer composite."""
+    from conftest import load_golden
+    from oracle import ref_select as RSel
+    from rdkv_b200.knapsack_solver import DEFAULT_EPSILON_K, DEFAULT_EPSILON_V
+    g = sub(load_golden("select.npz"), tag)
+    gq, budget, pool = (int(x) for x in g["args"])
+    layer, nv, v_bits, k_bits = RSel.select_and_pack(
+        g["K"], g["V"], g["token_scores"], g["channel_scores"], gqa_factor=gq, token_budget=budget,
+        k_budget_ratio=float(g["k_budget_ratio"]), pool_kernel_size=pool, eps_V=DEFAULT_EPSILON_V, eps_K=DEFAULT_EPSILON_K)
+    assert_layer_equal(layer, g, tag + ".")
+    assert int(g["t_eff"]) == layer["T_eff"]
+    if "new_v_only" in g:
+        assert np.array_equal(nv, g["new_v_only"])
+    else:
+        assert nv is None
