@@ -334,6 +334,19 @@ int rdkv_score_pool(const float* scores, int64_t row_stride, int rows, int len, 
                     int kernel_size, int reflect, float* out, int64_t out_row_stride, int out_len,
                     void* stream);
 
+/* ── decode: scores of a block of generated tokens for its recompression ──────
+ * Replaces _score_block and _channel_score of the blockwise decoder
+ * (obkv_accel/blockwise_decode.py:756-810).  queries: [H_kv*g][Q][D] (element strides between
+ * heads and between positions given), keys: [H_kv][T][D] (strides given); T <= 256, D <= 128.
+ *   token_out   fp32 [H_kv][T] = sum over the head's g query heads and Q positions of
+ *               softmax_t(q.k_t / sqrt(D)); causal != 0: position i sees keys t <= i (Q == T);
+ *               NULL = channel statistic only;
+ *   channel_out fp32 [H_kv][D] = mean_{g,Q}(q_d^2) * mean_t(k_d^2). */
+int rdkv_block_scores(const void* queries, int q_dtype, int64_t q_head_stride, int64_t q_pos_stride,
+                      const void* keys, int k_dtype, int64_t k_head_stride, int64_t k_row_stride,
+                      int H_kv, int g, int Q, int T, int D, int causal, float* token_out,
+                      float* channel_out, void* stream);
+
 /* ── packed layer -> fp16 K, V ────────────────────────────────────────────────
  * Replaces unpack_k_mixed (obkv_accel/packing.py:581-709), unpack_v_segment (:1427-1444) and the
  * per-layer body of unpack_trizone_to_past_kv (obkv_accel/trizone_decompress.py:43-183, 247-290):

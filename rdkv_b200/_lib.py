@@ -99,6 +99,7 @@ _PROTOTYPES = {
     "rdkv_score_chunks": ([_i], _i),
     "rdkv_score_layer": ([_p, _i, _p, _i, _p, _i, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p], _i),
     "rdkv_score_pool": ([_p, _i64, _i, _i, _i, _i, _i, _p, _i64, _i, _p], _i),
+    "rdkv_block_scores": ([_p, _i, _i64, _i64, _p, _i, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p], _i),
     "rdkv_unpack_layer": ([_p, _i, _i, _p, _i64, _p, _i, _i, _i, _p, _p, _i64, _i, _p], _i),
     "rdkv_sizeof_pack_job": ([], _i),
     "rdkv_pack_kv_batched": ([_p, _i, _i, _i, _i, _i, _i, _p], _i),

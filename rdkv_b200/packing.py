@@ -423,8 +423,8 @@ def select_and_pack(K: Tensor, V: Tensor, layer_scores: Tensor, channel_scores: 
                     token_budget: int, k_budget_ratio: float, obs_window: int = 0, pool_kernel_size: int = 5,
                     pool_padding: str = "reflect", pool_type: str = "avg", v_bit_options: Optional[Tensor] = None,
                     k_bit_options: Optional[Tensor] = None, eps_V: Optional[dict] = None,
-                    eps_K: Optional[dict] = None, build_mask: bool = True
-                    ) -> Tuple[PackedKVLayer, Optional[Tensor], int]:
+                    eps_K: Optional[dict] = None, build_mask: bool = True,
+                    retain_allocation_metadata: bool = False) -> Tuple[PackedKVLayer, Optional[Tensor], int]:
     """One layer of the prefill: pool the token scores, allocate V bits per head, derive every head's
     K budget from the tokens it kept, allocate K bits, drop the evicted channels and pack — the
     reference's per-layer composite ``_perhead_select_and_pack_joint`` (obkv_fast.py:899-1186) with
@@ -433,7 +433,9 @@ def select_and_pack(K: Tensor, V: Tensor, layer_scores: Tensor, channel_scores: 
     K, V [1,H_kv,T,D] fp16, layer_scores [H_kv,T], channel_scores [H_kv,D], all on the GPU.
     Everything stays on the device: the only host read is the one of the segment counts inside
     :func:`pack_kv` (the reference reads them too: the shared-max bounds are Python ints).
-    ``obs_window`` is accepted for signature compatibility (unused, as in the reference).
+    ``obs_window`` is accepted for signature compatibility (unused, as in the reference);
+    ``retain_allocation_metadata`` keeps the allocator's decisions on the layer
+    (``allocation_v_bits`` / ``allocation_k_bits``), as the blockwise decoder's accounting wants.
     """
     from .knapsack_solver import (DEFAULT_EPSILON_K, DEFAULT_EPSILON_V, k_average_bits_per_head,
                                   knapsack_bit_allocation_batched, v_average_bits)
@@ -454,7 +456,8 @@ def select_and_pack(K: Tensor, V: Tensor, layer_scores: Tensor, channel_scores: 
         channel_scores.float(), k_average_bits_per_head(token_budget, head_dim, k_budget_ratio, kept),
         epsilon=DEFAULT_EPSILON_K if eps_K is None else eps_K, bit_options=k_bit_options)       # [H_kv,D]
     K = torch.where((k_bits == 0)[None, :, None, :], torch.zeros_like(K), K)                   # evicted channels
-    layer, new_v_only = pack_kv(K, V, v_bits, k_bits, gqa_factor, build_mask=build_mask)
+    layer, new_v_only = pack_kv(K, V, v_bits, k_bits, gqa_factor, build_mask=build_mask,
+                                retain_allocation_metadata=retain_allocation_metadata)
     return layer, new_v_only, int(layer.T_eff)
 
 

@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own
 Python code (PyTorch CPU kernels) on seeded inputs.
 
-    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack] [select]
+    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack] [select] [blockwise]
     (or RDKV_REFERENCE=/path/to/reference/checkout in the environment; no part named = all)
 
 The reference checkout is only needed to (re)generate the files; the tests read
@@ -307,8 +307,85 @@ def make_select():
     print("select.npz", os.path.getsize(os.path.join(HERE, "select.npz")), "bytes")
 
 
+def make_blockwise():
+    """Blockwise recompression: the reference's planner, block scoring and _compress_block on CPU
+    (obkv_accel/blockwise_decode.py:89-140, 756-810, 812-1121), and attention over several packed
+    sources plus a tail, evaluated on the reference's own dequantised caches."""
+    import obkv_fast as ref_fast                                # noqa: F401  (resolves the decoder's lazy import)
+    from obkv_accel import blockwise_decode as BD
+    out = {}
+    # planner: the reference tests' cases and a sweep
+    cases = [(512, 64), (128, 64), (192, 64), (127, 64), (0, 64), (1, 64), (64, 64), (65, 64), (129, 128), (700, 128)]
+    out["plan_cases"] = np.asarray(cases, np.int64)
+    for n, bs in cases:
+        ev = BD.plan_block_compressions(n, bs)
+        out[f"plan_{n}_{bs}"] = np.asarray(
+            [[e["block_id"], e["token_start"], e["token_end"], e["query_source_block"], int(e["is_final_flush"]),
+              int(e["query_mode"] == "self_causal")] for e in ev], np.int64).reshape(-1, 6)
+    # block scoring: the shapes of the reference's own test (seed 7) and block-sized ones
+    torch.manual_seed(7)
+    q = torch.randn(4, 5, 8); k = torch.randn(1, 2, 4, 8)
+    tok, ch = BD._score_block(q, k, num_kv_groups=2, causal=False)
+    out.update(score_t_q=npy(q), score_t_k=npy(k), score_t_token=npy(tok), score_t_channel=npy(ch))
+    gen = torch.Generator().manual_seed(31)
+    for tag, (hkv, g, Q, T, dt, causal) in {"next": (2, 4, 64, 64, torch.float16, False),
+                                            "self": (2, 4, 37, 37, torch.float16, True),
+                                            "wide": (1, 8, 128, 128, torch.float32, False)}.items():
+        q = torch.randn(hkv * g, Q, 128, generator=gen).to(dt)
+        k = torch.randn(1, hkv, T, 128, generator=gen).to(dt)
+        tok, ch = BD._score_block(q, k, num_kv_groups=g, causal=causal)
+        out.update({f"score_{tag}_q": npy(q.float()), f"score_{tag}_k": npy(k.float()), f"score_{tag}_token": npy(tok),
+                    f"score_{tag}_channel": npy(ch), f"score_{tag}_args": np.asarray([g, int(causal), int(dt == torch.float16)])})
+    # one block of 64 generated tokens, two layers, through the reference's _compress_block
+    hkv, g, T, D = 2, 2, 64, 128
+    cfg = BD.BlockwiseRDKVConfig(block_size=64, block_budget_tokens=8, k_budget_ratio=0.5, obs_window=32,
+                                 pool_kernel_size=5, pool_padding="reflect", v_bit_options=None, k_bit_options=None,
+                                 epsilon_v=dict(KS.DEFAULT_EPSILON_V), epsilon_k=dict(KS.DEFAULT_EPSILON_K))
+    kvs, qs, toks = [], [], []
+    for layer in range(2):
+        K, V = synth.make_kv(hkv, T, seed=8100 + layer)
+        kvs.append(torch.cat([K, V], dim=-1))
+        qb = torch.randn(hkv * g, 64, D, generator=gen).half()
+        qs.append(qb)
+        toks.append(BD._score_block(qb, K, num_kv_groups=g, causal=False)[0])
+    block, _ = BD._compress_block(target_kv=kvs, query_block=qs, token_scores_by_layer=toks, block_id=0, token_start=0,
+                                  token_end=63, query_source_block=1, is_final_flush=False, causal=False, config=cfg,
+                                  num_kv_groups=g, model_dtype=torch.float16)
+    out["block_args"] = np.asarray([hkv, g, T], np.int64)
+    for layer in range(2):
+        out[f"block_l{layer}_kv"] = npy(kvs[layer]); out[f"block_l{layer}_q"] = npy(qs[layer].float())
+        out[f"block_l{layer}_token_scores"] = npy(toks[layer])
+        out.update(layer_to_dict(block.packed[layer], f"block_l{layer}_"))
+        if block.new_v_only[layer] is not None:
+            out[f"block_l{layer}_new_v_only"] = npy(block.new_v_only[layer])
+    out["block_logical_bits"] = np.asarray(block.logical_bits_per_layer, np.int64)
+    # attention over the prompt's layer, the block's layer 0 and a tail: one softmax over everything
+    Kp, Vp = synth.make_kv(hkv, 384, seed=8200)
+    vbp = synth.make_v_bits(hkv, 384, 128, seed=8200)
+    kbp = synth.make_k_bits(hkv, seed=8200)
+    prompt, prompt_nv = ref_pack_kv(Kp, Vp, vbp, kbp, g)
+    qd = synth.make_q(hkv * g, seed=8201)
+    tail_k = torch.randn(hkv, 9, D, generator=gen).half(); tail_v = torch.randn(hkv, 9, D, generator=gen).half()
+    ks, vs, masks = [], [], []
+    for pl, nv in ((prompt, prompt_nv), (block.packed[0], block.new_v_only[0])):
+        cache = P.TriZoneCache(packed=(pl,), new_v_only=[nv], new_both_k=[None], new_both_v=[None], original_seq_len=0)
+        (K_hat, V_hat), = TD.unpack_trizone_to_past_kv(cache, head_dim=D)
+        ks.append(K_hat[0].float().repeat_interleave(g, 0)); vs.append(V_hat[0].float().repeat_interleave(g, 0))
+        masks.append(pl.softmax_mask)
+    ks.append(tail_k.float().repeat_interleave(g, 0)); vs.append(tail_v.float().repeat_interleave(g, 0))
+    masks.append(torch.zeros(hkv * g, 9))
+    Kall, Vall, mall = torch.cat(ks, 1), torch.cat(vs, 1), torch.cat(masks, 1)
+    w = torch.softmax(torch.einsum("hd,htd->ht", qd.float(), Kall) / (D ** 0.5) + mall, dim=-1)
+    out.update(ms_K=npy(Kp), ms_V=npy(Vp), ms_v_bits=npy(vbp), ms_k_bits=npy(kbp), ms_q=npy(qd), ms_tail_k=npy(tail_k),
+               ms_tail_v=npy(tail_v), ms_attn_out=npy(torch.einsum("ht,htd->hd", w, Vall)))
+    np.savez_compressed(os.path.join(HERE, "blockwise.npz"), **out)
+    print("blockwise.npz", os.path.getsize(os.path.join(HERE, "blockwise.npz")), "bytes")
+
+
 if __name__ == "__main__":
-    parts = sys.argv[2:] or ["layers", "scoring", "unpack", "select"]
+    parts = sys.argv[2:] or ["layers", "scoring", "unpack", "select", "blockwise"]
+    if "blockwise" in parts:
+        make_blockwise()
     if "select" in parts:
         make_select()
     if "layers" in parts:
