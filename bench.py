@@ -198,7 +198,7 @@ def repeated_regions(fn, steps, barrier, world, device, *, min_reps=10, target_m
 
 
 def measure_decode(cfg, rank, world, device, *, steps, warmup, seq_parts=1, chunks=None, want_e2e=False,
-                   e2e_slices=None, small=False):
+                   e2e_slices=None, small=False, e2e_graph=None):
     """One decode workload on this rank's share: KV heads sharded over world/seq_parts head groups,
     the live rows of every head split over seq_parts ranks (row windows of the same packed layer,
     records merged after one all-gather per step).  Returns a dict of timings and byte counts
@@ -287,13 +287,16 @@ def measure_decode(cfg, rank, world, device, *, steps, warmup, seq_parts=1, chun
            "n_views": n_views, "Hq_loc": Hq_loc}
     if want_e2e:
         # end to end through the public call with host buffers: pinned q in, pinned out back, every step
-        q_host = [q.cpu().pin_memory() for q in q_pool[:min(n_q, 8)]]
+        # (two query buffers in turn; the call records each (buffer, table) pair's copies and launches
+        # as a graph on its second use and replays it afterwards, so every pair is warmed up twice)
+        q_host = [q.cpu().pin_memory() for q in q_pool[:min(n_q, 2)]]
         out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
 
         def e2e_step(i):
-            packed_decode_attention_host(q_host[i % len(q_host)], tables[i % R], out_host, slices=e2e_slices)
+            packed_decode_attention_host(q_host[i % len(q_host)], tables[i % R], out_host, slices=e2e_slices,
+                                         graph=e2e_graph)
 
-        for i in range(min(warmup, 3)):
+        for i in range(max(min(warmup, 3), 2 * len(q_host) * R + 1)):
             e2e_step(i)
         with sampler:
             e2e_ms, e2e_timing = repeated_regions(e2e_step, steps, barrier, world, device, min_reps=5, target_ms=30.0)
@@ -314,7 +317,8 @@ def run_decode(args, rank, world, device):
     if args.layers:
         cfg.update(layers=args.layers)
     m = measure_decode(cfg, rank, world, device, steps=args.steps, warmup=args.warmup, chunks=args.chunks,
-                       want_e2e=True, e2e_slices=args.e2e_slices, small=args.small)
+                       want_e2e=True, e2e_slices=args.e2e_slices, small=args.small,
+                       e2e_graph=None if args.e2e_graph is None else bool(args.e2e_graph))
     t0 = m["tables"][0]
     k_rest, rows_rest, n_whole = t0.plan(t0.n_views)
     h0, h1 = m["h"]
@@ -719,13 +723,96 @@ def run_alloc(args, rank, world, device):
     return line
 
 
+def run_aux(args, rank, world, device):
+    """The small kernels around the hot path, each timed alone on config-3-sized inputs: the
+    decompressor (one launch per layer), the uncompressed-tail kernel, the log-sum-exp combine, block
+    scoring of the blockwise decoder and the token / channel partition.  One step = each of them once."""
+    if rank != 0:
+        return None
+    from rdkv_b200 import synth
+    from rdkv_b200.blockwise import _score_block
+    from rdkv_b200.decode import DecodeTable, lse_combine, packed_decode_attention, tail_attention_partial
+    from rdkv_b200.decompress import unpack_trizone_to_past_kv
+    from rdkv_b200.packing import TriZoneCache, pack_kv, partition_by_bits
+    L, H, g, T, N = (args.layers or 8), 8, 4, 32768, 2048
+    layers, nvs = [], []
+    for layer in range(L):
+        seed = synth.unit_seed(3, layer, 0)
+        K, V = synth.make_kv(H, T, seed=seed, device=device)
+        pl, nv = pack_kv(K, V, synth.make_v_bits(H, T, N, seed=seed, device=device),
+                         synth.make_k_bits(H, seed=seed, device=device), g)
+        layers.append(pl); nvs.append(nv)
+        del K, V
+    cache = TriZoneCache(packed=tuple(layers), new_v_only=nvs, new_both_k=[None] * L, new_both_v=[None] * L,
+                         original_seq_len=T)
+    gen = torch.Generator(device=device); gen.manual_seed(5)
+    n_views, cap = 128, 1024
+    q = (torch.randn(n_views, H * g, 128, generator=gen, device=device) / 128 ** 0.5).half()
+    new_k = torch.randn(n_views, H, cap, 128, generator=gen, device=device).half()
+    new_v = torch.randn(n_views, H, cap, 128, generator=gen, device=device).half()
+    recs = torch.randn(512 * H * g, 2, 132, generator=gen, device=device)
+    recs[:, :, 1] = recs[:, :, 1].abs() + 0.5
+    bq = torch.randn(L, H * g, 64, 128, generator=gen, device=device).half()
+    bk = torch.randn(L, 1, H, 64, 128, generator=gen, device=device).half()
+    vbits = synth.make_v_bits(H * 32, T, 4096, seed=11, device=device).to(torch.int16)
+    kbits = synth.make_k_bits(H * 32, seed=11, device=device).to(torch.int16)
+    # the whole attention block of a decode step over 128 views (8 layers x batch 16 of config 3) with a
+    # 1024-row fp16 tail (the reference's latency protocol generates 1024 tokens): packed zones alone,
+    # the one-launch form (rotation, new token, tail, packed zones) and the three-launch form
+    cfg8 = dict(CFG3); cfg8.update(layers=8)
+    dl, dnv = build_decode_cache(cfg8, 0, H, 0, device)
+    dtab = DecodeTable(dl, dnv, H * g)
+    dbytes = sum(unit_bytes(pl, nv, None) for pl, nv in zip(dl, dnv))
+    k_cur = torch.randn(n_views, H, 128, generator=gen, device=device).half()
+    v_cur = torch.randn(n_views, H, 128, generator=gen, device=device).half()
+    pos = torch.rand(n_views, 64, generator=gen, device=device) * 500.0
+    rope = (torch.cos(pos), torch.sin(pos))
+    dout = torch.empty(n_views, H * g, 128, device=device)
+    tail_bytes = n_views * H * (cap - 1) * 128 * 2 * 2
+    parts = {
+        "decode block, packed zones only (decode_fused_kernel)": (lambda: packed_decode_attention(q, dtab, out=dout), dbytes),
+        "decode block, one launch: rotation + new token + 1023-row tail + packed zones (decode_fused_kernel, tail mode)": (
+            lambda: packed_decode_attention(q, dtab, out=dout, new_k=new_k, new_v=new_v, n_new=cap - 1, k_cur=k_cur,
+                                            v_cur=v_cur, rope=rope, append=False), dbytes + tail_bytes),
+        "decode block, three launches: packed zones + tail_attn_partial_kernel + lse_combine_kernel": (
+            lambda: packed_decode_attention(q, dtab, out=dout, new_k=new_k, new_v=new_v, n_new=cap - 1, one_launch=False),
+            dbytes + tail_bytes),
+        "unpack_layer_kernel": (lambda: unpack_trizone_to_past_kv(cache, head_dim=128),
+                                L * H * (N * (34 + 67.5) + 2 * N * 128 * 2)),
+        "tail_attn_partial_kernel": (lambda: tail_attention_partial(q, new_k, new_v, cap, H),
+                                     n_views * H * cap * 128 * 2 * 2),
+        "lse_combine_kernel": (lambda: lse_combine(recs), recs.numel() * 4 + recs.shape[0] * 128 * 4),
+        "block_score_kernel": (lambda: [_score_block(bq[l], bk[l], num_kv_groups=g, causal=False) for l in range(L)],
+                               L * (H * g * 64 + H * 64) * 128 * 2),
+        "partition_kernel": (lambda: (partition_by_bits(vbits, 0), partition_by_bits(kbits, 1)),
+                             vbits.numel() * 2 * 3 + kbits.numel() * 2 * 3),
+    }
+    peak, kind = load_peaks()
+    out = {}
+    sampler = ClockSampler(device.index or 0)
+    for name, (fn, nbytes) in parts.items():
+        for _ in range(args.warmup):
+            fn()
+        with sampler:
+            ms = timed_steps(lambda i: fn(), args.steps, lambda: None) / args.steps
+        out[name] = {"ms": ms, "algorithmic_bytes": int(nbytes), "gbs": nbytes / (ms / 1e3) / 1e9,
+                     "frac_of_hbm_peak": nbytes / (ms / 1e3) / 1e9 / peak}
+    return {"metric": "auxiliary kernels, ms per call", "value": sum(v["ms"] for v in out.values()), "unit": "ms",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp16 / u8", "data": "synthetic",
+            "config": {"workload": f"aux: decompress {L} config-3 layers; tail attention 128 views x 8 heads x 1024 rows; "
+                                   "combine 16384 x 2 records; block scores of 64-token blocks; partition 256 x 32768 maps"},
+            "kernels": out, "peak_kind": kind, "gpu_launches": args.steps * (1 + 1 + 3 + L + 1 + 1 + L + 2),
+            "clocks": sampler.summary()}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="rdkv_b200", choices=["rdkv_b200", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "decode-long", "pack", "alloc", "score"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode-long", "pack", "alloc", "score", "aux"])
     ap.add_argument("--seq-parts", type=int, default=1,
                     help="decode-long: ranks that split the live rows of the same heads (1 = KV-head sharding only)")
     ap.add_argument("--persistent", type=int, default=None, choices=[0, 1],
@@ -737,6 +824,8 @@ def main():
     ap.add_argument("--chunks", type=int, default=None, help="force this many chunks per (view, KV head) (default: planned)")
     ap.add_argument("--e2e-slices", type=int, default=None,
                     help="view ranges (streams) the host-buffer call overlaps its copies and kernels over")
+    ap.add_argument("--e2e-graph", type=int, choices=(0, 1), default=None,
+                    help="host-buffer call: 1 = replay a recorded graph, 0 = stream form (default: the call's own choice)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     global PERSISTENT
@@ -767,6 +856,8 @@ def main():
             line = run_pack(args, rank, world, device)
         elif args.workload == "score":
             line = run_score(args, rank, world, device)
+        elif args.workload == "aux":
+            line = run_aux(args, rank, world, device)
         else:
             line = run_alloc(args, rank, world, device)
         if rank == 0 and line is not None:

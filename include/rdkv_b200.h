@@ -155,6 +155,31 @@ int rdkv_decode_attn_partial(const rdkv_layer_view* views, int n_views, const vo
                              int H_q, int H_kv, int chunk_rows, int n_chunks, int k_row_bytes_max,
                              float* partials, float* out, int32_t* status, void* stream);
 
+/* The uncompressed tail and the token being decoded, for rdkv_decode_attn_tail.
+ * Replaces, together with the packed zones, the whole attention block of a decode step
+ * (obkv_accel/fast_decode.py:1644-1784): fused_rope on q and the new k (triton_rope.py:35-108),
+ * the append of the new K / V rows to the buffers of decode-generated tokens (:863-866) and one
+ * softmax over Zone A | Zone B | Zone C (:1719-1784). */
+typedef struct rdkv_tail_args {
+  void* new_k;                   /* [n_views][H_kv][cap][128] fp16 / bf16, rows contiguous; the   */
+  void* new_v;                   /*   tokens generated so far (Zone C); 16-byte aligned            */
+  int64_t view_stride;           /* elements between views (multiple of 8)                          */
+  int64_t head_stride;           /* elements between KV heads (multiple of 8)                       */
+  int32_t dtype;                 /* RDKV_F16 or RDKV_BF16: type of new_k, new_v, k_cur, v_cur       */
+  int32_t cap;                   /* rows each head's buffer holds                                   */
+  int32_t n_new;                 /* live rows of every view when n_new_per_view is NULL             */
+  int32_t rope_dtype;            /* type of rope_cos / rope_sin (RDKV_F16 / BF16 / F32)             */
+  const int32_t* n_new_per_view; /* device int32 [n_views] (clamped to [0, cap]), or NULL           */
+  const void* rope_cos;          /* [..][64] cosines / sines of the position (half format: channel  */
+  const void* rope_sin;          /*   i pairs with i + 64), or NULL / NULL: q and k_cur are rotated  */
+  int64_t rope_view_stride;      /* elements between views' tables (0: one table for all views)     */
+  const void* k_cur;             /* [n_views][H_kv][128] key / value row of the token being decoded */
+  const void* v_cur;             /*   (k_cur not yet rotated), or NULL / NULL: no such token        */
+  int32_t append;                /* 1: the rotated k_cur and v_cur are also written to row n_new of */
+  int32_t reserved;              /*   new_k / new_v (status bit 2 if the buffer is full)            */
+} rdkv_tail_args;
+int rdkv_sizeof_tail_args(void);           /* lets a binding check its struct layout */
+
 /* The same kernel with everything a decode step needs in ONE launch (new; same reference
  * block, obkv_accel/fast_decode.py:1701-1784):
  *   - seq_part / seq_parts: the sequence split.  Part i of n takes, of every head, rows
@@ -184,6 +209,27 @@ int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const void* q, i
                      int seq_part, int seq_parts, int k_row_bytes_max, const void* unit_recs, const void* k_slots, int nkb_max,
                      float* partials, int32_t* unit_counters, float* out, float* out_record,
                      int32_t* status, void* stream);
+
+/* rdkv_decode_attn plus the uncompressed tail in the same launch and the same softmax (one more
+ * tile phase of plain 16-bit K and V rows, scored on the tensor cores) and, optionally, the token
+ * being decoded: its key row is rotated like the queries, scored, weighted with its value row as
+ * the first term of the running softmax, and (append) written behind the tail for later steps;
+ * the queries are rotated on the way in (the caller's q is not written).  chunk_rows, row_begin /
+ * row_end and seq_part count the tail rows behind the fp16 rows of a head.  Always launches the
+ * one-item-per-CTA form of the kernel. */
+int rdkv_decode_attn_tail(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,
+                          int H_kv, int chunk_rows, int n_chunks, int n_whole_units, int row_begin, int row_end,
+                          int seq_part, int seq_parts, int k_row_bytes_max, const void* unit_recs,
+                          const void* k_slots, int nkb_max, float* partials, int32_t* unit_counters,
+                          float* out, float* out_record, int32_t* status, const rdkv_tail_args* tail,
+                          void* stream);
+
+/* fused_rope (obkv_accel/triton_rope.py:111-138) on its own: rotates n_q rows of q and n_k rows of
+ * k (128 channels each, row strides in elements) in place with one table of 64 cosines / sines;
+ * fp32 arithmetic with every product and sum rounded separately, result rounded to the rows'
+ * type (bit-identical to fused_rope_ref, :141-165). */
+int rdkv_rope(void* q, int q_dtype, int n_q, int64_t q_row_stride, void* k, int k_dtype, int n_k,
+              int64_t k_row_stride, const void* cos_half, const void* sin_half, int cs_dtype, void* stream);
 
 /* Persistent form of rdkv_decode_attn (same arguments and results): one resident CTA per slot
  * of the GPU goes through the launch's work items (whole units first, then chunks) in steps of the
@@ -321,12 +367,15 @@ int rdkv_tail_attn_partial(const void* q, int q_dtype, int64_t n_views, int H_q,
  *   layer_token   fp32 [BH][T] = sum_r aw (rounded to aw's dtype, as the reference's
  *                                 aw.sum(...).float() is),
  *   layer_channel fp32 [BH][D] = mean_r(q^2) * mean_t(k^2).
- * scratch: fp32 [BH][rdkv_score_chunks(T)][D].
+ * One launch (plus a memset node for the arrival counters).  scratch:
+ * rdkv_score_scratch_words(BH, T, D) 4-byte words = fp32 [BH][rdkv_score_chunks(T)][D]
+ * partial sums of k^2, then one arrival counter per BH.
  * rdkv_score_pool: sliding-window pooling (stride 1) of `rows` rows of `len` fp32
  * scores; pool_max 0 = average, 1 = maximum; reflect 0 = zero padding with
  * kernel_size taps, 1 = reflection padding with min(kernel_size, 2*len-1) taps;
  * out_len must be len + 2*(taps/2) - taps + 1. */
 int rdkv_score_chunks(int T);
+int64_t rdkv_score_scratch_words(int BH, int T, int D);
 int rdkv_score_layer(const void* aw, int aw_dtype, const void* q, int q_dtype, const void* k, int k_dtype,
                      int64_t k_head_stride, int64_t k_row_stride, int BH, int R, int T, int D,
                      float* scratch, float* layer_token, float* layer_channel, void* stream);

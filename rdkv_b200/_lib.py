@@ -22,6 +22,17 @@ HEAD_DIM = 128
 _STATUS_EXC = {1: ValueError, 2: ValueError, 3: ValueError, 4: RuntimeError, 5: RuntimeError}
 
 
+class TailArgs(C.Structure):
+    """Mirror of ``rdkv_tail_args``; field order and types must match the header."""
+    _fields_ = [
+        ("new_k", C.c_void_p), ("new_v", C.c_void_p), ("view_stride", C.c_int64), ("head_stride", C.c_int64),
+        ("dtype", C.c_int32), ("cap", C.c_int32), ("n_new", C.c_int32), ("rope_dtype", C.c_int32),
+        ("n_new_per_view", C.c_void_p), ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+        ("rope_view_stride", C.c_int64), ("k_cur", C.c_void_p), ("v_cur", C.c_void_p),
+        ("append", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 class LayerView(C.Structure):
     """Mirror of ``rdkv_layer_view``; field order and types must match the header."""
     _fields_ = [
@@ -77,6 +88,7 @@ _PROTOTYPES = {
     "rdkv_last_error_string": ([_i], C.c_char_p),
     "rdkv_last_cuda_error": ([], _i),
     "rdkv_sizeof_layer_view": ([], _i),
+    "rdkv_sizeof_tail_args": ([], _i),
     "rdkv_k_scores": ([C.POINTER(LayerView), _p, _i, _i64, _i, _i, _i, _p, _i64, _p], _i),
     "rdkv_v_weighted_sum": ([C.POINTER(LayerView), _p, _i64, _i, _i, _p, _i64, _p], _i),
     "rdkv_decode_stage_bytes": ([_i], _i),
@@ -87,6 +99,8 @@ _PROTOTYPES = {
     "rdkv_decode_prepared_bytes": ([_i64, _i, _i], _i64),
     "rdkv_decode_prepare": ([_p, _i, _i, _i, _p, _p, _p], _i),
     "rdkv_decode_attn": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p], _i),
+    "rdkv_decode_attn_tail": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p], _i),
+    "rdkv_rope": ([_p, _i, _i, _i64, _p, _i, _i, _i64, _p, _p, _i, _p], _i),
     "rdkv_decode_attn_persistent": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p], _i),
     "rdkv_tail_attn_partial": ([_p, _i, _i64, _i, _i, _p, _p, _i, _i64, _i64, _i64, _i, _p, _i, _p, _p], _i),
     "rdkv_lse_combine": ([_p, _i64, _i, _i64, _i64, _p, _p, _p, _p], _i),
@@ -97,6 +111,7 @@ _PROTOTYPES = {
     "rdkv_pack_k": ([_p, _i64, _i64, _i, _i, _p, _i64, _p, _i64, _i, _i, _p, _i64, _p, _i64,
                      _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p], _i),
     "rdkv_score_chunks": ([_i], _i),
+    "rdkv_score_scratch_words": ([_i, _i, _i], _i64),
     "rdkv_score_layer": ([_p, _i, _p, _i, _p, _i, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p], _i),
     "rdkv_score_pool": ([_p, _i64, _i, _i, _i, _i, _i, _p, _i64, _i, _p], _i),
     "rdkv_block_scores": ([_p, _i, _i64, _i64, _p, _i, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p], _i),
@@ -129,6 +144,8 @@ def lib() -> C.CDLL:
             raise RuntimeError("rdkv_b200: library ABI version mismatch; rebuild it")
         if handle.rdkv_sizeof_layer_view() != C.sizeof(LayerView):
             raise RuntimeError("rdkv_b200: rdkv_layer_view layout mismatch between header and binding")
+        if handle.rdkv_sizeof_tail_args() != C.sizeof(TailArgs):
+            raise RuntimeError("rdkv_b200: rdkv_tail_args layout mismatch between header and binding")
         if handle.rdkv_sizeof_pack_job() != C.sizeof(PackJob):
             raise RuntimeError("rdkv_b200: rdkv_pack_job layout mismatch between header and binding")
         _lib = handle

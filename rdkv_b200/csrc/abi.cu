@@ -4,6 +4,7 @@
 extern "C" int rdkv_version(void) { return 1; }
 
 extern "C" int rdkv_sizeof_layer_view(void) { return (int)sizeof(rdkv_layer_view); }
+extern "C" int rdkv_sizeof_tail_args(void) { return (int)sizeof(rdkv_tail_args); }
 
 extern "C" int rdkv_last_cuda_error(void) { return rdkv::g_last_cuda_error; }
 

@@ -6,10 +6,15 @@
 //   token[h][t]   = sum over the head's g query heads and the Q query positions of
 //                   softmax_t(q . k_t / sqrt(D))   (causal: position i sees keys t <= i)
 //   channel[h][d] = mean_{g,Q}(q_d^2) * mean_t(k_d^2)
-// One CTA per KV head: the head's keys sit in shared memory as fp32 (rows padded by one word, so
-// that lanes reading consecutive keys hit different banks); every warp takes (query head,
-// position) pairs in turn, scores the keys one per lane, normalises across the warp and keeps
-// its share of the column sums in registers; the warps' shares are added up in a fixed order.
+// One thread-block cluster of BS_CLUSTER CTAs per KV head (a decode block has 8 KV heads, far fewer
+// than the GPU has SMs): every CTA holds the head's keys in shared memory as fp32 (rows padded by
+// one word, so that lanes reading consecutive keys hit different banks) and takes every
+// BS_CLUSTER-th group of (query head, position) pairs; a warp scores the keys one per lane,
+// normalises across the warp and keeps its share of the column sums in registers.  The warps'
+// shares are added in warp order inside a CTA, and the CTAs' sums in rank order by the cluster's
+// first CTA, which reads them from the others' shared memory: the result repeats bit for bit.
+#include <cooperative_groups.h>
+
 #include "rdkv_common.cuh"
 
 namespace rdkv {
@@ -18,6 +23,7 @@ constexpr int BS_THREADS = 256;
 constexpr int BS_WARPS = BS_THREADS / 32;
 constexpr int BS_MAX_T = 256;                    // keys of a block (the reference uses 64 or 128)
 constexpr int BS_T_PER_LANE = BS_MAX_T / 32;
+constexpr int BS_CLUSTER = 8;                    // CTAs per KV head (the portable cluster limit)
 
 __global__ void __launch_bounds__(BS_THREADS)
 block_score_kernel(const void* __restrict__ queries, int q_dtype, int64_t q_head_stride, int64_t q_pos_stride,
@@ -25,12 +31,16 @@ block_score_kernel(const void* __restrict__ queries, int q_dtype, int64_t q_head
                    int g, int Q, int T, int Dh, int causal, float* __restrict__ token_out,
                    float* __restrict__ channel_out) {
   extern __shared__ float smem[];
-  const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = (int)cluster.block_rank(), csize = (int)cluster.num_blocks();
+  const int h = blockIdx.x / csize, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ld = Dh + 1;
+  const int span = T > Dh ? T : Dh;
   float* ks = smem;                                // [T][Dh + 1]
   float* qs = ks + (size_t)T * ld;                 // [BS_WARPS][Dh]: the pair a warp works on
-  float* part = qs + BS_WARPS * Dh;                // [BS_WARPS][max(T, Dh)]: the warps' shares
-  const int span = T > Dh ? T : Dh;
+  float* part = qs + BS_WARPS * Dh;                // [BS_WARPS][span]: the warps' shares
+  float* mine = part + BS_WARPS * span;            // [2][span]: this CTA's token sums, q^2 sums
   for (int i = tid; i < T * Dh; i += BS_THREADS) {
     const int t = i / Dh, d = i % Dh;
     ks[t * ld + d] = load_q(keys, k_dtype, (int64_t)h * k_head_stride + (int64_t)t * k_row_stride + d);
@@ -42,7 +52,7 @@ block_score_kernel(const void* __restrict__ queries, int q_dtype, int64_t q_head
   for (int i = 0; i < BS_T_PER_LANE; ++i) tok[i] = 0.f;
   float qsq[4] = {0.f, 0.f, 0.f, 0.f};             // sums of q_d^2 for d = lane, lane + 32, ...
   float* myq = qs + warp * Dh;
-  for (int pair = warp; pair < g * Q; pair += BS_WARPS) {
+  for (int pair = crank * BS_WARPS + warp; pair < g * Q; pair += csize * BS_WARPS) {
     const int gi = pair / Q, qi = pair % Q;
     const int64_t qoff = (int64_t)(h * g + gi) * q_head_stride + (int64_t)qi * q_pos_stride;
     __syncwarp();
@@ -80,7 +90,7 @@ block_score_kernel(const void* __restrict__ queries, int q_dtype, int64_t q_head
 #pragma unroll
     for (int i = 0; i < BS_T_PER_LANE; ++i) tok[i] = fmaf(s[i], r, tok[i]);
   }
-  // column sums: the warps' shares, added in warp order
+  // this CTA's sums: the warps' shares, added in warp order
   if (token_out != nullptr) {
 #pragma unroll
     for (int i = 0; i < BS_T_PER_LANE; ++i)
@@ -89,7 +99,7 @@ block_score_kernel(const void* __restrict__ queries, int q_dtype, int64_t q_head
     for (int t = tid; t < T; t += BS_THREADS) {
       float a = 0.f;
       for (int w = 0; w < BS_WARPS; ++w) a += part[w * span + t];
-      token_out[(int64_t)h * T + t] = a;
+      mine[t] = a;
     }
     __syncthreads();
   }
@@ -98,10 +108,26 @@ block_score_kernel(const void* __restrict__ queries, int q_dtype, int64_t q_head
   for (int d = tid; d < Dh; d += BS_THREADS) {
     float qa = 0.f;
     for (int w = 0; w < BS_WARPS; ++w) qa += part[w * span + d];
-    float ka = 0.f;
-    for (int t = 0; t < T; ++t) ka = fmaf(ks[t * ld + d], ks[t * ld + d], ka);
-    channel_out[(int64_t)h * Dh + d] = (qa / (float)(g * Q)) * (ka / (float)T);
+    mine[span + d] = qa;
   }
+  cluster.sync();
+  // the cluster's first CTA adds the CTAs' sums in rank order
+  if (crank == 0) {
+    if (token_out != nullptr)
+      for (int t = tid; t < T; t += BS_THREADS) {
+        float a = 0.f;
+        for (int r = 0; r < csize; ++r) a += cluster.map_shared_rank(mine, r)[t];
+        token_out[(int64_t)h * T + t] = a;
+      }
+    for (int d = tid; d < Dh; d += BS_THREADS) {
+      float qa = 0.f;
+      for (int r = 0; r < csize; ++r) qa += cluster.map_shared_rank(mine, r)[span + d];
+      float ka = 0.f;
+      for (int t = 0; t < T; ++t) ka = fmaf(ks[t * ld + d], ks[t * ld + d], ka);
+      channel_out[(int64_t)h * Dh + d] = (qa / (float)(g * Q)) * (ka / (float)T);
+    }
+  }
+  cluster.sync();                                  // the others' shared memory stays until it was read
 }
 
 }  // namespace rdkv
@@ -119,11 +145,24 @@ extern "C" int rdkv_block_scores(const void* queries, int q_dtype, int64_t q_hea
   if (causal && Q != T) return RDKV_ERR_BAD_SHAPE;
   if (H_kv == 0) return RDKV_OK;
   const int span = T > D ? T : D;
-  const size_t smem = sizeof(float) * ((size_t)T * (D + 1) + (size_t)BS_WARPS * D + (size_t)BS_WARPS * span);
+  const size_t smem =
+      sizeof(float) * ((size_t)T * (D + 1) + (size_t)BS_WARPS * D + (size_t)BS_WARPS * span + 2 * (size_t)span);
   cudaError_t e = cudaFuncSetAttribute(block_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
-  block_score_kernel<<<H_kv, BS_THREADS, smem, (cudaStream_t)stream>>>(
-      queries, q_dtype, q_head_stride, q_pos_stride, keys, k_dtype, k_head_stride, k_row_stride, g, Q, T, D, causal,
-      token_out, channel_out);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(H_kv * BS_CLUSTER);
+  cfg.blockDim = dim3(BS_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = BS_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, block_score_kernel, queries, q_dtype, q_head_stride, q_pos_stride, keys, k_dtype,
+                         k_head_stride, k_row_stride, g, Q, T, D, causal, token_out, channel_out);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
   return launch_status();
 }

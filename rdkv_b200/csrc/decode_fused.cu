@@ -59,7 +59,10 @@ constexpr unsigned WAIT_LIMIT = 1u << 22;  // try_wait rounds before a compute w
 constexpr float RESCALE_TH = 8.f;      // log2 slack before the running maximum is moved
 constexpr float M_NONE = -1.0e30f;     // reference maximum of a head that has seen no live score yet (finite: no inf - inf)
 
-__host__ __device__ constexpr int phase_tile_rows(int p) { return p < 2 ? TILE_MAX : p == 2 ? TILE_MAX / 2 : TILE_MAX / 4; }
+// (phase 4 = the uncompressed tail: plain K and V rows of 256 bytes each share the V area of a stage)
+__host__ __device__ constexpr int phase_tile_rows(int p) {
+  return p < 2 ? TILE_MAX : p == 2 ? TILE_MAX / 2 : p == 3 ? TILE_MAX / 4 : TILE_MAX / 8;
+}
 __host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : p == 1 ? 64 : p == 2 ? 128 : 256; }
 
 __host__ __device__ inline int align16i(int x) { return (x + 15) & ~15; }
@@ -237,6 +240,12 @@ __device__ __forceinline__ uint32_t lds32_unaligned(uint32_t a) {
   const uint32_t lo = lds32(a & ~3u), hi = lds32<4>(a & ~3u);
   return __funnelshift_r(lo, hi, (a & 3u) * 8);
 }
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+
 // ── K channel-slot map: which padded channel slot feeds MMA k-index e of thread j ──
 // e = 0..3 stands for k = 2j, 2j+1, 2j+8, 2j+9.  Returns the slot or -1, and the
 // power-of-two factor the masked code carries (folded into q*scale).
@@ -305,14 +314,15 @@ __device__ __forceinline__ int acc_exp(int phase, int v) {
 
 // Everything a worker needs to find and stage its tiles; filled once per CTA.
 struct CtaGeom {
-  int lo[4], hi[4];                    // live-row range of this CTA per phase (2-bit, 4-bit, 8-bit, fp16)
-  int first_tile[5];
+  int lo[5], hi[5];                    // live-row range of this CTA per phase (2-bit, 4-bit, 8-bit, fp16, uncompressed tail)
+  int first_tile[6];                   // [number of phases] = all tiles of the CTA, or -1: the view does not fit the launch
   int fast;                            // every staged range lies on whole 16-byte blocks of its tensor
   int64_t krow[4];                     // stripe row of live row lo[p]
   const unsigned char* k2[4];          // address of the K rows of live row lo[p]
   const unsigned char* k4[4];
   const unsigned char* k8[4];
-  const unsigned char* vrow[4];        // address of the V row of live row lo[p]
+  const unsigned char* vrow[5];        // address of the V row of live row lo[p]
+  const unsigned char* krow_tail;      // address of the plain K row of tail row lo[4]
   const unsigned char* sc[3];
   const unsigned char* zp[3];
 };
@@ -330,11 +340,12 @@ struct __align__(16) RangePlan { const unsigned char* src; int len; uint32_t dst
 struct __align__(16) TilePlan { RangePlan rg[6]; TileInfo info; };
 constexpr int PLAN_TILES = 32;         // tiles planned per round (one per staging lane)
 
+template <int NPH>
 __device__ __forceinline__ TileDesc tile_of(const CtaGeom& G, int idx) {
   TileDesc t;
   int p = 0;
 #pragma unroll
-  for (int k = 1; k < 4; ++k)
+  for (int k = 1; k < NPH; ++k)
     if (idx >= G.first_tile[k]) p = k;
   t.phase = p;
   const int tr = phase_tile_rows(p);
@@ -507,7 +518,17 @@ struct EpiInfo {
 // aux[(query head) * aux_stride + stripe row]; only sum_t w.V is computed (the V kernel of the
 // two-stage interface; K is not read), records carry m = 0 and l = 1 in chunk 0 so that the
 // combine kernel adds the chunks up.
-constexpr int MODE_ATTN = 0, MODE_SCORES = 1, MODE_WEIGHTS = 2;
+// MODE_ATTN_TAIL: MODE_ATTN over the packed zones plus, in the same softmax, the uncompressed tail
+// of decode-appended tokens (a fifth tile phase of plain 16-bit K and V rows) and the token being
+// decoded, with the rotary embedding of the query rows and of the new key row applied on the way
+// in (TailArgs).  A separate instantiation: the other modes' code is not touched by it.
+constexpr int MODE_ATTN = 0, MODE_SCORES = 1, MODE_WEIGHTS = 2, MODE_ATTN_TAIL = 3;
+constexpr int TAIL_TILE = TILE_MAX / 8;             // tail rows per tile: K rows and V rows fill the V area together
+constexpr int TAILQ_BYTES = 8 * 32 * 8;             // the queries as fp16 B fragments of the tail's score product
+constexpr int TAIL_EXTRA_BYTES = TAILQ_BYTES + 2 * 128 * 4 + 64;   // + new key row, new value row (fp32), its scores
+static_assert(2 * TAIL_TILE * 256 <= V_STAGE, "a tail tile's K and V rows share the V area");
+
+using TailArgs = rdkv_tail_args;
 
 template <int MODE>
 #ifdef RDKV_MAXNREG
@@ -521,7 +542,10 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
                     float* __restrict__ aux, int64_t aux_stride, int t_eff,
                     const UnitRec* __restrict__ unit_recs, const KSlotRec* __restrict__ kslots, int nkb_max,
                     int* __restrict__ unit_ctr, float* __restrict__ merged, int row_begin, int row_end,
-                    int part, int parts) {
+                    int part, int parts, const TailArgs ta) {
+  constexpr bool TAIL = MODE == MODE_ATTN_TAIL;
+  constexpr bool ATTN = MODE == MODE_ATTN || TAIL;
+  constexpr int NPH = TAIL ? 5 : 4;                // tile phases
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ rdkv_layer_view v;
   __shared__ CtaGeom G;
@@ -573,6 +597,25 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   KSlotRec km0 = {0u, 0u, 0u, 0u}, km1 = km0;              // this thread's slots of blocks warp, warp + FW
   int n2p = 0, n4p = 0, n8c = 0;                           // padded channel counts of the view
   bool geom_done = false;
+  int n_tail = 0;                                          // live rows of the uncompressed tail of this view
+  // the tail's share of this CTA, from the rows pn0..pn3 the part has of the four packed phases:
+  // window [lo, hi) in the part's row numbering, first tail row d, tiles
+  struct TailGeom { int lo, hi, d, tiles; };
+  auto tail_geom = [&](int pn0, int pn1, int pn2, int pn3, int c0, int c1) {
+    const int ps4 = part_cut(n_tail, part, parts), pn4 = part_cut(n_tail, part + 1, parts) - ps4;
+    const int lb4 = pn0 + pn1 + pn2 + pn3;
+    TailGeom t;
+    t.lo = max(lb4, c0); t.hi = max(t.lo, min(lb4 + pn4, c1));
+    t.d = ps4 + (t.lo - lb4);
+    t.tiles = (t.hi - t.lo + TAIL_TILE - 1) / TAIL_TILE;
+    return t;
+  };
+  auto tail_row = [&](const void* base, int row) {         // address of a row of this (view, KV head)'s tail buffer
+    return reinterpret_cast<const unsigned char*>(base) +
+           ((int64_t)view_idx * ta.view_stride + (int64_t)h * ta.head_stride + (int64_t)row * D) * 2;
+  };
+  if (TAIL)
+    n_tail = ta.n_new_per_view != nullptr ? min(max(ldg_keep(ta.n_new_per_view + view_idx), 0), ta.cap) : ta.n_new;
   if (warp == FW) {
     if (lane < FSTAGES) mbar_init(&s_full[lane], 64);      // per staging lane: one plain + one copy-completion arrival
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -608,6 +651,15 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         };
         const int t0 = __shfl_sync(0xffffffffu, ntile, 0), t1 = __shfl_sync(0xffffffffu, ntile, 1);
         const int t2 = __shfl_sync(0xffffffffu, ntile, 2), t3 = __shfl_sync(0xffffffffu, ntile, 3);
+        int t4 = 0;
+        if (TAIL) {
+          const TailGeom tg = tail_geom(pn0, pn1, pn2, __shfl_sync(0xffffffffu, pn, 3), c0, c1);
+          t4 = tg.tiles;
+          if (lane == 0) {
+            G.lo[4] = tg.lo; G.hi[4] = tg.hi; G.first_tile[4] = t0 + t1 + t2 + t3;
+            G.vrow[4] = tail_row(ta.new_v, tg.d); G.krow_tail = tail_row(ta.new_k, tg.d);
+          }
+        }
         if (lane < 4) {
           G.lo[p] = lo; G.hi[p] = hi;
           G.first_tile[p] = p == 0 ? 0 : p == 1 ? t0 : p == 2 ? t0 + t1 : t0 + t1 + t2;
@@ -620,7 +672,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         }
         if (lane == 0) {
           G.fast = 1;
-          G.first_tile[4] = fits_q ? t0 + t1 + t2 + t3 : -1;
+          G.first_tile[NPH] = fits_q ? t0 + t1 + t2 + t3 + t4 : -1;
         }
         __threadfence_block();
         __syncwarp();
@@ -742,6 +794,15 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     fast = __all_sync(0xffffffffu, fast);                  // lanes 4.. repeat lanes 0..3
     const int t0 = __shfl_sync(0xffffffffu, ntile, 0), t1 = __shfl_sync(0xffffffffu, ntile, 1);
     const int t2 = __shfl_sync(0xffffffffu, ntile, 2), t3 = __shfl_sync(0xffffffffu, ntile, 3);
+    int t4 = 0;
+    if (TAIL) {
+      const TailGeom tg = tail_geom(pn0, pn1, pn2, __shfl_sync(0xffffffffu, pn, 3), c0, c1);
+      t4 = tg.tiles;
+      if (lane == 0) {
+        G.lo[4] = tg.lo; G.hi[4] = tg.hi; G.first_tile[4] = t0 + t1 + t2 + t3;
+        G.vrow[4] = tail_row(ta.new_v, tg.d); G.krow_tail = tail_row(ta.new_k, tg.d);
+      }
+    }
     if (lane < 4) {
       G.lo[p] = lo; G.hi[p] = hi;
       G.first_tile[p] = p == 0 ? 0 : p == 1 ? t0 : p == 2 ? t0 + t1 : t0 + t1 + t2;
@@ -751,7 +812,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     }
     if (lane == 0) {
       G.fast = fast ? 1 : 0;
-      G.first_tile[4] = (!fits || (MODE != MODE_SCORES && hc.n16 > 0 && v.v16 == nullptr)) ? -1 : t0 + t1 + t2 + t3;
+      G.first_tile[NPH] = (!fits || (MODE != MODE_SCORES && hc.n16 > 0 && v.v16 == nullptr)) ? -1 : t0 + t1 + t2 + t3 + t4;
     }
     __threadfence_block();
     __syncwarp();
@@ -762,6 +823,81 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   //    warp works out the geometry and starts the first copies).  The head's scales, zero points
   //    and channel permutation come into shared memory with one coalesced read each; the fold
   //    itself then gathers from shared memory only. ──
+  // ── tail mode: rotary embedding of the query rows, the queries as fragments of the tail's score
+  //    product, and the token being decoded (its key row rotated, scored, appended to the tail) ──
+  uint2* qtA = reinterpret_cast<uint2*>(tail + TAIL_BYTES);                  // [8][32]
+  float* f_kc = reinterpret_cast<float*>(tail + TAIL_BYTES + TAILQ_BYTES);   // [128] new key row (rotated, rounded to the tail's type)
+  float* f_vc = f_kc + D;                                                    // [128] new value row
+  float* s_cur = f_vc + D;                                                   // [GH] the new token's scores, base-2 units
+  const bool seeded = TAIL && ta.k_cur != nullptr && chunk == 0 && part == 0;
+  if (TAIL && warp < FW) {
+    const bool rope = ta.rope_cos != nullptr;
+    float rc = 1.f, rs = 0.f;                              // every pair a thread rotates has the same position tid & 63
+    if (rope) {
+      const int64_t e = (int64_t)view_idx * ta.rope_view_stride + (tid & 63);
+      rc = load_q(ta.rope_cos, ta.rope_dtype, e); rs = load_q(ta.rope_sin, ta.rope_dtype, e);
+    }
+    auto round_as = [](float x, int dt) {
+      return dt == RDKV_F16 ? __half2float(__float2half_rn(x)) : dt == RDKV_BF16 ? __bfloat162float(__float2bfloat16_rn(x)) : x;
+    };
+    // half format: (x[i], x[i+64]) -> (x[i] c - x[i+64] s, x[i+64] c + x[i] s); products and sums rounded
+    // one by one, the result rounded to the tensor's own type (as the in-place operation would leave it)
+    auto rotate = [&](float& lo, float& hi, int dt) {
+      const float a = __fsub_rn(__fmul_rn(lo, rc), __fmul_rn(hi, rs)), b = __fadd_rn(__fmul_rn(hi, rc), __fmul_rn(lo, rs));
+      lo = round_as(a, dt); hi = round_as(b, dt);
+    };
+    if (rope && fits) {
+      for (int idx = tid; idx < gcnt * 64; idx += FW * 32) {
+        float* row = f_q + (idx >> 6) * D + (idx & 63);
+        float lo = row[0], hi = row[64];
+        rotate(lo, hi, q_dtype);
+        row[0] = lo; row[64] = hi;
+      }
+    }
+    if (seeded) {
+      const int64_t e = ((int64_t)view_idx * (H_q / g) + h) * D;
+      if (tid < 64) {
+        float lo = load_q(ta.k_cur, ta.dtype, e + tid), hi = load_q(ta.k_cur, ta.dtype, e + tid + 64);
+        if (rope) rotate(lo, hi, ta.dtype);
+        f_kc[tid] = lo; f_kc[tid + 64] = hi;
+      } else {
+        const int i = 2 * (tid - 64);
+        f_vc[i] = load_q(ta.v_cur, ta.dtype, e + i); f_vc[i + 1] = load_q(ta.v_cur, ta.dtype, e + i + 1);
+      }
+    }
+    bar_sync(BAR_COMPUTE, FW * 32);                        // rotated rows are in shared memory
+    // B fragments of the tail's score product: MMA m of a 16-row group contracts channels
+    // 32*(m/2) + 8j + 4*(m%2) + {0,1 | 2,3} of thread j against the K words the thread loads
+    for (int m = warp; m < 8; m += FW) {
+      const bool ok = r < gcnt;
+      const float* row = f_q + (ok ? r : 0) * D + 32 * (m >> 1) + 8 * j + 4 * (m & 1);
+      qtA[m * 32 + lane] = ok ? make_uint2(pack_h2(row[0], row[1]), pack_h2(row[2], row[3])) : make_uint2(0u, 0u);
+    }
+    if (seeded) {
+      for (int hh = 2 * warp; hh < 2 * warp + 2; ++hh) {   // the new token's scores: warp w takes heads 2w, 2w+1
+        float a = 0.f;
+        if (hh < gcnt)
+          for (int c = lane; c < D; c += 32) a = fmaf(f_q[hh * D + c], f_kc[c], a);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0) s_cur[hh] = a * (INV_SQRT_D * LOG2E);
+      }
+      if (ta.append && hgrp == 0) {                        // the rotated key row and the value row become tail row n_tail
+        if (n_tail < ta.cap) {
+          uint16_t* kd_row = reinterpret_cast<uint16_t*>(const_cast<unsigned char*>(tail_row(ta.new_k, n_tail)));
+          uint16_t* vd_row = reinterpret_cast<uint16_t*>(const_cast<unsigned char*>(tail_row(ta.new_v, n_tail)));
+          const bool bf = ta.dtype == RDKV_BF16;
+          auto bits = [&](float x) {
+            return bf ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
+          };
+          kd_row[tid] = bits(f_kc[tid]); vd_row[tid] = bits(f_vc[tid]);
+        } else if (tid == 0 && status != nullptr) {
+          atomicOr(status, 4);
+        }
+      }
+    }
+  }
+
   if (MODE != MODE_WEIGHTS && warp < FW && fits && prepared) {
     // prepared table: this thread's slot quadruples were requested at entry, together with the
     // view record; nothing else comes from global memory.  Blocks warp and warp + FW are folded
@@ -836,9 +972,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     bar_sync(BAR_COMPUTE, FW * 32);
   }
   if (warp < FW) bar_sync(BAR_GEOM, CTA_THREADS);          // geometry published
-  const int total_tiles = G.first_tile[4];
+  const int total_tiles = G.first_tile[NPH];
 
-  if (total_tiles <= 0) {                                  // nothing live here: empty records
+  if (total_tiles < 0 || (total_tiles == 0 && !seeded)) {  // nothing live here: empty records
     if (total_tiles < 0 && tid == 0 && status != nullptr) atomicOr(status, 2);
     if (MODE == MODE_SCORES) return;
     if (direct) {
@@ -849,7 +985,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         rec0[hq * rec_stride + e] = (e == 0) ? -INFINITY : 0.f;
       }
     }
-    if (MODE == MODE_ATTN && n_chunks > 1 && unit_ctr != nullptr)
+    if (ATTN && n_chunks > 1 && unit_ctr != nullptr)
       chunk_merge<false>(partials, unit_ctr + unit_y, n_chunks, gcnt,
                          (int64_t)view_idx * H_q + hq0, out, merged);
     return;
@@ -873,9 +1009,19 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       if (slot == 0) {                                     // plan tiles [it, it + 32)
         __syncwarp();
         if (it + lane < total_tiles) {
-          const TileDesc t = tile_of(G, it + lane);
+          const TileDesc t = tile_of<NPH>(G, it + lane);
           const int p = t.phase;
           TilePlan& P = s_plan[lane];
+          if (TAIL && p == 4) {
+            // tail tile: its V rows at the start of the V area, its K rows behind them; the block
+            // goes to warp (tile number within the tail) % FW
+            P.rg[0] = RangePlan{G.vrow[4] + (int64_t)t.row0 * 256, t.n * 256, (uint32_t)SL.v};
+            P.rg[1] = RangePlan{G.krow_tail + (int64_t)t.row0 * 256, t.n * 256, (uint32_t)(SL.v + TAIL_TILE * 256)};
+#pragma unroll
+            for (int k = 2; k < 6; ++k) P.rg[k] = RangePlan{nullptr, 0, 0u};
+            P.info.phase = 4 | ((t.row0 / TAIL_TILE) & (FW - 1)) << 8; P.info.n = t.n;
+            P.info.offs = 0u; P.info.krow0 = 0;
+          } else {
           const unsigned char* a_k2 = G.k2[p] + (int64_t)t.row0 * kd.sub2;
           const unsigned char* a_k4 = G.k4[p] + (int64_t)t.row0 * kd.sub4;
           const unsigned char* a_k8 = G.k8[p] + (int64_t)t.row0 * kd.n8;
@@ -898,6 +1044,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 | low4(a_v) << 12 |
                         (p < 3 ? low4(a_sc) << 16 | low4(a_zp) << 20 : 0u);
           P.info.krow0 = (int)(G.krow[p] + t.row0);
+          }
         }
         __syncwarp();
       }
@@ -926,11 +1073,15 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       } else {
         // a range whose covering blocks stick out of its tensor: guarded 16-byte copies by all lanes
         unsigned char* sb = smem_raw + (size_t)stage * stage_bytes;
-        const int p = ti.phase & 3;
+        const int p = ti.phase & 7;
 #pragma unroll 1
         for (int k = 0; k < 6; ++k) {
           const RangePlan rk = s_plan[slot].rg[k];
           if (rk.len <= 0) continue;
+          if (TAIL && p == 4) {                            // tail rows are 16-byte aligned: nothing sticks out
+            stage_range_guarded(sb + rk.dst_off, rk.src, rk.len, rk.src, rk.src + rk.len, lane, 32);
+            continue;
+          }
           const unsigned char* lo = k == 0 ? (p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : v16b)
                                   : k == 1 ? v.k2 : k == 2 ? v.k4 : k == 3 ? v.k8 : k == 4 ? scb : zpb;
           const int64_t ext = k == 0 ? (p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes)
@@ -940,7 +1091,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       }
       // rows past the tile's end must hold finite fp16 data in the fp16 phase: clear the
       // rest of the last 32-row block beyond the copied blocks
-      if ((ti.phase & 3) == 3 && (ti.n & 31)) {
+      if ((ti.phase & 7) >= 3 && (ti.n & 31)) {
         const int off = (int)((ti.offs >> 12) & 15u);
         const int first = (off + ti.n * 256 + 15) & ~15;
         const int last = min(off + ((ti.n + 31) & ~31) * 256, V_STAGE + 16);
@@ -959,6 +1110,26 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   // then holds scores of rows g16+r and g16+r+8 for heads 2j and 2j+1 — the same two
   // heads whose output columns it accumulates in the P.V product.
 #include "decode_state.inc"
+  // reference maxima of the tail's scores (they carry no zero-point bias): what cb holds beyond the bias
+  float tref_e = he_ok ? 0.f : INFINITY, tref_o = ho_ok ? 0.f : INFINITY;
+  if (TAIL && seeded && warp < FW) {
+    // the token being decoded starts the running softmax: reference = its score, weight 1, value row
+    // as the accumulator of warp 0
+    if (he_ok) { m_e = s_cur[2 * j]; cb_e = b1e + m_e; thr_e = RESCALE_TH; tref_e = m_e; }
+    if (ho_ok) { m_o = s_cur[2 * j + 1]; cb_o = b1o + m_o; thr_o = RESCALE_TH; tref_o = m_o; }
+    if (warp == 0) {
+      cur_phase = 3;
+      if (r == 0) { l_e = he_ok ? 1.f : 0.f; l_o = ho_ok ? 1.f : 0.f; }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int ch = 4 * r + 2 * (i >> 2) + 32 * (i & 3);
+        acc[i][0] = he_ok ? f_vc[ch] : 0.f; acc[i][1] = ho_ok ? f_vc[ch] : 0.f;
+        acc[i][2] = he_ok ? f_vc[ch + 1] : 0.f; acc[i][3] = ho_ok ? f_vc[ch + 1] : 0.f;
+      }
+    }
+  }
+  const uint32_t qt_lane = smem_u32(qtA) + 8 * lane;
+  const bool tail_bf = TAIL && ta.dtype == RDKV_BF16;
 
 #pragma unroll 1
   for (int it = 0; warp < FW && it < total_tiles; ++it) {
@@ -974,12 +1145,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       }
     }
     const TileInfo t = s_tile[stage];
-    const int p = t.phase & 3;
+    const int p = t.phase & 7;
     // this warp takes the tile's 32-row blocks pb, pb+FW, ... (two 16-row MMA groups each, worked on
     // together so that the two dependency chains overlap); the start rotates from tile to tile so
     // that short tiles (fewer blocks than warps) do not always land on the same warps
     const int nblocks = (t.n + 31) >> 5;
-    const int pb = (warp + FW - (it * (TILE_MAX / 128)) % FW) % FW;
+    const int pb = (TAIL && p == 4) ? (warp + FW - ((t.phase >> 8) & (FW - 1))) % FW
+                                    : (warp + FW - (it * (TILE_MAX / 128)) % FW) % FW;
 
 #include "decode_tile.inc"
     if (it + FSTAGES < total_tiles) bar_arrive(BAR_FREE + stage, CTA_THREADS);   // slot may be refilled
@@ -1014,7 +1186,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   __syncthreads();
   const EpiInfo ep = s_epi;
   final_merge<false>(red, &s_ml[0][0][0], s_fin, ep.gcnt, ep.how, ep.out_rows, ep.rec0, ep.rec_stride);
-  if (MODE == MODE_ATTN && ep.n_chunks > 1 && unit_ctr != nullptr)
+  if (ATTN && ep.n_chunks > 1 && unit_ctr != nullptr)
     chunk_merge<false>(partials, unit_ctr + ep.unit_y, ep.n_chunks, ep.gcnt, ep.row0, out, merged);
 }
 
@@ -1189,7 +1361,7 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
         if (slot == 0) {                                   // plan tiles [it, it + 32)
           __syncwarp();
           if (it + lane < total) {
-            const TileDesc t = tile_of(G, it + lane);
+            const TileDesc t = tile_of<4>(G, it + lane);
             const int tp = t.phase;
             TilePlan& P = s_plan[lane];
             const unsigned char* a_k2 = G.k2[tp] + (int64_t)t.row0 * kd.sub2;
@@ -1340,6 +1512,10 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
         if (j == 0) s_ml[warp][r][0] = bias_part;
         bar_sync(BAR_COMPUTE, FW * 32);
       }
+  constexpr bool TAIL = false, ATTN = MODE == MODE_ATTN;   // (no uncompressed tail in this form)
+  float tref_e = 0.f, tref_o = 0.f;
+  const uint32_t qt_lane = 0u;
+  const bool tail_bf = false;
 #include "decode_state.inc"
 #pragma unroll 1
       for (int it = 0; it < n_it; ++it) {
@@ -1482,7 +1658,8 @@ static int launch_fused(const rdkv_layer_view* views, int n_views, const void* q
                         float* aux, int64_t aux_stride, int t_eff, void* stream,
                         const void* unit_recs = nullptr, const void* kslots = nullptr, int nkb_max = 0,
                         int* unit_ctr = nullptr, float* merged = nullptr,
-                        int row_begin = 0, int row_end = 0x7fffffff, int n_whole = 0, int part = 0, int parts = 1) {
+                        int row_begin = 0, int row_end = 0x7fffffff, int n_whole = 0, int part = 0, int parts = 1,
+                        const TailArgs* tail = nullptr) {
   const int g = H_q / H_kv;
   const int n_hgrp = (g + GH - 1) / GH;
   const int64_t units = (int64_t)n_views * H_kv * n_hgrp;
@@ -1490,16 +1667,19 @@ static int launch_fused(const rdkv_layer_view* views, int n_views, const void* q
   const int64_t items = n_whole + (units - n_whole) * n_chunks;
   if (items > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
   const int stage_bytes = align16i(stage_capacity(k_row_bytes_max));
-  size_t smem = (size_t)FSTAGES * stage_bytes + TAIL_BYTES;
+  size_t smem = (size_t)FSTAGES * stage_bytes + TAIL_BYTES + (MODE == MODE_ATTN_TAIL ? TAIL_EXTRA_BYTES : 0);
   const size_t epilogue = (size_t)FW * GH * D * sizeof(float);
   if (smem < epilogue) smem = epilogue;
   if (smem > 227 * 1024) return RDKV_ERR_TOO_LARGE;
+  TailArgs ta;
+  memset(&ta, 0, sizeof(ta));
+  if (tail != nullptr) ta = *tail;
   cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
   decode_fused_kernel<MODE><<<(unsigned)items, CTA_THREADS, smem, (cudaStream_t)stream>>>(
       views, q, q_dtype, H_q, g, chunk_rows, n_chunks, n_whole, stage_bytes, partials, out, status, aux, aux_stride, t_eff,
       reinterpret_cast<const UnitRec*>(unit_recs), reinterpret_cast<const KSlotRec*>(kslots), nkb_max, unit_ctr, merged,
-      row_begin, row_end, part, parts);
+      row_begin, row_end, part, parts, ta);
   return launch_status();
 }
 
@@ -1563,6 +1743,90 @@ extern "C" int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const
   return launch_fused<MODE_ATTN>(views, n_views, q, q_dtype, H_q, H_kv, chunk_rows, n_chunks, k_row_bytes_max,
                                  partials, out, status, nullptr, 0, 0, stream, unit_recs, k_slots, nkb_max,
                                  unit_counters, out_record, row_begin, row_end, n_whole_units, seq_part, seq_parts);
+}
+
+extern "C" int rdkv_decode_attn_tail(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,
+                                     int H_kv, int chunk_rows, int n_chunks, int n_whole_units, int row_begin,
+                                     int row_end, int seq_part, int seq_parts, int k_row_bytes_max,
+                                     const void* unit_recs, const void* k_slots, int nkb_max, float* partials,
+                                     int32_t* unit_counters, float* out, float* out_record, int32_t* status,
+                                     const rdkv_tail_args* tail, void* stream) {
+  if (tail == nullptr) return RDKV_ERR_BAD_ARG;
+  if (n_chunks <= 0 || chunk_rows <= 0 || row_begin < 0 || row_end < row_begin) return RDKV_ERR_BAD_ARG;
+  if (seq_parts < 1 || seq_part < 0 || seq_part >= seq_parts) return RDKV_ERR_BAD_ARG;
+  if ((out == nullptr) == (out_record == nullptr)) return RDKV_ERR_BAD_ARG;
+  if (n_chunks > 1 && (partials == nullptr || unit_counters == nullptr)) return RDKV_ERR_BAD_ARG;
+  if ((unit_recs == nullptr) != (k_slots == nullptr)) return RDKV_ERR_BAD_ARG;
+  if (unit_recs != nullptr && ((reinterpret_cast<uintptr_t>(unit_recs) & 15) || (reinterpret_cast<uintptr_t>(k_slots) & 15) ||
+                               nkb_max <= 0 || nkb_max > KB_MAX))
+    return RDKV_ERR_BAD_ARG;
+  const rdkv_tail_args& t = *tail;
+  if (t.dtype != RDKV_F16 && t.dtype != RDKV_BF16) return RDKV_ERR_BAD_ARG;
+  if (t.cap < 0 || t.n_new < 0 || t.n_new > t.cap) return RDKV_ERR_BAD_ARG;
+  const bool rows = t.cap > 0 && (t.n_new > 0 || t.n_new_per_view != nullptr || t.append);
+  if (rows) {                                              // the staged rows: 16-byte aligned whatever the view, head and row
+    if (t.new_k == nullptr || t.new_v == nullptr) return RDKV_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(t.new_k) & 15) || (reinterpret_cast<uintptr_t>(t.new_v) & 15) ||
+        (t.view_stride & 7) || (t.head_stride & 7))
+      return RDKV_ERR_BAD_SHAPE;
+  }
+  if ((t.rope_cos == nullptr) != (t.rope_sin == nullptr)) return RDKV_ERR_BAD_ARG;
+  if (t.rope_cos != nullptr && (t.rope_dtype < RDKV_F16 || t.rope_dtype > RDKV_F32)) return RDKV_ERR_BAD_ARG;
+  if ((t.k_cur == nullptr) != (t.v_cur == nullptr)) return RDKV_ERR_BAD_ARG;
+  if (t.append && (t.k_cur == nullptr || t.new_k == nullptr || t.new_v == nullptr)) return RDKV_ERR_BAD_ARG;
+  if (t.append && t.n_new_per_view == nullptr && t.n_new >= t.cap) return RDKV_ERR_TOO_LARGE;
+  const int rc = check_fused_args(views, n_views, q, q_dtype, H_q, H_kv, k_row_bytes_max);
+  if (rc != RDKV_OK || n_views == 0) return rc;
+  return launch_fused<MODE_ATTN_TAIL>(views, n_views, q, q_dtype, H_q, H_kv, chunk_rows, n_chunks, k_row_bytes_max,
+                                      partials, out, status, nullptr, 0, 0, stream, unit_recs, k_slots, nkb_max,
+                                      unit_counters, out_record, row_begin, row_end, n_whole_units, seq_part,
+                                      seq_parts, tail);
+}
+
+// fused_rope on its own (rows of q and k rotated in place): one warp per row, lane i takes the
+// channel pairs (i, i + 64) and (i + 32, i + 96).
+namespace rdkv {
+__global__ void __launch_bounds__(128)
+rope_kernel(void* q, int q_dtype, int n_q, int64_t q_row_stride, void* k, int k_dtype, int n_k, int64_t k_row_stride,
+            const void* cos_half, const void* sin_half, int cs_dtype) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n_q + n_k) return;
+  const bool is_q = row < n_q;
+  void* base = is_q ? q : k;
+  const int dt = is_q ? q_dtype : k_dtype;
+  const int64_t off = is_q ? (int64_t)row * q_row_stride : (int64_t)(row - n_q) * k_row_stride;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int i = lane + 32 * u;
+    const float c = load_q(cos_half, cs_dtype, i), sn = load_q(sin_half, cs_dtype, i);
+    const float lo = load_q(base, dt, off + i), hi = load_q(base, dt, off + i + 64);
+    const float a = __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, sn)), b = __fadd_rn(__fmul_rn(hi, c), __fmul_rn(lo, sn));
+    if (dt == RDKV_F16) {
+      reinterpret_cast<__half*>(base)[off + i] = __float2half_rn(a);
+      reinterpret_cast<__half*>(base)[off + i + 64] = __float2half_rn(b);
+    } else if (dt == RDKV_BF16) {
+      reinterpret_cast<__nv_bfloat16*>(base)[off + i] = __float2bfloat16_rn(a);
+      reinterpret_cast<__nv_bfloat16*>(base)[off + i + 64] = __float2bfloat16_rn(b);
+    } else {
+      reinterpret_cast<float*>(base)[off + i] = a;
+      reinterpret_cast<float*>(base)[off + i + 64] = b;
+    }
+  }
+}
+}  // namespace rdkv
+
+extern "C" int rdkv_rope(void* q, int q_dtype, int n_q, int64_t q_row_stride, void* k, int k_dtype, int n_k,
+                         int64_t k_row_stride, const void* cos_half, const void* sin_half, int cs_dtype,
+                         void* stream) {
+  if (n_q < 0 || n_k < 0 || cos_half == nullptr || sin_half == nullptr) return RDKV_ERR_BAD_ARG;
+  if ((n_q > 0 && q == nullptr) || (n_k > 0 && k == nullptr)) return RDKV_ERR_BAD_ARG;
+  for (int dt : {n_q > 0 ? q_dtype : RDKV_F16, n_k > 0 ? k_dtype : RDKV_F16, cs_dtype})
+    if (dt < RDKV_F16 || dt > RDKV_F32) return RDKV_ERR_BAD_ARG;
+  const int n = n_q + n_k;
+  if (n == 0) return RDKV_OK;
+  rope_kernel<<<(n + 3) / 4, 128, 0, (cudaStream_t)stream>>>(q, q_dtype, n_q, q_row_stride, k, k_dtype, n_k, k_row_stride,
+                                                           cos_half, sin_half, cs_dtype);
+  return launch_status();
 }
 
 extern "C" int rdkv_decode_attn_persistent(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype,

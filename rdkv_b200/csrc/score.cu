@@ -3,7 +3,7 @@
 //   token score   [B,H_kv,T]   = sum over the group's query heads and window positions of aw
 //   channel score [B,H_kv,D]   = mean(q^2 over heads and window) * mean(k^2 over tokens)
 //   pooling                      avg / max over a sliding window, zero or reflect padding
-// All three are single passes over their inputs (HBM-bound).
+// Token and channel scores come from one launch; all passes read their inputs once (HBM-bound).
 #include "rdkv_common.cuh"
 
 namespace rdkv {
@@ -21,63 +21,154 @@ __device__ __forceinline__ float round_to(float x, int dtype) {
   return x;
 }
 
-// aw: [BH][R][T] (R = query heads of the group x window positions); out [BH][T]
-__global__ void __launch_bounds__(256)
-token_score_kernel(const void* __restrict__ aw, int dtype, int R, int T, float* __restrict__ out) {
-  const int bh = blockIdx.y;
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= T) return;
-  const int64_t base = (int64_t)bh * R * T + t;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  int r = 0;
-  for (; r + 4 <= R; r += 4) {
+// One launch scores a layer.  Block columns [0, n_tok) sum the attention weights of 512 tokens
+// over the R rows of the window; block columns [n_tok, n_tok + n_chunks) sum k^2 over a chunk of
+// tokens into part [BH][n_chunks][D], and the chunk block that arrives last for its head (a counter
+// per head, zeroed by the entry point) adds the chunks in chunk order, sums q^2 over the window
+// and writes the channel score.  Every sum runs in a fixed order, so results repeat bit for bit.
+//   aw [BH][R][T] -> token [BH][T];  k [BH][T][D], q [BH][R][D] -> channel [BH][D]
+constexpr int SC_THREADS = 256;
+constexpr int SC_VEC_SMEM = 16384;                      // shared memory of the vectorised k^2 pass: [row lanes][D] fp32
+__global__ void __launch_bounds__(SC_THREADS)
+score_layer_kernel(const void* __restrict__ aw, int aw_dtype, const void* __restrict__ q, int q_dtype,
+                   const void* __restrict__ k, int k_dtype, int64_t head_stride, int64_t row_stride, int R, int T,
+                   int D, int n_tok, int n_chunks, float* __restrict__ part, unsigned* __restrict__ arrived,
+                   float* __restrict__ token_out, float* __restrict__ channel_out) {
+  extern __shared__ float s_part[];                        // [rows_par][D], used twice by the last block
+  __shared__ int s_last;
+  const int bh = blockIdx.y, tid = threadIdx.x;
+  if ((int)blockIdx.x < n_tok) {
+    // 512 tokens per block: a thread sums two adjacent tokens (one 32-bit load per row for 16-bit
+    // weights), eight rows in flight; per token the rows are added in a fixed order
+    const int t = (blockIdx.x * SC_THREADS + tid) * 2;
+    if (t >= T) return;
+    const int64_t base = (int64_t)bh * R * T + t;
+    const bool pair = aw_dtype != RDKV_F32 && (T & 1) == 0 && (reinterpret_cast<uintptr_t>(aw) & 3) == 0;
+    float a0[8], a1[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u] += load_any(aw, dtype, base + (int64_t)(r + u) * T);
+    for (int u = 0; u < 8; ++u) a0[u] = a1[u] = 0.f;
+    int r = 0;
+    if (pair) {
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(aw) + base);
+      const int64_t row_words = T >> 1;
+      for (; r + 8 <= R; r += 8) {
+        uint32_t x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) x[u] = __ldg(w + (int64_t)(r + u) * row_words);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (aw_dtype == RDKV_F16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&x[u]));
+            a0[u] += f.x; a1[u] += f.y;
+          } else {
+            a0[u] += __uint_as_float(x[u] << 16); a1[u] += __uint_as_float(x[u] & 0xFFFF0000u);
+          }
+        }
+      }
+    }
+    const bool two = t + 1 < T;
+    for (; r < R; ++r) {
+      a0[r & 7] += load_any(aw, aw_dtype, base + (int64_t)r * T);
+      if (two) a1[r & 7] += load_any(aw, aw_dtype, base + (int64_t)r * T + 1);
+    }
+    token_out[(int64_t)bh * T + t] =
+        round_to(((a0[0] + a0[1]) + (a0[2] + a0[3])) + ((a0[4] + a0[5]) + (a0[6] + a0[7])), aw_dtype);
+    if (two)
+      token_out[(int64_t)bh * T + t + 1] =
+          round_to(((a1[0] + a1[1]) + (a1[2] + a1[3])) + ((a1[4] + a1[5]) + (a1[6] + a1[7])), aw_dtype);
+    return;
   }
-  for (; r < R; ++r) acc[0] += load_any(aw, dtype, base + (int64_t)r * T);
-  out[(int64_t)bh * T + t] = round_to((acc[0] + acc[1]) + (acc[2] + acc[3]), dtype);
-}
-
-// partial sums of k^2 over a chunk of tokens: k [BH][T][D] -> part [BH][n_chunks][D]
-constexpr int CH_THREADS = 256;
-__global__ void __launch_bounds__(CH_THREADS)
-channel_ksq_kernel(const void* __restrict__ k, int dtype, int T, int D, int64_t head_stride, int64_t row_stride,
-                   int n_chunks, float* __restrict__ part) {
-  extern __shared__ float s_part[];                        // [rows_par][D]
-  const int bh = blockIdx.y, chunk = blockIdx.x;
-  const int rows_par = CH_THREADS / D > 0 ? CH_THREADS / D : 1;
-  const int c = threadIdx.x % D, rl = threadIdx.x / D;
+  const int chunk = blockIdx.x - n_tok;
+  const int rows_par = SC_THREADS / D > 0 ? SC_THREADS / D : 1;
+  const bool on = tid < rows_par * D;
+  const int c = tid % D, rl = tid / D;
   const int per = (T + n_chunks - 1) / n_chunks;
   const int t0 = chunk * per, t1 = min(T, t0 + per);
   float acc = 0.f;
-  if (rl < rows_par && threadIdx.x < rows_par * D)
+  const int lanes_row = D >> 3;                            // threads per row at eight channels each
+  const bool vec = k_dtype != RDKV_F32 && (D & 7) == 0 && SC_THREADS % lanes_row == 0 && (row_stride & 7) == 0 &&
+                   (head_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(k) & 15) == 0 &&
+                   SC_THREADS / lanes_row * D * (int)sizeof(float) <= SC_VEC_SMEM;
+  if (vec) {
+    // 16-byte loads: thread (row lane, channel octet) sums the squares of its eight channels over
+    // every rows_v-th token, four rows in flight; the row lanes are then added in lane order
+    const int rows_v = SC_THREADS / lanes_row, o8 = (tid % lanes_row) * 8, rv = tid / lanes_row;
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const uint16_t* kb = reinterpret_cast<const uint16_t*>(k) + bh * head_stride + o8;
+    auto add = [&](const uint4& x) {
+      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float lo, hi;
+        if (k_dtype == RDKV_F16) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+          lo = f.x; hi = f.y;
+        } else {
+          lo = __uint_as_float(w[i] << 16); hi = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+        a[2 * i] = fmaf(lo, lo, a[2 * i]); a[2 * i + 1] = fmaf(hi, hi, a[2 * i + 1]);
+      }
+    };
+    int t = t0 + rv;
+    for (; t + 3 * rows_v < t1; t += 4 * rows_v) {
+      uint4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) x[u] = __ldg(reinterpret_cast<const uint4*>(kb + (int64_t)(t + u * rows_v) * row_stride));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) add(x[u]);
+    }
+    for (; t < t1; t += rows_v) add(__ldg(reinterpret_cast<const uint4*>(kb + (int64_t)t * row_stride)));
+    float* sv = s_part;                                    // [rows_v][D]
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sv[rv * D + o8 + i] = a[i];
+    __syncthreads();
+    if (tid < D) {
+      float s = 0.f;
+      for (int i = 0; i < rows_v; ++i) s += sv[i * D + tid];
+      part[((int64_t)bh * n_chunks + chunk) * D + tid] = s;
+      __threadfence();
+    }
+    __syncthreads();
+  } else {
+  if (on)
     for (int t = t0 + rl; t < t1; t += rows_par) {
-      const float x = load_any(k, dtype, bh * head_stride + (int64_t)t * row_stride + c);
+      const float x = load_any(k, k_dtype, bh * head_stride + (int64_t)t * row_stride + c);
       acc = fmaf(x, x, acc);
     }
-  if (threadIdx.x < rows_par * D) s_part[rl * D + c] = acc;
+  if (on) s_part[rl * D + c] = acc;
   __syncthreads();
-  if (threadIdx.x < D) {
+  if (tid < D) {
     float s = 0.f;
-    for (int i = 0; i < rows_par; ++i) s += s_part[i * D + threadIdx.x];
-    part[((int64_t)bh * n_chunks + chunk) * D + threadIdx.x] = s;
+    for (int i = 0; i < rows_par; ++i) s += s_part[i * D + tid];
+    part[((int64_t)bh * n_chunks + chunk) * D + tid] = s;
+    __threadfence();
   }
-}
-
-// channel[bh][c] = mean_r(q[bh][r][c]^2) * (sum_chunks part)/T
-__global__ void __launch_bounds__(128)
-channel_final_kernel(const void* __restrict__ q, int q_dtype, int R, int D, const float* __restrict__ part,
-                     int n_chunks, int T, float* __restrict__ out) {
-  const int bh = blockIdx.x;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) {
-    float qs = 0.f;
-    for (int r = 0; r < R; ++r) {
+  __syncthreads();
+  }
+  if (tid == 0) s_last = atomicAdd(&arrived[bh], 1u) == (unsigned)(n_chunks - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // the head's last chunk block: slices of the window rows and of the chunks per thread row
+  float qs = 0.f, ks = 0.f;
+  if (on) {
+    for (int r = rl; r < R; r += rows_par) {
       const float x = load_any(q, q_dtype, ((int64_t)bh * R + r) * D + c);
       qs = fmaf(x, x, qs);
     }
-    float ks = 0.f;
-    for (int i = 0; i < n_chunks; ++i) ks += part[((int64_t)bh * n_chunks + i) * D + c];
-    out[(int64_t)bh * D + c] = (qs / (float)R) * (ks / (float)T);
+    for (int i = rl; i < n_chunks; i += rows_par) ks += __ldcg(part + ((int64_t)bh * n_chunks + i) * D + c);
+  }
+  float qsum = 0.f, ksum = 0.f;
+  if (on) s_part[rl * D + c] = qs;
+  __syncthreads();
+  if (tid < D)
+    for (int i = 0; i < rows_par; ++i) qsum += s_part[i * D + tid];
+  __syncthreads();
+  if (on) s_part[rl * D + c] = ks;
+  __syncthreads();
+  if (tid < D) {
+    for (int i = 0; i < rows_par; ++i) ksum += s_part[i * D + tid];
+    channel_out[(int64_t)bh * D + tid] = (qsum / (float)R) * (ksum / (float)T);
   }
 }
 
@@ -114,6 +205,11 @@ extern "C" int rdkv_score_chunks(int T) {
   return n < 1 ? 1 : (n > 256 ? 256 : n);
 }
 
+extern "C" int64_t rdkv_score_scratch_words(int BH, int T, int D) {
+  if (BH < 0 || T <= 0 || D <= 0) return 0;
+  return (int64_t)BH * rdkv_score_chunks(T) * D + BH;
+}
+
 extern "C" int rdkv_score_layer(const void* aw, int aw_dtype, const void* q, int q_dtype, const void* k, int k_dtype,
                                 int64_t k_head_stride, int64_t k_row_stride, int BH, int R, int T, int D,
                                 float* scratch, float* layer_token, float* layer_channel, void* stream) {
@@ -126,16 +222,17 @@ extern "C" int rdkv_score_layer(const void* aw, int aw_dtype, const void* q, int
   if (BH == 0) return RDKV_OK;
   if (BH > 65535) return RDKV_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
-  token_score_kernel<<<dim3((T + 255) / 256, BH), 256, 0, st>>>(aw, aw_dtype, R, T, layer_token);
-  int rc = launch_status();
-  if (rc != RDKV_OK) return rc;
   const int n_chunks = rdkv_score_chunks(T);
-  const int rows_par = CH_THREADS / D > 0 ? CH_THREADS / D : 1;
-  channel_ksq_kernel<<<dim3(n_chunks, BH), CH_THREADS, (size_t)rows_par * D * sizeof(float), st>>>(
-      k, k_dtype, T, D, k_head_stride, k_row_stride, n_chunks, scratch);
-  rc = launch_status();
-  if (rc != RDKV_OK) return rc;
-  channel_final_kernel<<<BH, 128, 0, st>>>(q, q_dtype, R, D, scratch, n_chunks, T, layer_channel);
+  const int n_tok = (T + 2 * SC_THREADS - 1) / (2 * SC_THREADS);
+  const int rows_par = SC_THREADS / D > 0 ? SC_THREADS / D : 1;
+  size_t smem = (size_t)rows_par * D * sizeof(float);
+  if (smem < (size_t)SC_VEC_SMEM) smem = SC_VEC_SMEM;
+  unsigned* arrived = reinterpret_cast<unsigned*>(scratch + (int64_t)BH * n_chunks * D);
+  cudaError_t e = cudaMemsetAsync(arrived, 0, sizeof(unsigned) * BH, st);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
+  score_layer_kernel<<<dim3(n_tok + n_chunks, BH), SC_THREADS, smem, st>>>(
+      aw, aw_dtype, q, q_dtype, k, k_dtype, k_head_stride, k_row_stride, R, T, D, n_tok, n_chunks, scratch, arrived,
+      layer_token, layer_channel);
   return launch_status();
 }
 

@@ -16,7 +16,8 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 from torch import Tensor
 
-from ._lib import HEAD_DIM, PARTIAL_STRIDE, LayerView, check, lib, ptr, q_dtype_tag, require_cuda, stream_ptr
+from ._lib import (HEAD_DIM, PARTIAL_STRIDE, LayerView, TailArgs, check, lib, ptr, q_dtype_tag, require_cuda,
+                   stream_ptr)
 from .packing import PackedKVLayer, layer_identity, layer_view
 
 
@@ -122,6 +123,8 @@ class DecodeTable:
         after rewriting a layer's ``seg_bounds_per_head`` / ``n_v16_per_head`` / ``K_ch_scale`` /
         ``K_ch_zp`` / ``K_ch_perm_padded_idx_for_Q`` in place; packed payloads and V scales / zero
         points are always read from the layers' own tensors."""
+        if hasattr(self, "_host_io"):
+            del self._host_io                              # recorded launch plans of the host-buffer call
         if self.live_counts or self.nkb_max > 24:
             self.live_counts = True
             return
@@ -250,14 +253,17 @@ def _launch_fused(q: Tensor, table: DecodeTable, partials: Optional[Tensor], out
 def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int = 0, v1: Optional[int] = None,
                   *, out_record: Optional[Tensor] = None, rows: Optional[Tuple[int, int]] = None,
                   seq_part: Optional[Tuple[int, int]] = None, plan: Optional[Tuple[int, int, int]] = None,
-                  ctr_slot: int = 0) -> None:
+                  ctr_slot: int = 0, tail: Optional[TailArgs] = None, tail_rows: int = 0) -> None:
     """ONE launch of the fused kernel on views [v0, v1): whole units, or uniform chunks merged inside
     the kernel (DecodeTable.plan).  The result is the normalised ``out`` [n_views,H_q,128] or the
     un-normalised record per query head ``out_record`` [n_views*H_q,132]; ``seq_part`` = (i, n)
     restricts every head to part i of n of its rows (phase by phase), ``rows`` = (begin, end) to
-    that window of the rows that leaves.  q, out, out_record are the full-table
-    tensors, the view range is cut by pointer offsets; ``out`` may be pinned host memory."""
-    require_cuda(q, "q")
+    that window of the rows that leaves; ``tail`` (with up to ``tail_rows`` live rows per head)
+    adds the uncompressed tail and the token being decoded.  q, out, out_record are the full-table
+    tensors, the view range is cut by pointer offsets; ``out`` and ``q`` may be pinned host memory
+    (addressable from the device)."""
+    if not (q.is_cuda or q.is_pinned()):
+        raise ValueError("q must be a CUDA tensor or pinned host memory")
     if q.shape[-1] != HEAD_DIM or q.numel() != table.n_views * table.H_q * HEAD_DIM:
         raise ValueError(f"q must be [{table.n_views},{table.H_q},{HEAD_DIM}], got {tuple(q.shape)}")
     if not q.is_contiguous():
@@ -273,9 +279,11 @@ def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int 
     sp_i, sp_n = (0, 1) if seq_part is None else (int(seq_part[0]), int(seq_part[1]))
     if sp_n < 1 or not 0 <= sp_i < sp_n:
         raise ValueError(f"bad sequence part {sp_i} of {sp_n}")
-    part_rows = table.unit_rows if sp_n == 1 else -(-table.unit_rows // sp_n) + 128   # a part's rows, at most
+    all_rows = table.unit_rows + (tail_rows if tail is not None else 0)
+    part_rows = all_rows if sp_n == 1 else -(-all_rows // sp_n) + 160   # a part's rows, at most
     live = min(r1, part_rows) - r0
-    k, rows_k, n_whole = plan if plan is not None else table.plan(v1 - v0, None if (rows is None and sp_n == 1) else live)
+    k, rows_k, n_whole = plan if plan is not None else table.plan(
+        v1 - v0, None if (rows is None and sp_n == 1 and all_rows == table.unit_rows) else live)
     hy = table.H_kv * table._n_hgrp
     if plan is not None:                                   # a plan of the whole table: its whole units are the table's first
         n_whole -= v0 * hy
@@ -292,9 +300,22 @@ def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int 
     can = table._can_persist() and (q.data_ptr() + qrow * HEAD_DIM * q.element_size()) % 16 == 0
     want = (table.persistent if table.persistent is not None
             else (k == 1 and items >= table.PERSISTENT_MIN_ROUNDS * table._sms * table.CTAS_PER_SM))
-    persistent = can and want and ctr_slot < table.WORK_CTR_SLOTS
-    fn = lib().rdkv_decode_attn_persistent if persistent else lib().rdkv_decode_attn
+    persistent = can and want and ctr_slot < table.WORK_CTR_SLOTS and tail is None
+    fn = (lib().rdkv_decode_attn_tail if tail is not None
+          else lib().rdkv_decode_attn_persistent if persistent else lib().rdkv_decode_attn)
     extra = (table.work_ctr.data_ptr() + 8 * ctr_slot,) if persistent else ()
+    tail_arg = ()
+    if tail is not None:                                   # this range's views of the per-view tail tensors
+        es = 2
+        tv = TailArgs.from_buffer_copy(tail)
+        for name, per_view in (("new_k", tv.view_stride * es), ("new_v", tv.view_stride * es),
+                               ("n_new_per_view", 4), ("rope_cos", tv.rope_view_stride * _ELEM_SIZE[tv.rope_dtype]),
+                               ("rope_sin", tv.rope_view_stride * _ELEM_SIZE[tv.rope_dtype]),
+                               ("k_cur", table.H_kv * HEAD_DIM * es), ("v_cur", table.H_kv * HEAD_DIM * es)):
+            base = getattr(tv, name)
+            if base:
+                setattr(tv, name, base + v0 * per_view)
+        tail_arg = (C.byref(tv),)
     with torch.cuda.device(table.device):
         check(fn(table.views.data_ptr() + v0 * C.sizeof(LayerView), v1 - v0,
                                      off(q, HEAD_DIM), q_dtype_tag(q), table.H_q, table.H_kv, rows_k, k, n_whole, r0, r1, sp_i, sp_n,
@@ -304,8 +325,77 @@ def _launch_units(q: Tensor, table: DecodeTable, out: Optional[Tensor], v0: int 
                                      0 if table.live_counts else table.nkb_max,
                                      off(ws, k * PARTIAL_STRIDE), table.unit_ctr.data_ptr() + v0 * hy * 4, *extra,
                                      off(out, HEAD_DIM), off(out_record, PARTIAL_STRIDE),
-                                     ptr(table.status), stream_ptr(q.device)),
+                                     ptr(table.status), *tail_arg, stream_ptr(table.device)),
               "rdkv_decode_attn")
+
+
+_ELEM_SIZE = {0: 2, 1: 2, 2: 4}                           # bytes per element of RDKV_F16 / RDKV_BF16 / RDKV_F32
+
+
+def _tail_args(table: DecodeTable, new_k: Optional[Tensor], new_v: Optional[Tensor], n_new, k_cur: Optional[Tensor],
+               v_cur: Optional[Tensor], rope, append: bool) -> Optional[Tuple[TailArgs, int, list]]:
+    """The argument record of the one-launch form for these tail tensors, the most tail rows a head
+    has, and the tensors the record points into (kept alive by the caller until the launch is
+    queued); None when the tensors do not fit it (other types than fp16 / bf16, rows that are not
+    contiguous, unaligned addresses)."""
+    n_views, H_kv = table.n_views, table.H_kv
+    ref = new_k if new_k is not None else k_cur
+    if ref is None or ref.dtype not in (torch.float16, torch.bfloat16):
+        return None
+    ta, keep = TailArgs(), []
+    ta.dtype = q_dtype_tag(ref)
+    rows = 0
+    if new_k is not None:
+        require_cuda(new_k, "new_k"); require_cuda(new_v, "new_v")
+        if new_k.dim() != 4 or tuple(new_k.shape[:2]) != (n_views, H_kv) or new_k.shape[-1] != HEAD_DIM:
+            raise ValueError(f"new_k must be [{n_views},{H_kv},cap,{HEAD_DIM}], got {tuple(new_k.shape)}")
+        if new_v.shape != new_k.shape or new_v.dtype != new_k.dtype or new_v.stride() != new_k.stride():
+            raise ValueError("new_v must match new_k in shape, dtype and strides")
+        cap = int(new_k.shape[2])
+        if (new_k.stride(3) != 1 or (cap > 1 and new_k.stride(2) != HEAD_DIM) or new_k.stride(0) % 8 or new_k.stride(1) % 8
+                or new_k.data_ptr() % 16 or new_v.data_ptr() % 16):
+            return None
+        ta.new_k, ta.new_v, ta.cap = new_k.data_ptr(), new_v.data_ptr(), cap
+        ta.view_stride, ta.head_stride = new_k.stride(0), new_k.stride(1)
+        keep += [new_k, new_v]
+        if isinstance(n_new, Tensor):
+            require_cuda(n_new, "n_new")
+            if n_new.dtype != torch.int32 or n_new.numel() != n_views or not n_new.is_contiguous():
+                raise ValueError("n_new tensor must be contiguous int32 [n_views]")
+            ta.n_new_per_view, rows = n_new.data_ptr(), cap
+            keep.append(n_new)
+        else:
+            rows = int(n_new)
+            if not 0 <= rows <= cap:
+                raise ValueError(f"n_new={rows} outside [0, {cap}]")
+            ta.n_new = rows
+    if k_cur is not None:
+        if v_cur is None:
+            raise ValueError("k_cur needs v_cur")
+        for name, t in (("k_cur", k_cur), ("v_cur", v_cur)):
+            require_cuda(t, name)
+            if tuple(t.shape) != (n_views, H_kv, HEAD_DIM) or t.dtype != ref.dtype or not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous [{n_views},{H_kv},{HEAD_DIM}] of the tail's dtype")
+        ta.k_cur, ta.v_cur = k_cur.data_ptr(), v_cur.data_ptr()
+        keep += [k_cur, v_cur]
+        if append:
+            if new_k is None:
+                raise ValueError("append=True needs the tail buffers new_k / new_v")
+            if not isinstance(n_new, Tensor) and int(n_new) >= int(new_k.shape[2]):
+                raise ValueError("the tail buffers are full: no row left for the new token")
+            ta.append = 1
+    if rope is not None:
+        cos, sin = rope
+        require_cuda(cos, "rope cos"); require_cuda(sin, "rope sin")
+        if cos.shape != sin.shape or cos.dtype != sin.dtype or cos.shape[-1] != HEAD_DIM // 2 or not (
+                cos.is_contiguous() and sin.is_contiguous()):
+            raise ValueError("rope = (cos, sin): contiguous [64] or [n_views,64] tensors of one dtype")
+        if cos.dim() == 2 and cos.shape[0] != n_views or cos.dim() > 2:
+            raise ValueError(f"rope tables must be [64] or [{n_views},64]")
+        ta.rope_cos, ta.rope_sin, ta.rope_dtype = cos.data_ptr(), sin.data_ptr(), q_dtype_tag(cos)
+        ta.rope_view_stride = HEAD_DIM // 2 if cos.dim() == 2 else 0
+        keep += [cos, sin]
+    return ta, rows, keep
 
 
 def decode_attention_partial(q: Tensor, table: DecodeTable, out: Optional[Tensor] = None) -> Tensor:
@@ -368,7 +458,9 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
                             out_partial: Optional[Tensor] = None, new_k: Optional[Tensor] = None,
                             new_v: Optional[Tensor] = None, n_new=0,
                             rows: Optional[Tuple[int, int]] = None,
-                            seq_part: Optional[Tuple[int, int]] = None) -> Tensor:
+                            seq_part: Optional[Tuple[int, int]] = None, k_cur: Optional[Tensor] = None,
+                            v_cur: Optional[Tensor] = None, rope: Optional[Tuple[Tensor, Tensor]] = None,
+                            append: bool = True, one_launch: Optional[bool] = None) -> Tensor:
     """softmax(q·K̂ᵀ/√128)·V̂ over every view of ``table``.
 
     q [n_views,H_q,128] fp16/bf16/fp32 -> out [n_views,H_q,128] fp32.  With
@@ -379,14 +471,41 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
     (begin, end) to that window of the rows that leaves.  ``new_k`` / ``new_v``
     [n_views,H_kv,cap,128] with ``n_new`` live rows add the uncompressed tail of
     decode-appended tokens (Zone C) to the same softmax, as the reference's attention
-    block does (fast_decode.py:1719-1784).
-    One launch without a tail (chunked units are merged inside the kernel), else the
-    fused kernel, the tail kernel and the combine; no allocation after the first
-    call, no host synchronisation.
+    block does (fast_decode.py:1719-1784).  ``k_cur`` / ``v_cur`` [n_views,H_kv,128]: the
+    key and value row of the token being decoded; it joins the softmax and, with
+    ``append``, its rows are written to row ``n_new`` of the tail buffers (the caller
+    counts ``n_new`` up for the next step).  ``rope`` = (cos, sin), [64] or
+    [n_views,64]: the queries and ``k_cur`` are rotated first (half format, as
+    fused_rope does in place, triton_rope.py:35-108; q itself is not written), so the
+    call covers fast_decode.py:1699-1784 of a layer.
+    Always one launch (chunked units are merged inside the kernel) when the tail buffers
+    are fp16 / bf16 with contiguous rows; other tail buffers (``one_launch=False`` forces
+    this form, which takes neither ``k_cur`` nor ``rope``) take the fused kernel, the tail
+    kernel and the combine.  No allocation after the first call, no host synchronisation.
     """
+    if new_k is not None and new_v is None:
+        raise ValueError("new_k needs new_v")
+    if new_k is not None or k_cur is not None or rope is not None:
+        fused = None if one_launch is False else _tail_args(table, new_k, new_v, n_new, k_cur, v_cur, rope, append)
+        if fused is None and (k_cur is not None or rope is not None or one_launch):
+            raise ValueError("the one-launch form needs fp16 / bf16 tail buffers with contiguous, 16-byte aligned rows")
+        if fused is not None:
+            ta, tail_rows, _keep = fused
+            if out_partial is not None:
+                if (out_partial.dtype != torch.float32 or not out_partial.is_contiguous()
+                        or out_partial.numel() != table.n_views * table.H_q * PARTIAL_STRIDE):
+                    raise ValueError(f"out_partial must be contiguous float32 [{table.n_views * table.H_q},{PARTIAL_STRIDE}]")
+                _launch_units(q, table, None, out_record=out_partial, rows=rows, seq_part=seq_part, tail=ta,
+                              tail_rows=tail_rows)
+                return out_partial
+            if out is None:
+                out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=q.device)
+            if (not out.is_contiguous() or out.dtype != torch.float32
+                    or out.numel() != table.n_views * table.H_q * HEAD_DIM):
+                raise ValueError(f"out must be contiguous float32 [{table.n_views},{table.H_q},{HEAD_DIM}]")
+            _launch_units(q, table, out, rows=rows, seq_part=seq_part, tail=ta, tail_rows=tail_rows)
+            return out
     if new_k is not None:
-        if new_v is None:
-            raise ValueError("new_k needs new_v")
         n_rows = table.n_views * table.H_q
         ws = getattr(table, "_tail_ws", None)
         if ws is None:
@@ -419,6 +538,7 @@ def packed_decode_attention(q: Tensor, table: DecodeTable, *, out: Optional[Tens
 
 class _HostIO:
     """Device staging buffer for the queries and the streams of the host-buffer call, kept on the table."""
+    MAX_GRAPHS = 8
 
     def __init__(self, table: DecodeTable, q_dtype: torch.dtype, n_slices: int, growing: bool):
         dev = table.device
@@ -429,8 +549,11 @@ class _HostIO:
         if growing and n_slices > 1:
             # ranges of 1 : 2 : 4 : ... : rest — the first upload, the only one no kernel hides, is short
             unit = max(1, n // (2 ** n_slices - 1))
-            sizes = [unit * 2 ** i for i in range(n_slices - 1)]
-            sizes.append(n - sum(sizes))
+            sizes, left = [], n
+            for i in range(n_slices - 1):
+                sizes.append(min(unit * 2 ** i, left))
+                left -= sizes[-1]
+            sizes.append(left)
         else:
             step = -(-n // n_slices)
             sizes = [min(step, n - a) for a in range(0, n, step)]
@@ -440,21 +563,64 @@ class _HostIO:
                 self.ranges.append((a, a + sz))
                 a += sz
         self.streams = [torch.cuda.Stream(device=dev) for _ in self.ranges]
+        self.capture_stream = torch.cuda.Stream(device=dev)
+        self.graphs: dict = {}                             # (buffers, table, plan) -> the ranges' copies and launches, recorded
+        self.seen: set = set()
+        self.replays: dict = {}                            # the call's arguments as given -> its recording (shortcut of the next call)
+
+
+def _issue_host_ranges(io: "_HostIO", q_host: Tensor, out_host: Tensor, table: DecodeTable, out: Tensor,
+                       direct: bool, plan, in_place: int = 0) -> None:
+    """Every range on its own stream, forked from and joined to the current stream: upload of the
+    range's queries, its launch, and (pageable results only) its download.  The first ``in_place``
+    ranges read their queries straight from the (pinned) host buffer instead of uploading them."""
+    cur = torch.cuda.current_stream(table.device)
+    for slot, ((a, b), st) in enumerate(zip(io.ranges, io.streams)):
+        st.wait_stream(cur)
+        with torch.cuda.stream(st):
+            if slot < in_place:
+                _launch_units(q_host, table, out, a, b, plan=plan, ctr_slot=slot)
+            else:
+                io.q[a:b].copy_(q_host[a:b], non_blocking=True)
+                _launch_units(io.q, table, out, a, b, plan=plan, ctr_slot=slot)
+            if not direct:
+                out_host[a:b].copy_(io.out[a:b], non_blocking=True)
+    for st in io.streams[:len(io.ranges)]:
+        cur.wait_stream(st)
 
 
 def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: Tensor, *,
-                                 slices: Optional[int] = None) -> Tensor:
+                                 slices: Optional[int] = None, graph: Optional[bool] = None,
+                                 growing: Optional[bool] = None, in_place: Optional[int] = None) -> Tensor:
     """Host-buffer form of :func:`packed_decode_attention`: ``q_host`` [n_views,H_q,128]
     (fp16/bf16/fp32) and ``out_host`` [n_views,H_q,128] fp32 live in host memory.
 
-    The views are cut into ``slices`` ranges (default: two when each is at least one full wave of
-    CTAs); every range uploads its queries and runs the
+    The views are cut into ``slices`` ranges (default: sized by the waves of CTAs the table
+    fills, the first ranges short); every range uploads its queries and runs the
     kernel on a stream of its own, so the upload of one range overlaps the kernel of another.
     With a pinned ``out_host`` the kernels write their results straight into it (pinned host
     memory is addressable from the device), so the results cross the bus while the kernels
     run and no separate download is needed; a pageable ``out_host`` gets a copy per range.
+
+    With both buffers pinned, the second call with the same two buffers records the copies and
+    launches of all ranges as one CUDA graph, and that call and later ones replay it: a step then
+    costs one graph launch on the host instead of a dozen stream operations (``graph=False``
+    keeps the stream form; the graph holds the buffers' addresses, the table's and its launch
+    plan; a few recordings are kept per table, for callers that alternate between buffers;
+    :meth:`DecodeTable.refresh` drops them).  The kernels of the first ``in_place`` ranges
+    (default: one in the graph form) read their queries from the pinned buffer itself, so the
+    step does not start with an upload that nothing hides.
     Returns after the results have arrived in ``out_host``.
     """
+    io: Optional[_HostIO] = getattr(table, "_host_io", None)
+    call_key = (q_host.data_ptr(), out_host.data_ptr(), q_host.dtype, q_host.numel(), out_host.numel(), out_host.dtype,
+                slices, graph, growing, in_place)
+    if io is not None:                                     # a call seen before with a recording: nothing else to do
+        g = io.replays.get(call_key)
+        if g is not None:
+            g.replay()
+            torch.cuda.current_stream(table.device).synchronize()
+            return out_host
     if q_host.is_cuda or out_host.is_cuda:
         raise ValueError("packed_decode_attention_host takes host tensors; use packed_decode_attention on the device")
     if tuple(q_host.shape) != (table.n_views, table.H_q, HEAD_DIM) or not q_host.is_contiguous():
@@ -462,30 +628,54 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
     if tuple(out_host.shape) != tuple(q_host.shape) or out_host.dtype != torch.float32 or not out_host.is_contiguous():
         raise ValueError("out_host must be contiguous float32 with q_host's shape")
     q_dtype_tag(q_host)
-    growing = False
-    if slices is None:                                     # two ranges when each is at least a full wave of CTAs (measured best)
-        waves = (table.n_views * table.H_kv * table._n_hgrp) // (table._sms * table.CTAS_PER_SM)
-        slices = 2 if waves >= 2 else 1
+    direct = out_host.is_pinned()
+    use_graph = (direct and q_host.is_pinned()) if graph is None else bool(graph)
+    if use_graph and not (direct and q_host.is_pinned()):
+        raise ValueError("graph=True needs pinned q_host and out_host")
+    waves = (table.n_views * table.H_kv * table._n_hgrp) // (table._sms * table.CTAS_PER_SM)
+    if slices is None:
+        # measured best.  Stream form: two ranges when each is at least a full wave of CTAs (the
+        # host's per-range work is in the way of more).  Graph form: eight ranges for a table of
+        # many waves, two for one of at least one wave.
+        slices = ((8 if waves >= 8 else 2 if waves >= 1 else 1) if use_graph else (2 if waves >= 2 else 1))
+    growing = False if growing is None else bool(growing)  # ranges of 1 : 2 : 4 : ... instead of equal ones
     n_slices = max(1, min(int(slices), table.n_views))
-    io: Optional[_HostIO] = getattr(table, "_host_io", None)
     if io is None or io.key != (q_host.dtype, n_slices, growing):
         io = _HostIO(table, q_host.dtype, n_slices, growing)
         table._host_io = io
-    direct = out_host.is_pinned()
     if not direct and io.out is None:
         io.out = torch.empty((table.n_views, table.H_q, HEAD_DIM), dtype=torch.float32, device=table.device)
     out = out_host if direct else io.out
     cur = torch.cuda.current_stream(table.device)
     plan = table.plan(table.n_views)                       # the device call's launch shape: same results bit for bit
-    for slot, ((a, b), st) in enumerate(zip(io.ranges, io.streams)):
-        st.wait_stream(cur)
-        with torch.cuda.stream(st):
-            io.q[a:b].copy_(q_host[a:b], non_blocking=True)
-            _launch_units(io.q, table, out, a, b, plan=plan, ctr_slot=slot)
-            if not direct:
-                out_host[a:b].copy_(io.out[a:b], non_blocking=True)
-    for st in io.streams[:len(io.ranges)]:
-        cur.wait_stream(st)
+    # leading ranges whose kernels read the queries from the pinned host buffer itself: no upload to wait for
+    n_in_place = (1 if use_graph else 0) if in_place is None else int(in_place)
+    if n_in_place and not q_host.is_pinned():
+        raise ValueError("in_place needs a pinned q_host")
+    if use_graph:
+        key = (q_host.data_ptr(), out_host.data_ptr(), table.views.data_ptr(), plan, n_in_place)
+        g = io.graphs.get(key)
+        if g is None and key in io.seen:                   # second call with these buffers: record, then replay
+            if len(io.graphs) >= _HostIO.MAX_GRAPHS:       # a caller that keeps changing buffers: forget the oldest
+                old = io.graphs.pop(next(iter(io.graphs)))
+                io.replays = {k: v for k, v in io.replays.items() if v is not old}
+            g = torch.cuda.CUDAGraph()
+            io.capture_stream.wait_stream(cur)
+            with torch.cuda.graph(g, stream=io.capture_stream, capture_error_mode="thread_local"):
+                _issue_host_ranges(io, q_host, out_host, table, out, direct, plan, n_in_place)
+            cur.wait_stream(io.capture_stream)
+            io.graphs[key] = g
+        if g is not None:
+            if len(io.replays) >= 4 * _HostIO.MAX_GRAPHS:
+                io.replays.clear()
+            io.replays[call_key] = g
+            g.replay()
+            cur.synchronize()
+            return out_host
+        if len(io.seen) >= 4 * _HostIO.MAX_GRAPHS:
+            io.seen.clear()
+        io.seen.add(key)
+    _issue_host_ranges(io, q_host, out_host, table, out, direct, plan, n_in_place)
     cur.synchronize()
     return out_host
 

@@ -33,7 +33,7 @@ def _score_one_layer(aw: Tensor, q: Tensor, o, v: Tensor, head_dim: int, v_score
     dev = aw.device
     token = torch.empty((B, H, T), dtype=torch.float32, device=dev)
     channel = torch.empty((B, H, D), dtype=torch.float32, device=dev)
-    scratch = torch.empty((B * H, lib().rdkv_score_chunks(T), D), dtype=torch.float32, device=dev)
+    scratch = torch.empty(lib().rdkv_score_scratch_words(B * H, T, D), dtype=torch.float32, device=dev)
     check(lib().rdkv_score_layer(ptr(aw), q_dtype_tag(aw), ptr(q), q_dtype_tag(q), ptr(k), q_dtype_tag(k),
                                  k.stride(1), k.stride(2), B * H, g * W, T, D, ptr(scratch), ptr(token),
                                  ptr(channel), stream_ptr(dev)), "rdkv_score_layer")

@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own
 Python code (PyTorch CPU kernels) on seeded inputs.
 
-    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack] [select] [blockwise]
+    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack] [select] [blockwise] [rope]
     (or RDKV_REFERENCE=/path/to/reference/checkout in the environment; no part named = all)
 
 The reference checkout is only needed to (re)generate the files; the tests read
@@ -382,8 +382,31 @@ def make_blockwise():
     print("blockwise.npz", os.path.getsize(os.path.join(HERE, "blockwise.npz")), "bytes")
 
 
+def make_rope():
+    """fused_rope_ref (obkv_accel/triton_rope.py:141-165) on seeded rows: fp16 and bf16 rows (bf16
+    stored as its 16-bit patterns), tables of the rows' type and fp32 tables."""
+    from obkv_accel.triton_rope import fused_rope_ref
+    gen = torch.Generator().manual_seed(77)
+    out = {}
+    bits = lambda t: t.view(torch.int16).numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.numpy()
+    for tag, dt in (("f16", torch.float16), ("bf16", torch.bfloat16)):
+        for cs_tag, cs_dt in (("same", dt), ("f32", torch.float32)):
+            q = (torch.randn(12, 128, generator=gen) * 1.7).to(dt)
+            k = (torch.randn(4, 128, generator=gen) * 2.3).to(dt)
+            pos = torch.rand(64, generator=gen) * 900.0
+            cos, sin = torch.cos(pos).to(cs_dt), torch.sin(pos).to(cs_dt)
+            q2, k2 = fused_rope_ref(q, k, cos, sin)
+            key = f"{tag}_{cs_tag}_"
+            out.update({key + "q": bits(q), key + "k": bits(k), key + "cos": bits(cos), key + "sin": bits(sin),
+                        key + "q_out": bits(q2), key + "k_out": bits(k2)})
+    np.savez_compressed(os.path.join(HERE, "rope.npz"), **out)
+    print("rope.npz", os.path.getsize(os.path.join(HERE, "rope.npz")), "bytes")
+
+
 if __name__ == "__main__":
-    parts = sys.argv[2:] or ["layers", "scoring", "unpack", "select", "blockwise"]
+    parts = sys.argv[2:] or ["layers", "scoring", "unpack", "select", "blockwise", "rope"]
+    if "rope" in parts:
+        make_rope()
     if "blockwise" in parts:
         make_blockwise()
     if "select" in parts:

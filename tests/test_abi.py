@@ -31,6 +31,7 @@ def test_struct_layout_and_version():
     lib = _lib.lib()
     assert lib.rdkv_version() == _lib.ABI_VERSION
     assert lib.rdkv_sizeof_layer_view() == ctypes.sizeof(_lib.LayerView)
+    assert lib.rdkv_sizeof_tail_args() == ctypes.sizeof(_lib.TailArgs)
     assert lib.rdkv_last_error_string(0) == b"ok"
     assert b"argument" in lib.rdkv_last_error_string(1)
     assert lib.rdkv_decode_stage_bytes(34) >= 4096 + 64 * 34

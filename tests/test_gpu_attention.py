@@ -410,6 +410,50 @@ def test_host_buffer_call_equals_device_call():
         packed_decode_attention_host(q.cuda(), table, out_host)
 
 
+def test_host_buffer_call_replayed_as_a_graph_follows_the_buffers_contents():
+    """With pinned buffers the second call records the ranges' copies and launches as one graph and
+    later calls replay it: every call returns what the device call returns for the queries that
+    are in the buffer at that time; other buffers drop the recording."""
+    from rdkv_b200 import synth
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention, packed_decode_attention_host
+    from rdkv_b200.packing import pack_kv
+    H_kv, g = 4, 4
+    layers, nvs = [], []
+    for i in range(9):
+        seed = synth.unit_seed(6, i, 1)
+        T, N = 1280 + 64 * i, 512 + 32 * i
+        K, V = synth.make_kv(H_kv, T, seed=seed)
+        pl, nv = pack_kv(K.cuda(), V.cuda(), synth.make_v_bits(H_kv, T, N, seed=seed).cuda(),
+                         synth.make_k_bits(H_kv, seed=seed).cuda(), g)
+        layers.append(pl)
+        nvs.append(nv)
+    table = DecodeTable(layers, nvs, H_kv * g)
+    q_host = torch.empty((9, H_kv * g, 128), dtype=torch.bfloat16).pin_memory()
+    out_host = torch.empty((9, H_kv * g, 128)).pin_memory()
+    for step in range(5):                                  # stream form, recording, three replays
+        q = synth.make_q(H_kv * g, seed=10 + step, batch=9, dtype=torch.bfloat16)
+        q_host.copy_(q)
+        out_host.fill_(float("nan"))
+        packed_decode_attention_host(q_host, table, out_host, slices=3)
+        assert torch.equal(out_host, packed_decode_attention(q.cuda(), table).cpu()), step
+        assert len(table._host_io.graphs) == (1 if step >= 1 else 0)
+    other = torch.empty_like(out_host).pin_memory()
+    packed_decode_attention_host(q_host, table, other, slices=3)
+    assert torch.equal(other, out_host)
+    for in_place in (0, 2, 3):                             # ranges whose kernels read the pinned queries themselves
+        for _ in range(3):
+            other.fill_(float("nan"))
+            packed_decode_attention_host(q_host, table, other, slices=3, in_place=in_place)
+            assert torch.equal(other, out_host), in_place
+    table.refresh()                                        # drops the recordings
+    assert not hasattr(table, "_host_io")
+    packed_decode_attention_host(q_host, table, out_host, slices=3, graph=False)
+    assert torch.equal(other, out_host)
+    with pytest.raises(ValueError):
+        packed_decode_attention_host(q_host, table, torch.empty_like(out_host), graph=True)
+    table.check_status()
+
+
 def test_lse_combine_matches_oracle():
     from oracle import ref_attention as RA
     from rdkv_b200.decode import lse_combine

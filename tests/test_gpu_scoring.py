@@ -29,6 +29,25 @@ def test_score_one_layer_matches_reference_vectors():
         _score_one_layer(aw, q, None, k, 128)
 
 
+def test_score_one_layer_on_odd_shapes_matches_torch():
+    """Token counts that are odd or not a multiple of the block, windows that are not a multiple of
+    eight rows, head sizes other than 128, every dtype: against the same sums done by torch."""
+    from rdkv_b200.scoring import _score_one_layer
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    for (B, H, g, W, T, D), dt in (((1, 3, 2, 5, 1031, 128), torch.float16), ((2, 2, 4, 8, 4096, 96), torch.bfloat16),
+                                   ((1, 2, 1, 3, 777, 64), torch.float32), ((1, 1, 7, 9, 2, 256), torch.float16)):
+        aw = torch.softmax(torch.randn(B, H, g, W, T, device="cuda", generator=gen), -1).to(dt)
+        q = torch.randn(B, H, g, W, D, device="cuda", generator=gen).to(dt)
+        k = torch.randn(B, H, T, D, device="cuda", generator=gen).to(dt)
+        tok, ch = _score_one_layer(aw, q, None, k, D, k=k)
+        want_tok = aw.float().sum(dim=(2, 3)).to(dt).float()
+        want_ch = q.float().pow(2).mean(dim=(2, 3)) * k.float().pow(2).mean(dim=2)
+        torch.testing.assert_close(tok, want_tok, rtol={torch.float16: 2e-3, torch.bfloat16: 1e-2, torch.float32: 1e-5}[dt],
+                                   atol=1e-6)
+        torch.testing.assert_close(ch, want_ch, rtol=1e-5, atol=1e-7)
+        assert torch.equal(tok, _score_one_layer(aw, q, None, k, D, k=k)[0])   # fixed summation order
+
+
 def test_score_pooling_is_bit_exact():
     from rdkv_b200.scoring import apply_score_pooling
     g = load_golden("scoring.npz")

@@ -174,3 +174,17 @@ def test_select_and_pack_matches_reference(tag):
         assert np.array_equal(nv, g["new_v_only"])
     else:
         assert nv is None
+
+
+@pytest.mark.parametrize("tag", ["f16", "bf16"])
+@pytest.mark.parametrize("cs", ["same", "f32"])
+def test_rope_oracle_matches_reference_vectors(tag, cs):
+    """fused_rope_ref of the reference (triton_rope.py:141-165) on seeded rows, bit for bit."""
+    from oracle import ref_rope as RR
+    from conftest import load_golden
+    g = load_golden("rope.npz")
+    key = f"{tag}_{cs}_"
+    q_out, k_out = RR.fused_rope(g[key + "q"], g[key + "k"], g[key + "cos"], g[key + "sin"], tag,
+                                 tag if cs == "same" else "f32")
+    assert np.array_equal(q_out.view(np.uint16), g[key + "q_out"].view(np.uint16))
+    assert np.array_equal(k_out.view(np.uint16), g[key + "k_out"].view(np.uint16))
