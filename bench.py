@@ -769,7 +769,38 @@ def run_aux(args, rank, world, device):
     rope = (torch.cos(pos), torch.sin(pos))
     dout = torch.empty(n_views, H * g, 128, device=device)
     tail_bytes = n_views * H * (cap - 1) * 128 * 2 * 2
+    # the two-stage operators on one config-3 layer: score / weighted-sum mode of the fused kernel, and
+    # the scalar kernels that serve shapes outside it (called through the C ABI on the same layer)
+    import ctypes as C
+    from rdkv_b200._lib import check, lib, ptr, q_dtype_tag, stream_ptr
+    from rdkv_b200.k_kernel import k_mixed_qk_dot_into
+    from rdkv_b200.packing import layer_view
+    from rdkv_b200.v_kernel import v_dequant_weighted_sum_dispatch_into
+    pl0, nv0 = layers[0], nvs[0]
+    T_k = int(pl0.T_eff_k)
+    q1 = q[0].contiguous()
+    sc = torch.empty(H * g, T_k, device=device)
+    w1 = torch.softmax(torch.randn(H * g, T_k, generator=gen, device=device), -1)
+    o1 = torch.empty(H * g, 128, device=device)
+    view0, _keep0 = layer_view(pl0, nv0)
+    k_bytes, v_bytes = H * N * 34 + H * 256, H * N * (67.5 + 32) + w1.numel() * 4
+
+    def scalar_k():
+        check(lib().rdkv_k_scores(C.byref(view0), ptr(q1), q_dtype_tag(q1), q1.stride(0), H * g, H, T_k, ptr(sc),
+                                  sc.stride(0), stream_ptr(device)), "rdkv_k_scores")
+
+    def scalar_v():
+        check(lib().rdkv_v_weighted_sum(C.byref(view0), ptr(w1), w1.stride(0), H * g, H, ptr(o1), o1.stride(0),
+                                        stream_ptr(device)), "rdkv_v_weighted_sum")
+
     parts = {
+        "k_mixed_qk_dot_into, one layer (decode_fused_kernel, score mode)": (
+            lambda: k_mixed_qk_dot_into(q1, pl0, T_k, sc), k_bytes + sc.numel() * 4),
+        "v_dequant_weighted_sum_dispatch_into, one layer (decode_fused_kernel, weighted-sum mode)": (
+            lambda: v_dequant_weighted_sum_dispatch_into(w1, pl0, o1, V16=nv0[0], n_v16_per_head=pl0.n_v16_per_head,
+                                                         max_T_v=pl0.T_eff), v_bytes),
+        "k_scores_kernel (scalar), one layer": (scalar_k, k_bytes + sc.numel() * 4),
+        "v_weighted_sum_kernel (scalar), one layer": (scalar_v, v_bytes),
         "decode block, packed zones only (decode_fused_kernel)": (lambda: packed_decode_attention(q, dtab, out=dout), dbytes),
         "decode block, one launch: rotation + new token + 1023-row tail + packed zones (decode_fused_kernel, tail mode)": (
             lambda: packed_decode_attention(q, dtab, out=dout, new_k=new_k, new_v=new_v, n_new=cap - 1, k_cur=k_cur,
@@ -802,7 +833,7 @@ def run_aux(args, rank, world, device):
             "vs_baseline": None, "dtype": "fp16 / u8", "data": "synthetic",
             "config": {"workload": f"aux: decompress {L} config-3 layers; tail attention 128 views x 8 heads x 1024 rows; "
                                    "combine 16384 x 2 records; block scores of 64-token blocks; partition 256 x 32768 maps"},
-            "kernels": out, "peak_kind": kind, "gpu_launches": args.steps * (1 + 1 + 3 + L + 1 + 1 + L + 2),
+            "kernels": out, "peak_kind": kind, "gpu_launches": args.steps * (4 + 1 + 1 + 3 + L + 1 + 1 + L + 2),
             "clocks": sampler.summary()}
 
 

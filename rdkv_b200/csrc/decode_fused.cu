@@ -397,44 +397,41 @@ __device__ __forceinline__ void epi_sync() {
 }
 
 template <bool COMPUTE_ONLY>
-__device__ __noinline__ void final_merge(const float* red, const float* ml, float (*fin)[FW + 3], int gcnt, int how,
-                                         float* out_rows, float* rec0, int64_t rec_stride) {
-  const int tid = threadIdx.x;
-  if (tid < GH) {                                          // per head: maximum, weight of every warp, l, zero-point term
-    const int hq = tid;
+__device__ __noinline__ void final_merge(const float* red, const float* ml, int gcnt, int how, float* out_rows,
+                                         float* rec0, int64_t rec_stride) {
+  // Warp w of the first four takes heads w, w + 4; a lane four channels.  Every lane works out its
+  // head's maximum, the weight of every compute warp's partial, l and the zero-point term for itself
+  // (broadcast reads), so the merge needs no barrier of its own; kept small: it runs once per item,
+  // from a cold instruction cache.
+  const int t = threadIdx.x;
+  if (t >= 128) return;
+  const int d0 = (t & 31) * 4;
+#pragma unroll 1
+  for (int hq = t >> 5; hq < gcnt; hq += 4) {
     float M = M_NONE;
 #pragma unroll
     for (int w = 0; w < FW; ++w) M = fmaxf(M, ml[(w * GH + hq) * 3]);
     float L = 0.f, Z = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int w = 0; w < FW; ++w) {
       const float wgt = ex2(ml[(w * GH + hq) * 3] - M);
       L = fmaf(ml[(w * GH + hq) * 3 + 1], wgt, L);
       Z = fmaf(ml[(w * GH + hq) * 3 + 2], wgt, Z);
-      fin[hq][w] = wgt;
+      const float4 x = *reinterpret_cast<const float4*>(red + (w * GH + hq) * D + d0);
+      o.x = fmaf(x.x, wgt, o.x); o.y = fmaf(x.y, wgt, o.y); o.z = fmaf(x.z, wgt, o.z); o.w = fmaf(x.w, wgt, o.w);
     }
-    fin[hq][FW] = M; fin[hq][FW + 1] = L; fin[hq][FW + 2] = Z;
-  }
-  epi_sync<COMPUTE_ONLY>();
-  if (tid < D) {                                           // thread = channel; heads in turn
-    const int d = tid;
-    for (int hq = 0; hq < gcnt; ++hq) {
-      float o = -fin[hq][FW + 2];
-#pragma unroll
-      for (int w = 0; w < FW; ++w) o = fmaf(red[(w * GH + hq) * D + d], fin[hq][w], o);
-      const float L = fin[hq][FW + 1];
-      if (how == 2) {
-        out_rows[hq * D + d] = o;
-      } else if (how == 1) {
-        out_rows[hq * D + d] = L > 0.f ? o / L : 0.f;
-      } else {
-        float* rec = rec0 + hq * rec_stride;
-        rec[4 + d] = o;
-        if (d == 0) {                                      // m in natural-log units; -inf marks an empty record
-          const float M = fin[hq][FW];
-          rec[0] = M <= M_NONE ? -INFINITY : M * LN2; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f;
-        }
-      }
+    o.x -= Z; o.y -= Z; o.z -= Z; o.w -= Z;
+    if (how == 2) {
+      *reinterpret_cast<float4*>(out_rows + hq * D + d0) = o;
+    } else if (how == 1) {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      *reinterpret_cast<float4*>(out_rows + hq * D + d0) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+    } else {
+      float* rec = rec0 + hq * rec_stride;
+      *reinterpret_cast<float4*>(rec + 4 + d0) = o;
+      if (d0 == 0)                                         // m in natural-log units; -inf marks an empty record
+        *reinterpret_cast<float4*>(rec) = make_float4(M <= M_NONE ? -INFINITY : M * LN2, L, 0.f, 0.f);
     }
   }
 }
@@ -550,7 +547,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   __shared__ rdkv_layer_view v;
   __shared__ CtaGeom G;
   __shared__ float s_ml[FW][GH][3];               // per warp: m, l, zero-point term
-  __shared__ float s_fin[GH][FW + 3];             // final merge: weight of each warp's partial; M, L, zero-point term
+  __shared__ float s_bias[FW][GH];                // zero-point bias of the folded queries: the warps' partial sums
   __shared__ EpiInfo s_epi;
   __shared__ TileInfo s_tile[FSTAGES];
   __shared__ TilePlan s_plan[PLAN_TILES];          // private to the staging warp
@@ -935,7 +932,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     }
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
-    if (j == 0) s_ml[warp][r][0] = bias_part;            // summed over the warps where it is used
+    if (j == 0) s_bias[warp][r] = bias_part;             // summed over the warps where it is used
     bar_sync(BAR_COMPUTE, FW * 32);
   } else if (MODE != MODE_WEIGHTS && warp < FW && fits) {
     {
@@ -968,7 +965,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
     }
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
-    if (j == 0) s_ml[warp][r][0] = bias_part;            // summed over the warps where it is used
+    if (j == 0) s_bias[warp][r] = bias_part;             // summed over the warps where it is used
     bar_sync(BAR_COMPUTE, FW * 32);
   }
   if (warp < FW) bar_sync(BAR_GEOM, CTA_THREADS);          // geometry published
@@ -1185,7 +1182,7 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   }
   __syncthreads();
   const EpiInfo ep = s_epi;
-  final_merge<false>(red, &s_ml[0][0][0], s_fin, ep.gcnt, ep.how, ep.out_rows, ep.rec0, ep.rec_stride);
+  final_merge<false>(red, &s_ml[0][0][0], ep.gcnt, ep.how, ep.out_rows, ep.rec0, ep.rec_stride);
   if (ATTN && ep.n_chunks > 1 && unit_ctr != nullptr)
     chunk_merge<false>(partials, unit_ctr + ep.unit_y, ep.n_chunks, ep.gcnt, ep.row0, out, merged);
 }
@@ -1223,7 +1220,7 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ CtaGeom G;                            // private to the staging warp
   __shared__ float s_ml[FW][GH][3];
-  __shared__ float s_fin[GH][FW + 3];
+  __shared__ float s_bias[FW][GH];                 // (not in s_ml: a warp may fold the next item while others still merge this one)
   __shared__ EpiInfo s_epi;
   __shared__ TileInfo s_tile[FSTAGES];
   __shared__ ItemInfo s_item[2];
@@ -1461,20 +1458,6 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
       const int total_tiles = ii.total, n_it = max(total_tiles, 1);
       const KDims kd = k_dims(ii.n2p, ii.n4p, ii.n8c);
       const StageLayout SL = stage_layout(kd.sub2, kd.sub4, kd.n8);
-      {
-        const int n_chunks_ = n_chunks;
-        float* rec_base = (n_chunks_ > 1 || merged == nullptr) ? partials : merged;
-        if (tid == 0) {
-          s_epi.out_rows = out != nullptr ? out + ((int64_t)view_idx * H_q + hq0) * D : nullptr;
-          s_epi.rec0 = rec_base != nullptr
-                           ? rec_base + ((int64_t)(view_idx * H_q + hq0) * n_chunks_ + chunk) * RDKV_PARTIAL_STRIDE
-                           : nullptr;
-          s_epi.rec_stride = (int64_t)n_chunks_ * RDKV_PARTIAL_STRIDE;
-          s_epi.row0 = (int64_t)view_idx * H_q + hq0;
-          s_epi.how = (n_chunks_ == 1 && out != nullptr) ? 1 : 0;
-          s_epi.gcnt = gcnt; s_epi.n_chunks = n_chunks_; s_epi.unit_y = unit_y;
-        }
-      }
       // fold the item's queries from its header: q*scale in MMA fragment order, zero-point bias
       {
         const KSlotRec* hk = reinterpret_cast<const KSlotRec*>(hdr + hdr_q_bytes);
@@ -1501,16 +1484,36 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
           }
           qsA[kb * 32 + lane] = make_uint2(pack_h2(val[0], val[1]), pack_h2(val[2], val[3]));
         };
-        float b0 = 0.f, b1 = 0.f;
-        if (warp < kd.nkb) fold_block(hk[warp * 32 + lane], warp, b0);
-        if (warp + FW < kd.nkb) fold_block(hk[(warp + FW) * 32 + lane], warp + FW, b1);
-        float bias_part = b0 + b1;
+        // one copy of the fold code (it runs once per item, from a cold instruction cache); the sums
+        // are formed as in the one-item form of the kernel: the first two blocks of a warp on their own
+        // and then added, further blocks term by term
+        float bias_part = 0.f;
+        int nb = 0;
 #pragma unroll 1
-        for (int kb = warp + 2 * FW; kb < kd.nkb; kb += FW) fold_block(hk[kb * 32 + lane], kb, bias_part);
+        for (int kb = warp; kb < kd.nkb; kb += FW, ++nb) {
+          float b = nb < 2 ? 0.f : bias_part;
+          fold_block(hk[kb * 32 + lane], kb, b);
+          bias_part = nb < 2 ? bias_part + b : b;
+        }
         bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
         bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);
-        if (j == 0) s_ml[warp][r][0] = bias_part;
+        if (j == 0) s_bias[warp][r] = bias_part;
         bar_sync(BAR_COMPUTE, FW * 32);
+      }
+      // (written after the barrier: every warp has left the previous item's merge, which reads it)
+      {
+        const int n_chunks_ = n_chunks;
+        float* rec_base = (n_chunks_ > 1 || merged == nullptr) ? partials : merged;
+        if (tid == 0) {
+          s_epi.out_rows = out != nullptr ? out + ((int64_t)view_idx * H_q + hq0) * D : nullptr;
+          s_epi.rec0 = rec_base != nullptr
+                           ? rec_base + ((int64_t)(view_idx * H_q + hq0) * n_chunks_ + chunk) * RDKV_PARTIAL_STRIDE
+                           : nullptr;
+          s_epi.rec_stride = (int64_t)n_chunks_ * RDKV_PARTIAL_STRIDE;
+          s_epi.row0 = (int64_t)view_idx * H_q + hq0;
+          s_epi.how = (n_chunks_ == 1 && out != nullptr) ? 1 : 0;
+          s_epi.gcnt = gcnt; s_epi.n_chunks = n_chunks_; s_epi.unit_y = unit_y;
+        }
       }
   constexpr bool TAIL = false, ATTN = MODE == MODE_ATTN;   // (no uncompressed tail in this form)
   float tref_e = 0.f, tref_o = 0.f;
@@ -1559,7 +1562,7 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
       }
       bar_sync(BAR_COMPUTE, FW * 32);
       const EpiInfo ep = s_epi;
-      final_merge<true>(red, &s_ml[0][0][0], s_fin, ep.gcnt, ep.how, ep.out_rows, ep.rec0, ep.rec_stride);
+      final_merge<true>(red, &s_ml[0][0][0], ep.gcnt, ep.how, ep.out_rows, ep.rec0, ep.rec_stride);
       if (ep.n_chunks > 1 && unit_ctr != nullptr)
         chunk_merge<true>(partials, unit_ctr + ep.unit_y, ep.n_chunks, ep.gcnt, ep.row0, out, merged);
       __syncwarp();
