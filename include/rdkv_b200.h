@@ -439,9 +439,16 @@ typedef struct rdkv_pack_job {
 } rdkv_pack_job;
 
 int rdkv_sizeof_pack_job(void);
-/* max_slots: max over jobs of max_n2+max_n4+max_n8+max_n16; max_t_k, max_d_pad: max over jobs. */
+/* max_slots: max over jobs of max_n2+max_n4+max_n8+max_n16; max_t_k, max_d_pad: max over jobs.
+ * k_passes: how K is packed.  1 = one pass over the kept rows (a cluster of 8 CTAs per (layer, head)
+ * keeps them in shared memory between the extrema and the quantisation; head size 128, and
+ * ceil(max_t_k / 8) rows of max_d_pad fp16 values must fit 200 KB, else RDKV_ERR_TOO_LARGE);
+ * 3 = extrema pass, parameter pass, quantise pass (the rows are read twice); 0 = one pass where
+ * it fits.  Both give the same bytes.  max_k_quads: max over jobs of n_ch2_pad/4 +
+ * ceil(n_ch4_pad/4) + ceil(n_ch8/4) (what a parked row of the one-pass form holds, in 8-byte
+ * units), or 0 for the bound max_d_pad/4 + 2. */
 int rdkv_pack_kv_batched(const rdkv_pack_job* jobs, int n_jobs, int H, int D, int max_slots,
-                         int max_t_k, int max_d_pad, void* stream);
+                         int max_t_k, int max_d_pad, int k_passes, int max_k_quads, void* stream);
 
 /* ── prefill: batched Lagrangian bit allocator ────────────────────────────────
  * Replaces knapsack_bit_allocation_batched (knapsack_solver.py:121-248).

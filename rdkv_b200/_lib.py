@@ -117,7 +117,7 @@ _PROTOTYPES = {
     "rdkv_block_scores": ([_p, _i, _i64, _i64, _p, _i, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p], _i),
     "rdkv_unpack_layer": ([_p, _i, _i, _p, _i64, _p, _i, _i, _i, _p, _p, _i64, _i, _p], _i),
     "rdkv_sizeof_pack_job": ([], _i),
-    "rdkv_pack_kv_batched": ([_p, _i, _i, _i, _i, _i, _i, _p], _i),
+    "rdkv_pack_kv_batched": ([_p, _i, _i, _i, _i, _i, _i, _i, _i, _p], _i),
     "rdkv_knapsack_batched": ([_p, _i64, _i, _i, _p, C.POINTER(_f), C.POINTER(_f), _i, _i, _f, _p, _p, _p], _i),
     "rdkv_knapsack_rows": ([_p, _i64, _i, _i, _p, C.POINTER(_f), C.POINTER(_f), _i, _i, C.c_double, _p, _p], _i),
     "rdkv_knapsack_static_max_rows": ([], _i),

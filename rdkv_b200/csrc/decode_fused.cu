@@ -918,17 +918,19 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       }
       qsA[kb * 32 + lane] = make_uint2(pack_h2(val[0], val[1]), pack_h2(val[2], val[3]));
     };
-    {
-      float b0 = 0.f, b1 = 0.f;
-      if (warp < kd.nkb) fold_block(km0, warp, b0);
-      if (warp + FW < kd.nkb) fold_block(km1, warp + FW, b1);
-      bias_part = b0 + b1;
-    }
+    // (one copy of the fold code: it runs once per CTA, from a cold instruction cache.  The first
+    // two blocks of a warp are summed on their own and then added, further blocks term by term.)
+    int nb = 0;
 #pragma unroll 1
-    for (int kb = warp + 2 * FW; kb < kd.nkb; kb += FW) {
-      const int4 t = *(reinterpret_cast<const int4*>(kslots + unit * nkb_max * 32 + lane) + kb * 32);
-      const KSlotRec km = {(uint32_t)t.x, (uint32_t)t.y, (uint32_t)t.z, (uint32_t)t.w};
-      fold_block(km, kb, bias_part);
+    for (int kb = warp; kb < kd.nkb; kb += FW, ++nb) {
+      KSlotRec km = nb == 0 ? km0 : km1;
+      if (nb >= 2) {
+        const int4 t = *(reinterpret_cast<const int4*>(kslots + unit * nkb_max * 32 + lane) + kb * 32);
+        km = {(uint32_t)t.x, (uint32_t)t.y, (uint32_t)t.z, (uint32_t)t.w};
+      }
+      float b = nb < 2 ? 0.f : bias_part;
+      fold_block(km, kb, b);
+      bias_part = nb < 2 ? bias_part + b : b;
     }
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 1);
     bias_part += __shfl_xor_sync(0xffffffffu, bias_part, 2);

@@ -4,6 +4,8 @@
 // Bit-exactness contract (reference: obkv_accel/packing.py:141-165): fp32 math
 // with one IEEE rounding per operation — true division (__fdiv_rn), no fused
 // multiply-add, round-half-to-even (rintf), fp16 outputs rounded to nearest.
+#include <cooperative_groups.h>
+
 #include "rdkv_common.cuh"
 
 namespace rdkv {
@@ -38,9 +40,42 @@ partition_kernel(const void* bits, int elem_size, int64_t row_stride, int len, i
   const int per = (len + PART_THREADS - 1) / PART_THREADS;
   const int lo = min(len, tid * per), hi = min(len, lo + per);
   int cnt[4] = {0, 0, 0, 0};
-  for (int i = lo; i < hi; ++i) {
-    const int c = bit_class(load_int(bits, elem_size, off + i), mode);
-    if (c >= 0) cnt[c]++;
+  // Up to 32 elements per thread are classified once and remembered as three bit masks (kept, class
+  // bit 0, class bit 1), so the scatter pass below does not read the map again; 16-bit maps whose
+  // per-thread chunks are 16-byte aligned are read with 16-byte loads.
+  const bool cached = per <= 32;
+  uint32_t m_keep = 0u, m_c0 = 0u, m_c1 = 0u;
+  auto note = [&](int k, int64_t b) {
+    const int c = bit_class(b, mode);
+    if (c >= 0) {
+      cnt[c]++;
+      m_keep |= 1u << k; m_c0 |= (uint32_t)(c & 1) << k; m_c1 |= (uint32_t)(c >> 1) << k;
+    }
+  };
+  const bool vec = cached && elem_size == 2 && (per & 7) == 0 && hi - lo == per &&
+                   ((reinterpret_cast<uintptr_t>(bits) + 2 * (off + lo)) & 15) == 0;
+  if (vec) {
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const int16_t*>(bits) + off + lo);
+    uint4 w[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) w[u] = u * 8 < per ? __ldg(src + u) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (u * 8 >= per) break;
+      const uint32_t x[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        note(8 * u + 2 * e, (int16_t)(x[e] & 0xFFFFu));
+        note(8 * u + 2 * e + 1, (int16_t)(x[e] >> 16));
+      }
+    }
+  } else if (cached) {
+    for (int i = lo; i < hi; ++i) note(i - lo, load_int(bits, elem_size, off + i));
+  } else {
+    for (int i = lo; i < hi; ++i) {
+      const int c = bit_class(load_int(bits, elem_size, off + i), mode);
+      if (c >= 0) cnt[c]++;
+    }
   }
   int excl[4];
 #pragma unroll
@@ -81,9 +116,17 @@ partition_kernel(const void* bits, int elem_size, int64_t row_stride, int len, i
 #pragma unroll
   for (int c = 0; c < 4; ++c) pos[c] = class_base[c] + warp_tot[c][warp] + excl[c];
   int32_t* orow = order + (int64_t)row * len;
-  for (int i = lo; i < hi; ++i) {
-    const int c = bit_class(load_int(bits, elem_size, off + i), mode);
-    if (c >= 0) orow[pos[c]++] = i;
+  if (cached) {
+    for (uint32_t m = m_keep; m != 0u; m &= m - 1) {       // kept elements in ascending order
+      const int k = __ffs(m) - 1;
+      const int c = ((m_c0 >> k) & 1u) | (((m_c1 >> k) & 1u) << 1);
+      orow[pos[c]++] = lo + k;
+    }
+  } else {
+    for (int i = lo; i < hi; ++i) {
+      const int c = bit_class(load_int(bits, elem_size, off + i), mode);
+      if (c >= 0) orow[pos[c]++] = i;
+    }
   }
   const int kept = class_base[4];
   for (int i = kept + tid; i < len; i += PART_THREADS) orow[i] = -1;
@@ -894,6 +937,254 @@ pack_k_quant_batched_kernel(const rdkv_pack_job* __restrict__ jobs) {
   pack_k_quant_body(A, blockIdx.y, blockIdx.x, pk_smem);
 }
 
+// ── K in ONE pass over the kept rows ─────────────────────────────────────────
+// A thread-block cluster of KOP_CL CTAs per (layer, KV head); CTA c of the cluster owns the stripe
+// rows [c*rows_per, (c+1)*rows_per).  Phase A: its warps gather those rows from the context (whole
+// 256-byte rows, 16 in flight per warp), keep the extrema of all 128 channels in registers and park
+// the KEPT channels of every row in shared memory (fp16, in the order the quantisation phase reads
+// them: the four values of a lane's quad side by side).  The CTAs then publish
+// their extrema per channel slot; after a cluster barrier every CTA reduces the eight sets (read
+// from the other CTAs' shared memory; minima and maxima do not depend on the order) to scale and
+// zero point per slot, and the first CTA writes the head's tables.  Phase B: every CTA quantises
+// and bit-packs its own rows out of shared memory (the lane-quad scheme of pack_k_quant_body).
+// The kept rows are read from DRAM once instead of twice.  128 channels, fp16 rows.
+constexpr int KOP_CL = 8;
+constexpr int KOP_WARPS = 8;
+constexpr int KOP_MAX_SMEM = 200 * 1024;
+
+__host__ __device__ inline int kop_rows_per_cta(int t_k) { return (((t_k + KOP_CL - 1) / KOP_CL) + 31) & ~31; }
+// (a parked row holds a "quad" of four fp16 values per lane of the quantisation phase: at most
+//  d_pad/4 + 2 quads of 8 bytes)
+__host__ __device__ inline int kop_quads_bound(int d_pad) { return d_pad / 4 + 2; }
+__host__ __device__ inline size_t kop_smem(int t_k, int d_pad, int quads) {
+  return (size_t)d_pad * 20 + 256 + 16 + (size_t)kop_rows_per_cta(t_k) * 8 * quads;
+}
+
+__global__ void __launch_bounds__(KOP_WARPS * 32)
+pack_k_onepass_batched_kernel(const rdkv_pack_job* __restrict__ jobs, int rows_cap, int quads_cap) {
+  namespace cg = cooperative_groups;
+  extern __shared__ __align__(16) unsigned char kop_smem_raw[];
+  __shared__ PackKArgs A;
+  __shared__ __half2 s_wlo[KOP_WARPS][64], s_whi[KOP_WARPS][64];   // per warp: extrema of channel pairs
+  __shared__ int s_pad[KOP_WARPS];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  if (threadIdx.x == 0) job_to_kargs(jobs[blockIdx.z], A);
+  __syncthreads();
+  const int t_k = A.t_k, n2p = A.n2p, n4p = A.n4p, n8p = A.n8p, d_pad = n2p + n4p + n8p;
+  if (t_k <= 0 || d_pad == 0) return;                      // (the same for every CTA of the cluster)
+  const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const KMaps m = load_maps(h, A.tok_order, A.tok_order_rs, A.tok_counts, A.tok_counts_rs, A.max_t_v, t_k,
+                            A.ch_order, A.ch_order_rs, A.ch_counts, A.ch_counts_rs, n2p, n4p, n8p);
+  float* s_ext = reinterpret_cast<float*>(kop_smem_raw);          // [2][d_pad] this CTA's extrema per slot
+  float* s_scale = s_ext + 2 * d_pad;                              // [d_pad]
+  float* s_zp = s_scale + d_pad;                                   // [d_pad]
+  int* s_ch = reinterpret_cast<int*>(s_zp + d_pad);               // [d_pad] channel of a slot, or -1
+  int16_t* s_c2s = reinterpret_cast<int16_t*>(s_ch + d_pad);      // [128] where a channel's value is parked in a row (fp16 index), or -1
+  uint16_t* s_rows = reinterpret_cast<uint16_t*>(kop_smem_raw + (((size_t)d_pad * 20 + 256 + 15) & ~(size_t)15));
+  const int rows_per = min(kop_rows_per_cta(t_k), rows_cap);
+  const int r0 = min(t_k, rank * rows_per), r1 = min(t_k, r0 + rows_per), n_rows = r1 - r0;
+  // quads of the quantisation phase: four channel slots whose codes land in one output byte (2-bit),
+  // two adjacent bytes (4-bit) or four adjacent bytes (8-bit); slot p is value v of quad q
+  const int sub2 = n2p / 4, sub4 = n4p / 2;
+  const int nq2 = sub2, nq4 = (sub4 + 1) / 2, n8 = n8p, nq8 = (n8 + 3) / 4, base8 = n2p + n4p;
+  const int n_quads = nq2 + nq4 + nq8;
+  if (n_quads > quads_cap) return;                         // (the launch has no room for this layer's rows: refused on the host)
+  const int row_h = 4 * n_quads;                                    // fp16 values per parked row
+  auto park_pos = [&](int p) {
+    if (p < n2p) return 4 * (p % sub2) + p / sub2;
+    if (p < base8) { const int b = (p - n2p) % sub4, hi = (p - n2p) / sub4; return 4 * (nq2 + b / 2) + 2 * (b & 1) + hi; }
+    return 4 * (nq2 + nq4) + (p - base8);
+  };
+  if (tid < 128) s_c2s[tid] = -1;
+  {                                                         // rows start as zeros: slots without a channel, rows without a token
+    uint4* z = reinterpret_cast<uint4*>(s_rows);
+    const int n16 = (int)(((size_t)n_rows * row_h * 2 + 15) / 16);
+    for (int i = tid; i < n16; i += blockDim.x) z[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  __syncthreads();
+  for (int p = tid; p < d_pad; p += blockDim.x) {
+    const int ch = slot_channel(m, p);
+    s_ch[p] = ch;
+    if (ch >= 0) s_c2s[ch] = (int16_t)park_pos(p);
+  }
+  __syncthreads();
+
+  // ── phase A: gather, extrema, kept channels to shared memory ──
+  const bool aligned = pack_k_fast(128, A.k_row_stride, A.K + h * A.k_head_stride) && (A.k_head_stride & 3) == 0;
+  int sl[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) sl[e] = s_c2s[4 * lane + e];
+  const __half2 inf2 = __float2half2_rn(INFINITY), ninf2 = __float2half2_rn(-INFINITY);
+  __half2 lo2[2] = {inf2, inf2}, hi2[2] = {ninf2, ninf2};
+  bool pad = false;
+  const uint16_t* Kh = A.K + h * A.k_head_stride + 4 * lane;
+  for (int s0 = r0 + warp * 16; s0 < r1; s0 += KOP_WARPS * 16) {
+    const int tok_l = (lane < 16 && s0 + lane < r1) ? stripe_token(m, s0 + lane) : -2;
+    pad = pad || __any_sync(0xffffffffu, tok_l == -1);
+    uint2 w[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int tok = __shfl_sync(0xffffffffu, tok_l, k);
+      w[k] = make_uint2(0u, 0u);
+      if (tok >= 0) {
+        const uint16_t* src = Kh + (int64_t)tok * A.k_row_stride;
+        if (aligned) w[k] = *reinterpret_cast<const uint2*>(src);
+        else w[k] = make_uint2((uint32_t)src[0] | (uint32_t)src[1] << 16, (uint32_t)src[2] | (uint32_t)src[3] << 16);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int tok = __shfl_sync(0xffffffffu, tok_l, k);
+      if (tok == -2) continue;                               // (warp-uniform) past the CTA's rows
+      if (tok >= 0) {
+        const __half2 a = *reinterpret_cast<const __half2*>(&w[k].x), c = *reinterpret_cast<const __half2*>(&w[k].y);
+        lo2[0] = __hmin2(lo2[0], a); hi2[0] = __hmax2(hi2[0], a);
+        lo2[1] = __hmin2(lo2[1], c); hi2[1] = __hmax2(hi2[1], c);
+      }
+      if (tok < 0) continue;                                 // a row without a token stays a row of zeros
+      uint16_t* row = s_rows + (size_t)(s0 + k - r0) * row_h;
+      if (sl[0] >= 0) row[sl[0]] = (uint16_t)(w[k].x & 0xFFFFu);
+      if (sl[1] >= 0) row[sl[1]] = (uint16_t)(w[k].x >> 16);
+      if (sl[2] >= 0) row[sl[2]] = (uint16_t)(w[k].y & 0xFFFFu);
+      if (sl[3] >= 0) row[sl[3]] = (uint16_t)(w[k].y >> 16);
+    }
+  }
+  s_wlo[warp][2 * lane] = lo2[0]; s_wlo[warp][2 * lane + 1] = lo2[1];
+  s_whi[warp][2 * lane] = hi2[0]; s_whi[warp][2 * lane + 1] = hi2[1];
+  if (lane == 0) s_pad[warp] = pad ? 1 : 0;
+  __syncthreads();
+  {
+    bool any_pad = false;
+#pragma unroll
+    for (int w = 0; w < KOP_WARPS; ++w) any_pad = any_pad || s_pad[w] != 0;
+    for (int p = tid; p < d_pad; p += blockDim.x) {
+      const int ch = s_ch[p];
+      float l = INFINITY, u = -INFINITY;
+      if (n_rows > 0) {
+        if (ch < 0) { l = 0.f; u = 0.f; }
+        else {
+          const __half* wl = reinterpret_cast<const __half*>(&s_wlo[0][0]);
+          const __half* wh = reinterpret_cast<const __half*>(&s_whi[0][0]);
+#pragma unroll
+          for (int w = 0; w < KOP_WARPS; ++w) {
+            l = fminf(l, __half2float(wl[w * 128 + ch])); u = fmaxf(u, __half2float(wh[w * 128 + ch]));
+          }
+          if (any_pad) { l = fminf(l, 0.f); u = fmaxf(u, 0.f); }
+        }
+      }
+      s_ext[p] = l; s_ext[d_pad + p] = u;
+    }
+  }
+  cluster.sync();
+  // ── the head's parameters from the eight CTAs' extrema ──
+  for (int p = tid; p < d_pad; p += blockDim.x) {
+    float lo = INFINITY, hi = -INFINITY;
+#pragma unroll
+    for (int rk = 0; rk < KOP_CL; ++rk) {
+      const float* e = cluster.map_shared_rank(s_ext, rk);
+      lo = fminf(lo, e[p]); hi = fmaxf(hi, e[d_pad + p]);
+    }
+    const int qbits = p < n2p ? 2 : p < n2p + n4p ? 4 : 8;
+    const QParam qp = make_qparam(lo, hi, (float)((1 << qbits) - 1));
+    s_scale[p] = qp.scale; s_zp[p] = qp.zp;
+    if (rank == 0) {
+      A.out_scale[(int64_t)h * d_pad + p] = f2h_bits(qp.scale);
+      A.out_zp[(int64_t)h * d_pad + p] = f2h_bits(qp.zp);
+      const int64_t pc = s_ch[p] < 0 ? 0 : s_ch[p];
+      if (A.perm != nullptr) A.perm[(int64_t)h * d_pad + p] = pc;
+      if (A.perm_q != nullptr)
+        for (int i = 0; i < A.gqa; ++i) A.perm_q[((int64_t)h * A.gqa + i) * d_pad + p] = pc;
+    }
+  }
+  if (rank == 0) {
+    const int kept = m.n2c + m.n4c + m.n8c;
+    if (A.sort_idx != nullptr)
+      for (int j = tid; j < A.d_kept_max; j += blockDim.x)
+        A.sort_idx[(int64_t)h * A.d_kept_max + j] = j < kept ? m.ch_order[j] : 0;
+    if (A.seg_bounds != nullptr && tid == 0) {
+      A.seg_bounds[h * 3 + 0] = m.n2c; A.seg_bounds[h * 3 + 1] = m.n4c; A.seg_bounds[h * 3 + 2] = m.n8c;
+    }
+  }
+  cluster.sync();                                          // everybody has read everybody's extrema; parameters visible
+
+  // ── phase B: quantise and bit-pack this CTA's rows out of shared memory ──
+  const int64_t rows_k = A.rows_k;
+  const int qn = n_quads <= 8 ? 8 : n_quads <= 16 ? 16 : 32;   // lanes per row
+  const int rpp = 32 / qn, rsub = lane / qn;                   // rows per pass, this lane's row of a pass
+  const int rpw = rows_per / KOP_WARPS;                        // rows per warp (a multiple of 4)
+  const int wrow0 = warp * rpw;                                // this warp's first row within the CTA
+  const int kmax = min(rpw, n_rows - wrow0);                   // rows of this warp that exist
+  for (int q = lane % qn; q < n_quads; q += qn) {
+    int slq[4], nv, nb, shift, width, col;
+    float qmax;
+    uint8_t* dst;
+    if (q < nq2) {
+      nv = 4; nb = 1; shift = 2; qmax = 3.f; dst = A.k2; width = sub2; col = q;
+#pragma unroll
+      for (int v = 0; v < 4; ++v) slq[v] = q + v * sub2;
+    } else if (q < nq2 + nq4) {
+      const int b0 = 2 * (q - nq2);
+      nb = b0 + 1 < sub4 ? 2 : 1; nv = 2 * nb; shift = 4; qmax = 15.f; dst = A.k4; width = sub4; col = b0;
+      slq[0] = n2p + b0; slq[1] = n2p + b0 + sub4; slq[2] = n2p + b0 + 1; slq[3] = n2p + b0 + 1 + sub4;
+    } else {
+      const int b0 = 4 * (q - nq2 - nq4);
+      nb = min(4, n8 - b0); nv = nb; shift = 8; qmax = 255.f; dst = A.k8; width = n8; col = b0;
+#pragma unroll
+      for (int v = 0; v < 4; ++v) slq[v] = base8 + b0 + v;
+    }
+    float sc[4], zp[4], rinv[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const bool on = v < nv;
+      const int x = on ? slq[v] : slq[0];
+      sc[v] = s_scale[x];
+      zp[v] = on ? s_zp[x] : 0.f;                            // (a value that does not exist is a parked zero: code 0)
+      rinv[v] = on ? __frcp_rn(sc[v]) : 0.f;
+    }
+    const float mult = (float)(1 << shift);
+    uint8_t* out = dst + ((int64_t)h * rows_k + r0 + wrow0) * width + col;
+    const int am = nb == 2 ? 1 : 3;
+    const bool al = (nb == 2 || nb == 4) && (reinterpret_cast<uintptr_t>(out) & am) == 0 && (width & am) == 0;
+    const int how = nb == 1 ? 0 : (al && nb == 2) ? 1 : (al && nb == 4) ? 2 : 3;
+    const uint32_t rstride = 2u * (uint32_t)row_h;
+    const uint32_t qa = (uint32_t)__cvta_generic_to_shared(s_rows + (size_t)wrow0 * row_h) + 8u * (uint32_t)q;
+#pragma unroll 2
+    for (int k = rsub; k < kmax; k += rpp) {
+      uint2 raw;                                             // the quad's four fp16 values of row k
+      asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(raw.x), "=r"(raw.y) : "r"(qa + k * rstride));
+      const float2 x01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+      const float2 x23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+      const float x[4] = {x01.x, x01.y, x23.x, x23.y};
+      float c[4];
+      bool tie = false;
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {                          // quant_code_fast_f, the rare exact path taken for all four at once
+        const float y = __fmaf_rn(x[v], rinv[v], zp[v]);
+        const float yc = fminf(fmaxf(y, 0.f), qmax);
+        c[v] = __fadd_rn(__fadd_rn(yc, 12582912.f), -12582912.f);
+        tie = tie || fabsf(__fsub_rn(yc, c[v])) > 0.5f - 1.3e-4f;
+      }
+      if (tie) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          QParam qp; qp.scale = sc[v]; qp.zp = zp[v]; qp.qmax = qmax;
+          c[v] = quant_code_fast_f(x[v], rinv[v], qp);
+        }
+      }
+      // codes are small integers: bytes assemble exactly in fp32 (at most 16 bits per half)
+      const unsigned word = (unsigned)__fmaf_rn(c[1], mult, c[0]) | (unsigned)__fmaf_rn(c[3], mult, c[2]) << (2 * shift);
+      uint8_t* o = out + (int64_t)k * width;
+      if (how == 0) o[0] = (uint8_t)word;
+      else if (how == 1) *reinterpret_cast<uint16_t*>(o) = (uint16_t)word;
+      else if (how == 2) *reinterpret_cast<uint32_t*>(o) = word;
+      else {
+        for (int e = 0; e < nb; ++e) o[e] = (uint8_t)(word >> (8 * e));
+      }
+    }
+  }
+}
+
 }  // namespace rdkv
 
 using namespace rdkv;
@@ -995,7 +1286,9 @@ extern "C" int rdkv_pack_k(const uint16_t* K, int64_t k_head_stride, int64_t k_r
 extern "C" int rdkv_sizeof_pack_job(void) { return (int)sizeof(rdkv_pack_job); }
 
 extern "C" int rdkv_pack_kv_batched(const rdkv_pack_job* jobs, int n_jobs, int H, int D, int max_slots,
-                                    int max_t_k, int max_d_pad, void* stream) {
+                                    int max_t_k, int max_d_pad, int k_passes, int max_k_quads, void* stream) {
+  if (k_passes != 0 && k_passes != 1 && k_passes != 3) return RDKV_ERR_BAD_ARG;
+  if (max_k_quads < 0 || max_k_quads > kop_quads_bound(max_d_pad)) return RDKV_ERR_BAD_ARG;
   if (jobs == nullptr || n_jobs < 0 || H <= 0 || D <= 0 || max_slots < 0 || max_t_k < 0 || max_d_pad < 0)
     return RDKV_ERR_BAD_ARG;
   if (D > PACK_MAX_D || (D & 3)) return RDKV_ERR_BAD_SHAPE;
@@ -1009,6 +1302,29 @@ extern "C" int rdkv_pack_kv_batched(const rdkv_pack_job* jobs, int n_jobs, int H
   else pack_v_batched_kernel<<<gv, PACKV_WARPS * 32, 0, st>>>(jobs);
   int rc = launch_status();
   if (rc != RDKV_OK || max_t_k == 0 || max_d_pad == 0) return rc;
+  // K in one pass (the kept rows of a head held in the shared memory of a cluster) where they fit
+  const int quads = max_k_quads > 0 ? max_k_quads : kop_quads_bound(max_d_pad);
+  const size_t one_smem = kop_smem(max_t_k, max_d_pad, quads);
+  const bool one_fits = D == 128 && one_smem <= (size_t)KOP_MAX_SMEM;
+  if (k_passes == 1 && !one_fits) return RDKV_ERR_TOO_LARGE;
+  if (one_fits && k_passes != 3) {
+    cudaError_t e = cudaFuncSetAttribute(pack_k_onepass_batched_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)one_smem);
+    if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(KOP_CL, H, n_jobs);
+    cfg.blockDim = dim3(KOP_WARPS * 32);
+    cfg.dynamicSmemBytes = one_smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = KOP_CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, pack_k_onepass_batched_kernel, jobs, kop_rows_per_cta(max_t_k), quads);
+    if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
+    return launch_status();
+  }
   if (D == 128) pack_k_minmax128_batched_kernel<<<dim3(pack_k_slabs(max_t_k), H, n_jobs), 128, 0, st>>>(jobs);
   else pack_k_minmax_batched_kernel<<<dim3(pack_k_slabs(max_t_k), H, n_jobs), 128, 0, st>>>(jobs);
   rc = launch_status();

@@ -16,6 +16,7 @@ import ctypes as C
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 from torch import Tensor
 
@@ -461,8 +462,20 @@ def select_and_pack(K: Tensor, V: Tensor, layer_scores: Tensor, channel_scores: 
     return layer, new_v_only, int(layer.T_eff)
 
 
+_PACK_JOB_DTYPE = None
+
+
+def _pack_job_dtype():
+    """numpy record type with the layout of ``rdkv_pack_job`` (built once)."""
+    global _PACK_JOB_DTYPE
+    if _PACK_JOB_DTYPE is None:
+        _PACK_JOB_DTYPE = np.dtype(_lib.PackJob)
+    return _PACK_JOB_DTYPE
+
+
 def pack_kv_layers(Ks: Sequence[Tensor], Vs: Sequence[Tensor], v_bits: Tensor, k_bits: Tensor, gqa_factor: int, *,
-                   build_mask: bool = True, launch_events: Optional[list] = None) -> PackedLayerBatch:
+                   build_mask: bool = True, launch_events: Optional[list] = None,
+                   k_passes: int = 0) -> PackedLayerBatch:
     """:func:`pack_kv` for all layers of a cache at once (the reference packs a prefilled
     cache layer by layer: obkv_accel/packing.py:1323-1421, obkv_fast.py:1098-1166).
 
@@ -473,7 +486,9 @@ def pack_kv_layers(Ks: Sequence[Tensor], Vs: Sequence[Tensor], v_bits: Tensor, k
     Layers whose K bit maps lead to different padded channel widths cannot share tall
     tensors; they are then packed one by one.  ``launch_events``: a list that receives two
     (start, end) pairs of CUDA events per call, around the two partition launches and around
-    the packing launches (for measurements).
+    the packing launches (for measurements).  ``k_passes``: 1 = K packed in one pass over the kept
+    rows (held in the shared memory of a cluster of CTAs; raises if they do not fit), 3 = in three
+    (the rows are read twice), 0 = one pass where it fits; the bytes are the same.
     """
     import ctypes as C
     from ._lib import PackJob
@@ -552,33 +567,36 @@ def pack_kv_layers(Ks: Sequence[Tensor], Vs: Sequence[Tensor], v_bits: Tensor, k
             "sort_idx": span(SORT), "perm": span(PERM), "perm_q": span(PERMQ), "seg_bounds": span(SEG),
             "scratch": span(SCR)}
     to_p, tc_p, co_p, cc_p = tok_order.data_ptr(), tok_counts.data_ptr(), ch_order.data_ptr(), ch_counts.data_ptr()
-    mx_l, tv_l, tk_l = mx.tolist(), max_t_v.tolist(), t_k.tolist()
-    jobs = (PackJob * L)()
-    for i in range(L):
-        J = jobs[i]
-        K, V = Ks[i], Vs[i]
-        J.K, J.V = K.data_ptr(), V.data_ptr()
-        J.k_head_stride, J.k_row_stride, J.v_head_stride, J.v_row_stride = K.stride(1), K.stride(2), V.stride(1), V.stride(2)
-        J.tok_order, J.tok_counts = to_p + i * H * T * 4, tc_p + i * H * 16
-        J.ch_order, J.ch_counts = co_p + i * H * D * 4, cc_p + i * H * 16
-        J.tok_order_row_stride, J.ch_order_row_stride = T, D
-        J.D, J.gqa = D, gqa_factor
-        J.max_n2, J.max_n4, J.max_n8, J.max_n16 = mx_l[i]
-        J.max_t_v, J.t_k = tv_l[i], tk_l[i]
-        J.rows2, J.rows4, J.rows8, J.rows16, J.rows_meta, J.rows_k = R2, R4, R8, R16, max(RM, 1), RK
-        J.n_ch2_pad, J.n_ch4_pad, J.n_ch8, J.d_kept_max = N2P, N4P, N8P, DK
-        for name, (p0, step) in outs.items():
-            setattr(J, name, (p0 + i * step) if p0 else None)
-    jobs_dev = torch.frombuffer(bytearray(bytes(jobs)), dtype=torch.uint8).to(dev)
+    # the job table, column by column (a numpy record array with the layout of rdkv_pack_job)
+    jobs = np.zeros(L, dtype=_pack_job_dtype())
+    layer_idx = np.arange(L, dtype=np.int64)
+    jobs["K"], jobs["V"] = [k.data_ptr() for k in Ks], [v.data_ptr() for v in Vs]
+    jobs["k_head_stride"], jobs["k_row_stride"] = [k.stride(1) for k in Ks], [k.stride(2) for k in Ks]
+    jobs["v_head_stride"], jobs["v_row_stride"] = [v.stride(1) for v in Vs], [v.stride(2) for v in Vs]
+    jobs["tok_order"], jobs["tok_counts"] = to_p + layer_idx * (H * T * 4), tc_p + layer_idx * (H * 16)
+    jobs["ch_order"], jobs["ch_counts"] = co_p + layer_idx * (H * D * 4), cc_p + layer_idx * (H * 16)
+    jobs["tok_order_row_stride"], jobs["ch_order_row_stride"] = T, D
+    jobs["D"], jobs["gqa"] = D, gqa_factor
+    jobs["max_n2"], jobs["max_n4"], jobs["max_n8"], jobs["max_n16"] = mx[:, 0], mx[:, 1], mx[:, 2], mx[:, 3]
+    jobs["max_t_v"], jobs["t_k"] = max_t_v, t_k
+    jobs["rows2"], jobs["rows4"], jobs["rows8"], jobs["rows16"] = R2, R4, R8, R16
+    jobs["rows_meta"], jobs["rows_k"] = max(RM, 1), RK
+    jobs["n_ch2_pad"], jobs["n_ch4_pad"], jobs["n_ch8"], jobs["d_kept_max"] = N2P, N4P, N8P, DK
+    for name, (p0, step) in outs.items():
+        if p0:
+            jobs[name] = p0 + layer_idx * step
+    jobs_host = torch.from_numpy(jobs.view(np.uint8))
+    jobs_dev = jobs_host.to(dev)
     if launch_events is not None:
         ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
         ev[0].record()
     check(lib().rdkv_pack_kv_batched(jobs_dev.data_ptr(), L, H, D, int(mx.sum(axis=1).max()), RK, d_pad,
-                                     stream_ptr(dev)), "rdkv_pack_kv_batched")
+                                     int(k_passes), N2P // 4 + (N4P // 2 + 1) // 2 + (N8P + 3) // 4, stream_ptr(dev)),
+          "rdkv_pack_kv_batched")
     if launch_events is not None:
         ev[1].record()
         launch_events.append(ev)
-    keep = (jobs_dev, Ks, Vs, SCR)                                           # alive until the kernels have run
+    keep = (jobs_dev, jobs_host, Ks, Vs, SCR)                                # alive until the kernels have run
 
     def make(i: int) -> Tuple[PackedKVLayer, Optional[Tensor]]:
         _ = keep

@@ -183,14 +183,15 @@ def test_pack_kv_layers_equals_per_layer_packing():
         vbs.append(synth.make_v_bits(H, T, N, seed=seed, per_head_N=ragged))
         kbs.append(synth.make_k_bits(H, seed=seed))
     v_bits, k_bits = torch.stack(vbs).cuda(), torch.stack(kbs).cuda()
-    batch = pack_kv_layers(Ks, Vs, v_bits, k_bits, g)
-    assert len(batch) == 4
     singles = [pack_kv(Ks[i], Vs[i], v_bits[i], k_bits[i], g) for i in range(4)]
-    for i, ((pl, nv), (wl, wnv)) in enumerate(zip(batch, singles)):
-        assert_layer_equal(layer_to_np(pl), layer_to_np(wl), f"layer {i}.")
-        for f in ("K_ch_sort_idx", "K_ch_perm_padded_idx", "sort_idx"):
-            assert torch.equal(getattr(pl, f), getattr(wl, f)), f
-        assert (nv is None) == (wnv is None) and (nv is None or torch.equal(nv, wnv))
+    for k_passes in (0, 1, 3):                             # K in one pass over the kept rows (cluster) / in three
+        batch = pack_kv_layers(Ks, Vs, v_bits, k_bits, g, k_passes=k_passes)
+        assert len(batch) == 4
+        for i, ((pl, nv), (wl, wnv)) in enumerate(zip(batch, singles)):
+            assert_layer_equal(layer_to_np(pl), layer_to_np(wl), f"k_passes {k_passes} layer {i}.")
+            for f in ("K_ch_sort_idx", "K_ch_perm_padded_idx", "sort_idx"):
+                assert torch.equal(getattr(pl, f), getattr(wl, f)), f
+            assert (nv is None) == (wnv is None) and (nv is None or torch.equal(nv, wnv))
     # the fused kernel reads the (strided) views of the batch exactly as it reads single layers
     q = synth.make_q(H * g, seed=3, batch=4, dtype=torch.float16).cuda()
     got = packed_decode_attention(q, DecodeTable([b[0] for b in batch], [b[1] for b in batch], H * g))
@@ -256,11 +257,36 @@ def test_unaligned_strided_inputs():
         packed, nv = pack_kv(views[0], views[1], vbs[-1], kbs[-1], 2)
         assert_layer_equal(layer_to_np(packed), wants[-1][0], f"unaligned{layer}.")
         assert np.array_equal(to_np(nv), wants[-1][1])
-    batch = pack_kv_layers(Ks, Vs, torch.stack(vbs), torch.stack(kbs), 2)
+    for k_passes in (1, 3):
+        batch = pack_kv_layers(Ks, Vs, torch.stack(vbs), torch.stack(kbs), 2, k_passes=k_passes)
+        for layer in range(2):
+            packed, nv = batch[layer]
+            assert_layer_equal(layer_to_np(packed), wants[layer][0], f"unaligned.batched{layer}.{k_passes}.")
+            assert np.array_equal(to_np(nv), wants[layer][1])
+
+
+def test_one_pass_and_three_pass_k_packing_agree_at_full_size():
+    """Two config-1 layers (8 heads x 32768 tokens, budget 4096, ragged heads in the second): the
+    cluster kernel that reads the kept K rows once and the three-pass kernels write the same bytes;
+    rows that do not fit a cluster's shared memory are refused when one pass is demanded."""
+    from rdkv_b200 import synth
+    from rdkv_b200.packing import pack_kv_layers
+    H, T = 8, 32768
+    Ks, Vs, vbs, kbs = [], [], [], []
+    for layer, ragged in enumerate((None, [4096, 4000, 3000, 4096, 1, 4095, 2048, 777])):
+        seed = synth.unit_seed(1, layer)
+        K, V = synth.make_kv(H, T, seed=seed, device="cuda")
+        Ks.append(K); Vs.append(V)
+        vbs.append(synth.make_v_bits(H, T, 4096, seed=seed, device="cuda", per_head_N=ragged))
+        kbs.append(synth.make_k_bits(H, seed=seed, device="cuda"))
+    one = pack_kv_layers(Ks, Vs, torch.stack(vbs), torch.stack(kbs), 4, build_mask=False, k_passes=1)
+    three = pack_kv_layers(Ks, Vs, torch.stack(vbs), torch.stack(kbs), 4, build_mask=False, k_passes=3)
     for layer in range(2):
-        packed, nv = batch[layer]
-        assert_layer_equal(layer_to_np(packed), wants[layer][0], f"unaligned.batched{layer}.")
-        assert np.array_equal(to_np(nv), wants[layer][1])
+        assert_layer_equal(layer_to_np(one[layer][0]), layer_to_np(three[layer][0]), f"layer {layer}.")
+    big = synth.make_v_bits(H, T, 30000, seed=3, device="cuda")
+    with pytest.raises((RuntimeError, ValueError)):
+        pack_kv_layers(Ks[:1], Vs[:1], big[None], kbs[0][None], 4, build_mask=False, k_passes=1)
+    assert len(pack_kv_layers(Ks[:1], Vs[:1], big[None], kbs[0][None], 4, build_mask=False)) == 1   # falls back by itself
 
 
 def test_full_size_properties():
