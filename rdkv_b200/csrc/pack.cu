@@ -6,6 +6,8 @@
 // multiply-add, round-half-to-even (rintf), fp16 outputs rounded to nearest.
 #include <cooperative_groups.h>
 
+#include <type_traits>
+
 #include "rdkv_common.cuh"
 
 namespace rdkv {
@@ -960,7 +962,7 @@ __host__ __device__ inline size_t kop_smem(int t_k, int d_pad, int quads) {
   return (size_t)d_pad * 20 + 256 + 16 + (size_t)kop_rows_per_cta(t_k) * 8 * quads;
 }
 
-__global__ void __launch_bounds__(KOP_WARPS * 32)
+__global__ void __launch_bounds__(KOP_WARPS * 32, 3)
 pack_k_onepass_batched_kernel(const rdkv_pack_job* __restrict__ jobs, int rows_cap, int quads_cap) {
   namespace cg = cooperative_groups;
   extern __shared__ __align__(16) unsigned char kop_smem_raw[];
@@ -1019,37 +1021,53 @@ pack_k_onepass_batched_kernel(const rdkv_pack_job* __restrict__ jobs, int rows_c
   __half2 lo2[2] = {inf2, inf2}, hi2[2] = {ninf2, ninf2};
   bool pad = false;
   const uint16_t* Kh = A.K + h * A.k_head_stride + 4 * lane;
-  for (int s0 = r0 + warp * 16; s0 < r1; s0 += KOP_WARPS * 16) {
-    const int tok_l = (lane < 16 && s0 + lane < r1) ? stripe_token(m, s0 + lane) : -2;
-    pad = pad || __any_sync(0xffffffffu, tok_l == -1);
-    uint2 w[16];
+  // (shared-memory addresses as 32-bit offsets, the four parking places of this lane's channels as
+  //  byte offsets within a row: the inner loop is a handful of instructions per row)
+  const uint32_t rows32 = (uint32_t)__cvta_generic_to_shared(s_rows);
+  const uint32_t rstride_b = 2u * (uint32_t)row_h;
+  uint32_t off[4];
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const int tok = __shfl_sync(0xffffffffu, tok_l, k);
-      w[k] = make_uint2(0u, 0u);
-      if (tok >= 0) {
-        const uint16_t* src = Kh + (int64_t)tok * A.k_row_stride;
-        if (aligned) w[k] = *reinterpret_cast<const uint2*>(src);
-        else w[k] = make_uint2((uint32_t)src[0] | (uint32_t)src[1] << 16, (uint32_t)src[2] | (uint32_t)src[3] << 16);
+  for (int e = 0; e < 4; ++e) off[e] = 2u * (uint32_t)max(sl[e], 0);
+  const uint32_t kk0 = sl[0] >= 0, kk1 = sl[1] >= 0, kk2 = sl[2] >= 0, kk3 = sl[3] >= 0;
+  const int64_t k_rs = A.k_row_stride;                     // (in registers: the loop below must not re-read A)
+  auto gather = [&](auto AL) {
+    constexpr bool ALIGNED = decltype(AL)::value;
+    for (int s0 = r0 + warp * 16; s0 < r1; s0 += KOP_WARPS * 16) {
+      const int tok_l = (lane < 16 && s0 + lane < r1) ? stripe_token(m, s0 + lane) : -2;
+      pad = pad || __any_sync(0xffffffffu, tok_l == -1);
+      uint2 w[16];
+      int toks[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const int tok = __shfl_sync(0xffffffffu, tok_l, k);
+        toks[k] = tok;
+        w[k] = make_uint2(0u, 0u);
+        if (tok >= 0) {
+          const uint16_t* src = Kh + (int64_t)tok * k_rs;
+          if (ALIGNED) w[k] = *reinterpret_cast<const uint2*>(src);
+          else w[k] = make_uint2((uint32_t)src[0] | (uint32_t)src[1] << 16, (uint32_t)src[2] | (uint32_t)src[3] << 16);
+        }
       }
-    }
+      uint32_t rb = rows32 + (uint32_t)(s0 - r0) * rstride_b;
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const int tok = __shfl_sync(0xffffffffu, tok_l, k);
-      if (tok == -2) continue;                               // (warp-uniform) past the CTA's rows
-      if (tok >= 0) {
+      for (int k = 0; k < 16; ++k, rb += rstride_b) {
+        if (toks[k] < 0) continue;                           // (warp-uniform) no token: the row stays zeros
         const __half2 a = *reinterpret_cast<const __half2*>(&w[k].x), c = *reinterpret_cast<const __half2*>(&w[k].y);
         lo2[0] = __hmin2(lo2[0], a); hi2[0] = __hmax2(hi2[0], a);
         lo2[1] = __hmin2(lo2[1], c); hi2[1] = __hmax2(hi2[1], c);
+        // predicated stores (no branches: the lanes of a warp differ in which channels they keep)
+        asm volatile("{ .reg .pred p0, p1, p2, p3;\n"
+                     ".reg .b16 a0, a1, a2, a3;\n"
+                     "mov.b32 {a0, a1}, %4; mov.b32 {a2, a3}, %5;\n"
+                     "setp.ne.u32 p0, %6, 0; setp.ne.u32 p1, %7, 0; setp.ne.u32 p2, %8, 0; setp.ne.u32 p3, %9, 0;\n"
+                     "@p0 st.shared.u16 [%0], a0; @p1 st.shared.u16 [%1], a1;\n"
+                     "@p2 st.shared.u16 [%2], a2; @p3 st.shared.u16 [%3], a3; }"
+                     ::"r"(rb + off[0]), "r"(rb + off[1]), "r"(rb + off[2]), "r"(rb + off[3]), "r"(w[k].x), "r"(w[k].y),
+                       "r"(kk0), "r"(kk1), "r"(kk2), "r"(kk3));
       }
-      if (tok < 0) continue;                                 // a row without a token stays a row of zeros
-      uint16_t* row = s_rows + (size_t)(s0 + k - r0) * row_h;
-      if (sl[0] >= 0) row[sl[0]] = (uint16_t)(w[k].x & 0xFFFFu);
-      if (sl[1] >= 0) row[sl[1]] = (uint16_t)(w[k].x >> 16);
-      if (sl[2] >= 0) row[sl[2]] = (uint16_t)(w[k].y & 0xFFFFu);
-      if (sl[3] >= 0) row[sl[3]] = (uint16_t)(w[k].y >> 16);
     }
-  }
+  };
+  if (aligned) gather(std::true_type{}); else gather(std::false_type{});
   s_wlo[warp][2 * lane] = lo2[0]; s_wlo[warp][2 * lane + 1] = lo2[1];
   s_whi[warp][2 * lane] = hi2[0]; s_whi[warp][2 * lane + 1] = hi2[1];
   if (lane == 0) s_pad[warp] = pad ? 1 : 0;
