@@ -46,7 +46,7 @@ METRIC = "packed-KV decode-attn tokens/s"
 NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = 1.028
 # dram__bytes_read.sum + dram__bytes_write.sum of the packing launches of one config-1 step in the
 # committed ncu launch list (profiles/; a one-pass capture of the full workload)
-PACK_NCU_TRAFFIC_BYTES = 951.4e6
+PACK_NCU_TRAFFIC_BYTES = 664.9e6
 
 
 def load_peaks():
@@ -301,6 +301,7 @@ def measure_decode(cfg, rank, world, device, *, steps, warmup, seq_parts=1, chun
         with sampler:
             e2e_ms, e2e_timing = repeated_regions(e2e_step, steps, barrier, world, device, min_reps=5, target_ms=30.0)
         res["e2e_ms_region"], res["e2e_timing"] = e2e_ms, e2e_timing
+        res["e2e_ranges"] = len(tables[0]._host_io.ranges)
     for tb in tables:
         tb.check_status()
     return res
@@ -364,7 +365,8 @@ def run_decode(args, rank, world, device):
                     "h2d_bytes_per_step": m["q0"].numel() * m["q0"].element_size() * world,
                     "d2h_bytes_per_step": m["out"].numel() * m["out"].element_size() * world,
                     "ms_per_step": e2e_ms / args.steps, "reps": m["e2e_timing"]["reps"]},
-            "gpu_launches": args.steps * (m["timing"]["reps"] + 1) + args.steps * m["e2e_timing"]["reps"] * (2 if world == 1 else 1),
+            # (value pass + per-kernel event pass: one launch per step; host-buffer pass: one per view range)
+            "gpu_launches": args.steps * (m["timing"]["reps"] + 1) + args.steps * m["e2e_timing"]["reps"] * m["e2e_ranges"],
             "clocks": m["sampler"].summary(),
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -587,7 +589,7 @@ def run_pack(args, rank, world, device):
     state = {}
 
     def step(i):
-        state["batch"] = pack_kv_layers(Ks, Vs, v_bits, k_bits, 4, build_mask=False)
+        state["batch"] = pack_kv_layers(Ks, Vs, v_bits, k_bits, 4, build_mask=False, k_passes=args.k_passes)
 
     for i in range(args.warmup):
         step(i)
@@ -595,14 +597,14 @@ def run_pack(args, rank, world, device):
     with sampler:
         ms = timed_steps(step, args.steps, lambda: None)
     sec = ms / 1e3 / args.steps
-    # the three packing launches alone (device time of the dominant kernels), for the roofline
+    # the launches alone (device time of the two partition and the two packing kernels), for the roofline
     spans = []
     torch.cuda.profiler.start()
     for i in range(args.steps):
-        state["batch"] = pack_kv_layers(Ks, Vs, v_bits, k_bits, 4, build_mask=False, launch_events=spans)
+        state["batch"] = pack_kv_layers(Ks, Vs, v_bits, k_bits, 4, build_mask=False, k_passes=args.k_passes, launch_events=spans)
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
-    # per call two spans: the two partition launches, the four packing launches
+    # per call two spans: the two partition launches, the packing launches (V pass, one-pass K)
     kern_ms = sum(a.elapsed_time(b) for a, b in spans) / args.steps
     out_bytes = 0
     for pl, nv in state["batch"]:
@@ -624,9 +626,9 @@ def run_pack(args, rank, world, device):
             "roofline": {"bound": "hbm", "achieved": moved / (kern_ms / 1e3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": moved / (kern_ms / 1e3) / 1e9 / peak,
                          "traffic": PACK_NCU_TRAFFIC_BYTES, "peak_kind": kind,
-                         "kernel": "2 x partition_kernel + pack_v128_batched_kernel + pack_k_minmax128_batched_kernel + pack_k_params_batched_kernel + pack_k_quant_batched_kernel",
+                         "kernel": "2 x partition_kernel + pack_v128_batched_kernel + pack_k_onepass_batched_kernel",
                          "kernel_ms": kern_ms, "algorithmic_bytes_per_step": moved},
-            "gpu_launches": 6 * args.steps, "clocks": sampler.summary()}
+            "gpu_launches": 4 * 2 * args.steps, "clocks": sampler.summary()}
     if not args.no_cpu_baseline:
         from oracle import ref_packing as RP
         K, V, vb, kb = Ks[0].cpu().numpy(), Vs[0].cpu().numpy(), v_bits[0].cpu().numpy(), k_bits[0].cpu().numpy()
@@ -672,9 +674,9 @@ def run_score(args, rank, world, device):
                        "l2": "4 input sets of 201 MB rotated > L2"},
             "roofline": {"bound": "hbm", "achieved": moved / sec / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": moved / sec / 1e9 / peak, "traffic": None, "peak_kind": kind,
-                         "kernel": "token_score_kernel + channel_ksq_kernel + pool_kernel (whole step, 5 launches)",
+                         "kernel": "score_layer_kernel + pool_kernel (whole step, 2 launches)",
                          "algorithmic_bytes_per_step": moved},
-            "gpu_launches": 4 * args.steps, "clocks": sampler.summary()}
+            "gpu_launches": 2 * args.steps, "clocks": sampler.summary()}
 
 
 def run_alloc(args, rank, world, device):
@@ -853,6 +855,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling-sized runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--chunks", type=int, default=None, help="force this many chunks per (view, KV head) (default: planned)")
+    ap.add_argument("--k-passes", type=int, default=0, choices=[0, 1, 3],
+                    help="pack workload: K packed in one pass over the kept rows (1), in three (3), or as the library chooses (0)")
     ap.add_argument("--e2e-slices", type=int, default=None,
                     help="view ranges (streams) the host-buffer call overlaps its copies and kernels over")
     ap.add_argument("--e2e-graph", type=int, choices=(0, 1), default=None,
