@@ -203,7 +203,8 @@ int rdkv_sizeof_tail_args(void);           /* lets a binding check its struct la
  *     waits.  unit_counters: int32 [n_views][H_kv * ceil(g/8)], zero before the first launch; the
  *     kernel leaves them zero again.  Launches that share counters or partials must not overlap.
  *   - exactly one of out (normalised fp32 [n_views][H_q][128]) and out_record (un-normalised
- *     (m, l, -, -, o[128]) per (view, query head), input of rdkv_lse_combine across shards). */
+ *     (m, l, -, -, o[128]) per (view, query head), input of rdkv_lse_combine across shards);
+ *     out, out_record and partials 16-byte aligned (they are written four floats at a time). */
 int rdkv_decode_attn(const rdkv_layer_view* views, int n_views, const void* q, int q_dtype, int H_q,
                      int H_kv, int chunk_rows, int n_chunks, int n_whole_units, int row_begin, int row_end,
                      int seq_part, int seq_parts, int k_row_bytes_max, const void* unit_recs, const void* k_slots, int nkb_max,

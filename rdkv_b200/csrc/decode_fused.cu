@@ -1671,6 +1671,10 @@ static int launch_fused(const rdkv_layer_view* views, int n_views, const void* q
   if (n_whole < 0 || n_whole > units) return RDKV_ERR_BAD_ARG;
   const int64_t items = n_whole + (units - n_whole) * n_chunks;
   if (items > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
+  // results and records are written four floats at a time
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(partials) & 15) ||
+      (reinterpret_cast<uintptr_t>(merged) & 15))
+    return RDKV_ERR_BAD_ARG;
   const int stage_bytes = align16i(stage_capacity(k_row_bytes_max));
   size_t smem = (size_t)FSTAGES * stage_bytes + TAIL_BYTES + (MODE == MODE_ATTN_TAIL ? TAIL_EXTRA_BYTES : 0);
   const size_t epilogue = (size_t)FW * GH * D * sizeof(float);
@@ -1848,7 +1852,8 @@ extern "C" int rdkv_decode_attn_persistent(const rdkv_layer_view* views, int n_v
   if (n_chunks > 1 && (partials == nullptr || unit_counters == nullptr)) return RDKV_ERR_BAD_ARG;
   if (unit_recs == nullptr || k_slots == nullptr || nkb_max <= 0 || nkb_max > KB_MAX) return RDKV_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(unit_recs) & 15) || (reinterpret_cast<uintptr_t>(k_slots) & 15) ||
-      (reinterpret_cast<uintptr_t>(q) & 15))
+      (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+      (reinterpret_cast<uintptr_t>(partials) & 15) || (reinterpret_cast<uintptr_t>(out_record) & 15))
     return RDKV_ERR_BAD_ARG;
   const int rc = check_fused_args(views, n_views, q, q_dtype, H_q, H_kv, k_row_bytes_max);
   if (rc != RDKV_OK || n_views == 0) return rc;

@@ -198,7 +198,8 @@ class DecodeTable:
         st = int(self.status.item())
         if st:
             raise RuntimeError(f"rdkv_b200: fused decode kernel reported status {st} "
-                               "(1 = staging wait ran out, 2 = a view did not fit the launch)")
+                               "(bit 0 = a staging wait ran out, bit 1 = a view did not fit the launch, "
+                               "bit 2 = a tail buffer had no row left for the new token)")
 
 
 def lse_combine(partials: Tensor, out: Optional[Tensor] = None, *, out_ml: Optional[Tensor] = None,

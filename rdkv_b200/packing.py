@@ -706,15 +706,16 @@ def _pad_and_stack_per_head_layers(layers: List[PackedKVLayer], per_head_v16_V: 
     """Stack single-head layers (from ``build_packed_layer`` with deferred K) into the
     per-head stripe layout (reference: obkv_accel/packing.py:1019-1317).
 
-    V segments, scale/zp and fp16 values are zero-padded to the per-layer maxima;
-    K is quantised once over the zero-padded stripe canvas ``[1,H_kv,max_T_v +
-    max_n_v16,D]``, so pad rows take part in the per-channel range as they do in
-    the reference.
+    V segments, scale/zp and fp16 values are zero-padded to the per-layer maxima.
+    With ``k_bits_per_head`` K is quantised once over the zero-padded stripe canvas
+    ``[1,H_kv,max_T_v + max_n_v16,D]``, so pad rows take part in the per-channel range as
+    they do in the reference.  Without it (the reference's shared layout: one K bit map
+    for all heads, every inner layer carrying its own packed K) the inner layers' K
+    bytes are copied into the stripe, their scales and zero points stacked, and the
+    channel tables of the first non-empty head serve all heads.
     """
     H = len(layers)
     assert H_q == H * gqa_factor, f"H_q={H_q}, H_kv={H}, gqa={gqa_factor}"
-    if k_bits_per_head is None:
-        raise ValueError("rdkv_b200 stacks per-head layers only in per-head K mode (k_bits_per_head required)")
     D = head_dim
     t_v_h = [int(pl.T_eff) for pl in layers]
     n16_h = [int(pl.n_v16) for pl in layers]
@@ -742,6 +743,53 @@ def _pad_and_stack_per_head_layers(layers: List[PackedKVLayer], per_head_v16_V: 
         if t_v_h[h]:
             v_scale[0, h, :t_v_h[h]] = pl.V_scale[0, 0]
             v_zp[0, h, :t_v_h[h]] = pl.V_zp[0, 0]
+        if n16_h[h]:
+            new_v_only[0, h, :n16_h[h]] = per_head_v16_V[h][0, 0]
+    if t_k == 0:
+        raise RuntimeError("every head kept zero tokens")
+    ref_pl = next((pl for pl in layers if pl.T_eff_k > 0 or pl.T_eff > 0), layers[0])
+    i32 = dict(dtype=torch.int32, device=device)
+    t_v_t, n16_t = torch.tensor(t_v_h, **i32), torch.tensor(n16_h, **i32)
+    if k_bits_per_head is None:
+        # shared layout: copy every head's packed K rows ([compressed; fp16-V rows]) into the stripe
+        n2c, n4c, n8c = (int(x) for x in ref_pl.K_ch_seg_bounds)
+        d_pad = _pad_to(n2c, 4) + _pad_to(n4c, 2) + n8c
+
+        def stack_k(field: str, width: int):
+            if width == 0:
+                return None
+            out = torch.zeros((1, H, t_k, width), **u8)
+            for h, pl in enumerate(layers):
+                cur = getattr(pl, field)
+                if cur is None:
+                    continue
+                if t_v_h[h]:
+                    out[0, h, :t_v_h[h]] = cur[0, 0, :t_v_h[h]]
+                if n16_h[h]:
+                    out[0, h, max_t_v:max_t_v + n16_h[h]] = cur[0, 0, t_v_h[h]:t_v_h[h] + n16_h[h]]
+            return out
+
+        def stack_ch(field: str):
+            parts = []
+            for pl in layers:
+                t = getattr(pl, field)
+                parts.append(t if t.shape[3] == d_pad else torch.zeros((1, 1, 1, d_pad), dtype=torch.float16, device=device))
+            return torch.cat(parts, dim=1).contiguous()
+
+        packed = PackedKVLayer(
+            K_2bit=stack_k("K_2bit", _pad_to(n2c, 4) // 4), K_4bit=stack_k("K_4bit", _pad_to(n4c, 2) // 2),
+            K_8bit=stack_k("K_8bit", n8c), K_ch_scale=stack_ch("K_ch_scale"), K_ch_zp=stack_ch("K_ch_zp"),
+            K_ch_sort_idx=ref_pl.K_ch_sort_idx, K_ch_seg_bounds=ref_pl.K_ch_seg_bounds,
+            K_ch_perm_padded_idx=ref_pl.K_ch_perm_padded_idx,
+            V_2bit=v2, V_4bit=v4, V_8bit=v8, V_scale=v_scale, V_zp=v_zp, sort_idx=ref_pl.sort_idx,
+            seg_bounds=mx, T_eff=max_t_v, seg_bounds_per_head=torch.tensor(seg_h, **i32).view(H, 3),
+            T_eff_per_head=t_v_t, softmax_mask=_softmax_mask(t_v_t, n16_t, max_t_v, t_k, gqa_factor),
+            T_eff_k=t_k, n_v16=max_n16, T_eff_k_per_head=t_v_t + n16_t, n_v16_per_head=n16_t,
+            allocation_v_bits=(v_bits_per_head.to(device=device, dtype=torch.int16)
+                               if retain_allocation_metadata and v_bits_per_head is not None else None),
+        )
+        return packed, new_v_only
+    for h, pl in enumerate(layers):
         if t_v_h[h] + n16_h[h] == 0:
             continue
         rows = pl.deferred_k_for_stack
@@ -750,14 +798,8 @@ def _pad_and_stack_per_head_layers(layers: List[PackedKVLayer], per_head_v16_V: 
         canvas[0, h, :t_v_h[h]] = rows[0, 0, :t_v_h[h]]
         if n16_h[h]:
             canvas[0, h, max_t_v:max_t_v + n16_h[h]] = rows[0, 0, t_v_h[h]:]
-            new_v_only[0, h, :n16_h[h]] = per_head_v16_V[h][0, 0]
-    if t_k == 0:
-        raise RuntimeError("every head kept zero tokens")
     k2, k4, k8, k_scale, k_zp, sort_ph, perm_ph, seg_ch, ch_mx = pack_k_mixed_per_head(
         canvas, k_bits_per_head.to(device))
-    ref_pl = next((pl for pl in layers if pl.T_eff_k > 0 or pl.T_eff > 0), layers[0])
-    i32 = dict(dtype=torch.int32, device=device)
-    t_v_t, n16_t = torch.tensor(t_v_h, **i32), torch.tensor(n16_h, **i32)
     packed = PackedKVLayer(
         K_2bit=k2, K_4bit=k4, K_8bit=k8, K_ch_scale=k_scale, K_ch_zp=k_zp, K_ch_sort_idx=sort_ph[0],
         K_ch_seg_bounds=ch_mx, K_ch_perm_padded_idx=perm_ph[0],

@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own
 Python code (PyTorch CPU kernels) on seeded inputs.
 
-    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack] [select] [blockwise] [rope]
+    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack] [select] [blockwise] [rope] [legacy]
     (or RDKV_REFERENCE=/path/to/reference/checkout in the environment; no part named = all)
 
 The reference checkout is only needed to (re)generate the files; the tests read
@@ -78,6 +78,44 @@ def ref_pack_kv(K, V, v_bits, k_bits, g):
     return P._pad_and_stack_per_head_layers(
         layers, v16s, H_q=H_kv * g, gqa_factor=g, head_dim=D, device=K.device, dtype=K.dtype,
         k_bits_per_head=k_bits)
+
+
+def ref_pack_kv_legacy(K, V, v_bits, k_bits_shared, g):
+    """The shared-layout form of the same composite: one K bit map [D] for all heads, every head's K
+    quantised on its own rows by build_packed_layer, the packed bytes copied into the stripe
+    (packing.py:1019-1317 with k_bits_per_head=None)."""
+    H_kv, D = K.shape[1], K.shape[3]
+    layers, v16s = [], []
+    for h in range(H_kv):
+        kept = (v_bits[h] > 0).nonzero(as_tuple=True)[0]
+        kb = v_bits[h][kept]
+        counts = tuple(int((kb == b).sum()) for b in (2, 4, 8))
+        layer, _, v16 = P.build_packed_layer(
+            K[:, h:h + 1].index_select(2, kept).contiguous(),
+            V[:, h:h + 1].index_select(2, kept).contiguous(),
+            kb, k_bits_shared, v_segment_counts=counts)
+        layers.append(layer)
+        v16s.append(v16)
+    return P._pad_and_stack_per_head_layers(
+        layers, v16s, H_q=H_kv * g, gqa_factor=g, head_dim=D, device=K.device, dtype=K.dtype)
+
+
+def make_legacy():
+    """Shared-layout stacking on a ragged layer: the stacked layer's fields, the fp16 rows and the
+    dequantise-then-attend output."""
+    H_kv, g, T, N = 4, 2, 256, 96
+    seed = synth.unit_seed(21, 0)
+    K, V = synth.make_kv(H_kv, T, seed=seed)
+    v_bits = synth.make_v_bits(H_kv, T, N, seed=seed, per_head_N=[96, 64, 17, 80])
+    k_bits = synth.make_k_bits(1, seed=seed)[0]
+    pl, nv = ref_pack_kv_legacy(K, V, v_bits, k_bits, g)
+    q = synth.make_q(H_kv * g, seed=seed)
+    out = {"K": npy(K), "V": npy(V), "v_bits": npy(v_bits), "k_bits": npy(k_bits), "q": npy(q), "new_v_only": npy(nv)}
+    out.update(layer_to_dict(pl))
+    attn, K_hat, V_hat = ref_attend(q, pl, nv, 128)
+    out.update(attn_out=npy(attn), K_hat=npy(K_hat), V_hat=npy(V_hat))
+    np.savez_compressed(os.path.join(HERE, "legacy.npz"), **out)
+    print("legacy.npz", os.path.getsize(os.path.join(HERE, "legacy.npz")), "bytes")
 
 
 def ref_attend(q, pl, new_v_only, D, tail_k=None, tail_v=None):
@@ -404,7 +442,9 @@ def make_rope():
 
 
 if __name__ == "__main__":
-    parts = sys.argv[2:] or ["layers", "scoring", "unpack", "select", "blockwise", "rope"]
+    parts = sys.argv[2:] or ["layers", "scoring", "unpack", "select", "blockwise", "rope", "legacy"]
+    if "legacy" in parts:
+        make_legacy()
     if "rope" in parts:
         make_rope()
     if "blockwise" in parts:

@@ -65,6 +65,42 @@ def test_reference_unit_case_deferred_k_stack(golden_unit):
     assert np.array_equal(to_np(packed2.K_ch_perm_padded_idx), g["K_ch_perm_padded_idx"])
 
 
+def test_shared_layout_stacking_matches_reference_vectors():
+    """The reference's shared layout (one K bit map for all heads, every head's K quantised on its own
+    rows, packed bytes copied into the stripe: packing.py:1019-1317 without k_bits_per_head): layer
+    fields bit for bit, and the fused kernel, the two-stage operators and the decompressor on such a
+    layer against the reference's dequantise-then-attend output."""
+    from conftest import load_golden
+    from helpers import assert_attn_close
+    from rdkv_b200.decode import packed_layer_attention
+    from rdkv_b200.decompress import unpack_trizone_to_past_kv
+    from rdkv_b200.packing import TriZoneCache, _pad_and_stack_per_head_layers, build_packed_layer
+    g = load_golden("legacy.npz")
+    K, V, v_bits, k_bits = cuda(g["K"]), cuda(g["V"]), cuda(g["v_bits"]), cuda(g["k_bits"])
+    H = K.shape[1]
+    layers, v16s = [], []
+    for h in range(H):
+        kept = (v_bits[h] > 0).nonzero(as_tuple=True)[0]
+        kb = v_bits[h].index_select(0, kept)
+        counts = tuple(int((kb == b).sum()) for b in (2, 4, 8))
+        layer, _, v16 = build_packed_layer(K[:, h:h + 1].index_select(2, kept), V[:, h:h + 1].index_select(2, kept),
+                                           kb, k_bits, v_segment_counts=counts)
+        layers.append(layer)
+        v16s.append(v16)
+    packed, nv = _pad_and_stack_per_head_layers(layers, v16s, H_q=2 * H, gqa_factor=2, head_dim=128,
+                                                device=K.device, dtype=K.dtype)
+    assert_layer_equal(layer_to_np(packed), g, "shared.")
+    assert np.array_equal(to_np(nv), g["new_v_only"])
+    assert packed.K_ch_perm_padded_idx_for_Q is None and packed.K_ch_sort_idx_per_head is None
+    for name in ("K_ch_sort_idx", "K_ch_perm_padded_idx", "sort_idx"):
+        assert np.array_equal(to_np(getattr(packed, name)), g[name]), name
+    out = packed_layer_attention(cuda(g["q"]), packed, nv, use_mask=True)
+    assert_attn_close(to_np(out), g["attn_out"], "shared layout, fused kernel")
+    cache = TriZoneCache(packed=(packed,), new_v_only=[nv], new_both_k=[None], new_both_v=[None], original_seq_len=0)
+    (K_hat, V_hat), = unpack_trizone_to_past_kv(cache, head_dim=128)
+    assert np.array_equal(to_np(K_hat), g["K_hat"]) and np.array_equal(to_np(V_hat), g["V_hat"])
+
+
 @pytest.mark.parametrize("tag", ["even", "ragged", "gqa8"])
 def test_pack_kv_matches_golden(golden_layers, tag):
     g = sub(golden_layers, tag)
