@@ -107,15 +107,18 @@ class DecodeTable:
     CTAS_PER_SM = 3                      # resident CTAs of the fused kernel per SM
     WORK_CTR_SLOTS = 64                  # launches of one table that may overlap (view ranges on streams of their own)
     # The persistent form (one resident CTA per slot draws items from a counter) is used for launches
-    # of whole units that fill the CTA slots at least this many times over; measured on B200 it is
-    # about 2 % faster there and slower than one CTA per item when whole units and chunks are mixed.
-    PERSISTENT_MIN_ROUNDS = 4
+    # of whole units that fill the CTA slots at least this many times over.  Measured on B200
+    # (2048-row units): 2 % faster at 9 rounds, 3 % faster at 2.3 rounds than two rounds of whole units
+    # plus the leftover units in chunks (a chunk costs 5 - 8 us of prologue, merge and record
+    # traffic on top of its rows); no better than one CTA per item where whole units and chunks mix.
+    PERSISTENT_MIN_ROUNDS = 2
     # cost model of a launch (SM cycles, measured on B200): a CTA spends ROW_COST per live row it
     # attends over plus a fixed cost (prologue, first tile, merge of its warps, result): FIXED_WHOLE
     # when it has a whole unit, FIXED_CHUNK when it has a chunk (record + arrival counter on top)
     ROW_COST = 17.6
     FIXED_WHOLE = 13000.0
     FIXED_CHUNK = 17000.0
+    MERGE_PER_CHUNK = 1500.0             # per chunk of a unit: its record read back by the unit's last CTA, contention on the counter
 
     def refresh(self) -> None:
         """Rebuild the table's snapshot of the per-head quantities (one small launch on the current
@@ -154,8 +157,8 @@ class DecodeTable:
         k_max = max(1, min(16, rows // 128))
         whole = rows * self.ROW_COST + self.FIXED_WHOLE
 
-        def chunk_cost(k):
-            return self._chunk_rows_for(k, rows) * self.ROW_COST + self.FIXED_CHUNK
+        def chunk_cost(k):                                  # (the unit's last CTA also reads all k records)
+            return self._chunk_rows_for(k, rows) * self.ROW_COST + self.FIXED_CHUNK + k * self.MERGE_PER_CHUNK
 
         best = (-(-units // slots) * whole, 1, units)                       # all whole
         full, left = divmod(units, slots)
