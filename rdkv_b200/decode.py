@@ -117,7 +117,7 @@ class DecodeTable:
     # when it has a whole unit, FIXED_CHUNK when it has a chunk (record + arrival counter on top)
     ROW_COST = 17.6
     FIXED_WHOLE = 13000.0
-    FIXED_CHUNK = 17000.0
+    FIXED_CHUNK = 11000.0
     MERGE_PER_CHUNK = 1500.0             # per chunk of a unit: its record read back by the unit's last CTA, contention on the counter
 
     def refresh(self) -> None:
