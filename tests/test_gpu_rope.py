@@ -44,7 +44,7 @@ def test_fused_rope_is_bit_exact(tag, cs):
         fused_rope(q[:, :64], k, cos, sin)
 
 
-def _case(kv_dtype, n_views, tails, cap, seed):
+def _case(kv_dtype, n_views, tails, cap, seed, H_kv=4, g=4):
     """Packed layers, tail buffers, the new token's rows and rotation tables for n_views views, and
     per view the oracle's result of the whole block."""
     from oracle import ref_attention as RA
@@ -52,7 +52,6 @@ def _case(kv_dtype, n_views, tails, cap, seed):
     from oracle import ref_rope as RR
     from rdkv_b200 import synth
     from rdkv_b200.packing import pack_kv
-    H_kv, g = 4, 4
     tag = "bf16" if kv_dtype == torch.bfloat16 else "f16"
     gen = torch.Generator().manual_seed(seed)
     q = synth.make_q(H_kv * g, seed=seed, batch=n_views, dtype=kv_dtype)
@@ -104,6 +103,23 @@ def test_one_launch_block_with_rotation_new_token_and_tail(kv_dtype):
             assert torch.equal(new_v[i, :, tails[i]].cpu(), c["v_cur"][i])
             assert torch.equal(new_k[i, :, :tails[i]].cpu(), c["new_k"][i, :, :tails[i]])
         table.check_status()
+
+
+def test_one_launch_block_with_more_query_heads_than_a_cta_takes():
+    """16 query heads per KV head: two CTAs per (view, KV head), each with eight of the heads; both
+    seed their softmax with the new token, one of them appends its rows."""
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention
+    tails, cap = [70, 5], 80
+    c = _case(torch.float16, 2, tails, cap, seed=13, H_kv=2, g=16)
+    new_k, new_v = c["new_k"].cuda(), c["new_v"].cuda()
+    table = DecodeTable(c["layers"], c["nvs"], c["H_q"])
+    out = packed_decode_attention(c["q"].cuda(), table, new_k=new_k, new_v=new_v,
+                                  n_new=torch.tensor(tails, dtype=torch.int32, device="cuda"), k_cur=c["k_cur"].cuda(),
+                                  v_cur=c["v_cur"].cuda(), rope=(c["cos"].cuda(), c["sin"].cuda()))
+    for i, w in enumerate(c["wants"]):
+        assert_attn_close(to_np(out[i]), w, f"g=16 view {i}")
+        assert np.array_equal(_bits(new_k[i, :, tails[i]]), c["k_rot"][i].view(np.uint16))
+    table.check_status()
 
 
 def test_one_launch_block_equals_the_separate_steps():
