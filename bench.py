@@ -645,7 +645,7 @@ def run_score(args, rank, world, device):
     observation window over 32768 tokens, fp16) followed by the default pooling (avg, 5, reflect)."""
     if rank != 0:
         return None
-    from rdkv_b200.scoring import _score_one_layer, apply_score_pooling
+    from rdkv_b200.scoring import _score_one_layer, apply_score_pooling, obs_window_scores
     B, H, g, W, T, D = 1, 8, 4, 32, 32768, 128
     gen = torch.Generator(device=device)
     gen.manual_seed(77)
@@ -667,6 +667,30 @@ def run_score(args, rank, world, device):
     sec = ms / 1e3 / args.steps
     moved = aws[0].numel() * 2 + ks[0].numel() * 2 + qs[0].numel() * 2 + H * T * 4 * 3
     peak, kind = load_peaks()
+    # the same scores straight from the window's queries and the keys (no attention weights in memory),
+    # and what producing the weights first costs (matmul, mask, softmax by torch; then the scoring kernel)
+    q_obs = [q.view(B, H * g, W, D) for q in qs]
+    mask = torch.arange(T, device=device)[None, :] > torch.arange(T - W, T, device=device)[:, None]
+
+    def fused(i):
+        tok, ch = obs_window_scores(q_obs[i % n_rep], ks[i % n_rep])
+        apply_score_pooling(tok[0], "avg", 5, "reflect")
+
+    def two_step(i):
+        j = i % n_rep
+        aw = torch.matmul(q_obs[j], ks[j].repeat_interleave(g, dim=1).transpose(-1, -2)) * (1.0 / D ** 0.5)
+        aw = aw.masked_fill_(mask[None, None], float("-inf")).softmax(dim=-1)
+        tok, ch = _score_one_layer(aw.view(B, H, g, W, T), qs[j], None, ks[j], D, k=ks[j])
+        apply_score_pooling(tok[0], "avg", 5, "reflect")
+
+    extra = {}
+    for name, fn in (("from_queries_and_keys", fused), ("weights_by_torch_then_scoring", two_step)):
+        for i in range(args.warmup):
+            fn(i)
+        with sampler:
+            t_ms = timed_steps(fn, args.steps, lambda: None) / args.steps
+        nbytes = ks[0].numel() * 2 + q_obs[0].numel() * 2 + H * T * 4 * 3
+        extra[name] = {"ms_per_step": t_ms, "algorithmic_bytes": nbytes, "frac_of_hbm_peak": nbytes / (t_ms / 1e3) / 1e9 / peak}
     return {"metric": "importance scoring + pooling, layers/s", "value": 1.0 / sec, "unit": "layers/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp16 in, fp32 accumulate", "data": "synthetic",
@@ -676,7 +700,8 @@ def run_score(args, rank, world, device):
                          "frac": moved / sec / 1e9 / peak, "traffic": None, "peak_kind": kind,
                          "kernel": "score_layer_kernel + pool_kernel (whole step, 2 launches)",
                          "algorithmic_bytes_per_step": moved},
-            "gpu_launches": 2 * args.steps, "clocks": sampler.summary()}
+            "obs_window": extra,
+            "gpu_launches": (2 + 4 + 2) * args.steps, "clocks": sampler.summary()}
 
 
 def run_alloc(args, rank, world, device):

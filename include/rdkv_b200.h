@@ -375,6 +375,18 @@ int rdkv_tail_attn_partial(const void* q, int q_dtype, int64_t n_views, int H_q,
  * scores; pool_max 0 = average, 1 = maximum; reflect 0 = zero padding with
  * kernel_size taps, 1 = reflection padding with min(kernel_size, 2*len-1) taps;
  * out_len must be len + 2*(taps/2) - taps + 1. */
+/* rdkv_obs_scores: the same two scores straight from the observation window's queries and the
+ * layer's keys, without the attention weights ever reaching memory.  Replaces the scoring step
+ * of the prefill (obkv_fast.py:1443-1450: matmul in the model's 16-bit type, scaling, causal mask
+ * of the window, softmax) together with _score_one_layer (:854-896).  q_obs: [BH*g] query heads of
+ * W window positions x 128 (q_head_stride, q_row_stride in elements; KV head bh owns query heads
+ * bh*g .. bh*g+g-1), k: [BH][T][128]; dtype RDKV_F16 or RDKV_BF16 for both; causal: window position
+ * w sees keys <= T-W+w.  g*W <= 256.  scratch: rdkv_obs_scratch_words(BH, g, W, T) 4-byte words.
+ * Three launches (tile statistics, reduction, token sums); the keys are read twice. */
+int64_t rdkv_obs_scratch_words(int BH, int g, int W, int T);
+int rdkv_obs_scores(const void* q_obs, const void* k, int dtype, int64_t q_head_stride, int64_t q_row_stride,
+                    int64_t k_head_stride, int64_t k_row_stride, int BH, int g, int W, int T, int causal,
+                    float* scratch, float* layer_token, float* layer_channel, void* stream);
 int rdkv_score_chunks(int T);
 int64_t rdkv_score_scratch_words(int BH, int T, int D);
 int rdkv_score_layer(const void* aw, int aw_dtype, const void* q, int q_dtype, const void* k, int k_dtype,

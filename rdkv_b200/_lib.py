@@ -110,6 +110,8 @@ _PROTOTYPES = {
     "rdkv_pack_k_slabs": ([_i], _i),
     "rdkv_pack_k": ([_p, _i64, _i64, _i, _i, _p, _i64, _p, _i64, _i, _i, _p, _i64, _p, _i64,
                      _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p], _i),
+    "rdkv_obs_scratch_words": ([_i, _i, _i, _i], _i64),
+    "rdkv_obs_scores": ([_p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _p, _p, _p, _p], _i),
     "rdkv_score_chunks": ([_i], _i),
     "rdkv_score_scratch_words": ([_i, _i, _i], _i64),
     "rdkv_score_layer": ([_p, _i, _p, _i, _p, _i, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p], _i),

@@ -40,6 +40,49 @@ def _score_one_layer(aw: Tensor, q: Tensor, o, v: Tensor, head_dim: int, v_score
     return token, channel
 
 
+def obs_window_scores(q_obs: Tensor, k: Tensor, *, causal: bool = True, normalise: bool = False):
+    """Token and channel scores of a prefilled layer from the observation window's queries and the
+    layer's keys in one step: what the reference computes with a matmul, a masked softmax and
+    ``_score_one_layer`` (obkv_fast.py:1443-1466), without materialising the ``[H_q,W,T]`` weights.
+
+    q_obs [B,H_q,W,128] (the last W query positions, after RoPE), k [B,H_kv,T,128], both fp16 or both
+    bf16 -> (layer_token [B,H_kv,T], layer_channel [B,H_kv,128]) fp32, as ``_score_one_layer`` returns
+    them.  ``causal``: window position w sees keys up to T-W+w (the reference's ``obs_mask``).
+    ``normalise``: divide the token scores by the number of window positions that can see each key
+    (the reference's ``correct_norm``, obkv_fast.py:1342-1344, 1461)."""
+    require_cuda(q_obs, "q_obs"); require_cuda(k, "k")
+    if q_obs.dim() != 4 or k.dim() != 4 or q_obs.shape[-1] != 128 or k.shape[-1] != 128:
+        raise ValueError("q_obs must be [B,H_q,W,128] and k [B,H_kv,T,128]")
+    if q_obs.dtype != k.dtype or q_obs.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("q_obs and k must both be fp16 or both bf16")
+    B, H_q, W, D = q_obs.shape
+    H, T = int(k.shape[1]), int(k.shape[2])
+    if k.shape[0] != B or H_q % H != 0:
+        raise ValueError(f"k must be [{B},H_kv,T,128] with H_kv dividing {H_q}")
+    g = H_q // H
+    if g * W > 256:
+        raise ValueError(f"g*W = {g * W} rows per KV head: at most 256")
+    if causal and W > T:
+        raise ValueError("the observation window is longer than the sequence")
+    if q_obs.stride(3) != 1 or q_obs.stride(0) != H_q * q_obs.stride(1):
+        q_obs = q_obs.contiguous()
+    if k.stride(3) != 1 or k.stride(0) != H * k.stride(1):
+        k = k.contiguous()
+    dev = q_obs.device
+    token = torch.empty((B, H, T), dtype=torch.float32, device=dev)
+    channel = torch.empty((B, H, D), dtype=torch.float32, device=dev)
+    scratch = torch.empty(lib().rdkv_obs_scratch_words(B * H, g, W, T), dtype=torch.float32, device=dev)
+    check(lib().rdkv_obs_scores(ptr(q_obs), ptr(k), q_dtype_tag(q_obs), q_obs.stride(1), q_obs.stride(2), k.stride(1),
+                                k.stride(2), B * H, g, W, T, 1 if causal else 0, ptr(scratch), ptr(token), ptr(channel),
+                                stream_ptr(dev)), "rdkv_obs_scores")
+    if normalise:
+        norm = torch.full((T,), float(W), dtype=torch.float32, device=dev)
+        if causal:
+            norm[T - W:] = torch.arange(W, 0, -1, dtype=torch.float32, device=dev)
+        token = token / norm
+    return token, channel
+
+
 def apply_score_pooling(scores: Tensor, pool_type: str, kernel_size: int, padding_mode: str = "zero") -> Tensor:
     """Sliding-window average (``pool_type == "avg"``) or maximum of a score row / of the rows of a
     2-D score tensor; ``padding_mode`` "zero" or "reflect" (the window shrinks to ``2*len-1`` taps

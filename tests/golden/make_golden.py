@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own
 Python code (PyTorch CPU kernels) on seeded inputs.
 
-    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack] [select] [blockwise] [rope] [legacy]
+    python tests/golden/make_golden.py /path/to/reference/checkout [layers] [scoring] [unpack] [select] [blockwise] [rope] [legacy] [obs]
     (or RDKV_REFERENCE=/path/to/reference/checkout in the environment; no part named = all)
 
 The reference checkout is only needed to (re)generate the files; the tests read
@@ -420,6 +420,33 @@ def make_blockwise():
     print("blockwise.npz", os.path.getsize(os.path.join(HERE, "blockwise.npz")), "bytes")
 
 
+def make_obs():
+    """Token and channel scores of a layer from the observation window's queries and the keys: the
+    reference's inline scoring step (obkv_fast.py:1443-1450: 16-bit matmul, scaling, causal mask of
+    the window, softmax) followed by its _score_one_layer (:854-896), on seeded tensors."""
+    import math
+    import obkv_fast as ref_fast
+    gen = torch.Generator().manual_seed(4321)
+    out = {}
+    bits = lambda t: t.view(torch.int16).numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.numpy()
+    for tag, dt, (B, H, g, W, T) in (("f16", torch.float16, (1, 2, 4, 8, 300)), ("bf16", torch.bfloat16, (1, 2, 4, 8, 300)),
+                                     ("f16w32", torch.float16, (2, 1, 4, 32, 1000))):
+        D = 128
+        q_obs = torch.randn(B, H * g, W, D, generator=gen).to(dt)
+        k = (torch.randn(B, H, T, D, generator=gen) * 0.7).to(dt)
+        k_exp = k.repeat_interleave(g, dim=1)
+        query_positions = torch.arange(T - W, T)
+        obs_mask = torch.arange(T).unsqueeze(0) > query_positions.unsqueeze(1)
+        aw = torch.matmul(q_obs, k_exp.transpose(-1, -2)) * (1.0 / math.sqrt(D))
+        aw.masked_fill_(obs_mask.unsqueeze(0).unsqueeze(0), float("-inf"))
+        aw = aw.softmax(dim=-1)
+        tok, ch = ref_fast._score_one_layer(aw.view(B, H, g, W, T), q_obs.view(B, H, g, W, D), None, k, D, k=k)
+        out.update({f"{tag}_q": bits(q_obs), f"{tag}_k": bits(k), f"{tag}_token": tok.numpy(), f"{tag}_channel": ch.numpy(),
+                    f"{tag}_shape": np.asarray([B, H, g, W, T], dtype=np.int64)})
+    np.savez_compressed(os.path.join(HERE, "obs.npz"), **out)
+    print("obs.npz", os.path.getsize(os.path.join(HERE, "obs.npz")), "bytes")
+
+
 def make_rope():
     """fused_rope_ref (obkv_accel/triton_rope.py:141-165) on seeded rows: fp16 and bf16 rows (bf16
     stored as its 16-bit patterns), tables of the rows' type and fp32 tables."""
@@ -442,7 +469,9 @@ def make_rope():
 
 
 if __name__ == "__main__":
-    parts = sys.argv[2:] or ["layers", "scoring", "unpack", "select", "blockwise", "rope", "legacy"]
+    parts = sys.argv[2:] or ["layers", "scoring", "unpack", "select", "blockwise", "rope", "legacy", "obs"]
+    if "obs" in parts:
+        make_obs()
     if "legacy" in parts:
         make_legacy()
     if "rope" in parts:

@@ -48,6 +48,51 @@ def test_score_one_layer_on_odd_shapes_matches_torch():
         assert torch.equal(tok, _score_one_layer(aw, q, None, k, D, k=k)[0])   # fixed summation order
 
 
+@pytest.mark.parametrize("tag", ["f16", "bf16", "f16w32"])
+def test_obs_window_scores_match_reference_vectors(tag):
+    """Scores straight from the window's queries and the keys (no attention weights in memory) against
+    vectors from the reference's scoring step (obkv_fast.py:1443-1450) and its _score_one_layer."""
+    from rdkv_b200.scoring import obs_window_scores
+    g = load_golden("obs.npz")
+    B, H, gq, W, T = (int(x) for x in g[f"{tag}_shape"])
+    dt = torch.bfloat16 if tag == "bf16" else torch.float16
+    as_t = lambda a: (torch.from_numpy(np.ascontiguousarray(a)).view(torch.int16).view(torch.bfloat16)
+                      if tag == "bf16" else torch.from_numpy(np.ascontiguousarray(a))).cuda()
+    q, k = as_t(g[f"{tag}_q"]), as_t(g[f"{tag}_k"])
+    assert q.dtype == dt
+    tok, ch = obs_window_scores(q, k)
+    # (the weights are rounded to 16 bits before they are summed, in another order than the reference's)
+    np.testing.assert_allclose(to_np(tok), g[f"{tag}_token"], rtol=1.5e-2 if tag == "bf16" else 4e-3, atol=2e-5)
+    np.testing.assert_allclose(to_np(ch), g[f"{tag}_channel"], rtol=1e-5)
+    assert torch.equal(tok, obs_window_scores(q, k)[0])    # fixed summation order
+    # a strided K (a slice of a longer context) and the normalised form
+    k_wide = torch.zeros(B, H, T + 5, 128, dtype=dt, device="cuda")
+    k_wide[:, :, :T] = k
+    tok2, ch2 = obs_window_scores(q, k_wide[:, :, :T], normalise=True)
+    norm = torch.full((T,), float(W), device="cuda")
+    norm[T - W:] = torch.arange(W, 0, -1, device="cuda").float()
+    assert torch.equal(tok2, tok / norm) and torch.equal(ch2, ch)
+    with pytest.raises(ValueError):
+        obs_window_scores(q.float(), k.float())
+
+
+def test_obs_window_scores_at_full_size_against_the_two_step_path():
+    """Config-1 shape (8 KV heads x 32768 keys, 4 x 32 window rows per head): the fused scores
+    against torch's matmul + softmax followed by _score_one_layer on the same device."""
+    from rdkv_b200.scoring import _score_one_layer, obs_window_scores
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    B, H, gq, W, T = 1, 8, 4, 32, 32768
+    q = torch.randn(B, H * gq, W, 128, device="cuda", generator=gen).half()
+    k = (torch.randn(B, H, T, 128, device="cuda", generator=gen) * 0.5).half()
+    tok, ch = obs_window_scores(q, k)
+    aw = torch.matmul(q, k.repeat_interleave(gq, dim=1).transpose(-1, -2)) * (1.0 / 128 ** 0.5)
+    mask = torch.arange(T, device="cuda")[None, :] > torch.arange(T - W, T, device="cuda")[:, None]
+    aw = aw.masked_fill(mask[None, None], float("-inf")).softmax(dim=-1)
+    want_tok, want_ch = _score_one_layer(aw.view(B, H, gq, W, T), q.view(B, H, gq, W, 128), None, k, 128, k=k)
+    torch.testing.assert_close(tok, want_tok, rtol=1e-2, atol=1e-5)
+    torch.testing.assert_close(ch, want_ch, rtol=1e-5, atol=1e-8)
+
+
 def test_score_pooling_is_bit_exact():
     from rdkv_b200.scoring import apply_score_pooling
     g = load_golden("scoring.npz")

@@ -188,3 +188,16 @@ def test_rope_oracle_matches_reference_vectors(tag, cs):
                                  tag if cs == "same" else "f32")
     assert np.array_equal(q_out.view(np.uint16), g[key + "q_out"].view(np.uint16))
     assert np.array_equal(k_out.view(np.uint16), g[key + "k_out"].view(np.uint16))
+
+
+@pytest.mark.parametrize("tag", ["f16", "bf16", "f16w32"])
+def test_obs_window_scores_oracle_matches_reference_vectors(tag):
+    """Scores from the observation window's queries and the keys (obkv_fast.py:1443-1450 + :854-896)."""
+    from oracle import ref_scoring as RS
+    from conftest import load_golden
+    g = load_golden("obs.npz")
+    B, H, gq, W, T = (int(x) for x in g[f"{tag}_shape"])
+    tok, ch = RS.obs_window_scores(g[f"{tag}_q"], g[f"{tag}_k"], "bf16" if tag == "bf16" else "f16", gq)
+    # (sums of 16-bit weights in another order: the last 16-bit place may differ)
+    np.testing.assert_allclose(tok, g[f"{tag}_token"], rtol=1e-2 if tag == "bf16" else 2e-3, atol=1e-5)
+    np.testing.assert_allclose(ch, g[f"{tag}_channel"], rtol=1e-5)
