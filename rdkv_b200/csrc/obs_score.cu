@@ -110,7 +110,7 @@ struct ObsArgs {
 
 // PASS 0: row statistics and k^2 sums of a tile.  PASS 1: token scores of a tile.
 template <bool BF16, int PASS>
-__global__ void __launch_bounds__(OBS_THREADS)
+__global__ void __launch_bounds__(OBS_THREADS, 3)
 obs_tile_kernel(ObsArgs A) {
   extern __shared__ __align__(16) unsigned char obs_raw[];
   const int tile = blockIdx.x, bh = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -146,10 +146,9 @@ obs_tile_kernel(ObsArgs A) {
   }
 
   const uint32_t q32 = obs_smem(s_q), k32 = obs_smem(s_k);
-  float col[OBS_KEYS / 8][2];                                // PASS 1: this thread's share of the column sums
-  if (PASS == 1) {
-#pragma unroll
-    for (int nt = 0; nt < OBS_KEYS / 8; ++nt) col[nt][0] = col[nt][1] = 0.f;
+  if (PASS == 1) {                                           // the warps' column sums start at zero
+    for (int i = tid; i < OBS_WARPS * OBS_KEYS; i += OBS_THREADS) s_col[i] = 0.f;
+    __syncthreads();
   }
   for (int mt = warp; mt * 16 < R; mt += OBS_WARPS) {
     uint32_t a[8][4];
@@ -165,38 +164,51 @@ obs_tile_kernel(ObsArgs A) {
     // (only tiles that reach into the window or past the sequence's end have anything to mask)
     const bool edge = t0 + OBS_KEYS > (A.causal ? T - A.W : T);
     if (PASS == 0) {
-      // all scores of the m-tile against the staged keys, then the rows' maxima, then one exponential each
-      float sc[OBS_KEYS / 8][4];
+      // half a tile at a time: its scores, the rows' maxima over the half, one exponential each; the
+      // two halves merge like two tiles
+      float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+#pragma unroll 1
+      for (int hf = 0; hf < 2; ++hf) {
+        constexpr int NH = OBS_KEYS / 16;
+        float sc[NH][4];
 #pragma unroll
-      for (int nt = 0; nt < OBS_KEYS / 8; ++nt) {
-        obs_scores<BF16>(sc[nt], a, k32, nt, lane);
-        if (edge) {
-          const int t = t0 + nt * 8 + 2 * j;
-          if (t > lim_a) sc[nt][0] = -INFINITY;
-          if (t + 1 > lim_a) sc[nt][1] = -INFINITY;
-          if (t > lim_b) sc[nt][2] = -INFINITY;
-          if (t + 1 > lim_b) sc[nt][3] = -INFINITY;
+        for (int i = 0; i < NH; ++i) {
+          const int nt = hf * NH + i;
+          obs_scores<BF16>(sc[i], a, k32, nt, lane);
+          if (edge) {
+            const int t = t0 + nt * 8 + 2 * j;
+            if (t > lim_a) sc[i][0] = -INFINITY;
+            if (t + 1 > lim_a) sc[i][1] = -INFINITY;
+            if (t > lim_b) sc[i][2] = -INFINITY;
+            if (t + 1 > lim_b) sc[i][3] = -INFINITY;
+          }
         }
-      }
-      float m_a = -INFINITY, m_b = -INFINITY;
+        float h_a = -INFINITY, h_b = -INFINITY;
 #pragma unroll
-      for (int nt = 0; nt < OBS_KEYS / 8; ++nt) {
-        m_a = fmaxf(m_a, fmaxf(sc[nt][0], sc[nt][1])); m_b = fmaxf(m_b, fmaxf(sc[nt][2], sc[nt][3]));
-      }
+        for (int i = 0; i < NH; ++i) {
+          h_a = fmaxf(h_a, fmaxf(sc[i][0], sc[i][1])); h_b = fmaxf(h_b, fmaxf(sc[i][2], sc[i][3]));
+        }
+        const float n_a = fmaxf(m_a, h_a), n_b = fmaxf(m_b, h_b);
+        const float ca = n_a > -INFINITY ? n_a * OBS_LOG2E : 0.f, cb = n_b > -INFINITY ? n_b * OBS_LOG2E : 0.f;
+        float s_a = 0.f, s_b = 0.f;
 #pragma unroll
-      for (int o = 1; o < 4; o <<= 1) {                      // the four threads of a quad hold the same rows
-        m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, o)); m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, o));
+        for (int i = 0; i < NH; ++i) {                       // (2^-inf = 0: masked keys add nothing)
+          s_a += obs_ex2(fmaf(sc[i][0], OBS_LOG2E, -ca)) + obs_ex2(fmaf(sc[i][1], OBS_LOG2E, -ca));
+          s_b += obs_ex2(fmaf(sc[i][2], OBS_LOG2E, -cb)) + obs_ex2(fmaf(sc[i][3], OBS_LOG2E, -cb));
+        }
+        l_a = (m_a > -INFINITY ? l_a * obs_ex2(fmaf(m_a, OBS_LOG2E, -ca)) : 0.f) + s_a;
+        l_b = (m_b > -INFINITY ? l_b * obs_ex2(fmaf(m_b, OBS_LOG2E, -cb)) : 0.f) + s_b;
+        m_a = n_a; m_b = n_b;
       }
-      const float ca = m_a > -INFINITY ? m_a * OBS_LOG2E : 0.f, cb = m_b > -INFINITY ? m_b * OBS_LOG2E : 0.f;
-      float l_a = 0.f, l_b = 0.f;
-#pragma unroll
-      for (int nt = 0; nt < OBS_KEYS / 8; ++nt) {            // (2^-inf = 0: masked keys add nothing)
-        l_a += obs_ex2(fmaf(sc[nt][0], OBS_LOG2E, -ca)) + obs_ex2(fmaf(sc[nt][1], OBS_LOG2E, -ca));
-        l_b += obs_ex2(fmaf(sc[nt][2], OBS_LOG2E, -cb)) + obs_ex2(fmaf(sc[nt][3], OBS_LOG2E, -cb));
-      }
+      // the four threads of a quad hold the same rows: merge their (m, l) along a fixed tree
 #pragma unroll
       for (int o = 1; o < 4; o <<= 1) {
-        l_a += __shfl_xor_sync(0xffffffffu, l_a, o); l_b += __shfl_xor_sync(0xffffffffu, l_b, o);
+        const float om_a = __shfl_xor_sync(0xffffffffu, m_a, o), ol_a = __shfl_xor_sync(0xffffffffu, l_a, o);
+        const float om_b = __shfl_xor_sync(0xffffffffu, m_b, o), ol_b = __shfl_xor_sync(0xffffffffu, l_b, o);
+        const float na = fmaxf(m_a, om_a), nb = fmaxf(m_b, om_b);
+        l_a = na > -INFINITY ? l_a * obs_ex2((m_a - na) * OBS_LOG2E) + ol_a * obs_ex2((om_a - na) * OBS_LOG2E) : 0.f;
+        l_b = nb > -INFINITY ? l_b * obs_ex2((m_b - nb) * OBS_LOG2E) + ol_b * obs_ex2((om_b - nb) * OBS_LOG2E) : 0.f;
+        m_a = na; m_b = nb;
       }
       if (j == 0) {
         float* dst = A.part + (((int64_t)bh * A.n_tiles + tile) * R) * 2;
@@ -209,7 +221,7 @@ obs_tile_kernel(ObsArgs A) {
       const float M_b = row_b < R ? st[2 * row_b] : 0.f, L_b = row_b < R ? st[2 * row_b + 1] : 1.f;
       const float ca = M_a * OBS_LOG2E, cb = M_b * OBS_LOG2E;
       const float ia = row_a < R ? __frcp_rn(L_a) : 0.f, ib = row_b < R ? __frcp_rn(L_b) : 0.f;   // (a row past R weighs nothing)
-#pragma unroll                                               // (col[] stays in registers)
+#pragma unroll 4
       for (int nt = 0; nt < OBS_KEYS / 8; ++nt) {
         float s[4];
         obs_scores<BF16>(s, a, k32, nt, lane);
@@ -225,22 +237,21 @@ obs_tile_kernel(ObsArgs A) {
         const float p1 = obs_round<BF16>(obs_ex2(fmaf(s[1], OBS_LOG2E, -ca)) * ia);
         const float p2 = obs_round<BF16>(obs_ex2(fmaf(s[2], OBS_LOG2E, -cb)) * ib);
         const float p3 = obs_round<BF16>(obs_ex2(fmaf(s[3], OBS_LOG2E, -cb)) * ib);
-        col[nt][0] += p0 + p2; col[nt][1] += p1 + p3;
+        // column sums over the m-tile's rows (lanes with the same j), added to the warp's own line
+        float c0 = p0 + p2, c1 = p1 + p3;
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          c0 += __shfl_xor_sync(0xffffffffu, c0, o); c1 += __shfl_xor_sync(0xffffffffu, c1, o);
+        }
+        if (r == 0) {
+          float* dst = s_col + warp * OBS_KEYS + nt * 8 + 2 * j;
+          dst[0] += c0; dst[1] += c1;
+        }
       }
     }
   }
   if (PASS == 1) {
-    // column sums: over the rows of a warp (lanes with the same j), then over the warps, in a fixed order
-#pragma unroll
-    for (int nt = 0; nt < OBS_KEYS / 8; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float v = col[nt][e];
-#pragma unroll
-        for (int o = 4; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (r == 0) s_col[warp * OBS_KEYS + nt * 8 + 2 * j + e] = v;
-      }
-    }
+    // the warps' lines are added in warp order
     __syncthreads();
     if (tid < n_keys) {
       float v = 0.f;
