@@ -40,7 +40,7 @@ def _score_one_layer(aw: Tensor, q: Tensor, o, v: Tensor, head_dim: int, v_score
     return token, channel
 
 
-def obs_window_scores(q_obs: Tensor, k: Tensor, *, causal: bool = True, normalise: bool = False):
+def obs_window_scores(q_obs: Tensor, k: Tensor, *, causal: bool = True, normalise: bool = False, check_status: bool = False):
     """Token and channel scores of a prefilled layer from the observation window's queries and the
     layer's keys in one step: what the reference computes with a matmul, a masked softmax and
     ``_score_one_layer`` (obkv_fast.py:1443-1466), without materialising the ``[H_q,W,T]`` weights.
@@ -49,7 +49,9 @@ def obs_window_scores(q_obs: Tensor, k: Tensor, *, causal: bool = True, normalis
     bf16 -> (layer_token [B,H_kv,T], layer_channel [B,H_kv,128]) fp32, as ``_score_one_layer`` returns
     them.  ``causal``: window position w sees keys up to T-W+w (the reference's ``obs_mask``).
     ``normalise``: divide the token scores by the number of window positions that can see each key
-    (the reference's ``correct_norm``, obkv_fast.py:1342-1344, 1461)."""
+    (the reference's ``correct_norm``, obkv_fast.py:1342-1344, 1461).  ``check_status``: wait for the kernels
+    and raise if one of their bounded waits (for the staged operands, for the tensor-core products)
+    ran out, in which case the scores are invalid; without it the call returns at once."""
     require_cuda(q_obs, "q_obs"); require_cuda(k, "k")
     if q_obs.dim() != 4 or k.dim() != 4 or q_obs.shape[-1] != 128 or k.shape[-1] != 128:
         raise ValueError("q_obs must be [B,H_q,W,128] and k [B,H_kv,T,128]")
@@ -75,6 +77,11 @@ def obs_window_scores(q_obs: Tensor, k: Tensor, *, causal: bool = True, normalis
     check(lib().rdkv_obs_scores(ptr(q_obs), ptr(k), q_dtype_tag(q_obs), q_obs.stride(1), q_obs.stride(2), k.stride(1),
                                 k.stride(2), B * H, g, W, T, 1 if causal else 0, ptr(scratch), ptr(token), ptr(channel),
                                 stream_ptr(dev)), "rdkv_obs_scores")
+    if check_status:
+        status = int(scratch[-1:].view(torch.int32).item())    # (the last scratch word)
+        if status != 0:
+            raise RuntimeError(f"rdkv_obs_scores: a device-side wait ran out (status {status}: 1 = operands, "
+                               f"2 = products); the scores are invalid")
     if normalise:
         norm = torch.full((T,), float(W), dtype=torch.float32, device=dev)
         if causal:

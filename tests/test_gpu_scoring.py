@@ -60,7 +60,7 @@ def test_obs_window_scores_match_reference_vectors(tag):
                       if tag == "bf16" else torch.from_numpy(np.ascontiguousarray(a))).cuda()
     q, k = as_t(g[f"{tag}_q"]), as_t(g[f"{tag}_k"])
     assert q.dtype == dt
-    tok, ch = obs_window_scores(q, k)
+    tok, ch = obs_window_scores(q, k, check_status=True)
     # (the weights are rounded to 16 bits before they are summed, in another order than the reference's)
     np.testing.assert_allclose(to_np(tok), g[f"{tag}_token"], rtol=1.5e-2 if tag == "bf16" else 4e-3, atol=2e-5)
     np.testing.assert_allclose(to_np(ch), g[f"{tag}_channel"], rtol=1e-5)
@@ -84,13 +84,45 @@ def test_obs_window_scores_at_full_size_against_the_two_step_path():
     B, H, gq, W, T = 1, 8, 4, 32, 32768
     q = torch.randn(B, H * gq, W, 128, device="cuda", generator=gen).half()
     k = (torch.randn(B, H, T, 128, device="cuda", generator=gen) * 0.5).half()
-    tok, ch = obs_window_scores(q, k)
+    tok, ch = obs_window_scores(q, k, check_status=True)
     aw = torch.matmul(q, k.repeat_interleave(gq, dim=1).transpose(-1, -2)) * (1.0 / 128 ** 0.5)
     mask = torch.arange(T, device="cuda")[None, :] > torch.arange(T - W, T, device="cuda")[:, None]
     aw = aw.masked_fill(mask[None, None], float("-inf")).softmax(dim=-1)
     want_tok, want_ch = _score_one_layer(aw.view(B, H, gq, W, T), q.view(B, H, gq, W, 128), None, k, 128, k=k)
     torch.testing.assert_close(tok, want_tok, rtol=1e-2, atol=1e-5)
     torch.testing.assert_close(ch, want_ch, rtol=1e-5, atol=1e-8)
+
+
+@pytest.mark.parametrize("gq,W,T,dt,causal,k_pad", [
+    (8, 32, 700, torch.float16, True, 0),      # 256 rows: two accumulator blocks, operands by TMA
+    (8, 32, 513, torch.bfloat16, True, 0),
+    (3, 20, 450, torch.float16, True, 0),      # window not a multiple of 8: queries staged by plain loads
+    (5, 48, 300, torch.bfloat16, True, 0),     # a head's rows would straddle the two blocks: plain loads
+    (2, 24, 257, torch.float16, False, 0),     # 48 rows (zero rows up to 128), no mask
+    (4, 32, 1000, torch.bfloat16, True, 4),    # key rows 132 elements apart: keys staged by unaligned plain loads
+    (4, 32, 640, torch.float16, True, 8),      # key rows 136 elements apart: still a valid tensor map
+    (1, 1, 1, torch.float16, True, 0),
+])
+def test_obs_window_scores_over_shapes_and_layouts(gq, W, T, dt, causal, k_pad):
+    """Both ways the operands reach shared memory (tensor maps / plain loads), one and two row
+    blocks, ragged last tiles: against torch's matmul + softmax and _score_one_layer on the device."""
+    from rdkv_b200.scoring import _score_one_layer, obs_window_scores
+    gen = torch.Generator(device="cuda").manual_seed(gq * 1000 + W + T)
+    B, H = 2, 3
+    q = torch.randn(B, H * gq, W, 128, device="cuda", generator=gen).to(dt)
+    k_store = (torch.randn(B, H, T, 128 + k_pad, device="cuda", generator=gen) * 0.6).to(dt)
+    k = k_store[..., :128]
+    tok, ch = obs_window_scores(q, k, causal=causal, check_status=True)
+    aw = torch.matmul(q, k.repeat_interleave(gq, dim=1).transpose(-1, -2)) * (1.0 / 128 ** 0.5)
+    if causal:
+        mask = torch.arange(T, device="cuda")[None, :] > torch.arange(T - W, T, device="cuda")[:, None]
+        aw = aw.masked_fill(mask[None, None], float("-inf"))
+    aw = aw.softmax(dim=-1)
+    kc = k.contiguous()
+    want_tok, want_ch = _score_one_layer(aw.view(B, H, gq, W, T), q.view(B, H, gq, W, 128), None, kc, 128, k=kc)
+    torch.testing.assert_close(tok, want_tok, rtol=3e-2 if dt == torch.bfloat16 else 1e-2, atol=2e-5)
+    torch.testing.assert_close(ch, want_ch, rtol=1e-5, atol=1e-8)
+    assert torch.equal(tok, obs_window_scores(q, k, causal=causal)[0])
 
 
 def test_score_pooling_is_bit_exact():
