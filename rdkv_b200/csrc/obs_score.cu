@@ -21,10 +21,11 @@
 //   obs_tile_kernel<.,0>  per tile: scores rounded as the reference's 16-bit matmul and scaling
 //                         round them, masked; per row and half tile the maximum and the sum of
 //                         exponentials; per channel the tile's sum of k^2.
-//   obs_reduce_kernel     per KV head: the rows' maxima and sums over all tiles; the channel score.
+//   obs_reduce_kernel     per KV head: the rows' maxima and sums over all tiles.
 //   obs_tile_kernel<.,1>  per tile: the same scores again, p = exp(s - M) / L rounded to the 16-bit
 //                         type, parked in shared memory (over the spent operands) and summed over
-//                         the rows: the token scores of the tile.
+//                         the rows: the token scores of the tile.  One more CTA per head turns the
+//                         tiles' k^2 sums and the queries into the channel score meanwhile.
 // The keys are read twice (the second time mostly from L2); sums run in a fixed order.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out sets a bit in the status word (the
@@ -33,6 +34,7 @@
 #include <cuda.h>   // CUtensorMap and its enums (the encoder itself is looked up through the runtime)
 
 #include <cstring>
+#include <type_traits>
 
 #include "rdkv_common.cuh"
 
@@ -69,6 +71,27 @@ __device__ __forceinline__ uint32_t obs_pack(float lo, float hi) {   // two valu
 template <bool BF16>
 __device__ __forceinline__ float obs_unpack(uint32_t bits16) {
   return BF16 ? __uint_as_float(bits16 << 16) : h2f((uint16_t)bits16);
+}
+template <bool BF16>
+__device__ __forceinline__ float2 obs_unpack2(uint32_t w) {          // both halves of a packed pair
+  if (BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t obs_max2(uint32_t a, uint32_t b) {   // element-wise maximum of two packed pairs
+  if (BF16) {
+    const __nv_bfloat162 v = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  const __half2 v = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+// A pair of accumulator values as the pair of scores the reference sees: the 16-bit matmul result
+// times 1/sqrt(128) in fp32, rounded to the 16-bit type again (two values per conversion).
+template <bool BF16>
+__device__ __forceinline__ uint32_t obs_score2(uint32_t acc_lo, uint32_t acc_hi) {
+  const float2 f = obs_unpack2<BF16>(obs_pack<BF16>(__uint_as_float(acc_lo), __uint_as_float(acc_hi)));
+  return obs_pack<BF16>(f.x * INV_SQRT_D, f.y * INV_SQRT_D);
 }
 
 // ── mbarrier, TMA, tcgen05 ──────────────────────────────────────────────────────────────────
@@ -175,6 +198,7 @@ struct ObsArgs {
   const uint16_t* q; const uint16_t* k;
   int64_t q_head_stride, q_row_stride, k_head_stride, k_row_stride;   // elements
   int g, W, T, causal, n_tiles;
+  int BH, extra_rows;  // heads; rows of the second tile launch's grid that compute channel scores
   int tma_q, tma_k;    // operands come through the tensor maps (else by plain loads)
   float* part;         // [BH][2*n_tiles][R][2] half-tile maxima and sums
   float* ksq;          // [BH][n_tiles][128] tile sums of k^2
@@ -184,7 +208,29 @@ struct ObsArgs {
   int* status;         // bit 0: operands did not arrive, bit 1: products did not complete
 };
 
-// PASS 0: row statistics and k^2 sums of a tile.  PASS 1: token scores of a tile.
+// The channel score of KV head bh = mean(q^2) * mean_t(k^2), by one CTA of OBS_THREADS threads:
+// threads (half, channel) sum every other row / tile, the halves are added at the end.  Runs as an
+// extra CTA of the second tile launch (the tiles' k^2 sums come from the first).
+template <bool BF16>
+__device__ __forceinline__ void obs_channel_score(const ObsArgs& A, int bh, float* s_sum /* [4][128] */) {
+  const int tid = threadIdx.x, c = tid & 127, half = tid >> 7, R = A.g * A.W;
+  float qs = 0.f, ks = 0.f;
+#pragma unroll 8
+  for (int row = half; row < R; row += 2) {
+    const uint16_t b = A.q[((int64_t)bh * A.g + row / A.W) * A.q_head_stride + (int64_t)(row % A.W) * A.q_row_stride + c];
+    const float x = obs_unpack<BF16>(b);
+    qs = fmaf(x, x, qs);
+  }
+#pragma unroll 16
+  for (int i = half; i < A.n_tiles; i += 2) ks += A.ksq[((int64_t)bh * A.n_tiles + i) * 128 + c];
+  s_sum[half * 128 + c] = qs; s_sum[256 + half * 128 + c] = ks;
+  __syncthreads();
+  if (tid < 128)
+    A.channel[(int64_t)bh * 128 + tid] = ((s_sum[tid] + s_sum[128 + tid]) / (float)R) * ((s_sum[256 + tid] + s_sum[384 + tid]) / (float)A.T);
+}
+
+// PASS 0: row statistics and k^2 sums of a tile.  PASS 1: token scores of a tile; the first
+// extra_rows rows of its grid (dispatched first) compute the heads' channel scores instead.
 template <bool BF16, int PASS>
 __global__ void __launch_bounds__(OBS_THREADS, 3)
 obs_tile_kernel(const ObsArgs A, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k) {
@@ -192,7 +238,13 @@ obs_tile_kernel(const ObsArgs A, const __grid_constant__ CUtensorMap tm_q, const
   __shared__ __align__(8) uint64_t s_bar[2];                 // [0] operands landed, [1] products complete
   __shared__ uint32_t s_tmem;                                // base of the CTA's tensor-memory columns
   __shared__ float s_col[4 * OBS_KEYS];
-  const int tile = blockIdx.x, bh = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (PASS == 1 && (int)blockIdx.y < A.extra_rows) {        // the grid's first rows: one CTA per head for the channel scores
+    const int head = blockIdx.y * gridDim.x + blockIdx.x;
+    if (head < A.BH) obs_channel_score<BF16>(A, head, s_col);
+    return;
+  }
+  const int tile = blockIdx.x, bh = PASS == 1 ? (int)blockIdx.y - A.extra_rows : (int)blockIdx.y;
   const int R = A.g * A.W, T = A.T, MB = (R + OBS_ROWS - 1) / OBS_ROWS;
   const uint32_t raw32 = obs_smem(obs_raw), k32 = (raw32 + 1023u) & ~1023u, q32 = k32 + OBS_BLOCK;
   unsigned char* s_k = obs_raw + (k32 - raw32);              // [128 keys] operand block, 1024-byte aligned
@@ -266,20 +318,32 @@ obs_tile_kernel(const ObsArgs A, const __grid_constant__ CUtensorMap tm_q, const
     }
   }
 
-  if (PASS == 0) {                                           // k^2 of the tile: thread = (half of the keys, channel)
+  if (PASS == 0) {
+    // k^2 of the tile.  Lanes 0-15 / 16-31 of warp w take the 16-byte chunk (8 channels) 2w / 2w+1 of
+    // keys rs, rs+16, ... (rs = lane & 15); a quarter warp's loads fall on distinct banks.  The 16
+    // lanes of a chunk then add up along a fixed tree.  (Rows past the tile's keys are zeros.)
     obs_bar_wait(bar_ld, 0);
-    const int c = tid & 127, half = tid >> 7, ch = (c & 63) >> 3;
-    const unsigned char* col = s_k + (c >> 6) * OBS_PANEL + (c & 7) * 2;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int t = half * (OBS_KEYS / 2); t < (half + 1) * (OBS_KEYS / 2); ++t) {   // (rows past the tile's keys are zeros)
-      const uint16_t b = *reinterpret_cast<const uint16_t*>(col + (t >> 3) * 1024 + (t & 7) * 128 + ((ch ^ (t & 7)) << 4));
-      const float x = obs_unpack<BF16>(b);
-      acc[t & 3] = fmaf(x, x, acc[t & 3]);
+    const int c16 = warp * 2 + (lane >> 4), rs = lane & 15;
+    const unsigned char* src = s_k + (c16 >> 3) * OBS_PANEL + (rs >> 3) * 1024 + (rs & 7) * 128 + (((c16 & 7) ^ (rs & 7)) << 4);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < OBS_KEYS / 16; ++j) {                // key j*16 + rs: two groups of 8 rows further each time
+      const uint4 v = *reinterpret_cast<const uint4*>(src + j * 2048);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = obs_unpack2<BF16>(w[e]);
+        acc[2 * e] = fmaf(x.x, x.x, acc[2 * e]); acc[2 * e + 1] = fmaf(x.y, x.y, acc[2 * e + 1]);
+      }
     }
-    s_col[half * 128 + c] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-    __syncthreads();
-    if (tid < 128) A.ksq[((int64_t)bh * A.n_tiles + tile) * 128 + tid] = s_col[tid] + s_col[128 + tid];
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+    if (rs == 0) {
+      float4* dst = reinterpret_cast<float4*>(A.ksq + ((int64_t)bh * A.n_tiles + tile) * 128 + c16 * 8);
+      dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]); dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
   }
 
   if (!obs_bar_wait(bar_mma, 0) && lane == 0) atomicOr(A.status, 2);
@@ -289,61 +353,75 @@ obs_tile_kernel(const ObsArgs A, const __grid_constant__ CUtensorMap tm_q, const
   // (only tiles that reach into the window or past the sequence's end have anything to mask)
   const bool edge = t0 + OBS_KEYS > (A.causal ? T - A.W : T);
   uint32_t* s_p = reinterpret_cast<uint32_t*>(s_k);          // PASS 1: [R][OBS_P_LD] pairs of weights, over the spent operands
-  for (int mb = 0; mb < MB; ++mb) {
-    const int row = mb * OBS_ROWS + q4 * 32 + lane;
-    if (row - lane >= R) continue;                           // (the whole warp)
-    const int lim = A.causal ? T - A.W + (row % A.W) : T - 1;   // last key this row may see
-    const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(mb * OBS_KEYS + half * 64);
-    const int tk = t0 + half * 64;
-    if (PASS == 0) {
-      // 32 keys at a time: the scores, the row's maximum over them, one exponential each; the
-      // chunks merge like tiles
-      float m = -INFINITY, l = 0.f;
-#pragma unroll 1
-      for (int ck = 0; ck < 2; ++ck) {
-        uint32_t v[32];
-        obs_tmem_ld(taddr + (uint32_t)ck * 32u, v);
-        float h = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = obs_round<BF16>(obs_round<BF16>(__uint_as_float(v[i])) * INV_SQRT_D);
-          if (edge && tk + ck * 32 + i > lim) s = -INFINITY;
-          v[i] = __float_as_uint(s);
-          h = fmaxf(h, s);
-        }
-        const float n = fmaxf(m, h);
-        const float c = n > -INFINITY ? n * OBS_LOG2E : 0.f;
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sum[i & 3] += obs_ex2(fmaf(__uint_as_float(v[i]), OBS_LOG2E, -c));   // (2^-inf = 0)
-        l = (m > -INFINITY ? l * obs_ex2(fmaf(m, OBS_LOG2E, -c)) : 0.f) + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
-        m = n;
-      }
-      if (row < R)
-        *reinterpret_cast<float2*>(A.part + ((((int64_t)bh * A.n_tiles + tile) * 2 + half) * R + row) * 2) = make_float2(m, l);
-    } else {
-      const float* st = A.stats + ((int64_t)bh * R + min(row, R - 1)) * 2;
-      const float cM = st[0] * OBS_LOG2E, inv = __frcp_rn(st[1]);
-      uint32_t* prow = s_p + (size_t)min(row, R - 1) * OBS_P_LD + half * 32;
-#pragma unroll 1
-      for (int ck = 0; ck < 2; ++ck) {
-        uint32_t v[32];
-        obs_tmem_ld(taddr + (uint32_t)ck * 32u, v);
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float s0 = obs_round<BF16>(obs_round<BF16>(__uint_as_float(v[i])) * INV_SQRT_D);
-          float s1 = obs_round<BF16>(obs_round<BF16>(__uint_as_float(v[i + 1])) * INV_SQRT_D);
-          if (edge) {
-            if (tk + ck * 32 + i > lim) s0 = -INFINITY;
-            if (tk + ck * 32 + i + 1 > lim) s1 = -INFINITY;
+  // the tile's epilogue, compiled once with and once without the masking
+  auto epilogue = [&](auto edge_c) {
+    constexpr bool EDGE = decltype(edge_c)::value;
+    for (int mb = 0; mb < MB; ++mb) {
+      const int row = mb * OBS_ROWS + q4 * 32 + lane;
+      if (row - lane >= R) continue;                           // (the whole warp)
+      const int lim = A.causal ? T - A.W + (row % A.W) : T - 1;   // last key this row may see
+      const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(mb * OBS_KEYS + half * 64);
+      const int tk = t0 + half * 64;
+      if (PASS == 0) {
+        // 32 keys at a time: the scores (as packed pairs), the row's maximum over them, one exponential
+        // each; the chunks merge like tiles
+        float m = -INFINITY, l = 0.f;
+  #pragma unroll 1
+        for (int ck = 0; ck < 2; ++ck) {
+          uint32_t v[32];
+          obs_tmem_ld(taddr + (uint32_t)ck * 32u, v);
+          uint32_t h2 = BF16 ? 0xFF80FF80u : 0xFC00FC00u;      // (-inf, -inf)
+  #pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            uint32_t s2 = obs_score2<BF16>(v[2 * i], v[2 * i + 1]);
+            if (EDGE) {                                        // (per CTA: only the last tiles mask anything)
+              const int t = tk + ck * 32 + 2 * i;
+              if (t > lim) s2 = (s2 & 0xFFFF0000u) | (BF16 ? 0xFF80u : 0xFC00u);
+              if (t + 1 > lim) s2 = (s2 & 0x0000FFFFu) | (BF16 ? 0xFF800000u : 0xFC000000u);
+            }
+            v[i] = s2;
+            h2 = obs_max2<BF16>(h2, s2);
           }
-          // p = exp(s - M) / L in fp32, rounded to the 16-bit type as the reference's softmax output is
-          const uint32_t pp = obs_pack<BF16>(obs_ex2(fmaf(s0, OBS_LOG2E, -cM)) * inv, obs_ex2(fmaf(s1, OBS_LOG2E, -cM)) * inv);
-          if (row < R) prow[ck * 16 + (i >> 1)] = pp;
+          const float2 hh = obs_unpack2<BF16>(h2);
+          const float n = fmaxf(m, fmaxf(hh.x, hh.y));
+          const float c = n > -INFINITY ? n * OBS_LOG2E : 0.f;
+          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+  #pragma unroll
+          for (int i = 0; i < 16; ++i) {                       // (2^-inf = 0: masked keys add nothing)
+            const float2 sc = obs_unpack2<BF16>(v[i]);
+            sum[(2 * i) & 3] += obs_ex2(fmaf(sc.x, OBS_LOG2E, -c));
+            sum[(2 * i + 1) & 3] += obs_ex2(fmaf(sc.y, OBS_LOG2E, -c));
+          }
+          l = (m > -INFINITY ? l * obs_ex2(fmaf(m, OBS_LOG2E, -c)) : 0.f) + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+          m = n;
+        }
+        if (row < R)
+          *reinterpret_cast<float2*>(A.part + ((((int64_t)bh * A.n_tiles + tile) * 2 + half) * R + row) * 2) = make_float2(m, l);
+      } else {
+        const float* st = A.stats + ((int64_t)bh * R + min(row, R - 1)) * 2;
+        const float cM = st[0] * OBS_LOG2E, inv = __frcp_rn(st[1]);
+        uint32_t* prow = s_p + (size_t)min(row, R - 1) * OBS_P_LD + half * 32;
+  #pragma unroll 1
+        for (int ck = 0; ck < 2; ++ck) {
+          uint32_t v[32];
+          obs_tmem_ld(taddr + (uint32_t)ck * 32u, v);
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float2 sc = obs_unpack2<BF16>(obs_score2<BF16>(v[i], v[i + 1]));
+            if (EDGE) {
+              if (tk + ck * 32 + i > lim) sc.x = -INFINITY;
+              if (tk + ck * 32 + i + 1 > lim) sc.y = -INFINITY;
+            }
+            // p = exp(s - M) / L in fp32, rounded to the 16-bit type as the reference's softmax output is
+            const uint32_t pp = obs_pack<BF16>(obs_ex2(fmaf(sc.x, OBS_LOG2E, -cM)) * inv, obs_ex2(fmaf(sc.y, OBS_LOG2E, -cM)) * inv);
+            if (row < R) prow[ck * 16 + (i >> 1)] = pp;
+          }
         }
       }
     }
-  }
+  };
+  if (edge) epilogue(std::true_type{});
+  else epilogue(std::false_type{});
   obs_fence_before();
   __syncthreads();
   if (warp == 1)
@@ -356,7 +434,8 @@ obs_tile_kernel(const ObsArgs A, const __grid_constant__ CUtensorMap tm_q, const
 #pragma unroll 4
     for (int r = qtr * per; r < r_end; ++r) {
       const uint32_t w = s_p[(size_t)r * OBS_P_LD + cp];
-      a0 += obs_unpack<BF16>(w & 0xFFFFu); a1 += obs_unpack<BF16>(w >> 16);
+      const float2 p = obs_unpack2<BF16>(w);
+      a0 += p.x; a1 += p.y;
     }
     s_col[qtr * OBS_KEYS + 2 * cp] = a0; s_col[qtr * OBS_KEYS + 2 * cp + 1] = a1;
     __syncthreads();
@@ -367,59 +446,56 @@ obs_tile_kernel(const ObsArgs A, const __grid_constant__ CUtensorMap tm_q, const
   }
 }
 
-// Per KV head: the rows' maxima and sums over all half tiles, and the channel score.  blockIdx.y <
-// OBS_RED_ROWS takes an eighth of the rows, a warp per row: the lanes take every 32nd half tile,
-// then merge their (m, l) pairs along a fixed tree; the last blockIdx.y takes the channels.
+// The rows' maxima and sums over all half tiles.  A CTA takes 8 rows of a head: thread (slice, row)
+// merges every 64th half tile of its row (a warp's loads cover 4 slices x 8 rows = 4 runs of 64
+// bytes), the 64 slices of a row are then merged by one warp along a fixed tree.
 constexpr int OBS_RED_ROWS = 8;
-template <bool BF16>
-__global__ void __launch_bounds__(256)
+constexpr int OBS_RED_SLICES = 64;
+constexpr int OBS_RED_THREADS = OBS_RED_ROWS * OBS_RED_SLICES;
+__device__ __forceinline__ void obs_merge(float& M, float& L, float m, float l) {   // (M, L) <- (M, L) + (m, l)
+  if (m > -INFINITY) {
+    const float n = fmaxf(M, m);
+    L = L * obs_ex2((M - n) * OBS_LOG2E) + l * obs_ex2((m - n) * OBS_LOG2E);
+    M = n;
+  }
+}
+__global__ void __launch_bounds__(OBS_RED_THREADS)
 obs_reduce_kernel(ObsArgs A) {
-  const int bh = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  __shared__ float2 s_ml[OBS_RED_SLICES][OBS_RED_ROWS];
+  const int bh = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int R = A.g * A.W, n_parts = 2 * A.n_tiles;
-  if ((int)blockIdx.y < OBS_RED_ROWS) {
-    const int per = (R + OBS_RED_ROWS - 1) / OBS_RED_ROWS;
-    const int r_end = min(R, ((int)blockIdx.y + 1) * per);
-    for (int row = blockIdx.y * per + warp; row < r_end; row += 8) {
-      const float* p = A.part + ((int64_t)bh * n_parts * R + row) * 2;
-      float M = -INFINITY, L = 0.f;
-      for (int i = lane; i < n_parts; i += 32) {
-        const float2 ml = *reinterpret_cast<const float2*>(p + (int64_t)i * R * 2);
-        if (ml.x > -INFINITY) {
-          const float n = fmaxf(M, ml.x);
-          L = L * obs_ex2((M - n) * OBS_LOG2E) + ml.y * obs_ex2((ml.x - n) * OBS_LOG2E);
-          M = n;
-        }
+  const int r = tid & (OBS_RED_ROWS - 1), slice = tid / OBS_RED_ROWS;
+  const int row = blockIdx.x * OBS_RED_ROWS + r;
+  float M = -INFINITY, L = 0.f;
+  if (row < R) {
+    const float* p = A.part + ((int64_t)bh * n_parts * R + row) * 2;
+    for (int base = slice; base < n_parts; base += 8 * OBS_RED_SLICES) {
+      float2 ml[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {                          // eight loads in flight
+        const int i = base + u * OBS_RED_SLICES;
+        ml[u] = i < n_parts ? *reinterpret_cast<const float2*>(p + (int64_t)i * R * 2) : make_float2(-INFINITY, 0.f);
       }
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float om = __shfl_xor_sync(0xffffffffu, M, o), ol = __shfl_xor_sync(0xffffffffu, L, o);
-        const float n = fmaxf(M, om);
-        L = n > -INFINITY ? L * obs_ex2((M - n) * OBS_LOG2E) + ol * obs_ex2((om - n) * OBS_LOG2E) : 0.f;
-        M = n;
-      }
-      if (lane == 0) {
-        A.stats[((int64_t)bh * R + row) * 2] = M;
-        A.stats[((int64_t)bh * R + row) * 2 + 1] = L;
-      }
+      for (int u = 0; u < 8; ++u) obs_merge(M, L, ml[u].x, ml[u].y);
     }
-    return;
   }
-  // channel score: threads (half, channel) sum every other row / tile, the halves are added at the end
-  __shared__ float s_q2[2][128], s_k2[2][128];
-  const int c = tid & 127, half = tid >> 7;
-  float qs = 0.f, ks = 0.f;
-#pragma unroll 4
-  for (int row = half; row < R; row += 2) {
-    const uint16_t b = A.q[((int64_t)bh * A.g + row / A.W) * A.q_head_stride + (int64_t)(row % A.W) * A.q_row_stride + c];
-    const float x = obs_unpack<BF16>(b);
-    qs = fmaf(x, x, qs);
-  }
-#pragma unroll 8
-  for (int i = half; i < A.n_tiles; i += 2) ks += A.ksq[((int64_t)bh * A.n_tiles + i) * 128 + c];
-  s_q2[half][c] = qs; s_k2[half][c] = ks;
+  s_ml[slice][r] = make_float2(M, L);
   __syncthreads();
-  if (tid < 128)
-    A.channel[(int64_t)bh * 128 + tid] = ((s_q2[0][tid] + s_q2[1][tid]) / (float)R) * ((s_k2[0][tid] + s_k2[1][tid]) / (float)A.T);
+  if (warp < OBS_RED_ROWS) {                                 // warp w: the 64 slices of row w
+    const float2 a = s_ml[lane][warp], b = s_ml[lane + 32][warp];
+    M = a.x; L = a.x > -INFINITY ? a.y : 0.f;
+    obs_merge(M, L, b.x, b.y);
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, M, o), ol = __shfl_xor_sync(0xffffffffu, L, o);
+      const float n = fmaxf(M, om);
+      L = n > -INFINITY ? L * obs_ex2((M - n) * OBS_LOG2E) + ol * obs_ex2((om - n) * OBS_LOG2E) : 0.f;
+      M = n;
+    }
+    const int out_row = blockIdx.x * OBS_RED_ROWS + warp;
+    if (lane == 0 && out_row < R) *reinterpret_cast<float2*>(A.stats + ((int64_t)bh * R + out_row) * 2) = make_float2(M, L);
+  }
 }
 
 // ── tensor maps ─────────────────────────────────────────────────────────────────────────────
@@ -481,12 +557,13 @@ extern "C" int rdkv_obs_scores(const void* q_obs, const void* k, int dtype, int6
   if (BH < 0 || g <= 0 || W <= 0 || T <= 0 || (causal && W > T)) return RDKV_ERR_BAD_SHAPE;
   if ((int64_t)g * W > OBS_MAX_ROWS) return RDKV_ERR_TOO_LARGE;
   if (BH == 0) return RDKV_OK;
-  if (BH > 65535) return RDKV_ERR_TOO_LARGE;
+  if (BH > 65000) return RDKV_ERR_TOO_LARGE;
   const bool bf = dtype == RDKV_BF16;
   ObsArgs A;
   A.q = reinterpret_cast<const uint16_t*>(q_obs); A.k = reinterpret_cast<const uint16_t*>(k);
   A.q_head_stride = q_head_stride; A.q_row_stride = q_row_stride; A.k_head_stride = k_head_stride; A.k_row_stride = k_row_stride;
   A.g = g; A.W = W; A.T = T; A.causal = causal ? 1 : 0; A.n_tiles = (T + OBS_KEYS - 1) / OBS_KEYS;
+  A.BH = BH; A.extra_rows = (BH + A.n_tiles - 1) / A.n_tiles;
   const int64_t R = (int64_t)g * W;
   const int MB = (int)((R + OBS_ROWS - 1) / OBS_ROWS);
   A.part = scratch;
@@ -513,12 +590,12 @@ extern "C" int rdkv_obs_scores(const void* q_obs, const void* k, int dtype, int6
     kern_stats<<<grid, OBS_THREADS, smem, st>>>(A, tm_q, tm_k);
     int rc = launch_status();
     if (rc != RDKV_OK) return rc;
-    kern_reduce<<<dim3(BH, OBS_RED_ROWS + 1), 256, 0, st>>>(A);
+    kern_reduce<<<dim3((unsigned)((R + OBS_RED_ROWS - 1) / OBS_RED_ROWS), BH), OBS_RED_THREADS, 0, st>>>(A);
     rc = launch_status();
     if (rc != RDKV_OK) return rc;
-    kern_token<<<grid, OBS_THREADS, smem, st>>>(A, tm_q, tm_k);
+    kern_token<<<dim3(A.n_tiles, BH + A.extra_rows), OBS_THREADS, smem, st>>>(A, tm_q, tm_k);
     return launch_status();
   };
-  if (bf) return launch(obs_tile_kernel<true, 0>, obs_reduce_kernel<true>, obs_tile_kernel<true, 1>);
-  return launch(obs_tile_kernel<false, 0>, obs_reduce_kernel<false>, obs_tile_kernel<false, 1>);
+  if (bf) return launch(obs_tile_kernel<true, 0>, obs_reduce_kernel, obs_tile_kernel<true, 1>);
+  return launch(obs_tile_kernel<false, 0>, obs_reduce_kernel, obs_tile_kernel<false, 1>);
 }
