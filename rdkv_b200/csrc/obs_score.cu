@@ -8,31 +8,35 @@
 // mean_t(k^2).  The reference materialises the weights (2 bytes x H_q x W x T) and reads them
 // back; here a tile of scores lives in tensor memory and registers only.
 //
-// The contraction runs on the fifth-generation tensor cores.  Per (KV head, 128-key tile) one CTA
-//   * brings the tile's keys and the head's g*W query rows into shared memory in the tensor
-//     cores' K-major layout with 128-byte swizzle: tiled TMA copies through two tensor maps when
-//     the strides allow it, plain 16-byte loads with the same swizzle otherwise;
-//   * has one thread issue eight tcgen05.mma (M = 128 rows, N = 128 keys, K = 16 channels each) per
-//     128-row block into an fp32 accumulator in tensor memory, followed by a tcgen05.commit onto
-//     an mbarrier;
-//   * reads the accumulator back with tcgen05.ld: a thread holds 32 consecutive keys of ONE row at
-//     a time, so the row statistics need no exchange between threads.
+// The contraction runs on the fifth-generation tensor cores.  A CTA belongs to one KV head and
+// streams every P-th 128-key tile of it (P CTAs per head, about two CTAs per SM in all):
+//   * the head's g*W query rows arrive once, the key tiles through a ring of two buffers, all in
+//     the tensor cores' K-major layout with 128-byte swizzle: tiled TMA copies through two tensor
+//     maps when the strides allow it, plain 16-byte loads with the same swizzle otherwise;
+//   * thread 0 issues eight tcgen05.mma (K = 16 channels each) per tile into one of two fp32
+//     accumulators in tensor memory and a tcgen05.commit onto an mbarrier; the products of tile
+//     n+1 and the copies of tile n+2 run while the 8 warps work through tile n;
+//   * the warps read the accumulator back with tcgen05.ld, 32 columns of ONE accumulator row per
+//     thread at a time.
 // Three launches per layer:
-//   obs_tile_kernel<.,0>  per tile: scores rounded as the reference's 16-bit matmul and scaling
-//                         round them, masked; per row and half tile the maximum and the sum of
-//                         exponentials; per channel the tile's sum of k^2.
-//   obs_reduce_kernel     per KV head: the rows' maxima and sums over all tiles.
-//   obs_tile_kernel<.,1>  per tile: the same scores again, p = exp(s - M) / L rounded to the 16-bit
-//                         type, parked in shared memory (over the spent operands) and summed over
-//                         the rows: the token scores of the tile.  One more CTA per head turns the
-//                         tiles' k^2 sums and the queries into the channel score meanwhile.
+//   obs_stream_kernel<.,0>  S = Q.K^T (accumulator row = query row): scores rounded as the
+//                           reference's 16-bit matmul and scaling round them, masked; a thread
+//                           keeps its row's running maximum and sum of exponentials over the
+//                           CTA's tiles (no exchange between threads) and the tile's k^2.
+//   obs_reduce_kernel       the rows' maxima and sums over the CTAs of a head.
+//   obs_stream_kernel<.,1>  S^T = K.Q^T (accumulator row = key): the same scores again, p =
+//                           exp(s - M) / L rounded to the 16-bit type and summed over the query
+//                           rows inside the thread: the token scores.  One more CTA per head
+//                           turns the k^2 sums and the queries into the channel score meanwhile.
 // The keys are read twice (the second time mostly from L2); sums run in a fixed order.
 //
-// Every wait on an mbarrier is bounded; a wait that runs out sets a bit in the status word (the
-// last word of the scratch buffer: 1 = the operands did not arrive, 2 = the products did not
-// complete), the kernel still frees its tensor memory and returns, and the results are invalid.
+// Only thread 0 waits on mbarriers, every such wait is bounded, and the other threads meet it at
+// CTA barriers.  A wait that runs out sets a bit in the status word (the last word of the scratch
+// buffer: 1 = operands did not arrive, 2 = products did not complete); the kernel still frees its
+// tensor memory and returns, and the results are invalid.
 #include <cuda.h>   // CUtensorMap and its enums (the encoder itself is looked up through the runtime)
 
+#include <algorithm>
 #include <cstring>
 #include <type_traits>
 
@@ -40,13 +44,12 @@
 
 namespace rdkv {
 
-constexpr int OBS_THREADS = 256;                 // 8 warps: warp w reads accumulator rows 32*(w&3).., key half w>>2
-constexpr int OBS_KEYS = 128;                    // keys per tile = N of one MMA
-constexpr int OBS_ROWS = 128;                    // rows per accumulator block = M of one MMA
+constexpr int OBS_THREADS = 256;                 // 8 warps: warp w reads accumulator rows 32*(w&3).., column half w>>2
+constexpr int OBS_KEYS = 128;                    // keys per tile
+constexpr int OBS_ROWS = 128;                    // query rows per block of the first pass (M of its MMAs)
 constexpr int OBS_MAX_ROWS = 256;                // (query head, position) pairs per KV head: two blocks
 constexpr int OBS_PANEL = 128 * 128;             // bytes: 128 rows of 64 16-bit channels, 128 bytes a row
 constexpr int OBS_BLOCK = 2 * OBS_PANEL;         // a 128-row operand: channels 0-63, then channels 64-127
-constexpr int OBS_P_LD = 65;                     // words per row of the parked weights (odd: rows fall on distinct banks)
 constexpr unsigned OBS_WAIT_LIMIT = 1u << 18;    // try_wait rounds before a wait gives up (a wait normally ends within microseconds)
 
 __device__ __forceinline__ uint32_t obs_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -131,13 +134,12 @@ __device__ __forceinline__ uint64_t obs_desc(uint32_t addr) {
   return (uint64_t)((addr >> 4) & 0x3FFFu) | (uint64_t)1 << 16 | (uint64_t)(1024 >> 4) << 32 | (uint64_t)1 << 46 |
          (uint64_t)2 << 61;
 }
-// Instruction descriptor of a dense 16-bit MMA with fp32 accumulation, both operands K-major:
-// bits [4,6) accumulator 1 = fp32, [7,10) and [10,13) operand types (0 = fp16, 1 = bf16),
-// [17,23) N / 8, [24,29) M / 16.
+// Instruction descriptor of a dense 16-bit MMA of 128 x n (n a multiple of 16) with fp32
+// accumulation, both operands K-major: bits [4,6) accumulator 1 = fp32, [7,10) and [10,13) operand
+// types (0 = fp16, 1 = bf16), [17,23) N / 8, [24,29) M / 16.
 template <bool BF16>
-__device__ __forceinline__ constexpr uint32_t obs_idesc() {
-  return 1u << 4 | (BF16 ? 1u : 0u) << 7 | (BF16 ? 1u : 0u) << 10 | (uint32_t)(OBS_KEYS >> 3) << 17 |
-         (uint32_t)(OBS_ROWS >> 4) << 24;
+__device__ __forceinline__ constexpr uint32_t obs_idesc(int n) {
+  return 1u << 4 | (BF16 ? 1u : 0u) << 7 | (BF16 ? 1u : 0u) << 10 | (uint32_t)(n >> 3) << 17 | (uint32_t)(128 >> 4) << 24;
 }
 __device__ __forceinline__ void obs_mma(uint32_t tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -166,16 +168,17 @@ __device__ __forceinline__ void obs_tmem_ld(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
 }
 
-// Byte offset, inside a 128-row operand, of 16-byte chunk c16 (8 channels; 0..15) of row `row`:
-// the chunk's place within its 128-byte row is XORed with the row's place within its group of 8.
-__device__ __forceinline__ uint32_t obs_off(int row, int c16) {
-  return (uint32_t)((c16 >> 3) * OBS_PANEL + (row >> 3) * 1024 + (row & 7) * 128 + (((c16 & 7) ^ (row & 7)) << 4));
+// Byte offset, inside an operand of `panel` bytes per 64 channels, of 16-byte chunk c16 (8
+// channels; 0..15) of row `row`: rows of 128 bytes, the chunk's place within its row XORed with the
+// row's place within its group of 8.
+__device__ __forceinline__ uint32_t obs_off(int row, int c16, int panel) {
+  return (uint32_t)((c16 >> 3) * panel + row * 128 + (((c16 & 7) ^ (row & 7)) << 4));
 }
 
 // `rows` rows of 128 16-bit elements (row stride in elements) into operand rows row0.. of the
-// operand blocks at dst, by plain loads; rows >= rows_valid are zero-filled.
-__device__ __forceinline__ void obs_stage(unsigned char* dst, int row0, const uint16_t* src, int64_t row_stride, int rows,
-                                          int rows_valid, bool aligned) {
+// operand at dst, by plain loads; rows >= rows_valid are zero-filled.
+__device__ __forceinline__ void obs_stage(unsigned char* dst, int panel, int row0, const uint16_t* src, int64_t row_stride,
+                                          int rows, int rows_valid, bool aligned) {
   for (int i = threadIdx.x; i < rows * 16; i += OBS_THREADS) {
     const int row = i >> 4, c16 = i & 15;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -189,8 +192,7 @@ __device__ __forceinline__ void obs_stage(unsigned char* dst, int row0, const ui
         v = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
-    const int r = row0 + row;
-    *reinterpret_cast<uint4*>(dst + (size_t)(r >> 7) * OBS_BLOCK + obs_off(r & 127, c16)) = v;
+    *reinterpret_cast<uint4*>(dst + obs_off(row0 + row, c16, panel)) = v;
   }
 }
 
@@ -198,10 +200,12 @@ struct ObsArgs {
   const uint16_t* q; const uint16_t* k;
   int64_t q_head_stride, q_row_stride, k_head_stride, k_row_stride;   // elements
   int g, W, T, causal, n_tiles;
-  int BH, extra_rows;  // heads; rows of the second tile launch's grid that compute channel scores
+  int BH, P;           // heads; CTAs per head (CTA x of a head takes tiles x, x+P, ...)
+  int extra_rows;      // rows of the second pass's grid that compute channel scores
+  int n_pad;           // query rows rounded up to a multiple of 64: N of the second pass's MMAs
   int tma_q, tma_k;    // operands come through the tensor maps (else by plain loads)
-  float* part;         // [BH][2*n_tiles][R][2] half-tile maxima and sums
-  float* ksq;          // [BH][n_tiles][128] tile sums of k^2
+  float* part;         // [BH][2*P][R][2] maxima and sums per (CTA, half of a tile's keys)
+  float* ksq;          // [BH][P][128] sums of k^2 per CTA
   float* stats;        // [BH][R][2] maxima and sums over all keys
   float* token;        // [BH][T]
   float* channel;      // [BH][128]
@@ -209,8 +213,8 @@ struct ObsArgs {
 };
 
 // The channel score of KV head bh = mean(q^2) * mean_t(k^2), by one CTA of OBS_THREADS threads:
-// threads (half, channel) sum every other row / tile, the halves are added at the end.  Runs as an
-// extra CTA of the second tile launch (the tiles' k^2 sums come from the first).
+// threads (half, channel) sum every other row / CTA sum, the halves are added at the end.  Runs as
+// an extra CTA of the second pass (the k^2 sums come from the first).
 template <bool BF16>
 __device__ __forceinline__ void obs_channel_score(const ObsArgs& A, int bh, float* s_sum /* [4][128] */) {
   const int tid = threadIdx.x, c = tid & 127, half = tid >> 7, R = A.g * A.W;
@@ -222,39 +226,47 @@ __device__ __forceinline__ void obs_channel_score(const ObsArgs& A, int bh, floa
     qs = fmaf(x, x, qs);
   }
 #pragma unroll 16
-  for (int i = half; i < A.n_tiles; i += 2) ks += A.ksq[((int64_t)bh * A.n_tiles + i) * 128 + c];
+  for (int i = half; i < A.P; i += 2) ks += A.ksq[((int64_t)bh * A.P + i) * 128 + c];
   s_sum[half * 128 + c] = qs; s_sum[256 + half * 128 + c] = ks;
   __syncthreads();
   if (tid < 128)
     A.channel[(int64_t)bh * 128 + tid] = ((s_sum[tid] + s_sum[128 + tid]) / (float)R) * ((s_sum[256 + tid] + s_sum[384 + tid]) / (float)A.T);
 }
 
-// PASS 0: row statistics and k^2 sums of a tile.  PASS 1: token scores of a tile; the first
-// extra_rows rows of its grid (dispatched first) compute the heads' channel scores instead.
+// PASS 0: row statistics and k^2 sums.  PASS 1: token scores; the first extra_rows rows of its grid
+// (dispatched first) compute the heads' channel scores instead.
 template <bool BF16, int PASS>
-__global__ void __launch_bounds__(OBS_THREADS, 3)
-obs_tile_kernel(const ObsArgs A, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k) {
+__global__ void __launch_bounds__(OBS_THREADS, 2)
+obs_stream_kernel(const ObsArgs A, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k) {
   extern __shared__ unsigned char obs_raw[];
-  __shared__ __align__(8) uint64_t s_bar[2];                 // [0] operands landed, [1] products complete
+  __shared__ __align__(8) uint64_t s_bar[4];                 // [b] key buffer b has landed (the first time with the queries), [2+b] products into accumulator b complete
   __shared__ uint32_t s_tmem;                                // base of the CTA's tensor-memory columns
-  __shared__ float s_col[4 * OBS_KEYS];
+  __shared__ float s_col[4 * OBS_KEYS];                      // PASS 1: the two row halves' sums per key; channel CTAs: their partial sums
+  __shared__ __align__(16) float2 s_ci[OBS_MAX_ROWS];        // PASS 1: per query row (M * log2 e, 1 / L); (0, 0) past R
+  __shared__ __align__(16) int s_lim[OBS_MAX_ROWS];          // PASS 1: last key the row may see
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (PASS == 1 && (int)blockIdx.y < A.extra_rows) {        // the grid's first rows: one CTA per head for the channel scores
     const int head = blockIdx.y * gridDim.x + blockIdx.x;
     if (head < A.BH) obs_channel_score<BF16>(A, head, s_col);
     return;
   }
-  const int tile = blockIdx.x, bh = PASS == 1 ? (int)blockIdx.y - A.extra_rows : (int)blockIdx.y;
-  const int R = A.g * A.W, T = A.T, MB = (R + OBS_ROWS - 1) / OBS_ROWS;
-  const uint32_t raw32 = obs_smem(obs_raw), k32 = (raw32 + 1023u) & ~1023u, q32 = k32 + OBS_BLOCK;
-  unsigned char* s_k = obs_raw + (k32 - raw32);              // [128 keys] operand block, 1024-byte aligned
-  unsigned char* s_q = s_k + OBS_BLOCK;                      // [MB] operand blocks of query rows
-  const uint32_t bar_ld = obs_smem(&s_bar[0]), bar_mma = obs_smem(&s_bar[1]);
-  const int t0 = tile * OBS_KEYS, n_keys = min(OBS_KEYS, T - t0);
-  const uint32_t tmem_cols = MB == 1 ? 128u : 256u;          // one fp32 column per key and row block
+  const int cx = blockIdx.x, bh = PASS == 1 ? (int)blockIdx.y - A.extra_rows : (int)blockIdx.y;
+  const int R = A.g * A.W, T = A.T, MB = (R + OBS_ROWS - 1) / OBS_ROWS, P = A.P;
+  const int n_my = (A.n_tiles - cx + P - 1) / P;             // tiles cx, cx+P, ... (P <= n_tiles: at least one)
+  const int q_panel = MB * OBS_PANEL;                        // the queries: [MB*128 rows] x 64 channels, twice
+  const uint32_t raw32 = obs_smem(obs_raw), k32 = (raw32 + 1023u) & ~1023u, q32 = k32 + 2 * OBS_BLOCK;
+  unsigned char* s_k = obs_raw + (k32 - raw32);              // two key buffers of OBS_BLOCK bytes, 1024-byte aligned
+  unsigned char* s_q = s_k + 2 * OBS_BLOCK;
+  const uint32_t bar0 = obs_smem(&s_bar[0]);
+  // accumulator columns: PASS 0 one column per key and row block, PASS 1 one per (padded) query row; two accumulators
+  const uint32_t acc_cols = PASS == 0 ? (uint32_t)MB * OBS_KEYS : (A.n_pad <= 128 ? 128u : 256u);
+  const uint32_t tmem_cols = 2 * acc_cols;
+  const bool k_al = (A.k_row_stride & 7) == 0 && (A.k_head_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(A.k) & 15) == 0;
+  const uint16_t* k_head = A.k + bh * A.k_head_stride;
 
   if (tid == 0) {
-    obs_bar_init(bar_ld, 1); obs_bar_init(bar_mma, 1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) obs_bar_init(bar0 + 8 * i, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {                                           // this warp owns the tensor-memory allocation
@@ -262,192 +274,246 @@ obs_tile_kernel(const ObsArgs A, const __grid_constant__ CUtensorMap tm_q, const
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // rows past R of the last block are zeros; operands that do not come by TMA are staged here
-  for (int i = tid; i < (MB * OBS_ROWS - R) * 16; i += OBS_THREADS) {
-    const int r = R + (i >> 4);
-    *reinterpret_cast<uint4*>(s_q + (size_t)(r >> 7) * OBS_BLOCK + obs_off(r & 127, i & 15)) = make_uint4(0u, 0u, 0u, 0u);
-  }
-  if (!A.tma_k) {
-    const bool al = (A.k_row_stride & 7) == 0 && (A.k_head_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(A.k) & 15) == 0;
-    obs_stage(s_k, 0, A.k + bh * A.k_head_stride + (int64_t)t0 * A.k_row_stride, A.k_row_stride, OBS_KEYS, n_keys, al);
-  }
+  // query rows past R are zeros; operands that do not come by TMA are staged here (the first two key tiles)
+  for (int i = tid; i < (MB * OBS_ROWS - R) * 16; i += OBS_THREADS)
+    *reinterpret_cast<uint4*>(s_q + obs_off(R + (i >> 4), i & 15, q_panel)) = make_uint4(0u, 0u, 0u, 0u);
   if (!A.tma_q) {
     const bool al = (A.q_row_stride & 7) == 0 && (A.q_head_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(A.q) & 15) == 0;
     for (int gi = 0; gi < A.g; ++gi)                         // row gi*W + w = query head gi of the group, window position w
-      obs_stage(s_q, gi * A.W, A.q + ((int64_t)bh * A.g + gi) * A.q_head_stride, A.q_row_stride, A.W, A.W, al);
+      obs_stage(s_q, q_panel, gi * A.W, A.q + ((int64_t)bh * A.g + gi) * A.q_head_stride, A.q_row_stride, A.W, A.W, al);
   }
+  if (!A.tma_k)
+    for (int n = 0; n < min(n_my, 2); ++n) {
+      const int t0 = (cx + n * P) * OBS_KEYS;
+      obs_stage(s_k + n * OBS_BLOCK, OBS_PANEL, 0, k_head + (int64_t)t0 * A.k_row_stride, A.k_row_stride, OBS_KEYS,
+                min(OBS_KEYS, T - t0), k_al);
+    }
+  if (PASS == 1)
+    for (int r = tid; r < OBS_MAX_ROWS; r += OBS_THREADS) {
+      float2 ci = make_float2(0.f, 0.f);
+      if (r < R) {
+        const float2 ml = *reinterpret_cast<const float2*>(A.stats + ((int64_t)bh * R + r) * 2);
+        ci = make_float2(ml.x * OBS_LOG2E, __frcp_rn(ml.y));
+      }
+      s_ci[r] = ci;
+      s_lim[r] = A.causal ? T - A.W + (r % A.W) : T - 1;
+    }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the plain stores above, as the tensor cores will see them
   obs_fence_before();
   __syncthreads();
   obs_fence_after();
   const uint32_t tmem = s_tmem;
 
-  if (tid == 0) {
-    const uint32_t tx = (A.tma_k ? (uint32_t)OBS_BLOCK : 0u) + (A.tma_q ? (uint32_t)R * 256u : 0u);
-    if (tx != 0) {
-      obs_bar_arrive_tx(bar_ld, tx);
-      if (A.tma_k) {                                         // keys t0.. of head bh: two boxes of 64 channels (rows past T arrive as zeros)
-        obs_tma_3d(k32, &tm_k, 0, t0, bh, bar_ld);
-        obs_tma_3d(k32 + OBS_PANEL, &tm_k, 64, t0, bh, bar_ld);
-      }
-      if (A.tma_q)
-        for (int gi = 0; gi < A.g; ++gi) {                   // the W rows of query head gi (W is a multiple of 8 here and no box straddles two blocks)
-          const int r0 = gi * A.W;
-          const uint32_t dst = q32 + (uint32_t)(r0 >> 7) * OBS_BLOCK + (uint32_t)(r0 & 127) * 128u;
-          obs_tma_3d(dst, &tm_q, 0, 0, bh * A.g + gi, bar_ld);
-          obs_tma_3d(dst + OBS_PANEL, &tm_q, 64, 0, bh * A.g + gi, bar_ld);
-        }
-    } else {
-      obs_bar_arrive(bar_ld);
+  // thread 0: the copies of key tile n into buffer n & 1 (with the queries the first time), or the arrival that stands for them
+  auto load_tile = [&](int n, bool with_q) {
+    const uint32_t bar = bar0 + 8 * (n & 1);
+    const uint32_t tx = (A.tma_k ? (uint32_t)OBS_BLOCK : 0u) + (with_q && A.tma_q ? (uint32_t)R * 256u : 0u);
+    if (tx == 0) { obs_bar_arrive(bar); return; }
+    obs_bar_arrive_tx(bar, tx);
+    if (A.tma_k) {                                           // two boxes of 64 channels (rows past T arrive as zeros)
+      const uint32_t dst = k32 + (uint32_t)(n & 1) * OBS_BLOCK;
+      const int t0 = (cx + n * P) * OBS_KEYS;
+      obs_tma_3d(dst, &tm_k, 0, t0, bh, bar);
+      obs_tma_3d(dst + OBS_PANEL, &tm_k, 64, t0, bh, bar);
     }
-    if (obs_bar_wait(bar_ld, 0)) {
-      obs_fence_after();
-      constexpr uint32_t idesc = obs_idesc<BF16>();
+    if (with_q && A.tma_q)
+      for (int gi = 0; gi < A.g; ++gi) {                     // the W rows of query head gi (W is a multiple of 8 here)
+        const uint32_t dst = q32 + (uint32_t)(gi * A.W) * 128u;
+        obs_tma_3d(dst, &tm_q, 0, 0, bh * A.g + gi, bar);
+        obs_tma_3d(dst + (uint32_t)q_panel, &tm_q, 64, 0, bh * A.g + gi, bar);
+      }
+  };
+  // thread 0: once tile n's operands are there, its products into accumulator n & 1
+  auto issue_tile = [&](int n) {
+    const int b = n & 1;
+    if (!obs_bar_wait(bar0 + 8 * b, (uint32_t)(n >> 1) & 1u)) {
+      atomicOr(A.status, 1);
+      obs_bar_wait(bar0 + 8 * b, (uint32_t)(n >> 1) & 1u);   // (one more bounded wait for the copies in flight)
+      obs_bar_arrive(bar0 + 8 * (2 + b));
+      return;
+    }
+    obs_fence_after();
+    const uint32_t kb = k32 + (uint32_t)b * OBS_BLOCK, acc = tmem + (uint32_t)b * acc_cols;
+    if (PASS == 0) {                                         // S = Q.K^T per 128-row block
+      const uint32_t idesc = obs_idesc<BF16>(OBS_KEYS);
       for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {                     // 16 channels a step: 32 bytes along the swizzled row, the second panel after four
-          const uint32_t o = (uint32_t)(kk >> 2) * OBS_PANEL + (uint32_t)(kk & 3) * 32u;
-          obs_mma(tmem + (uint32_t)mb * OBS_KEYS, obs_desc(q32 + (uint32_t)mb * OBS_BLOCK + o), obs_desc(k32 + o), idesc,
-                  kk > 0 ? 1u : 0u);
-        }
-      obs_commit(bar_mma);
-    } else {                                                 // give the copies one more bounded wait, then let the others go on
-      atomicOr(A.status, 1);
-      obs_bar_wait(bar_ld, 0);
-      obs_bar_arrive(bar_mma);
+        for (int kk = 0; kk < 8; ++kk)                       // 16 channels a step: 32 bytes along the swizzled row, the second panel after four
+          obs_mma(acc + (uint32_t)mb * OBS_KEYS,
+                  obs_desc(q32 + (uint32_t)(kk >> 2) * q_panel + (uint32_t)mb * OBS_PANEL + (uint32_t)(kk & 3) * 32u),
+                  obs_desc(kb + (uint32_t)(kk >> 2) * OBS_PANEL + (uint32_t)(kk & 3) * 32u), idesc, kk > 0 ? 1u : 0u);
+    } else {                                                 // S^T = K.Q^T: all (padded) query rows at once
+      const uint32_t idesc = obs_idesc<BF16>(A.n_pad);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        obs_mma(acc, obs_desc(kb + (uint32_t)(kk >> 2) * OBS_PANEL + (uint32_t)(kk & 3) * 32u),
+                obs_desc(q32 + (uint32_t)(kk >> 2) * q_panel + (uint32_t)(kk & 3) * 32u), idesc, kk > 0 ? 1u : 0u);
     }
+    obs_commit(bar0 + 8 * (2 + b));
+  };
+
+  if (tid == 0) {
+    load_tile(0, true);
+    if (n_my > 1) load_tile(1, false);
+    issue_tile(0);
+  }
+
+  const int q4 = warp & 3, half = warp >> 2;
+  // PASS 0: a thread's rows (one per row block), their running statistics over this half of the keys; its share of k^2
+  float run_m[2] = {-INFINITY, -INFINITY}, run_l[2] = {0.f, 0.f};
+  float ksq_acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const int c16 = warp * 2 + (lane >> 4), rs = lane & 15;    // k^2: this thread's 16-byte chunk and set of keys
+
+#pragma unroll 1
+  for (int n = 0; n < n_my; ++n) {
+    const int b = n & 1, tile = cx + n * P, t0 = tile * OBS_KEYS, n_keys = min(OBS_KEYS, T - t0);
+    if (tid == 0 && !obs_bar_wait(bar0 + 8 * (2 + b), (uint32_t)(n >> 1) & 1u)) atomicOr(A.status, 2);
+    __syncthreads();                                         // tile n's products are complete (and everybody is done with tile n-1)
+    obs_fence_after();
+    if (tid == 0) {
+      // PASS 1 reads no keys from shared memory: buffer b is free now that tile n's products are done,
+      // and tile n+2 gets the whole of this tile's work to arrive
+      if (PASS == 1 && A.tma_k && n + 2 < n_my) load_tile(n + 2, false);
+      if (n + 1 < n_my) issue_tile(n + 1);                   // the other accumulator: its last readers passed the barrier above
+    }
+    // (only tiles that reach into the window or past the sequence's end have anything to mask)
+    const bool edge = t0 + OBS_KEYS > (A.causal ? T - A.W : T);
+    const uint32_t acc = tmem + (uint32_t)b * acc_cols + ((uint32_t)(q4 * 32) << 16);
+
+    if (PASS == 0) {
+      {
+        // k^2 of the tile.  Lanes 0-15 / 16-31 of warp w take the 16-byte chunk (8 channels) 2w / 2w+1 of
+        // keys rs, rs+16, ...; a quarter warp's loads fall on distinct banks.  (Rows past T are zeros.)
+        const unsigned char* src = s_k + b * OBS_BLOCK + obs_off(rs, c16, OBS_PANEL);
+#pragma unroll
+        for (int j = 0; j < OBS_KEYS / 16; ++j) {            // key j*16 + rs: two groups of 8 rows further each time
+          const uint4 v = *reinterpret_cast<const uint4*>(src + j * 2048);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 x = obs_unpack2<BF16>(w[e]);
+            ksq_acc[2 * e] = fmaf(x.x, x.x, ksq_acc[2 * e]); ksq_acc[2 * e + 1] = fmaf(x.y, x.y, ksq_acc[2 * e + 1]);
+          }
+        }
+      }
+      if (A.tma_k && n + 2 < n_my) {                         // the k^2 sums were the last readers of buffer b: tile n+2 may come
+        __syncthreads();
+        if (tid == 0) load_tile(n + 2, false);
+      }
+      auto stats = [&](auto edge_c) {                        // compiled once with and once without the masking
+        constexpr bool EDGE = decltype(edge_c)::value;
+#pragma unroll
+        for (int mb = 0; mb < 2; ++mb) {
+          const int row = mb * OBS_ROWS + q4 * 32 + lane;
+          if (mb >= MB || row - lane >= R) continue;         // (the whole warp)
+          const int lim = A.causal ? T - A.W + (row % A.W) : T - 1;   // last key this row may see
+          const int tk = t0 + half * 64;
+          float m = run_m[mb], l = run_l[mb];
+          // 32 keys at a time: the scores (as packed pairs), the row's maximum over them, one exponential each
+#pragma unroll 1
+          for (int ck = 0; ck < 2; ++ck) {
+            uint32_t v[32];
+            obs_tmem_ld(acc + (uint32_t)(mb * OBS_KEYS + half * 64 + ck * 32), v);
+            uint32_t h2 = BF16 ? 0xFF80FF80u : 0xFC00FC00u;  // (-inf, -inf)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              uint32_t s2 = obs_score2<BF16>(v[2 * i], v[2 * i + 1]);
+              if (EDGE) {
+                const int t = tk + ck * 32 + 2 * i;
+                if (t > lim) s2 = (s2 & 0xFFFF0000u) | (BF16 ? 0xFF80u : 0xFC00u);
+                if (t + 1 > lim) s2 = (s2 & 0x0000FFFFu) | (BF16 ? 0xFF800000u : 0xFC000000u);
+              }
+              v[i] = s2;
+              h2 = obs_max2<BF16>(h2, s2);
+            }
+            const float2 hh = obs_unpack2<BF16>(h2);
+            const float nm = fmaxf(m, fmaxf(hh.x, hh.y));
+            const float c = nm > -INFINITY ? nm * OBS_LOG2E : 0.f;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {                   // (2^-inf = 0: masked keys add nothing)
+              const float2 sc = obs_unpack2<BF16>(v[i]);
+              sum[(2 * i) & 3] += obs_ex2(fmaf(sc.x, OBS_LOG2E, -c));
+              sum[(2 * i + 1) & 3] += obs_ex2(fmaf(sc.y, OBS_LOG2E, -c));
+            }
+            l = (m > -INFINITY ? l * obs_ex2(fmaf(m, OBS_LOG2E, -c)) : 0.f) + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+            m = nm;
+          }
+          run_m[mb] = m; run_l[mb] = l;
+        }
+      };
+      if (edge) stats(std::true_type{});
+      else stats(std::false_type{});
+    } else {
+      // this thread's key against its half of the (padded) query rows, 32 at a time; the weights are
+      // rounded to the 16-bit type as the reference's softmax output is and summed inside the thread
+      const int t = t0 + q4 * 32 + lane, rows_half = A.n_pad >> 1;
+      float colsum = 0.f;
+      auto sums = [&](auto edge_c) {
+        constexpr bool EDGE = decltype(edge_c)::value;
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int r0 = half * rows_half; r0 < (half + 1) * rows_half; r0 += 32) {
+          uint32_t v[32];
+          obs_tmem_ld(acc + (uint32_t)r0, v);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float2 sc = obs_unpack2<BF16>(obs_score2<BF16>(v[i], v[i + 1]));
+            const float4 ci = *reinterpret_cast<const float4*>(&s_ci[r0 + i]);   // (all lanes the same address)
+            if (EDGE) {
+              const int2 lim = *reinterpret_cast<const int2*>(&s_lim[r0 + i]);
+              if (t > lim.x) sc.x = -INFINITY;
+              if (t > lim.y) sc.y = -INFINITY;
+            }
+            const float2 p = obs_unpack2<BF16>(obs_pack<BF16>(obs_ex2(fmaf(sc.x, OBS_LOG2E, -ci.x)) * ci.y,
+                                                              obs_ex2(fmaf(sc.y, OBS_LOG2E, -ci.z)) * ci.w));
+            a[(i >> 1) & 3] += p.x + p.y;
+          }
+        }
+        colsum = (a[0] + a[1]) + (a[2] + a[3]);
+      };
+      if (edge) sums(std::true_type{});
+      else sums(std::false_type{});
+      s_col[half * OBS_KEYS + q4 * 32 + lane] = colsum;
+    }
+    obs_fence_before();
+    __syncthreads();                                         // everybody is done with key buffer b and accumulator b
+    if (!A.tma_k && n + 2 < n_my) {                          // without TMA: tile n+2 into the buffer by plain loads, here
+      const int t2 = (cx + (n + 2) * P) * OBS_KEYS;
+      obs_stage(s_k + b * OBS_BLOCK, OBS_PANEL, 0, k_head + (int64_t)t2 * A.k_row_stride, A.k_row_stride, OBS_KEYS,
+                min(OBS_KEYS, T - t2), k_al);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (tid == 0) load_tile(n + 2, false);                 // (the arrival that stands for the copies; the products are issued after the next CTA barrier)
+    }
+    if (PASS == 1 && tid < n_keys)                           // (the reference's aw.sum(...) is in aw's type)
+      A.token[(int64_t)bh * T + t0 + tid] = obs_round<BF16>(s_col[tid] + s_col[OBS_KEYS + tid]);
   }
 
   if (PASS == 0) {
-    // k^2 of the tile.  Lanes 0-15 / 16-31 of warp w take the 16-byte chunk (8 channels) 2w / 2w+1 of
-    // keys rs, rs+16, ... (rs = lane & 15); a quarter warp's loads fall on distinct banks.  The 16
-    // lanes of a chunk then add up along a fixed tree.  (Rows past the tile's keys are zeros.)
-    obs_bar_wait(bar_ld, 0);
-    const int c16 = warp * 2 + (lane >> 4), rs = lane & 15;
-    const unsigned char* src = s_k + (c16 >> 3) * OBS_PANEL + (rs >> 3) * 1024 + (rs & 7) * 128 + (((c16 & 7) ^ (rs & 7)) << 4);
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < OBS_KEYS / 16; ++j) {                // key j*16 + rs: two groups of 8 rows further each time
-      const uint4 v = *reinterpret_cast<const uint4*>(src + j * 2048);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 x = obs_unpack2<BF16>(w[e]);
-        acc[2 * e] = fmaf(x.x, x.x, acc[2 * e]); acc[2 * e + 1] = fmaf(x.y, x.y, acc[2 * e + 1]);
-      }
+    for (int mb = 0; mb < 2; ++mb) {
+      const int row = mb * OBS_ROWS + q4 * 32 + lane;
+      if (mb < MB && row < R)
+        *reinterpret_cast<float2*>(A.part + ((((int64_t)bh * P + cx) * 2 + half) * R + row) * 2) = make_float2(run_m[mb], run_l[mb]);
     }
+    // the 16 lanes of a chunk add their k^2 up along a fixed tree
 #pragma unroll
     for (int o = 1; o < 16; o <<= 1)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+      for (int e = 0; e < 8; ++e) ksq_acc[e] += __shfl_xor_sync(0xffffffffu, ksq_acc[e], o);
     if (rs == 0) {
-      float4* dst = reinterpret_cast<float4*>(A.ksq + ((int64_t)bh * A.n_tiles + tile) * 128 + c16 * 8);
-      dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]); dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      float4* dst = reinterpret_cast<float4*>(A.ksq + ((int64_t)bh * P + cx) * 128 + c16 * 8);
+      dst[0] = make_float4(ksq_acc[0], ksq_acc[1], ksq_acc[2], ksq_acc[3]);
+      dst[1] = make_float4(ksq_acc[4], ksq_acc[5], ksq_acc[6], ksq_acc[7]);
     }
   }
-
-  if (!obs_bar_wait(bar_mma, 0) && lane == 0) atomicOr(A.status, 2);
-  __syncwarp();
-  obs_fence_after();
-  const int q4 = warp & 3, half = warp >> 2;
-  // (only tiles that reach into the window or past the sequence's end have anything to mask)
-  const bool edge = t0 + OBS_KEYS > (A.causal ? T - A.W : T);
-  uint32_t* s_p = reinterpret_cast<uint32_t*>(s_k);          // PASS 1: [R][OBS_P_LD] pairs of weights, over the spent operands
-  // the tile's epilogue, compiled once with and once without the masking
-  auto epilogue = [&](auto edge_c) {
-    constexpr bool EDGE = decltype(edge_c)::value;
-    for (int mb = 0; mb < MB; ++mb) {
-      const int row = mb * OBS_ROWS + q4 * 32 + lane;
-      if (row - lane >= R) continue;                           // (the whole warp)
-      const int lim = A.causal ? T - A.W + (row % A.W) : T - 1;   // last key this row may see
-      const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(mb * OBS_KEYS + half * 64);
-      const int tk = t0 + half * 64;
-      if (PASS == 0) {
-        // 32 keys at a time: the scores (as packed pairs), the row's maximum over them, one exponential
-        // each; the chunks merge like tiles
-        float m = -INFINITY, l = 0.f;
-  #pragma unroll 1
-        for (int ck = 0; ck < 2; ++ck) {
-          uint32_t v[32];
-          obs_tmem_ld(taddr + (uint32_t)ck * 32u, v);
-          uint32_t h2 = BF16 ? 0xFF80FF80u : 0xFC00FC00u;      // (-inf, -inf)
-  #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            uint32_t s2 = obs_score2<BF16>(v[2 * i], v[2 * i + 1]);
-            if (EDGE) {                                        // (per CTA: only the last tiles mask anything)
-              const int t = tk + ck * 32 + 2 * i;
-              if (t > lim) s2 = (s2 & 0xFFFF0000u) | (BF16 ? 0xFF80u : 0xFC00u);
-              if (t + 1 > lim) s2 = (s2 & 0x0000FFFFu) | (BF16 ? 0xFF800000u : 0xFC000000u);
-            }
-            v[i] = s2;
-            h2 = obs_max2<BF16>(h2, s2);
-          }
-          const float2 hh = obs_unpack2<BF16>(h2);
-          const float n = fmaxf(m, fmaxf(hh.x, hh.y));
-          const float c = n > -INFINITY ? n * OBS_LOG2E : 0.f;
-          float sum[4] = {0.f, 0.f, 0.f, 0.f};
-  #pragma unroll
-          for (int i = 0; i < 16; ++i) {                       // (2^-inf = 0: masked keys add nothing)
-            const float2 sc = obs_unpack2<BF16>(v[i]);
-            sum[(2 * i) & 3] += obs_ex2(fmaf(sc.x, OBS_LOG2E, -c));
-            sum[(2 * i + 1) & 3] += obs_ex2(fmaf(sc.y, OBS_LOG2E, -c));
-          }
-          l = (m > -INFINITY ? l * obs_ex2(fmaf(m, OBS_LOG2E, -c)) : 0.f) + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
-          m = n;
-        }
-        if (row < R)
-          *reinterpret_cast<float2*>(A.part + ((((int64_t)bh * A.n_tiles + tile) * 2 + half) * R + row) * 2) = make_float2(m, l);
-      } else {
-        const float* st = A.stats + ((int64_t)bh * R + min(row, R - 1)) * 2;
-        const float cM = st[0] * OBS_LOG2E, inv = __frcp_rn(st[1]);
-        uint32_t* prow = s_p + (size_t)min(row, R - 1) * OBS_P_LD + half * 32;
-  #pragma unroll 1
-        for (int ck = 0; ck < 2; ++ck) {
-          uint32_t v[32];
-          obs_tmem_ld(taddr + (uint32_t)ck * 32u, v);
-  #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float2 sc = obs_unpack2<BF16>(obs_score2<BF16>(v[i], v[i + 1]));
-            if (EDGE) {
-              if (tk + ck * 32 + i > lim) sc.x = -INFINITY;
-              if (tk + ck * 32 + i + 1 > lim) sc.y = -INFINITY;
-            }
-            // p = exp(s - M) / L in fp32, rounded to the 16-bit type as the reference's softmax output is
-            const uint32_t pp = obs_pack<BF16>(obs_ex2(fmaf(sc.x, OBS_LOG2E, -cM)) * inv, obs_ex2(fmaf(sc.y, OBS_LOG2E, -cM)) * inv);
-            if (row < R) prow[ck * 16 + (i >> 1)] = pp;
-          }
-        }
-      }
-    }
-  };
-  if (edge) epilogue(std::true_type{});
-  else epilogue(std::false_type{});
-  obs_fence_before();
-  __syncthreads();
+  // (the loop's last barrier came after every read of tensor memory)
   if (warp == 1)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
-  if (PASS == 1) {
-    // column sums: thread = (quarter of the rows, pair of keys), rows in order; then the quarters in order
-    const int cp = tid & 63, qtr = tid >> 6, per = MB * 32;
-    const int r_end = min(R, (qtr + 1) * per);
-    float a0 = 0.f, a1 = 0.f;
-#pragma unroll 4
-    for (int r = qtr * per; r < r_end; ++r) {
-      const uint32_t w = s_p[(size_t)r * OBS_P_LD + cp];
-      const float2 p = obs_unpack2<BF16>(w);
-      a0 += p.x; a1 += p.y;
-    }
-    s_col[qtr * OBS_KEYS + 2 * cp] = a0; s_col[qtr * OBS_KEYS + 2 * cp + 1] = a1;
-    __syncthreads();
-    if (tid < n_keys) {
-      const float v = ((s_col[tid] + s_col[OBS_KEYS + tid]) + s_col[2 * OBS_KEYS + tid]) + s_col[3 * OBS_KEYS + tid];
-      A.token[(int64_t)bh * T + t0 + tid] = obs_round<BF16>(v);      // (the reference's aw.sum(...) is in aw's type)
-    }
-  }
 }
 
-// The rows' maxima and sums over all half tiles.  A CTA takes 8 rows of a head: thread (slice, row)
-// merges every 64th half tile of its row (a warp's loads cover 4 slices x 8 rows = 4 runs of 64
+// The rows' maxima and sums over the first pass's CTAs.  A CTA takes 8 rows of a head: thread (slice, row)
+// merges every 64th partial result of its row (a warp's loads cover 4 slices x 8 rows = 4 runs of 64
 // bytes), the 64 slices of a row are then merged by one warp along a fixed tree.
 constexpr int OBS_RED_ROWS = 8;
 constexpr int OBS_RED_SLICES = 64;
@@ -463,7 +529,7 @@ __global__ void __launch_bounds__(OBS_RED_THREADS)
 obs_reduce_kernel(ObsArgs A) {
   __shared__ float2 s_ml[OBS_RED_SLICES][OBS_RED_ROWS];
   const int bh = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int R = A.g * A.W, n_parts = 2 * A.n_tiles;
+  const int R = A.g * A.W, n_parts = 2 * A.P;
   const int r = tid & (OBS_RED_ROWS - 1), slice = tid / OBS_RED_ROWS;
   const int row = blockIdx.x * OBS_RED_ROWS + r;
   float M = -INFINITY, L = 0.f;
@@ -543,7 +609,7 @@ using namespace rdkv;
 
 extern "C" int64_t rdkv_obs_scratch_words(int BH, int g, int W, int T) {
   if (BH < 0 || g <= 0 || W <= 0 || T <= 0) return 0;
-  const int64_t n_tiles = (T + OBS_KEYS - 1) / OBS_KEYS, R = (int64_t)g * W;
+  const int64_t n_tiles = (T + OBS_KEYS - 1) / OBS_KEYS, R = (int64_t)g * W;   // (sized for one CTA per tile; fewer run)
   return BH * (2 * n_tiles * R * 2 + n_tiles * 128 + R * 2) + 1;
 }
 
@@ -559,43 +625,49 @@ extern "C" int rdkv_obs_scores(const void* q_obs, const void* k, int dtype, int6
   if (BH == 0) return RDKV_OK;
   if (BH > 65000) return RDKV_ERR_TOO_LARGE;
   const bool bf = dtype == RDKV_BF16;
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess || sms <= 0) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
   ObsArgs A;
   A.q = reinterpret_cast<const uint16_t*>(q_obs); A.k = reinterpret_cast<const uint16_t*>(k);
   A.q_head_stride = q_head_stride; A.q_row_stride = q_row_stride; A.k_head_stride = k_head_stride; A.k_row_stride = k_row_stride;
   A.g = g; A.W = W; A.T = T; A.causal = causal ? 1 : 0; A.n_tiles = (T + OBS_KEYS - 1) / OBS_KEYS;
-  A.BH = BH; A.extra_rows = (BH + A.n_tiles - 1) / A.n_tiles;
   const int64_t R = (int64_t)g * W;
   const int MB = (int)((R + OBS_ROWS - 1) / OBS_ROWS);
+  // CTAs per head: the resident CTAs (two per SM with one row block, one with two) shared out over the heads
+  const int slots = sms * (MB == 1 ? 2 : 1);
+  A.BH = BH; A.P = std::min(A.n_tiles, std::max(1, slots / BH));
+  A.extra_rows = (BH + A.P - 1) / A.P;
+  A.n_pad = (int)((R + 63) / 64) * 64;
   A.part = scratch;
   A.ksq = A.part + (int64_t)BH * 2 * A.n_tiles * R * 2;
   A.stats = A.ksq + (int64_t)BH * A.n_tiles * 128;
   A.status = reinterpret_cast<int*>(A.stats + (int64_t)BH * R * 2);
   A.token = layer_token; A.channel = layer_channel;
   // the operands come by TMA when their layout can be mapped; a head's W query rows are one box,
-  // which must start on a group of 8 rows and stay inside one 128-row block
+  // which must start on a group of 8 rows
   CUtensorMap tm_q, tm_k;
   memset(&tm_q, 0, sizeof(tm_q)); memset(&tm_k, 0, sizeof(tm_k));
   A.tma_k = obs_map(&tm_k, k, bf, k_head_stride, k_row_stride, BH, T, OBS_KEYS) ? 1 : 0;
-  A.tma_q = (W % 8 == 0 && (R <= OBS_ROWS || OBS_ROWS % W == 0) &&
-             obs_map(&tm_q, q_obs, bf, q_head_stride, q_row_stride, (int64_t)BH * g, W, W)) ? 1 : 0;
-  const size_t smem = 1024 + (size_t)(1 + MB) * OBS_BLOCK;   // (the base is rounded up to 1024 bytes in the kernel)
+  A.tma_q = (W % 8 == 0 && obs_map(&tm_q, q_obs, bf, q_head_stride, q_row_stride, (int64_t)BH * g, W, W)) ? 1 : 0;
+  const size_t smem = 1024 + (size_t)(2 + MB) * OBS_BLOCK;   // (the base is rounded up to 1024 bytes in the kernel)
   cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t e = cudaMemsetAsync(A.status, 0, sizeof(int), st);
+  e = cudaMemsetAsync(A.status, 0, sizeof(int), st);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
-  const dim3 grid(A.n_tiles, BH);
-  auto launch = [&](auto kern_stats, auto kern_reduce, auto kern_token) -> int {
+  auto launch = [&](auto kern_stats, auto kern_token) -> int {
     cudaError_t e = cudaFuncSetAttribute(kern_stats, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kern_token, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { g_last_cuda_error = (int)e; return RDKV_ERR_LAUNCH; }
-    kern_stats<<<grid, OBS_THREADS, smem, st>>>(A, tm_q, tm_k);
+    kern_stats<<<dim3(A.P, BH), OBS_THREADS, smem, st>>>(A, tm_q, tm_k);
     int rc = launch_status();
     if (rc != RDKV_OK) return rc;
-    kern_reduce<<<dim3((unsigned)((R + OBS_RED_ROWS - 1) / OBS_RED_ROWS), BH), OBS_RED_THREADS, 0, st>>>(A);
+    obs_reduce_kernel<<<dim3((unsigned)((R + OBS_RED_ROWS - 1) / OBS_RED_ROWS), BH), OBS_RED_THREADS, 0, st>>>(A);
     rc = launch_status();
     if (rc != RDKV_OK) return rc;
-    kern_token<<<dim3(A.n_tiles, BH + A.extra_rows), OBS_THREADS, smem, st>>>(A, tm_q, tm_k);
+    kern_token<<<dim3(A.P, BH + A.extra_rows), OBS_THREADS, smem, st>>>(A, tm_q, tm_k);
     return launch_status();
   };
-  if (bf) return launch(obs_tile_kernel<true, 0>, obs_reduce_kernel, obs_tile_kernel<true, 1>);
-  return launch(obs_tile_kernel<false, 0>, obs_reduce_kernel, obs_tile_kernel<false, 1>);
+  if (bf) return launch(obs_stream_kernel<true, 0>, obs_stream_kernel<true, 1>);
+  return launch(obs_stream_kernel<false, 0>, obs_stream_kernel<false, 1>);
 }

@@ -93,22 +93,25 @@ def test_obs_window_scores_at_full_size_against_the_two_step_path():
     torch.testing.assert_close(ch, want_ch, rtol=1e-5, atol=1e-8)
 
 
-@pytest.mark.parametrize("gq,W,T,dt,causal,k_pad", [
-    (8, 32, 700, torch.float16, True, 0),      # 256 rows: two accumulator blocks, operands by TMA
-    (8, 32, 513, torch.bfloat16, True, 0),
-    (3, 20, 450, torch.float16, True, 0),      # window not a multiple of 8: queries staged by plain loads
-    (5, 48, 300, torch.bfloat16, True, 0),     # a head's rows would straddle the two blocks: plain loads
-    (2, 24, 257, torch.float16, False, 0),     # 48 rows (zero rows up to 128), no mask
-    (4, 32, 1000, torch.bfloat16, True, 4),    # key rows 132 elements apart: keys staged by unaligned plain loads
-    (4, 32, 640, torch.float16, True, 8),      # key rows 136 elements apart: still a valid tensor map
-    (1, 1, 1, torch.float16, True, 0),
+@pytest.mark.parametrize("B,H,gq,W,T,dt,causal,k_pad", [
+    (2, 3, 8, 32, 700, torch.float16, True, 0),      # 256 rows: two row blocks in the first pass, 256 columns in the second
+    (2, 3, 8, 32, 513, torch.bfloat16, True, 0),
+    (2, 3, 3, 20, 450, torch.float16, True, 0),      # window not a multiple of 8: queries staged by plain loads
+    (2, 3, 5, 48, 300, torch.bfloat16, True, 0),     # 240 rows, a head's rows straddle the two row blocks
+    (2, 3, 2, 24, 257, torch.float16, False, 0),     # 48 rows (zero rows up to 64 / 128), no mask
+    (2, 3, 4, 32, 1000, torch.bfloat16, True, 4),    # key rows 132 elements apart: keys staged by unaligned plain loads
+    (2, 3, 4, 32, 640, torch.float16, True, 8),      # key rows 136 elements apart: still a valid tensor map
+    (1, 40, 4, 32, 3000, torch.float16, True, 0),    # many heads: few CTAs per head, each streams 3-4 tiles through the ring
+    (1, 40, 2, 32, 3000, torch.bfloat16, False, 4),  # the same with keys staged by plain loads
+    (1, 20, 8, 32, 2500, torch.float16, True, 0),    # two row blocks, several tiles per CTA
+    (1, 1, 1, 1, 1, torch.float16, True, 0),
 ])
-def test_obs_window_scores_over_shapes_and_layouts(gq, W, T, dt, causal, k_pad):
+def test_obs_window_scores_over_shapes_and_layouts(B, H, gq, W, T, dt, causal, k_pad):
     """Both ways the operands reach shared memory (tensor maps / plain loads), one and two row
-    blocks, ragged last tiles: against torch's matmul + softmax and _score_one_layer on the device."""
+    blocks, ragged last tiles, one and several tiles per CTA: against torch's matmul + softmax and
+    _score_one_layer on the device."""
     from rdkv_b200.scoring import _score_one_layer, obs_window_scores
     gen = torch.Generator(device="cuda").manual_seed(gq * 1000 + W + T)
-    B, H = 2, 3
     q = torch.randn(B, H * gq, W, 128, device="cuda", generator=gen).to(dt)
     k_store = (torch.randn(B, H, T, 128 + k_pad, device="cuda", generator=gen) * 0.6).to(dt)
     k = k_store[..., :128]
