@@ -382,7 +382,12 @@ int rdkv_tail_attn_partial(const void* q, int q_dtype, int64_t n_views, int H_q,
  * W window positions x 128 (q_head_stride, q_row_stride in elements; KV head bh owns query heads
  * bh*g .. bh*g+g-1), k: [BH][T][128]; dtype RDKV_F16 or RDKV_BF16 for both; causal: window position
  * w sees keys <= T-W+w.  g*W <= 256.  scratch: rdkv_obs_scratch_words(BH, g, W, T) 4-byte words.
- * Three launches (tile statistics, reduction, token sums); the keys are read twice. */
+ * Three launches (row statistics, reduction, token sums); the keys are read twice.  The products run
+ * on the tensor cores (tcgen05.mma into tensor memory); the operands are staged by tiled TMA when the
+ * base addresses are 16-byte aligned, the strides multiples of 8 elements and W a multiple of 8, by
+ * plain loads otherwise (same results).  The device code waits on mbarriers with a limit: the last
+ * word of scratch, read as an int after the stream has drained, is 0 if no wait ran out (bit 0: the
+ * staged operands did not arrive, bit 1: the products did not complete; the scores are then invalid). */
 int64_t rdkv_obs_scratch_words(int BH, int g, int W, int T);
 int rdkv_obs_scores(const void* q_obs, const void* k, int dtype, int64_t q_head_stride, int64_t q_row_stride,
                     int64_t k_head_stride, int64_t k_row_stride, int BH, int g, int W, int T, int causal,
