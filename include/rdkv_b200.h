@@ -267,7 +267,24 @@ int rdkv_decode_attn_persistent(const rdkv_layer_view* views, int n_views, const
 int rdkv_decode_k_blocks(int n_ch2_pad, int n_ch4_pad, int n_ch8);
 int64_t rdkv_decode_prepared_bytes(int64_t n_units, int nkb_max, int which);
 int rdkv_decode_prepare(const rdkv_layer_view* views, int n_views, int H_kv, int nkb_max, void* unit_recs,
-                        void* k_slots, void* stream);
+                        void* k_slots, const void* v_maps, void* stream);
+/* Tensor maps of the views' V tensors (new; no counterpart in the reference).  With them the fused
+ * kernel brings a tile's V rows into shared memory as one tiled TMA box per tile whose inner extent
+ * is 16 bytes wider than a row (the excess arrives as zeros), so that the rows sit 48 / 80 / 144 /
+ * 272 bytes apart and the four rows a quad of threads reads together fall on distinct banks;
+ * without them (v_maps == NULL, or a phase whose map could not be encoded: base not 16-byte
+ * aligned, empty tensor) the staging warp places the rows at the same pitch with 16-byte copies.
+ *   rdkv_decode_v_map_bytes(n_views): size of the map block, 4 maps of 128 bytes per view (2-bit,
+ *     4-bit, 8-bit, fp16 rows);
+ *   rdkv_decode_encode_v_maps(views_host, n_views, maps_host): HOST call: encodes the maps of
+ *     n_views view records held in host memory (their v2 / v4 / v8 / v16 pointers and byte
+ *     counts) into maps_host; returns the number of maps encoded (the others are all zero), or -1
+ *     on bad arguments.  The caller copies the block to device memory (64-byte aligned) and hands
+ *     it to rdkv_decode_prepare as v_maps, which records per (view, KV head, phase) the map and the
+ *     row number of the head's first row.  The block must stay alive and unchanged as long as the
+ *     table is used; a table whose V tensors move is encoded and prepared again. */
+int64_t rdkv_decode_v_map_bytes(int n_views);
+int rdkv_decode_encode_v_maps(const rdkv_layer_view* views_host, int n_views, void* maps_host);
 
 /* Log-sum-exp merge of split-sequence partials (new; the reference has no
  * split path — it is the combine step of the fused call above and of the

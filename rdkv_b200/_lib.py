@@ -97,7 +97,9 @@ _PROTOTYPES = {
     "rdkv_decode_attn_partial": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p], _i),
     "rdkv_decode_k_blocks": ([_i, _i, _i], _i),
     "rdkv_decode_prepared_bytes": ([_i64, _i, _i], _i64),
-    "rdkv_decode_prepare": ([_p, _i, _i, _i, _p, _p, _p], _i),
+    "rdkv_decode_prepare": ([_p, _i, _i, _i, _p, _p, _p, _p], _i),
+    "rdkv_decode_v_map_bytes": ([_i], _i64),
+    "rdkv_decode_encode_v_maps": ([_p, _i, _p], _i),
     "rdkv_decode_attn": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p], _i),
     "rdkv_decode_attn_tail": ([_p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p], _i),
     "rdkv_rope": ([_p, _i, _i, _i64, _p, _i, _i, _i64, _p, _p, _i, _p], _i),

@@ -14,6 +14,9 @@
 // Probabilities never leave registers.  Zero points are handled outside the products:
 // sum_c zp*q*scale once per CTA (K side, reference "bias trick",
 // obkv_accel/triton_k_kernel.py:14-16) and sum_t p*scale*zp per head (V side).
+#include <cuda.h>   // CUtensorMap (the V tiles arrive through tensor maps; the encoder is looked up through the runtime)
+
+#include <cstring>
 #include <type_traits>
 
 #include "rdkv_common.cuh"
@@ -36,7 +39,11 @@ constexpr int FW = RDKV_FW;            // consumer (compute) warps per CTA; one 
 constexpr int CTA_THREADS = (FW + 1) * 32;
 constexpr int FSTAGES = RDKV_FSTAGES;  // ring depth
 constexpr int TILE_MAX = RDKV_TILE_ROWS;           // rows per tile (2-bit and 4-bit phases)
-constexpr int V_STAGE = 64 * TILE_MAX;             // V payload bytes per stage
+constexpr int V_PAD = 16;                          // bytes between V rows in a stage: rows 2j of a group fall on distinct banks
+#ifndef RDKV_V_STAGE_PER_ROW
+#define RDKV_V_STAGE_PER_ROW 72
+#endif
+constexpr int V_STAGE = RDKV_V_STAGE_PER_ROW * TILE_MAX;   // V payload bytes per stage (the 8-bit phase: TILE_MAX / 2 rows of 128 + 16 bytes)
 constexpr int GH = 8;                  // query heads per CTA pass (N of the P.V product)
 #ifndef RDKV_KB_MAX
 #define RDKV_KB_MAX 24
@@ -64,8 +71,23 @@ __host__ __device__ constexpr int phase_tile_rows(int p) {
   return p < 2 ? TILE_MAX : p == 2 ? TILE_MAX / 2 : p == 3 ? TILE_MAX / 4 : TILE_MAX / 8;
 }
 __host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : p == 1 ? 64 : p == 2 ? 128 : 256; }
+// Distance of consecutive V rows in a stage.  A thread of the P.V product reads the same bytes of
+// rows 2j (j = its place in its quad): with rows of 32 .. 256 bytes laid end to end the four rows
+// of a quad would share their banks; 16 bytes more per row puts them 32 bytes apart modulo 128.
+// (The tail's plain rows keep their 256 bytes.)
+#ifndef RDKV_V_PAD_FROM
+#define RDKV_V_PAD_FROM 2
+#endif
+constexpr int V_PAD_FROM = RDKV_V_PAD_FROM;        // first V phase whose rows are spaced (the phases before it lie end to end)
+__host__ __device__ constexpr int phase_pitch(int p) {
+  return (p == 4 || p < V_PAD_FROM) ? phase_row_bytes(p) : phase_row_bytes(p) + V_PAD;
+}
+static_assert(phase_tile_rows(0) * phase_pitch(0) <= V_STAGE && phase_tile_rows(1) * phase_pitch(1) <= V_STAGE &&
+              phase_tile_rows(2) * phase_pitch(2) <= V_STAGE && phase_tile_rows(3) * phase_pitch(3) <= V_STAGE,
+              "a tile's V rows fit the V area at their padded pitch");
 
 __host__ __device__ inline int align16i(int x) { return (x + 15) & ~15; }
+__host__ __device__ inline int align128i(int x) { return (x + 127) & ~127; }
 
 struct StageLayout {                   // byte offsets inside one stage
   int v, k2, k4, k8, sc, zp, total;
@@ -122,6 +144,13 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+               : "memory");
+}
+// One box of a 2-D tensor map (x in elements of the map's type, y = row) into shared memory (128-byte
+// aligned), counted in bytes on `bar` like a bulk copy; rows and columns past the tensor arrive as zeros.
+__device__ __forceinline__ void tma_g2s_2d(uint32_t dst, const void* map, int x, int y, uint64_t* bar, uint64_t pol) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(pol)
                : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_on_copies(uint64_t* bar) {
@@ -285,13 +314,14 @@ __device__ inline int k_slot(const KDims& d, int kb, int j, int e, float* factor
 // does every sub-range a chunk may take), and per V phase where its rows start in every tensor, so
 // that a chunk's geometry is a few integer operations on one record.  16-byte aligned.
 struct __align__(16) PhaseRec {                 // one V phase (2-bit, 4-bit, 8-bit, fp16 rows) of the head
-  int b_lo, b_hi, pad0, pad1;                    // its live-row range
+  int b_lo, b_hi, v_row, pad1;                   // its live-row range; row b_lo's number in the phase's tensor map (-1: no map)
   const unsigned char *k2, *k4, *k8, *vrow, *sc, *zp;   // addresses of row b_lo in the K streams, the V tensor, V scale / zero point
 };
 struct __align__(16) UnitRec {
   int n2, n4, n8, n16;
   int flags, nkb, n_ch2_pad, n_ch4_pad;
-  int n_ch8, max_t_v, pad0, pad1;
+  int n_ch8, max_t_v;
+  unsigned vmaps_lo, vmaps_hi;                   // the view's four tensor maps (128 bytes each, by phase), or 0
   PhaseRec ph[4];
 };
 static_assert(sizeof(PhaseRec) == 64 && sizeof(UnitRec) == 304, "prepared-table records are read as int4 words");
@@ -322,6 +352,8 @@ struct CtaGeom {
   const unsigned char* k4[4];
   const unsigned char* k8[4];
   const unsigned char* vrow[5];        // address of the V row of live row lo[p]
+  int vrow_idx[4];                     // its row number in the phase's tensor map, or -1
+  const unsigned char* vmaps;          // the view's four tensor maps (by phase), or null
   const unsigned char* krow_tail;      // address of the plain K row of tail row lo[4]
   const unsigned char* sc[3];
   const unsigned char* zp[3];
@@ -382,6 +414,28 @@ __device__ __noinline__ void stage_range_guarded(unsigned char* dst_ptr, const u
       if (th > lo) cp16_partial(dst + 16 * b, reinterpret_cast<const void*>(lo), (int)(th - lo));
     } else {
       cp16(dst + 16 * b, reinterpret_cast<const void*>(lo));
+    }
+  }
+}
+
+// V rows of a tile into a stage at their padded pitch by the lanes of the staging warp (what a
+// tensor map does in one instruction when the table has one): 16-byte copies when the rows are
+// aligned, bytes otherwise.  The rows lie inside their tensor.
+__device__ __noinline__ void stage_v_rows_padded(unsigned char* dst_ptr, const unsigned char* src, int n_rows, int row_bytes,
+                                                 int pitch, int lane) {
+  if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const int per = row_bytes >> 4;
+    const uint32_t dst = smem_u32(dst_ptr);
+#pragma unroll 1
+    for (int b = lane; b < n_rows * per; b += 32) {
+      const int row = b / per, c = b - row * per;
+      cp16(dst + row * pitch + 16 * c, src + 16 * (int64_t)b);
+    }
+  } else {
+#pragma unroll 1
+    for (int x = lane; x < n_rows * row_bytes; x += 32) {
+      const int row = x / row_bytes;
+      dst_ptr[row * pitch + (x - row * row_bytes)] = src[x];
     }
   }
 }
@@ -665,9 +719,11 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           G.k4[p] = ptr_of(a1.z, a1.w) + (int64_t)d * kq.sub4;
           G.k8[p] = ptr_of(a2.x, a2.y) + (int64_t)d * kq.n8;
           G.vrow[p] = ptr_of(a2.z, a2.w) + (int64_t)d * phase_row_bytes(p);
+          G.vrow_idx[p] = a0.z >= 0 ? a0.z + d : -1;
           if (p < 3) { G.sc[p] = ptr_of(a3.x, a3.y) + 2 * d; G.zp[p] = ptr_of(a3.z, a3.w) + 2 * d; }
         }
         if (lane == 0) {
+          G.vmaps = ptr_of(h2.z, h2.w);
           G.fast = 1;
           G.first_tile[NPH] = fits_q ? t0 + t1 + t2 + t3 + t4 : -1;
         }
@@ -805,9 +861,11 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       G.first_tile[p] = p == 0 ? 0 : p == 1 ? t0 : p == 2 ? t0 + t1 : t0 + t1 + t2;
       G.krow[p] = krow;
       G.k2[p] = gk2; G.k4[p] = gk4; G.k8[p] = gk8; G.vrow[p] = vb;
+      G.vrow_idx[p] = -1;
       if (p < 3) { G.sc[p] = gsc; G.zp[p] = gzp; }
     }
     if (lane == 0) {
+      G.vmaps = nullptr;
       G.fast = fast ? 1 : 0;
       G.first_tile[NPH] = (!fits || (MODE != MODE_SCORES && hc.n16 > 0 && v.v16 == nullptr)) ? -1 : t0 + t1 + t2 + t3 + t4;
     }
@@ -1027,7 +1085,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           const unsigned char* a_v = G.vrow[p] + (int64_t)t.row0 * phase_row_bytes(p);
           const unsigned char* a_sc = G.sc[p < 3 ? p : 0] + t.row0 * 2;
           const unsigned char* a_zp = G.zp[p < 3 ? p : 0] + t.row0 * 2;
-          P.rg[0] = RangePlan{a_v, MODE == MODE_SCORES ? 0 : t.n * phase_row_bytes(p), (uint32_t)SL.v};
+          // the V rows: one box of the phase's tensor map (src = the map, len = the box's bytes, dst_off = its
+          // first row) when the table has maps, else copies by the lanes at the padded pitch
+          // (a ragged last fp16 block goes that way too: the rows behind it are cleared)
+          const bool v_any = MODE != MODE_SCORES && t.n > 0;
+          const bool v_tma = v_any && p >= V_PAD_FROM && fast && G.vmaps != nullptr && G.vrow_idx[p] >= 0 && (p < 3 || (t.n & 31) == 0);
+          if (v_tma) P.rg[0] = RangePlan{G.vmaps + 128 * p, phase_tile_rows(p) * phase_pitch(p), (uint32_t)(G.vrow_idx[p] + t.row0)};
+          else P.rg[0] = RangePlan{a_v, v_any ? t.n * phase_row_bytes(p) : 0, (uint32_t)SL.v};
           P.rg[1] = RangePlan{a_k2, MODE == MODE_WEIGHTS ? 0 : t.n * kd.sub2, (uint32_t)SL.k2};
           P.rg[2] = RangePlan{a_k4, MODE == MODE_WEIGHTS ? 0 : t.n * kd.sub4, (uint32_t)SL.k4};
           P.rg[3] = RangePlan{a_k8, MODE == MODE_WEIGHTS ? 0 : t.n * kd.n8, (uint32_t)SL.k8};
@@ -1039,8 +1103,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
           for (int qq = 0; qq < 3; ++qq)
             if (qq < p) blocks_before += (G.hi[qq] - G.lo[qq] + 31) >> 5;
           blocks_before += t.row0 >> 5;
-          P.info.phase = p | (blocks_before & (FW - 1)) << 8; P.info.n = t.n;
-          P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 | low4(a_v) << 12 |
+          P.info.phase = p | (blocks_before & (FW - 1)) << 8 | (v_tma ? 1 << 16 : (v_any && (p >= V_PAD_FROM || !fast || low4(a_v) != 0u)) ? 1 << 17 : 0); P.info.n = t.n;
+          P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 |
                         (p < 3 ? low4(a_sc) << 16 | low4(a_zp) << 20 : 0u);
           P.info.krow0 = (int)(G.krow[p] + t.row0);
           }
@@ -1052,8 +1116,11 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       RangePlan rp = s_plan[slot].rg[lane < 6 ? lane : 0];
       if (lane >= 6) rp.len = 0;
       const TileInfo ti = s_plan[slot].info;
+      const bool v_tma = (ti.phase >> 16) & 1, v_lanes = (ti.phase >> 17) & 1;   // how the V rows travel (neither: the tail, or none)
       const uintptr_t a = reinterpret_cast<uintptr_t>(rp.src), a0 = a & ~(uintptr_t)15;
-      const uint32_t bytes = rp.len > 0 ? (uint32_t)(((a + rp.len + 15) & ~(uintptr_t)15) - a0) : 0u;   // covering 16-byte blocks
+      uint32_t bytes = rp.len > 0 ? (uint32_t)(((a + rp.len + 15) & ~(uintptr_t)15) - a0) : 0u;   // covering 16-byte blocks
+      if (lane == 0 && v_tma) bytes = (uint32_t)rp.len;    // (the whole box is counted, whatever part of it lies in the tensor)
+      if (lane == 0 && v_lanes) bytes = 0u;
       uint32_t total = bytes;
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
@@ -1064,11 +1131,19 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         // every range is contiguous in its tensor: ONE bulk copy each, completion counted in bytes
         if (lane == 0) mbar_expect_tx(&s_full[stage], total);
         __syncwarp();
+        if (lane == 0 && v_tma) {
+          tma_g2s_2d(sbu + SL.v, rp.src, 0, (int)rp.dst_off, &s_full[stage], pol_stream);
+        } else {
 #if RDKV_L2HINT
-        if (bytes) bulk_g2s_hint(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage], pol_stream);
+          if (bytes) bulk_g2s_hint(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage], pol_stream);
 #else
-        if (bytes) bulk_g2s(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage]);
+          if (bytes) bulk_g2s(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage]);
 #endif
+        }
+        if (v_lanes) {
+          const RangePlan rv = s_plan[slot].rg[0];
+          stage_v_rows_padded(smem_raw + (size_t)stage * stage_bytes + SL.v, rv.src, ti.n, phase_row_bytes(ti.phase & 7), phase_pitch(ti.phase & 7), lane);
+        }
       } else {
         // a range whose covering blocks stick out of its tensor: guarded 16-byte copies by all lanes
         unsigned char* sb = smem_raw + (size_t)stage * stage_bytes;
@@ -1081,6 +1156,10 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
             stage_range_guarded(sb + rk.dst_off, rk.src, rk.len, rk.src, rk.src + rk.len, lane, 32);
             continue;
           }
+          if (k == 0) {                                    // V rows: at the padded pitch
+            stage_v_rows_padded(sb + SL.v, rk.src, ti.n, phase_row_bytes(p), phase_pitch(p), lane);
+            continue;
+          }
           const unsigned char* lo = k == 0 ? (p == 0 ? v.v2 : p == 1 ? v.v4 : p == 2 ? v.v8 : v16b)
                                   : k == 1 ? v.k2 : k == 2 ? v.k4 : k == 3 ? v.k8 : k == 4 ? scb : zpb;
           const int64_t ext = k == 0 ? (p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes)
@@ -1091,9 +1170,9 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
       // rows past the tile's end must hold finite fp16 data in the fp16 phase: clear the
       // rest of the last 32-row block beyond the copied blocks
       if ((ti.phase & 7) >= 3 && (ti.n & 31)) {
-        const int off = (int)((ti.offs >> 12) & 15u);
-        const int first = (off + ti.n * 256 + 15) & ~15;
-        const int last = min(off + ((ti.n + 31) & ~31) * 256, V_STAGE + 16);
+        const int pitch = phase_pitch(ti.phase & 7);       // (the tail's rows: 256 bytes; fp16 V rows: padded)
+        const int first = ti.n * pitch;
+        const int last = min(((ti.n + 31) & ~31) * pitch, V_STAGE);
         unsigned char* sv = smem_raw + (size_t)stage * stage_bytes + SL.v;
         for (int i = first + 4 * lane; i < last; i += 4 * 32) *reinterpret_cast<uint32_t*>(sv + i) = 0u;
       }
@@ -1347,8 +1426,10 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
         G.k4[p] = ptr_of(a1.z, a1.w) + (int64_t)d * kd.sub4;
         G.k8[p] = ptr_of(a2.x, a2.y) + (int64_t)d * kd.n8;
         G.vrow[p] = ptr_of(a2.z, a2.w) + (int64_t)d * phase_row_bytes(p);
+        G.vrow_idx[p] = a0.z >= 0 ? a0.z + d : -1;
         if (p < 3) { G.sc[p] = ptr_of(a3.x, a3.y) + 2 * d; G.zp[p] = ptr_of(a3.z, a3.w) + 2 * d; }
       }
+      if (lane == 0) G.vmaps = ptr_of(h2.z, h2.w);
       __syncwarp();
       const int total = fits ? t0 + t1 + t2 + t3 : 0;
       if (!fits && lane == 0 && status != nullptr) atomicOr(status, 2);
@@ -1369,7 +1450,12 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
             const unsigned char* a_v = G.vrow[tp] + (int64_t)t.row0 * phase_row_bytes(tp);
             const unsigned char* a_sc = G.sc[tp < 3 ? tp : 0] + t.row0 * 2;
             const unsigned char* a_zp = G.zp[tp < 3 ? tp : 0] + t.row0 * 2;
-            P.rg[0] = RangePlan{a_v, t.n * phase_row_bytes(tp), (uint32_t)SL.v};
+            // the V rows: one box of the phase's tensor map (src = the map, len = the box's bytes, dst_off = its
+            // first row) when the table has maps, else copies by the lanes at the padded pitch
+            // (a ragged last fp16 block goes that way too: the rows behind it are cleared)
+            const bool v_tma = tp >= V_PAD_FROM && G.vmaps != nullptr && G.vrow_idx[tp] >= 0 && (tp < 3 || (t.n & 31) == 0);
+            if (v_tma) P.rg[0] = RangePlan{G.vmaps + 128 * tp, phase_tile_rows(tp) * phase_pitch(tp), (uint32_t)(G.vrow_idx[tp] + t.row0)};
+            else P.rg[0] = RangePlan{a_v, t.n * phase_row_bytes(tp), (uint32_t)SL.v};
             P.rg[1] = RangePlan{a_k2, t.n * kd.sub2, (uint32_t)SL.k2};
             P.rg[2] = RangePlan{a_k4, t.n * kd.sub4, (uint32_t)SL.k4};
             P.rg[3] = RangePlan{a_k8, t.n * kd.n8, (uint32_t)SL.k8};
@@ -1381,8 +1467,8 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
             for (int qq = 0; qq < 3; ++qq)
               if (qq < tp) blocks_before += (G.hi[qq] - G.lo[qq] + 31) >> 5;
             blocks_before += t.row0 >> 5;
-            P.info.phase = tp | (blocks_before & (FW - 1)) << 8; P.info.n = t.n;
-            P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 | low4(a_v) << 12 |
+            P.info.phase = tp | (blocks_before & (FW - 1)) << 8 | (v_tma ? 1 << 16 : (tp >= V_PAD_FROM || low4(a_v) != 0u) ? 1 << 17 : 0); P.info.n = t.n;
+            P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 |
                           (tp < 3 ? low4(a_sc) << 16 | low4(a_zp) << 20 : 0u);
             P.info.krow0 = (int)(G.krow[tp] + t.row0);
           }
@@ -1406,8 +1492,11 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
           rp.src = reinterpret_cast<const unsigned char*>(kslots + unit * nkb_max * 32);
           rp.len = nkb_max * 32 * (int)sizeof(KSlotRec); dst = smem_u32(hdr + hdr_q_bytes);
         }
+        const bool v_tma = (ti.phase >> 16) & 1, v_lanes = (ti.phase >> 17) & 1;   // how the V rows travel
         const uintptr_t a = reinterpret_cast<uintptr_t>(rp.src), al = a & ~(uintptr_t)15;
-        const uint32_t bytes = rp.len > 0 ? (uint32_t)(((a + rp.len + 15) & ~(uintptr_t)15) - al) : 0u;
+        uint32_t bytes = rp.len > 0 ? (uint32_t)(((a + rp.len + 15) & ~(uintptr_t)15) - al) : 0u;
+        if (lane == 0 && v_tma) bytes = (uint32_t)rp.len;  // (the whole box is counted, whatever part of it lies in the tensor)
+        if (lane == 0 && v_lanes) bytes = 0u;
         uint32_t tx = bytes;
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
@@ -1423,11 +1512,15 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
         }
         if (lane == 0) mbar_expect_tx(&s_full[stage], tx);
         __syncwarp();
-        if (bytes) bulk_g2s_hint(dst, reinterpret_cast<const void*>(al), bytes, &s_full[stage], pol_stream);
+        if (lane == 0 && v_tma) tma_g2s_2d(sbu + SL.v, rp.src, 0, (int)rp.dst_off, &s_full[stage], pol_stream);
+        else if (bytes) bulk_g2s_hint(dst, reinterpret_cast<const void*>(al), bytes, &s_full[stage], pol_stream);
+        if (v_lanes) {
+          const RangePlan rv = s_plan[slot].rg[0];
+          stage_v_rows_padded(smem_raw + (size_t)stage * stage_bytes + SL.v, rv.src, ti.n, phase_row_bytes(ti.phase & 3), phase_pitch(ti.phase & 3), lane);
+        }
         if ((ti.phase & 3) == 3 && (ti.n & 31)) {          // fp16 phase: finite data past the tile's end
-          const int off = (int)((ti.offs >> 12) & 15u);
-          const int first = (off + ti.n * 256 + 15) & ~15;
-          const int last = min(off + ((ti.n + 31) & ~31) * 256, V_STAGE + 16);
+          const int first = ti.n * phase_pitch(3);
+          const int last = min(((ti.n + 31) & ~31) * phase_pitch(3), V_STAGE);
           unsigned char* sv = smem_raw + (size_t)stage * stage_bytes + SL.v;
           for (int i = first + 4 * lane; i < last; i += 4 * 32) *reinterpret_cast<uint32_t*>(sv + i) = 0u;
         }
@@ -1579,7 +1672,7 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
 
 using namespace rdkv;
 
-extern "C" int rdkv_decode_stage_bytes(int k_row_bytes_max) { return stage_capacity(k_row_bytes_max); }
+extern "C" int rdkv_decode_stage_bytes(int k_row_bytes_max) { return align128i(stage_capacity(k_row_bytes_max)); }
 
 // Prepared table of a set of views: per (view, KV head) a UnitRec (row counts, whole-head
 // alignment flag) and the K slot quadruples in the order the fused kernel's threads consume them.
@@ -1589,7 +1682,7 @@ extern "C" int rdkv_decode_stage_bytes(int k_row_bytes_max) { return stage_capac
 // round trip and the slot arithmetic is redone by every CTA.  One block per unit.
 __global__ void __launch_bounds__(128)
 decode_prepare_kernel(const rdkv_layer_view* __restrict__ views, int H_kv, int nkb_max,
-                      UnitRec* __restrict__ recs, KSlotRec* __restrict__ kslots) {
+                      UnitRec* __restrict__ recs, KSlotRec* __restrict__ kslots, const unsigned char* __restrict__ v_maps) {
   const int64_t unit = blockIdx.x;
   const rdkv_layer_view& v = views[unit / H_kv];
   const int h = (int)(unit % H_kv);
@@ -1647,12 +1740,22 @@ decode_prepare_kernel(const rdkv_layer_view* __restrict__ views, int H_kv, int n
           fast = fast && blocks_inside(gzp, gzp + n * 2, zpb, zpb + v.v_meta_bytes);
         }
       }
-      u.ph[p].b_lo = lo; u.ph[p].b_hi = hi; u.ph[p].pad0 = 0; u.ph[p].pad1 = 0;
+      // row lo's number in the phase's tensor map (a map whose first 16 bytes are zero was not encoded)
+      int v_row = -1;
+      if (v_maps != nullptr && vb != nullptr && n > 0) {
+        const int4 m0 = *reinterpret_cast<const int4*>(v_maps + ((unit / H_kv) * 4 + p) * 128);
+        const int64_t delta = vb - vlo;
+        const int rb = phase_row_bytes(p);
+        if ((m0.x | m0.y | m0.z | m0.w) != 0 && delta >= 0 && delta % rb == 0 && delta / rb + n < 0x7fffffffLL) v_row = (int)(delta / rb);
+      }
+      u.ph[p].b_lo = lo; u.ph[p].b_hi = hi; u.ph[p].v_row = v_row; u.ph[p].pad1 = 0;
       u.ph[p].k2 = a2; u.ph[p].k4 = a4; u.ph[p].k8 = a8; u.ph[p].vrow = vb; u.ph[p].sc = gsc; u.ph[p].zp = gzp;
     }
     u.n2 = hc.n2; u.n4 = hc.n4; u.n8 = hc.n8; u.n16 = hc.n16;
     u.flags = fast ? 1 : 0; u.nkb = kd.nkb; u.n_ch2_pad = kd.n2p; u.n_ch4_pad = kd.n4p;
-    u.n_ch8 = kd.n8; u.max_t_v = v.max_t_v; u.pad0 = 0; u.pad1 = 0;
+    u.n_ch8 = kd.n8; u.max_t_v = v.max_t_v;
+    const uintptr_t vm = v_maps != nullptr ? reinterpret_cast<uintptr_t>(v_maps + (unit / H_kv) * 4 * 128) : 0;
+    u.vmaps_lo = (unsigned)(vm & 0xFFFFFFFFu); u.vmaps_hi = (unsigned)(vm >> 32);
     recs[unit] = u;
   }
 }
@@ -1675,7 +1778,7 @@ static int launch_fused(const rdkv_layer_view* views, int n_views, const void* q
   if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(partials) & 15) ||
       (reinterpret_cast<uintptr_t>(merged) & 15))
     return RDKV_ERR_BAD_ARG;
-  const int stage_bytes = align16i(stage_capacity(k_row_bytes_max));
+  const int stage_bytes = align128i(stage_capacity(k_row_bytes_max));   // (a tile's V box lands on a 128-byte boundary)
   size_t smem = (size_t)FSTAGES * stage_bytes + TAIL_BYTES + (MODE == MODE_ATTN_TAIL ? TAIL_EXTRA_BYTES : 0);
   const size_t epilogue = (size_t)FW * GH * D * sizeof(float);
   if (smem < epilogue) smem = epilogue;
@@ -1721,16 +1824,73 @@ extern "C" int64_t rdkv_decode_prepared_bytes(int64_t n_units, int nkb_max, int 
   return which == 0 ? n_units * (int64_t)sizeof(UnitRec) : n_units * nkb_max * 32 * (int64_t)sizeof(KSlotRec);
 }
 
+// The driver's tensor-map encoder, found through the runtime (the library does not link the driver).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn v_map_encoder() {
+  static const EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) != cudaSuccess ||
+        res != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return (EncodeTiledFn) nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+extern "C" int64_t rdkv_decode_v_map_bytes(int n_views) { return n_views < 0 ? -1 : (int64_t)n_views * 4 * (int64_t)sizeof(CUtensorMap); }
+
+extern "C" int rdkv_decode_encode_v_maps(const rdkv_layer_view* views_host, int n_views, void* maps_host) {
+  static_assert(sizeof(CUtensorMap) == 128, "a tensor map is 128 bytes");
+  if (views_host == nullptr || maps_host == nullptr || n_views < 0) return -1;
+  memset(maps_host, 0, (size_t)n_views * 4 * sizeof(CUtensorMap));
+  EncodeTiledFn enc = v_map_encoder();
+  if (enc == nullptr) return 0;
+  int done = 0;
+  for (int i = 0; i < n_views; ++i) {
+    const rdkv_layer_view& v = views_host[i];
+    for (int p = 0; p < 4; ++p) {
+      const void* base = p == 0 ? (const void*)v.v2 : p == 1 ? (const void*)v.v4 : p == 2 ? (const void*)v.v8 : (const void*)v.v16;
+      const int64_t bytes = p == 0 ? v.v2_bytes : p == 1 ? v.v4_bytes : p == 2 ? v.v8_bytes : v.v16_bytes;
+      const int rb = phase_row_bytes(p);
+      if (base == nullptr || bytes < rb || (reinterpret_cast<uintptr_t>(base) & 15) != 0) continue;
+      const int64_t rows = bytes / rb;
+      if (rows > 0x7fffffffLL) continue;
+      // the tensor as rows of rb bytes (fp16 rows as 128 16-bit elements: a box is at most 256 elements wide);
+      // the box is one tile of rows, V_PAD bytes wider than a row: the excess arrives as zeros and
+      // spaces the rows in shared memory
+      CUtensorMap* tm = reinterpret_cast<CUtensorMap*>(maps_host) + (size_t)i * 4 + p;
+      const int es = p == 3 ? 2 : 1;
+      const cuuint64_t dims[2] = {(cuuint64_t)(rb / es), (cuuint64_t)rows};
+      const cuuint64_t strides[1] = {(cuuint64_t)rb};
+      const cuuint32_t box[2] = {(cuuint32_t)(phase_pitch(p) / es), (cuuint32_t)phase_tile_rows(p)};
+      const cuuint32_t elem[2] = {1u, 1u};
+      const CUresult r = enc(tm, p == 3 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base),
+                             dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) memset(tm, 0, sizeof(CUtensorMap));
+      else ++done;
+    }
+  }
+  return done;
+}
+
 extern "C" int rdkv_decode_prepare(const rdkv_layer_view* views, int n_views, int H_kv, int nkb_max, void* unit_recs,
-                                   void* k_slots, void* stream) {
+                                   void* k_slots, const void* v_maps, void* stream) {
   if (views == nullptr || unit_recs == nullptr || k_slots == nullptr || n_views < 0 || H_kv <= 0) return RDKV_ERR_BAD_ARG;
   if (nkb_max <= 0 || nkb_max > KB_MAX) return RDKV_ERR_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(unit_recs) & 15) || (reinterpret_cast<uintptr_t>(k_slots) & 15)) return RDKV_ERR_BAD_ARG;
   const int64_t n = (int64_t)n_views * H_kv;
   if (n == 0) return RDKV_OK;
   if (n > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
+  if (reinterpret_cast<uintptr_t>(v_maps) & 63) return RDKV_ERR_BAD_ARG;
   decode_prepare_kernel<<<(unsigned)n, 128, 0, (cudaStream_t)stream>>>(
-      views, H_kv, nkb_max, reinterpret_cast<UnitRec*>(unit_recs), reinterpret_cast<KSlotRec*>(k_slots));
+      views, H_kv, nkb_max, reinterpret_cast<UnitRec*>(unit_recs), reinterpret_cast<KSlotRec*>(k_slots),
+      reinterpret_cast<const unsigned char*>(v_maps));
   return launch_status();
 }
 
@@ -1863,7 +2023,7 @@ extern "C" int rdkv_decode_attn_persistent(const rdkv_layer_view* views, int n_v
   if (n_whole_units < 0 || n_whole_units > units) return RDKV_ERR_BAD_ARG;
   const int64_t items = n_whole_units + (units - n_whole_units) * n_chunks;
   if (items > 0x7fffffffLL) return RDKV_ERR_TOO_LARGE;
-  const int stage_bytes = align16i(stage_capacity(k_row_bytes_max));
+  const int stage_bytes = align128i(stage_capacity(k_row_bytes_max));   // (a tile's V box lands on a 128-byte boundary)
   const int q_elt = q_dtype == RDKV_F32 ? 4 : 2;
   size_t smem = (size_t)FSTAGES * stage_bytes + (size_t)nkb_max * 256 +
                 2 * ((size_t)GH * D * q_elt + (size_t)nkb_max * 32 * sizeof(KSlotRec));

@@ -78,6 +78,14 @@ class DecodeTable:
         raw = bytes(views)
         host = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
         self.views = host.to(self.device)
+        # tensor maps of the views' V tensors (encoded on the host from the records above; the kernel's
+        # staging warp brings a tile's V rows in with one tiled TMA box each where a map exists)
+        with torch.cuda.device(self.device):
+            maps_host = torch.zeros(int(lib().rdkv_decode_v_map_bytes(self.n_views)), dtype=torch.uint8)
+            self.n_v_maps = int(lib().rdkv_decode_encode_v_maps(host.data_ptr(), self.n_views, maps_host.data_ptr()))
+        if self.n_v_maps < 0:
+            raise RuntimeError("rdkv_decode_encode_v_maps failed")
+        self.v_maps = maps_host.to(self.device) if self.n_v_maps > 0 else None
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # snapshot of every head's row counts (one round trip less in the kernel's prologue) and the
         # arrival counters of chunked units (zero between launches)
@@ -134,6 +142,7 @@ class DecodeTable:
         with torch.cuda.device(self.device):
             check(lib().rdkv_decode_prepare(self.views.data_ptr(), self.n_views, self.H_kv, self.nkb_max,
                                             self.unit_recs.data_ptr(), self.k_slots.data_ptr(),
+                                            self.v_maps.data_ptr() if self.v_maps is not None else None,
                                             stream_ptr(self.device)), "rdkv_decode_prepare")
 
     def plan(self, n_views: int, rows: Optional[int] = None):
