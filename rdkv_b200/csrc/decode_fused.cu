@@ -78,7 +78,11 @@ __host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : 
 #ifndef RDKV_V_PAD_FROM
 #define RDKV_V_PAD_FROM 2
 #endif
-constexpr int V_PAD_FROM = RDKV_V_PAD_FROM;        // first V phase whose rows are spaced (the phases before it lie end to end)
+// First V phase whose rows are spaced: the 8-bit rows (128 bytes) and the fp16 rows (256 bytes), whose
+// loads are 32 per 32-row block and conflict four ways when the rows lie end to end.  The 2-bit and
+// 4-bit rows (8 and 16 loads per block) stay dense: as 48- and 80-byte box rows they travel more
+// slowly than in one bulk copy (measured: spacing all four phases is slower than spacing none).
+constexpr int V_PAD_FROM = RDKV_V_PAD_FROM;
 __host__ __device__ constexpr int phase_pitch(int p) {
   return (p == 4 || p < V_PAD_FROM) ? phase_row_bytes(p) : phase_row_bytes(p) + V_PAD;
 }
@@ -152,6 +156,22 @@ __device__ __forceinline__ void tma_g2s_2d(uint32_t dst, const void* map, int x,
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(pol)
                : "memory");
+}
+// The two copies as predicated instructions: a warp whose lanes issue different kinds of copy (or
+// none) stays on one straight path.
+__device__ __forceinline__ void bulk_g2s_hint_if(bool on, uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %5, 0;\n"
+      " @p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n}\n"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol), "r"((uint32_t)on)
+      : "memory");
+}
+__device__ __forceinline__ void tma_g2s_2d_if(bool on, uint32_t dst, const void* map, int x, int y, uint64_t* bar, uint64_t pol) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %6, 0;\n"
+      " @p cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;\n}\n"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(pol), "r"((uint32_t)on)
+      : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_on_copies(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -1131,13 +1151,13 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
         // every range is contiguous in its tensor: ONE bulk copy each, completion counted in bytes
         if (lane == 0) mbar_expect_tx(&s_full[stage], total);
         __syncwarp();
-        if (lane == 0 && v_tma) {
-          tma_g2s_2d(sbu + SL.v, rp.src, 0, (int)rp.dst_off, &s_full[stage], pol_stream);
-        } else {
+        {
+          const bool by_map = lane == 0 && v_tma;
+          tma_g2s_2d_if(by_map, sbu + SL.v, rp.src, 0, (int)rp.dst_off, &s_full[stage], pol_stream);
 #if RDKV_L2HINT
-          if (bytes) bulk_g2s_hint(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage], pol_stream);
+          bulk_g2s_hint_if(bytes != 0u && !by_map, sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage], pol_stream);
 #else
-          if (bytes) bulk_g2s(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage]);
+          if (bytes != 0u && !by_map) bulk_g2s(sbu + rp.dst_off, reinterpret_cast<const void*>(a0), bytes, &s_full[stage]);
 #endif
         }
         if (v_lanes) {
@@ -1399,7 +1419,7 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
       const int n2p = h1.z, n4p = h1.w, n8c = h2.x;
       const KDims kd = k_dims(n2p, n4p, n8c);
       const StageLayout SL = stage_layout(kd.sub2, kd.sub4, kd.n8);
-      const bool fits = (h1.x & 1) && SL.total <= stage_bytes && kd.n2p + kd.n4p + kd.n8 > 0 &&
+      const bool fits = (h1.x & 3) == 3 && SL.total <= stage_bytes && kd.n2p + kd.n4p + kd.n8 > 0 &&
                         kd.n2p + kd.n4p + kd.n8 <= DPAD_MAX && kd.nkb <= KB_MAX && kd.nkb <= nkb_max;
       const int c0 = row_begin + chunk * chunk_rows, c1 = n_chunks == 1 ? row_end : min(c0 + chunk_rows, row_end);
       const int np = a0.y - a0.x, ps = part_cut(np, part, parts), pn = part_cut(np, part + 1, parts) - ps;
@@ -1467,7 +1487,7 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
             for (int qq = 0; qq < 3; ++qq)
               if (qq < tp) blocks_before += (G.hi[qq] - G.lo[qq] + 31) >> 5;
             blocks_before += t.row0 >> 5;
-            P.info.phase = tp | (blocks_before & (FW - 1)) << 8 | (v_tma ? 1 << 16 : (tp >= V_PAD_FROM || low4(a_v) != 0u) ? 1 << 17 : 0); P.info.n = t.n;
+            P.info.phase = tp | (blocks_before & (FW - 1)) << 8 | (v_tma ? 1 << 16 : tp >= V_PAD_FROM ? 1 << 17 : 0); P.info.n = t.n;
             P.info.offs = low4(a_k2) | low4(a_k4) << 4 | low4(a_k8) << 8 |
                           (tp < 3 ? low4(a_sc) << 16 | low4(a_zp) << 20 : 0u);
             P.info.krow0 = (int)(G.krow[tp] + t.row0);
@@ -1512,11 +1532,16 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
         }
         if (lane == 0) mbar_expect_tx(&s_full[stage], tx);
         __syncwarp();
-        if (lane == 0 && v_tma) tma_g2s_2d(sbu + SL.v, rp.src, 0, (int)rp.dst_off, &s_full[stage], pol_stream);
-        else if (bytes) bulk_g2s_hint(dst, reinterpret_cast<const void*>(al), bytes, &s_full[stage], pol_stream);
-        if (v_lanes) {
-          const RangePlan rv = s_plan[slot].rg[0];
-          stage_v_rows_padded(smem_raw + (size_t)stage * stage_bytes + SL.v, rv.src, ti.n, phase_row_bytes(ti.phase & 3), phase_pitch(ti.phase & 3), lane);
+        {
+          const bool by_map = lane == 0 && v_tma;
+          tma_g2s_2d_if(by_map, sbu + SL.v, rp.src, 0, (int)rp.dst_off, &s_full[stage], pol_stream);
+          bulk_g2s_hint_if(bytes != 0u && !by_map, dst, reinterpret_cast<const void*>(al), bytes, &s_full[stage], pol_stream);
+        }
+        if (v_lanes) {                                     // (here: a ragged last fp16 block; 16-byte aligned rows of 256 bytes)
+          const unsigned char* vsrc = s_plan[slot].rg[0].src;
+          const uint32_t vdst = sbu + SL.v;
+#pragma unroll 1
+          for (int b = lane; b < ti.n * 16; b += 32) cp16(vdst + (b >> 4) * phase_pitch(3) + 16 * (b & 15), vsrc + 16 * b);
         }
         if ((ti.phase & 3) == 3 && (ti.n & 31)) {          // fp16 phase: finite data past the tile's end
           const int first = ti.n * phase_pitch(3);
@@ -1711,7 +1736,7 @@ decode_prepare_kernel(const rdkv_layer_view* __restrict__ views, int H_kv, int n
   }
   if (threadIdx.x == 0) {
     const HeadCounts hc = head_counts(v, h);
-    bool fast = true;
+    bool fast = true, mapped = true;                      // mapped: the V rows of every spaced-out phase can come through a tensor map
     UnitRec u;
     for (int p = 0; p < 4; ++p) {                          // the whole head, phase by phase (as the kernel's geometry does per chunk)
       const int lo = p == 0 ? 0 : p == 1 ? hc.n2 : p == 2 ? hc.n2 + hc.n4 : hc.t_v;
@@ -1748,11 +1773,12 @@ decode_prepare_kernel(const rdkv_layer_view* __restrict__ views, int H_kv, int n
         const int rb = phase_row_bytes(p);
         if ((m0.x | m0.y | m0.z | m0.w) != 0 && delta >= 0 && delta % rb == 0 && delta / rb + n < 0x7fffffffLL) v_row = (int)(delta / rb);
       }
+      if (n > 0 && p >= V_PAD_FROM && v_row < 0) mapped = false;
       u.ph[p].b_lo = lo; u.ph[p].b_hi = hi; u.ph[p].v_row = v_row; u.ph[p].pad1 = 0;
       u.ph[p].k2 = a2; u.ph[p].k4 = a4; u.ph[p].k8 = a8; u.ph[p].vrow = vb; u.ph[p].sc = gsc; u.ph[p].zp = gzp;
     }
     u.n2 = hc.n2; u.n4 = hc.n4; u.n8 = hc.n8; u.n16 = hc.n16;
-    u.flags = fast ? 1 : 0; u.nkb = kd.nkb; u.n_ch2_pad = kd.n2p; u.n_ch4_pad = kd.n4p;
+    u.flags = (fast ? 1 : 0) | (fast && mapped ? 2 : 0); u.nkb = kd.nkb; u.n_ch2_pad = kd.n2p; u.n_ch4_pad = kd.n4p;
     u.n_ch8 = kd.n8; u.max_t_v = v.max_t_v;
     const uintptr_t vm = v_maps != nullptr ? reinterpret_cast<uintptr_t>(v_maps + (unit / H_kv) * 4 * 128) : 0;
     u.vmaps_lo = (unsigned)(vm & 0xFFFFFFFFu); u.vmaps_hi = (unsigned)(vm >> 32);

@@ -110,7 +110,7 @@ class DecodeTable:
         self._all_fast = False
         if not self.live_counts:
             recs = self.unit_recs.view(torch.int32).view(n_units, self._unit_rec_bytes // 4)
-            self._all_fast = bool((recs[:, 4] & 1).all().item())
+            self._all_fast = bool(((recs[:, 4] & 3) == 3).all().item())   # (bit 1: the V rows come through tensor maps)
 
     CTAS_PER_SM = 3                      # resident CTAs of the fused kernel per SM
     WORK_CTR_SLOTS = 64                  # launches of one table that may overlap (view ranges on streams of their own)
