@@ -43,7 +43,7 @@ METRIC = "packed-KV decode-attn tokens/s"
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one fused-kernel launch in
 # the committed ncu capture (profiles/; an 8-layer launch); traffic grows with the units processed,
 # so the ratio carries over to the full launch.
-NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = 1.028
+NCU_TRAFFIC_BYTES_PER_ALGO_BYTE = 1.025
 # dram__bytes_read.sum + dram__bytes_write.sum of the packing launches of one config-1 step in the
 # committed ncu launch list (profiles/; a one-pass capture of the full workload)
 PACK_NCU_TRAFFIC_BYTES = 664.9e6
