@@ -16,6 +16,7 @@
 // obkv_accel/triton_k_kernel.py:14-16) and sum_t p*scale*zp per head (V side).
 #include <cuda.h>   // CUtensorMap (the V tiles arrive through tensor maps; the encoder is looked up through the runtime)
 
+#include <algorithm>
 #include <cstring>
 #include <type_traits>
 
@@ -648,7 +649,10 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   const uint32_t smem0 = smem_u32(smem_raw);
   const uint32_t qs_base = smem0 + FSTAGES * stage_bytes;  // uint2 qsA[nkb][32]
   unsigned char* tail = smem_raw + (size_t)FSTAGES * stage_bytes;
-  const int qs_bytes = QS_BYTES;
+  // (a launch with a prepared table knows the largest number of K blocks of its views: the folded
+  // queries take that many blocks of 256 bytes, not the 24 a view may have at most)
+  const int qs_bytes = (nkb_max > 0 ? min(nkb_max, KB_MAX) : KB_MAX) * 256;
+  const int tail_bytes = qs_bytes + FOLD_Q_BYTES + FOLD_META_BYTES;
   uint2* qsA = reinterpret_cast<uint2*>(tail);
   float* f_q = reinterpret_cast<float*>(tail + qs_bytes);                   // [gcnt][128] query rows as fp32
   uint16_t* f_sc = reinterpret_cast<uint16_t*>(tail + qs_bytes + FOLD_Q_BYTES);   // [d_pad] K scales (fp16 bits; launches without a prepared table)
@@ -900,8 +904,8 @@ decode_fused_kernel(const rdkv_layer_view* __restrict__ views, const void* __res
   //    itself then gathers from shared memory only. ──
   // ── tail mode: rotary embedding of the query rows, the queries as fragments of the tail's score
   //    product, and the token being decoded (its key row rotated, scored, appended to the tail) ──
-  uint2* qtA = reinterpret_cast<uint2*>(tail + TAIL_BYTES);                  // [8][32]
-  float* f_kc = reinterpret_cast<float*>(tail + TAIL_BYTES + TAILQ_BYTES);   // [128] new key row (rotated, rounded to the tail's type)
+  uint2* qtA = reinterpret_cast<uint2*>(tail + tail_bytes);                  // [8][32]
+  float* f_kc = reinterpret_cast<float*>(tail + tail_bytes + TAILQ_BYTES);   // [128] new key row (rotated, rounded to the tail's type)
   float* f_vc = f_kc + D;                                                    // [128] new value row
   float* s_cur = f_vc + D;                                                   // [GH] the new token's scores, base-2 units
   const bool seeded = TAIL && ta.k_cur != nullptr && chunk == 0 && part == 0;
@@ -1805,7 +1809,9 @@ static int launch_fused(const rdkv_layer_view* views, int n_views, const void* q
       (reinterpret_cast<uintptr_t>(merged) & 15))
     return RDKV_ERR_BAD_ARG;
   const int stage_bytes = align128i(stage_capacity(k_row_bytes_max));   // (a tile's V box lands on a 128-byte boundary)
-  size_t smem = (size_t)FSTAGES * stage_bytes + TAIL_BYTES + (MODE == MODE_ATTN_TAIL ? TAIL_EXTRA_BYTES : 0);
+  const int qs_bytes = (nkb_max > 0 ? std::min(nkb_max, KB_MAX) : KB_MAX) * 256;   // (as the kernel lays it out)
+  size_t smem = (size_t)FSTAGES * stage_bytes + qs_bytes + FOLD_Q_BYTES + FOLD_META_BYTES +
+                (MODE == MODE_ATTN_TAIL ? TAIL_EXTRA_BYTES : 0);
   const size_t epilogue = (size_t)FW * GH * D * sizeof(float);
   if (smem < epilogue) smem = epilogue;
   if (smem > 227 * 1024) return RDKV_ERR_TOO_LARGE;
