@@ -328,6 +328,37 @@ def test_persistent_form_equals_the_one_item_form():
             assert int(per.unit_ctr.abs().sum().item()) == 0
 
 
+def test_v_rows_through_tensor_maps_equal_the_lane_copies():
+    """The 8-bit and fp16 V rows of a tile reach shared memory as one tiled TMA box where the table
+    has tensor maps, and by 16-byte copies of the staging warp at the same pitch where it has none:
+    both ways, in both kernel forms, give the same bits (ragged heads, heads without rows)."""
+    from rdkv_b200 import synth
+    from rdkv_b200.decode import DecodeTable, packed_decode_attention
+    from rdkv_b200.packing import pack_kv
+    H_kv, g, T = 4, 4, 2048
+    layers, nvs = [], []
+    for i, ragged in enumerate((None, [700, 64, 0, 333], [17, 1024, 256, 1], [0, 0, 480, 480])):
+        seed = synth.unit_seed(11, i, 3)
+        K, V = synth.make_kv(H_kv, T, seed=seed)
+        vb = synth.make_v_bits(H_kv, T, 1024, seed=seed, per_head_N=ragged)
+        kb = synth.make_k_bits(H_kv, seed=seed)
+        pl, nv = pack_kv(K.cuda(), V.cuda(), vb.cuda(), kb.cuda(), g, build_mask=False)
+        layers.append(pl); nvs.append(nv)
+    q = synth.make_q(H_kv * g, seed=5, batch=len(layers), dtype=torch.float16).cuda()
+    for persistent in (False, True):
+        mapped = DecodeTable(layers, nvs, H_kv * g, persistent=persistent)
+        assert mapped.n_v_maps > 0 and mapped._all_fast
+        want = packed_decode_attention(q, mapped)
+        plain = DecodeTable(layers, nvs, H_kv * g, persistent=False)
+        plain.v_maps = None                                   # a table without maps: rows by lane copies
+        plain.refresh()
+        recs = plain.unit_recs.view(torch.int32).view(-1, plain._unit_rec_bytes // 4)
+        assert int((recs[:, 4] & 2).sum().item()) == 0 or int(recs[:, 14::16].max().item()) < 0
+        got = packed_decode_attention(q, plain)
+        assert torch.equal(want, got), (persistent, float((want - got).abs().max()))
+        mapped.check_status(); plain.check_status()
+
+
 def test_cached_views_follow_reassigned_fields_and_counts_rewritten_in_place():
     """The one-view tables that the layer-level operators cache on the layer object are keyed by the
     identity of every tensor they point into: a field that is re-assigned (another packing of the
