@@ -2,8 +2,10 @@
 //
 // One CTA = (view, KV head, chunk of live rows), 160 threads.  Warp 4 (the staging warp) works out
 // the CTA's geometry, plans its tiles (up to 256 rows: six contiguous byte ranges each) and streams
-// them into a 2-slot shared-memory ring with one bulk copy per range, completion counted on an
-// mbarrier.  Warps 0-3 (the compute warps) fold the queries meanwhile and then work through the
+// them into a 2-slot shared-memory ring with one bulk copy per range — the 8-bit and fp16 V rows as
+// one tiled TMA box through a tensor map of the view's V tensor, 16 bytes wider than a row, so that
+// the rows land at a pitch at which the P.V operand loads have no bank conflicts — completion
+// counted on an mbarrier.  Warps 0-3 (the compute warps) fold the queries meanwhile and then work through the
 // tiles, 32 rows (two 16-row MMA groups) per warp and step:
 //   * q.K scores on the tensor cores (mma.sync m16n8k16, rows on M, query heads on N): packed
 //     2/4/8-bit K codes are masked in place into fp16 SUBNORMAL integers (code * 2^-24, exact), so
