@@ -34,7 +34,9 @@ def test_struct_layout_and_version():
     assert lib.rdkv_sizeof_tail_args() == ctypes.sizeof(_lib.TailArgs)
     assert lib.rdkv_last_error_string(0) == b"ok"
     assert b"argument" in lib.rdkv_last_error_string(1)
-    assert lib.rdkv_decode_stage_bytes(34) >= 4096 + 64 * 34
+    assert lib.rdkv_decode_stage_bytes(34) >= 4096 + 64 * 34 and lib.rdkv_decode_stage_bytes(34) % 128 == 0
+    assert lib.rdkv_decode_v_map_bytes(3) == 3 * 4 * 128 and lib.rdkv_decode_v_map_bytes(-1) == -1
+    assert lib.rdkv_decode_encode_v_maps(None, 1, None) == -1
     assert lib.rdkv_pack_k_slabs(1) == 2 and lib.rdkv_pack_k_slabs(10 ** 6) <= 65   # slabs + the block of final parameters
     assert lib.rdkv_sizeof_pack_job() == ctypes.sizeof(_lib.PackJob)
 
