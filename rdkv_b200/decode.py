@@ -30,6 +30,9 @@ class DecodeTable:
     zero points and channel permutation are read from a snapshot the table keeps on the
     device: call :meth:`refresh` after rewriting those in place (or build the table with
     ``live_counts=True``, which makes every CTA read the layers' own tensors for them).
+    The table also keeps tensor maps of the layers' V tensors (their addresses and extents as of
+    construction), through which the kernel stages the 8-bit and fp16 rows of a tile: rewriting
+    payloads in place is fine, a V tensor that moves or grows needs a new table.
     """
 
     def __init__(self, layers: Sequence[PackedKVLayer], new_v_only: Sequence[Optional[Tensor]], H_q: int,
