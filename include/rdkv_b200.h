@@ -304,7 +304,9 @@ int rdkv_lse_combine(const float* partials, int64_t n_rows, int n_splits, int64_
  * 240-256).  bits: [n_rows][len] integers of elem_size bytes (1,2,4,8).
  * mode 0 (tokens): classes 2,4,8,16 ; mode 1 (channels): 16 counts as 8, classes 2,4,8.
  * order[row][j]: source index of the j-th kept element in class order (class 2
- * first ... each class ascending), -1 past the kept count.  counts[row][4]. */
+ * first ... each class ascending), -1 past the kept count.  counts[row][4].
+ * mode + 4: the entries past the kept count are left as they are (a caller that reads the lists
+ * through counts saves the fill: 7/8 of the writes at a budget of 1/8 of the tokens). */
 int rdkv_partition_by_bits(const void* bits, int elem_size, int64_t row_stride, int n_rows, int len,
                            int mode, int32_t* order, int32_t* counts, void* stream);
 

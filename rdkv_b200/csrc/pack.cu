@@ -33,8 +33,9 @@ __device__ __forceinline__ int bit_class(int64_t b, int mode) {
 }
 
 __global__ void __launch_bounds__(PART_THREADS)
-partition_kernel(const void* bits, int elem_size, int64_t row_stride, int len, int mode,
+partition_kernel(const void* bits, int elem_size, int64_t row_stride, int len, int mode_flags,
                  int32_t* order, int32_t* counts) {
+  const int mode = mode_flags & 1;                         // (bit 2 of mode_flags: leave the entries past the kept count alone)
   __shared__ int warp_tot[4][PART_THREADS / 32];
   __shared__ int class_base[5];
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -130,6 +131,7 @@ partition_kernel(const void* bits, int elem_size, int64_t row_stride, int len, i
       if (c >= 0) orow[pos[c]++] = i;
     }
   }
+  if (mode_flags & 4) return;
   const int kept = class_base[4];
   for (int i = kept + tid; i < len; i += PART_THREADS) orow[i] = -1;
 }
@@ -1211,7 +1213,7 @@ extern "C" int rdkv_partition_by_bits(const void* bits, int elem_size, int64_t r
                                       int len, int mode, int32_t* order, int32_t* counts, void* stream) {
   if (bits == nullptr || order == nullptr || counts == nullptr || n_rows < 0 || len < 0) return RDKV_ERR_BAD_ARG;
   if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return RDKV_ERR_BAD_ARG;
-  if (mode != 0 && mode != 1) return RDKV_ERR_BAD_ARG;
+  if ((mode & ~4) != 0 && (mode & ~4) != 1) return RDKV_ERR_BAD_ARG;
   if (n_rows == 0) return RDKV_OK;
   partition_kernel<<<n_rows, PART_THREADS, 0, (cudaStream_t)stream>>>(bits, elem_size, row_stride, len, mode,
                                                                      order, counts);

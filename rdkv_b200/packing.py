@@ -110,11 +110,12 @@ def _as_fp16_rows(x: Tensor, name: str) -> Tensor:
 
 # ── C-ABI wrappers ───────────────────────────────────────────────────────────
 
-def partition_by_bits(bits: Tensor, mode: int) -> Tuple[Tensor, Tensor]:
+def partition_by_bits(bits: Tensor, mode: int, fill: bool = True) -> Tuple[Tensor, Tensor]:
     """Stable class partition of integer bit maps ``[R,L]``.
 
     Returns ``(order int32 [R,L], counts int32 [R,4])``; mode 0 = tokens
-    (classes 2,4,8,16), mode 1 = channels (16 counted as 8).
+    (classes 2,4,8,16), mode 1 = channels (16 counted as 8).  ``fill=False``: the entries of
+    ``order`` past a row's kept count are left uninitialised (for callers that go by ``counts``).
     """
     require_cuda(bits, "bits")
     if bits.dim() != 2:
@@ -127,7 +128,8 @@ def partition_by_bits(bits: Tensor, mode: int) -> Tuple[Tensor, Tensor]:
     order = torch.empty((R, L), dtype=torch.int32, device=bits.device)
     counts = torch.zeros((R, 4), dtype=torch.int32, device=bits.device)
     if R and L:
-        check(lib().rdkv_partition_by_bits(ptr(bits), bits.element_size(), bits.stride(0), R, L, mode,
+        check(lib().rdkv_partition_by_bits(ptr(bits), bits.element_size(), bits.stride(0), R, L,
+                                           mode if fill else mode + 4,
                                            ptr(order), ptr(counts), stream_ptr(bits.device)),
               "rdkv_partition_by_bits")
     return order, counts
@@ -507,8 +509,8 @@ def pack_kv_layers(Ks: Sequence[Tensor], Vs: Sequence[Tensor], v_bits: Tensor, k
     if launch_events is not None:
         pev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
         pev[0].record()
-    tok_order, tok_counts = partition_by_bits(v_bits.reshape(L * H, T), 0)
-    ch_order, ch_counts = partition_by_bits(k_bits.reshape(L * H, D), 1)
+    tok_order, tok_counts = partition_by_bits(v_bits.reshape(L * H, T), 0, fill=False)   # (read through the counts only)
+    ch_order, ch_counts = partition_by_bits(k_bits.reshape(L * H, D), 1, fill=False)
     if launch_events is not None:
         pev[1].record()
         launch_events.append(pev)
