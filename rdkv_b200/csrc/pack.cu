@@ -62,16 +62,28 @@ partition_kernel(const void* bits, int elem_size, int64_t row_stride, int len, i
     uint4 w[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) w[u] = u * 8 < per ? __ldg(src + u) : make_uint4(0u, 0u, 0u, 0u);
+    // 16-bit values without branches: kept = a power of two in [2, 16]; class = log2 - 1 (16 counts as 8
+    // for channel maps); the four class counts (at most 32 each) share one register, 8 bits apiece
+    uint32_t cnt4 = 0u;
+    auto note16 = [&](int k, uint32_t v) {
+      const uint32_t ok = (uint32_t)((v - 2u <= 14u) & ((v & (v - 1u)) == 0u));
+      uint32_t c = (30u - (uint32_t)__clz((int)(v | 1u))) & 3u;
+      if (mode != 0) c = min(c, 2u);
+      cnt4 += ok << (8u * c);
+      m_keep |= ok << k; m_c0 |= (ok & c) << k; m_c1 |= (ok & (c >> 1)) << k;
+    };
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       if (u * 8 >= per) break;
       const uint32_t x[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        note(8 * u + 2 * e, (int16_t)(x[e] & 0xFFFFu));
-        note(8 * u + 2 * e + 1, (int16_t)(x[e] >> 16));
+        note16(8 * u + 2 * e, x[e] & 0xFFFFu);
+        note16(8 * u + 2 * e + 1, x[e] >> 16);
       }
     }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) cnt[c] = (int)((cnt4 >> (8 * c)) & 0xFFu);
   } else if (cached) {
     for (int i = lo; i < hi; ++i) note(i - lo, load_int(bits, elem_size, off + i));
   } else {
