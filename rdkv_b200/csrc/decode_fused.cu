@@ -78,6 +78,9 @@ __host__ __device__ constexpr int phase_row_bytes(int p) { return p == 0 ? 32 : 
 // rows 2j (j = its place in its quad): with rows of 32 .. 256 bytes laid end to end the four rows
 // of a quad would share their banks; 16 bytes more per row puts them 32 bytes apart modulo 128.
 // (The tail's plain rows keep their 256 bytes.)
+#ifndef RDKV_STATIC_ROUNDS
+#define RDKV_STATIC_ROUNDS 1
+#endif
 #ifndef RDKV_V_PAD_FROM
 #define RDKV_V_PAD_FROM 2
 #endif
@@ -1358,6 +1361,12 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
   }
   __syncthreads();
 
+#if RDKV_STATIC_ROUNDS
+#ifndef RDKV_DYN_TAIL
+#define RDKV_DYN_TAIL 2
+#endif
+  const int static_rounds = max(1, n_items / (int)gridDim.x - RDKV_DYN_TAIL);
+#endif
   int git = 0;                                             // tiles this CTA has been through (empty items count one)
   int li = 0;                                              // items this CTA has been through
   int item = blockIdx.x;                                   // staging warp: the item in hand; compute warps: as told with its first tile
@@ -1461,6 +1470,20 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
       if (!fits && lane == 0 && status != nullptr) atomicOr(status, 2);
       const int n_it = max(total, 1);
       const uint64_t pol_stream = l2_policy_stream();
+#if RDKV_STATIC_ROUNDS
+      // the CTA's first rounds of items are dealt out statically (item = CTA + round * CTAs: the CTAs keep
+      // pace while there is plenty of work), so the next item is known now and the lines of its unit
+      // record and K slots can be on their way to L2 while this item's tiles are issued; only the last
+      // round or two are drawn from the counter
+      if (li + 1 < static_rounds) {
+        const int ni = (int)blockIdx.x + (li + 1) * (int)gridDim.x;
+        const int uy = ni < n_whole ? ni : n_whole + (ni - n_whole) / k_chunks;
+        const int64_t nu = (int64_t)(uy / hy) * (H_q / g) + (uy % hy) / n_hgrp;
+        if (lane < 3) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const unsigned char*>(unit_recs + nu) + 128 * lane));
+        else if (lane - 3 < (nkb_max * 32 * (int)sizeof(KSlotRec) + 127) / 128)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const unsigned char*>(kslots + nu * nkb_max * 32) + 128 * (lane - 3)));
+      }
+#endif
 #pragma unroll 1
       for (int it = 0; it < n_it; ++it) {
         const int slot = it % PLAN_TILES;
@@ -1565,7 +1588,12 @@ decode_persist_kernel(const void* __restrict__ q, int q_dtype, int H_q, int g, i
       git += n_it;
       // the next item: drawn now, when this one's tiles are all on their way (the compute warps are
       // still two tiles behind), so that whichever CTA gets through its items first takes the next
+#if RDKV_STATIC_ROUNDS
+      if (li + 1 < static_rounds) next_item = (int)blockIdx.x + (li + 1) * (int)gridDim.x;   // (every lane; no round trip)
+      else if (lane == 0) next_item = atomicAdd(work, 1) + static_rounds * (int)gridDim.x;
+#else
       if (lane == 0) next_item = atomicAdd(work, 1) + (int)gridDim.x;
+#endif
       item = __shfl_sync(0xffffffffu, next_item, 0);
     } else {
       // ── compute warps ──
