@@ -611,8 +611,8 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
     """Host-buffer form of :func:`packed_decode_attention`: ``q_host`` [n_views,H_q,128]
     (fp16/bf16/fp32) and ``out_host`` [n_views,H_q,128] fp32 live in host memory.
 
-    The views are cut into ``slices`` ranges (default: sized by the waves of CTAs the table
-    fills, the first ranges short); every range uploads its queries and runs the
+    The views are cut into ``slices`` ranges (default: one or two, by the waves of CTAs the table
+    fills); every range uploads its queries and runs the
     kernel on a stream of its own, so the upload of one range overlaps the kernel of another.
     With a pinned ``out_host`` the kernels write their results straight into it (pinned host
     memory is addressable from the device), so the results cross the bus while the kernels
@@ -651,9 +651,11 @@ def packed_decode_attention_host(q_host: Tensor, table: DecodeTable, out_host: T
     waves = (table.n_views * table.H_kv * table._n_hgrp) // (table._sms * table.CTAS_PER_SM)
     if slices is None:
         # measured best.  Stream form: two ranges when each is at least a full wave of CTAs (the
-        # host's per-range work is in the way of more).  Graph form: eight ranges for a table of
-        # many waves, two for one of at least one wave.
-        slices = ((8 if waves >= 8 else 2 if waves >= 1 else 1) if use_graph else (2 if waves >= 2 else 1))
+        # host's per-range work is in the way of more).  Graph form: two ranges for a table of one
+        # to three waves; ONE for a larger table, whose kernel then reads its queries from the pinned
+        # buffer itself (in_place) and writes its results into the other: a launch of many waves deals
+        # most of its items out statically, which cutting it into ranges would undo.
+        slices = ((2 if 1 <= waves <= 3 else 1) if use_graph else (2 if waves >= 2 else 1))
     growing = False if growing is None else bool(growing)  # ranges of 1 : 2 : 4 : ... instead of equal ones
     n_slices = max(1, min(int(slices), table.n_views))
     if io is None or io.key != (q_host.dtype, n_slices, growing):
